@@ -1,0 +1,83 @@
+"""ctypes binding of libillatio_b200.so -- the same C ABI a Lisp host binds.
+
+There is no fallback: if the library is missing or a call fails, an exception
+is raised.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libillatio_b200.so")
+
+_c = ctypes
+_P = _c.c_uint64   # ill_dptr
+_S = _c.c_void_p   # ill_stream
+_I = _c.c_int
+_L = _c.c_int64
+_F = _c.c_float
+
+SIGNATURES = {
+    "ill_b200_version": (_I, []),
+    "ill_error_string": (_c.c_char_p, [_I]),
+    "ill_last_cuda_error": (_I, []),
+    "ill_block_bytes": (_I, [_I]),
+    "ill_block_weights": (_I, [_I]),
+    "ill_device_status": (_I, [_c.POINTER(_c.c_uint), _S]),
+    "ill_quant_q8_0": (_I, [_P, _P, _P, _P, _L, _I, _S]),
+    "ill_quant_q8_k": (_I, [_P, _P, _P, _P, _L, _S]),
+    "ill_dequant_rows": (_I, [_I, _P, _I, _P, _L, _I, _P, _S]),
+    "ill_mv": (_I, [_I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _S]),
+    "ill_mv_3": (_I, [_I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _S]),
+    "ill_mv_glu": (_I, [_I, _P, _P, _I, _I, _P, _P, _P, _P, _S]),
+}
+
+
+class IllatioError(RuntimeError):
+    def __init__(self, fn, code, text, cuda=0):
+        super().__init__("%s failed: %s (status %d%s)" % (fn, text, code, ", cudaError %d" % cuda if cuda else ""))
+        self.code = code
+        self.cuda = cuda
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "libillatio_b200.so is not built (run `python -m illatio_b200.build`); there is no fallback path")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            if not hasattr(L, name):
+                continue
+            f = getattr(L, name)
+            f.restype = res
+            f.argtypes = args
+        _lib = L
+    return _lib
+
+
+def register(name, res, args):
+    """Add the signature of an entry point declared after this module was written."""
+    SIGNATURES[name] = (res, args)
+    if _lib is not None and hasattr(_lib, name):
+        f = getattr(_lib, name)
+        f.restype = res
+        f.argtypes = args
+
+
+def call(name, *args):
+    """Call entry point NAME; a non-zero status becomes an IllatioError."""
+    L = lib()
+    rc = getattr(L, name)(*args)
+    if rc != 0:
+        raise IllatioError(name, rc, L.ill_error_string(rc).decode(), L.ill_last_cuda_error() if rc == 4 else 0)
+    return rc
+
+
+def status(name, *args):
+    """Call entry point NAME and return its status code without raising."""
+    return getattr(lib(), name)(*args)

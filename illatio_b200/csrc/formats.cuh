@@ -1,0 +1,342 @@
+// formats.cuh -- the five GGUF block formats as the kernels read them.
+//
+// A "unit" is the slice of a row one lane multiplies at a time: a Q8_0 block
+// (32 weights), an IQ2_XXS sub-block (32 weights), or a quarter of a Q4_K /
+// Q6_K / Q2_K super-block (64 weights) chosen so that every 16- or 32-weight
+// scale group lies whole inside one unit.  For each format:
+//
+//   XReg  one token's activations for a unit, in registers
+//   WReg  the unit's weights unpacked to int8x4 words, plus its scales
+//   load_x / load_w / dot
+//
+// Integer dots are exact (dp4a); the float steps per unit follow the reference
+// CPU kernels' formulas (src/tensor.lisp:321-336, src/kquant.lisp:171-236,
+// src/iquant.lisp:126-215), so results differ from them only by the order in
+// which fp32 partial sums are added.
+//
+// Weights are read from a shared-memory copy of the raw row bytes at any byte
+// alignment; activations from a shared-memory copy laid out by x_layout().
+#pragma once
+#include "common.cuh"
+
+namespace ill {
+
+template <int FMT> struct Fmt;
+template <> struct Fmt<ILL_Q8_0>    { static constexpr int BB = 34,  BW = 32,  UW = 32, UPB = 1; };
+template <> struct Fmt<ILL_Q4_K>    { static constexpr int BB = 144, BW = 256, UW = 64, UPB = 4; };
+template <> struct Fmt<ILL_Q6_K>    { static constexpr int BB = 210, BW = 256, UW = 64, UPB = 4; };
+template <> struct Fmt<ILL_Q2_K>    { static constexpr int BB = 84,  BW = 256, UW = 64, UPB = 4; };
+template <> struct Fmt<ILL_IQ2_XXS> { static constexpr int BB = 66,  BW = 256, UW = 32, UPB = 8; };
+
+__host__ __device__ inline int fmt_block_bytes(int fmt) {
+  return fmt == ILL_Q8_0 ? 34 : fmt == ILL_Q4_K ? 144 : fmt == ILL_Q6_K ? 210 : fmt == ILL_Q2_K ? 84
+         : fmt == ILL_IQ2_XXS ? 66 : 0;
+}
+__host__ __device__ inline int fmt_block_weights(int fmt) {
+  return fmt == ILL_Q8_0 ? 32 : (fmt >= ILL_Q4_K && fmt <= ILL_IQ2_XXS) ? 256 : 0;
+}
+
+// One token's activations in shared memory.
+struct ActS {
+  const i8* q;        // quants, 16-byte aligned
+  const float* s;     // one scale per 32 (Q8_0) or per 256 (Q8_K)
+  const int16_t* bs;  // sums of 16 quants (Q8_K)
+};
+
+// words at an arbitrarily aligned shared-memory byte pointer
+template <int N>
+__device__ __forceinline__ void ld_words(const u8* p, uint32_t (&out)[N]) {
+  const uint32_t sh = ((uint32_t)(uintptr_t)p & 3u) * 8u;
+  const uint32_t* b = (const uint32_t*)((uintptr_t)p & ~(uintptr_t)3);
+  uint32_t prev = b[0];
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    uint32_t next = b[i + 1];
+    out[i] = __funnelshift_r(prev, next, sh);
+    prev = next;
+  }
+}
+__device__ __forceinline__ uint32_t ld_u16(const u8* p) { return *(const u16*)p; }  // p is 2-byte aligned
+
+template <int N>
+__device__ __forceinline__ void ld_x128(const i8* p, uint32_t* out) {  // N uint4 loads, 16-byte aligned
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    uint4 v = ((const uint4*)p)[i];
+    out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+  }
+}
+
+// ---- Q8_0: unit = block ------------------------------------------------------
+template <int FMT> struct XReg;
+template <int FMT> struct WReg;
+
+template <> struct XReg<ILL_Q8_0> { uint32_t q[8]; float s; };
+template <> struct WReg<ILL_Q8_0> { uint32_t q[8]; float d; };
+
+__device__ __forceinline__ void load_x(XReg<ILL_Q8_0>& x, const ActS& a, int u) {
+  ld_x128<2>(a.q + 32 * u, x.q);
+  x.s = a.s[u];
+}
+__device__ __forceinline__ void load_w(WReg<ILL_Q8_0>& w, const u8* row, int u) {
+  const u8* p = row + 34 * u;
+  w.d = h2f(ld_u16(p));
+  ld_words<8>(p + 2, w.q);
+}
+__device__ __forceinline__ float dot(const WReg<ILL_Q8_0>& w, const XReg<ILL_Q8_0>& x) {
+  int acc = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc = __dp4a((int)w.q[i], (int)x.q[i], acc);
+  return (float)acc * (w.d * x.s);
+}
+
+// ---- Q4_K: unit = 64 weights (groups 2k and 2k+1 of a super-block) ------------
+template <> struct XReg<ILL_Q4_K> { uint32_t q[16]; float d; int bs0, bs1; };
+template <> struct WReg<ILL_Q4_K> { uint32_t q[8]; float d, dmin; int sc0, sc1, m0, m1; };
+
+__device__ __forceinline__ void load_x(XReg<ILL_Q4_K>& x, const ActS& a, int u) {
+  const int i = u >> 2, k = u & 3;
+  ld_x128<4>(a.q + 256 * i + 64 * k, x.q);
+  x.d = a.s[i];
+  const int2 b = *(const int2*)(a.bs + 16 * i + 4 * k);  // four int16 sums, 8-byte aligned
+  x.bs0 = (int)(short)(b.x & 0xffff) + (b.x >> 16);
+  x.bs1 = (int)(short)(b.y & 0xffff) + (b.y >> 16);
+}
+__device__ __forceinline__ void load_w(WReg<ILL_Q4_K>& w, const u8* row, int u) {
+  const int i = u >> 2, k = u & 3;
+  const u8* p = row + 144 * i;
+  uint32_t h[4];  // d|dmin, then the 12 scale bytes
+  ld_words<4>(p, h);
+  w.d = h2f(h[0] & 0xffff);
+  w.dmin = h2f(h[0] >> 16);
+  // get_scale_min_k4 for groups j = 2k, 2k+1 (src/kquant.lisp:64-72)
+  if (k < 2) {
+    const int sh = 16 * k;
+    w.sc0 = (h[1] >> sh) & 63; w.sc1 = (h[1] >> (sh + 8)) & 63;
+    w.m0 = (h[2] >> sh) & 63;  w.m1 = (h[2] >> (sh + 8)) & 63;
+  } else {
+    const int sh = 16 * (k - 2);
+    const uint32_t lo0 = (h[3] >> sh) & 0xff, lo1 = (h[3] >> (sh + 8)) & 0xff;
+    w.sc0 = (lo0 & 0xF) | (((h[1] >> (sh + 6)) & 3) << 4);
+    w.sc1 = (lo1 & 0xF) | (((h[1] >> (sh + 14)) & 3) << 4);
+    w.m0 = (lo0 >> 4) | (((h[2] >> (sh + 6)) & 3) << 4);
+    w.m1 = (lo1 >> 4) | (((h[2] >> (sh + 14)) & 3) << 4);
+  }
+  ld_words<8>(p + 16 + 32 * k, w.q);
+}
+__device__ __forceinline__ float dot(const WReg<ILL_Q4_K>& w, const XReg<ILL_Q4_K>& x) {
+  int lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    lo = __dp4a((int)(w.q[i] & 0x0F0F0F0Fu), (int)x.q[i], lo);
+    hi = __dp4a((int)((w.q[i] >> 4) & 0x0F0F0F0Fu), (int)x.q[8 + i], hi);
+  }
+  const int isum = lo * w.sc0 + hi * w.sc1, imin = w.m0 * x.bs0 + w.m1 * x.bs1;
+  return (x.d * w.d) * (float)isum - (x.d * w.dmin) * (float)imin;
+}
+
+// ---- Q6_K: unit = half c, 16-lane half hq: four groups of 16 ------------------
+template <> struct XReg<ILL_Q6_K> { uint32_t q[16]; float d; int bs[4]; };
+template <> struct WReg<ILL_Q6_K> { uint32_t q[16]; float d; int sc[4]; };
+
+__device__ __forceinline__ void load_x(XReg<ILL_Q6_K>& x, const ActS& a, int u) {
+  const int i = u >> 2, c = (u >> 1) & 1, hq = u & 1;
+  const i8* q = a.q + 256 * i + 128 * c + 16 * hq;
+  const int16_t* bs = a.bs + 16 * i + 8 * c + hq;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    ld_x128<1>(q + 32 * g, x.q + 4 * g);
+    x.bs[g] = bs[2 * g];
+  }
+  x.d = a.s[i];
+}
+__device__ __forceinline__ void load_w(WReg<ILL_Q6_K>& w, const u8* row, int u) {
+  const int i = u >> 2, c = (u >> 1) & 1, hq = u & 1;
+  const u8* p = row + 210 * i;
+  uint32_t a[4], b[4], h[4], s[2];
+  ld_words<4>(p + 64 * c + 16 * hq, a);
+  ld_words<4>(p + 64 * c + 32 + 16 * hq, b);
+  ld_words<4>(p + 128 + 32 * c + 16 * hq, h);
+  ld_words<2>(p + 192 + 8 * c, s);  // the half's eight int8 scales
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    w.q[j]      = (a[j] & 0x0F0F0F0Fu) | ((h[j] << 4) & 0x30303030u);
+    w.q[4 + j]  = (b[j] & 0x0F0F0F0Fu) | ((h[j] << 2) & 0x30303030u);
+    w.q[8 + j]  = ((a[j] >> 4) & 0x0F0F0F0Fu) | (h[j] & 0x30303030u);
+    w.q[12 + j] = ((b[j] >> 4) & 0x0F0F0F0Fu) | ((h[j] >> 2) & 0x30303030u);
+  }
+  // scale of group g: byte hq + 2g of the eight
+  const uint32_t lo = s[0] >> (8 * hq), hi = s[1] >> (8 * hq);
+  w.sc[0] = (int)(signed char)(lo & 0xff);
+  w.sc[1] = (int)(signed char)((lo >> 16) & 0xff);
+  w.sc[2] = (int)(signed char)(hi & 0xff);
+  w.sc[3] = (int)(signed char)((hi >> 16) & 0xff);
+  w.d = h2f(ld_u16(p + 208));
+}
+__device__ __forceinline__ float dot(const WReg<ILL_Q6_K>& w, const XReg<ILL_Q6_K>& x) {
+  int isum = 0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    int d = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) d = __dp4a((int)w.q[4 * g + j], (int)x.q[4 * g + j], d);
+    isum += w.sc[g] * (d - 32 * x.bs[g]);
+  }
+  return (w.d * x.d) * (float)isum;
+}
+
+// ---- Q2_K: unit = half h, 16-byte half: four groups of 16 ---------------------
+template <> struct XReg<ILL_Q2_K> { uint32_t q[16]; float d; int bs[4]; };
+template <> struct WReg<ILL_Q2_K> { uint32_t q[4]; float d, dmin; int sc[4]; };
+
+__device__ __forceinline__ void load_x(XReg<ILL_Q2_K>& x, const ActS& a, int u) {
+  const int i = u >> 2, h = (u >> 1) & 1, half = u & 1;
+  const i8* q = a.q + 256 * i + 128 * h + 16 * half;
+  const int16_t* bs = a.bs + 16 * i + 8 * h + half;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    ld_x128<1>(q + 32 * k, x.q + 4 * k);
+    x.bs[k] = bs[2 * k];
+  }
+  x.d = a.s[i];
+}
+__device__ __forceinline__ void load_w(WReg<ILL_Q2_K>& w, const u8* row, int u) {
+  const int i = u >> 2, h = (u >> 1) & 1, half = u & 1;
+  const u8* p = row + 84 * i;
+  uint32_t s[2], dd[1];
+  ld_words<2>(p + 8 * h, s);  // the half's eight scale bytes
+  ld_words<4>(p + 16 + 32 * h + 16 * half, w.q);
+  ld_words<1>(p + 80, dd);
+  const uint32_t lo = s[0] >> (8 * half), hi = s[1] >> (8 * half);
+  w.sc[0] = lo & 0xff; w.sc[1] = (lo >> 16) & 0xff; w.sc[2] = hi & 0xff; w.sc[3] = (hi >> 16) & 0xff;
+  w.d = h2f(dd[0] & 0xffff);
+  w.dmin = h2f(dd[0] >> 16);
+}
+__device__ __forceinline__ float dot(const WReg<ILL_Q2_K>& w, const XReg<ILL_Q2_K>& x) {
+  int isum = 0, mins = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    int d = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) d = __dp4a((int)((w.q[j] >> (2 * k)) & 0x03030303u), (int)x.q[4 * k + j], d);
+    isum += (w.sc[k] & 15) * d;
+    mins += (w.sc[k] >> 4) * x.bs[k];
+  }
+  return (x.d * w.d) * (float)isum - (x.d * w.dmin) * (float)mins;
+}
+
+// ---- IQ2_XXS: unit = sub-block of 32 -------------------------------------------
+// The codebook (256 x 8 magnitudes) and the sign patterns expanded to byte
+// masks (0xFF where the weight is negative) sit in shared memory.
+struct IqTables { const uint2* grid; const uint2* smask; };
+
+template <> struct XReg<ILL_IQ2_XXS> { uint32_t q[8]; float d; };
+template <> struct WReg<ILL_IQ2_XXS> { uint32_t q[8]; float d; float ls; };
+
+__device__ __forceinline__ void load_x(XReg<ILL_IQ2_XXS>& x, const ActS& a, int u) {
+  ld_x128<2>(a.q + 32 * u, x.q);
+  x.d = a.s[u >> 3];
+}
+__device__ __forceinline__ void load_w(WReg<ILL_IQ2_XXS>& w, const u8* row, int u, const IqTables& t) {
+  const u8* p = row + 66 * (u >> 3);
+  uint32_t v[2];
+  ld_words<2>(p + 2 + 8 * (u & 7), v);
+  const uint32_t idx = v[0], aux = v[1];
+#pragma unroll
+  for (int l = 0; l < 4; ++l) {
+    const uint2 g = t.grid[(idx >> (8 * l)) & 0xff];
+    const uint2 m = t.smask[(aux >> (7 * l)) & 127];
+    // (g ^ m) - m per byte; g <= 43, so adding 1 to a flipped byte never carries
+    w.q[2 * l] = (g.x ^ m.x) + (m.x & 0x01010101u);
+    w.q[2 * l + 1] = (g.y ^ m.y) + (m.y & 0x01010101u);
+  }
+  w.ls = 0.5f + (float)(aux >> 28);
+  w.d = h2f(ld_u16(p));
+}
+__device__ __forceinline__ float dot(const WReg<ILL_IQ2_XXS>& w, const XReg<ILL_IQ2_XXS>& x) {
+  int acc = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc = __dp4a((int)w.q[i], (int)x.q[i], acc);
+  return ((w.d * x.d) * ((float)acc * w.ls)) * 0.25f;
+}
+
+// Fills the IQ2_XXS tables in shared memory (call from all threads, then sync).
+__device__ __forceinline__ void iq_tables_fill(uint2* grid, uint2* smask, const uint64_t* ggrid, const u8* gsigns) {
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    const uint64_t g = ggrid[i];
+    grid[i] = make_uint2((uint32_t)g, (uint32_t)(g >> 32));
+  }
+  for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+    const uint32_t s = gsigns[i];
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if ((s >> j) & 1) lo |= 0xffu << (8 * j);
+      if ((s >> (4 + j)) & 1) hi |= 0xffu << (8 * j);
+    }
+    smask[i] = make_uint2(lo, hi);
+  }
+}
+
+// ---- one weight as a float, for rows-as-floats -----------------------------------
+// The reference's dequantization, operation for operation (no fused
+// multiply-add: the intrinsics round each step).
+template <int FMT>
+__device__ __forceinline__ float dequant_weight(const u8* __restrict__ row, int col, const uint64_t* ggrid,
+                                                const u8* gsigns);
+
+__device__ __forceinline__ float gh2f(const u8* p) { return h2f((uint32_t)p[0] | ((uint32_t)p[1] << 8)); }
+
+template <>
+__device__ __forceinline__ float dequant_weight<ILL_Q8_0>(const u8* __restrict__ row, int col, const uint64_t*,
+                                                          const u8*) {
+  const u8* p = row + 34 * (col >> 5);
+  return __fmul_rn(gh2f(p), (float)(int)(signed char)p[2 + (col & 31)]);
+}
+template <>
+__device__ __forceinline__ float dequant_weight<ILL_Q4_K>(const u8* __restrict__ row, int col, const uint64_t*,
+                                                          const u8*) {
+  const u8* p = row + 144 * (col >> 8);
+  const int w = col & 255, k = w >> 6, hi = (w >> 5) & 1, l = w & 31, j = 2 * k + hi;
+  const u8* q = p + 4;
+  int sc, mn;
+  if (j < 4) { sc = q[j] & 63; mn = q[j + 4] & 63; }
+  else { sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4); mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+  const u8 byte = p[16 + 32 * k + l];
+  const int qv = hi ? (byte >> 4) : (byte & 0xF);
+  return __fsub_rn(__fmul_rn(__fmul_rn(gh2f(p), (float)sc), (float)qv), __fmul_rn(gh2f(p + 2), (float)mn));
+}
+template <>
+__device__ __forceinline__ float dequant_weight<ILL_Q6_K>(const u8* __restrict__ row, int col, const uint64_t*,
+                                                          const u8*) {
+  const u8* p = row + 210 * (col >> 8);
+  const int w = col & 255, c = w >> 7, g = (w >> 5) & 3, l = w & 31;
+  const u8 lo = p[64 * c + 32 * (g & 1) + l], h = p[128 + 32 * c + l];
+  const int q = ((g < 2) ? (lo & 0xF) : (lo >> 4)) | (((h >> (2 * g)) & 3) << 4);
+  const int sc = (int)(signed char)p[192 + 8 * c + (l >> 4) + 2 * g];
+  return __fmul_rn(__fmul_rn(gh2f(p + 208), (float)sc), (float)(q - 32));
+}
+template <>
+__device__ __forceinline__ float dequant_weight<ILL_Q2_K>(const u8* __restrict__ row, int col, const uint64_t*,
+                                                          const u8*) {
+  const u8* p = row + 84 * (col >> 8);
+  const int w = col & 255, h = w >> 7, k = (w >> 5) & 3, half = (w >> 4) & 1, l = w & 15;
+  const u8 sb = p[8 * h + 2 * k + half];
+  const int q = (p[16 + 32 * h + 16 * half + l] >> (2 * k)) & 3;
+  return __fsub_rn(__fmul_rn(__fmul_rn(gh2f(p + 80), (float)(sb & 15)), (float)q),
+                   __fmul_rn(gh2f(p + 82), (float)(sb >> 4)));
+}
+template <>
+__device__ __forceinline__ float dequant_weight<ILL_IQ2_XXS>(const u8* __restrict__ row, int col,
+                                                             const uint64_t* ggrid, const u8* gsigns) {
+  const u8* p = row + 66 * (col >> 8);
+  const int w = col & 255, ib = w >> 5, l = (w >> 3) & 3, j = w & 7;
+  const u8* so = p + 2 + 8 * ib;
+  const uint32_t aux = (uint32_t)so[4] | ((uint32_t)so[5] << 8) | ((uint32_t)so[6] << 16) | ((uint32_t)so[7] << 24);
+  const float db = __fmul_rn(__fmul_rn(gh2f(p), __fadd_rn(0.5f, (float)(aux >> 28))), 0.25f);
+  const float mag = (float)(uint32_t)((ggrid[so[l]] >> (8 * j)) & 0xff);
+  const float sg = ((gsigns[(aux >> (7 * l)) & 127] >> j) & 1) ? -1.0f : 1.0f;
+  return __fmul_rn(__fmul_rn(db, mag), sg);
+}
+
+}  // namespace ill

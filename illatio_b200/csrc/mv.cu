@@ -1,0 +1,467 @@
+// mv.cu -- dequant-fused quantized matrix x vector products (decode path).
+//
+// HBM-bound: one pass over the raw GGUF bytes.  A persistent grid walks the
+// matrix in tiles of whole rows.  Thread 0 of each CTA streams tiles into a ring
+// of shared-memory stages with 1-D bulk asynchronous copies (cp.async.bulk,
+// completion counted on an mbarrier per stage); all threads then unpack the
+// blocks from shared memory, take exact integer dots against the quantized
+// activations (also staged in shared memory) with dp4a, scale in fp32 and
+// reduce across the lanes that share a row with shuffles.  A copy covers the
+// 16-byte aligned superset of the tile's byte range, so rows of any byte length
+// and base alignment are read where they lie (no repacking or padding).
+//
+// Replaces mv_q8 / mv_q8_3 / mv_q8_glu (src/cuda/dense.cu:194-250), mv_k /
+// mv_k_glu (src/cuda/kquant.cu:169-193), d4_mvq8 / d4_mvq8n (src/cuda/ds4f.cu:
+// 50-107) and the per-expert d4_mv_iq2_xxs / d4_mv_q2_k (src/cuda/ds4f.cu:769,
+// 837) of the reference.
+#include "formats.cuh"
+#include "iq2xxs_tables.cuh"
+#include "host.h"
+
+namespace ill {
+
+constexpr int MV_THREADS = 256;
+constexpr int MV_MAX_MATS = 3;
+constexpr int MV_MAX_TOK = 16;
+
+enum { MODE_PLAIN = 0, MODE_GLU = 1, MODE_MOE_GLU = 2 };
+
+struct MvParams {
+  // matrices (PLAIN: up to three sharing the activations; GLU: gate, up)
+  const u8* w[MV_MAX_MATS];
+  float* y[MV_MAX_MATS];
+  const float* bias[MV_MAX_MATS];
+  int rows[MV_MAX_MATS];
+  int tile0[MV_MAX_MATS + 1];  // first tile of each matrix; tile0[nmat] = tiles per segment
+  int nmat;
+  int cols, row_bytes, units;  // units per row
+  // activations (global): token t at xq + t*cols etc.
+  const i8* xq;
+  const float* xs;
+  const int16_t* xsum;
+  int n;                 // tokens
+  int acc;
+  int rows_per_tile, lanes_per_row;
+  uint32_t stage_bytes;  // bytes of one stage (one matrix' part of it in GLU modes)
+  int nstages;
+  uint32_t x_bytes;      // shared bytes of the activation region
+  uint32_t xs_off, bs_off;
+  // segments (grid.y): expert z's weights at ptrs[z] + add (+ up_add for "up"),
+  // its activations at token z*x_seg (0: shared), its output at y + z*y_seg
+  const unsigned long long* ptrs;
+  long long add, up_add;
+  int x_seg;
+  long long y_seg;
+  const float* seg_w;    // MOE_GLU: weight of segment z
+  float clamp;
+  unsigned int* status;
+};
+
+// The row r0 .. of one matrix that a tile covers, and where its bytes are.
+struct TileRef {
+  int m, row0, nrows;
+  const u8* g;  // global address of the first row
+};
+
+__device__ __forceinline__ TileRef tile_ref(const MvParams& p, int tile, const u8* const* wbase) {
+  TileRef t;
+  int m = 0;
+#pragma unroll
+  for (int i = 1; i < MV_MAX_MATS; ++i)
+    if (i < p.nmat && tile >= p.tile0[i]) m = i;
+  t.m = m;
+  t.row0 = (tile - p.tile0[m]) * p.rows_per_tile;
+  t.nrows = min(p.rows_per_tile, p.rows[m] - t.row0);
+  t.g = wbase[m] + (long long)t.row0 * p.row_bytes;
+  return t;
+}
+
+template <int FMT, int MODE, int NT>
+__global__ void __launch_bounds__(MV_THREADS) mv_kernel(const MvParams p) {
+  extern __shared__ __align__(128) u8 smem[];
+  constexpr bool GLU = MODE != MODE_PLAIN;
+  constexpr bool IQ = FMT == ILL_IQ2_XXS;
+  const int tid = threadIdx.x;
+  const int z = blockIdx.y;
+
+  u8* xreg = smem;
+  u8* stage0 = smem + p.x_bytes;
+  const uint32_t stage_stride = p.stage_bytes * (GLU ? 2u : 1u);
+  u8* after = stage0 + (size_t)stage_stride * p.nstages;
+  uint2* iq_grid = (uint2*)after;
+  uint2* iq_smask = iq_grid + 256;
+  uint64_t* full = (uint64_t*)(after + (IQ ? 3072 : 0));
+
+  // this segment's matrices
+  const u8* wbase[MV_MAX_MATS];
+  if (p.ptrs) {
+    const u8* b = (const u8*)(uintptr_t)p.ptrs[z] + p.add;
+    wbase[0] = b;
+    wbase[1] = b + p.up_add;
+    wbase[2] = b;
+  } else {
+#pragma unroll
+    for (int i = 0; i < MV_MAX_MATS; ++i) wbase[i] = p.w[i];
+  }
+  const int ntiles = p.tile0[p.nmat];
+  const int first = blockIdx.x, step = gridDim.x;
+
+  auto issue = [&](int tile, int s) {
+    const TileRef t = tile_ref(p, tile, wbase);
+    const uint32_t len = (uint32_t)t.nrows * (uint32_t)p.row_bytes;
+    u8* dst = stage0 + (size_t)s * stage_stride;
+    const uintptr_t a0 = (uintptr_t)t.g & ~(uintptr_t)15;
+    const uint32_t bytes = (uint32_t)((((uintptr_t)t.g + len + 15) & ~(uintptr_t)15) - a0);
+    if (GLU) {
+      const u8* g2 = wbase[1] + (long long)t.row0 * p.row_bytes;
+      const uintptr_t b0 = (uintptr_t)g2 & ~(uintptr_t)15;
+      const uint32_t bytes2 = (uint32_t)((((uintptr_t)g2 + len + 15) & ~(uintptr_t)15) - b0);
+      mbar_expect_tx(&full[s], bytes + bytes2);
+      bulk_g2s(dst, (const void*)a0, bytes, &full[s]);
+      bulk_g2s(dst + p.stage_bytes, (const void*)b0, bytes2, &full[s]);
+    } else {
+      mbar_expect_tx(&full[s], bytes);
+      bulk_g2s(dst, (const void*)a0, bytes, &full[s]);
+    }
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < p.nstages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+    // weights do not depend on the previous kernel: start streaming them now
+    for (int s = 0; s < p.nstages; ++s) {
+      const int tile = first + s * step;
+      if (tile < ntiles) issue(tile, s);
+    }
+  }
+  if (IQ) iq_tables_fill(iq_grid, iq_smask, ill_iq2xxs_grid, ill_ksigns_iq2xs);
+  pdl_launch_dependents();
+  pdl_wait();  // activations may come from the previous kernel
+
+  // activations -> shared memory
+  {
+    const int ntok_x = p.x_seg ? 1 : p.n;  // a segment with its own activations has one token
+    const long long tok0 = (long long)z * p.x_seg;
+    const int nsc = FMT == ILL_Q8_0 ? p.cols / 32 : p.cols / 256;
+    const uint4* src = (const uint4*)(p.xq + tok0 * p.cols);
+    uint4* dst = (uint4*)xreg;
+    for (int i = tid; i < ntok_x * p.cols / 16; i += MV_THREADS) dst[i] = src[i];
+    const float* ssrc = p.xs + tok0 * nsc;
+    float* sdst = (float*)(xreg + p.xs_off);
+    for (int i = tid; i < ntok_x * nsc; i += MV_THREADS) sdst[i] = ssrc[i];
+    if (FMT != ILL_Q8_0 && FMT != ILL_IQ2_XXS) {
+      const int16_t* bsrc = p.xsum + tok0 * (p.cols / 16);
+      int16_t* bdst = (int16_t*)(xreg + p.bs_off);
+      for (int i = tid; i < ntok_x * p.cols / 16; i += MV_THREADS) bdst[i] = bsrc[i];
+    }
+  }
+  __syncthreads();
+
+  const int L = p.lanes_per_row;
+  const int group = tid / L, lane_in = tid % L, ngroups = MV_THREADS / L;
+  const int nsc = FMT == ILL_Q8_0 ? p.cols / 32 : p.cols / 256;
+  IqTables iqt;
+  iqt.grid = iq_grid;
+  iqt.smask = iq_smask;
+
+  int it = 0;
+  bool failed = false;
+  for (int tile = first; tile < ntiles; tile += step, ++it) {
+    const int s = it % p.nstages;
+    const uint32_t parity = (uint32_t)(it / p.nstages) & 1u;
+    const bool ok = mbar_wait(&full[s], parity, p.status, ST_MV_WAIT + FMT);
+    if (__syncthreads_or(!ok)) { failed = true; break; }
+
+    const TileRef t = tile_ref(p, tile, wbase);
+    const u8* sbase = stage0 + (size_t)s * stage_stride;
+    const u8* rows_s = sbase + ((uintptr_t)t.g & 15);
+    const u8* rows_u = nullptr;
+    if (GLU) rows_u = sbase + p.stage_bytes + ((uintptr_t)(wbase[1] + (long long)t.row0 * p.row_bytes) & 15);
+
+    const int passes = (t.nrows + ngroups - 1) / ngroups;
+    for (int ps = 0; ps < passes; ++ps) {
+      const int r = ps * ngroups + group;
+      const bool valid = r < t.nrows;
+      float sum[NT], sum2[GLU ? NT : 1];
+#pragma unroll
+      for (int k = 0; k < NT; ++k) sum[k] = 0.0f;
+      sum2[0] = 0.0f;
+      if (valid) {
+        const u8* rowp = rows_s + (size_t)r * p.row_bytes;
+        for (int u = lane_in; u < p.units; u += L) {
+          WReg<FMT> w;
+          if constexpr (IQ) load_w(w, rowp, u, iqt); else load_w(w, rowp, u);
+          if constexpr (GLU) {
+            WReg<FMT> w2;
+            const u8* rowu = rows_u + (size_t)r * p.row_bytes;
+            if constexpr (IQ) load_w(w2, rowu, u, iqt); else load_w(w2, rowu, u);
+            ActS a;
+            a.q = (const i8*)xreg;
+            a.s = (const float*)(xreg + p.xs_off);
+            a.bs = (const int16_t*)(xreg + p.bs_off);
+            XReg<FMT> x;
+            load_x(x, a, u);
+            sum[0] += dot(w, x);
+            sum2[0] += dot(w2, x);
+          } else {
+#pragma unroll
+            for (int k = 0; k < NT; ++k) {
+              if (k < p.n) {
+                ActS a;
+                a.q = (const i8*)xreg + (size_t)k * p.cols;
+                a.s = (const float*)(xreg + p.xs_off) + (size_t)k * nsc;
+                a.bs = (const int16_t*)(xreg + p.bs_off) + (size_t)k * (p.cols / 16);
+                XReg<FMT> x;
+                load_x(x, a, u);
+                sum[k] += dot(w, x);
+              }
+            }
+          }
+        }
+      }
+      // lanes of a row meet
+      for (int o = L >> 1; o > 0; o >>= 1) {
+#pragma unroll
+        for (int k = 0; k < NT; ++k) sum[k] += __shfl_xor_sync(0xffffffffu, sum[k], o);
+        if (GLU) sum2[0] += __shfl_xor_sync(0xffffffffu, sum2[0], o);
+      }
+      if (valid && lane_in == 0) {
+        const long long row = t.row0 + r;
+        if constexpr (MODE == MODE_GLU) {
+          const float g = sum[0];
+          p.y[0][(long long)z * p.y_seg + row] = (g / (1.0f + expf(-g))) * sum2[0];
+        } else if constexpr (MODE == MODE_MOE_GLU) {
+          // D4-ROUTED!'s middle (src/ds4f.lisp:1016-1019): silu(min(g,c)) * clamp(u) * weight
+          float g = sum[0], uu = sum2[0];
+          if (p.clamp > 1e-6f) { g = fminf(g, p.clamp); uu = fmaxf(-p.clamp, fminf(uu, p.clamp)); }
+          const float sg = g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : (expf(g) / (1.0f + expf(g)));
+          p.y[0][(long long)z * p.y_seg + row] = ((g * sg) * uu) * p.seg_w[z];
+        } else {
+          float* y = p.y[t.m] + (long long)z * p.y_seg;
+          const float* bias = p.bias[t.m];
+#pragma unroll
+          for (int k = 0; k < NT; ++k) {
+            if (k < p.n) {
+              float v = sum[k];
+              if (bias) v += bias[row];
+              const long long o = (long long)k * p.rows[t.m] + row;
+              y[o] = p.acc ? y[o] + v : v;
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();  // every lane is done with the stage
+    if (tid == 0) {
+      const int nt = tile + p.nstages * step;
+      if (nt < ntiles) issue(nt, s);
+    }
+  }
+  if (failed) {
+    // give copies still in flight a bounded time to land before the CTA's
+    // shared memory is released
+    int it2 = it;
+    for (int tile = first + it * step; tile < ntiles && it2 < it + p.nstages; tile += step, ++it2)
+      mbar_wait(&full[it2 % p.nstages], (uint32_t)(it2 / p.nstages) & 1u, nullptr, 0);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------
+
+static unsigned int* status_ptr() {
+  static thread_local int cached_dev = -1;
+  static thread_local unsigned int* cached = nullptr;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != cached_dev) {
+    cached = device_status_word();
+    cached_dev = dev;
+  }
+  return cached;
+}
+
+struct MvPlan {
+  int rows_per_tile, lanes, nstages, grid_x;
+  uint32_t stage_bytes, x_bytes, xs_off, bs_off, smem;
+};
+
+static int g_sm_count = 0;
+static int sm_count() {
+  if (!g_sm_count) {
+    int dev = 0, n = 148;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count = n;
+  }
+  return g_sm_count;
+}
+
+static uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+// Tiling: aim for ~8 tiles per SM in flight across the grid when the matrix is
+// small, at most 16 KB per stage when it is large; four stages per CTA.
+static int plan_mv(int fmt, long long total_rows, int cols, int ntok_smem, int nseg, bool glu, MvPlan* pl) {
+  const int bw = fmt_block_weights(fmt), bb = fmt_block_bytes(fmt);
+  const long long row_bytes = (long long)(cols / bw) * bb;
+  const uint32_t max_stage = glu ? 12288 : 16384;
+  if (row_bytes + 32 > 49152) return ILL_ERR_UNSUPPORTED;
+  const int sms = sm_count();
+  long long target = total_rows * row_bytes * nseg / ((long long)sms * 16);
+  if (target > max_stage) target = max_stage;
+  if (target < 2048) target = 2048;
+  long long rpt = target / row_bytes;
+  if (rpt < 1) rpt = 1;
+  if (rpt > total_rows) rpt = total_rows;
+  pl->rows_per_tile = (int)rpt;
+  pl->stage_bytes = align_up((uint32_t)(rpt * row_bytes) + 32, 128);
+  pl->nstages = 4;
+  const int units = cols / (fmt == ILL_Q8_0 || fmt == ILL_IQ2_XXS ? 32 : 64);
+  int L = 32;
+  while (L > 1 && (L / 2) * rpt >= MV_THREADS) L >>= 1;  // enough rows to fill the CTA with fewer lanes a row
+  while (L > 1 && L / 2 >= units) L >>= 1;
+  pl->lanes = L;
+  const int nsc = fmt == ILL_Q8_0 ? cols / 32 : cols / 256;
+  pl->xs_off = align_up((uint32_t)ntok_smem * cols, 16);
+  pl->bs_off = align_up(pl->xs_off + 4u * ntok_smem * nsc, 16);
+  pl->x_bytes = align_up(pl->bs_off + 2u * ntok_smem * (cols / 16), 128);
+  pl->smem = pl->x_bytes + pl->stage_bytes * (glu ? 2 : 1) * pl->nstages + (fmt == ILL_IQ2_XXS ? 3072 : 0) + 64;
+  if (pl->smem > 227 * 1024) return ILL_ERR_UNSUPPORTED;
+  return ILL_OK;
+}
+
+template <int FMT, int MODE, int NT>
+static int launch_mv_t(const MvParams& p, const MvPlan& pl, int grid_x, int grid_y, cudaStream_t st) {
+  auto k = mv_kernel<FMT, MODE, NT>;
+  if (pl.smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid_x, grid_y, 1);
+  cfg.blockDim = dim3(MV_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, k, p);
+  return e == cudaSuccess ? ILL_OK : cuda_fail(e);
+}
+
+template <int FMT>
+static int launch_mv_f(int mode, const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
+  if (mode == MODE_GLU) return launch_mv_t<FMT, MODE_GLU, 1>(p, pl, gx, gy, st);
+  if (mode == MODE_MOE_GLU) return launch_mv_t<FMT, MODE_MOE_GLU, 1>(p, pl, gx, gy, st);
+  if (p.n == 1) return launch_mv_t<FMT, MODE_PLAIN, 1>(p, pl, gx, gy, st);
+  if (p.n <= 4) return launch_mv_t<FMT, MODE_PLAIN, 4>(p, pl, gx, gy, st);
+  if (p.n <= 8) return launch_mv_t<FMT, MODE_PLAIN, 8>(p, pl, gx, gy, st);
+  return launch_mv_t<FMT, MODE_PLAIN, 16>(p, pl, gx, gy, st);
+}
+
+static int launch_mv(int fmt, int mode, const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
+  switch (fmt) {
+    case ILL_Q8_0: return launch_mv_f<ILL_Q8_0>(mode, p, pl, gx, gy, st);
+    case ILL_Q4_K: return launch_mv_f<ILL_Q4_K>(mode, p, pl, gx, gy, st);
+    case ILL_Q6_K: return launch_mv_f<ILL_Q6_K>(mode, p, pl, gx, gy, st);
+    case ILL_Q2_K: return launch_mv_f<ILL_Q2_K>(mode, p, pl, gx, gy, st);
+    case ILL_IQ2_XXS: return launch_mv_f<ILL_IQ2_XXS>(mode, p, pl, gx, gy, st);
+  }
+  return ILL_ERR_ARG;
+}
+
+static bool needs_bsums(int fmt) { return fmt == ILL_Q4_K || fmt == ILL_Q6_K || fmt == ILL_Q2_K; }
+
+// Common entry: NMAT matrices of one format sharing the activations.
+static int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, int cols, ill_dptr xq, ill_dptr xs,
+                     ill_dptr xsum, const ill_dptr* y, const ill_dptr* bias, int acc, int n, ill_dptr ptrs, int nseg,
+                     long long add, long long up_add, int x_seg, long long y_seg, ill_dptr seg_w, float clamp,
+                     ill_stream stream) {
+  const int bw = fmt_block_weights(fmt);
+  if (!bw || nmat < 1 || nmat > MV_MAX_MATS || cols <= 0 || cols % (bw == 32 ? 32 : 256)) return ILL_ERR_ARG;
+  if (n < 1 || n > MV_MAX_TOK || nseg < 1 || nseg > 65535) return ILL_ERR_ARG;
+  if (!xq || !xs || (needs_bsums(fmt) && !xsum)) return ILL_ERR_ARG;
+  if (xq & 15 || xs & 3 || xsum & 7) return ILL_ERR_ALIGN;
+  long long total_rows = 0;
+  for (int i = 0; i < nmat; ++i) {
+    if (rows[i] <= 0 || !y[i] || (!ptrs && !w[i])) return ILL_ERR_ARG;
+    if (y[i] & 3) return ILL_ERR_ALIGN;
+    total_rows += rows[i];
+  }
+  const bool glu = mode != MODE_PLAIN;
+  MvPlan pl;
+  const int ntok_smem = x_seg ? 1 : n;
+  int rc = plan_mv(fmt, glu ? rows[0] : total_rows, cols, ntok_smem, nseg, glu, &pl);
+  if (rc) return rc;
+  MvParams p = {};
+  p.nmat = glu ? 1 : nmat;
+  int tiles = 0;
+  for (int i = 0; i < MV_MAX_MATS; ++i) {
+    p.w[i] = i < nmat ? (const u8*)(uintptr_t)w[i] : nullptr;
+    p.y[i] = i < nmat ? (float*)(uintptr_t)y[i] : nullptr;
+    p.bias[i] = (i < nmat && bias) ? (const float*)(uintptr_t)bias[i] : nullptr;
+    p.rows[i] = i < nmat ? rows[i] : 0;
+    p.tile0[i] = tiles;
+    if (i < p.nmat) tiles += (rows[i] + pl.rows_per_tile - 1) / pl.rows_per_tile;
+  }
+  p.tile0[p.nmat] = tiles;
+  for (int i = p.nmat + 1; i <= MV_MAX_MATS; ++i) p.tile0[i] = tiles;
+  p.cols = cols;
+  p.row_bytes = cols / bw * fmt_block_bytes(fmt);
+  p.units = cols / (fmt == ILL_Q8_0 || fmt == ILL_IQ2_XXS ? 32 : 64);
+  p.xq = (const i8*)(uintptr_t)xq;
+  p.xs = (const float*)(uintptr_t)xs;
+  p.xsum = (const int16_t*)(uintptr_t)xsum;
+  p.n = n;
+  p.acc = acc;
+  p.rows_per_tile = pl.rows_per_tile;
+  p.lanes_per_row = pl.lanes;
+  p.stage_bytes = pl.stage_bytes;
+  p.nstages = pl.nstages;
+  p.x_bytes = pl.x_bytes;
+  p.xs_off = pl.xs_off;
+  p.bs_off = pl.bs_off;
+  p.ptrs = (const unsigned long long*)(uintptr_t)ptrs;
+  p.add = add;
+  p.up_add = up_add;
+  p.x_seg = x_seg;
+  p.y_seg = y_seg;
+  p.seg_w = (const float*)(uintptr_t)seg_w;
+  p.clamp = clamp;
+  p.status = status_ptr();
+  // persistent grid: as many CTAs as can be resident, split over the segments
+  const int per_sm = (int)((227u * 1024u) / (pl.smem + 1024u));
+  int resident = sm_count() * (per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm));
+  int gx = (resident + nseg - 1) / nseg;
+  if (gx > tiles) gx = tiles;
+  if (gx < 1) gx = 1;
+  return launch_mv(fmt, mode, p, pl, gx, nseg, (cudaStream_t)stream);
+}
+
+}  // namespace ill
+
+using namespace ill;
+
+extern "C" int ill_mv(int fmt, ill_dptr w, int rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y,
+                      ill_dptr bias, int acc, int n, ill_stream stream) {
+  const ill_dptr ws[1] = {w}, ys[1] = {y}, bs[1] = {bias};
+  const int rs[1] = {rows};
+  return mv_common(fmt, MODE_PLAIN, 1, ws, rs, cols, xq, xs, xsum, ys, bs, acc, n, 0, 1, 0, 0, 0, 0, 0, 0.0f, stream);
+}
+
+extern "C" int ill_mv_3(int fmt, ill_dptr w0, ill_dptr w1, ill_dptr w2, int rows0, int rows1, int rows2, int cols,
+                        ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y0, ill_dptr y1, ill_dptr y2, ill_dptr b0,
+                        ill_dptr b1, ill_dptr b2, ill_stream stream) {
+  const ill_dptr ws[3] = {w0, w1, w2}, ys[3] = {y0, y1, y2}, bs[3] = {b0, b1, b2};
+  const int rs[3] = {rows0, rows1, rows2};
+  return mv_common(fmt, MODE_PLAIN, 3, ws, rs, cols, xq, xs, xsum, ys, bs, 0, 1, 0, 1, 0, 0, 0, 0, 0, 0.0f, stream);
+}
+
+extern "C" int ill_mv_glu(int fmt, ill_dptr wg, ill_dptr wu, int rows, int cols, ill_dptr xq, ill_dptr xs,
+                          ill_dptr xsum, ill_dptr y, ill_stream stream) {
+  const ill_dptr ws[2] = {wg, wu}, ys[2] = {y, y};
+  const int rs[2] = {rows, rows};
+  if (!wu) return ILL_ERR_ARG;
+  return mv_common(fmt, MODE_GLU, 2, ws, rs, cols, xq, xs, xsum, ys, nullptr, 0, 1, 0, 1, 0, 0, 0, 0, 0, 0.0f, stream);
+}

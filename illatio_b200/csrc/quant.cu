@@ -1,0 +1,172 @@
+// quant.cu -- activation quantizers and rows-as-floats.
+//
+// The quantizers reproduce the reference's CPU routines bit for bit
+// (QUANTIZE-Q8! src/tensor.lisp:245-262, QUANTIZE-Q8K! src/kquant.lisp:130-167):
+// IEEE division and round-half-even conversion, no fused multiply-add, the
+// first of equal maxima wins.  They are what lets the products on the device
+// follow the CPU kernels instead of the reference's own CUDA kernels, which feed
+// K-quants Q8_0 blocks (src/cuda/kquant.cu:3-14).
+#include "formats.cuh"
+#include "iq2xxs_tables.cuh"
+#include "host.h"
+
+namespace ill {
+
+__global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict__ x, i8* __restrict__ xq,
+                                                         float* __restrict__ xs, int* __restrict__ xsum,
+                                                         long long nblocks, int f16_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= nblocks) return;
+  const float v = x[b * 32 + lane];
+  float amax = fabsf(v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float d = __fdiv_rn(amax, 127.0f);
+  const float id = d == 0.0f ? 0.0f : __fdiv_rn(1.0f, d);
+  const int q = __float2int_rn(__fmul_rn(v, id));
+  xq[b * 32 + lane] = (i8)q;
+  if (xsum) {
+    int t = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) xsum[b] = t;
+  }
+  if (lane == 0) xs[b] = f16_scale ? __half2float(__float2half_rn(d)) : d;
+}
+
+// A warp a super-block; lane l holds elements 8l .. 8l+7.
+__global__ void __launch_bounds__(256) quant_q8_k_kernel(const float* __restrict__ x, i8* __restrict__ xq,
+                                                         float* __restrict__ xd, int16_t* __restrict__ bsums,
+                                                         long long nblocks) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= nblocks) return;
+  const float4 v0 = ((const float4*)(x + b * 256))[2 * lane], v1 = ((const float4*)(x + b * 256))[2 * lane + 1];
+  const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  // the largest magnitude, the first of equal ones, and the value that has it
+  float amax = 0.0f, mx = 0.0f;
+  int idx = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float a = fabsf(v[j]);
+    if (a > amax) { amax = a; mx = v[j]; idx = 8 * lane + j; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float oa = __shfl_xor_sync(0xffffffffu, amax, o), om = __shfl_xor_sync(0xffffffffu, mx, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (oa > amax || (oa == amax && oi < idx)) { amax = oa; mx = om; idx = oi; }
+  }
+  int q[8];
+  float d = 0.0f;
+  if (amax == 0.0f) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = 0;
+  } else {
+    const float iscale = __fdiv_rn(-127.0f, mx);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = min(127, __float2int_rn(__fmul_rn(iscale, v[j])));
+    d = __fdiv_rn(1.0f, iscale);
+  }
+  int s = 0;
+  uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    s += q[j] + q[4 + j];
+    w0 |= (uint32_t)(q[j] & 0xff) << (8 * j);
+    w1 |= (uint32_t)(q[4 + j] & 0xff) << (8 * j);
+  }
+  ((uint2*)(xq + b * 256))[lane] = make_uint2(w0, w1);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  if (!(lane & 1)) bsums[b * 16 + (lane >> 1)] = (int16_t)s;
+  if (lane == 0) xd[b] = d;
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(256) dequant_rows_kernel(const u8* __restrict__ w, int cols, long long row_bytes,
+                                                           const int* __restrict__ row_ids, long long first_row,
+                                                           float* __restrict__ out) {
+  const int i = blockIdx.x;
+  const long long row = row_ids ? (long long)row_ids[i] : first_row + i;
+  const u8* rp = w + row * row_bytes;
+  for (int c = blockIdx.y * 256 + threadIdx.x; c < cols; c += gridDim.y * 256)
+    out[(long long)i * cols + c] = dequant_weight<FMT>(rp, c, ill_iq2xxs_grid, ill_ksigns_iq2xs);
+}
+
+static int launch_pdl(const void* fn, dim3 grid, dim3 block, void** args, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
+  return e == cudaSuccess ? ILL_OK : cuda_fail(e);
+}
+
+}  // namespace ill
+
+using namespace ill;
+
+extern "C" int ill_quant_q8_0(ill_dptr x, ill_dptr xq, ill_dptr xs, ill_dptr xsum, int64_t nblocks, int f16_scale,
+                              ill_stream stream) {
+  if (nblocks < 0 || !x || !xq || !xs) return ILL_ERR_ARG;
+  if ((x & 3) || (xs & 3) || (xsum & 3)) return ILL_ERR_ALIGN;
+  if (nblocks == 0) return ILL_OK;
+  const float* xp = (const float*)(uintptr_t)x;
+  i8* qp = (i8*)(uintptr_t)xq;
+  float* sp = (float*)(uintptr_t)xs;
+  int* sump = (int*)(uintptr_t)xsum;
+  long long nb = nblocks;
+  void* args[] = {&xp, &qp, &sp, &sump, &nb, &f16_scale};
+  return launch_pdl((const void*)quant_q8_0_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), args,
+                    (cudaStream_t)stream);
+}
+
+extern "C" int ill_quant_q8_k(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums, int64_t nblocks,
+                              ill_stream stream) {
+  if (nblocks < 0 || !x || !xq || !xd || !bsums) return ILL_ERR_ARG;
+  if ((x & 15) || (xq & 7) || (xd & 3) || (bsums & 1)) return ILL_ERR_ALIGN;
+  if (nblocks == 0) return ILL_OK;
+  const float* xp = (const float*)(uintptr_t)x;
+  i8* qp = (i8*)(uintptr_t)xq;
+  float* dp = (float*)(uintptr_t)xd;
+  int16_t* bp = (int16_t*)(uintptr_t)bsums;
+  long long nb = nblocks;
+  void* args[] = {&xp, &qp, &dp, &bp, &nb};
+  return launch_pdl((const void*)quant_q8_k_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), args,
+                    (cudaStream_t)stream);
+}
+
+extern "C" int ill_dequant_rows(int fmt, ill_dptr w, int cols, ill_dptr row_ids, int64_t first_row, int nrows,
+                                ill_dptr out, ill_stream stream) {
+  const int bw = fmt_block_weights(fmt);
+  if (!bw || cols <= 0 || cols % bw || nrows < 0 || !w || !out || first_row < 0) return ILL_ERR_ARG;
+  if ((out & 3) || (row_ids & 3)) return ILL_ERR_ALIGN;
+  if (nrows == 0) return ILL_OK;
+  const long long row_bytes = (long long)(cols / bw) * fmt_block_bytes(fmt);
+  const u8* wp = (const u8*)(uintptr_t)w;
+  const int* ids = (const int*)(uintptr_t)row_ids;
+  float* op = (float*)(uintptr_t)out;
+  dim3 grid(nrows, (cols + 2047) / 2048 > 0 ? (cols + 2047) / 2048 : 1);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (fmt) {
+    case ILL_Q8_0: dequant_rows_kernel<ILL_Q8_0><<<grid, 256, 0, st>>>(wp, cols, row_bytes, ids, first_row, op); break;
+    case ILL_Q4_K: dequant_rows_kernel<ILL_Q4_K><<<grid, 256, 0, st>>>(wp, cols, row_bytes, ids, first_row, op); break;
+    case ILL_Q6_K: dequant_rows_kernel<ILL_Q6_K><<<grid, 256, 0, st>>>(wp, cols, row_bytes, ids, first_row, op); break;
+    case ILL_Q2_K: dequant_rows_kernel<ILL_Q2_K><<<grid, 256, 0, st>>>(wp, cols, row_bytes, ids, first_row, op); break;
+    case ILL_IQ2_XXS:
+      dequant_rows_kernel<ILL_IQ2_XXS><<<grid, 256, 0, st>>>(wp, cols, row_bytes, ids, first_row, op);
+      break;
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? ILL_OK : cuda_fail(e);
+}

@@ -1,0 +1,165 @@
+"""Host side of the dense decode path: the reference's src/cuda-dense.lisp,
+mirrored name for name over the C ABI.
+
+The reference drives its kernels from Lisp (`launch`, src/cuda.lisp:323); no
+Lisp implementation is available to run, so this module plays the part of the
+Lisp caller: the same operators (UPLOAD-GMAT, QUANT-Q8, CMAT-MUL, QKV-MUL,
+GLU-MUL, EMBED), the same argument meaning, over libillatio_b200.so.  torch is
+used only to own device memory and streams.
+
+Differences from the reference's device layout, all invisible to callers of
+these operators: matrices stay as raw GGUF blocks (no repack_q8 / repack_q6k),
+and K-quant products take Q8_K activations as the CPU path does (`xs` is then
+one float per 256 and `xsum` one int16 per 16 quants).
+"""
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+from .blocks import BLOCK_BYTES, BLOCK_WEIGHTS, NAMES, Q8_0, row_bytes
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+@dataclass
+class CMat:
+    """A matrix on the device (CMAT, src/cuda-dense.lisp:13-16): raw blocks."""
+    name: str
+    type: int
+    rows: int
+    cols: int
+    qs: torch.Tensor  # uint8, rows * row_bytes
+
+    @property
+    def row_bytes(self):
+        return row_bytes(self.type, self.cols)
+
+    @property
+    def nbytes(self):
+        return self.rows * self.row_bytes
+
+
+def cmat_kquant_p(w):
+    return w.type != Q8_0
+
+
+def upload_gmat(blocks, fmt, rows, cols, name="", device="cuda"):
+    """UPLOAD-GMAT (src/cuda-dense.lisp:75-100): a tensor's raw blocks (uint8
+    numpy array or tensor) to the device, as they are."""
+    if cols % BLOCK_WEIGHTS[fmt]:
+        raise ValueError("%s: %d columns is not a whole number of blocks" % (name, cols))
+    t = torch.as_tensor(blocks).reshape(-1)
+    if t.dtype != torch.uint8 or t.numel() != rows * row_bytes(fmt, cols):
+        raise ValueError("%s: expected %d bytes of %s blocks" % (name, rows * row_bytes(fmt, cols), NAMES[fmt]))
+    return CMat(name, fmt, rows, cols, t.to(device, non_blocking=True).contiguous())
+
+
+@dataclass
+class QAct:
+    """Quantized activations of N tokens (the cctx's xq / xs / xsum)."""
+    kind: str            # "q8" (Q8_0 blocks) or "q8k" (Q8_K super-blocks)
+    xq: torch.Tensor     # int8 [n * cols]
+    xs: torch.Tensor     # float32 per 32 (q8) or per 256 (q8k)
+    xsum: torch.Tensor   # q8: int32 per 32 (or None); q8k: int16 per 16
+
+
+def make_qact(n, kind, device="cuda", want_xsum=False):
+    """Room for N activations in KIND (MAKE-QACT, src/kquant.lisp:506-510)."""
+    if kind == "q8":
+        return QAct(kind, torch.empty(n, dtype=torch.int8, device=device),
+                    torch.empty(n // 32, dtype=torch.float32, device=device),
+                    torch.empty(n // 32, dtype=torch.int32, device=device) if want_xsum else None)
+    return QAct(kind, torch.empty(n, dtype=torch.int8, device=device),
+                torch.empty(n // 256, dtype=torch.float32, device=device),
+                torch.empty(n // 16, dtype=torch.int16, device=device))
+
+
+def matrix_act_kind(w):
+    """MATRIX-ACT-KIND (src/kquant.lisp:532-533)."""
+    return "q8k" if cmat_kquant_p(w) else "q8"
+
+
+def quant_q8(x, act, f16_scale=True):
+    """X (float32, a whole number of blocks) quantized into ACT: the reference's
+    quant_q8 launch (src/cuda-dense.lisp:366,417), in the kind ACT holds."""
+    n = x.numel()
+    if act.kind == "q8":
+        _lib.call("ill_quant_q8_0", _ptr(x), _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum), n // 32,
+                  1 if f16_scale else 0, _stream())
+    else:
+        _lib.call("ill_quant_q8_k", _ptr(x), _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum), n // 256, _stream())
+    return act
+
+
+def cmat_mul(w, act, y, n=1, bias=None, acc=False):
+    """CMAT-MUL (src/cuda-dense.lisp:220-248): Y = W X for N tokens (token t's X
+    at t*cols, its Y at t*rows), or Y += it when ACC."""
+    done = 0
+    while done < n:  # the kernel takes up to 16 tokens a launch
+        k = min(16, n - done)
+        sc = w.cols // (32 if act.kind == "q8" else 256)
+        _lib.call("ill_mv", w.type, _ptr(w.qs), w.rows, w.cols,
+                  act.xq.data_ptr() + done * w.cols, act.xs.data_ptr() + 4 * done * sc,
+                  0 if act.kind == "q8" else act.xsum.data_ptr() + 2 * done * (w.cols // 16),
+                  y.data_ptr() + 4 * done * w.rows, _ptr(bias), 1 if acc else 0, k, _stream())
+        done += k
+    return y
+
+
+def qkv_mul(wq, wk, wv, act, q, k, v, bq=None, bk=None, bv=None, n=1):
+    """QKV-MUL (src/cuda-dense.lisp:309-324): one launch when the three formats
+    agree and there is one token, else three products."""
+    if n == 1 and wq.type == wk.type == wv.type:
+        _lib.call("ill_mv_3", wq.type, _ptr(wq.qs), _ptr(wk.qs), _ptr(wv.qs), wq.rows, wk.rows, wv.rows, wq.cols,
+                  _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum) if act.kind == "q8k" else 0,
+                  _ptr(q), _ptr(k), _ptr(v), _ptr(bq), _ptr(bk), _ptr(bv), _stream())
+    else:
+        cmat_mul(wq, act, q, n, bias=bq)
+        cmat_mul(wk, act, k, n, bias=bk)
+        cmat_mul(wv, act, v, n, bias=bv)
+
+
+def glu_mul(g, u, act, fa, n=1, fb=None):
+    """GLU-MUL (src/cuda-dense.lisp:326-339): silu(G x) * (U x) into FA."""
+    if n == 1 and g.type == u.type:
+        _lib.call("ill_mv_glu", g.type, _ptr(g.qs), _ptr(u.qs), g.rows, g.cols, _ptr(act.xq), _ptr(act.xs),
+                  _ptr(act.xsum) if act.kind == "q8k" else 0, _ptr(fa), _stream())
+        return fa
+    if fb is None:
+        fb = torch.empty_like(fa)
+    cmat_mul(g, act, fa, n)
+    cmat_mul(u, act, fb, n)
+    fa.copy_((fa / (1.0 + torch.exp(-fa))) * fb)  # the reference's swiglu kernel; not on the decode path
+    return fa
+
+
+def embed(emb, tokens, x):
+    """EMBED (src/cuda-dense.lisp:302-307): rows TOKENS (int32 on the device) of
+    EMB as floats in X."""
+    _lib.call("ill_dequant_rows", emb.type, _ptr(emb.qs), emb.cols, _ptr(tokens), 0, tokens.numel(), _ptr(x),
+              _stream())
+    return x
+
+
+def dequant_rows(w, first_row, nrows, out=None):
+    """Rows FIRST_ROW.. of W as floats (the bit-exactness check point)."""
+    if out is None:
+        out = torch.empty(nrows, w.cols, dtype=torch.float32, device=w.qs.device)
+    _lib.call("ill_dequant_rows", w.type, _ptr(w.qs), w.cols, 0, first_row, nrows, _ptr(out), _stream())
+    return out
+
+
+def device_status():
+    """The device status word (0 = no kernel gave up a wait); synchronises."""
+    import ctypes
+    v = ctypes.c_uint(0)
+    _lib.status("ill_device_status", ctypes.byref(v), _stream())
+    return v.value

@@ -1,0 +1,140 @@
+/* illatio_b200.h -- C ABI of libillatio_b200.so.
+ *
+ * A B200 (sm_100a) implementation of illatio's quantized-product hot path: the
+ * dequant-fused matrix x vector product over raw GGUF blocks (Q8_0, Q4_K, Q6_K,
+ * Q2_K, IQ2_XXS) and the routed mixture-of-experts product.  The reference
+ * drives its CUDA kernels from Common Lisp through `launch` (src/cuda.lisp:
+ * 323-352); a host binds these functions instead, with SBCL's
+ * `load-shared-object` / `alien-funcall` exactly as it binds libcuda
+ * (src/cuda.lisp:17-49).
+ *
+ * Conventions (they mirror the reference's driver binding):
+ *   - Device pointers are CUdeviceptr values passed as uint64_t; `ill_stream`
+ *     is a CUstream / cudaStream_t.  0 is the default stream.
+ *   - Every function returns 0 on success or an ILL_ERR_* code; nothing throws,
+ *     aborts or traps.  `ill_error_string` gives the text.
+ *   - Calls only enqueue work on the stream and return; none synchronises
+ *     (except where stated).  The caller owns every buffer; the library
+ *     allocates and frees nothing and keeps no pointer across calls.
+ *   - The caller makes the right device current first (cuCtxSetCurrent /
+ *     cudaSetDevice), as CUDA-CURRENT does (src/cuda.lisp:90-92).
+ *   - Weights are raw GGUF blocks, row-major, exactly as they lie in the file:
+ *     no repacking (the reference's repack_q8 / repack_q6k are not needed).
+ *     The buffer must be readable up to the next 16-byte boundary past its end
+ *     (true of any cuMemAlloc'd buffer).
+ *   - Activations are quantized the way the reference's CPU path quantizes
+ *     them, so results follow the CPU kernels: Q8_0 blocks (int8 + a float
+ *     scale per 32) for Q8_0 weights, Q8_K super-blocks (int8 + a float scale
+ *     per 256 + an int16 sum per 16) for Q4_K / Q6_K / Q2_K / IQ2_XXS weights.
+ */
+#ifndef ILLATIO_B200_H
+#define ILLATIO_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ILL_API __attribute__((visibility("default")))
+
+typedef uint64_t ill_dptr;
+typedef void* ill_stream;
+
+/* weight formats (GGUF block types, src/gguf.lisp:31-40) */
+#define ILL_Q8_0 0    /*  32 weights /  34 bytes */
+#define ILL_Q4_K 1    /* 256 weights / 144 bytes */
+#define ILL_Q6_K 2    /* 256 weights / 210 bytes */
+#define ILL_Q2_K 3    /* 256 weights /  84 bytes */
+#define ILL_IQ2_XXS 4 /* 256 weights /  66 bytes */
+
+#define ILL_OK 0
+#define ILL_ERR_ARG 1         /* a size or flag is out of range, or a required pointer is null */
+#define ILL_ERR_ALIGN 2       /* a pointer or stride is not aligned as documented */
+#define ILL_ERR_UNSUPPORTED 3 /* a shape this build has no kernel for */
+#define ILL_ERR_CUDA 4        /* a CUDA runtime call failed; see ill_last_cuda_error */
+#define ILL_ERR_DEVICE_WAIT 5 /* a kernel gave up a bounded wait (ill_device_status) */
+#define ILL_ERR_TOO_LARGE 6   /* a size exceeds a documented fixed maximum */
+
+/* ---- library --------------------------------------------------------------- */
+
+/* Library version, major*100 + minor. */
+ILL_API int ill_b200_version(void);
+
+/* Text for a status code (static storage).  Plays the part cuGetErrorString
+ * plays for the reference's CU macro (src/cuda.lisp:41-49). */
+ILL_API const char* ill_error_string(int code);
+
+/* The cudaError_t behind the calling thread's most recent ILL_ERR_CUDA. */
+ILL_API int ill_last_cuda_error(void);
+
+/* Bytes per block and weights per block of FMT (0 for an unknown format);
+ * src/gguf.lisp:31-40. */
+ILL_API int ill_block_bytes(int fmt);
+ILL_API int ill_block_weights(int fmt);
+
+/* Reads the current device's status word into *OUT after synchronising STREAM,
+ * and clears it.  0 means no kernel gave up a wait.  (The reference has no
+ * device-side waits; this is the counterpart of checking each driver call,
+ * src/cuda.lisp:41-49.) */
+ILL_API int ill_device_status(unsigned int* out, ill_stream stream);
+
+/* ---- activations ----------------------------------------------------------- */
+
+/* X (nblocks*32 floats) -> Q8_0 blocks: d = amax/127, q = round-half-even(x *
+ * (1/d)) with the unrounded d; XS[b] = d rounded through fp16 when F16_SCALE,
+ * else d itself (ds4's activations).  XSUM (int32 per block, may be 0) gets
+ * each block's sum of quants.  Replaces quant_q8 (src/cuda/dense.cu:84) and
+ * d4_quant (src/cuda/ds4f.cu:35); bit-for-bit QUANTIZE-Q8! (src/tensor.lisp:
+ * 245-262).  XQ must be 16-byte aligned. */
+ILL_API int ill_quant_q8_0(ill_dptr x, ill_dptr xq, ill_dptr xs, ill_dptr xsum, int64_t nblocks, int f16_scale,
+                           ill_stream stream);
+
+/* X (nblocks*256 floats) -> Q8_K super-blocks: XQ int8, XD one float per 256,
+ * BSUMS one int16 per 16 quants.  Bit-for-bit QUANTIZE-Q8K! (src/kquant.lisp:
+ * 130-167); the reference's CUDA path has no Q8_K kernel (it feeds K-quants
+ * Q8_0 blocks, src/cuda/kquant.cu:3-14), which is why its results differ from
+ * its CPU path and these do not. */
+ILL_API int ill_quant_q8_k(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums, int64_t nblocks, ill_stream stream);
+
+/* ---- rows as floats --------------------------------------------------------- */
+
+/* OUT[i*cols ..] = row ROW_IDS[i] (int32, on the device) of the FMT matrix W
+ * dequantized, i < NROWS; with ROW_IDS = 0, rows FIRST_ROW .. FIRST_ROW+NROWS-1.
+ * Bit-for-bit the reference's CPU dequantization (Q8MAT-ROW! src/tensor.lisp:
+ * 354, KMAT-ROW! src/kquant.lisp:466, IQ2XXS-ROW-FLOATS! / Q2K-ROW-FLOATS!
+ * src/iquant.lisp:161,217).  Replaces embed_q8 (src/cuda/dense.cu:53) and
+ * embed_k (src/cuda/kquant.cu:202). */
+ILL_API int ill_dequant_rows(int fmt, ill_dptr w, int cols, ill_dptr row_ids, int64_t first_row, int nrows,
+                             ill_dptr out, ill_stream stream);
+
+/* ---- matrix x vector -------------------------------------------------------- */
+
+/* Y[t*rows + r] (+)= W[r] . X[t] (+ BIAS[r]) for N tokens (1 <= N <= 16):
+ * token t's quants at XQ + t*cols, its scales at XS + t*(cols/32) (Q8_0) or
+ * t*(cols/256) (others), its sums of 16 at XSUM + t*(cols/16) (int16; unused
+ * for Q8_0 and IQ2_XXS and may be 0 then).  ACC != 0 adds into Y.  BIAS may
+ * be 0.  Replaces mv_q8 (src/cuda/dense.cu:194), mv_k (src/cuda/kquant.cu:169)
+ * and d4_mvq8 / d4_mvq8n (src/cuda/ds4f.cu:50,66) behind CMAT-MUL
+ * (src/cuda-dense.lisp:220) and DK-Q8MV (src/cuda-ds4f.lisp:773).  XQ must be
+ * 16-byte aligned and cols a multiple of 256 (32 for Q8_0). */
+ILL_API int ill_mv(int fmt, ill_dptr w, int rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y,
+                   ill_dptr bias, int acc, int n, ill_stream stream);
+
+/* Three products sharing one token's activations in one launch: Yk = Wk . X
+ * (+ Bk).  Replaces mv_q8_3 (src/cuda/dense.cu:210) behind QKV-MUL
+ * (src/cuda-dense.lisp:309); also takes the K-quant formats. */
+ILL_API int ill_mv_3(int fmt, ill_dptr w0, ill_dptr w1, ill_dptr w2, int rows0, int rows1, int rows2, int cols,
+                     ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y0, ill_dptr y1, ill_dptr y2, ill_dptr b0,
+                     ill_dptr b1, ill_dptr b2, ill_stream stream);
+
+/* Y[r] = silu(G[r] . X) * (U[r] . X), silu(g) = g / (1 + exp(-g)), one token.
+ * Replaces mv_q8_glu (src/cuda/dense.cu:230) and mv_k_glu (src/cuda/kquant.cu:
+ * 183) behind GLU-MUL (src/cuda-dense.lisp:326). */
+ILL_API int ill_mv_glu(int fmt, ill_dptr wg, ill_dptr wu, int rows, int cols, ill_dptr xq, ill_dptr xs,
+                       ill_dptr xsum, ill_dptr y, ill_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,200 @@
+"""The CPU oracle against its pins: gguf-py's dequantized floats (the fixtures
+in tests/golden/), fp16 conversion against numpy, and the reference's own
+row-dot criterion (inspect/iquant-test.lisp:45-53,61: |dot - exact| / sum|terms|
+< 1e-6 against the float64 dot of the dequantized weights with the dequantized
+activations)."""
+import os
+
+import numpy as np
+import pytest
+
+from illatio_b200 import blocks as B
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+FMTS = list(range(5))
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_dequant_matches_golden(oracle, fmt):
+    z = np.load(os.path.join(GOLD, "dequant_%s.npz" % B.NAMES[fmt]))
+    blk, want = z["blocks"], z["floats"]
+    bw = B.BLOCK_WEIGHTS[fmt]
+    got = oracle.dequant(fmt, blk.reshape(-1), 1, blk.shape[0] * bw).reshape(-1, bw)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_dequant_matches_gguf_py_live(oracle, fmt):
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    T = gguf.GGMLQuantizationType
+    gg = {B.Q8_0: T.Q8_0, B.Q4_K: T.Q4_K, B.Q6_K: T.Q6_K, B.Q2_K: T.Q2_K, B.IQ2_XXS: T.IQ2_XXS}[fmt]
+    nb = 20000
+    blk = B.synth_blocks(fmt, nb, seed=77 + fmt)
+    bw = B.BLOCK_WEIGHTS[fmt]
+    got = oracle.dequant(fmt, blk.reshape(-1), 1, nb * bw).reshape(nb, bw)
+    want = quants.dequantize(blk, gg).astype(np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_iq2xxs_tables_match_gguf_py(oracle):
+    """The grid and sign tables (taken from the reference) against gguf-py's."""
+    pytest.importorskip("gguf")
+    from gguf import quants
+    q = quants.IQ2_XXS
+    q.init_grid()
+    grid = np.asarray(q.grid).reshape(256, 8)
+    # dequantize one block per grid index with d = 1, LS = 0, no signs: 0.125 * grid
+    blk = np.zeros((256, 66), np.uint8)
+    blk[:, 0:2] = np.array([1.0], np.float16).view(np.uint8)
+    blk[:, 2] = np.arange(256)
+    got = oracle.dequant(B.IQ2_XXS, blk.reshape(-1), 256, 256)[:, :8]
+    assert np.array_equal(got, grid.astype(np.float32) * 0.125)
+
+
+def test_half_conversions(oracle):
+    h = np.arange(65536, dtype=np.uint16)
+    want = h.view(np.float16).astype(np.float32)
+    got = np.array([oracle.half_to_single(int(v)) for v in h[::7]], np.float32)
+    w = want[::7]
+    fin = np.isfinite(w)
+    assert np.array_equal(got[fin].view(np.uint32), w[fin].view(np.uint32))
+    rng = np.random.default_rng(3)
+    xs = np.concatenate([rng.standard_normal(4000).astype(np.float32) * s for s in (1e-7, 1e-4, 1.0, 300.0, 7e4)])
+    xs = np.concatenate([xs, np.array([0.0, -0.0, 65504.0, 65520.0, 6.1e-5, 5.96e-8, 2.98e-8, 2.99e-8], np.float32)])
+    with np.errstate(over="ignore"):
+        want16 = xs.astype(np.float16).view(np.uint16)
+    got16 = np.array([oracle.single_to_half(float(v)) for v in xs], np.uint16)
+    assert np.array_equal(got16, want16)
+
+
+def test_quantize_q8_0(oracle):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal(32 * 64).astype(np.float32)
+    x[32:64] = 0.0
+    q, s = oracle.quantize_q8_0(x, f16_scale=False)
+    amax = np.abs(x.reshape(-1, 32)).max(1)
+    assert np.array_equal(s, (amax / np.float32(127.0)).astype(np.float32))
+    assert (q[32:64] == 0).all() and s[1] == 0.0
+    assert np.abs(q.reshape(-1, 32)).max(1)[0] == 127
+    q2, s2 = oracle.quantize_q8_0(x, f16_scale=True)
+    assert np.array_equal(q, q2)
+    assert np.array_equal(s2, s.astype(np.float16).astype(np.float32))
+    # round half to even: x/d exactly k + 0.5
+    x = np.zeros(32, np.float32)
+    x[0] = 127.0
+    x[1:5] = [0.5, 1.5, 2.5, -2.5]
+    q, _ = oracle.quantize_q8_0(x, f16_scale=False)
+    assert list(q[:5]) == [127, 0, 2, 2, -2]
+
+
+def test_quantize_q8k(oracle):
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal(256 * 8).astype(np.float32)
+    x[256:512] = 0.0
+    x[512] = 3.0
+    x[513] = -3.0  # equal magnitudes: the first one sets the sign
+    x[514:768] *= 0.1
+    q, d, bs = oracle.quantize_q8k(x)
+    assert d[1] == 0.0 and (q[256:512] == 0).all() and (bs[16:32] == 0).all()
+    assert q[512] == -127 and q[513] == 127 and d[2] < 0
+    assert np.array_equal(bs, q.reshape(-1, 16).astype(np.int32).sum(1))
+    # the block's largest magnitude maps to -127 and d is the inverse of -127/max
+    for b in (0, 3, 4):
+        xb = x[256 * b:256 * (b + 1)]
+        mx = xb[np.argmax(np.abs(xb))]
+        isc = np.float32(-127.0) / np.float32(mx)
+        assert d[b] == np.float32(1.0) / isc
+        assert q[256 * b + np.argmax(np.abs(xb))] == -127
+
+
+def _exact_dot(oracle, fmt, w, rows, cols, act):
+    xq, xs, _ = act
+    per = 32 if fmt == B.Q8_0 else 256
+    xf = xq.astype(np.float64) * np.repeat(xs.astype(np.float64), per)
+    wf = oracle.dequant(fmt, w, rows, cols).astype(np.float64)
+    return wf @ xf, np.abs(wf) @ np.abs(xf)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_row_dot_criterion(oracle, fmt):
+    rows, cols = 64, 2048
+    w = B.synth_matrix(fmt, rows, cols, seed=11 + fmt)
+    rng = np.random.default_rng(7)  # U(-1,1), seed 7: inspect/iquant-test.lisp:37-38
+    x = rng.uniform(-1, 1, cols).astype(np.float32)
+    act = oracle.quantize_act(fmt, x)
+    got = oracle.matvec(fmt, w, rows, cols, act)[0]
+    exact, terms = _exact_dot(oracle, fmt, w, rows, cols, act)
+    assert (np.abs(got - exact) / terms).max() < 1e-6
+
+
+@pytest.mark.parametrize("fmt", [B.Q2_K, B.IQ2_XXS])
+def test_x86_order_close_to_portable(oracle, fmt):
+    rows, cols = 32, 4096
+    w = B.synth_matrix(fmt, rows, cols, seed=21 + fmt)
+    x = np.random.default_rng(8).standard_normal(cols).astype(np.float32)
+    act = oracle.quantize_act(fmt, x)
+    port = oracle.matvec(fmt, w, rows, cols, act)[0]
+    rb = B.row_bytes(fmt, cols)
+    x86 = np.array([oracle.row_dot_x86(fmt, w[r * rb:(r + 1) * rb], cols, act) for r in range(rows)], np.float32)
+    _, terms = _exact_dot(oracle, fmt, w, rows, cols, act)
+    assert (np.abs(port - x86) / terms).max() < 1e-6
+
+
+def test_matvec_threads_and_bias(oracle):
+    rows, cols = 37, 512
+    w = B.synth_matrix(B.Q4_K, rows, cols, seed=31)
+    x = np.random.default_rng(9).standard_normal(2 * cols).astype(np.float32)
+    act = oracle.quantize_act(B.Q4_K, x)
+    bias = np.arange(rows, dtype=np.float32)
+    a = oracle.matvec(B.Q4_K, w, rows, cols, act, n=2, bias=bias, threads=1)
+    b = oracle.matvec(B.Q4_K, w, rows, cols, act, n=2, bias=bias, threads=5)
+    assert np.array_equal(a, b)  # 1 thread = many (inspect/consistency-test.lisp:48-51)
+    c = oracle.matvec(B.Q4_K, w, rows, cols, act, n=2)
+    assert np.array_equal(a, c + bias)
+
+
+def test_route(oracle):
+    rng = np.random.default_rng(10)
+    logits = rng.standard_normal((5, 64)).astype(np.float32)
+    logits[0, 7] = logits[0, 3] = 4.0  # a tie: the earlier expert first
+    for mode in (0, 2):
+        sel, w = oracle.route(logits, 6, mode=mode, scale=1.5)
+        assert list(sel[0][:2]) == [3, 7]
+        p = 1 / (1 + np.exp(-logits.astype(np.float64))) if mode == 2 else np.sqrt(np.log1p(np.exp(logits.astype(np.float64))))
+        for t in range(5):
+            order = np.argsort(-p[t], kind="stable")[:6]
+            assert list(sel[t]) == list(order)
+            np.testing.assert_allclose(w[t], p[t][order] / p[t][order].sum() * 1.5, rtol=1e-5)
+    bias = np.zeros(64, np.float32)
+    bias[60] = 10.0
+    sel, w = oracle.route(logits, 6, mode=2, bias=bias)
+    assert (sel[:, 0] == 60).all()  # biased scores pick, unbiased probabilities weigh
+    assert abs(w.sum(1) - 1).max() < 1e-5
+
+
+def test_moe_routed_composition(oracle):
+    """orc_moe_routed against the same steps taken one at a time."""
+    d, ff, ne, nu = 512, 256, 8, 3
+    gate = B.synth_matrix(B.IQ2_XXS, ne * ff, d, seed=41)
+    up = B.synth_matrix(B.IQ2_XXS, ne * ff, d, seed=42)
+    down = B.synth_matrix(B.Q2_K, ne * d, ff, seed=43)
+    x = np.random.default_rng(11).standard_normal(d).astype(np.float32)
+    sel = np.array([5, 0, 6], np.int32)
+    wts = np.array([0.5, 0.3, 0.2], np.float32)
+    clamp = 0.05
+    moe, mid = oracle.moe_routed(d, ff, B.IQ2_XXS, B.Q2_K, gate, up, down, x, sel, wts, clamp, threads=3, want_mid=True)
+    act = oracle.quantize_q8k(x)
+    grb, drb = B.row_bytes(B.IQ2_XXS, d), B.row_bytes(B.Q2_K, ff)
+    want = np.zeros(d, np.float32)
+    for i, e in enumerate(sel):
+        g = oracle.matvec(B.IQ2_XXS, gate[e * ff * grb:(e + 1) * ff * grb], ff, d, act)[0]
+        u = oracle.matvec(B.IQ2_XXS, up[e * ff * grb:(e + 1) * ff * grb], ff, d, act)[0]
+        g = np.minimum(g, np.float32(clamp))
+        u = np.clip(u, -np.float32(clamp), np.float32(clamp))
+        silu = np.array([oracle.lib().orc_silu(float(v)) for v in g], np.float32)
+        m = ((silu * u).astype(np.float32) * wts[i]).astype(np.float32)
+        assert np.array_equal(m, mid[i * ff:(i + 1) * ff])
+        dn = oracle.matvec(B.Q2_K, down[e * d * drb:(e + 1) * d * drb], d, ff, oracle.quantize_q8k(m))[0]
+        want = (want + dn).astype(np.float32)
+    assert np.array_equal(moe, want)
