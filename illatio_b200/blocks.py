@@ -46,3 +46,21 @@ def synth_matrix(fmt, rows, cols, seed):
     """A rows x cols matrix as a flat uint8 array of raw row-major blocks."""
     nb = rows * (cols // BLOCK_WEIGHTS[fmt])
     return synth_blocks(fmt, nb, seed).reshape(-1)
+
+
+def synth_matrix_torch(fmt, rows, cols, seed, device="cuda"):
+    """synth_matrix drawn on the device with torch's generator (same
+    distributions, different stream of numbers): for matrices too large to be
+    worth drawing on the host."""
+    import torch
+    nb = rows * (cols // BLOCK_WEIGHTS[fmt])
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    blk = torch.randint(0, 256, (nb, BLOCK_BYTES[fmt]), dtype=torch.uint8, device=device, generator=g)
+    if fmt == Q8_0:
+        q = torch.randint(-127, 128, (nb, 32), dtype=torch.int8, device=device, generator=g)
+        blk[:, 2:34] = q.view(torch.uint8)
+    for off in SCALE_OFFSETS[fmt]:
+        d = (torch.randn(nb, device=device, generator=g).abs() * SCALE_SIGMA[fmt]).to(torch.float16)
+        blk[:, off:off + 2] = d.view(torch.uint8).reshape(nb, 2)
+    return blk.reshape(-1)

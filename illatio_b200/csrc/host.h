@@ -11,4 +11,11 @@ int cuda_fail(cudaError_t e);
 // library; no allocation).  Null if the address cannot be taken.
 unsigned int* device_status_word();
 
+// Whether launches carry the programmatic-stream-serialization attribute.
+bool pdl_enabled();
+
+// Launch FN (grid, block, dynamic shared bytes) on ST with ARGS, with the
+// programmatic-dependent-launch attribute when enabled.
+int launch_kernel(const void* fn, dim3 grid, dim3 block, size_t smem, void** args, cudaStream_t st);
+
 }  // namespace ill

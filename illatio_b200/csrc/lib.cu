@@ -25,9 +25,33 @@ unsigned int* device_status_word() {
   return p;
 }
 
+static int g_pdl = 1;
+bool pdl_enabled() { return g_pdl != 0; }
+
+int launch_kernel(const void* fn, dim3 grid, dim3 block, size_t smem, void** args, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = g_pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
+  return e == cudaSuccess ? ILL_OK : cuda_fail(e);
+}
+
 }  // namespace ill
 
 using namespace ill;
+
+extern "C" int ill_set_pdl(int on) {
+  const int prev = g_pdl;
+  g_pdl = on ? 1 : 0;
+  return prev;
+}
 
 extern "C" int ill_b200_version(void) { return 100; }
 

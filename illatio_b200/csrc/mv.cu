@@ -336,18 +336,9 @@ static int launch_mv_t(const MvParams& p, const MvPlan& pl, int grid_x, int grid
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
     if (e != cudaSuccess) return cuda_fail(e);
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid_x, grid_y, 1);
-  cfg.blockDim = dim3(MV_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = pl.smem;
-  cfg.stream = st;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = at;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, k, p);
-  return e == cudaSuccess ? ILL_OK : cuda_fail(e);
+  MvParams pp = p;
+  void* args[] = {&pp};
+  return launch_kernel((const void*)k, dim3(grid_x, grid_y, 1), dim3(MV_THREADS, 1, 1), pl.smem, args, st);
 }
 
 template <int FMT>
@@ -382,7 +373,7 @@ static int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* 
   if (!bw || nmat < 1 || nmat > MV_MAX_MATS || cols <= 0 || cols % (bw == 32 ? 32 : 256)) return ILL_ERR_ARG;
   if (n < 1 || n > MV_MAX_TOK || nseg < 1 || nseg > 65535) return ILL_ERR_ARG;
   if (!xq || !xs || (needs_bsums(fmt) && !xsum)) return ILL_ERR_ARG;
-  if (xq & 15 || xs & 3 || xsum & 7) return ILL_ERR_ALIGN;
+  if (xq & 15 || xs & 3 || xsum & 1) return ILL_ERR_ALIGN;
   long long total_rows = 0;
   for (int i = 0; i < nmat; ++i) {
     if (rows[i] <= 0 || !y[i] || (!ptrs && !w[i])) return ILL_ERR_ARG;
@@ -455,7 +446,8 @@ extern "C" int ill_mv_3(int fmt, ill_dptr w0, ill_dptr w1, ill_dptr w2, int rows
                         ill_dptr b1, ill_dptr b2, ill_stream stream) {
   const ill_dptr ws[3] = {w0, w1, w2}, ys[3] = {y0, y1, y2}, bs[3] = {b0, b1, b2};
   const int rs[3] = {rows0, rows1, rows2};
-  return mv_common(fmt, MODE_PLAIN, 3, ws, rs, cols, xq, xs, xsum, ys, bs, 0, 1, 0, 1, 0, 0, 0, 0, 0, 0.0f, stream);
+  const int nmat = (rows2 == 0 && !w2) ? 2 : 3;
+  return mv_common(fmt, MODE_PLAIN, nmat, ws, rs, cols, xq, xs, xsum, ys, bs, 0, 1, 0, 1, 0, 0, 0, 0, 0, 0.0f, stream);
 }
 
 extern "C" int ill_mv_glu(int fmt, ill_dptr wg, ill_dptr wu, int rows, int cols, ill_dptr xq, ill_dptr xs,

@@ -98,20 +98,6 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(const u8* __restrict_
     out[(long long)i * cols + c] = dequant_weight<FMT>(rp, c, ill_iq2xxs_grid, ill_ksigns_iq2xs);
 }
 
-static int launch_pdl(const void* fn, dim3 grid, dim3 block, void** args, cudaStream_t st) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.stream = st;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = at;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
-  return e == cudaSuccess ? ILL_OK : cuda_fail(e);
-}
-
 }  // namespace ill
 
 using namespace ill;
@@ -127,8 +113,8 @@ extern "C" int ill_quant_q8_0(ill_dptr x, ill_dptr xq, ill_dptr xs, ill_dptr xsu
   int* sump = (int*)(uintptr_t)xsum;
   long long nb = nblocks;
   void* args[] = {&xp, &qp, &sp, &sump, &nb, &f16_scale};
-  return launch_pdl((const void*)quant_q8_0_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), args,
-                    (cudaStream_t)stream);
+  return launch_kernel((const void*)quant_q8_0_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), 0, args,
+                       (cudaStream_t)stream);
 }
 
 extern "C" int ill_quant_q8_k(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums, int64_t nblocks,
@@ -142,8 +128,8 @@ extern "C" int ill_quant_q8_k(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsu
   int16_t* bp = (int16_t*)(uintptr_t)bsums;
   long long nb = nblocks;
   void* args[] = {&xp, &qp, &dp, &bp, &nb};
-  return launch_pdl((const void*)quant_q8_k_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), args,
-                    (cudaStream_t)stream);
+  return launch_kernel((const void*)quant_q8_k_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), 0, args,
+                       (cudaStream_t)stream);
 }
 
 extern "C" int ill_dequant_rows(int fmt, ill_dptr w, int cols, ill_dptr row_ids, int64_t first_row, int nrows,

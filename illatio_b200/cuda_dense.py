@@ -121,6 +121,12 @@ def qkv_mul(wq, wk, wv, act, q, k, v, bq=None, bk=None, bv=None, n=1):
         _lib.call("ill_mv_3", wq.type, _ptr(wq.qs), _ptr(wk.qs), _ptr(wv.qs), wq.rows, wk.rows, wv.rows, wq.cols,
                   _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum) if act.kind == "q8k" else 0,
                   _ptr(q), _ptr(k), _ptr(v), _ptr(bq), _ptr(bk), _ptr(bv), _stream())
+    elif n == 1 and wq.type == wk.type:
+        # Q4_K_M files keep V in Q6_K: Q and K in one launch, V in its own
+        _lib.call("ill_mv_3", wq.type, _ptr(wq.qs), _ptr(wk.qs), 0, wq.rows, wk.rows, 0, wq.cols,
+                  _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum) if act.kind == "q8k" else 0,
+                  _ptr(q), _ptr(k), 0, _ptr(bq), _ptr(bk), 0, _stream())
+        cmat_mul(wv, act, v, n, bias=bv)
     else:
         cmat_mul(wq, act, q, n, bias=bq)
         cmat_mul(wk, act, k, n, bias=bk)

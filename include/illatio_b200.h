@@ -79,6 +79,14 @@ ILL_API int ill_block_weights(int fmt);
  * src/cuda.lisp:41-49.) */
 ILL_API int ill_device_status(unsigned int* out, ill_stream stream);
 
+/* Programmatic dependent launch: when ON (the default), each kernel is launched
+ * so that it may start streaming its weights while the previous kernel of the
+ * stream drains; it still waits for that kernel's results before it reads its
+ * activations or writes.  OFF launches plainly.  Returns the previous setting.
+ * (No counterpart in the reference, which launches with cuLaunchKernel,
+ * src/cuda.lisp:345-350.) */
+ILL_API int ill_set_pdl(int on);
+
 /* ---- activations ----------------------------------------------------------- */
 
 /* X (nblocks*32 floats) -> Q8_0 blocks: d = amax/127, q = round-half-even(x *
@@ -122,8 +130,9 @@ ILL_API int ill_mv(int fmt, ill_dptr w, int rows, int cols, ill_dptr xq, ill_dpt
                    ill_dptr bias, int acc, int n, ill_stream stream);
 
 /* Three products sharing one token's activations in one launch: Yk = Wk . X
- * (+ Bk).  Replaces mv_q8_3 (src/cuda/dense.cu:210) behind QKV-MUL
- * (src/cuda-dense.lisp:309); also takes the K-quant formats. */
+ * (+ Bk).  With W2 = 0 and ROWS2 = 0, two products.  Replaces mv_q8_3
+ * (src/cuda/dense.cu:210) behind QKV-MUL (src/cuda-dense.lisp:309); also takes
+ * the K-quant formats. */
 ILL_API int ill_mv_3(int fmt, ill_dptr w0, ill_dptr w1, ill_dptr w2, int rows0, int rows1, int rows2, int cols,
                      ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y0, ill_dptr y1, ill_dptr y2, ill_dptr b0,
                      ill_dptr b1, ill_dptr b2, ill_stream stream);
