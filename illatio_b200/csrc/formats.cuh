@@ -56,6 +56,22 @@ __device__ __forceinline__ void ld_words(const u8* p, uint32_t (&out)[N]) {
     prev = next;
   }
 }
+// words at a pointer known to be 4-byte (A4) or 16-byte (A16) aligned
+template <int N, int AL>
+__device__ __forceinline__ void ld_words_al(const u8* p, uint32_t (&out)[N]) {
+  if constexpr (AL >= 16 && N % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      const uint4 v = ((const uint4*)p)[i];
+      out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+    }
+  } else if constexpr (AL >= 4) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = ((const uint32_t*)p)[i];
+  } else {
+    ld_words<N>(p, out);
+  }
+}
 __device__ __forceinline__ uint32_t ld_u16(const u8* p) { return *(const u16*)p; }  // p is 2-byte aligned
 
 template <int N>
@@ -65,6 +81,13 @@ __device__ __forceinline__ void ld_x128(const i8* p, uint32_t* out) {  // N uint
     uint4 v = ((const uint4*)p)[i];
     out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
   }
+}
+
+// unsigned bytes of A times signed bytes of B, accumulated
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
 }
 
 // ---- Q8_0: unit = block ------------------------------------------------------
@@ -78,6 +101,7 @@ __device__ __forceinline__ void load_x(XReg<ILL_Q8_0>& x, const ActS& a, int u) 
   ld_x128<2>(a.q + 32 * u, x.q);
   x.s = a.s[u];
 }
+template <int AL = 1>
 __device__ __forceinline__ void load_w(WReg<ILL_Q8_0>& w, const u8* row, int u) {
   const u8* p = row + 34 * u;
   w.d = h2f(ld_u16(p));
@@ -102,11 +126,12 @@ __device__ __forceinline__ void load_x(XReg<ILL_Q4_K>& x, const ActS& a, int u) 
   x.bs0 = (int)(short)(b.x & 0xffff) + (b.x >> 16);
   x.bs1 = (int)(short)(b.y & 0xffff) + (b.y >> 16);
 }
+template <int AL = 1>
 __device__ __forceinline__ void load_w(WReg<ILL_Q4_K>& w, const u8* row, int u) {
   const int i = u >> 2, k = u & 3;
   const u8* p = row + 144 * i;
   uint32_t h[4];  // d|dmin, then the 12 scale bytes
-  ld_words<4>(p, h);
+  ld_words_al<4, AL>(p, h);
   w.d = h2f(h[0] & 0xffff);
   w.dmin = h2f(h[0] >> 16);
   // get_scale_min_k4 for groups j = 2k, 2k+1 (src/kquant.lisp:64-72)
@@ -122,16 +147,17 @@ __device__ __forceinline__ void load_w(WReg<ILL_Q4_K>& w, const u8* row, int u) 
     w.m0 = (lo0 >> 4) | (((h[2] >> (sh + 6)) & 3) << 4);
     w.m1 = (lo1 >> 4) | (((h[2] >> (sh + 14)) & 3) << 4);
   }
-  ld_words<8>(p + 16 + 32 * k, w.q);
+  ld_words_al<8, AL>(p + 16 + 32 * k, w.q);
 }
 __device__ __forceinline__ float dot(const WReg<ILL_Q4_K>& w, const XReg<ILL_Q4_K>& x) {
+  // high nibbles stay in place (16 * q as an unsigned byte); the 16 comes out of the sum
   int lo = 0, hi = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     lo = __dp4a((int)(w.q[i] & 0x0F0F0F0Fu), (int)x.q[i], lo);
-    hi = __dp4a((int)((w.q[i] >> 4) & 0x0F0F0F0Fu), (int)x.q[8 + i], hi);
+    hi = dp4a_us(w.q[i] & 0xF0F0F0F0u, (int)x.q[8 + i], hi);
   }
-  const int isum = lo * w.sc0 + hi * w.sc1, imin = w.m0 * x.bs0 + w.m1 * x.bs1;
+  const int isum = lo * w.sc0 + (hi >> 4) * w.sc1, imin = w.m0 * x.bs0 + w.m1 * x.bs1;
   return (x.d * w.d) * (float)isum - (x.d * w.dmin) * (float)imin;
 }
 
@@ -150,6 +176,7 @@ __device__ __forceinline__ void load_x(XReg<ILL_Q6_K>& x, const ActS& a, int u) 
   }
   x.d = a.s[i];
 }
+template <int AL = 1>
 __device__ __forceinline__ void load_w(WReg<ILL_Q6_K>& w, const u8* row, int u) {
   const int i = u >> 2, c = (u >> 1) & 1, hq = u & 1;
   const u8* p = row + 210 * i;
@@ -200,13 +227,15 @@ __device__ __forceinline__ void load_x(XReg<ILL_Q2_K>& x, const ActS& a, int u) 
   }
   x.d = a.s[i];
 }
+template <int AL = 1>
 __device__ __forceinline__ void load_w(WReg<ILL_Q2_K>& w, const u8* row, int u) {
   const int i = u >> 2, h = (u >> 1) & 1, half = u & 1;
   const u8* p = row + 84 * i;
   uint32_t s[2], dd[1];
-  ld_words<2>(p + 8 * h, s);  // the half's eight scale bytes
-  ld_words<4>(p + 16 + 32 * h + 16 * half, w.q);
-  ld_words<1>(p + 80, dd);
+  constexpr int A = AL >= 4 ? 4 : 1;  // an 84-byte block keeps 4-byte alignment at best
+  ld_words_al<2, A>(p + 8 * h, s);  // the half's eight scale bytes
+  ld_words_al<4, A>(p + 16 + 32 * h + 16 * half, w.q);
+  ld_words_al<1, A>(p + 80, dd);
   const uint32_t lo = s[0] >> (8 * half), hi = s[1] >> (8 * half);
   w.sc[0] = lo & 0xff; w.sc[1] = (lo >> 16) & 0xff; w.sc[2] = hi & 0xff; w.sc[3] = (hi >> 16) & 0xff;
   w.d = h2f(dd[0] & 0xffff);
@@ -237,6 +266,7 @@ __device__ __forceinline__ void load_x(XReg<ILL_IQ2_XXS>& x, const ActS& a, int 
   ld_x128<2>(a.q + 32 * u, x.q);
   x.d = a.s[u >> 3];
 }
+template <int AL = 1>
 __device__ __forceinline__ void load_w(WReg<ILL_IQ2_XXS>& w, const u8* row, int u, const IqTables& t) {
   const u8* p = row + 66 * (u >> 3);
   uint32_t v[2];

@@ -18,4 +18,14 @@ bool pdl_enabled();
 // programmatic-dependent-launch attribute when enabled.
 int launch_kernel(const void* fn, dim3 grid, dim3 block, size_t smem, void** args, cudaStream_t st);
 
+enum { MODE_PLAIN = 0, MODE_GLU = 1, MODE_MOE_GLU = 2 };
+
+// The matvec family's common entry (mv.cu): NMAT matrices of one format sharing
+// the activations; NSEG segments when PTRS (a device table of base addresses)
+// is given.  See ill_mv / ill_moe_mv for the argument meaning.
+int mv_common(int fmt, int mode, int nmat, const unsigned long long* w, const int* rows, int cols,
+              unsigned long long xq, unsigned long long xs, unsigned long long xsum, const unsigned long long* y,
+              const unsigned long long* bias, int acc, int n, unsigned long long ptrs, int nseg, long long add,
+              long long up_add, int x_seg, long long y_seg, unsigned long long seg_w, float clamp, void* stream);
+
 }  // namespace ill

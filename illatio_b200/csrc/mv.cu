@@ -24,7 +24,7 @@ constexpr int MV_THREADS = 256;
 constexpr int MV_MAX_MATS = 3;
 constexpr int MV_MAX_TOK = 16;
 
-enum { MODE_PLAIN = 0, MODE_GLU = 1, MODE_MOE_GLU = 2 };
+
 
 struct MvParams {
   // matrices (PLAIN: up to three sharing the activations; GLU: gate, up)
@@ -42,6 +42,7 @@ struct MvParams {
   int n;                 // tokens
   int acc;
   int rows_per_tile, lanes_per_row;
+  int tps, slots;        // one-token kernel: threads per row slot, row slots
   uint32_t stage_bytes;  // bytes of one stage (one matrix' part of it in GLU modes)
   int nstages;
   uint32_t x_bytes;      // shared bytes of the activation region
@@ -77,7 +78,7 @@ __device__ __forceinline__ TileRef tile_ref(const MvParams& p, int tile, const u
 }
 
 template <int FMT, int MODE, int NT>
-__global__ void __launch_bounds__(MV_THREADS) mv_kernel(const MvParams p) {
+__global__ void __launch_bounds__(MV_THREADS) mvn_kernel(const MvParams p) {
   extern __shared__ __align__(128) u8 smem[];
   constexpr bool GLU = MODE != MODE_PLAIN;
   constexpr bool IQ = FMT == ILL_IQ2_XXS;
@@ -266,6 +267,174 @@ __global__ void __launch_bounds__(MV_THREADS) mv_kernel(const MvParams p) {
   }
 }
 
+// ---- one token: activations in registers ---------------------------------------
+//
+// Thread t belongs to row slot t / tps and owns units j, j + tps, ... (j = t %
+// tps) of every row its slot takes: the activations of those units are loaded
+// from global memory once, into registers, and reused for every row.  Per tile
+// a thread writes one partial sum per row to shared memory; after the tile's
+// barrier the warps add each row's partials and write the outputs.
+template <int FMT, int MODE, int UPT, int AL>
+__global__ void __launch_bounds__(MV_THREADS) mv1_kernel(const MvParams p) {
+  extern __shared__ __align__(128) u8 smem[];
+  constexpr bool GLU = MODE != MODE_PLAIN;
+  constexpr bool IQ = FMT == ILL_IQ2_XXS;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int z = blockIdx.y;
+
+  const uint32_t stage_stride = p.stage_bytes * (GLU ? 2u : 1u);
+  u8* stage0 = smem;
+  u8* after = stage0 + (size_t)stage_stride * p.nstages;
+  float* part = (float*)after;  // [2 buffers][GLU ? 2 : 1][rows_per_tile * tps]
+  const int part_n = p.rows_per_tile * p.tps;
+  u8* after2 = after + (size_t)part_n * 4 * 2 * (GLU ? 2 : 1);
+  uint2* iq_grid = (uint2*)after2;
+  uint2* iq_smask = iq_grid + 256;
+  uint64_t* full = (uint64_t*)(after2 + (IQ ? 3072 : 0));
+
+  const u8* wbase[MV_MAX_MATS];
+  if (p.ptrs) {
+    const u8* b = (const u8*)(uintptr_t)p.ptrs[z] + p.add;
+    wbase[0] = b;
+    wbase[1] = b + p.up_add;
+    wbase[2] = b;
+  } else {
+#pragma unroll
+    for (int i = 0; i < MV_MAX_MATS; ++i) wbase[i] = p.w[i];
+  }
+  const int ntiles = p.tile0[p.nmat];
+  const int first = blockIdx.x, step = gridDim.x;
+
+  auto issue = [&](int tile, int s) {
+    const TileRef t = tile_ref(p, tile, wbase);
+    const uint32_t len = (uint32_t)t.nrows * (uint32_t)p.row_bytes;
+    u8* dst = stage0 + (size_t)s * stage_stride;
+    const uintptr_t a0 = (uintptr_t)t.g & ~(uintptr_t)15;
+    const uint32_t bytes = (uint32_t)((((uintptr_t)t.g + len + 15) & ~(uintptr_t)15) - a0);
+    if (GLU) {
+      const u8* g2 = wbase[1] + (long long)t.row0 * p.row_bytes;
+      const uintptr_t b0 = (uintptr_t)g2 & ~(uintptr_t)15;
+      const uint32_t bytes2 = (uint32_t)((((uintptr_t)g2 + len + 15) & ~(uintptr_t)15) - b0);
+      mbar_expect_tx(&full[s], bytes + bytes2);
+      bulk_g2s(dst, (const void*)a0, bytes, &full[s]);
+      bulk_g2s(dst + p.stage_bytes, (const void*)b0, bytes2, &full[s]);
+    } else {
+      mbar_expect_tx(&full[s], bytes);
+      bulk_g2s(dst, (const void*)a0, bytes, &full[s]);
+    }
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < p.nstages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+    for (int s = 0; s < p.nstages; ++s) {  // weights do not depend on the previous kernel
+      const int tile = first + s * step;
+      if (tile < ntiles) issue(tile, s);
+    }
+  }
+  if (IQ) iq_tables_fill(iq_grid, iq_smask, ill_iq2xxs_grid, ill_ksigns_iq2xs);
+  pdl_launch_dependents();
+  pdl_wait();  // the activations may come from the previous kernel
+
+  const int slot = tid / p.tps, j = tid - slot * p.tps;
+  const bool active = slot < p.slots;
+  XReg<FMT> x[UPT];
+  {
+    const long long tok0 = (long long)z * p.x_seg;
+    const int nsc = FMT == ILL_Q8_0 ? p.cols / 32 : p.cols / 256;
+    ActS a;
+    a.q = p.xq + tok0 * p.cols;
+    a.s = p.xs + tok0 * nsc;
+    a.bs = p.xsum + tok0 * (p.cols / 16);
+#pragma unroll
+    for (int k = 0; k < UPT; ++k) {
+      const int u = j + k * p.tps;
+      if (active && u < p.units) load_x(x[k], a, u);
+    }
+  }
+  IqTables iqt;
+  iqt.grid = iq_grid;
+  iqt.smask = iq_smask;
+  __syncthreads();  // barriers initialised, tables filled
+
+  int it = 0, pp = 0;
+  bool failed = false;
+  for (int tile = first; tile < ntiles; tile += step, ++it, pp ^= 1) {
+    const int s = it % p.nstages;
+    const uint32_t parity = (uint32_t)(it / p.nstages) & 1u;
+    const bool ok = mbar_wait(&full[s], parity, p.status, ST_MV_WAIT + FMT);
+    const TileRef t = tile_ref(p, tile, wbase);
+    const u8* sbase = stage0 + (size_t)s * stage_stride;
+    const u8* rows_s = sbase + ((uintptr_t)t.g & 15);
+    const u8* rows_u = sbase + p.stage_bytes + ((uintptr_t)(wbase[1] + (long long)t.row0 * p.row_bytes) & 15);
+    float* pa = part + (size_t)pp * part_n * (GLU ? 2 : 1);
+
+    if (ok && active) {
+      for (int r = slot; r < t.nrows; r += p.slots) {
+        const u8* rowp = rows_s + (size_t)r * p.row_bytes;
+        const u8* rowu = rows_u + (size_t)r * p.row_bytes;
+        float sum = 0.0f, sum2 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < UPT; ++k) {
+          const int u = j + k * p.tps;
+          if (u < p.units) {
+            WReg<FMT> w;
+            if constexpr (IQ) load_w<AL>(w, rowp, u, iqt); else load_w<AL>(w, rowp, u);
+            sum += dot(w, x[k]);
+            if constexpr (GLU) {
+              WReg<FMT> w2;
+              if constexpr (IQ) load_w<AL>(w2, rowu, u, iqt); else load_w<AL>(w2, rowu, u);
+              sum2 += dot(w2, x[k]);
+            }
+          }
+        }
+        pa[r * p.tps + j] = sum;
+        if constexpr (GLU) pa[part_n + r * p.tps + j] = sum2;
+      }
+    }
+    if (__syncthreads_or(!ok)) { failed = true; ++it; break; }
+    if (tid == 0) {  // every lane is done with the stage: refill it
+      const int nt = tile + p.nstages * step;
+      if (nt < ntiles) issue(nt, s);
+    }
+    // the rows' partial sums meet, a warp a row
+    for (int r = warp; r < t.nrows; r += MV_THREADS / 32) {
+      float v = 0.0f, v2 = 0.0f;
+      for (int i = lane; i < p.tps; i += 32) {
+        v += pa[r * p.tps + i];
+        if constexpr (GLU) v2 += pa[part_n + r * p.tps + i];
+      }
+      v = warp_sum(v);
+      if constexpr (GLU) v2 = warp_sum(v2);
+      if (lane == 0) {
+        const long long row = t.row0 + r;
+        if constexpr (MODE == MODE_GLU) {
+          p.y[0][(long long)z * p.y_seg + row] = (v / (1.0f + expf(-v))) * v2;
+        } else if constexpr (MODE == MODE_MOE_GLU) {
+          // D4-ROUTED!'s middle (src/ds4f.lisp:1016-1019): silu(min(g,c)) * clamp(u) * weight
+          float g = v, uu = v2;
+          if (p.clamp > 1e-6f) { g = fminf(g, p.clamp); uu = fmaxf(-p.clamp, fminf(uu, p.clamp)); }
+          float sg;
+          if (g >= 0.0f) sg = __fdiv_rn(1.0f, 1.0f + expf(-g));
+          else { const float e = expf(g); sg = __fdiv_rn(e, 1.0f + e); }
+          p.y[0][(long long)z * p.y_seg + row] = __fmul_rn(__fmul_rn(__fmul_rn(g, sg), uu), p.seg_w[z]);
+        } else {
+          float* y = p.y[t.m] + (long long)z * p.y_seg;
+          if (p.bias[t.m]) v += p.bias[t.m][row];
+          y[row] = p.acc ? y[row] + v : v;
+        }
+      }
+    }
+  }
+  if (failed) {
+    // give copies still in flight a bounded time to land before the CTA's
+    // shared memory is released
+    int it2 = it;
+    for (int tile = first + it * step; tile < ntiles && it2 < it + p.nstages - 1; tile += step, ++it2)
+      mbar_wait(&full[it2 % p.nstages], (uint32_t)(it2 / p.nstages) & 1u, nullptr, 0);
+  }
+}
+
 // ---- host side ----------------------------------------------------------------
 
 static unsigned int* status_ptr() {
@@ -280,11 +449,6 @@ static unsigned int* status_ptr() {
   return cached;
 }
 
-struct MvPlan {
-  int rows_per_tile, lanes, nstages, grid_x;
-  uint32_t stage_bytes, x_bytes, xs_off, bs_off, smem;
-};
-
 static int g_sm_count = 0;
 static int sm_count() {
   if (!g_sm_count) {
@@ -297,94 +461,171 @@ static int sm_count() {
 }
 
 static uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+static int unit_weights(int fmt) { return (fmt == ILL_Q8_0 || fmt == ILL_IQ2_XXS) ? 32 : 64; }
 
-// Tiling: aim for ~8 tiles per SM in flight across the grid when the matrix is
-// small, at most 16 KB per stage when it is large; four stages per CTA.
-static int plan_mv(int fmt, long long total_rows, int cols, int ntok_smem, int nseg, bool glu, MvPlan* pl) {
-  const int bw = fmt_block_weights(fmt), bb = fmt_block_bytes(fmt);
-  const long long row_bytes = (long long)(cols / bw) * bb;
-  const uint32_t max_stage = glu ? 12288 : 16384;
+struct MvPlan {
+  bool one;  // the one-token kernel (activations in registers)
+  int rows_per_tile, lanes, nstages, upt, tps, slots, al;
+  uint32_t stage_bytes, x_bytes, xs_off, bs_off, smem;
+};
+
+// Tile size: small matrices are cut into many tiles so every SM gets several;
+// large ones use stages of at most STAGE_CAP bytes.
+static long long tile_target(long long total_bytes, uint32_t cap) {
+  long long t = total_bytes / ((long long)sm_count() * 16);
+  if (t > cap) t = cap;
+  if (t < 2048) t = 2048;
+  return t;
+}
+
+static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu, MvPlan* pl) {
+  const long long row_bytes = (long long)(cols / fmt_block_weights(fmt)) * fmt_block_bytes(fmt);
+  const uint32_t cap = glu ? 8192 : 12288;
   if (row_bytes + 32 > 49152) return ILL_ERR_UNSUPPORTED;
-  const int sms = sm_count();
-  long long target = total_rows * row_bytes * nseg / ((long long)sms * 16);
-  if (target > max_stage) target = max_stage;
-  if (target < 2048) target = 2048;
-  long long rpt = target / row_bytes;
+  const int units = cols / unit_weights(fmt);
+  const int upt_max = unit_weights(fmt) == 32 ? 4 : 2;
+  long long rpt = tile_target(total_rows * row_bytes * nseg, cap) / row_bytes;
   if (rpt < 1) rpt = 1;
   if (rpt > total_rows) rpt = total_rows;
+  int best_upt = 0, best_tps = 0, best_slots = 0;
+  long long best_util = -1;
+  for (int upt = 1; upt <= upt_max; upt *= 2) {
+    const int tps = (units + upt - 1) / upt;
+    if (tps > MV_THREADS) continue;
+    int slots = MV_THREADS / tps;
+    if (slots > rpt) slots = (int)rpt;
+    const long long util = (long long)slots * tps;
+    if (util > best_util) { best_util = util; best_upt = upt; best_tps = tps; best_slots = slots; }
+  }
+  if (!best_upt) return ILL_ERR_UNSUPPORTED;
+  rpt = rpt / best_slots * best_slots;
+  pl->one = true;
+  pl->upt = best_upt;
+  pl->tps = best_tps;
+  pl->slots = best_slots;
+  pl->rows_per_tile = (int)rpt;
+  pl->lanes = 0;
+  pl->nstages = 4;
+  pl->stage_bytes = align_up((uint32_t)(rpt * row_bytes) + 32, 128);
+  pl->x_bytes = pl->xs_off = pl->bs_off = 0;
+  const uint32_t part = (uint32_t)rpt * best_tps * 4u * 2u * (glu ? 2u : 1u);
+  pl->smem = pl->stage_bytes * (glu ? 2 : 1) * pl->nstages + align_up(part, 16) + (fmt == ILL_IQ2_XXS ? 3072 : 0) + 64;
+  return pl->smem > 200 * 1024 ? ILL_ERR_UNSUPPORTED : ILL_OK;
+}
+
+static int plan_many(int fmt, long long total_rows, int cols, int ntok, int nseg, MvPlan* pl) {
+  const long long row_bytes = (long long)(cols / fmt_block_weights(fmt)) * fmt_block_bytes(fmt);
+  if (row_bytes + 32 > 49152) return ILL_ERR_UNSUPPORTED;
+  long long rpt = tile_target(total_rows * row_bytes * nseg, 16384) / row_bytes;
+  if (rpt < 1) rpt = 1;
+  if (rpt > total_rows) rpt = total_rows;
+  pl->one = false;
+  pl->upt = pl->tps = pl->slots = 0;
+  pl->al = 1;
   pl->rows_per_tile = (int)rpt;
   pl->stage_bytes = align_up((uint32_t)(rpt * row_bytes) + 32, 128);
   pl->nstages = 4;
-  const int units = cols / (fmt == ILL_Q8_0 || fmt == ILL_IQ2_XXS ? 32 : 64);
+  const int units = cols / unit_weights(fmt);
   int L = 32;
   while (L > 1 && (L / 2) * rpt >= MV_THREADS) L >>= 1;  // enough rows to fill the CTA with fewer lanes a row
   while (L > 1 && L / 2 >= units) L >>= 1;
   pl->lanes = L;
   const int nsc = fmt == ILL_Q8_0 ? cols / 32 : cols / 256;
-  pl->xs_off = align_up((uint32_t)ntok_smem * cols, 16);
-  pl->bs_off = align_up(pl->xs_off + 4u * ntok_smem * nsc, 16);
-  pl->x_bytes = align_up(pl->bs_off + 2u * ntok_smem * (cols / 16), 128);
-  pl->smem = pl->x_bytes + pl->stage_bytes * (glu ? 2 : 1) * pl->nstages + (fmt == ILL_IQ2_XXS ? 3072 : 0) + 64;
-  if (pl->smem > 227 * 1024) return ILL_ERR_UNSUPPORTED;
-  return ILL_OK;
+  pl->xs_off = align_up((uint32_t)ntok * cols, 16);
+  pl->bs_off = align_up(pl->xs_off + 4u * ntok * nsc, 16);
+  pl->x_bytes = align_up(pl->bs_off + 2u * ntok * (cols / 16), 128);
+  pl->smem = pl->x_bytes + pl->stage_bytes * pl->nstages + (fmt == ILL_IQ2_XXS ? 3072 : 0) + 64;
+  return pl->smem > 227 * 1024 ? ILL_ERR_UNSUPPORTED : ILL_OK;
 }
 
-template <int FMT, int MODE, int NT>
-static int launch_mv_t(const MvParams& p, const MvPlan& pl, int grid_x, int grid_y, cudaStream_t st) {
-  auto k = mv_kernel<FMT, MODE, NT>;
+template <typename K>
+static int launch_k(K k, const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
   if (pl.smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
     if (e != cudaSuccess) return cuda_fail(e);
   }
   MvParams pp = p;
   void* args[] = {&pp};
-  return launch_kernel((const void*)k, dim3(grid_x, grid_y, 1), dim3(MV_THREADS, 1, 1), pl.smem, args, st);
+  return launch_kernel((const void*)k, dim3(gx, gy, 1), dim3(MV_THREADS, 1, 1), pl.smem, args, st);
+}
+
+template <int FMT, int MODE, int AL>
+static int launch_one_u(const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
+  constexpr int UMAX = (FMT == ILL_Q8_0 || FMT == ILL_IQ2_XXS) ? 4 : 2;
+  if (pl.upt == 1) return launch_k(mv1_kernel<FMT, MODE, 1, AL>, p, pl, gx, gy, st);
+  if (pl.upt == 2) return launch_k(mv1_kernel<FMT, MODE, 2, AL>, p, pl, gx, gy, st);
+  if constexpr (UMAX >= 4) return launch_k(mv1_kernel<FMT, MODE, 4, AL>, p, pl, gx, gy, st);
+  return ILL_ERR_UNSUPPORTED;
+}
+
+template <int FMT, int MODE>
+static int launch_one_a(const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
+  if constexpr (FMT == ILL_Q4_K) {
+    if (pl.al >= 16) return launch_one_u<FMT, MODE, 16>(p, pl, gx, gy, st);
+  }
+  if constexpr (FMT == ILL_Q2_K) {
+    if (pl.al >= 4) return launch_one_u<FMT, MODE, 4>(p, pl, gx, gy, st);
+  }
+  return launch_one_u<FMT, MODE, 1>(p, pl, gx, gy, st);
 }
 
 template <int FMT>
-static int launch_mv_f(int mode, const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
-  if (mode == MODE_GLU) return launch_mv_t<FMT, MODE_GLU, 1>(p, pl, gx, gy, st);
-  if (mode == MODE_MOE_GLU) return launch_mv_t<FMT, MODE_MOE_GLU, 1>(p, pl, gx, gy, st);
-  if (p.n == 1) return launch_mv_t<FMT, MODE_PLAIN, 1>(p, pl, gx, gy, st);
-  if (p.n <= 4) return launch_mv_t<FMT, MODE_PLAIN, 4>(p, pl, gx, gy, st);
-  if (p.n <= 8) return launch_mv_t<FMT, MODE_PLAIN, 8>(p, pl, gx, gy, st);
-  return launch_mv_t<FMT, MODE_PLAIN, 16>(p, pl, gx, gy, st);
+static int launch_fmt(int mode, const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
+  if (pl.one) {
+    if (mode == MODE_GLU) return launch_one_a<FMT, MODE_GLU>(p, pl, gx, gy, st);
+    if (mode == MODE_MOE_GLU) {
+      if constexpr (FMT == ILL_IQ2_XXS || FMT == ILL_Q2_K) return launch_one_a<FMT, MODE_MOE_GLU>(p, pl, gx, gy, st);
+      return ILL_ERR_UNSUPPORTED;
+    }
+    return launch_one_a<FMT, MODE_PLAIN>(p, pl, gx, gy, st);
+  }
+  if (mode != MODE_PLAIN) return ILL_ERR_UNSUPPORTED;
+  if (p.n == 1) return launch_k(mvn_kernel<FMT, MODE_PLAIN, 1>, p, pl, gx, gy, st);
+  if (p.n <= 4) return launch_k(mvn_kernel<FMT, MODE_PLAIN, 4>, p, pl, gx, gy, st);
+  if (p.n <= 8) return launch_k(mvn_kernel<FMT, MODE_PLAIN, 8>, p, pl, gx, gy, st);
+  return launch_k(mvn_kernel<FMT, MODE_PLAIN, 16>, p, pl, gx, gy, st);
 }
 
 static int launch_mv(int fmt, int mode, const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
   switch (fmt) {
-    case ILL_Q8_0: return launch_mv_f<ILL_Q8_0>(mode, p, pl, gx, gy, st);
-    case ILL_Q4_K: return launch_mv_f<ILL_Q4_K>(mode, p, pl, gx, gy, st);
-    case ILL_Q6_K: return launch_mv_f<ILL_Q6_K>(mode, p, pl, gx, gy, st);
-    case ILL_Q2_K: return launch_mv_f<ILL_Q2_K>(mode, p, pl, gx, gy, st);
-    case ILL_IQ2_XXS: return launch_mv_f<ILL_IQ2_XXS>(mode, p, pl, gx, gy, st);
+    case ILL_Q8_0: return launch_fmt<ILL_Q8_0>(mode, p, pl, gx, gy, st);
+    case ILL_Q4_K: return launch_fmt<ILL_Q4_K>(mode, p, pl, gx, gy, st);
+    case ILL_Q6_K: return launch_fmt<ILL_Q6_K>(mode, p, pl, gx, gy, st);
+    case ILL_Q2_K: return launch_fmt<ILL_Q2_K>(mode, p, pl, gx, gy, st);
+    case ILL_IQ2_XXS: return launch_fmt<ILL_IQ2_XXS>(mode, p, pl, gx, gy, st);
   }
   return ILL_ERR_ARG;
 }
 
 static bool needs_bsums(int fmt) { return fmt == ILL_Q4_K || fmt == ILL_Q6_K || fmt == ILL_Q2_K; }
 
-// Common entry: NMAT matrices of one format sharing the activations.
-static int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, int cols, ill_dptr xq, ill_dptr xs,
-                     ill_dptr xsum, const ill_dptr* y, const ill_dptr* bias, int acc, int n, ill_dptr ptrs, int nseg,
-                     long long add, long long up_add, int x_seg, long long y_seg, ill_dptr seg_w, float clamp,
-                     ill_stream stream) {
+// Common entry: NMAT matrices of one format sharing the activations, NSEG
+// segments (experts) of them.
+int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, int cols, ill_dptr xq, ill_dptr xs,
+              ill_dptr xsum, const ill_dptr* y, const ill_dptr* bias, int acc, int n, ill_dptr ptrs, int nseg,
+              long long add, long long up_add, int x_seg, long long y_seg, ill_dptr seg_w, float clamp,
+              ill_stream stream) {
   const int bw = fmt_block_weights(fmt);
   if (!bw || nmat < 1 || nmat > MV_MAX_MATS || cols <= 0 || cols % (bw == 32 ? 32 : 256)) return ILL_ERR_ARG;
   if (n < 1 || n > MV_MAX_TOK || nseg < 1 || nseg > 65535) return ILL_ERR_ARG;
   if (!xq || !xs || (needs_bsums(fmt) && !xsum)) return ILL_ERR_ARG;
-  if (xq & 15 || xs & 3 || xsum & 1) return ILL_ERR_ALIGN;
+  if (xq & 15 || xs & 3 || xsum & 7) return ILL_ERR_ALIGN;
   long long total_rows = 0;
+  uint64_t align_bits = (uint64_t)add | (uint64_t)up_add;
   for (int i = 0; i < nmat; ++i) {
     if (rows[i] <= 0 || !y[i] || (!ptrs && !w[i])) return ILL_ERR_ARG;
     if (y[i] & 3) return ILL_ERR_ALIGN;
     total_rows += rows[i];
+    if (!ptrs) align_bits |= w[i];
   }
   const bool glu = mode != MODE_PLAIN;
+  if (glu && n != 1) return ILL_ERR_ARG;
   MvPlan pl;
-  const int ntok_smem = x_seg ? 1 : n;
-  int rc = plan_mv(fmt, glu ? rows[0] : total_rows, cols, ntok_smem, nseg, glu, &pl);
+  int rc = ILL_ERR_UNSUPPORTED;
+  if (n == 1) rc = plan_one(fmt, glu ? rows[0] : total_rows, cols, nseg, glu, &pl);
+  if (rc == ILL_ERR_UNSUPPORTED && !glu) rc = plan_many(fmt, total_rows, cols, x_seg ? 1 : n, nseg, &pl);
   if (rc) return rc;
+  pl.al = (align_bits & 15) == 0 ? 16 : (align_bits & 3) == 0 ? 4 : 1;
   MvParams p = {};
   p.nmat = glu ? 1 : nmat;
   int tiles = 0;
@@ -400,7 +641,7 @@ static int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* 
   for (int i = p.nmat + 1; i <= MV_MAX_MATS; ++i) p.tile0[i] = tiles;
   p.cols = cols;
   p.row_bytes = cols / bw * fmt_block_bytes(fmt);
-  p.units = cols / (fmt == ILL_Q8_0 || fmt == ILL_IQ2_XXS ? 32 : 64);
+  p.units = cols / unit_weights(fmt);
   p.xq = (const i8*)(uintptr_t)xq;
   p.xs = (const float*)(uintptr_t)xs;
   p.xsum = (const int16_t*)(uintptr_t)xsum;
@@ -408,6 +649,8 @@ static int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* 
   p.acc = acc;
   p.rows_per_tile = pl.rows_per_tile;
   p.lanes_per_row = pl.lanes;
+  p.tps = pl.tps;
+  p.slots = pl.slots;
   p.stage_bytes = pl.stage_bytes;
   p.nstages = pl.nstages;
   p.x_bytes = pl.x_bytes;
@@ -422,9 +665,9 @@ static int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* 
   p.clamp = clamp;
   p.status = status_ptr();
   // persistent grid: as many CTAs as can be resident, split over the segments
-  const int per_sm = (int)((227u * 1024u) / (pl.smem + 1024u));
-  int resident = sm_count() * (per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm));
-  int gx = (resident + nseg - 1) / nseg;
+  int per_sm = (int)((227u * 1024u) / (pl.smem + 1024u));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
+  int gx = (sm_count() * per_sm + nseg - 1) / nseg;
   if (gx > tiles) gx = tiles;
   if (gx < 1) gx = 1;
   return launch_mv(fmt, mode, p, pl, gx, nseg, (cudaStream_t)stream);
