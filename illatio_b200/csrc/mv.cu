@@ -267,30 +267,30 @@ __global__ void __launch_bounds__(MV_THREADS) mvn_kernel(const MvParams p) {
   }
 }
 
-// ---- one token: activations in registers ---------------------------------------
+// ---- one token: activations in registers, a pipeline per warp --------------------
 //
-// Thread t belongs to row slot t / tps and owns units j, j + tps, ... (j = t %
-// tps) of every row its slot takes: the activations of those units are loaded
-// from global memory once, into registers, and reused for every row.  Per tile
-// a thread writes one partial sum per row to shared memory; after the tile's
-// barrier the warps add each row's partials and write the outputs.
+// Each warp streams its own tiles of rows through its own ring of stages: lane 0
+// issues the bulk copies, all lanes wait on the stage's mbarrier, and after a
+// __syncwarp the stage is refilled -- no CTA-wide barrier anywhere.  A row is
+// shared by L consecutive lanes (L = 8, 16 or 32, so 32/L rows are in progress
+// per warp); lane sl of them owns units sl, sl+L, ... of every row, and loads
+// those units' activations from global memory into registers once.  A row's
+// lanes meet with log2(L) shuffles.
 template <int FMT, int MODE, int UPT, int AL>
-__global__ void __launch_bounds__(MV_THREADS) mv1_kernel(const MvParams p) {
+__global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
   extern __shared__ __align__(128) u8 smem[];
   constexpr bool GLU = MODE != MODE_PLAIN;
   constexpr bool IQ = FMT == ILL_IQ2_XXS;
+  constexpr int WARPS = MV_THREADS / 32;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int z = blockIdx.y;
 
   const uint32_t stage_stride = p.stage_bytes * (GLU ? 2u : 1u);
-  u8* stage0 = smem;
-  u8* after = stage0 + (size_t)stage_stride * p.nstages;
-  float* part = (float*)after;  // [2 buffers][GLU ? 2 : 1][rows_per_tile * tps]
-  const int part_n = p.rows_per_tile * p.tps;
-  u8* after2 = after + (size_t)part_n * 4 * 2 * (GLU ? 2 : 1);
-  uint2* iq_grid = (uint2*)after2;
+  u8* wstage = smem + (size_t)warp * stage_stride * p.nstages;
+  u8* after = smem + (size_t)WARPS * stage_stride * p.nstages;
+  uint2* iq_grid = (uint2*)after;
   uint2* iq_smask = iq_grid + 256;
-  uint64_t* full = (uint64_t*)(after2 + (IQ ? 3072 : 0));
+  uint64_t* full = (uint64_t*)(after + (IQ ? 3072 : 0)) + warp * p.nstages;
 
   const u8* wbase[MV_MAX_MATS];
   if (p.ptrs) {
@@ -303,12 +303,12 @@ __global__ void __launch_bounds__(MV_THREADS) mv1_kernel(const MvParams p) {
     for (int i = 0; i < MV_MAX_MATS; ++i) wbase[i] = p.w[i];
   }
   const int ntiles = p.tile0[p.nmat];
-  const int first = blockIdx.x, step = gridDim.x;
+  const int first = blockIdx.x * WARPS + warp, step = gridDim.x * WARPS;
 
   auto issue = [&](int tile, int s) {
     const TileRef t = tile_ref(p, tile, wbase);
     const uint32_t len = (uint32_t)t.nrows * (uint32_t)p.row_bytes;
-    u8* dst = stage0 + (size_t)s * stage_stride;
+    u8* dst = wstage + (size_t)s * stage_stride;
     const uintptr_t a0 = (uintptr_t)t.g & ~(uintptr_t)15;
     const uint32_t bytes = (uint32_t)((((uintptr_t)t.g + len + 15) & ~(uintptr_t)15) - a0);
     if (GLU) {
@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(MV_THREADS) mv1_kernel(const MvParams p) {
     }
   };
 
-  if (tid == 0) {
+  if (lane == 0) {
     for (int s = 0; s < p.nstages; ++s) mbar_init(&full[s], 1);
     mbar_fence_init();
     for (int s = 0; s < p.nstages; ++s) {  // weights do not depend on the previous kernel
@@ -332,12 +332,15 @@ __global__ void __launch_bounds__(MV_THREADS) mv1_kernel(const MvParams p) {
       if (tile < ntiles) issue(tile, s);
     }
   }
-  if (IQ) iq_tables_fill(iq_grid, iq_smask, ill_iq2xxs_grid, ill_ksigns_iq2xs);
+  if (IQ) {
+    iq_tables_fill(iq_grid, iq_smask, ill_iq2xxs_grid, ill_ksigns_iq2xs);
+    __syncthreads();
+  }
   pdl_launch_dependents();
   pdl_wait();  // the activations may come from the previous kernel
+  __syncwarp();
 
-  const int slot = tid / p.tps, j = tid - slot * p.tps;
-  const bool active = slot < p.slots;
+  const int L = p.lanes_per_row, sub = lane / L, sl = lane - sub * L, nsub = 32 / L;
   XReg<FMT> x[UPT];
   {
     const long long tok0 = (long long)z * p.x_seg;
@@ -348,36 +351,36 @@ __global__ void __launch_bounds__(MV_THREADS) mv1_kernel(const MvParams p) {
     a.bs = p.xsum + tok0 * (p.cols / 16);
 #pragma unroll
     for (int k = 0; k < UPT; ++k) {
-      const int u = j + k * p.tps;
-      if (active && u < p.units) load_x(x[k], a, u);
+      const int u = sl + k * L;
+      if (u < p.units) load_x(x[k], a, u);
     }
   }
   IqTables iqt;
   iqt.grid = iq_grid;
   iqt.smask = iq_smask;
-  __syncthreads();  // barriers initialised, tables filled
 
-  int it = 0, pp = 0;
-  bool failed = false;
-  for (int tile = first; tile < ntiles; tile += step, ++it, pp ^= 1) {
-    const int s = it % p.nstages;
-    const uint32_t parity = (uint32_t)(it / p.nstages) & 1u;
-    const bool ok = mbar_wait(&full[s], parity, p.status, ST_MV_WAIT + FMT);
+  int s = 0;
+  uint32_t parity = 0;
+  for (int tile = first; tile < ntiles; tile += step) {
+    bool ok = mbar_wait(&full[s], parity, p.status, ST_MV_WAIT + FMT);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;  // the copy never landed: the status word says so; nothing is read
     const TileRef t = tile_ref(p, tile, wbase);
-    const u8* sbase = stage0 + (size_t)s * stage_stride;
+    const u8* sbase = wstage + (size_t)s * stage_stride;
     const u8* rows_s = sbase + ((uintptr_t)t.g & 15);
     const u8* rows_u = sbase + p.stage_bytes + ((uintptr_t)(wbase[1] + (long long)t.row0 * p.row_bytes) & 15);
-    float* pa = part + (size_t)pp * part_n * (GLU ? 2 : 1);
 
-    if (ok && active) {
-      for (int r = slot; r < t.nrows; r += p.slots) {
+    for (int r0 = 0; r0 < t.nrows; r0 += nsub) {
+      const int r = r0 + sub;
+      const bool valid = r < t.nrows;
+      float sum = 0.0f, sum2 = 0.0f;
+      if (valid) {
         const u8* rowp = rows_s + (size_t)r * p.row_bytes;
         const u8* rowu = rows_u + (size_t)r * p.row_bytes;
-        float sum = 0.0f, sum2 = 0.0f;
 #pragma unroll
         for (int k = 0; k < UPT; ++k) {
-          const int u = j + k * p.tps;
-          if (u < p.units) {
+          const int u = sl + k * L;
+          if (k < UPT - 1 || u < p.units) {
             WReg<FMT> w;
             if constexpr (IQ) load_w<AL>(w, rowp, u, iqt); else load_w<AL>(w, rowp, u);
             sum += dot(w, x[k]);
@@ -388,31 +391,18 @@ __global__ void __launch_bounds__(MV_THREADS) mv1_kernel(const MvParams p) {
             }
           }
         }
-        pa[r * p.tps + j] = sum;
-        if constexpr (GLU) pa[part_n + r * p.tps + j] = sum2;
       }
-    }
-    if (__syncthreads_or(!ok)) { failed = true; ++it; break; }
-    if (tid == 0) {  // every lane is done with the stage: refill it
-      const int nt = tile + p.nstages * step;
-      if (nt < ntiles) issue(nt, s);
-    }
-    // the rows' partial sums meet, a warp a row
-    for (int r = warp; r < t.nrows; r += MV_THREADS / 32) {
-      float v = 0.0f, v2 = 0.0f;
-      for (int i = lane; i < p.tps; i += 32) {
-        v += pa[r * p.tps + i];
-        if constexpr (GLU) v2 += pa[part_n + r * p.tps + i];
+      for (int o = L >> 1; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if constexpr (GLU) sum2 += __shfl_xor_sync(0xffffffffu, sum2, o);
       }
-      v = warp_sum(v);
-      if constexpr (GLU) v2 = warp_sum(v2);
-      if (lane == 0) {
+      if (valid && sl == 0) {
         const long long row = t.row0 + r;
         if constexpr (MODE == MODE_GLU) {
-          p.y[0][(long long)z * p.y_seg + row] = (v / (1.0f + expf(-v))) * v2;
+          p.y[0][(long long)z * p.y_seg + row] = (sum / (1.0f + expf(-sum))) * sum2;
         } else if constexpr (MODE == MODE_MOE_GLU) {
           // D4-ROUTED!'s middle (src/ds4f.lisp:1016-1019): silu(min(g,c)) * clamp(u) * weight
-          float g = v, uu = v2;
+          float g = sum, uu = sum2;
           if (p.clamp > 1e-6f) { g = fminf(g, p.clamp); uu = fmaxf(-p.clamp, fminf(uu, p.clamp)); }
           float sg;
           if (g >= 0.0f) sg = __fdiv_rn(1.0f, 1.0f + expf(-g));
@@ -420,18 +410,18 @@ __global__ void __launch_bounds__(MV_THREADS) mv1_kernel(const MvParams p) {
           p.y[0][(long long)z * p.y_seg + row] = __fmul_rn(__fmul_rn(__fmul_rn(g, sg), uu), p.seg_w[z]);
         } else {
           float* y = p.y[t.m] + (long long)z * p.y_seg;
+          float v = sum;
           if (p.bias[t.m]) v += p.bias[t.m][row];
           y[row] = p.acc ? y[row] + v : v;
         }
       }
     }
-  }
-  if (failed) {
-    // give copies still in flight a bounded time to land before the CTA's
-    // shared memory is released
-    int it2 = it;
-    for (int tile = first + it * step; tile < ntiles && it2 < it + p.nstages - 1; tile += step, ++it2)
-      mbar_wait(&full[it2 % p.nstages], (uint32_t)(it2 / p.nstages) & 1u, nullptr, 0);
+    __syncwarp();  // every lane is done with the stage
+    if (lane == 0) {
+      const int nt = tile + p.nstages * step;
+      if (nt < ntiles) issue(nt, s);
+    }
+    if (++s == p.nstages) { s = 0; parity ^= 1u; }
   }
 }
 
@@ -478,39 +468,40 @@ static long long tile_target(long long total_bytes, uint32_t cap) {
   return t;
 }
 
+// One-token plan: L lanes a row and UPT units a lane, chosen for the fewest idle
+// lanes; a warp's stage holds (32/L) * RPS rows, about 3.5 KB.
 static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu, MvPlan* pl) {
   const long long row_bytes = (long long)(cols / fmt_block_weights(fmt)) * fmt_block_bytes(fmt);
-  const uint32_t cap = glu ? 8192 : 12288;
-  if (row_bytes + 32 > 49152) return ILL_ERR_UNSUPPORTED;
   const int units = cols / unit_weights(fmt);
-  const int upt_max = unit_weights(fmt) == 32 ? 4 : 2;
-  long long rpt = tile_target(total_rows * row_bytes * nseg, cap) / row_bytes;
-  if (rpt < 1) rpt = 1;
-  if (rpt > total_rows) rpt = total_rows;
-  int best_upt = 0, best_tps = 0, best_slots = 0;
-  long long best_util = -1;
-  for (int upt = 1; upt <= upt_max; upt *= 2) {
-    const int tps = (units + upt - 1) / upt;
-    if (tps > MV_THREADS) continue;
-    int slots = MV_THREADS / tps;
-    if (slots > rpt) slots = (int)rpt;
-    const long long util = (long long)slots * tps;
-    if (util > best_util) { best_util = util; best_upt = upt; best_tps = tps; best_slots = slots; }
+  const int upt_max = unit_weights(fmt) == 32 ? 5 : 3;
+  int bestL = 0, bestU = 0;
+  double best = -1.0;
+  for (int L = 32; L >= 8; L >>= 1) {
+    const int upt = (units + L - 1) / L;
+    if (upt > upt_max) continue;
+    const double eff = (double)units / ((double)L * upt) - 0.01 * upt;  // ties: fewer registers
+    if (eff > best) { best = eff; bestL = L; bestU = upt; }
   }
-  if (!best_upt) return ILL_ERR_UNSUPPORTED;
-  rpt = rpt / best_slots * best_slots;
+  if (!bestL) return ILL_ERR_UNSUPPORTED;
+  const int nsub = 32 / bestL;
+  // rows per warp tile: ~3.5 KB a stage, but small matrices are cut finer so that every warp gets some
+  const long long warps = (long long)sm_count() * 16;
+  long long tr = 3584 / row_bytes;
+  const long long share = (total_rows * nseg + warps - 1) / warps;
+  if (tr > share) tr = share;
+  tr = tr / nsub * nsub;
+  if (tr < nsub) tr = nsub;
   pl->one = true;
-  pl->upt = best_upt;
-  pl->tps = best_tps;
-  pl->slots = best_slots;
-  pl->rows_per_tile = (int)rpt;
-  pl->lanes = 0;
-  pl->nstages = 4;
-  pl->stage_bytes = align_up((uint32_t)(rpt * row_bytes) + 32, 128);
+  pl->upt = bestU;
+  pl->lanes = bestL;
+  pl->tps = pl->slots = 0;
+  pl->rows_per_tile = (int)tr;
+  pl->nstages = row_bytes * tr > 6144 ? 3 : 4;
+  pl->stage_bytes = align_up((uint32_t)(tr * row_bytes) + 32, 128);
   pl->x_bytes = pl->xs_off = pl->bs_off = 0;
-  const uint32_t part = (uint32_t)rpt * best_tps * 4u * 2u * (glu ? 2u : 1u);
-  pl->smem = pl->stage_bytes * (glu ? 2 : 1) * pl->nstages + align_up(part, 16) + (fmt == ILL_IQ2_XXS ? 3072 : 0) + 64;
-  return pl->smem > 200 * 1024 ? ILL_ERR_UNSUPPORTED : ILL_OK;
+  pl->smem = pl->stage_bytes * (glu ? 2 : 1) * pl->nstages * (MV_THREADS / 32) + (fmt == ILL_IQ2_XXS ? 3072 : 0) +
+             8 * pl->nstages * (MV_THREADS / 32) + 64;
+  return pl->smem > 220 * 1024 ? ILL_ERR_UNSUPPORTED : ILL_OK;
 }
 
 static int plan_many(int fmt, long long total_rows, int cols, int ntok, int nseg, MvPlan* pl) {
@@ -551,10 +542,14 @@ static int launch_k(K k, const MvParams& p, const MvPlan& pl, int gx, int gy, cu
 
 template <int FMT, int MODE, int AL>
 static int launch_one_u(const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
-  constexpr int UMAX = (FMT == ILL_Q8_0 || FMT == ILL_IQ2_XXS) ? 4 : 2;
-  if (pl.upt == 1) return launch_k(mv1_kernel<FMT, MODE, 1, AL>, p, pl, gx, gy, st);
-  if (pl.upt == 2) return launch_k(mv1_kernel<FMT, MODE, 2, AL>, p, pl, gx, gy, st);
-  if constexpr (UMAX >= 4) return launch_k(mv1_kernel<FMT, MODE, 4, AL>, p, pl, gx, gy, st);
+  constexpr int UMAX = (FMT == ILL_Q8_0 || FMT == ILL_IQ2_XXS) ? 5 : 3;
+  switch (pl.upt) {
+    case 1: return launch_k(mvw_kernel<FMT, MODE, 1, AL>, p, pl, gx, gy, st);
+    case 2: return launch_k(mvw_kernel<FMT, MODE, 2, AL>, p, pl, gx, gy, st);
+    case 3: return launch_k(mvw_kernel<FMT, MODE, 3, AL>, p, pl, gx, gy, st);
+    case 4: if constexpr (UMAX >= 4) return launch_k(mvw_kernel<FMT, MODE, 4, AL>, p, pl, gx, gy, st); break;
+    case 5: if constexpr (UMAX >= 5) return launch_k(mvw_kernel<FMT, MODE, 5, AL>, p, pl, gx, gy, st); break;
+  }
   return ILL_ERR_UNSUPPORTED;
 }
 
@@ -668,7 +663,8 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
   int per_sm = (int)((227u * 1024u) / (pl.smem + 1024u));
   per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
   int gx = (sm_count() * per_sm + nseg - 1) / nseg;
-  if (gx > tiles) gx = tiles;
+  const int work = pl.one ? (tiles + MV_THREADS / 32 - 1) / (MV_THREADS / 32) : tiles;  // a warp a tile, or a CTA a tile
+  if (gx > work) gx = work;
   if (gx < 1) gx = 1;
   return launch_mv(fmt, mode, p, pl, gx, nseg, (cudaStream_t)stream);
 }
