@@ -23,6 +23,7 @@ SIGNATURES = {
     "ill_block_bytes": (_I, [_I]),
     "ill_block_weights": (_I, [_I]),
     "ill_set_pdl": (_I, [_I]),
+    "ill_set_tuning": (_I, [_I, _I, _I, _I]),
     "ill_device_status": (_I, [_c.POINTER(_c.c_uint), _S]),
     "ill_quant_q8_0": (_I, [_P, _P, _P, _P, _L, _I, _S]),
     "ill_quant_q8_k": (_I, [_P, _P, _P, _P, _L, _S]),

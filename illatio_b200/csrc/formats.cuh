@@ -43,11 +43,13 @@ struct ActS {
   const int16_t* bs;  // sums of 16 quants (Q8_K)
 };
 
-// words at an arbitrarily aligned shared-memory byte pointer
+// words at an arbitrarily aligned shared-memory byte pointer (pointer arithmetic
+// only, so the compiler keeps the shared address space)
 template <int N>
 __device__ __forceinline__ void ld_words(const u8* p, uint32_t (&out)[N]) {
-  const uint32_t sh = ((uint32_t)(uintptr_t)p & 3u) * 8u;
-  const uint32_t* b = (const uint32_t*)((uintptr_t)p & ~(uintptr_t)3);
+  const uint32_t mis = (uint32_t)(uintptr_t)p & 3u;
+  const uint32_t* b = (const uint32_t*)(p - mis);
+  const uint32_t sh = mis * 8u;
   uint32_t prev = b[0];
 #pragma unroll
   for (int i = 0; i < N; ++i) {
@@ -56,7 +58,7 @@ __device__ __forceinline__ void ld_words(const u8* p, uint32_t (&out)[N]) {
     prev = next;
   }
 }
-// words at a pointer known to be 4-byte (A4) or 16-byte (A16) aligned
+// words at a pointer known to be 4-byte (AL 4) or 16-byte (AL 16) aligned
 template <int N, int AL>
 __device__ __forceinline__ void ld_words_al(const u8* p, uint32_t (&out)[N]) {
   if constexpr (AL >= 16 && N % 4 == 0) {
@@ -89,65 +91,83 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
   asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
+// two signed 16-bit halves of A times the two low signed bytes of B, accumulated
+__device__ __forceinline__ int dp2a_lo(int a, int b, int c) {
+  int d;
+  asm("dp2a.lo.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// The IQ2_XXS codebook (256 x 8 magnitudes) and the sign patterns expanded to
+// byte masks (0xFF where the weight is negative), in shared memory.
+struct IqTables { const uint2* grid; const uint2* smask; };
+
+template <int FMT> struct XReg;  // one token's activations for a unit
+template <int FMT> struct WReg;  // a unit's weights, unpacked
+template <int FMT> struct UPos;  // where a unit lies in its row: byte offsets and shifts, fixed per lane
 
 // ---- Q8_0: unit = block ------------------------------------------------------
-template <int FMT> struct XReg;
-template <int FMT> struct WReg;
-
 template <> struct XReg<ILL_Q8_0> { uint32_t q[8]; float s; };
 template <> struct WReg<ILL_Q8_0> { uint32_t q[8]; float d; };
+template <> struct UPos<ILL_Q8_0> { int off; };
 
+__device__ __forceinline__ void unit_pos(UPos<ILL_Q8_0>& o, int u) { o.off = 34 * u; }
 __device__ __forceinline__ void load_x(XReg<ILL_Q8_0>& x, const ActS& a, int u) {
   ld_x128<2>(a.q + 32 * u, x.q);
   x.s = a.s[u];
 }
 template <int AL = 1>
-__device__ __forceinline__ void load_w(WReg<ILL_Q8_0>& w, const u8* row, int u) {
-  const u8* p = row + 34 * u;
+__device__ __forceinline__ void load_w(WReg<ILL_Q8_0>& w, const u8* row, const UPos<ILL_Q8_0>& o, const IqTables&) {
+  const u8* p = row + o.off;
   w.d = h2f(ld_u16(p));
   ld_words<8>(p + 2, w.q);
 }
 __device__ __forceinline__ float dot(const WReg<ILL_Q8_0>& w, const XReg<ILL_Q8_0>& x) {
-  int acc = 0;
+  int a0 = 0, a1 = 0;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc = __dp4a((int)w.q[i], (int)x.q[i], acc);
-  return (float)acc * (w.d * x.s);
+  for (int i = 0; i < 4; ++i) {
+    a0 = __dp4a((int)w.q[i], (int)x.q[i], a0);
+    a1 = __dp4a((int)w.q[4 + i], (int)x.q[4 + i], a1);
+  }
+  return (float)(a0 + a1) * (w.d * x.s);
 }
 
 // ---- Q4_K: unit = 64 weights (groups 2k and 2k+1 of a super-block) ------------
-template <> struct XReg<ILL_Q4_K> { uint32_t q[16]; float d; int bs0, bs1; };
-template <> struct WReg<ILL_Q4_K> { uint32_t q[8]; float d, dmin; int sc0, sc1, m0, m1; };
+// bsp packs the two groups' activation sums as int16 halves for dp2a.
+template <> struct XReg<ILL_Q4_K> { uint32_t q[16]; float d; int bsp; };
+template <> struct WReg<ILL_Q4_K> { uint32_t q[8]; float d, dmin; uint32_t sc, mn; };  // sc, mn: two bytes each
+template <> struct UPos<ILL_Q4_K> { int off, qoff, sh; bool high; };
 
+__device__ __forceinline__ void unit_pos(UPos<ILL_Q4_K>& o, int u) {
+  const int k = u & 3;
+  o.off = 144 * (u >> 2);
+  o.qoff = o.off + 16 + 32 * k;
+  o.sh = 16 * (k & 1);
+  o.high = k >= 2;
+}
 __device__ __forceinline__ void load_x(XReg<ILL_Q4_K>& x, const ActS& a, int u) {
   const int i = u >> 2, k = u & 3;
   ld_x128<4>(a.q + 256 * i + 64 * k, x.q);
   x.d = a.s[i];
   const int2 b = *(const int2*)(a.bs + 16 * i + 4 * k);  // four int16 sums, 8-byte aligned
-  x.bs0 = (int)(short)(b.x & 0xffff) + (b.x >> 16);
-  x.bs1 = (int)(short)(b.y & 0xffff) + (b.y >> 16);
+  const int bs0 = (int)(short)(b.x & 0xffff) + (b.x >> 16), bs1 = (int)(short)(b.y & 0xffff) + (b.y >> 16);
+  x.bsp = (bs0 & 0xffff) | (bs1 << 16);
 }
 template <int AL = 1>
-__device__ __forceinline__ void load_w(WReg<ILL_Q4_K>& w, const u8* row, int u) {
-  const int i = u >> 2, k = u & 3;
-  const u8* p = row + 144 * i;
+__device__ __forceinline__ void load_w(WReg<ILL_Q4_K>& w, const u8* row, const UPos<ILL_Q4_K>& o, const IqTables&) {
   uint32_t h[4];  // d|dmin, then the 12 scale bytes
-  ld_words_al<4, AL>(p, h);
+  ld_words_al<4, AL>(row + o.off, h);
+  ld_words_al<8, AL>(row + o.qoff, w.q);
   w.d = h2f(h[0] & 0xffff);
   w.dmin = h2f(h[0] >> 16);
-  // get_scale_min_k4 for groups j = 2k, 2k+1 (src/kquant.lisp:64-72)
-  if (k < 2) {
-    const int sh = 16 * k;
-    w.sc0 = (h[1] >> sh) & 63; w.sc1 = (h[1] >> (sh + 8)) & 63;
-    w.m0 = (h[2] >> sh) & 63;  w.m1 = (h[2] >> (sh + 8)) & 63;
-  } else {
-    const int sh = 16 * (k - 2);
-    const uint32_t lo0 = (h[3] >> sh) & 0xff, lo1 = (h[3] >> (sh + 8)) & 0xff;
-    w.sc0 = (lo0 & 0xF) | (((h[1] >> (sh + 6)) & 3) << 4);
-    w.sc1 = (lo1 & 0xF) | (((h[1] >> (sh + 14)) & 3) << 4);
-    w.m0 = (lo0 >> 4) | (((h[2] >> (sh + 6)) & 3) << 4);
-    w.m1 = (lo1 >> 4) | (((h[2] >> (sh + 14)) & 3) << 4);
-  }
-  ld_words_al<8, AL>(p + 16 + 32 * k, w.q);
+  // get_scale_min_k4 for groups j = 2k, 2k+1 (src/kquant.lisp:64-72), both at once
+  // as two bytes: j < 4 reads six bits of bytes j and j+4; j >= 4 joins the nibbles
+  // of byte j+4 with the top two bits of bytes j-4 and j
+  const uint32_t a = (h[1] >> o.sh) & 0xffffu, b = (h[2] >> o.sh) & 0xffffu, c = (h[3] >> o.sh) & 0xffffu;
+  const uint32_t sc_lo = a & 0x3f3fu, mn_lo = b & 0x3f3fu;
+  const uint32_t sc_hi = (c & 0x0f0fu) | ((a >> 2) & 0x3030u), mn_hi = ((c >> 4) & 0x0f0fu) | ((b >> 2) & 0x3030u);
+  w.sc = o.high ? sc_hi : sc_lo;
+  w.mn = o.high ? mn_hi : mn_lo;
 }
 __device__ __forceinline__ float dot(const WReg<ILL_Q4_K>& w, const XReg<ILL_Q4_K>& x) {
   // high nibbles stay in place (16 * q as an unsigned byte); the 16 comes out of the sum
@@ -157,14 +177,24 @@ __device__ __forceinline__ float dot(const WReg<ILL_Q4_K>& w, const XReg<ILL_Q4_
     lo = __dp4a((int)(w.q[i] & 0x0F0F0F0Fu), (int)x.q[i], lo);
     hi = dp4a_us(w.q[i] & 0xF0F0F0F0u, (int)x.q[8 + i], hi);
   }
-  const int isum = lo * w.sc0 + (hi >> 4) * w.sc1, imin = w.m0 * x.bs0 + w.m1 * x.bs1;
+  const int isum = lo * (int)(w.sc & 0xff) + (hi >> 4) * (int)(w.sc >> 8);
+  const int imin = dp2a_lo(x.bsp, (int)w.mn, 0);
   return (x.d * w.d) * (float)isum - (x.d * w.dmin) * (float)imin;
 }
 
-// ---- Q6_K: unit = half c, 16-lane half hq: four groups of 16 ------------------
-template <> struct XReg<ILL_Q6_K> { uint32_t q[16]; float d; int bs[4]; };
+// ---- Q6_K: unit = half c, 16-weight column hq of each 32: four groups of 16 ------
+template <> struct XReg<ILL_Q6_K> { uint32_t q[16]; float d; int bs[4]; };  // bs: 32 * the group's sum
 template <> struct WReg<ILL_Q6_K> { uint32_t q[16]; float d; int sc[4]; };
+template <> struct UPos<ILL_Q6_K> { int offa, offh, offs, offd, sh; };
 
+__device__ __forceinline__ void unit_pos(UPos<ILL_Q6_K>& o, int u) {
+  const int i = u >> 2, c = (u >> 1) & 1, hq = u & 1, b = 210 * i;
+  o.offa = b + 64 * c + 16 * hq;
+  o.offh = b + 128 + 32 * c + 16 * hq;
+  o.offs = b + 192 + 8 * c;
+  o.offd = b + 208;
+  o.sh = 8 * hq;
+}
 __device__ __forceinline__ void load_x(XReg<ILL_Q6_K>& x, const ActS& a, int u) {
   const int i = u >> 2, c = (u >> 1) & 1, hq = u & 1;
   const i8* q = a.q + 256 * i + 128 * c + 16 * hq;
@@ -172,19 +202,17 @@ __device__ __forceinline__ void load_x(XReg<ILL_Q6_K>& x, const ActS& a, int u) 
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     ld_x128<1>(q + 32 * g, x.q + 4 * g);
-    x.bs[g] = bs[2 * g];
+    x.bs[g] = 32 * (int)bs[2 * g];
   }
   x.d = a.s[i];
 }
 template <int AL = 1>
-__device__ __forceinline__ void load_w(WReg<ILL_Q6_K>& w, const u8* row, int u) {
-  const int i = u >> 2, c = (u >> 1) & 1, hq = u & 1;
-  const u8* p = row + 210 * i;
+__device__ __forceinline__ void load_w(WReg<ILL_Q6_K>& w, const u8* row, const UPos<ILL_Q6_K>& o, const IqTables&) {
   uint32_t a[4], b[4], h[4], s[2];
-  ld_words<4>(p + 64 * c + 16 * hq, a);
-  ld_words<4>(p + 64 * c + 32 + 16 * hq, b);
-  ld_words<4>(p + 128 + 32 * c + 16 * hq, h);
-  ld_words<2>(p + 192 + 8 * c, s);  // the half's eight int8 scales
+  ld_words<4>(row + o.offa, a);
+  ld_words<4>(row + o.offa + 32, b);
+  ld_words<4>(row + o.offh, h);
+  ld_words<2>(row + o.offs, s);  // the half's eight int8 scales
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     w.q[j]      = (a[j] & 0x0F0F0F0Fu) | ((h[j] << 4) & 0x30303030u);
@@ -193,29 +221,37 @@ __device__ __forceinline__ void load_w(WReg<ILL_Q6_K>& w, const u8* row, int u) 
     w.q[12 + j] = ((b[j] >> 4) & 0x0F0F0F0Fu) | ((h[j] >> 2) & 0x30303030u);
   }
   // scale of group g: byte hq + 2g of the eight
-  const uint32_t lo = s[0] >> (8 * hq), hi = s[1] >> (8 * hq);
+  const uint32_t lo = s[0] >> o.sh, hi = s[1] >> o.sh;
   w.sc[0] = (int)(signed char)(lo & 0xff);
   w.sc[1] = (int)(signed char)((lo >> 16) & 0xff);
   w.sc[2] = (int)(signed char)(hi & 0xff);
   w.sc[3] = (int)(signed char)((hi >> 16) & 0xff);
-  w.d = h2f(ld_u16(p + 208));
+  w.d = h2f(ld_u16(row + o.offd));
 }
 __device__ __forceinline__ float dot(const WReg<ILL_Q6_K>& w, const XReg<ILL_Q6_K>& x) {
   int isum = 0;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    int d = 0;
+    int d = -x.bs[g];  // the quants are 0..63; their -32 comes off through the activations' sum
 #pragma unroll
     for (int j = 0; j < 4; ++j) d = __dp4a((int)w.q[4 * g + j], (int)x.q[4 * g + j], d);
-    isum += w.sc[g] * (d - 32 * x.bs[g]);
+    isum += w.sc[g] * d;
   }
   return (w.d * x.d) * (float)isum;
 }
 
 // ---- Q2_K: unit = half h, 16-byte half: four groups of 16 ---------------------
 template <> struct XReg<ILL_Q2_K> { uint32_t q[16]; float d; int bs[4]; };
-template <> struct WReg<ILL_Q2_K> { uint32_t q[4]; float d, dmin; int sc[4]; };
+template <> struct WReg<ILL_Q2_K> { uint32_t q[4]; float d, dmin; uint32_t sc[4]; };
+template <> struct UPos<ILL_Q2_K> { int offs, offq, offd, sh; };
 
+__device__ __forceinline__ void unit_pos(UPos<ILL_Q2_K>& o, int u) {
+  const int i = u >> 2, h = (u >> 1) & 1, half = u & 1, b = 84 * i;
+  o.offs = b + 8 * h;
+  o.offq = b + 16 + 32 * h + 16 * half;
+  o.offd = b + 80;
+  o.sh = 8 * half;
+}
 __device__ __forceinline__ void load_x(XReg<ILL_Q2_K>& x, const ActS& a, int u) {
   const int i = u >> 2, h = (u >> 1) & 1, half = u & 1;
   const i8* q = a.q + 256 * i + 128 * h + 16 * half;
@@ -228,15 +264,13 @@ __device__ __forceinline__ void load_x(XReg<ILL_Q2_K>& x, const ActS& a, int u) 
   x.d = a.s[i];
 }
 template <int AL = 1>
-__device__ __forceinline__ void load_w(WReg<ILL_Q2_K>& w, const u8* row, int u) {
-  const int i = u >> 2, h = (u >> 1) & 1, half = u & 1;
-  const u8* p = row + 84 * i;
+__device__ __forceinline__ void load_w(WReg<ILL_Q2_K>& w, const u8* row, const UPos<ILL_Q2_K>& o, const IqTables&) {
   uint32_t s[2], dd[1];
   constexpr int A = AL >= 4 ? 4 : 1;  // an 84-byte block keeps 4-byte alignment at best
-  ld_words_al<2, A>(p + 8 * h, s);  // the half's eight scale bytes
-  ld_words_al<4, A>(p + 16 + 32 * h + 16 * half, w.q);
-  ld_words_al<1, A>(p + 80, dd);
-  const uint32_t lo = s[0] >> (8 * half), hi = s[1] >> (8 * half);
+  ld_words_al<2, A>(row + o.offs, s);  // the half's eight scale bytes
+  ld_words_al<4, A>(row + o.offq, w.q);
+  ld_words_al<1, A>(row + o.offd, dd);
+  const uint32_t lo = s[0] >> o.sh, hi = s[1] >> o.sh;
   w.sc[0] = lo & 0xff; w.sc[1] = (lo >> 16) & 0xff; w.sc[2] = hi & 0xff; w.sc[3] = (hi >> 16) & 0xff;
   w.d = h2f(dd[0] & 0xffff);
   w.dmin = h2f(dd[0] >> 16);
@@ -248,29 +282,30 @@ __device__ __forceinline__ float dot(const WReg<ILL_Q2_K>& w, const XReg<ILL_Q2_
     int d = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) d = __dp4a((int)((w.q[j] >> (2 * k)) & 0x03030303u), (int)x.q[4 * k + j], d);
-    isum += (w.sc[k] & 15) * d;
-    mins += (w.sc[k] >> 4) * x.bs[k];
+    isum += (int)(w.sc[k] & 15) * d;
+    mins += (int)(w.sc[k] >> 4) * x.bs[k];
   }
   return (x.d * w.d) * (float)isum - (x.d * w.dmin) * (float)mins;
 }
 
 // ---- IQ2_XXS: unit = sub-block of 32 -------------------------------------------
-// The codebook (256 x 8 magnitudes) and the sign patterns expanded to byte
-// masks (0xFF where the weight is negative) sit in shared memory.
-struct IqTables { const uint2* grid; const uint2* smask; };
-
 template <> struct XReg<ILL_IQ2_XXS> { uint32_t q[8]; float d; };
 template <> struct WReg<ILL_IQ2_XXS> { uint32_t q[8]; float d; float ls; };
+template <> struct UPos<ILL_IQ2_XXS> { int off, qoff; };
 
+__device__ __forceinline__ void unit_pos(UPos<ILL_IQ2_XXS>& o, int u) {
+  o.off = 66 * (u >> 3);
+  o.qoff = o.off + 2 + 8 * (u & 7);
+}
 __device__ __forceinline__ void load_x(XReg<ILL_IQ2_XXS>& x, const ActS& a, int u) {
   ld_x128<2>(a.q + 32 * u, x.q);
   x.d = a.s[u >> 3];
 }
 template <int AL = 1>
-__device__ __forceinline__ void load_w(WReg<ILL_IQ2_XXS>& w, const u8* row, int u, const IqTables& t) {
-  const u8* p = row + 66 * (u >> 3);
+__device__ __forceinline__ void load_w(WReg<ILL_IQ2_XXS>& w, const u8* row, const UPos<ILL_IQ2_XXS>& o,
+                                       const IqTables& t) {
   uint32_t v[2];
-  ld_words<2>(p + 2 + 8 * (u & 7), v);
+  ld_words<2>(row + o.qoff, v);
   const uint32_t idx = v[0], aux = v[1];
 #pragma unroll
   for (int l = 0; l < 4; ++l) {
@@ -281,7 +316,7 @@ __device__ __forceinline__ void load_w(WReg<ILL_IQ2_XXS>& w, const u8* row, int 
     w.q[2 * l + 1] = (g.y ^ m.y) + (m.y & 0x01010101u);
   }
   w.ls = 0.5f + (float)(aux >> 28);
-  w.d = h2f(ld_u16(p));
+  w.d = h2f(ld_u16(row + o.off));
 }
 __device__ __forceinline__ float dot(const WReg<ILL_IQ2_XXS>& w, const XReg<ILL_IQ2_XXS>& x) {
   int acc = 0;

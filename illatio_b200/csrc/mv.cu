@@ -191,11 +191,13 @@ __global__ void __launch_bounds__(MV_THREADS) mvn_kernel(const MvParams p) {
         const u8* rowp = rows_s + (size_t)r * p.row_bytes;
         for (int u = lane_in; u < p.units; u += L) {
           WReg<FMT> w;
-          if constexpr (IQ) load_w(w, rowp, u, iqt); else load_w(w, rowp, u);
+          UPos<FMT> up;
+          unit_pos(up, u);
+          load_w(w, rowp, up, iqt);
           if constexpr (GLU) {
             WReg<FMT> w2;
             const u8* rowu = rows_u + (size_t)r * p.row_bytes;
-            if constexpr (IQ) load_w(w2, rowu, u, iqt); else load_w(w2, rowu, u);
+            load_w(w2, rowu, up, iqt);
             ActS a;
             a.q = (const i8*)xreg;
             a.s = (const float*)(xreg + p.xs_off);
@@ -342,6 +344,7 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
 
   const int L = p.lanes_per_row, sub = lane / L, sl = lane - sub * L, nsub = 32 / L;
   XReg<FMT> x[UPT];
+  UPos<FMT> up[UPT];
   {
     const long long tok0 = (long long)z * p.x_seg;
     const int nsc = FMT == ILL_Q8_0 ? p.cols / 32 : p.cols / 256;
@@ -352,6 +355,7 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
 #pragma unroll
     for (int k = 0; k < UPT; ++k) {
       const int u = sl + k * L;
+      unit_pos(up[k], u);
       if (u < p.units) load_x(x[k], a, u);
     }
   }
@@ -382,11 +386,11 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
           const int u = sl + k * L;
           if (k < UPT - 1 || u < p.units) {
             WReg<FMT> w;
-            if constexpr (IQ) load_w<AL>(w, rowp, u, iqt); else load_w<AL>(w, rowp, u);
+            load_w<AL>(w, rowp, up[k], iqt);
             sum += dot(w, x[k]);
             if constexpr (GLU) {
               WReg<FMT> w2;
-              if constexpr (IQ) load_w<AL>(w2, rowu, u, iqt); else load_w<AL>(w2, rowu, u);
+              load_w<AL>(w2, rowu, up[k], iqt);
               sum2 += dot(w2, x[k]);
             }
           }
@@ -468,6 +472,10 @@ static long long tile_target(long long total_bytes, uint32_t cap) {
   return t;
 }
 
+// Tuning overrides for experiments (ill_set_tuning): lanes a row, rows a warp
+// tile, stages, CTAs per SM.  0 = planned.
+static int g_env_L = 0, g_env_TR = 0, g_env_NST = 0, g_env_CTAS = 0;
+
 // One-token plan: L lanes a row and UPT units a lane, chosen for the fewest idle
 // lanes; a warp's stage holds (32/L) * RPS rows, about 3.5 KB.
 static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu, MvPlan* pl) {
@@ -479,16 +487,19 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
   for (int L = 32; L >= 8; L >>= 1) {
     const int upt = (units + L - 1) / L;
     if (upt > upt_max) continue;
-    const double eff = (double)units / ((double)L * upt) - 0.01 * upt;  // ties: fewer registers
+    const double eff = (double)units / ((double)L * upt) + (L == 16 ? 0.02 : L == 32 ? 0.01 : 0.0);  // ties: 16, then 32
     if (eff > best) { best = eff; bestL = L; bestU = upt; }
   }
+  if (g_env_L && (units + g_env_L - 1) / g_env_L <= upt_max) { bestL = g_env_L; bestU = (units + g_env_L - 1) / g_env_L; }
   if (!bestL) return ILL_ERR_UNSUPPORTED;
   const int nsub = 32 / bestL;
-  // rows per warp tile: ~3.5 KB a stage, but small matrices are cut finer so that every warp gets some
+  // rows per warp tile: about 3 KB a stage (small stages keep more CTAs resident, which is what
+  // hides the copy latency), and small matrices are cut finer so that every warp gets some
   const long long warps = (long long)sm_count() * 16;
-  long long tr = 3584 / row_bytes;
+  long long tr = 3072 / row_bytes;
   const long long share = (total_rows * nseg + warps - 1) / warps;
   if (tr > share) tr = share;
+  if (g_env_TR) tr = g_env_TR;
   tr = tr / nsub * nsub;
   if (tr < nsub) tr = nsub;
   pl->one = true;
@@ -496,8 +507,11 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
   pl->lanes = bestL;
   pl->tps = pl->slots = 0;
   pl->rows_per_tile = (int)tr;
-  pl->nstages = row_bytes * tr > 6144 ? 3 : 4;
   pl->stage_bytes = align_up((uint32_t)(tr * row_bytes) + 32, 128);
+  // stages: four if two CTAs still fit an SM, else three, else two
+  const uint32_t per_stage = pl->stage_bytes * (glu ? 2 : 1) * (MV_THREADS / 32);
+  pl->nstages = per_stage * 4 <= 110 * 1024 ? 4 : per_stage * 3 <= 110 * 1024 ? 3 : per_stage * 3 <= 200 * 1024 ? 3 : 2;
+  if (g_env_NST) pl->nstages = g_env_NST;
   pl->x_bytes = pl->xs_off = pl->bs_off = 0;
   pl->smem = pl->stage_bytes * (glu ? 2 : 1) * pl->nstages * (MV_THREADS / 32) + (fmt == ILL_IQ2_XXS ? 3072 : 0) +
              8 * pl->nstages * (MV_THREADS / 32) + 64;
@@ -662,6 +676,7 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
   // persistent grid: as many CTAs as can be resident, split over the segments
   int per_sm = (int)((227u * 1024u) / (pl.smem + 1024u));
   per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
+  if (g_env_CTAS) per_sm = g_env_CTAS;
   int gx = (sm_count() * per_sm + nseg - 1) / nseg;
   const int work = pl.one ? (tiles + MV_THREADS / 32 - 1) / (MV_THREADS / 32) : tiles;  // a warp a tile, or a CTA a tile
   if (gx > work) gx = work;
@@ -672,6 +687,16 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
 }  // namespace ill
 
 using namespace ill;
+
+extern "C" int ill_set_tuning(int lanes, int tile_rows, int stages, int ctas_per_sm) {
+  if (lanes && lanes != 8 && lanes != 16 && lanes != 32) return ILL_ERR_ARG;
+  if (tile_rows < 0 || stages < 0 || stages > 8 || ctas_per_sm < 0 || ctas_per_sm > 16) return ILL_ERR_ARG;
+  g_env_L = lanes;
+  g_env_TR = tile_rows;
+  g_env_NST = stages;
+  g_env_CTAS = ctas_per_sm;
+  return ILL_OK;
+}
 
 extern "C" int ill_mv(int fmt, ill_dptr w, int rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y,
                       ill_dptr bias, int acc, int n, ill_stream stream) {

@@ -14,7 +14,7 @@ from . import blocks as B
 from . import cuda_dense as D
 
 
-def run(fmt, rows, cols, n=1, glu=False, copies=2, iters=10, warmup=2):
+def run(fmt, rows, cols, n=1, glu=False, copies=2, iters=10, warmup=2, graph=False):
     dev = torch.device("cuda")
     mats = [D.CMat("w", fmt, rows, cols, B.synth_matrix_torch(fmt, rows, cols, seed=5 + i, device=dev))
             for i in range(copies * (2 if glu else 1))]
@@ -33,10 +33,25 @@ def run(fmt, rows, cols, n=1, glu=False, copies=2, iters=10, warmup=2):
         one(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        one(i)
-    e1.record()
+    if graph:  # the launches back to back in one CUDA graph: no host launch cost between them
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for i in range(iters):
+                    one(i)
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record()
+        for i in range(iters):
+            one(i)
+        e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / iters
     nbytes = mats[0].nbytes * (2 if glu else 1)
@@ -54,8 +69,9 @@ def main():
     ap.add_argument("--copies", type=int, default=2)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--graph", action="store_true")
     a = ap.parse_args()
-    print(json.dumps(run(B.BY_NAME[a.fmt], a.rows, a.cols, a.n, a.glu, a.copies, a.iters, a.warmup)))
+    print(json.dumps(run(B.BY_NAME[a.fmt], a.rows, a.cols, a.n, a.glu, a.copies, a.iters, a.warmup, a.graph)))
 
 
 if __name__ == "__main__":

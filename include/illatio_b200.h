@@ -87,6 +87,13 @@ ILL_API int ill_device_status(unsigned int* out, ill_stream stream);
  * src/cuda.lisp:345-350.) */
 ILL_API int ill_set_pdl(int on);
 
+/* Overrides the one-token product's launch plan, for tuning experiments: lanes
+ * that share a row (8, 16 or 32), rows per warp tile, pipeline stages, CTAs per
+ * SM.  0 leaves a value to the planner; (0,0,0,0) restores the defaults.  Not
+ * for production use.  (No counterpart in the reference, whose launch shapes
+ * are fixed at each Lisp call site.) */
+ILL_API int ill_set_tuning(int lanes, int tile_rows, int stages, int ctas_per_sm);
+
 /* ---- activations ----------------------------------------------------------- */
 
 /* X (nblocks*32 floats) -> Q8_0 blocks: d = amax/127, q = round-half-even(x *
