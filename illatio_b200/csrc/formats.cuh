@@ -325,6 +325,90 @@ __device__ __forceinline__ float dot(const WReg<ILL_IQ2_XXS>& w, const XReg<ILL_
   return ((w.d * x.d) * ((float)acc * w.ls)) * 0.25f;
 }
 
+// ---- activations staged in shared memory as planes ---------------------------------
+// For rows staged in column chunks the activations cannot stay in registers; they
+// are read from shared memory per unit.  To keep those reads free of bank
+// conflicts (consecutive lanes take consecutive units) the 16-byte pieces of a
+// unit's activations are stored plane by plane: piece j of unit u at
+// (j * U + u) * 16; the sums of 16 likewise, [g][u] as int16 (Q6_K, Q2_K), or
+// already paired and packed per unit (Q4_K).
+struct ActP {
+  const u8* q;        // planes of 16-byte pieces
+  const float* s;     // scales, as in ActS
+  const int16_t* bs;  // planes of sums (Q6_K, Q2_K); Q4_K: packed pair sums, an int per unit
+  int U;
+};
+template <int FMT> struct PlaneGeom;
+template <> struct PlaneGeom<ILL_Q8_0>    { static constexpr int PPU = 2, BSP = 0; };
+template <> struct PlaneGeom<ILL_IQ2_XXS> { static constexpr int PPU = 2, BSP = 0; };
+template <> struct PlaneGeom<ILL_Q4_K>    { static constexpr int PPU = 4, BSP = 2; };  // 4 bytes a unit
+template <> struct PlaneGeom<ILL_Q6_K>    { static constexpr int PPU = 4, BSP = 4; };  // 4 int16 a unit
+template <> struct PlaneGeom<ILL_Q2_K>    { static constexpr int PPU = 4, BSP = 4; };
+
+// source piece (16 bytes of the token's quants) of piece j of unit u
+template <int FMT>
+__device__ __forceinline__ int plane_src(int u, int j) {
+  if constexpr (FMT == ILL_Q6_K || FMT == ILL_Q2_K) return 16 * (u >> 2) + 8 * ((u >> 1) & 1) + 2 * j + (u & 1);
+  else return PlaneGeom<FMT>::PPU * u + j;
+}
+// bytes of shared memory the planes of a token with U units take (16-byte multiple)
+template <int FMT>
+__host__ __device__ inline uint32_t plane_bytes(int U, int nsc) {
+  return (uint32_t)(PlaneGeom<FMT>::PPU * U * 16) + ((uint32_t)(4 * nsc + 15) & ~15u) +
+         ((uint32_t)(PlaneGeom<FMT>::BSP * 2 * U + 15) & ~15u);
+}
+// Stage one token's activations (global, ActS layout) as planes at DST; all threads of the CTA.
+template <int FMT>
+__device__ __forceinline__ void planes_fill(u8* dst, const ActS& a, int U, int nsc, ActP& out) {
+  constexpr int PPU = PlaneGeom<FMT>::PPU;
+  uint4* dq = (uint4*)dst;
+  for (int d = threadIdx.x; d < PPU * U; d += blockDim.x) {
+    const int j = d / U, u = d - j * U;
+    dq[d] = ((const uint4*)a.q)[plane_src<FMT>(u, j)];
+  }
+  float* ds = (float*)(dst + PPU * U * 16);
+  for (int i = threadIdx.x; i < nsc; i += blockDim.x) ds[i] = a.s[i];
+  int16_t* db = (int16_t*)((u8*)ds + ((4 * nsc + 15) & ~15));
+  if constexpr (FMT == ILL_Q4_K) {
+    int* dp = (int*)db;
+    for (int u = threadIdx.x; u < U; u += blockDim.x) {
+      const int16_t* b = a.bs + 4 * u;  // 16 i + 4 k with u = 4 i + k
+      dp[u] = ((b[0] + b[1]) & 0xffff) | ((b[2] + b[3]) << 16);
+    }
+  } else if constexpr (FMT == ILL_Q6_K || FMT == ILL_Q2_K) {
+    for (int d = threadIdx.x; d < 4 * U; d += blockDim.x) {
+      const int g = d / U, u = d - g * U;
+      db[d] = a.bs[16 * (u >> 2) + 8 * ((u >> 1) & 1) + 2 * g + (u & 1)];
+    }
+  }
+  out.q = dst;
+  out.s = ds;
+  out.bs = db;
+  out.U = U;
+}
+template <int FMT>
+__device__ __forceinline__ void load_x_planes(XReg<FMT>& x, const ActP& a, int u) {
+  constexpr int PPU = PlaneGeom<FMT>::PPU;
+#pragma unroll
+  for (int j = 0; j < PPU; ++j) {
+    const uint4 v = ((const uint4*)a.q)[j * a.U + u];
+    x.q[4 * j] = v.x; x.q[4 * j + 1] = v.y; x.q[4 * j + 2] = v.z; x.q[4 * j + 3] = v.w;
+  }
+  if constexpr (FMT == ILL_Q8_0) x.s = a.s[u];
+  else if constexpr (FMT == ILL_IQ2_XXS) x.d = a.s[u >> 3];
+  else {
+    x.d = a.s[u >> 2];
+    if constexpr (FMT == ILL_Q4_K) x.bsp = ((const int*)a.bs)[u];
+    else if constexpr (FMT == ILL_Q6_K) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) x.bs[g] = 32 * (int)a.bs[g * a.U + u];
+    } else {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) x.bs[g] = (int)a.bs[g * a.U + u];
+    }
+  }
+}
+
 // Fills the IQ2_XXS tables in shared memory (call from all threads, then sync).
 __device__ __forceinline__ void iq_tables_fill(uint2* grid, uint2* smask, const uint64_t* ggrid, const u8* gsigns) {
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {

@@ -42,7 +42,9 @@ struct MvParams {
   int n;                 // tokens
   int acc;
   int rows_per_tile, lanes_per_row;
-  int tps, slots;        // one-token kernel: threads per row slot, row slots
+  int nchunks;           // one-token kernel: column chunks a row is staged in (1: whole rows)
+  int chunk_units;       // units per chunk
+  uint32_t chunk_bytes;
   uint32_t stage_bytes;  // bytes of one stage (one matrix' part of it in GLU modes)
   int nstages;
   uint32_t x_bytes;      // shared bytes of the activation region
@@ -269,30 +271,38 @@ __global__ void __launch_bounds__(MV_THREADS) mvn_kernel(const MvParams p) {
   }
 }
 
-// ---- one token: activations in registers, a pipeline per warp --------------------
+// ---- one token: a pipeline per warp ------------------------------------------------
 //
-// Each warp streams its own tiles of rows through its own ring of stages: lane 0
-// issues the bulk copies, all lanes wait on the stage's mbarrier, and after a
-// __syncwarp the stage is refilled -- no CTA-wide barrier anywhere.  A row is
-// shared by L consecutive lanes (L = 8, 16 or 32, so 32/L rows are in progress
-// per warp); lane sl of them owns units sl, sl+L, ... of every row, and loads
-// those units' activations from global memory into registers once.  A row's
-// lanes meet with log2(L) shuffles.
-template <int FMT, int MODE, int UPT, int AL>
+// Each warp streams its own tiles through its own ring of stages: lane 0 issues
+// the bulk copies, all lanes wait on the stage's mbarrier, and after a __syncwarp
+// the stage is refilled -- no CTA-wide barrier in the loop.  A row is shared by L
+// consecutive lanes (L = 8, 16 or 32, so 32/L rows are in progress per warp);
+// lane sl of them owns units sl, sl+L, ... and keeps those units' activations in
+// registers, loaded from global memory once.  A row's lanes meet with log2(L)
+// shuffles.
+//
+// A warp's unit of work is a group of G stages whose sums it carries in
+// registers: the gate rows and then the up rows of a gated product (G = 2), or,
+// for rows too long to stage whole (XS), a row's column chunks one after another
+// (G = chunks, or twice that when gated).  In XS mode the activations are staged
+// in shared memory once per CTA and read from there.
+constexpr int MV_MAXRI = 4;  // row iterations a warp tile may take when sums are carried
+
+template <int FMT, int MODE, int UPT, int AL, bool XS>
 __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
   extern __shared__ __align__(128) u8 smem[];
   constexpr bool GLU = MODE != MODE_PLAIN;
   constexpr bool IQ = FMT == ILL_IQ2_XXS;
-  constexpr int WARPS = MV_THREADS / 32;
+  const int WARPS = blockDim.x >> 5;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int z = blockIdx.y;
 
-  const uint32_t stage_stride = p.stage_bytes * (GLU ? 2u : 1u);
-  u8* wstage = smem + (size_t)warp * stage_stride * p.nstages;
-  u8* after = smem + (size_t)WARPS * stage_stride * p.nstages;
+  u8* wstage = smem + (size_t)warp * p.stage_bytes * p.nstages;
+  u8* after = smem + (size_t)WARPS * p.stage_bytes * p.nstages;
   uint2* iq_grid = (uint2*)after;
   uint2* iq_smask = iq_grid + 256;
   uint64_t* full = (uint64_t*)(after + (IQ ? 3072 : 0)) + warp * p.nstages;
+  u8* xsm = after + (IQ ? 3072 : 0) + 8 * WARPS * p.nstages;  // XS: the activations (16-byte aligned)
 
   const u8* wbase[MV_MAX_MATS];
   if (p.ptrs) {
@@ -304,47 +314,57 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
 #pragma unroll
     for (int i = 0; i < MV_MAX_MATS; ++i) wbase[i] = p.w[i];
   }
-  const int ntiles = p.tile0[p.nmat];
+  const int ngroups = p.tile0[p.nmat];
+  const int NC = XS ? p.nchunks : 1;
+  const int G = (GLU ? 2 : 1) * NC;
   const int first = blockIdx.x * WARPS + warp, step = gridDim.x * WARPS;
 
-  auto issue = [&](int tile, int s) {
-    const TileRef t = tile_ref(p, tile, wbase);
-    const uint32_t len = (uint32_t)t.nrows * (uint32_t)p.row_bytes;
-    u8* dst = wstage + (size_t)s * stage_stride;
-    const uintptr_t a0 = (uintptr_t)t.g & ~(uintptr_t)15;
-    const uint32_t bytes = (uint32_t)((((uintptr_t)t.g + len + 15) & ~(uintptr_t)15) - a0);
-    if (GLU) {
-      const u8* g2 = wbase[1] + (long long)t.row0 * p.row_bytes;
-      const uintptr_t b0 = (uintptr_t)g2 & ~(uintptr_t)15;
-      const uint32_t bytes2 = (uint32_t)((((uintptr_t)g2 + len + 15) & ~(uintptr_t)15) - b0);
-      mbar_expect_tx(&full[s], bytes + bytes2);
-      bulk_g2s(dst, (const void*)a0, bytes, &full[s]);
-      bulk_g2s(dst + p.stage_bytes, (const void*)b0, bytes2, &full[s]);
-    } else {
-      mbar_expect_tx(&full[s], bytes);
-      bulk_g2s(dst, (const void*)a0, bytes, &full[s]);
+  // stage G of group GRP: which matrix (gate / up), which column chunk, where its bytes are
+  auto locate = [&](int grp, int g, int& nrows, long long& row0, int& m) -> const u8* {
+    const TileRef t = tile_ref(p, grp, wbase);
+    nrows = t.nrows;
+    row0 = t.row0;
+    m = t.m;
+    const int which = GLU ? g / NC : 0, c = g - which * NC;
+    const u8* base = GLU ? (wbase[which] + (long long)t.row0 * p.row_bytes) : t.g;
+    return base + (size_t)c * p.chunk_bytes;
+  };
+  auto issue = [&](int grp, int g, int s) {
+    int nrows, m;
+    long long row0;
+    const u8* src = locate(grp, g, nrows, row0, m);
+    uint32_t len = (uint32_t)nrows * (uint32_t)p.row_bytes;
+    if (XS) {
+      const int c = g % NC;
+      len = min(p.chunk_bytes, (uint32_t)p.row_bytes - (uint32_t)c * p.chunk_bytes);
     }
+    const uintptr_t a0 = (uintptr_t)src & ~(uintptr_t)15;
+    const uint32_t bytes = (uint32_t)((((uintptr_t)src + len + 15) & ~(uintptr_t)15) - a0);
+    mbar_expect_tx(&full[s], bytes);
+    bulk_g2s(wstage + (size_t)s * p.stage_bytes, (const void*)a0, bytes, &full[s]);
   };
 
+  // the warp's stages in order: (group, g) for i = 0, 1, ...
+  int i_grp = first, i_g = 0;  // next stage to issue
+  auto issue_next = [&](int s) {
+    if (i_grp < ngroups) {
+      issue(i_grp, i_g, s);
+      if (++i_g == G) { i_g = 0; i_grp += step; }
+    }
+  };
   if (lane == 0) {
     for (int s = 0; s < p.nstages; ++s) mbar_init(&full[s], 1);
     mbar_fence_init();
-    for (int s = 0; s < p.nstages; ++s) {  // weights do not depend on the previous kernel
-      const int tile = first + s * step;
-      if (tile < ntiles) issue(tile, s);
-    }
+    for (int s = 0; s < p.nstages; ++s) issue_next(s);  // weights do not depend on the previous kernel
   }
-  if (IQ) {
-    iq_tables_fill(iq_grid, iq_smask, ill_iq2xxs_grid, ill_ksigns_iq2xs);
-    __syncthreads();
-  }
+  if (IQ) iq_tables_fill(iq_grid, iq_smask, ill_iq2xxs_grid, ill_ksigns_iq2xs);
   pdl_launch_dependents();
   pdl_wait();  // the activations may come from the previous kernel
-  __syncwarp();
 
   const int L = p.lanes_per_row, sub = lane / L, sl = lane - sub * L, nsub = 32 / L;
-  XReg<FMT> x[UPT];
+  XReg<FMT> x[XS ? 1 : UPT];
   UPos<FMT> up[UPT];
+  ActP xa;
   {
     const long long tok0 = (long long)z * p.x_seg;
     const int nsc = FMT == ILL_Q8_0 ? p.cols / 32 : p.cols / 256;
@@ -352,80 +372,112 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
     a.q = p.xq + tok0 * p.cols;
     a.s = p.xs + tok0 * nsc;
     a.bs = p.xsum + tok0 * (p.cols / 16);
+    if constexpr (XS) planes_fill<FMT>(xsm, a, p.units, nsc, xa);
 #pragma unroll
     for (int k = 0; k < UPT; ++k) {
       const int u = sl + k * L;
       unit_pos(up[k], u);
-      if (u < p.units) load_x(x[k], a, u);
+      if constexpr (!XS) {
+        if (u < p.units) load_x(x[k], a, u);
+      }
     }
   }
+  if (IQ || XS) __syncthreads();  // tables / activations staged
+  else __syncwarp();
   IqTables iqt;
   iqt.grid = iq_grid;
   iqt.smask = iq_smask;
 
   int s = 0;
   uint32_t parity = 0;
-  for (int tile = first; tile < ntiles; tile += step) {
-    bool ok = mbar_wait(&full[s], parity, p.status, ST_MV_WAIT + FMT);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) break;  // the copy never landed: the status word says so; nothing is read
-    const TileRef t = tile_ref(p, tile, wbase);
-    const u8* sbase = wstage + (size_t)s * stage_stride;
-    const u8* rows_s = sbase + ((uintptr_t)t.g & 15);
-    const u8* rows_u = sbase + p.stage_bytes + ((uintptr_t)(wbase[1] + (long long)t.row0 * p.row_bytes) & 15);
-
-    for (int r0 = 0; r0 < t.nrows; r0 += nsub) {
-      const int r = r0 + sub;
-      const bool valid = r < t.nrows;
-      float sum = 0.0f, sum2 = 0.0f;
-      if (valid) {
-        const u8* rowp = rows_s + (size_t)r * p.row_bytes;
-        const u8* rowu = rows_u + (size_t)r * p.row_bytes;
+  bool dead = false;
+  for (int grp = first; grp < ngroups && !dead; grp += step) {
+    float acc[MV_MAXRI], acc2[MV_MAXRI];
 #pragma unroll
-        for (int k = 0; k < UPT; ++k) {
-          const int u = sl + k * L;
-          if (k < UPT - 1 || u < p.units) {
-            WReg<FMT> w;
-            load_w<AL>(w, rowp, up[k], iqt);
-            sum += dot(w, x[k]);
-            if constexpr (GLU) {
-              WReg<FMT> w2;
-              load_w<AL>(w2, rowu, up[k], iqt);
-              sum2 += dot(w2, x[k]);
+    for (int i = 0; i < MV_MAXRI; ++i) acc[i] = acc2[i] = 0.0f;
+    int nrows = 0, m = 0;
+    long long row0 = 0;
+    for (int g = 0; g < G; ++g) {
+      bool ok = mbar_wait(&full[s], parity, p.status, ST_MV_WAIT + FMT);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { dead = true; break; }  // the copy never landed: the status word says so; nothing is read
+      const u8* src = locate(grp, g, nrows, row0, m);
+      const u8* rows_s = wstage + (size_t)s * p.stage_bytes + ((uintptr_t)src & 15);
+      const int which = GLU ? g / NC : 0, c = g - which * NC;
+      const int ubase = XS ? c * p.chunk_units : 0;
+      const int uend = XS ? min(p.units, ubase + p.chunk_units) : p.units;
+      // plain, whole rows: the sums of a row iteration are written at once, so a tile may take any
+      // number of them; carried sums (gated, chunked) are limited to MV_MAXRI iterations
+#pragma unroll 1
+      for (int r0 = 0, ri = 0; r0 < nrows; r0 += nsub, ++ri) {
+        const int r = r0 + sub;
+        const bool valid = r < nrows;
+        float sum = 0.0f;
+        if (valid) {
+          const u8* rowp = rows_s + (size_t)r * p.row_bytes;
+#pragma unroll
+          for (int k = 0; k < UPT; ++k) {
+            const int u = ubase + sl + k * L;
+            if ((!XS && k < UPT - 1) || u < uend) {
+              if constexpr (XS) load_x_planes<FMT>(x[0], xa, u);
+              WReg<FMT> w;
+              load_w<AL>(w, rowp, up[k], iqt);
+              sum += dot(w, x[XS ? 0 : k]);
             }
           }
         }
-      }
-      for (int o = L >> 1; o > 0; o >>= 1) {
-        sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if constexpr (GLU) sum2 += __shfl_xor_sync(0xffffffffu, sum2, o);
-      }
-      if (valid && sl == 0) {
-        const long long row = t.row0 + r;
-        if constexpr (MODE == MODE_GLU) {
-          p.y[0][(long long)z * p.y_seg + row] = (sum / (1.0f + expf(-sum))) * sum2;
-        } else if constexpr (MODE == MODE_MOE_GLU) {
-          // D4-ROUTED!'s middle (src/ds4f.lisp:1016-1019): silu(min(g,c)) * clamp(u) * weight
-          float g = sum, uu = sum2;
-          if (p.clamp > 1e-6f) { g = fminf(g, p.clamp); uu = fmaxf(-p.clamp, fminf(uu, p.clamp)); }
-          float sg;
-          if (g >= 0.0f) sg = __fdiv_rn(1.0f, 1.0f + expf(-g));
-          else { const float e = expf(g); sg = __fdiv_rn(e, 1.0f + e); }
-          p.y[0][(long long)z * p.y_seg + row] = __fmul_rn(__fmul_rn(__fmul_rn(g, sg), uu), p.seg_w[z]);
+        if constexpr (!GLU && !XS) {
+          for (int o = L >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+          if (valid && sl == 0) {
+            const long long row = row0 + r;
+            float* y = p.y[m] + (long long)z * p.y_seg;
+            float v = sum;
+            if (p.bias[m]) v += p.bias[m][row];
+            y[row] = p.acc ? y[row] + v : v;
+          }
         } else {
-          float* y = p.y[t.m] + (long long)z * p.y_seg;
-          float v = sum;
-          if (p.bias[t.m]) v += p.bias[t.m][row];
-          y[row] = p.acc ? y[row] + v : v;
+          // ri < MV_MAXRI by the plan; the select chain keeps the sums in registers
+#pragma unroll
+          for (int i = 0; i < MV_MAXRI; ++i) {
+            if (i == ri) { if (which == 0) acc[i] += sum; else acc2[i] += sum; }
+          }
+        }
+      }
+      __syncwarp();  // every lane is done with the stage
+      if (lane == 0) issue_next(s);
+      if (++s == p.nstages) { s = 0; parity ^= 1u; }
+    }
+    if constexpr (GLU || XS) {
+      if (dead) break;
+#pragma unroll
+      for (int i = 0; i < MV_MAXRI; ++i) {
+        const int r = i * nsub + sub;
+        if (i * nsub >= nrows) break;
+        float v = acc[i], v2 = acc2[i];
+        for (int o = L >> 1; o > 0; o >>= 1) {
+          v += __shfl_xor_sync(0xffffffffu, v, o);
+          if constexpr (GLU) v2 += __shfl_xor_sync(0xffffffffu, v2, o);
+        }
+        if (r < nrows && sl == 0) {
+          const long long row = row0 + r;
+          if constexpr (MODE == MODE_GLU) {
+            p.y[0][(long long)z * p.y_seg + row] = (v / (1.0f + expf(-v))) * v2;
+          } else if constexpr (MODE == MODE_MOE_GLU) {
+            // D4-ROUTED!'s middle (src/ds4f.lisp:1016-1019): silu(min(g,c)) * clamp(u) * weight
+            float g = v, uu = v2;
+            if (p.clamp > 1e-6f) { g = fminf(g, p.clamp); uu = fmaxf(-p.clamp, fminf(uu, p.clamp)); }
+            float sg;
+            if (g >= 0.0f) sg = __fdiv_rn(1.0f, 1.0f + expf(-g));
+            else { const float e = expf(g); sg = __fdiv_rn(e, 1.0f + e); }
+            p.y[0][(long long)z * p.y_seg + row] = __fmul_rn(__fmul_rn(__fmul_rn(g, sg), uu), p.seg_w[z]);
+          } else {
+            float* y = p.y[m] + (long long)z * p.y_seg;
+            if (p.bias[m]) v += p.bias[m][row];
+            y[row] = p.acc ? y[row] + v : v;
+          }
         }
       }
     }
-    __syncwarp();  // every lane is done with the stage
-    if (lane == 0) {
-      const int nt = tile + p.nstages * step;
-      if (nt < ntiles) issue(nt, s);
-    }
-    if (++s == p.nstages) { s = 0; parity ^= 1u; }
   }
 }
 
@@ -459,6 +511,10 @@ static int unit_weights(int fmt) { return (fmt == ILL_Q8_0 || fmt == ILL_IQ2_XXS
 
 struct MvPlan {
   bool one;  // the one-token kernel (activations in registers)
+  bool xs;   // ... rows staged in column chunks, the activations read from shared memory
+  int warps; // warps per CTA
+  int nchunks, chunk_units;
+  uint32_t chunk_bytes;
   int rows_per_tile, lanes, nstages, upt, tps, slots, al;
   uint32_t stage_bytes, x_bytes, xs_off, bs_off, smem;
 };
@@ -474,14 +530,17 @@ static long long tile_target(long long total_bytes, uint32_t cap) {
 
 // Tuning overrides for experiments (ill_set_tuning): lanes a row, rows a warp
 // tile, stages, CTAs per SM.  0 = planned.
-static int g_env_L = 0, g_env_TR = 0, g_env_NST = 0, g_env_CTAS = 0;
+static int g_env_L = 0, g_env_TR = 0, g_env_NST = 0, g_env_CTAS = 0, g_env_XS = 0;
 
-// One-token plan: L lanes a row and UPT units a lane, chosen for the fewest idle
-// lanes; a warp's stage holds (32/L) * RPS rows, about 3.5 KB.
+// One-token plan.  Whole rows: L lanes a row and UPT units a lane in registers,
+// chosen for the fewest idle lanes; a warp's stage holds (32/L) * k rows, about
+// 3 KB.  Rows too long for that (or FORCE_XS): 32 lanes a row, the row staged in
+// column chunks of whole blocks, the activations in shared memory.
 static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu, MvPlan* pl) {
-  const long long row_bytes = (long long)(cols / fmt_block_weights(fmt)) * fmt_block_bytes(fmt);
-  const int units = cols / unit_weights(fmt);
-  const int upt_max = unit_weights(fmt) == 32 ? 5 : 3;
+  const int bb = fmt_block_bytes(fmt), bw = fmt_block_weights(fmt), uw = unit_weights(fmt);
+  const long long row_bytes = (long long)(cols / bw) * bb;
+  const int units = cols / uw;
+  const int upt_max = uw == 32 ? 5 : 3;
   int bestL = 0, bestU = 0;
   double best = -1.0;
   for (int L = 32; L >= 8; L >>= 1) {
@@ -491,30 +550,68 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
     if (eff > best) { best = eff; bestL = L; bestU = upt; }
   }
   if (g_env_L && (units + g_env_L - 1) / g_env_L <= upt_max) { bestL = g_env_L; bestU = (units + g_env_L - 1) / g_env_L; }
-  if (!bestL) return ILL_ERR_UNSUPPORTED;
-  const int nsub = 32 / bestL;
-  // rows per warp tile: about 3 KB a stage (small stages keep more CTAs resident, which is what
-  // hides the copy latency), and small matrices are cut finer so that every warp gets some
-  const long long warps = (long long)sm_count() * 16;
-  long long tr = 3072 / row_bytes;
-  const long long share = (total_rows * nseg + warps - 1) / warps;
-  if (tr > share) tr = share;
-  if (g_env_TR) tr = g_env_TR;
-  tr = tr / nsub * nsub;
-  if (tr < nsub) tr = nsub;
   pl->one = true;
+  pl->xs = false;
+  pl->nchunks = 1;
+  pl->chunk_units = units;
+  pl->chunk_bytes = (uint32_t)row_bytes;
+  long long tr;
+  if (!bestL || g_env_XS) {
+    // blocks per chunk: a multiple that makes the chunk's units a multiple of 32, near 3 KB
+    const int upb = bw / uw;                  // units per block
+    int bpc = 32 / upb > 0 ? 32 / upb : 1;    // 32 units
+    while ((long long)bpc * 2 * bb <= 3400 && bpc * 2 * upb <= 128) bpc *= 2;
+    const int blocks = cols / bw;
+    if (bpc > blocks) bpc = blocks;
+    pl->xs = true;
+    pl->nchunks = (blocks + bpc - 1) / bpc;
+    pl->chunk_units = bpc * upb;
+    pl->chunk_bytes = (uint32_t)bpc * bb;
+    bestL = 32;
+    bestU = (pl->chunk_units + 31) / 32;
+    if (bestU > 4) return ILL_ERR_UNSUPPORTED;
+    tr = 1;
+  } else {
+    const int nsub = 32 / bestL;
+    // rows per warp tile: about 3 KB a stage (small stages keep more CTAs resident, which is what
+    // hides the copy latency), and small matrices are cut finer so that every warp gets some
+    const long long warps = (long long)sm_count() * 16;
+    tr = 3072 / row_bytes;
+    const long long share = (total_rows * nseg + warps - 1) / warps;
+    if (tr > share) tr = share;
+    if (g_env_TR) tr = g_env_TR;
+    tr = tr / nsub * nsub;
+    if (tr < nsub) tr = nsub;
+    if (glu && tr > (long long)MV_MAXRI * nsub) tr = (long long)MV_MAXRI * nsub;
+  }
+  pl->warps = MV_THREADS / 32;
+  {  // few groups: smaller CTAs, so that the warps spread over every SM
+    const long long groups = (total_rows * nseg + tr - 1) / tr;
+    while (pl->warps > 1 && groups < (long long)sm_count() * 2 * pl->warps) pl->warps >>= 1;
+  }
   pl->upt = bestU;
   pl->lanes = bestL;
-  pl->tps = pl->slots = 0;
   pl->rows_per_tile = (int)tr;
-  pl->stage_bytes = align_up((uint32_t)(tr * row_bytes) + 32, 128);
-  // stages: four if two CTAs still fit an SM, else three, else two
-  const uint32_t per_stage = pl->stage_bytes * (glu ? 2 : 1) * (MV_THREADS / 32);
-  pl->nstages = per_stage * 4 <= 110 * 1024 ? 4 : per_stage * 3 <= 110 * 1024 ? 3 : per_stage * 3 <= 200 * 1024 ? 3 : 2;
-  if (g_env_NST) pl->nstages = g_env_NST;
+  pl->stage_bytes = align_up((pl->xs ? pl->chunk_bytes : (uint32_t)(tr * row_bytes)) + 32, 128);
   pl->x_bytes = pl->xs_off = pl->bs_off = 0;
-  pl->smem = pl->stage_bytes * (glu ? 2 : 1) * pl->nstages * (MV_THREADS / 32) + (fmt == ILL_IQ2_XXS ? 3072 : 0) +
-             8 * pl->nstages * (MV_THREADS / 32) + 64;
+  if (pl->xs) {
+    const int nsc = fmt == ILL_Q8_0 ? cols / 32 : cols / 256;
+    switch (fmt) {
+      case ILL_Q8_0: pl->x_bytes = plane_bytes<ILL_Q8_0>(units, nsc); break;
+      case ILL_Q4_K: pl->x_bytes = plane_bytes<ILL_Q4_K>(units, nsc); break;
+      case ILL_Q6_K: pl->x_bytes = plane_bytes<ILL_Q6_K>(units, nsc); break;
+      case ILL_Q2_K: pl->x_bytes = plane_bytes<ILL_Q2_K>(units, nsc); break;
+      default: pl->x_bytes = plane_bytes<ILL_IQ2_XXS>(units, nsc); break;
+    }
+  }
+  // stages: four if two CTAs still fit an SM, else three (two CTAs, else one), else two
+  const uint32_t fixed = (fmt == ILL_IQ2_XXS ? 3072 : 0) + 8 * 8 * pl->warps + pl->x_bytes + 64 + 1024;
+  const uint32_t per_stage = pl->stage_bytes * pl->warps;
+  const uint32_t two = 113 * 1024;  // half an SM's shared memory
+  pl->nstages = per_stage * 4 + fixed <= two ? 4 : per_stage * 3 + fixed <= two ? 3 : per_stage * 3 + fixed <= 200 * 1024 ? 3 : 2;
+  if (g_env_NST) pl->nstages = g_env_NST;
+  pl->smem = pl->stage_bytes * pl->nstages * pl->warps + (fmt == ILL_IQ2_XXS ? 3072 : 0) + 8 * pl->nstages * pl->warps +
+             pl->x_bytes + 64;
   return pl->smem > 220 * 1024 ? ILL_ERR_UNSUPPORTED : ILL_OK;
 }
 
@@ -525,7 +622,12 @@ static int plan_many(int fmt, long long total_rows, int cols, int ntok, int nseg
   if (rpt < 1) rpt = 1;
   if (rpt > total_rows) rpt = total_rows;
   pl->one = false;
-  pl->upt = pl->tps = pl->slots = 0;
+  pl->xs = false;
+  pl->warps = MV_THREADS / 32;
+  pl->upt = 0;
+  pl->nchunks = 1;
+  pl->chunk_units = 0;
+  pl->chunk_bytes = 0;
   pl->al = 1;
   pl->rows_per_tile = (int)rpt;
   pl->stage_bytes = align_up((uint32_t)(rpt * row_bytes) + 32, 128);
@@ -551,18 +653,27 @@ static int launch_k(K k, const MvParams& p, const MvPlan& pl, int gx, int gy, cu
   }
   MvParams pp = p;
   void* args[] = {&pp};
-  return launch_kernel((const void*)k, dim3(gx, gy, 1), dim3(MV_THREADS, 1, 1), pl.smem, args, st);
+  return launch_kernel((const void*)k, dim3(gx, gy, 1), dim3(32 * pl.warps, 1, 1), pl.smem, args, st);
 }
 
 template <int FMT, int MODE, int AL>
 static int launch_one_u(const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
   constexpr int UMAX = (FMT == ILL_Q8_0 || FMT == ILL_IQ2_XXS) ? 5 : 3;
+  if (pl.xs) {
+    switch (pl.upt) {
+      case 1: return launch_k(mvw_kernel<FMT, MODE, 1, AL, true>, p, pl, gx, gy, st);
+      case 2: return launch_k(mvw_kernel<FMT, MODE, 2, AL, true>, p, pl, gx, gy, st);
+      case 3: return launch_k(mvw_kernel<FMT, MODE, 3, AL, true>, p, pl, gx, gy, st);
+      case 4: return launch_k(mvw_kernel<FMT, MODE, 4, AL, true>, p, pl, gx, gy, st);
+    }
+    return ILL_ERR_UNSUPPORTED;
+  }
   switch (pl.upt) {
-    case 1: return launch_k(mvw_kernel<FMT, MODE, 1, AL>, p, pl, gx, gy, st);
-    case 2: return launch_k(mvw_kernel<FMT, MODE, 2, AL>, p, pl, gx, gy, st);
-    case 3: return launch_k(mvw_kernel<FMT, MODE, 3, AL>, p, pl, gx, gy, st);
-    case 4: if constexpr (UMAX >= 4) return launch_k(mvw_kernel<FMT, MODE, 4, AL>, p, pl, gx, gy, st); break;
-    case 5: if constexpr (UMAX >= 5) return launch_k(mvw_kernel<FMT, MODE, 5, AL>, p, pl, gx, gy, st); break;
+    case 1: return launch_k(mvw_kernel<FMT, MODE, 1, AL, false>, p, pl, gx, gy, st);
+    case 2: return launch_k(mvw_kernel<FMT, MODE, 2, AL, false>, p, pl, gx, gy, st);
+    case 3: return launch_k(mvw_kernel<FMT, MODE, 3, AL, false>, p, pl, gx, gy, st);
+    case 4: if constexpr (UMAX >= 4) return launch_k(mvw_kernel<FMT, MODE, 4, AL, false>, p, pl, gx, gy, st); break;
+    case 5: if constexpr (UMAX >= 5) return launch_k(mvw_kernel<FMT, MODE, 5, AL, false>, p, pl, gx, gy, st); break;
   }
   return ILL_ERR_UNSUPPORTED;
 }
@@ -658,8 +769,9 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
   p.acc = acc;
   p.rows_per_tile = pl.rows_per_tile;
   p.lanes_per_row = pl.lanes;
-  p.tps = pl.tps;
-  p.slots = pl.slots;
+  p.nchunks = pl.nchunks;
+  p.chunk_units = pl.chunk_units;
+  p.chunk_bytes = pl.chunk_bytes;
   p.stage_bytes = pl.stage_bytes;
   p.nstages = pl.nstages;
   p.x_bytes = pl.x_bytes;
@@ -675,10 +787,11 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
   p.status = status_ptr();
   // persistent grid: as many CTAs as can be resident, split over the segments
   int per_sm = (int)((227u * 1024u) / (pl.smem + 1024u));
-  per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
+  const int per_sm_cap = pl.one ? 16 / pl.warps * 2 : 6;  // up to 32 warps an SM
+  per_sm = per_sm < 1 ? 1 : (per_sm > per_sm_cap ? per_sm_cap : per_sm);
   if (g_env_CTAS) per_sm = g_env_CTAS;
   int gx = (sm_count() * per_sm + nseg - 1) / nseg;
-  const int work = pl.one ? (tiles + MV_THREADS / 32 - 1) / (MV_THREADS / 32) : tiles;  // a warp a tile, or a CTA a tile
+  const int work = pl.one ? (tiles + pl.warps - 1) / pl.warps : tiles;  // a warp a tile, or a CTA a tile
   if (gx > work) gx = work;
   if (gx < 1) gx = 1;
   return launch_mv(fmt, mode, p, pl, gx, nseg, (cudaStream_t)stream);
@@ -689,6 +802,8 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
 using namespace ill;
 
 extern "C" int ill_set_tuning(int lanes, int tile_rows, int stages, int ctas_per_sm) {
+  g_env_XS = 0;
+  if (lanes == 1) { g_env_XS = 1; lanes = 0; }  // 1: stage rows in column chunks whatever their length
   if (lanes && lanes != 8 && lanes != 16 && lanes != 32) return ILL_ERR_ARG;
   if (tile_rows < 0 || stages < 0 || stages > 8 || ctas_per_sm < 0 || ctas_per_sm > 16) return ILL_ERR_ARG;
   g_env_L = lanes;

@@ -88,7 +88,7 @@ ILL_API int ill_device_status(unsigned int* out, ill_stream stream);
 ILL_API int ill_set_pdl(int on);
 
 /* Overrides the one-token product's launch plan, for tuning experiments: lanes
- * that share a row (8, 16 or 32), rows per warp tile, pipeline stages, CTAs per
+ * that share a row (8, 16 or 32; 1 = stage rows in column chunks), rows per warp tile, pipeline stages, CTAs per
  * SM.  0 leaves a value to the planner; (0,0,0,0) restores the defaults.  Not
  * for production use.  (No counterpart in the reference, whose launch shapes
  * are fixed at each Lisp call site.) */
