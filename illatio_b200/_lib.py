@@ -31,6 +31,14 @@ SIGNATURES = {
     "ill_mv": (_I, [_I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _S]),
     "ill_mv_3": (_I, [_I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _S]),
     "ill_mv_glu": (_I, [_I, _P, _P, _I, _I, _P, _P, _P, _P, _S]),
+    "ill_moe_mv": (_I, [_I, _I, _I, _L, _P, _I, _P, _P, _P, _I, _P, _L, _S]),
+    "ill_moe_glu": (_I, [_I, _I, _I, _L, _L, _P, _I, _P, _P, _P, _I, _F, _P, _P, _L, _S]),
+    "ill_swiglu_w": (_I, [_L, _I, _F, _P, _P, _P, _P, _S]),
+    "ill_moe_sum": (_I, [_I, _I, _L, _P, _P, _P, _P, _S]),
+    "ill_moe_route": (_I, [_I, _I, _I, _F, _L, _P, _P, _P, _P, _S]),
+    "ill_moe_group_scratch_bytes": (_L, [_L, _I]),
+    "ill_moe_group": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _S]),
+    "ill_gather_rows": (_I, [_L, _L, _P, _P, _P, _S]),
 }
 
 

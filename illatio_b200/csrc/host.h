@@ -1,6 +1,7 @@
 // host.h -- host-side helpers shared by the translation units of the library.
 #pragma once
 #include <cuda_runtime.h>
+#include <stdint.h>
 
 namespace ill {
 
@@ -23,9 +24,8 @@ enum { MODE_PLAIN = 0, MODE_GLU = 1, MODE_MOE_GLU = 2 };
 // The matvec family's common entry (mv.cu): NMAT matrices of one format sharing
 // the activations; NSEG segments when PTRS (a device table of base addresses)
 // is given.  See ill_mv / ill_moe_mv for the argument meaning.
-int mv_common(int fmt, int mode, int nmat, const unsigned long long* w, const int* rows, int cols,
-              unsigned long long xq, unsigned long long xs, unsigned long long xsum, const unsigned long long* y,
-              const unsigned long long* bias, int acc, int n, unsigned long long ptrs, int nseg, long long add,
-              long long up_add, int x_seg, long long y_seg, unsigned long long seg_w, float clamp, void* stream);
+int mv_common(int fmt, int mode, int nmat, const uint64_t* w, const int* rows, int cols, uint64_t xq, uint64_t xs,
+              uint64_t xsum, const uint64_t* y, const uint64_t* bias, int acc, int n, uint64_t ptrs, int nseg,
+              long long add, long long up_add, int x_seg, long long y_seg, uint64_t seg_w, float clamp, void* stream);
 
 }  // namespace ill

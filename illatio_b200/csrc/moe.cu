@@ -1,0 +1,343 @@
+// moe.cu -- the routed experts' small kernels: routing, grouping rows by expert,
+// the gated middle, the sums in slot order; and the per-expert products of a
+// decoded token, which are the matvec kernels (mv.cu) run over a table of expert
+// addresses.
+//
+// Replaces d4_mv_iq2_xxs / d4_mv_q2_k / d4_swiglu_w / d4_moe_sum
+// (src/cuda/ds4f.cu:645,769,837,902) and d4_route / d4_group_* / d4_gather_rows /
+// d4_moe_sum_rows (src/cuda/ds4f_chunk.cu:393-508) of the reference.
+#include "formats.cuh"
+#include "host.h"
+
+namespace ill {
+
+// D4-SIGMOID (src/ds4f.lisp:248-250), each step rounded as written.
+__device__ __forceinline__ float d4_sigmoid(float x) {
+  if (x >= 0.0f) return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x)));
+  const float e = expf(x);
+  return __fdiv_rn(e, __fadd_rn(1.0f, e));
+}
+
+// MID[r*ff + j] = silu(min(G, c)) * clamp(U, +-c) * W[r]  (src/ds4f.lisp:1016-1019)
+__global__ void __launch_bounds__(256) swiglu_w_kernel(long long n, int ff, float clamp, const float* __restrict__ g,
+                                                       const float* __restrict__ u, const float* __restrict__ w,
+                                                       float* __restrict__ mid) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float gv = g[i], uv = u[i];
+  if (clamp > 1e-6f) { gv = fminf(gv, clamp); uv = fmaxf(-clamp, fminf(uv, clamp)); }
+  const float wv = w ? w[i / ff] : 1.0f;
+  mid[i] = __fmul_rn(__fmul_rn(__fmul_rn(gv, d4_sigmoid(gv)), uv), wv);
+}
+
+// MOE[t*d + r] = sum over the token's NU slots, in slot order, of DOWN[row(t, s)*d + r], plus SHARED
+// (src/ds4f.lisp:1031-1036, 1226-1231).  MAP gives row(t, s) (null: t*nu + s).
+__global__ void __launch_bounds__(256) moe_sum_kernel(int d, int nu, long long ntok, const float* __restrict__ down,
+                                                      const unsigned* __restrict__ map,
+                                                      const float* __restrict__ shared_, float* __restrict__ moe) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= ntok * d) return;
+  const long long t = gid / d;
+  const int r = (int)(gid - t * d);
+  float acc = 0.0f;
+  for (int s = 0; s < nu; ++s) {
+    const long long row = map ? (long long)map[t * nu + s] : t * nu + s;
+    acc = __fadd_rn(acc, down[row * d + r]);
+  }
+  moe[gid] = shared_ ? __fadd_rn(acc, shared_[gid]) : acc;
+}
+
+// ---- routing -----------------------------------------------------------------------
+// A warp a token.  MODE 0: p = sqrt(softplus(logit)) (D4-ROUTE, src/ds4f.lisp:950-978);
+// MODE 2: p = sigmoid(logit) (G53-ROUTE, src/glm53.lisp:360-379).  The NU largest of
+// p + bias, the earlier expert first among equals; weights p / max(sum p, 6.103515625e-5) * scale.
+constexpr int ROUTE_MAX_PER_LANE = 16;  // up to 512 experts
+
+__global__ void __launch_bounds__(128) route_kernel(int ne, int nu, int mode, float scale, long long ntok,
+                                                    const float* __restrict__ logits, const float* __restrict__ bias,
+                                                    unsigned* __restrict__ sel, float* __restrict__ wout) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= ntok) return;
+  float p[ROUTE_MAX_PER_LANE], sc[ROUTE_MAX_PER_LANE];
+#pragma unroll
+  for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
+    const int e = j * 32 + lane;
+    p[j] = 0.0f;
+    sc[j] = -INFINITY;
+    if (e < ne) {
+      const float l = logits[t * ne + e];
+      float pv;
+      if (mode == 2) pv = d4_sigmoid(l);
+      else {
+        const float sp = l > 20.0f ? l : (l < -20.0f ? expf(l) : logf(__fadd_rn(1.0f, expf(l))));
+        pv = sqrtf(sp);
+      }
+      p[j] = pv;
+      sc[j] = bias ? __fadd_rn(pv, bias[e]) : pv;
+    }
+  }
+  float sum = 0.0f, mine = 0.0f;
+  unsigned mysel = 0;
+  for (int k = 0; k < nu; ++k) {
+    // this lane's best (lowest index among equals: j ascending, strict >)
+    float bv = -INFINITY;
+    int bj = 0;
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j)
+      if (sc[j] > bv) { bv = sc[j]; bj = j; }
+    int be = bj * 32 + lane;
+    float v = bv;
+    int e = be;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, e, o);
+      if (ov > v || (ov == v && oe < e)) { v = ov; e = oe; }
+    }
+    // the winner's lane takes it out of the running and reports its probability
+    float pw = 0.0f;
+    if ((e & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j)
+        if (j == (e >> 5)) { pw = p[j]; sc[j] = -INFINITY; }
+    }
+    pw = __shfl_sync(0xffffffffu, pw, e & 31);
+    sum = __fadd_rn(sum, pw);
+    if (lane == k) { mine = pw; mysel = (unsigned)e; }
+  }
+  if (sum < 6.103515625e-5f) sum = 6.103515625e-5f;
+  if (lane < nu) {
+    sel[t * nu + lane] = mysel;
+    wout[t * nu + lane] = __fmul_rn(__fdiv_rn(mine, sum), scale);
+  }
+}
+
+// ---- grouping (token, slot) rows by expert: a stable counting sort -------------------
+// Rows are taken in blocks of GROUP_BLOCK; within a block a row's rank among its
+// expert's rows follows row order (so an expert's rows stay in token order and
+// the result does not depend on scheduling).
+constexpr int GROUP_BLOCK = 1024;
+
+// pass 1: per block, each expert's count; each row's rank inside its block
+__global__ void __launch_bounds__(GROUP_BLOCK) group_count_kernel(long long rows, int ne, const unsigned* __restrict__ sel,
+                                                                  unsigned* __restrict__ block_counts,
+                                                                  unsigned* __restrict__ rank) {
+  extern __shared__ unsigned gsm[];  // ne counters, then 32 * ne per-warp counters
+  pdl_launch_dependents();
+  pdl_wait();
+  unsigned* warp_counts = gsm;  // [32][ne]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < 32 * ne; i += GROUP_BLOCK) warp_counts[i] = 0;
+  __syncthreads();
+  const long long row = (long long)blockIdx.x * GROUP_BLOCK + tid;
+  const bool valid = row < rows;
+  const unsigned e = valid ? sel[row] : 0xffffffffu;
+  // rank within the warp: lanes below with the same expert
+  const unsigned same = __match_any_sync(0xffffffffu, e);
+  const unsigned below = same & ((1u << lane) - 1u);
+  const unsigned r_in_warp = __popc(below);
+  if (valid && r_in_warp == 0) warp_counts[warp * ne + e] = __popc(same);  // one writer per (warp, expert)
+  __syncthreads();
+  // exclusive scan over the warps, per expert
+  for (int x = tid; x < ne; x += GROUP_BLOCK) {
+    unsigned run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const unsigned c = warp_counts[w * ne + x];
+      warp_counts[w * ne + x] = run;
+      run += c;
+    }
+    block_counts[(long long)blockIdx.x * ne + x] = run;
+  }
+  __syncthreads();
+  if (valid) rank[row] = warp_counts[warp * ne + e] + r_in_warp;
+}
+
+// pass 2 (one CTA): blocks scanned per expert, experts scanned -> COUNTS, BASES, block bases
+__global__ void __launch_bounds__(512) group_scan_kernel(int nblocks, int ne, unsigned* __restrict__ block_counts,
+                                                         unsigned* __restrict__ counts, unsigned* __restrict__ bases) {
+  __shared__ unsigned tot[512];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = threadIdx.x;
+  unsigned run = 0;
+  if (e < ne)
+    for (int b = 0; b < nblocks; ++b) {
+      const unsigned c = block_counts[(long long)b * ne + e];
+      block_counts[(long long)b * ne + e] = run;  // rows of expert e in earlier blocks
+      run += c;
+    }
+  tot[e] = e < ne ? run : 0;
+  __syncthreads();
+  if (e == 0) {
+    unsigned acc = 0;
+    for (int i = 0; i < ne; ++i) { const unsigned c = tot[i]; tot[i] = acc; acc += c; }
+  }
+  __syncthreads();
+  if (e < ne) { counts[e] = run; bases[e] = tot[e]; }
+}
+
+// pass 3: each row to its place; RMAP[place] = token, SMAP[row] = place, WROW[place] = weight
+__global__ void __launch_bounds__(256) group_scatter_kernel(long long rows, int ne, int nu, const unsigned* __restrict__ sel,
+                                                            const unsigned* __restrict__ rank,
+                                                            const unsigned* __restrict__ block_counts,
+                                                            const unsigned* __restrict__ bases, const float* __restrict__ w,
+                                                            unsigned* __restrict__ rmap, unsigned* __restrict__ smap,
+                                                            float* __restrict__ wrow) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const unsigned e = sel[row];
+  const unsigned place = bases[e] + block_counts[(row / GROUP_BLOCK) * ne + e] + rank[row];
+  rmap[place] = (unsigned)(row / nu);
+  smap[row] = place;
+  if (wrow) wrow[place] = w[row];
+}
+
+// X[r] = SRC[MAP[r]] for rows of ROW_BYTES bytes (a multiple of 16): gathers quantized activations
+// or floats per expert.
+__global__ void __launch_bounds__(256) gather_rows_kernel(long long rows, int row_vec, const uint4* __restrict__ src,
+                                                          const unsigned* __restrict__ map, uint4* __restrict__ dst) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= rows * row_vec) return;
+  const long long r = gid / row_vec;
+  const int j = (int)(gid - r * row_vec);
+  dst[gid] = src[(long long)map[r] * row_vec + j];
+}
+
+}  // namespace ill
+
+using namespace ill;
+
+static int check_ptr(ill_dptr p, unsigned align) { return p && !(p & (align - 1)); }
+
+extern "C" int ill_moe_mv(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, int nz, ill_dptr xq, ill_dptr xs,
+                          ill_dptr xsum, int x_per_expert, ill_dptr y, int64_t y_stride, ill_stream stream) {
+  if (!ptrs || nz < 1 || (ptrs & 7) || (x_per_expert != 0 && x_per_expert != 1)) return ILL_ERR_ARG;
+  const uint64_t ws[1] = {0}, ys[1] = {y};
+  const int rs[1] = {nrows};
+  return mv_common(fmt, MODE_PLAIN, 1, ws, rs, ncols, xq, xs, xsum, ys, nullptr, 0, 1, ptrs, nz, add, 0, x_per_expert,
+                   y_stride, 0, 0.0f, stream);
+}
+
+extern "C" int ill_moe_glu(int fmt, int ncols, int nrows, int64_t gate_add, int64_t up_add, ill_dptr ptrs, int nz,
+                           ill_dptr xq, ill_dptr xs, ill_dptr xsum, int x_per_expert, float clamp, ill_dptr weights,
+                           ill_dptr mid, int64_t mid_stride, ill_stream stream) {
+  if (!ptrs || nz < 1 || (ptrs & 7) || !weights || (weights & 3) || (x_per_expert != 0 && x_per_expert != 1))
+    return ILL_ERR_ARG;
+  const uint64_t ws[2] = {0, 0}, ys[2] = {mid, mid};
+  const int rs[2] = {nrows, nrows};
+  return mv_common(fmt, MODE_MOE_GLU, 2, ws, rs, ncols, xq, xs, xsum, ys, nullptr, 0, 1, ptrs, nz, gate_add,
+                   up_add - gate_add, x_per_expert, mid_stride, weights, clamp, stream);
+}
+
+extern "C" int ill_swiglu_w(int64_t n, int ff, float clamp, ill_dptr g, ill_dptr u, ill_dptr w, ill_dptr mid,
+                            ill_stream stream) {
+  if (n < 0 || ff <= 0 || !check_ptr(g, 4) || !check_ptr(u, 4) || !check_ptr(mid, 4) || (w & 3)) return ILL_ERR_ARG;
+  if (n == 0) return ILL_OK;
+  long long nn = n;
+  const float *gp = (const float*)(uintptr_t)g, *up = (const float*)(uintptr_t)u, *wp = (const float*)(uintptr_t)w;
+  float* mp = (float*)(uintptr_t)mid;
+  void* args[] = {&nn, &ff, &clamp, &gp, &up, &wp, &mp};
+  return launch_kernel((const void*)swiglu_w_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, args,
+                       (cudaStream_t)stream);
+}
+
+extern "C" int ill_moe_sum(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr shared_, ill_dptr moe,
+                           ill_stream stream) {
+  if (d <= 0 || nu <= 0 || ntok < 0 || !check_ptr(down, 4) || !check_ptr(moe, 4) || (map & 3) || (shared_ & 3))
+    return ILL_ERR_ARG;
+  if (ntok == 0) return ILL_OK;
+  long long nt = ntok;
+  const float *dp = (const float*)(uintptr_t)down, *sp = (const float*)(uintptr_t)shared_;
+  const unsigned* mp = (const unsigned*)(uintptr_t)map;
+  float* op = (float*)(uintptr_t)moe;
+  void* args[] = {&d, &nu, &nt, &dp, &mp, &sp, &op};
+  return launch_kernel((const void*)moe_sum_kernel, dim3((unsigned)((ntok * d + 255) / 256)), dim3(256), 0, args,
+                       (cudaStream_t)stream);
+}
+
+extern "C" int ill_moe_route(int ne, int nu, int mode, float scale, int64_t ntok, ill_dptr logits, ill_dptr bias,
+                             ill_dptr sel, ill_dptr weights, ill_stream stream) {
+  if (ne <= 0 || ne > 32 * ROUTE_MAX_PER_LANE || nu <= 0 || nu > 32 || nu > ne || (mode != 0 && mode != 2) || ntok < 0)
+    return ILL_ERR_ARG;
+  if (!check_ptr(logits, 4) || !check_ptr(sel, 4) || !check_ptr(weights, 4) || (bias & 3)) return ILL_ERR_ARG;
+  if (ntok == 0) return ILL_OK;
+  long long nt = ntok;
+  const float *lp = (const float*)(uintptr_t)logits, *bp = (const float*)(uintptr_t)bias;
+  unsigned* sp = (unsigned*)(uintptr_t)sel;
+  float* wp = (float*)(uintptr_t)weights;
+  void* args[] = {&ne, &nu, &mode, &scale, &nt, &lp, &bp, &sp, &wp};
+  return launch_kernel((const void*)route_kernel, dim3((unsigned)((ntok + 3) / 4)), dim3(128), 0, args,
+                       (cudaStream_t)stream);
+}
+
+extern "C" int64_t ill_moe_group_scratch_bytes(int64_t rows, int ne) {
+  if (rows < 0 || ne <= 0) return 0;
+  const int64_t nblocks = (rows + GROUP_BLOCK - 1) / GROUP_BLOCK;
+  return 4 * (rows + nblocks * ne);  // rank per row, counts per (block, expert)
+}
+
+extern "C" int ill_moe_group(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w, ill_dptr scratch, ill_dptr counts,
+                             ill_dptr bases, ill_dptr rmap, ill_dptr smap, ill_dptr wrow, ill_stream stream) {
+  if (rows < 0 || ne <= 0 || ne > 512 || nu <= 0) return ILL_ERR_ARG;
+  if (!check_ptr(sel, 4) || !check_ptr(scratch, 4) || !check_ptr(counts, 4) || !check_ptr(bases, 4) ||
+      !check_ptr(rmap, 4) || !check_ptr(smap, 4) || (wrow & 3) || (wrow && !check_ptr(w, 4)))
+    return ILL_ERR_ARG;
+  long long nrows = rows;
+  int nblocks = (int)((rows + GROUP_BLOCK - 1) / GROUP_BLOCK);
+  if (nblocks < 1) nblocks = 1;
+  unsigned* rank = (unsigned*)(uintptr_t)scratch;
+  unsigned* block_counts = rank + rows;
+  const unsigned* selp = (const unsigned*)(uintptr_t)sel;
+  unsigned *cp = (unsigned*)(uintptr_t)counts, *bp = (unsigned*)(uintptr_t)bases, *rp = (unsigned*)(uintptr_t)rmap,
+           *sp = (unsigned*)(uintptr_t)smap;
+  const float* wp = (const float*)(uintptr_t)w;
+  float* wr = (float*)(uintptr_t)wrow;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)32 * ne * 4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(group_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  {
+    void* args[] = {&nrows, &ne, &selp, &block_counts, &rank};
+    int rc = launch_kernel((const void*)group_count_kernel, dim3(nblocks), dim3(GROUP_BLOCK), smem, args, st);
+    if (rc) return rc;
+  }
+  {
+    void* args[] = {&nblocks, &ne, &block_counts, &cp, &bp};
+    int rc = launch_kernel((const void*)group_scan_kernel, dim3(1), dim3(512), 0, args, st);
+    if (rc) return rc;
+  }
+  if (rows == 0) return ILL_OK;
+  const unsigned* rk = rank;
+  const unsigned* bc = block_counts;
+  const unsigned* bs = bp;
+  void* args[] = {&nrows, &ne, &nu, &selp, &rk, &bc, &bs, &wp, &rp, &sp, &wr};
+  return launch_kernel((const void*)group_scatter_kernel, dim3((unsigned)((rows + 255) / 256)), dim3(256), 0, args, st);
+}
+
+extern "C" int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,
+                               ill_stream stream) {
+  if (rows < 0 || row_bytes <= 0 || (row_bytes & 15) || !check_ptr(src, 16) || !check_ptr(dst, 16) || !check_ptr(map, 4))
+    return ILL_ERR_ARG;
+  if (rows == 0) return ILL_OK;
+  long long nrows = rows;
+  int row_vec = (int)(row_bytes / 16);
+  const uint4* sp = (const uint4*)(uintptr_t)src;
+  const unsigned* mp = (const unsigned*)(uintptr_t)map;
+  uint4* dp = (uint4*)(uintptr_t)dst;
+  void* args[] = {&nrows, &row_vec, &sp, &mp, &dp};
+  return launch_kernel((const void*)gather_rows_kernel, dim3((unsigned)((rows * row_vec + 255) / 256)), dim3(256), 0,
+                       args, (cudaStream_t)stream);
+}

@@ -150,6 +150,70 @@ ILL_API int ill_mv_3(int fmt, ill_dptr w0, ill_dptr w1, ill_dptr w2, int rows0, 
 ILL_API int ill_mv_glu(int fmt, ill_dptr wg, ill_dptr wu, int rows, int cols, ill_dptr xq, ill_dptr xs,
                        ill_dptr xsum, ill_dptr y, ill_stream stream);
 
+/* ---- routed experts: one decoded token ------------------------------------------ */
+
+/* Y[z*y_stride + r] = W_z[r] . X_z for each expert z < NZ: W_z's NROWS rows of
+ * NCOLS weights start at PTRS[z] + ADD (PTRS: a device table of 64-bit device
+ * addresses, the experts' slots; 16-byte aligned addresses and ADD); X_z is
+ * token z of XQ/XS/XSUM when X_PER_EXPERT is 1, token 0 for every expert when
+ * it is 0.  Replaces d4_mv_iq2_xxs / d4_mv_q2_k (src/cuda/ds4f.cu:769,837)
+ * behind DK-FFN-TAIL (src/cuda-ds4f.lisp:908-956); activations are Q8_K, as
+ * the CPU path's are (src/ds4f.lisp:1001,1021). */
+ILL_API int ill_moe_mv(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, int nz, ill_dptr xq, ill_dptr xs,
+                       ill_dptr xsum, int x_per_expert, ill_dptr y, int64_t y_stride, ill_stream stream);
+
+/* MID[z*mid_stride + r] = silu(min(g, c)) * clamp(u, +-c) * WEIGHTS[z] with g =
+ * G_z[r] . X, u = U_z[r] . X, G_z at PTRS[z] + GATE_ADD, U_z at PTRS[z] + UP_ADD
+ * (CLAMP <= 1e-6: no clamping); FMT is ILL_IQ2_XXS or ILL_Q2_K.  One launch for
+ * what the reference does with two d4_mv_iq2_xxs grids and d4_swiglu_w
+ * (src/cuda-ds4f.lisp:937-939); the arithmetic is D4-ROUTED!'s
+ * (src/ds4f.lisp:1012-1019). */
+ILL_API int ill_moe_glu(int fmt, int ncols, int nrows, int64_t gate_add, int64_t up_add, ill_dptr ptrs, int nz,
+                        ill_dptr xq, ill_dptr xs, ill_dptr xsum, int x_per_expert, float clamp, ill_dptr weights,
+                        ill_dptr mid, int64_t mid_stride, ill_stream stream);
+
+/* MID[i] = silu(min(G[i], c)) * clamp(U[i], +-c) * W[i / ff] for i < N (W = 0: no
+ * weights).  Replaces d4_swiglu_w (src/cuda/ds4f.cu:645); quantize the result
+ * with ill_quant_q8_0 / ill_quant_q8_k. */
+ILL_API int ill_swiglu_w(int64_t n, int ff, float clamp, ill_dptr g, ill_dptr u, ill_dptr w, ill_dptr mid,
+                         ill_stream stream);
+
+/* MOE[t*d + r] = sum over slots s < NU, in slot order, of DOWN[row(t,s)*d + r]
+ * (+ SHARED[t*d + r] unless 0); row(t,s) = MAP[t*nu + s], or t*nu + s when MAP
+ * is 0.  Replaces d4_moe_sum (src/cuda/ds4f.cu:902) and d4_moe_sum_rows
+ * (src/cuda/ds4f_chunk.cu:402). */
+ILL_API int ill_moe_sum(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr shared_, ill_dptr moe,
+                        ill_stream stream);
+
+/* ---- routed experts: a chunk of tokens -------------------------------------------- */
+
+/* Per token: SEL[t*nu ..] the NU experts with the largest p + BIAS (BIAS may be
+ * 0), the earlier expert first among equals, and WEIGHTS[t*nu ..] = p / max(sum
+ * of the chosen p, 6.103515625e-5) * SCALE; p = sqrt(softplus(logit)) for MODE 0
+ * (D4-ROUTE, src/ds4f.lisp:950-978), sigmoid(logit) for MODE 2 (G53-ROUTE,
+ * src/glm53.lisp:360-379).  NE <= 512, NU <= 32.  Replaces d4_route
+ * (src/cuda/ds4f_chunk.cu:420). */
+ILL_API int ill_moe_route(int ne, int nu, int mode, float scale, int64_t ntok, ill_dptr logits, ill_dptr bias,
+                          ill_dptr sel, ill_dptr weights, ill_stream stream);
+
+/* Bytes of scratch ill_moe_group needs for ROWS (token, slot) rows and NE experts. */
+ILL_API int64_t ill_moe_group_scratch_bytes(int64_t rows, int ne);
+
+/* Groups the ROWS = tokens*NU (token, slot) rows by expert, an expert's rows in
+ * token order (a stable counting sort: the result does not depend on
+ * scheduling): COUNTS[e], BASES[e] (uint32 per expert); RMAP[place] = the row's
+ * token; SMAP[t*nu + s] = the row's place; WROW[place] = W[t*nu + s] (WROW may
+ * be 0).  SCRATCH: ill_moe_group_scratch_bytes.  Replaces d4_group_zero / count
+ * / scan / scatter (src/cuda/ds4f_chunk.cu:476-508), whose order inside an
+ * expert follows an atomic counter. */
+ILL_API int ill_moe_group(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w, ill_dptr scratch, ill_dptr counts,
+                          ill_dptr bases, ill_dptr rmap, ill_dptr smap, ill_dptr wrow, ill_stream stream);
+
+/* DST row r = SRC row MAP[r], rows of ROW_BYTES bytes (a multiple of 16; both
+ * 16-byte aligned).  Replaces d4_gather_rows (src/cuda/ds4f_chunk.cu:393). */
+ILL_API int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,
+                            ill_stream stream);
+
 #ifdef __cplusplus
 }
 #endif
