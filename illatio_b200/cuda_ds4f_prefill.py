@@ -1,0 +1,91 @@
+"""Host side of the mixture-of-experts prefill path: DK-FFN-ROUTED-CHUNK of the
+reference's src/cuda-ds4f-prefill.lisp (:315-356), mirrored over the C ABI.
+
+The chunk's routing, grouping and products all run on the device with no host
+synchronisation, as in the reference; the products run on tcgen05 tensor cores
+over the Q8_K-quantized activations (so the results follow the reference's CPU
+prefill, src/ds4f.lisp:1168-1239, within fp16 operand rounding).
+"""
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from . import cuda_dense as D
+from .cuda_ds4f import ExpertPool, swiglu_w
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+@dataclass
+class ChunkScratch:
+    """The buffers of a chunk (the reference's PB scratch, src/cuda-ds4f-prefill.lisp:35-47)."""
+    n: int
+    rows: int
+    sel: torch.Tensor
+    w: torch.Tensor
+    counts: torch.Tensor
+    bases: torch.Tensor
+    rmap: torch.Tensor
+    smap: torch.Tensor
+    wrow: torch.Tensor
+    group: torch.Tensor
+    xq: D.QAct
+    xh: torch.Tensor
+    g: torch.Tensor
+    u: torch.Tensor
+    mid: torch.Tensor
+    midq: D.QAct
+    mh: torch.Tensor
+    down: torch.Tensor
+    moe: torch.Tensor
+
+
+def make_chunk_scratch(pool, n, nu, device="cuda"):
+    d, ff, ne = pool.d, pool.ff, pool.n_expert
+    rows = n * nu
+    i32 = dict(dtype=torch.int32, device=device)
+    f32 = dict(dtype=torch.float32, device=device)
+    return ChunkScratch(
+        n, rows, torch.empty(n, nu, **i32), torch.empty(n, nu, **f32), torch.empty(ne, **i32), torch.empty(ne, **i32),
+        torch.empty(rows, **i32), torch.empty(rows, **i32), torch.empty(rows, **f32),
+        torch.empty(_lib.lib().ill_moe_group_scratch_bytes(rows, ne), dtype=torch.uint8, device=device),
+        D.make_qact(n * d, "q8k", device=device), torch.empty(rows, d, dtype=torch.float16, device=device),
+        torch.empty(rows, ff, **f32), torch.empty(rows, ff, **f32), torch.empty(rows, ff, **f32),
+        D.make_qact(rows * ff, "q8k", device=device), torch.empty(rows, ff, dtype=torch.float16, device=device),
+        torch.empty(rows, d, **f32), torch.empty(n, d, **f32))
+
+
+def mm_id(pool, fmt, ncols, nrows, add, ptrs, sc, xh, y):
+    """d4_mm_id_<fmt> (src/cuda-ds4f-prefill.lisp:345-347)."""
+    _lib.call("ill_moe_mm_id", fmt, ncols, nrows, add, _ptr(ptrs), _ptr(sc.counts), _ptr(sc.bases), pool.n_expert,
+              sc.rows, _ptr(xh), _ptr(y), nrows, _stream())
+
+
+def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, scale=1.0, shared=None):
+    """DK-FFN-ROUTED-CHUNK (src/cuda-ds4f-prefill.lisp:315-356): the chunk's N
+    tokens (NORMS [n, d] floats, LOGITS [n, ne] router logits) through their
+    routed experts; returns MOE [n, d] (plus SHARED [n, d] when given)."""
+    n, d = norms.shape
+    ff, ne = pool.ff, pool.n_expert
+    st = _stream()
+    _lib.call("ill_moe_route", ne, nu, mode, float(scale), n, _ptr(logits), _ptr(bias), _ptr(sc.sel), _ptr(sc.w), st)
+    _lib.call("ill_moe_group", sc.rows, ne, nu, _ptr(sc.sel), _ptr(sc.w), _ptr(sc.group), _ptr(sc.counts),
+              _ptr(sc.bases), _ptr(sc.rmap), _ptr(sc.smap), _ptr(sc.wrow), st)
+    D.quant_q8(norms, sc.xq)                                       # each token's Q8_K, once
+    _lib.call("ill_act_f16", sc.rows, d, _ptr(sc.xq.xq), _ptr(sc.xq.xs), _ptr(sc.rmap), _ptr(sc.xh), st)
+    ptrs = pool.ptrs_all                                           # every expert is resident
+    mm_id(pool, pool.gate_fmt, d, ff, 0, ptrs, sc, sc.xh, sc.g)
+    mm_id(pool, pool.gate_fmt, d, ff, pool.gate_bytes, ptrs, sc, sc.xh, sc.u)
+    swiglu_w(sc.g, sc.u, sc.wrow, sc.mid, ff, clamp)
+    D.quant_q8(sc.mid, sc.midq)                                    # per (token, slot) row, as the CPU path does
+    _lib.call("ill_act_f16", sc.rows, ff, _ptr(sc.midq.xq), _ptr(sc.midq.xs), 0, _ptr(sc.mh), st)
+    mm_id(pool, pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptrs, sc, sc.mh, sc.down)
+    _lib.call("ill_moe_sum", d, nu, n, _ptr(sc.down), _ptr(sc.smap), _ptr(shared), _ptr(sc.moe), st)
+    return sc.moe

@@ -214,6 +214,27 @@ ILL_API int ill_moe_group(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w
 ILL_API int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,
                             ill_stream stream);
 
+/* XH[place*cols + k] = fp16(XQ[t*cols + k] * XD[t*(cols/256) + k/256]), t =
+ * MAP[place] (MAP = 0: t = place): the Q8_K activations, dequantized to the
+ * very values the reference's CPU kernels multiply, gathered into expert order
+ * and rounded once to fp16 for the tensor cores.  (The reference's d4_mm_id
+ * rounds the unquantized floats to fp16 instead, src/cuda/ds4f_mm.cu:1-20,
+ * which is why its prefill drifts from its CPU path.)  XQ, XH 16-byte aligned. */
+ILL_API int ill_act_f16(int64_t rows, int cols, ill_dptr xq, ill_dptr xd, ill_dptr map, ill_dptr xh,
+                        ill_stream stream);
+
+/* The routed experts' product for a chunk: for each expert e < NE and each row
+ * `place` in [BASES[e], BASES[e] + COUNTS[e]): Y[place*y_stride + n] = W_e[n] .
+ * XH[place], n < NROWS, W_e the FMT (ILL_IQ2_XXS or ILL_Q2_K) matrix at PTRS[e]
+ * + ADD.  COUNTS / BASES are read on the device (no host synchronisation);
+ * TOTAL_ROWS is the number of rows of XH and Y.  tcgen05 MMA (fp16 operands,
+ * fp32 accumulators in tensor memory), 128 x 128 tiles, the weights
+ * dequantized tile by tile into shared memory.  Replaces d4_mm_id_iq2_xxs /
+ * d4_mm_id_q2_k (src/cuda/ds4f_mm.cu:229-257) behind DK-FFN-ROUTED-CHUNK
+ * (src/cuda-ds4f-prefill.lisp:345-351). */
+ILL_API int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases,
+                          int ne, int64_t total_rows, ill_dptr xh, ill_dptr y, int64_t y_stride, ill_stream stream);
+
 #ifdef __cplusplus
 }
 #endif
