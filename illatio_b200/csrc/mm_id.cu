@@ -29,10 +29,9 @@
 
 namespace ill {
 
-constexpr int MM_BM = 128, MM_BN = 128, MM_BK = 64, MM_STAGES = 3;  // 3 stages: two CTAs fit an SM
-constexpr int MM_THREADS = 192;
+constexpr int MM_BM = 128, MM_BN = 128, MM_BK = 64, MM_STAGES = 6;
+constexpr int MM_THREADS = 320;                        // TMA warp, MMA warp, 8 dequantize / drain warps
 constexpr uint32_t MM_TILE_BYTES = MM_BM * MM_BK * 2;  // 16 KB, A or B
-constexpr uint32_t MM_TMEM_COLS = 128;
 
 struct MmParams {
   int ncols, nrows;            // K and N of every expert matrix
@@ -41,10 +40,12 @@ struct MmParams {
   const unsigned long long* ptrs;
   const unsigned* counts;
   const unsigned* bases;
+  const float* xd;             // the activations' block scales, [token][K/256]
+  const unsigned* map;         // token of each row of X (null: the row itself)
+  long long total_rows;
   float* y;
   long long y_stride;          // floats between rows of Y
   int ne;
-  int max_mtiles;
   unsigned int* status;
 };
 
@@ -100,19 +101,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
-  const __half2 h = __floats2half2_rn(a, b);
-  return *(const uint32_t*)&h;
-}
-
-// ---- dequantization of 64 weights of one row into the swizzled B tile ----------------
-// ROW is the thread's weight row (0..127) in the tile; the 64 weights are 8 chunks of 8
-// halves; chunk c goes to 16-byte slot c ^ (row % 8) of the row's 128 bytes.
+// ---- the weights' integer parts into the swizzled B tile ---------------------------------
+// A thread owns half of a weight row's 64-wide K step: 32 weights = 4 chunks of 8 halves;
+// chunk c of the row goes to 16-byte slot c ^ (row % 8) of the row's 128 bytes.
 __device__ __forceinline__ void store_chunk(u8* tile, int row, int c, uint4 v) {
   *(uint4*)(tile + (row >> 3) * 1024 + (row & 7) * 128 + ((c ^ (row & 7)) << 4)) = v;
 }
 
-// words [first, first+N) of the block at P (any 2-byte alignment), from global memory
+// N words at P (any alignment), from global memory
 template <int N>
 __device__ __forceinline__ void ldg_words(const u8* p, uint32_t (&out)[N]) {
   const uint32_t mis = (uint32_t)(uintptr_t)p & 3u;
@@ -127,70 +123,85 @@ __device__ __forceinline__ void ldg_words(const u8* p, uint32_t (&out)[N]) {
   }
 }
 
-// IQ2_XXS: K step KS (0..3) of the block at BLK: sub-blocks 2*ks, 2*ks+1.  Values as
-// IQ2XXS-ROW-FLOATS! computes them (src/iquant.lisp:161-175), then rounded to fp16.
-__device__ __forceinline__ void dequant64_iq2xxs(const u8* blk, int ks, u8* tile, int row, const uint2* grid,
-                                                 const u8* signs) {
-  uint32_t v[4];
-  ldg_words<4>(blk + 2 + 16 * ks, v);
-  const float d = h2f((uint32_t)__ldg((const u16*)blk));
+// two unsigned bytes (byte positions B0, B1 of V) as the halves 1024 + byte
+__device__ __forceinline__ uint32_t bytes_to_h2_1024(uint32_t v, uint32_t sel) {
+  return __byte_perm(v, 0x64646464u, sel);
+}
+__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t h2_of(float a) {
+  const __half2 h = __float2half2_rn(a);
+  return *(const uint32_t*)&h;
+}
+
+// IQ2_XXS sub-block IB of the block at BLK: the 32 integers grid * sign * (2 LS + 1)
+// (at most 43 * 31: exact in fp16) as chunks 4*(ib&1) .. +3 of the row.  The block's
+// float part is d / 8 (src/avx2.lisp:77-110 takes the products this way).
+__device__ __forceinline__ void b_iq2xxs(const u8* blk, int ib, u8* tile, int row, const uint2* grid, const uint2* smask) {
+  uint32_t v[2];
+  ldg_words<2>(blk + 2 + 8 * ib, v);
+  const uint32_t idx = v[0], aux = v[1];
+  const float ls = (float)(2 * (aux >> 28) + 1);
+  const uint32_t s2 = h2_of(ls), bias = h2_of(-1152.0f * ls);  // (1024 + (b + 128)) * s - 1152 s = b * s
 #pragma unroll
-  for (int sb = 0; sb < 2; ++sb) {
-    const uint32_t idx = v[2 * sb], aux = v[2 * sb + 1];
-    const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)(aux >> 28))), 0.25f);
-#pragma unroll
-    for (int l = 0; l < 4; ++l) {
-      const uint2 g = grid[(idx >> (8 * l)) & 0xff];
-      const uint32_t s = signs[(aux >> (7 * l)) & 127];
-      float f[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float mag = (float)(((j < 4 ? g.x : g.y) >> (8 * (j & 3))) & 0xff);
-        f[j] = __fmul_rn(db, mag);
-        if ((s >> j) & 1) f[j] = -f[j];
-      }
-      store_chunk(tile, row, 4 * sb + l,
-                  make_uint4(pack_h2(f[0], f[1]), pack_h2(f[2], f[3]), pack_h2(f[4], f[5]), pack_h2(f[6], f[7])));
-    }
+  for (int l = 0; l < 4; ++l) {
+    const uint2 g = grid[(idx >> (8 * l)) & 0xff];
+    const uint2 m = smask[(aux >> (7 * l)) & 127];
+    // signed bytes: (g ^ m) - m per byte; then + 128 to make them unsigned for the conversion
+    const uint32_t lo = ((g.x ^ m.x) + (m.x & 0x01010101u)) ^ 0x80808080u;
+    const uint32_t hi = ((g.y ^ m.y) + (m.y & 0x01010101u)) ^ 0x80808080u;
+    store_chunk(tile, row, 4 * (ib & 1) + l,
+                make_uint4(hfma2(bytes_to_h2_1024(lo, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(lo, 0x4342), s2, bias),
+                           hfma2(bytes_to_h2_1024(hi, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(hi, 0x4342), s2, bias)));
   }
 }
 
-// Q2_K: K step KS of the block at BLK: weights 64*ks .. 64*ks+63 = half h = ks/2, shifts
-// k = 2*(ks%2), 2*(ks%2)+1.  Values as Q2K-ROW-FLOATS! (src/iquant.lisp:217-230), to fp16.
-__device__ __forceinline__ void dequant64_q2k(const u8* blk, int ks, u8* tile, int row) {
-  const int h = ks >> 1, k0 = 2 * (ks & 1);
+// Q2_K: K step KS (0..3) of the block, the thread's half KK (shift k = 2*(ks&1) + kk): the 32
+// integers (scale & 15) * q (at most 45) as chunks 4*kk .. +3.
+__device__ __forceinline__ void b_q2k(const u8* blk, int ks, int kk, u8* tile, int row) {
+  const int h = ks >> 1, k = 2 * (ks & 1) + kk;
   const uint32_t* q32 = (const uint32_t*)(blk + 16 + 32 * h);  // 32 bytes of quants, 4-byte aligned
-  uint32_t q[8];
+  const uint32_t sc2 = __ldg((const u16*)(blk + 8 * h + 2 * k));  // scale bytes 8h + 2k + half, half = 0, 1
 #pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = __ldg(q32 + i);
-  const uint32_t dd = __ldg((const uint32_t*)(blk + 80));
-  const float d = h2f(dd & 0xffff), dmin = h2f(dd >> 16);
-  const uint32_t sc4 = __ldg((const uint32_t*)(blk + 8 * h + 4 * (ks & 1)));  // scale bytes 8h + 2k + half, k = k0, k0+1
+  for (int half = 0; half < 2; ++half) {
+    const float sc = (float)((sc2 >> (8 * half)) & 15u);
+    const uint32_t s2 = h2_of(sc), bias = h2_of(-1024.0f * sc);
 #pragma unroll
-  for (int kk = 0; kk < 2; ++kk) {
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const uint32_t sb = (sc4 >> (8 * (2 * kk + half))) & 0xff;
-      const float dl = __fmul_rn(d, (float)(sb & 15)), ml = __fmul_rn(dmin, (float)(sb >> 4));
-      // 16 weights: bytes 16*half .. 16*half+15 of the 32, shifted by 2*(k0+kk)
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float f[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int byte = 16 * half + 8 * c + j;
-          const uint32_t qv = (q[byte >> 2] >> (8 * (byte & 3) + 2 * (k0 + kk))) & 3u;
-          f[j] = __fsub_rn(__fmul_rn(dl, (float)qv), ml);
-        }
-        store_chunk(tile, row, 4 * kk + 2 * half + c,
-                    make_uint4(pack_h2(f[0], f[1]), pack_h2(f[2], f[3]), pack_h2(f[4], f[5]), pack_h2(f[6], f[7])));
-      }
+    for (int c = 0; c < 2; ++c) {
+      const uint32_t w0 = (__ldg(q32 + 4 * half + 2 * c) >> (2 * k)) & 0x03030303u;
+      const uint32_t w1 = (__ldg(q32 + 4 * half + 2 * c + 1) >> (2 * k)) & 0x03030303u;
+      store_chunk(tile, row, 4 * kk + 2 * half + c,
+                  make_uint4(hfma2(bytes_to_h2_1024(w0, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w0, 0x4342), s2, bias),
+                             hfma2(bytes_to_h2_1024(w1, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w1, 0x4342), s2, bias)));
     }
   }
 }
+// Q2_K: the block's sixteen mins (scale >> 4), eight per thread, as chunk HALF of the "mins" tile
+__device__ __forceinline__ void b_q2k_mins(const u8* blk, int half, u8* tile, int row) {
+  const uint2 s = make_uint2(__ldg((const uint32_t*)(blk + 8 * half)), __ldg((const uint32_t*)(blk + 8 * half + 4)));
+  const uint32_t lo = (s.x >> 4) & 0x0f0f0f0fu, hi = (s.y >> 4) & 0x0f0f0f0fu;
+  const uint32_t k1024 = 0xe400e400u;  // -1024 twice
+  uint32_t r[4];
+  r[0] = bytes_to_h2_1024(lo, 0x4140); r[1] = bytes_to_h2_1024(lo, 0x4342);
+  r[2] = bytes_to_h2_1024(hi, 0x4140); r[3] = bytes_to_h2_1024(hi, 0x4342);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) asm("add.rn.f16x2 %0, %0, %1;" : "+r"(r[i]) : "r"(k1024));
+  store_chunk(tile, row, half, make_uint4(r[0], r[1], r[2], r[3]));
+}
+
+// K steps per 256-wide block: four of the quants; for Q2_K a fifth whose A tile holds the
+// activations' sums of 16 and whose B tile holds the mins (one K = 16 MMA into a second
+// accumulator).
+template <int FMT> struct MmGeom { static constexpr int SPB = FMT == ILL_Q2_K ? 5 : 4, ACCS = FMT == ILL_Q2_K ? 2 : 1; };
 
 template <int FMT>
-__global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant__ CUtensorMap xmap, const MmParams p) {
+__global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                           const __grid_constant__ CUtensorMap emap, const MmParams p) {
+  constexpr int SPB = MmGeom<FMT>::SPB, ACCS = MmGeom<FMT>::ACCS;
+  constexpr uint32_t TMEM_COLS = 2 * ACCS * MM_BN;  // two buffers of accumulators
   extern __shared__ __align__(1024) u8 smem_raw[];
   // [A stages][B stages] (each tile 1024-byte aligned, as the 128-byte swizzle needs), then barriers, tables
   u8* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -198,13 +209,15 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   u8* b_tiles = smem + MM_STAGES * MM_TILE_BYTES;
   u8* tail = smem + 2 * MM_STAGES * MM_TILE_BYTES;
   uint64_t* full_a = (uint64_t*)tail;            // TMA bytes landed
-  uint64_t* full_b = full_a + MM_STAGES;         // 4 dequant warps arrived
+  uint64_t* full_b = full_a + MM_STAGES;         // 8 dequantizing warps arrived
   uint64_t* empty = full_b + MM_STAGES;          // the MMAs that read the stage completed
-  uint64_t* acc_full = empty + MM_STAGES;        // all MMAs of the tile completed
-  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
-  int* tile_info = (int*)(tmem_slot + 1);        // expert, row0, nrows valid
-  uint2* iq_grid = (uint2*)(tail + 256);
-  u8* iq_signs = (u8*)(iq_grid + 256);
+  uint64_t* acc_full = empty + MM_STAGES;        // [2] a block's MMAs completed
+  uint64_t* acc_free = acc_full + 2;             // [2] the 8 drain warps read the buffer
+  uint32_t* tmem_slot = (uint32_t*)(acc_free + 2);
+  int* tile_info = (int*)(tmem_slot + 1);        // expert, row0, rows valid
+  float* wsc = (float*)(tail + 256);             // [2 buffers][128 rows][2]: d (and dmin) of the block
+  uint2* iq_grid = (uint2*)(tail + 256 + 2048);
+  uint2* iq_smask = iq_grid + 256;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nt = blockIdx.x;   // tile along the weights' rows
@@ -239,8 +252,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     if (lane == 0) { tile_info[0] = found; tile_info[1] = row0; tile_info[2] = nvalid; }
   }
   if (tid == 32) {
-    for (int s = 0; s < MM_STAGES; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 4); mbar_init(&empty[s], 1); }
-    mbar_init(acc_full, 1);
+    for (int s = 0; s < MM_STAGES; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 8); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_free[b], 8); }
     mbar_fence_init();
   }
   if (FMT == ILL_IQ2_XXS) {
@@ -248,29 +261,41 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       const uint64_t g = ill_iq2xxs_grid[i];
       iq_grid[i] = make_uint2((uint32_t)g, (uint32_t)(g >> 32));
     }
-    for (int i = tid; i < 128; i += MM_THREADS) iq_signs[i] = ill_ksigns_iq2xs[i];
+    for (int i = tid; i < 128; i += MM_THREADS) {
+      const uint32_t sg = ill_ksigns_iq2xs[i];
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if ((sg >> j) & 1) lo |= 0xffu << (8 * j);
+        if ((sg >> (4 + j)) & 1) hi |= 0xffu << (8 * j);
+      }
+      iq_smask[i] = make_uint2(lo, hi);
+    }
   }
   __syncthreads();
   const int expert = tile_info[0], row0 = tile_info[1], nvalid = tile_info[2];
   if (expert < 0) return;  // past the last row tile: nothing allocated, nothing in flight
-  if (warp == 1) tmem_alloc(tmem_slot, MM_TMEM_COLS);
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int ksteps = p.ncols / MM_BK;
+  const int nkb = p.ncols / 256;
+  const int nsteps = nkb * SPB;
   const u8* wexp = (const u8*)(uintptr_t)p.ptrs[expert] + p.add;
   bool ok = true;
 
   if (warp == 0) {
-    // ---- TMA producer of the X tile
+    // ---- TMA producer of the X tiles
     if (lane == 0) {
-      for (int ks = 0; ks < ksteps; ++ks) {
-        const int s = ks % MM_STAGES, use = ks / MM_STAGES;
+      for (int st = 0; st < nsteps; ++st) {
+        const int s = st % MM_STAGES, use = st / MM_STAGES;
         if (use > 0 && !mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY)) { ok = false; break; }
+        const int kb = st / SPB, j = st - kb * SPB;
         mbar_expect_tx(&full_a[s], MM_TILE_BYTES);
-        tma_load_2d(a_tiles + s * MM_TILE_BYTES, &xmap, ks * MM_BK, row0, &full_a[s]);
+        if (j < 4) tma_load_2d(a_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &full_a[s]);
+        else tma_load_2d(a_tiles + s * MM_TILE_BYTES, &emap, kb * MM_BK, row0, &full_a[s]);  // the sums of 16
       }
     }
   } else if (warp == 1) {
@@ -278,86 +303,154 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     if (lane == 0) {
       // fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
       const uint32_t idesc = (1u << 4) | ((uint32_t)(MM_BN >> 3) << 17) | ((uint32_t)(MM_BM >> 4) << 24);
-      for (int ks = 0; ks < ksteps; ++ks) {
-        const int s = ks % MM_STAGES;
-        const uint32_t par = (uint32_t)(ks / MM_STAGES) & 1u;
-        if (!mbar_wait(&full_a[s], par, p.status, ST_MM_WAIT_FULL) ||
-            !mbar_wait(&full_b[s], par, p.status, ST_MM_WAIT_FULL + 1)) { ok = false; break; }
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int b = kb & 1;
+        if (kb >= 2 && !mbar_wait(&acc_free[b], (uint32_t)(kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t ad = umma_desc(a_tiles + s * MM_TILE_BYTES), bd = umma_desc(b_tiles + s * MM_TILE_BYTES);
+        const uint32_t d1 = tmem_base + (uint32_t)(b * ACCS * MM_BN);
+        for (int j = 0; j < SPB; ++j) {
+          const int st = kb * SPB + j, s = st % MM_STAGES;
+          const uint32_t par = (uint32_t)(st / MM_STAGES) & 1u;
+          if (!mbar_wait(&full_a[s], par, p.status, ST_MM_WAIT_FULL) ||
+              !mbar_wait(&full_b[s], par, p.status, ST_MM_WAIT_FULL + 1)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t ad = umma_desc(a_tiles + s * MM_TILE_BYTES), bd = umma_desc(b_tiles + s * MM_TILE_BYTES);
+          if (j < 4) {
 #pragma unroll
-        for (int k = 0; k < MM_BK / 16; ++k)  // 32 bytes further along K inside the swizzle atom each time
-          umma_f16(tmem_base, ad + 2 * k, bd + 2 * k, idesc, (ks | k) ? 1u : 0u);
-        umma_commit(&empty[s]);  // frees the stage when these MMAs are done
+            for (int k = 0; k < MM_BK / 16; ++k)  // 32 bytes further along K inside the swizzle atom each time
+              umma_f16(d1, ad + 2 * k, bd + 2 * k, idesc, (j | k) ? 1u : 0u);
+          } else {
+            umma_f16(d1 + MM_BN, ad, bd, idesc, 0u);  // mins x sums of 16: one K = 16 product
+          }
+          umma_commit(&empty[s]);  // frees the stage when these MMAs are done
+        }
+        if (ok) umma_commit(&acc_full[b]);
       }
-      if (ok) umma_commit(acc_full);
     }
   } else {
-    // ---- dequantizing producers of the W tile (warps 2..5), then the epilogue
-    const int row = (warp - 2) * 32 + lane;        // weight row in the tile
+    // ---- warps 2..9: the weights' integer parts into the B tiles; the accumulators drained block by
+    // block with the block's float scales; the final store
+    const int t = tid - 64;                        // 0..255
+    const int row = t >> 1, half = t & 1;          // weight row in the tile, half of each K step
     const int n = nt * MM_BN + row;
     const bool has_row = n < p.nrows;
     const u8* wrow = wexp + (long long)(has_row ? n : 0) * p.row_bytes;
     constexpr int BB = FMT == ILL_IQ2_XXS ? 66 : 84;
-    for (int ks = 0; ks < ksteps; ++ks) {
-      const int s = ks % MM_STAGES, use = ks / MM_STAGES;
-      if (use > 0) {
-        bool w_ok = mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
-        w_ok = __all_sync(0xffffffffu, w_ok);
-        if (!w_ok) { ok = false; break; }
-      }
-      u8* tile = b_tiles + s * MM_TILE_BYTES;
-      const u8* blk = wrow + (ks >> 2) * BB;
-      if (has_row) {
-        if constexpr (FMT == ILL_IQ2_XXS) dequant64_iq2xxs(blk, ks & 3, tile, row, iq_grid, iq_signs);
-        else dequant64_q2k(blk, ks & 3, tile, row);
-      } else {
+    const int q = warp & 3;                        // TMEM lanes 32q .. 32q+31 are this warp's
+    const int m = q * 32 + lane;                   // accumulator row
+    const int chalf = (warp - 2) >> 2;             // columns 64*chalf .. +63
+    const long long place = (long long)row0 + m;
+    const long long tok = place < p.total_rows ? (p.map ? (long long)p.map[place] : place) : -1;
+    float out[64];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) store_chunk(tile, row, c, make_uint4(0, 0, 0, 0));
+    for (int i = 0; i < 64; ++i) out[i] = 0.0f;
+
+    auto produce = [&](int kb) -> bool {
+      const int b = kb & 1;
+      if (kb >= 2) {  // the scales of block kb - 2 have been read by every drain warp
+        bool w_ok = mbar_wait(&acc_free[b], (uint32_t)(kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI + 1);
+        if (!__all_sync(0xffffffffu, w_ok)) return false;
       }
-      fence_async_smem();  // the tensor core reads the tile through the async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&full_b[s]);
-    }
-    // ---- epilogue: this warp reads the 32 accumulator rows it may access
-    if (ok) {
-      bool e_ok = mbar_wait(acc_full, 0, p.status, ST_MM_WAIT_ACC);
-      e_ok = __all_sync(0xffffffffu, e_ok);
-      if (e_ok) {
-        tc_fence_after();
-        const int q = warp & 3;                   // TMEM lanes 32q .. 32q+31
-        const int r = q * 32 + lane;              // row of the tile
-        float* yrow = p.y + (long long)(row0 + r) * p.y_stride + (long long)nt * MM_BN;
-#pragma unroll 1
-        for (int c0 = 0; c0 < MM_BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-          if (r < nvalid) {
+      const u8* blk = wrow + (long long)kb * BB;
+      if (half == 0) {
+        float d = 0.0f, dmin = 0.0f;
+        if (has_row) {
+          if constexpr (FMT == ILL_IQ2_XXS) d = h2f((uint32_t)__ldg((const u16*)blk));
+          else { const uint32_t dd = __ldg((const uint32_t*)(blk + 80)); d = h2f(dd & 0xffff); dmin = h2f(dd >> 16); }
+        }
+        wsc[(b * 128 + row) * 2] = d;
+        wsc[(b * 128 + row) * 2 + 1] = dmin;
+      }
+      for (int j = 0; j < SPB; ++j) {
+        const int st = kb * SPB + j, s = st % MM_STAGES, use = st / MM_STAGES;
+        if (use > 0) {
+          bool w_ok = mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
+          if (!__all_sync(0xffffffffu, w_ok)) return false;
+        }
+        u8* tile = b_tiles + s * MM_TILE_BYTES;
+        if (has_row) {
+          if constexpr (FMT == ILL_IQ2_XXS) b_iq2xxs(blk, 2 * j + half, tile, row, iq_grid, iq_smask);
+          else if (j < 4) b_q2k(blk, j, half, tile, row);
+          else b_q2k_mins(blk, half, tile, row);
+        } else {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              if (nt * MM_BN + c0 + j + 3 < p.nrows) {
-                *(float4*)(yrow + c0 + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                        __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-              } else {
-                for (int jj = 0; jj < 4; ++jj)
-                  if (nt * MM_BN + c0 + j + jj < p.nrows) yrow[c0 + j + jj] = __uint_as_float(v[j + jj]);
-              }
-            }
+          for (int c = 0; c < 4; ++c) store_chunk(tile, row, 4 * half + c, make_uint4(0, 0, 0, 0));
+        }
+        fence_async_smem();  // the tensor core reads the tile through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_b[s]);
+      }
+      return true;
+    };
+    auto drain = [&](int kb) -> bool {
+      const int b = kb & 1;
+      bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(kb / 2) & 1u, p.status, ST_MM_WAIT_ACC);
+      if (!__all_sync(0xffffffffu, e_ok)) return false;
+      tc_fence_after();
+      const float dx = tok >= 0 ? p.xd[tok * nkb + kb] : 0.0f;
+      const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * ACCS * MM_BN + 64 * chalf);
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(t0 + c0, v);
+        if constexpr (FMT == ILL_IQ2_XXS) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float dw = wsc[(b * 128 + 64 * chalf + c0 + i) * 2];
+            // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum; the 1/8 at the end
+            out[c0 + i] = __fadd_rn(out[c0 + i], __fmul_rn(__fmul_rn(dw, dx), __uint_as_float(v[i])));
           }
+        } else {
+          uint32_t v2[32];
+          tmem_ld32(t0 + MM_BN + c0, v2);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float2 sc = *(const float2*)&wsc[(b * 128 + 64 * chalf + c0 + i) * 2];
+            // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
+            out[c0 + i] = __fadd_rn(out[c0 + i], __fsub_rn(__fmul_rn(__fmul_rn(dx, sc.x), __uint_as_float(v[i])),
+                                                           __fmul_rn(__fmul_rn(dx, sc.y), __uint_as_float(v2[i]))));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_free[b]);
+      return true;
+    };
+
+    for (int kb = 0; kb < nkb && ok; ++kb) {
+      ok = produce(kb);
+      if (ok && kb >= 1) ok = drain(kb - 1);
+    }
+    if (ok) ok = drain(nkb - 1);
+    if (ok && m < nvalid) {
+      float* yrow = p.y + place * p.y_stride + (long long)nt * MM_BN + 64 * chalf;
+      const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
+#pragma unroll
+      for (int j = 0; j < 64; j += 4) {
+        const int n0 = nt * MM_BN + 64 * chalf + j;
+        if (n0 + 3 < p.nrows) {
+          *(float4*)(yrow + j) = make_float4(out[j] * fin, out[j + 1] * fin, out[j + 2] * fin, out[j + 3] * fin);
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj)
+            if (n0 + jj < p.nrows) yrow[j + jj] = out[j + jj] * fin;
         }
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, MM_TMEM_COLS);
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-// X (tokens' Q8_K quants) -> fp16 rows in expert order: XH[place, k] = fp16(q[t, k] * d[t, k/256]),
-// t = MAP[place] (or place when MAP is null).
+// The Q8_K activations as the tensor cores take them, in expert order: XH[place, k] = fp16(q[t, k])
+// (exact), t = MAP[place] (or place when MAP is null); and, when XE is given, the sums of 16 as
+// XE[place, kb, 0..15] = fp16(bsums[t, 16 kb ..]) (exact: at most 2032), the other 48 of each 64 zero.
 __global__ void __launch_bounds__(256) act_f16_kernel(long long rows, int cols, const i8* __restrict__ xq,
-                                                      const float* __restrict__ xd, const unsigned* __restrict__ map,
-                                                      __half* __restrict__ xh) {
+                                                      const int16_t* __restrict__ bsums,
+                                                      const unsigned* __restrict__ map, __half* __restrict__ xh,
+                                                      __half* __restrict__ xe) {
   pdl_launch_dependents();
   pdl_wait();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread: 16 values
@@ -367,18 +460,27 @@ __global__ void __launch_bounds__(256) act_f16_kernel(long long rows, int cols, 
   const int j = (int)(gid - place * per_row);
   const long long t = map ? (long long)map[place] : place;
   const uint4 q = *(const uint4*)(xq + t * cols + 16 * j);
-  const float d = xd[t * (cols / 256) + (16 * j) / 256];
   const uint32_t w[4] = {q.x, q.y, q.z, q.w};
   uint32_t h[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int b0 = (int)(signed char)((w[i >> 1] >> (16 * (i & 1))) & 0xff);
     const int b1 = (int)(signed char)((w[i >> 1] >> (16 * (i & 1) + 8)) & 0xff);
-    h[i] = pack_h2(__fmul_rn((float)b0, d), __fmul_rn((float)b1, d));
+    const __half2 hh = __floats2half2_rn((float)b0, (float)b1);
+    h[i] = *(const uint32_t*)&hh;
   }
   uint4* dst = (uint4*)(xh + place * cols + 16 * j);
   dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
   dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+  if (xe) {
+    // this thread's 16 quants are one sum of 16: element j%16 of block j/16; it also clears 3 of the 48 zeros
+    const int kb = j >> 4, g = j & 15;
+    __half* e = xe + (place * (cols / 256) + kb) * 64;
+    e[g] = __float2half_rn((float)bsums[t * (cols / 16) + j]);
+    e[16 + 3 * g] = __float2half_rn(0.0f);
+    e[16 + 3 * g + 1] = __float2half_rn(0.0f);
+    e[16 + 3 * g + 2] = __float2half_rn(0.0f);
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -401,42 +503,52 @@ static EncodeTiledFn encode_tiled_fn() {
 
 using namespace ill;
 
-extern "C" int ill_act_f16(int64_t rows, int cols, ill_dptr xq, ill_dptr xd, ill_dptr map, ill_dptr xh,
+extern "C" int ill_act_f16(int64_t rows, int cols, ill_dptr xq, ill_dptr bsums, ill_dptr map, ill_dptr xh, ill_dptr xe,
                            ill_stream stream) {
-  if (rows < 0 || cols <= 0 || cols % 256 || !xq || !xd || !xh) return ILL_ERR_ARG;
-  if ((xq & 15) || (xd & 3) || (map & 3) || (xh & 15)) return ILL_ERR_ALIGN;
+  if (rows < 0 || cols <= 0 || cols % 256 || !xq || !xh || (xe && !bsums)) return ILL_ERR_ARG;
+  if ((xq & 15) || (bsums & 1) || (map & 3) || (xh & 15) || (xe & 15)) return ILL_ERR_ALIGN;
   if (rows == 0) return ILL_OK;
   long long nrows = rows;
   const i8* qp = (const i8*)(uintptr_t)xq;
-  const float* dp = (const float*)(uintptr_t)xd;
+  const int16_t* bp = (const int16_t*)(uintptr_t)bsums;
   const unsigned* mp = (const unsigned*)(uintptr_t)map;
   __half* hp = (__half*)(uintptr_t)xh;
-  void* args[] = {&nrows, &cols, &qp, &dp, &mp, &hp};
+  __half* ep = (__half*)(uintptr_t)xe;
+  void* args[] = {&nrows, &cols, &qp, &bp, &mp, &hp, &ep};
   const long long threads = rows * (cols / 16);
   return launch_kernel((const void*)act_f16_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, args,
                        (cudaStream_t)stream);
 }
 
+static int encode_map(CUtensorMap* map, ill_dptr base, int64_t inner, int64_t rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return cuda_fail(cudaErrorNotSupported);
+  const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)inner * 2};
+  const cuuint32_t box[2] = {MM_BK, MM_BM};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)(uintptr_t)base, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? ILL_OK : cuda_fail(cudaErrorInvalidValue);
+}
+
 extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases,
-                             int ne, int64_t total_rows, ill_dptr xh, ill_dptr y, int64_t y_stride, ill_stream stream) {
+                             int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr y,
+                             int64_t y_stride, ill_stream stream) {
   if (fmt != ILL_IQ2_XXS && fmt != ILL_Q2_K) return ILL_ERR_UNSUPPORTED;
   if (ncols <= 0 || ncols % 256 || nrows <= 0 || ne <= 0 || ne > 65535 || total_rows < 0 || y_stride < nrows)
     return ILL_ERR_ARG;
-  if (!ptrs || !counts || !bases || !xh || !y) return ILL_ERR_ARG;
-  if ((ptrs & 7) || (counts & 3) || (bases & 3) || (xh & 15) || (y & 15) || (y_stride & 3) || (add & 3))
+  if (!ptrs || !counts || !bases || !xh || !xd || !y || (fmt == ILL_Q2_K && !xe)) return ILL_ERR_ARG;
+  if ((ptrs & 7) || (counts & 3) || (bases & 3) || (xh & 15) || (xe & 15) || (xd & 3) || (map & 3) || (y & 15) ||
+      (y_stride & 3) || (add & 3))
     return ILL_ERR_ALIGN;
   if (total_rows == 0) return ILL_OK;
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return cuda_fail(cudaErrorNotSupported);
-  CUtensorMap map;
-  const cuuint64_t dims[2] = {(cuuint64_t)ncols, (cuuint64_t)total_rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ncols * 2};
-  const cuuint32_t box[2] = {MM_BK, MM_BM};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)(uintptr_t)xh, dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  CUtensorMap xmap, emap;
+  int rc = encode_map(&xmap, xh, ncols, total_rows);
+  if (rc) return rc;
+  rc = fmt == ILL_Q2_K ? encode_map(&emap, xe, (int64_t)(ncols / 256) * 64, total_rows) : encode_map(&emap, xh, ncols, total_rows);
+  if (rc) return rc;
   MmParams p;
   p.ncols = ncols;
   p.nrows = nrows;
@@ -445,18 +557,21 @@ extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dpt
   p.ptrs = (const unsigned long long*)(uintptr_t)ptrs;
   p.counts = (const unsigned*)(uintptr_t)counts;
   p.bases = (const unsigned*)(uintptr_t)bases;
+  p.xd = (const float*)(uintptr_t)xd;
+  p.map = (const unsigned*)(uintptr_t)map;
+  p.total_rows = total_rows;
   p.y = (float*)(uintptr_t)y;
   p.y_stride = y_stride;
   p.ne = ne;
-  p.max_mtiles = (int)((total_rows + MM_BM - 1) / MM_BM) + ne;  // every expert may end with a partial tile
   p.status = device_status_word();
-  const size_t smem = 2 * MM_STAGES * MM_TILE_BYTES + 256 + 2048 + 128 + 1024;
+  const int max_mtiles = (int)((total_rows + MM_BM - 1) / MM_BM) + ne;  // every expert may end with a partial tile
+  const size_t smem = 2 * MM_STAGES * MM_TILE_BYTES + 256 + 2048 + 2048 + 1024 + 1024;
   const void* k = fmt == ILL_IQ2_XXS ? (const void*)mm_id_kernel<ILL_IQ2_XXS> : (const void*)mm_id_kernel<ILL_Q2_K>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e);
-  void* args[] = {&map, &p};
+  void* args[] = {&xmap, &emap, &p};
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((nrows + MM_BN - 1) / MM_BN, p.max_mtiles, 1);
+  cfg.gridDim = dim3((nrows + MM_BN - 1) / MM_BN, max_mtiles, 1);
   cfg.blockDim = dim3(MM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = (cudaStream_t)stream;

@@ -12,6 +12,7 @@ import torch
 
 from . import _lib
 from . import cuda_dense as D
+from .blocks import Q2_K
 from .cuda_ds4f import ExpertPool, swiglu_w
 
 
@@ -38,11 +39,13 @@ class ChunkScratch:
     group: torch.Tensor
     xq: D.QAct
     xh: torch.Tensor
+    xe: torch.Tensor
     g: torch.Tensor
     u: torch.Tensor
     mid: torch.Tensor
     midq: D.QAct
     mh: torch.Tensor
+    me: torch.Tensor
     down: torch.Tensor
     moe: torch.Tensor
 
@@ -57,15 +60,22 @@ def make_chunk_scratch(pool, n, nu, device="cuda"):
         torch.empty(rows, **i32), torch.empty(rows, **i32), torch.empty(rows, **f32),
         torch.empty(_lib.lib().ill_moe_group_scratch_bytes(rows, ne), dtype=torch.uint8, device=device),
         D.make_qact(n * d, "q8k", device=device), torch.empty(rows, d, dtype=torch.float16, device=device),
+        torch.empty(rows, d // 256, 64, dtype=torch.float16, device=device) if pool.gate_fmt == Q2_K else None,
         torch.empty(rows, ff, **f32), torch.empty(rows, ff, **f32), torch.empty(rows, ff, **f32),
         D.make_qact(rows * ff, "q8k", device=device), torch.empty(rows, ff, dtype=torch.float16, device=device),
+        torch.empty(rows, ff // 256, 64, dtype=torch.float16, device=device) if pool.down_fmt == Q2_K else None,
         torch.empty(rows, d, **f32), torch.empty(n, d, **f32))
 
 
-def mm_id(pool, fmt, ncols, nrows, add, ptrs, sc, xh, y):
-    """d4_mm_id_<fmt> (src/cuda-ds4f-prefill.lisp:345-347)."""
-    _lib.call("ill_moe_mm_id", fmt, ncols, nrows, add, _ptr(ptrs), _ptr(sc.counts), _ptr(sc.bases), pool.n_expert,
-              sc.rows, _ptr(xh), _ptr(y), nrows, _stream())
+def act_f16(act, cols, rows, rmap, xh, xe):
+    """The Q8_K activations ACT as fp16 integers in expert order (and the sums of 16)."""
+    _lib.call("ill_act_f16", rows, cols, _ptr(act.xq), _ptr(act.xsum), _ptr(rmap), _ptr(xh), _ptr(xe), _stream())
+
+
+def mm_id(pool, fmt, ncols, nrows, add, sc, xh, xe, xd, rmap, y):
+    """d4_mm_id_<fmt> (src/cuda-ds4f-prefill.lisp:345-347); every expert is resident."""
+    _lib.call("ill_moe_mm_id", fmt, ncols, nrows, add, _ptr(pool.ptrs_all), _ptr(sc.counts), _ptr(sc.bases),
+              pool.n_expert, sc.rows, _ptr(xh), _ptr(xe), _ptr(xd), _ptr(rmap), _ptr(y), nrows, _stream())
 
 
 def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, scale=1.0, shared=None):
@@ -79,13 +89,12 @@ def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, s
     _lib.call("ill_moe_group", sc.rows, ne, nu, _ptr(sc.sel), _ptr(sc.w), _ptr(sc.group), _ptr(sc.counts),
               _ptr(sc.bases), _ptr(sc.rmap), _ptr(sc.smap), _ptr(sc.wrow), st)
     D.quant_q8(norms, sc.xq)                                       # each token's Q8_K, once
-    _lib.call("ill_act_f16", sc.rows, d, _ptr(sc.xq.xq), _ptr(sc.xq.xs), _ptr(sc.rmap), _ptr(sc.xh), st)
-    ptrs = pool.ptrs_all                                           # every expert is resident
-    mm_id(pool, pool.gate_fmt, d, ff, 0, ptrs, sc, sc.xh, sc.g)
-    mm_id(pool, pool.gate_fmt, d, ff, pool.gate_bytes, ptrs, sc, sc.xh, sc.u)
+    act_f16(sc.xq, d, sc.rows, sc.rmap, sc.xh, sc.xe)
+    mm_id(pool, pool.gate_fmt, d, ff, 0, sc, sc.xh, sc.xe, sc.xq.xs, sc.rmap, sc.g)
+    mm_id(pool, pool.gate_fmt, d, ff, pool.gate_bytes, sc, sc.xh, sc.xe, sc.xq.xs, sc.rmap, sc.u)
     swiglu_w(sc.g, sc.u, sc.wrow, sc.mid, ff, clamp)
     D.quant_q8(sc.mid, sc.midq)                                    # per (token, slot) row, as the CPU path does
-    _lib.call("ill_act_f16", sc.rows, ff, _ptr(sc.midq.xq), _ptr(sc.midq.xs), 0, _ptr(sc.mh), st)
-    mm_id(pool, pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptrs, sc, sc.mh, sc.down)
+    act_f16(sc.midq, ff, sc.rows, None, sc.mh, sc.me)
+    mm_id(pool, pool.down_fmt, ff, d, 2 * pool.gate_bytes, sc, sc.mh, sc.me, sc.midq.xs, None, sc.down)
     _lib.call("ill_moe_sum", d, nu, n, _ptr(sc.down), _ptr(sc.smap), _ptr(shared), _ptr(sc.moe), st)
     return sc.moe

@@ -214,26 +214,34 @@ ILL_API int ill_moe_group(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w
 ILL_API int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,
                             ill_stream stream);
 
-/* XH[place*cols + k] = fp16(XQ[t*cols + k] * XD[t*(cols/256) + k/256]), t =
- * MAP[place] (MAP = 0: t = place): the Q8_K activations, dequantized to the
- * very values the reference's CPU kernels multiply, gathered into expert order
- * and rounded once to fp16 for the tensor cores.  (The reference's d4_mm_id
- * rounds the unquantized floats to fp16 instead, src/cuda/ds4f_mm.cu:1-20,
- * which is why its prefill drifts from its CPU path.)  XQ, XH 16-byte aligned. */
-ILL_API int ill_act_f16(int64_t rows, int cols, ill_dptr xq, ill_dptr xd, ill_dptr map, ill_dptr xh,
+/* The Q8_K activations as the tensor cores take them, gathered into expert
+ * order: XH[place*cols + k] = fp16(XQ[t*cols + k]) (the int8 quant, exact), t =
+ * MAP[place] (MAP = 0: t = place).  With XE given (Q2_K weights need it), also
+ * the sums of 16: XE[(place*(cols/256) + kb)*64 + g] = fp16(BSUMS[t*(cols/16) +
+ * 16*kb + g]) for g < 16 (exact), the other 48 of each 64 zero.  XQ, XH, XE
+ * 16-byte aligned.  (The reference's d4_mm_id rounds the unquantized floats to
+ * fp16 instead, src/cuda/ds4f_mm.cu:1-20, and so drifts from its CPU path.) */
+ILL_API int ill_act_f16(int64_t rows, int cols, ill_dptr xq, ill_dptr bsums, ill_dptr map, ill_dptr xh, ill_dptr xe,
                         ill_stream stream);
 
 /* The routed experts' product for a chunk: for each expert e < NE and each row
  * `place` in [BASES[e], BASES[e] + COUNTS[e]): Y[place*y_stride + n] = W_e[n] .
- * XH[place], n < NROWS, W_e the FMT (ILL_IQ2_XXS or ILL_Q2_K) matrix at PTRS[e]
- * + ADD.  COUNTS / BASES are read on the device (no host synchronisation);
- * TOTAL_ROWS is the number of rows of XH and Y.  tcgen05 MMA (fp16 operands,
- * fp32 accumulators in tensor memory), 128 x 128 tiles, the weights
- * dequantized tile by tile into shared memory.  Replaces d4_mm_id_iq2_xxs /
- * d4_mm_id_q2_k (src/cuda/ds4f_mm.cu:229-257) behind DK-FFN-ROUTED-CHUNK
- * (src/cuda-ds4f-prefill.lisp:345-351). */
+ * X[place], n < NROWS, W_e the FMT (ILL_IQ2_XXS or ILL_Q2_K) matrix at PTRS[e]
+ * + ADD, X the Q8_K activations XH (+ XE for Q2_K) of ill_act_f16 with block
+ * scales XD[t*(ncols/256) + kb], t = MAP[place] (MAP = 0: t = place).  COUNTS /
+ * BASES are read on the device (no host synchronisation); TOTAL_ROWS is the
+ * number of rows of XH and Y.
+ *
+ * tcgen05 MMA, 128 x 128 tiles: the operands are the integers of both sides as
+ * fp16 (exact), accumulated per 256-wide block in tensor memory (fp32, two
+ * buffers), and each block's sum is scaled by d_w * d_x in fp32 as it is
+ * drained -- the arithmetic of the reference's CPU kernels (src/avx2.lisp:
+ * 77-150), so results agree with them to fp32 rounding.  Replaces
+ * d4_mm_id_iq2_xxs / d4_mm_id_q2_k (src/cuda/ds4f_mm.cu:229-257) behind
+ * DK-FFN-ROUTED-CHUNK (src/cuda-ds4f-prefill.lisp:345-351). */
 ILL_API int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases,
-                          int ne, int64_t total_rows, ill_dptr xh, ill_dptr y, int64_t y_stride, ill_stream stream);
+                          int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr y,
+                          int64_t y_stride, ill_stream stream);
 
 #ifdef __cplusplus
 }

@@ -1,9 +1,10 @@
 """The chunk's routed-expert product (tcgen05) against the CPU oracle.
 
-The oracle multiplies Q8_K activations with exact integer dots; the device
-multiplies the same dequantized values rounded to fp16 (weights and
-activations) with fp32 accumulation, so outputs agree to about 5e-4 of the
-largest output -- inside the 2e-3 the path is specified to.
+Both sides multiply the same integers exactly (the device as fp16 operands of
+tcgen05 MMAs, block by block) and scale each 256-wide block's sum by d_w * d_x
+in fp32, so the products agree to fp32 rounding; across the whole layer the
+only other difference is expf in the gate, whose last-place differences can
+move a quantized middle value by one step now and then.
 """
 import numpy as np
 import pytest
@@ -39,8 +40,8 @@ def _pool(d, ff, ne, gate_fmt, seed):
     (B.Q2_K, 384, 256, [128, 129, 0, 0, 3]),    # exact tile, tile + 1
     (B.IQ2_XXS, 200, 1024, [40]),               # weight rows not a multiple of the tile
 ])
-def test_mm_id_matches_float64_product(oracle, fmt, rows_w, cols, counts):
-    """One indexed product alone: Y = XH . dequant(W_e)^T against float64."""
+def test_mm_id_matches_oracle_rows(oracle, fmt, rows_w, cols, counts):
+    """One indexed product alone: each valid row of Y against the oracle's row dots."""
     ne = len(counts)
     rb = B.row_bytes(fmt, cols)
     w = B.synth_matrix(fmt, ne * rows_w, cols, seed=len(counts))
@@ -51,21 +52,30 @@ def test_mm_id_matches_float64_product(oracle, fmt, rows_w, cols, counts):
     total = sum(counts)
     rng = np.random.default_rng(1)
     x = rng.standard_normal((total, cols)).astype(np.float32)
-    xq, xd, _ = oracle.quantize_q8k(x)
+    xq, xd, bs = oracle.quantize_q8k(x)
+    dxq, dxd, dbs = to_dev(xq), to_dev(xd), to_dev(bs.astype(np.int16))  # named: they must outlive the launches
     xh = torch.empty(total, cols, dtype=torch.float16, device="cuda")
-    _lib.call("ill_act_f16", total, cols, to_dev(xq).data_ptr(), to_dev(xd).data_ptr(), 0, xh.data_ptr(), None)
-    xdeq = xq.reshape(total, cols).astype(np.float32) * np.repeat(xd, 256).reshape(total, cols)
-    assert np.array_equal(xh.cpu().numpy(), xdeq.astype(np.float16))
+    xe = torch.full((total, cols // 256, 64), 9.0, dtype=torch.float16, device="cuda")
+    _lib.call("ill_act_f16", total, cols, dxq.data_ptr(), dbs.data_ptr(), 0, xh.data_ptr(), xe.data_ptr(), None)
+    assert np.array_equal(xh.cpu().numpy().astype(np.int32), xq.reshape(total, cols))
+    xeh = xe.cpu().numpy()
+    assert np.array_equal(xeh[:, :, :16].astype(np.int32), bs.reshape(total, cols // 256, 16)) and (xeh[:, :, 16:] == 0).all()
     y = torch.full((total + 4, rows_w), 7.0, dtype=torch.float32, device="cuda")
     bases = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.int32)
-    _lib.call("ill_moe_mm_id", fmt, cols, rows_w, 0, ptrs.data_ptr(), to_dev(np.array(counts, np.int32)).data_ptr(),
-              to_dev(bases).data_ptr(), ne, total, xh.data_ptr(), y.data_ptr(), rows_w, None)
+    dcounts, dbases = to_dev(np.array(counts, np.int32)), to_dev(bases)
+    _lib.call("ill_moe_mm_id", fmt, cols, rows_w, 0, ptrs.data_ptr(), dcounts.data_ptr(), dbases.data_ptr(), ne, total,
+              xh.data_ptr(), xe.data_ptr(), dxd.data_ptr(), 0, y.data_ptr(), rows_w, None)
     got = y.cpu().numpy()
     assert (got[total:] == 7.0).all()
-    wf = oracle.dequant(fmt, w, ne * rows_w, cols).astype(np.float64).reshape(ne, rows_w, cols)
-    want = np.concatenate([xdeq[b:b + c].astype(np.float64) @ wf[e].T for e, (b, c) in enumerate(zip(bases, counts))])
+    want = np.empty((total, rows_w), np.float32)
+    for e, (b, c) in enumerate(zip(bases, counts)):
+        we = w[e * rows_w * rb:(e + 1) * rows_w * rb]
+        for r in range(b, b + c):
+            act = (xq[r * cols:(r + 1) * cols], xd[r * (cols // 256):(r + 1) * (cols // 256)],
+                   bs[r * (cols // 16):(r + 1) * (cols // 16)])
+            want[r] = oracle.matvec(fmt, we, rows_w, cols, act)[0]
     a, _ = rel_errors(got[:total], want)
-    assert a < 1e-3, a
+    assert a < 1e-5, a
 
 
 @pytest.mark.parametrize("d,ff,ne,nu,n,gate_fmt,clamp", [
@@ -85,4 +95,4 @@ def test_chunk_matches_oracle_small(oracle, d, ff, ne, nu, n, gate_fmt, clamp):
     want = np.stack([oracle.moe_routed(d, ff, gate_fmt, B.Q2_K, gate, up, down, norms[t], osel[t], ow[t], clamp, threads=4)
                      for t in range(n)])
     a, _ = rel_errors(got, want)
-    assert a < TOL_SPEC, a
+    assert a < TOL_SPEC and a < 2e-4, a
