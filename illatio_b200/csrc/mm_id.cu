@@ -137,13 +137,33 @@ __device__ __forceinline__ uint32_t h2_of(float a) {
   return *(const uint32_t*)&h;
 }
 
-// IQ2_XXS sub-block IB of the block at BLK: the 32 integers grid * sign * (2 LS + 1)
-// (at most 43 * 31: exact in fp16) as chunks 4*(ib&1) .. +3 of the row.  The block's
-// float part is d / 8 (src/avx2.lisp:77-110 takes the products this way).
-__device__ __forceinline__ void b_iq2xxs(const u8* blk, int ib, u8* tile, int row, const uint2* grid, const uint2* smask) {
-  uint32_t v[2];
-  ldg_words<2>(blk + 2 + 8 * ib, v);
-  const uint32_t idx = v[0], aux = v[1];
+// A thread's raw share of one block, prefetched a block ahead: half H of the block's quants (32
+// bytes: IQ2_XXS sub-blocks 4h..4h+3; Q2_K quant bytes 32h..32h+31), Q2_K's 8 scale bytes of that
+// half, and the block's fp16 scale(s).
+struct RawBlk { uint32_t w[8]; uint32_t s[2]; uint32_t dd; };
+
+template <int FMT>
+__device__ __forceinline__ void load_raw(RawBlk& r, const u8* blk, int h) {
+  if constexpr (FMT == ILL_IQ2_XXS) {
+    ldg_words<8>(blk + 2 + 32 * h, r.w);
+    r.dd = __ldg((const u16*)blk);
+    r.s[0] = r.s[1] = 0;
+  } else {
+    const uint4* q = (const uint4*)(blk + 16 + 32 * h);  // a block is 4-byte aligned; 16-byte loads need more
+    const uint32_t* q32 = (const uint32_t*)q;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r.w[i] = __ldg(q32 + i);
+    r.s[0] = __ldg((const uint32_t*)(blk + 8 * h));
+    r.s[1] = __ldg((const uint32_t*)(blk + 8 * h + 4));
+    r.dd = __ldg((const uint32_t*)(blk + 80));
+  }
+}
+
+// IQ2_XXS: one sub-block (IDX, AUX) as the 32 integers grid * sign * (2 LS + 1) (at most 43 * 31:
+// exact in fp16), chunks CB .. CB+3 of the row.  The block's float part is d / 8
+// (src/avx2.lisp:77-110 takes the products this way).
+__device__ __forceinline__ void b_iq2xxs(uint32_t idx, uint32_t aux, int cb, u8* tile, int row, const uint2* grid,
+                                         const uint2* smask) {
   const float ls = (float)(2 * (aux >> 28) + 1);
   const uint32_t s2 = h2_of(ls), bias = h2_of(-1152.0f * ls);  // (1024 + (b + 128)) * s - 1152 s = b * s
 #pragma unroll
@@ -153,43 +173,44 @@ __device__ __forceinline__ void b_iq2xxs(const u8* blk, int ib, u8* tile, int ro
     // signed bytes: (g ^ m) - m per byte; then + 128 to make them unsigned for the conversion
     const uint32_t lo = ((g.x ^ m.x) + (m.x & 0x01010101u)) ^ 0x80808080u;
     const uint32_t hi = ((g.y ^ m.y) + (m.y & 0x01010101u)) ^ 0x80808080u;
-    store_chunk(tile, row, 4 * (ib & 1) + l,
+    store_chunk(tile, row, cb + l,
                 make_uint4(hfma2(bytes_to_h2_1024(lo, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(lo, 0x4342), s2, bias),
                            hfma2(bytes_to_h2_1024(hi, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(hi, 0x4342), s2, bias)));
   }
 }
 
-// Q2_K: K step KS (0..3) of the block, the thread's half KK (shift k = 2*(ks&1) + kk): the 32
-// integers (scale & 15) * q (at most 45) as chunks 4*kk .. +3.
-__device__ __forceinline__ void b_q2k(const u8* blk, int ks, int kk, u8* tile, int row) {
-  const int h = ks >> 1, k = 2 * (ks & 1) + kk;
-  const uint32_t* q32 = (const uint32_t*)(blk + 16 + 32 * h);  // 32 bytes of quants, 4-byte aligned
-  const uint32_t sc2 = __ldg((const u16*)(blk + 8 * h + 2 * k));  // scale bytes 8h + 2k + half, half = 0, 1
+// Q2_K: K step JJ (0, 1) of the thread's half block: shifts k = 2 jj, 2 jj + 1; the 64 integers
+// (scale & 15) * q (at most 45) as the row's 8 chunks.
+__device__ __forceinline__ void b_q2k(const RawBlk& r, int jj, u8* tile, int row) {
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const float sc = (float)((sc2 >> (8 * half)) & 15u);
-    const uint32_t s2 = h2_of(sc), bias = h2_of(-1024.0f * sc);
+  for (int kk = 0; kk < 2; ++kk) {
+    const int k = 2 * jj + kk;
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const uint32_t w0 = (__ldg(q32 + 4 * half + 2 * c) >> (2 * k)) & 0x03030303u;
-      const uint32_t w1 = (__ldg(q32 + 4 * half + 2 * c + 1) >> (2 * k)) & 0x03030303u;
-      store_chunk(tile, row, 4 * kk + 2 * half + c,
-                  make_uint4(hfma2(bytes_to_h2_1024(w0, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w0, 0x4342), s2, bias),
-                             hfma2(bytes_to_h2_1024(w1, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w1, 0x4342), s2, bias)));
+    for (int half = 0; half < 2; ++half) {
+      const int sb = 2 * k + half;  // scale byte of the half block
+      const float sc = (float)((r.s[sb >> 2] >> (8 * (sb & 3))) & 15u);
+      const uint32_t s2 = h2_of(sc), bias = h2_of(-1024.0f * sc);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t w0 = (r.w[4 * half + 2 * c] >> (2 * k)) & 0x03030303u;
+        const uint32_t w1 = (r.w[4 * half + 2 * c + 1] >> (2 * k)) & 0x03030303u;
+        store_chunk(tile, row, 4 * kk + 2 * half + c,
+                    make_uint4(hfma2(bytes_to_h2_1024(w0, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w0, 0x4342), s2, bias),
+                               hfma2(bytes_to_h2_1024(w1, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w1, 0x4342), s2, bias)));
+      }
     }
   }
 }
-// Q2_K: the block's sixteen mins (scale >> 4), eight per thread, as chunk HALF of the "mins" tile
-__device__ __forceinline__ void b_q2k_mins(const u8* blk, int half, u8* tile, int row) {
-  const uint2 s = make_uint2(__ldg((const uint32_t*)(blk + 8 * half)), __ldg((const uint32_t*)(blk + 8 * half + 4)));
-  const uint32_t lo = (s.x >> 4) & 0x0f0f0f0fu, hi = (s.y >> 4) & 0x0f0f0f0fu;
+// Q2_K: the half block's eight mins (scale >> 4) as chunk H of the "mins" tile
+__device__ __forceinline__ void b_q2k_mins(const RawBlk& r, int h, u8* tile, int row) {
+  const uint32_t lo = (r.s[0] >> 4) & 0x0f0f0f0fu, hi = (r.s[1] >> 4) & 0x0f0f0f0fu;
   const uint32_t k1024 = 0xe400e400u;  // -1024 twice
-  uint32_t r[4];
-  r[0] = bytes_to_h2_1024(lo, 0x4140); r[1] = bytes_to_h2_1024(lo, 0x4342);
-  r[2] = bytes_to_h2_1024(hi, 0x4140); r[3] = bytes_to_h2_1024(hi, 0x4342);
+  uint32_t v[4];
+  v[0] = bytes_to_h2_1024(lo, 0x4140); v[1] = bytes_to_h2_1024(lo, 0x4342);
+  v[2] = bytes_to_h2_1024(hi, 0x4140); v[3] = bytes_to_h2_1024(hi, 0x4342);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) asm("add.rn.f16x2 %0, %0, %1;" : "+r"(r[i]) : "r"(k1024));
-  store_chunk(tile, row, half, make_uint4(r[0], r[1], r[2], r[3]));
+  for (int i = 0; i < 4; ++i) asm("add.rn.f16x2 %0, %0, %1;" : "+r"(v[i]) : "r"(k1024));
+  store_chunk(tile, row, h, make_uint4(v[0], v[1], v[2], v[3]));
 }
 
 // K steps per 256-wide block: four of the quants; for Q2_K a fifth whose A tile holds the
@@ -345,38 +366,52 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
 #pragma unroll
     for (int i = 0; i < 64; ++i) out[i] = 0.0f;
 
-    auto produce = [&](int kb) -> bool {
+    // Block KB's B tiles from CUR (its raw words, loaded a block ago); NXT gets block KB+1's.
+    // The thread's half H of the block is K steps 2h and 2h+1 (all 64 columns of its row).
+    auto produce = [&](int kb, const RawBlk& cur, RawBlk& nxt) -> bool {
       const int b = kb & 1;
+      if (kb + 1 < nkb && has_row) load_raw<FMT>(nxt, wrow + (long long)(kb + 1) * BB, half);
       if (kb >= 2) {  // the scales of block kb - 2 have been read by every drain warp
         bool w_ok = mbar_wait(&acc_free[b], (uint32_t)(kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI + 1);
         if (!__all_sync(0xffffffffu, w_ok)) return false;
       }
-      const u8* blk = wrow + (long long)kb * BB;
       if (half == 0) {
         float d = 0.0f, dmin = 0.0f;
-        if (has_row) {
-          if constexpr (FMT == ILL_IQ2_XXS) d = h2f((uint32_t)__ldg((const u16*)blk));
-          else { const uint32_t dd = __ldg((const uint32_t*)(blk + 80)); d = h2f(dd & 0xffff); dmin = h2f(dd >> 16); }
-        }
+        if (has_row) { d = h2f(cur.dd & 0xffff); dmin = h2f(cur.dd >> 16); }
         wsc[(b * 128 + row) * 2] = d;
         wsc[(b * 128 + row) * 2 + 1] = dmin;
       }
-      for (int j = 0; j < SPB; ++j) {
-        const int st = kb * SPB + j, s = st % MM_STAGES, use = st / MM_STAGES;
-        if (use > 0) {
-          bool w_ok = mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
-          if (!__all_sync(0xffffffffu, w_ok)) return false;
-        }
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int st = kb * SPB + 2 * half + jj, s = st % MM_STAGES, use = st / MM_STAGES;
+        bool w_ok = true;
+        if (use > 0) w_ok = mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
+        if (!__all_sync(0xffffffffu, w_ok)) return false;
         u8* tile = b_tiles + s * MM_TILE_BYTES;
         if (has_row) {
-          if constexpr (FMT == ILL_IQ2_XXS) b_iq2xxs(blk, 2 * j + half, tile, row, iq_grid, iq_smask);
-          else if (j < 4) b_q2k(blk, j, half, tile, row);
-          else b_q2k_mins(blk, half, tile, row);
+          if constexpr (FMT == ILL_IQ2_XXS) {
+            b_iq2xxs(cur.w[4 * jj], cur.w[4 * jj + 1], 0, tile, row, iq_grid, iq_smask);
+            b_iq2xxs(cur.w[4 * jj + 2], cur.w[4 * jj + 3], 4, tile, row, iq_grid, iq_smask);
+          } else {
+            b_q2k(cur, jj, tile, row);
+          }
         } else {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) store_chunk(tile, row, 4 * half + c, make_uint4(0, 0, 0, 0));
+          for (int c = 0; c < 8; ++c) store_chunk(tile, row, c, make_uint4(0, 0, 0, 0));
         }
         fence_async_smem();  // the tensor core reads the tile through the async proxy
+        __syncwarp();
+        if (lane < 2) mbar_arrive(&full_b[s]);  // lane 0 for the h = 0 lanes' stage, lane 1 for the h = 1 lanes'
+      }
+      if constexpr (SPB == 5) {
+        const int st = kb * SPB + 4, s = st % MM_STAGES, use = st / MM_STAGES;
+        bool w_ok = true;
+        if (use > 0) w_ok = mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
+        if (!__all_sync(0xffffffffu, w_ok)) return false;
+        u8* tile = b_tiles + s * MM_TILE_BYTES;
+        if (has_row) b_q2k_mins(cur, half, tile, row);
+        else store_chunk(tile, row, half, make_uint4(0, 0, 0, 0));
+        fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_b[s]);
       }
@@ -418,9 +453,15 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       return true;
     };
 
-    for (int kb = 0; kb < nkb && ok; ++kb) {
-      ok = produce(kb);
+    RawBlk r0, r1;
+    if (has_row) load_raw<FMT>(r0, wrow, half);
+    for (int kb = 0; kb < nkb && ok; kb += 2) {
+      ok = produce(kb, r0, r1);
       if (ok && kb >= 1) ok = drain(kb - 1);
+      if (ok && kb + 1 < nkb) {
+        ok = produce(kb + 1, r1, r0);
+        if (ok) ok = drain(kb);
+      }
     }
     if (ok) ok = drain(nkb - 1);
     if (ok && m < nvalid) {
