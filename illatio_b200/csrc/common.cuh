@@ -2,9 +2,9 @@
 //
 // Bulk asynchronous copies (cp.async.bulk) land raw GGUF bytes in shared
 // memory; an mbarrier per stage counts the bytes.  Every wait on an mbarrier is
-// bounded: after ILL_SPIN_LIMIT polls the waiter records a code in the device
-// status word and returns false, and the kernel unwinds without touching the
-// stage, so a lost copy can never hang the GPU.
+// bounded in time (ILL_WAIT_NS): a waiter that gives up records a code in the
+// device status word and returns false, and the kernel unwinds without touching
+// the stage, so a lost copy can never hang the GPU.
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -12,7 +12,7 @@
 
 #include "../../include/illatio_b200.h"
 
-#define ILL_SPIN_LIMIT (1u << 22)
+#define ILL_WAIT_NS 2000000000ull  // a wait on an mbarrier gives up after two seconds
 
 namespace ill {
 
@@ -41,22 +41,32 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// One poll: the thread may be suspended by the hardware for up to HINT_NS nanoseconds while the
+// phase is incomplete (it takes no issue slots meanwhile).
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and records CODE) when the phase never completes.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up ILL_WAIT_NS nanoseconds after it began.  Returns false (and records CODE in
+// the status word, first writer wins) when the phase never completes.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code) {
-  for (uint32_t i = 0; i < ILL_SPIN_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) __nanosleep(32);
+  if (mbar_try_wait(bar, parity, 0)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    if (mbar_try_wait(bar, parity, 20000)) return true;
+    if (global_ns() - t0 > ILL_WAIT_NS) break;
   }
   if (status) atomicCAS(status, 0u, code);
   return false;
@@ -76,46 +86,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 // prologue / wait until the previous kernel's memory is visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-
-// N consecutive 32-bit words starting at an arbitrarily aligned shared-memory
-// byte address: aligned loads of N+1 words, realigned with funnel shifts.
-template <int N>
-__device__ __forceinline__ void lds_words(uint32_t addr, uint32_t (&out)[N]) {
-  const uint32_t base = addr & ~3u, sh = (addr & 3u) * 8u;
-  uint32_t prev = lds32(base);
-#pragma unroll
-  for (int i = 0; i < N; ++i) {
-    uint32_t next = lds32(base + 4u * (i + 1));
-    out[i] = __funnelshift_r(prev, next, sh);
-    prev = next;
-  }
-}
 
 __device__ __forceinline__ float h2f(uint32_t bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
 

@@ -162,14 +162,16 @@ __device__ __forceinline__ void load_raw(RawBlk& r, const u8* blk, int h) {
 // IQ2_XXS: one sub-block (IDX, AUX) as the 32 integers grid * sign * (2 LS + 1) (at most 43 * 31:
 // exact in fp16), chunks CB .. CB+3 of the row.  The block's float part is d / 8
 // (src/avx2.lisp:77-110 takes the products this way).
+// GRID and SMASK point at this lane's copy of the tables (eight interleaved copies: entry e of
+// copy c at [8 e + c], so lanes that use different copies never meet in a bank).
 __device__ __forceinline__ void b_iq2xxs(uint32_t idx, uint32_t aux, int cb, u8* tile, int row, const uint2* grid,
                                          const uint2* smask) {
   const float ls = (float)(2 * (aux >> 28) + 1);
   const uint32_t s2 = h2_of(ls), bias = h2_of(-1152.0f * ls);  // (1024 + (b + 128)) * s - 1152 s = b * s
 #pragma unroll
   for (int l = 0; l < 4; ++l) {
-    const uint2 g = grid[(idx >> (8 * l)) & 0xff];
-    const uint2 m = smask[(aux >> (7 * l)) & 127];
+    const uint2 g = grid[8 * ((idx >> (8 * l)) & 0xff)];
+    const uint2 m = smask[8 * ((aux >> (7 * l)) & 127)];
     // signed bytes: (g ^ m) - m per byte; then + 128 to make them unsigned for the conversion
     const uint32_t lo = ((g.x ^ m.x) + (m.x & 0x01010101u)) ^ 0x80808080u;
     const uint32_t hi = ((g.y ^ m.y) + (m.y & 0x01010101u)) ^ 0x80808080u;
@@ -181,9 +183,10 @@ __device__ __forceinline__ void b_iq2xxs(uint32_t idx, uint32_t aux, int cb, u8*
 
 // Q2_K: K step JJ (0, 1) of the thread's half block: shifts k = 2 jj, 2 jj + 1; the 64 integers
 // (scale & 15) * q (at most 45) as the row's 8 chunks.
-__device__ __forceinline__ void b_q2k(const RawBlk& r, int jj, u8* tile, int row) {
+__device__ __forceinline__ void b_q2k(const RawBlk& r, int jj, int flip, u8* tile, int row) {
 #pragma unroll
-  for (int kk = 0; kk < 2; ++kk) {
+  for (int kk0 = 0; kk0 < 2; ++kk0) {
+    const int kk = kk0 ^ flip;  // the two lanes of a row write different halves of their tiles at any moment
     const int k = 2 * jj + kk;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -236,9 +239,9 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   uint64_t* acc_free = acc_full + 2;             // [2] the 8 drain warps read the buffer
   uint32_t* tmem_slot = (uint32_t*)(acc_free + 2);
   int* tile_info = (int*)(tmem_slot + 1);        // expert, row0, rows valid
-  float* wsc = (float*)(tail + 256);             // [2 buffers][128 rows][2]: d (and dmin) of the block
-  uint2* iq_grid = (uint2*)(tail + 256 + 2048);
-  uint2* iq_smask = iq_grid + 256;
+  float* wsc = (float*)(tail + 256);             // [2 buffers][2: d, dmin][128 rows] of the block
+  uint2* iq_grid = (uint2*)(tail + 256 + 2048);  // eight interleaved copies
+  uint2* iq_smask = iq_grid + 8 * 256;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nt = blockIdx.x;   // tile along the weights' rows
@@ -278,12 +281,12 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     mbar_fence_init();
   }
   if (FMT == ILL_IQ2_XXS) {
-    for (int i = tid; i < 256; i += MM_THREADS) {
-      const uint64_t g = ill_iq2xxs_grid[i];
+    for (int i = tid; i < 8 * 256; i += MM_THREADS) {
+      const uint64_t g = ill_iq2xxs_grid[i >> 3];
       iq_grid[i] = make_uint2((uint32_t)g, (uint32_t)(g >> 32));
     }
-    for (int i = tid; i < 128; i += MM_THREADS) {
-      const uint32_t sg = ill_ksigns_iq2xs[i];
+    for (int i = tid; i < 8 * 128; i += MM_THREADS) {
+      const uint32_t sg = ill_ksigns_iq2xs[i >> 3];
       uint32_t lo = 0, hi = 0;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -378,8 +381,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       if (half == 0) {
         float d = 0.0f, dmin = 0.0f;
         if (has_row) { d = h2f(cur.dd & 0xffff); dmin = h2f(cur.dd >> 16); }
-        wsc[(b * 128 + row) * 2] = d;
-        wsc[(b * 128 + row) * 2 + 1] = dmin;
+        wsc[b * 256 + row] = d;
+        wsc[b * 256 + 128 + row] = dmin;
       }
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) {
@@ -390,10 +393,13 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         u8* tile = b_tiles + s * MM_TILE_BYTES;
         if (has_row) {
           if constexpr (FMT == ILL_IQ2_XXS) {
-            b_iq2xxs(cur.w[4 * jj], cur.w[4 * jj + 1], 0, tile, row, iq_grid, iq_smask);
-            b_iq2xxs(cur.w[4 * jj + 2], cur.w[4 * jj + 3], 4, tile, row, iq_grid, iq_smask);
+            // the two lanes of a row write different halves of their (different) tiles at any moment: no bank meets
+            const uint32_t i0 = half ? cur.w[4 * jj + 2] : cur.w[4 * jj], a0 = half ? cur.w[4 * jj + 3] : cur.w[4 * jj + 1];
+            const uint32_t i1 = half ? cur.w[4 * jj] : cur.w[4 * jj + 2], a1 = half ? cur.w[4 * jj + 1] : cur.w[4 * jj + 3];
+            b_iq2xxs(i0, a0, 4 * half, tile, row, iq_grid + (lane & 7), iq_smask + (lane & 7));
+            b_iq2xxs(i1, a1, 4 - 4 * half, tile, row, iq_grid + (lane & 7), iq_smask + (lane & 7));
           } else {
-            b_q2k(cur, jj, tile, row);
+            b_q2k(cur, jj, half, tile, row);
           }
         } else {
 #pragma unroll
@@ -422,28 +428,38 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(kb / 2) & 1u, p.status, ST_MM_WAIT_ACC);
       if (!__all_sync(0xffffffffu, e_ok)) return false;
       tc_fence_after();
-      const float dx = tok >= 0 ? p.xd[tok * nkb + kb] : 0.0f;
-      const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * ACCS * MM_BN + 64 * chalf);
+      if (32 * q < nvalid) {  // a quarter of the tile with no valid row is not read
+        const float dx = tok >= 0 ? p.xd[tok * nkb + kb] : 0.0f;
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * ACCS * MM_BN + 64 * chalf);
+        const float4* wd = (const float4*)(wsc + b * 256 + 64 * chalf);
 #pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(t0 + c0, v);
-        if constexpr (FMT == ILL_IQ2_XXS) {
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(t0 + c0, v);
+          if constexpr (FMT == ILL_IQ2_XXS) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float dw = wsc[(b * 128 + 64 * chalf + c0 + i) * 2];
-            // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum; the 1/8 at the end
-            out[c0 + i] = __fadd_rn(out[c0 + i], __fmul_rn(__fmul_rn(dw, dx), __uint_as_float(v[i])));
-          }
-        } else {
-          uint32_t v2[32];
-          tmem_ld32(t0 + MM_BN + c0, v2);
+            for (int i = 0; i < 32; i += 4) {
+              const float4 dw = wd[(c0 + i) >> 2];
+              // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum; the 1/8 at the end
+              out[c0 + i] = fmaf(__fmul_rn(dw.x, dx), __uint_as_float(v[i]), out[c0 + i]);
+              out[c0 + i + 1] = fmaf(__fmul_rn(dw.y, dx), __uint_as_float(v[i + 1]), out[c0 + i + 1]);
+              out[c0 + i + 2] = fmaf(__fmul_rn(dw.z, dx), __uint_as_float(v[i + 2]), out[c0 + i + 2]);
+              out[c0 + i + 3] = fmaf(__fmul_rn(dw.w, dx), __uint_as_float(v[i + 3]), out[c0 + i + 3]);
+            }
+          } else {
+            uint32_t v2[32];
+            tmem_ld32(t0 + MM_BN + c0, v2);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float2 sc = *(const float2*)&wsc[(b * 128 + 64 * chalf + c0 + i) * 2];
-            // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
-            out[c0 + i] = __fadd_rn(out[c0 + i], __fsub_rn(__fmul_rn(__fmul_rn(dx, sc.x), __uint_as_float(v[i])),
-                                                           __fmul_rn(__fmul_rn(dx, sc.y), __uint_as_float(v2[i]))));
+            for (int i = 0; i < 32; i += 4) {
+              const float4 dw = wd[(c0 + i) >> 2], dm = wd[32 + ((c0 + i) >> 2)];
+              const float dws[4] = {dw.x, dw.y, dw.z, dw.w}, dms[4] = {dm.x, dm.y, dm.z, dm.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
+                const float t1 = fmaf(__fmul_rn(dx, dws[e]), __uint_as_float(v[i + e]), out[c0 + i + e]);
+                out[c0 + i + e] = fmaf(-__fmul_rn(dx, dms[e]), __uint_as_float(v2[i + e]), t1);
+              }
+            }
           }
         }
       }
@@ -606,7 +622,7 @@ extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dpt
   p.ne = ne;
   p.status = device_status_word();
   const int max_mtiles = (int)((total_rows + MM_BM - 1) / MM_BM) + ne;  // every expert may end with a partial tile
-  const size_t smem = 2 * MM_STAGES * MM_TILE_BYTES + 256 + 2048 + 2048 + 1024 + 1024;
+  const size_t smem = 2 * MM_STAGES * MM_TILE_BYTES + 256 + 2048 + 8 * 2048 + 8 * 1024 + 1024;  // tiles, barriers, scales, tables x 8, alignment
   const void* k = fmt == ILL_IQ2_XXS ? (const void*)mm_id_kernel<ILL_IQ2_XXS> : (const void*)mm_id_kernel<ILL_Q2_K>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e);
