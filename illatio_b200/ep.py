@@ -1,0 +1,215 @@
+"""Expert parallelism and the row-split output head over the GPUs of one box.
+
+The reference has no multi-GPU path of this kind: its second device holds a
+fixed "tier" of experts and exchanges activations through pinned host memory
+(D4-TIER-LAUNCH, src/cuda-ds4f.lisp:594-618), and "a model split across the
+two GPUs" is an open item (TODO.md:112).  Here:
+
+* Experts are placed expert-parallel: rank r of G holds experts
+  [r*E/G, (r+1)*E/G) resident in its HBM.  A chunk's tokens are split evenly by
+  position; every rank routes its own tokens, sends each (token, slot) row to
+  the rank that owns the chosen expert (all-to-all over NVLink, NCCL), runs the
+  indexed products for its experts, and sends the down rows back; the owner of
+  a token adds its slots' rows in slot order, as D4_MOE_SUM_ROWS does.
+  What travels is the token's Q8_K form (int8 quants, block scales, sums of 16:
+  1.14 bytes a value) -- fewer bytes than bf16 and exactly what the products
+  consume, so the result is bit-identical to the single-GPU path whatever G is.
+  The down rows come back as fp32 so that the slot-order sum is unchanged.
+* The output head (151936 rows) is split by rows; each rank multiplies its slice
+  into its part of the logits buffer and one in-place all-gather completes it.
+
+The index plumbing (which rows go where, where arrivals land) is written with
+plain torch ops on whatever device the tensors live on, so it is tested on CPU
+ranks over gloo; the products are the CUDA kernels.
+"""
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def expert_owner(experts, n_expert, world):
+    """Rank that holds each expert: contiguous blocks of n_expert / world."""
+    return experts // (n_expert // world)
+
+
+@dataclass
+class DispatchPlan:
+    """Where a rank's grouped rows go and where the rows it receives land."""
+    send_counts: list          # rows sent to each rank (host ints)
+    recv_counts: list          # rows received from each rank (host ints)
+    recv_expert_counts: torch.Tensor   # [world, local experts] rows from each source for each local expert
+    counts: torch.Tensor       # [local experts] rows per local expert (int32)
+    bases: torch.Tensor        # [local experts] first place of each local expert (int32)
+    place_to_recv: torch.Tensor  # [total recv rows] arrival index of the row at each place (int32)
+    recv_to_place: torch.Tensor  # inverse
+
+
+def plan_dispatch(local_counts, world, group=None):
+    """LOCAL_COUNTS: this rank's rows per expert (all E experts, int32/int64 on any
+    device), its rows already sorted by expert.  Exchanges the counts (one small
+    all-to-all) and builds the plan.  Rows arrive source by source, each source's
+    rows in expert order; an expert's rows are placed source after source, so the
+    place order is (expert, source, arrival order)."""
+    E = local_counts.numel()
+    per = E // world
+    dev = local_counts.device
+    lc = local_counts.to(torch.int64).view(world, per)          # [dest rank, its experts]
+    if world > 1:
+        rc = torch.empty_like(lc)                                # [source rank, my experts]
+        dist.all_to_all_single(rc, lc.contiguous(), group=group)
+    else:
+        rc = lc.clone()
+    send_counts = lc.sum(1).tolist()                             # host: the split sizes NCCL needs
+    recv_counts = rc.sum(1).tolist()
+    counts = rc.sum(0)                                           # per local expert
+    bases = torch.cumsum(counts, 0) - counts
+    # arrival index of (source s, expert e, i): offset of source s + offset of e inside s + i
+    src_off = torch.cumsum(rc.sum(1), 0) - rc.sum(1)             # [world]
+    in_src = torch.cumsum(rc, 1) - rc                            # [world, per]
+    # place of (s, e, i): bases[e] + rows of e from sources before s + i
+    before = torch.cumsum(rc, 0) - rc                            # [world, per]
+    total = int(sum(recv_counts))
+    seg_len = rc.reshape(-1)                                     # segments in arrival order: (s, e)
+    seg_arrival = (src_off[:, None] + in_src).reshape(-1)
+    seg_place = (bases[None, :] + before).reshape(-1)
+    seg_id = torch.repeat_interleave(torch.arange(seg_len.numel(), device=dev), seg_len, output_size=total)
+    within = torch.arange(total, device=dev) - torch.repeat_interleave(seg_arrival, seg_len, output_size=total)
+    recv_to_place = (seg_place[seg_id] + within).to(torch.int32)  # arrival order is seg_arrival + within = arange
+    place_to_recv = torch.empty(total, dtype=torch.int32, device=dev)
+    place_to_recv[recv_to_place.long()] = torch.arange(total, dtype=torch.int32, device=dev)
+    return DispatchPlan(send_counts, recv_counts, rc, counts.to(torch.int32), bases.to(torch.int32), place_to_recv,
+                        recv_to_place)
+
+
+def exchange_rows(rows, send_counts, recv_counts, group=None):
+    """All-to-all of ROWS [n, ...] split by SEND_COUNTS; returns the received rows."""
+    total = int(sum(recv_counts))
+    out = torch.empty((total,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_counts),
+                               input_split_sizes=list(send_counts), group=group)
+    else:
+        out.copy_(rows)
+    return out
+
+
+def moe_chunk_ep(norms, logits, nu, route_fn, quantize_fn, expert_fn, sum_fn, n_expert, group=None):
+    """One chunk's routed experts over the ranks of GROUP; every rank passes its
+    own tokens (NORMS [n, d], LOGITS [n, E]) and gets its tokens' output.
+
+    The compute steps are callables so that the same plumbing runs the CUDA
+    kernels on GPUs and stand-ins on CPU ranks in the tests:
+      route_fn(logits) -> sel [n, nu] int, w [n, nu] float
+      quantize_fn(norms) -> tuple of per-token row tensors (what a row carries)
+      expert_fn(payload rows (tuple, arrival order), wrow, plan) -> down rows [recv rows, d] in arrival order
+      sum_fn(down rows back in send order [n*nu, d], smap [n*nu]) -> [n, d]
+    """
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    n = norms.shape[0]
+    sel, w = route_fn(logits)
+    flat = sel.reshape(-1).to(torch.int64)
+    order = torch.argsort(flat, stable=True)                     # this rank's rows grouped by expert, token order inside
+    local_counts = torch.bincount(flat, minlength=n_expert)
+    plan = plan_dispatch(local_counts, world, group)
+    tok = (order // nu)
+    payload = quantize_fn(norms)
+    sent = tuple(exchange_rows(p[tok], plan.send_counts, plan.recv_counts, group) for p in payload)
+    wrow = exchange_rows(w.reshape(-1)[order].contiguous(), plan.send_counts, plan.recv_counts, group)
+    down = expert_fn(sent, wrow, plan)                           # arrival order
+    back = exchange_rows(down, plan.recv_counts, plan.send_counts, group)  # rows return in the order they were sent
+    smap = torch.empty_like(order)
+    smap[order] = torch.arange(order.numel(), device=order.device)
+    return sum_fn(back, smap.to(torch.int32), n)
+
+
+# ---- the CUDA steps ----------------------------------------------------------------------
+
+class CudaExperts:
+    """This rank's experts and the CUDA steps of moe_chunk_ep."""
+
+    def __init__(self, pool, nu, clamp, mode=2, scale=1.0):
+        self.pool, self.nu, self.clamp, self.mode, self.scale = pool, nu, clamp, mode, scale
+
+    def route(self, logits):
+        from . import cuda_ds4f as M
+        return M.route(logits, self.nu, mode=self.mode, scale=self.scale)
+
+    def quantize(self, norms):
+        from . import cuda_dense as D
+        n, d = norms.shape
+        act = D.make_qact(n * d, "q8k", device=norms.device)
+        D.quant_q8(norms.contiguous(), act)
+        return (act.xq.view(n, d), act.xs.view(n, d // 256), act.xsum.view(n, d // 16))
+
+    def experts(self, payload, wrow, plan):
+        """The local experts' gate / up / down on the arrived rows; rows back in arrival order."""
+        from . import _lib
+        from . import cuda_dense as D
+        from .blocks import Q2_K
+        from .cuda_ds4f import swiglu_w
+        pool = self.pool
+        d, ff = pool.d, pool.ff
+        xq, xd, xbs = (p.contiguous() for p in payload)
+        rows = xq.shape[0]
+        dev = xq.device
+        st = torch.cuda.current_stream().cuda_stream
+        f32 = dict(dtype=torch.float32, device=dev)
+        if rows == 0:
+            return torch.empty(0, d, **f32)
+        p2r = plan.place_to_recv
+        xh = torch.empty(rows, d, dtype=torch.float16, device=dev)
+        xe = torch.empty(rows, d // 256, 64, dtype=torch.float16, device=dev) if pool.gate_fmt == Q2_K else None
+        ptr = lambda t: 0 if t is None else t.data_ptr()  # noqa: E731
+        _lib.call("ill_act_f16", rows, d, ptr(xq), ptr(xbs), ptr(p2r), ptr(xh), ptr(xe), st)
+        g, u = torch.empty(rows, ff, **f32), torch.empty(rows, ff, **f32)
+        for add, y in ((0, g), (pool.gate_bytes, u)):
+            _lib.call("ill_moe_mm_id", pool.gate_fmt, d, ff, add, ptr(pool.ptrs_all), ptr(plan.counts), ptr(plan.bases),
+                      pool.n_expert, rows, ptr(xh), ptr(xe), ptr(xd), ptr(p2r), ptr(y), ff, st)
+        wplace = wrow[p2r.long()].contiguous()
+        mid = torch.empty(rows, ff, **f32)
+        swiglu_w(g, u, wplace, mid, ff, self.clamp)
+        midq = D.make_qact(rows * ff, "q8k", device=dev)
+        D.quant_q8(mid, midq)
+        mh = torch.empty(rows, ff, dtype=torch.float16, device=dev)
+        me = torch.empty(rows, ff // 256, 64, dtype=torch.float16, device=dev) if pool.down_fmt == Q2_K else None
+        _lib.call("ill_act_f16", rows, ff, ptr(midq.xq), ptr(midq.xsum), 0, ptr(mh), ptr(me), st)
+        down = torch.empty(rows, d, **f32)
+        _lib.call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(plan.counts),
+                  ptr(plan.bases), pool.n_expert, rows, ptr(mh), ptr(me), ptr(midq.xs), 0, ptr(down), d, st)
+        out = torch.empty_like(down)
+        _lib.call("ill_gather_rows", rows, d * 4, ptr(down), ptr(plan.recv_to_place), ptr(out), st)
+        return out
+
+    def sum(self, back, smap, n):
+        from . import _lib
+        d = back.shape[1]
+        moe = torch.empty(n, d, dtype=torch.float32, device=back.device)
+        _lib.call("ill_moe_sum", d, self.nu, n, back.data_ptr(), smap.data_ptr(), 0, moe.data_ptr(),
+                  torch.cuda.current_stream().cuda_stream)
+        return moe
+
+    def chunk(self, norms, logits, n_expert_total, group=None):
+        return moe_chunk_ep(norms, logits, self.nu, self.route, self.quantize, self.experts, self.sum, n_expert_total,
+                            group)
+
+
+def head_rows(rows, world, rank):
+    """[first, end) of the output head's rows on RANK: equal slices (the last takes the remainder)."""
+    per = rows // world
+    first = rank * per
+    return first, (rows if rank == world - 1 else first + per)
+
+
+def head_mul_allgather(w_slice, act, logits, rows, group=None):
+    """The row-split output head: this rank's slice of the matrix times the
+    (replicated) activations into its part of LOGITS, then one in-place all-gather.
+    ROWS must divide evenly by the world size."""
+    from . import cuda_dense as D
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    first, end = head_rows(rows, world, rank)
+    D.cmat_mul(w_slice, act, logits[first:end], 1)
+    if world > 1:
+        dist.all_gather_into_tensor(logits, logits[first:end], group=group)
+    return logits
