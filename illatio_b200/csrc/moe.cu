@@ -327,6 +327,80 @@ extern "C" int ill_moe_group(int64_t rows, int ne, int nu, ill_dptr sel, ill_dpt
   return launch_kernel((const void*)group_scatter_kernel, dim3((unsigned)((rows + 255) / 256)), dim3(256), 0, args, st);
 }
 
+// ---- grouping without any allocation ------------------------------------------------------
+// Scratch for ill_moe_group_static: a fixed array in the library's own device image, so a
+// caller that may not allocate needs to provide none.  Sized for ILL_GROUP_STATIC_MAX_ROWS
+// (token, slot) rows and ILL_GROUP_STATIC_MAX_EXPERTS experts: 4 bytes a row for the ranks plus
+// 4 bytes per (block of 1024 rows, expert) for the counts -- 384 KB, held by every GPU that
+// loads the library until the process exits.
+constexpr long long GROUP_STATIC_WORDS =
+    ILL_GROUP_STATIC_MAX_ROWS + (ILL_GROUP_STATIC_MAX_ROWS / GROUP_BLOCK) * ILL_GROUP_STATIC_MAX_EXPERTS;
+static __device__ __align__(256) unsigned g_group_scratch[GROUP_STATIC_WORDS];
+
+// The array's device address, looked up once per device (the name above is only a host-side
+// handle for the symbol; kernels must be given the address cudaGetSymbolAddress returns).
+static unsigned* group_scratch_address(int* rc) {
+  constexpr int MAX_DEV = 64;
+  static unsigned* addr[MAX_DEV] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEV) { *rc = cuda_fail(e == cudaSuccess ? cudaErrorInvalidDevice : e); return nullptr; }
+  unsigned* p = __atomic_load_n(&addr[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    e = cudaGetSymbolAddress((void**)&p, g_group_scratch);  // with DEV current: that device's copy
+    if (e != cudaSuccess || !p) { *rc = cuda_fail(e == cudaSuccess ? cudaErrorInvalidSymbol : e); return nullptr; }
+    __atomic_store_n(&addr[dev], p, __ATOMIC_RELEASE);
+  }
+  *rc = ILL_OK;
+  return p;
+}
+
+extern "C" int ill_moe_group_static(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w, ill_dptr counts, ill_dptr bases,
+                                    ill_dptr rmap, ill_dptr smap, ill_dptr wrow, ill_stream stream) {
+  if (rows < 0 || ne <= 0 || nu <= 0) return ILL_ERR_ARG;
+  if (rows > ILL_GROUP_STATIC_MAX_ROWS || ne > ILL_GROUP_STATIC_MAX_EXPERTS) return ILL_ERR_TOO_LARGE;
+  if (!check_ptr(sel, 4) || !check_ptr(counts, 4) || !check_ptr(bases, 4) || !check_ptr(rmap, 4) || !check_ptr(smap, 4) ||
+      (wrow & 3) || (wrow && !check_ptr(w, 4)))
+    return ILL_ERR_ARG;
+  int rc = ILL_OK;
+  unsigned* scratch = group_scratch_address(&rc);
+  if (!scratch) return rc;
+  long long nrows = rows;
+  int nblocks = (int)((rows + GROUP_BLOCK - 1) / GROUP_BLOCK);
+  if (nblocks < 1) nblocks = 1;
+  // every word the passes read is written first by an earlier pass of this same call (ranks
+  // for all ROWS, counts for all NBLOCKS x NE), so nothing left by a previous call is seen
+  unsigned* rank = scratch;
+  unsigned* block_counts = scratch + ILL_GROUP_STATIC_MAX_ROWS;
+  const unsigned* selp = (const unsigned*)(uintptr_t)sel;
+  unsigned *cp = (unsigned*)(uintptr_t)counts, *bp = (unsigned*)(uintptr_t)bases, *rp = (unsigned*)(uintptr_t)rmap,
+           *sp = (unsigned*)(uintptr_t)smap;
+  const float* wp = (const float*)(uintptr_t)w;
+  float* wr = (float*)(uintptr_t)wrow;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)32 * ne * 4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(group_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  {
+    void* args[] = {&nrows, &ne, &selp, &block_counts, &rank};
+    rc = launch_kernel((const void*)group_count_kernel, dim3(nblocks), dim3(GROUP_BLOCK), smem, args, st);
+    if (rc) return rc;
+  }
+  {
+    void* args[] = {&nblocks, &ne, &block_counts, &cp, &bp};
+    rc = launch_kernel((const void*)group_scan_kernel, dim3(1), dim3(512), 0, args, st);
+    if (rc) return rc;
+  }
+  if (rows == 0) return ILL_OK;
+  const unsigned* rk = rank;
+  const unsigned* bc = block_counts;
+  const unsigned* bs = bp;
+  void* args[] = {&nrows, &ne, &nu, &selp, &rk, &bc, &bs, &wp, &rp, &sp, &wr};
+  return launch_kernel((const void*)group_scatter_kernel, dim3((unsigned)((rows + 255) / 256)), dim3(256), 0, args, st);
+}
+
 extern "C" int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,
                                ill_stream stream) {
   if (rows < 0 || row_bytes <= 0 || (row_bytes & 15) || !check_ptr(src, 16) || !check_ptr(dst, 16) || !check_ptr(map, 4))

@@ -209,6 +209,27 @@ ILL_API int64_t ill_moe_group_scratch_bytes(int64_t rows, int ne);
 ILL_API int ill_moe_group(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w, ill_dptr scratch, ill_dptr counts,
                           ill_dptr bases, ill_dptr rmap, ill_dptr smap, ill_dptr wrow, ill_stream stream);
 
+/* ill_moe_group for callers that cannot allocate device memory and have none
+ * to spare for scratch: a host whose whole device budget is committed at
+ * start-up (illatio sizes its expert pool to all the memory that is left and
+ * records every allocation so it can give the device up and come back), or one
+ * that runs where an allocation would stall the device.  Same arguments and
+ * results as ill_moe_group, without SCRATCH: the scratch is a fixed array inside
+ * the library's device image (384 KB on every GPU that loads the library, held
+ * until the process exits).  No counterpart in the reference.
+ *   - Limits: ROWS <= ILL_GROUP_STATIC_MAX_ROWS and NE <=
+ *     ILL_GROUP_STATIC_MAX_EXPERTS, else ILL_ERR_TOO_LARGE.
+ *   - The first call on a device looks the array's address up (a host-side
+ *     query, no allocation); make that first call outside any stream capture.
+ *   - The function calls no cudaMalloc / cudaFree and no allocating routine.
+ *   - All calls on a device share the one array.  A call reads nothing an
+ *     earlier call left there, but two calls whose kernels overlap on the GPU
+ *     (different streams) race: keep them in one stream or order them. */
+#define ILL_GROUP_STATIC_MAX_ROWS 65536
+#define ILL_GROUP_STATIC_MAX_EXPERTS 512
+ILL_API int ill_moe_group_static(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w, ill_dptr counts, ill_dptr bases,
+                                 ill_dptr rmap, ill_dptr smap, ill_dptr wrow, ill_stream stream);
+
 /* DST row r = SRC row MAP[r], rows of ROW_BYTES bytes (a multiple of 16; both
  * 16-byte aligned).  Replaces d4_gather_rows (src/cuda/ds4f_chunk.cu:393). */
 ILL_API int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,
