@@ -178,6 +178,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-formats", action="store_true", help="skip the per-format sweep")
+    ap.add_argument("--no-moe", action="store_true", help="skip the mixture-of-experts layer")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -338,6 +339,62 @@ def main():
             del ms_
             torch.cuda.empty_cache()
 
+    # free the sweep's matrices before the mixture-of-experts layer is built
+    torch.cuda.empty_cache()
+
+    # ---- the sharded paths: (1) the row-split output head with an all-gather of the logits,
+    # (2) one DeepSeek-V4-Flash-shaped MoE layer (configs[3]) over a 4096-token chunk, experts placed
+    # expert-parallel (256 / N per rank), tokens split by position (strong scaling)
+    from illatio_b200 import ep as EP
+    from illatio_b200 import microbench_moe as MB
+    first_row, end_row = EP.head_rows(VOCAB, world, rank)
+    rb = B.row_bytes(HEAD[1], HIDDEN)
+    head_slice = D.CMat("head_slice", HEAD[1], end_row - first_row, HIDDEN, head.qs[first_row * rb:end_row * rb])
+    for _ in range(3):
+        EP.head_mul_allgather(head_slice, act_d, logits, VOCAB)
+    barrier()
+    e0.record()
+    for _ in range(20):
+        EP.head_mul_allgather(head_slice, act_d, logits, VOCAB)
+    e1.record()
+    barrier()
+    head_us = e0.elapsed_time(e1) * 1e3 / 20
+
+    moe = None
+    if not args.no_moe:
+        cfg = MB.CONFIGS["c4"]
+        n_tok = 4096
+        per = cfg["ne"] // world
+        pool = MB.make_pool(cfg, n_local=per, first=rank * per, seed=7, device=dev)
+        gm = torch.Generator(device=dev)
+        gm.manual_seed(11)  # the same chunk on every rank; each takes its slice of the tokens
+        norms_all = torch.randn(n_tok, cfg["d"], device=dev, generator=gm)
+        logits_all = MB.router_logits(cfg, n_tok, seed=12, device=dev)
+        lo, hi = rank * n_tok // world, (rank + 1) * n_tok // world
+        norms_l, logits_l = norms_all[lo:hi].contiguous(), logits_all[lo:hi].contiguous()
+        del norms_all, logits_all
+        ce = EP.CudaExperts(pool, cfg["nu"], 10.0)
+        for _ in range(2):
+            ce.chunk(norms_l, logits_l, cfg["ne"])
+        barrier()
+        reps = 5
+        e0.record()
+        for _ in range(reps):
+            ce.chunk(norms_l, logits_l, cfg["ne"])
+        e1.record()
+        barrier()
+        moe_ms = e0.elapsed_time(e1) / reps
+        mt = torch.tensor([moe_ms, head_us], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(mt, op=dist.ReduceOp.MAX)
+        moe_ms, head_us = mt.tolist()
+        flop = 2.0 * n_tok * cfg["nu"] * 3 * cfg["d"] * cfg["ff"]
+        moe = {"workload": "configs[3]: hidden 4096, 256 experts of FFN 2048, top-6, IQ2_XXS gate/up, Q2_K down; one 4096-token chunk through the routed experts",
+               "n_gpus": world, "experts_per_gpu": per, "tokens": n_tok, "ms_per_chunk": moe_ms,
+               "tok_per_s": n_tok / moe_ms * 1e3, "tflops": flop / moe_ms / 1e9, "scaling": "strong",
+               "exchange": "NCCL all-to-all of Q8_K rows out (1.14 B/value), fp32 rows back" if world > 1 else "none (one GPU)"}
+        del pool, ce
+
     status = D.device_status()
     tmax = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -367,6 +424,10 @@ def main():
                          "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                          "us_per_launch": glu_us, "algorithmic_bytes_per_launch": glu_bytes},
             "clocks": clocks, "formats": formats, "device_status": status,
+            "head_rowsplit": {"rows_per_gpu": end_row - first_row, "us_per_token": head_us,
+                              "GBps": B.matrix_bytes(HEAD[1], VOCAB, HIDDEN) / head_us / 1e3,
+                              "collective": "in-place all-gather of fp32 logits" if world > 1 else "none (one GPU)"},
+            "moe_prefill": moe,
         }
         if not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline_sample()

@@ -1,0 +1,81 @@
+"""Expert parallelism on GPUs.  With one GPU: the expert-parallel driver run as a
+world of one must give the single-GPU chunk driver's result bit for bit.  With
+two or more GPUs (run under a multi-GPU box): two ranks over NCCL against the
+one-rank result."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from illatio_b200 import blocks as B
+from illatio_b200 import cuda_dense as D
+from illatio_b200 import cuda_ds4f as M
+from illatio_b200 import cuda_ds4f_prefill as P
+from illatio_b200 import ep as EP
+from illatio_b200 import microbench_moe as MB
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CFG = dict(d=1024, ff=512, ne=8, nu=2, gate_fmt=B.IQ2_XXS, zipf=0.0)
+
+
+def test_world_of_one_equals_chunk_driver(cuda_lib):
+    pool = MB.make_pool(CFG, seed=3)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    n = 300
+    norms = torch.randn(n, CFG["d"], device="cuda", generator=g)
+    logits = torch.randn(n, CFG["ne"], device="cuda", generator=g)
+    sc = P.make_chunk_scratch(pool, n, CFG["nu"])
+    want = P.dk_ffn_routed_chunk(pool, norms, logits, CFG["nu"], 10.0, sc).clone()
+    got = EP.CudaExperts(pool, CFG["nu"], 10.0).chunk(norms, logits, CFG["ne"])
+    assert torch.equal(got, want)
+    assert D.device_status() == 0
+
+
+WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, %r)
+from illatio_b200 import blocks as B, ep as EP, microbench_moe as MB, cuda_ds4f_prefill as P, cuda_dense as D
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+cfg = dict(d=1024, ff=512, ne=8, nu=2, gate_fmt=B.IQ2_XXS, zipf=0.0)
+full = MB.make_pool(cfg, seed=3)
+per = cfg["ne"] // world
+mine = MB.make_pool(cfg, n_local=per, first=rank * per, seed=3)
+# the local experts must be the same bytes as the full layer's
+assert torch.equal(mine.pool.view(per, -1), full.pool.view(cfg["ne"], -1)[rank * per:(rank + 1) * per])
+g = torch.Generator(device="cuda").manual_seed(1)
+n = 300
+norms = torch.randn(n, cfg["d"], device="cuda", generator=g)
+logits = torch.randn(n, cfg["ne"], device="cuda", generator=g)
+sc = P.make_chunk_scratch(full, n, cfg["nu"])
+want = P.dk_ffn_routed_chunk(full, norms, logits, cfg["nu"], 10.0, sc)
+lo, hi = rank * n // world, (rank + 1) * n // world
+got = EP.CudaExperts(mine, cfg["nu"], 10.0).chunk(norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"])
+ok = torch.equal(got, want[lo:hi]) and D.device_status() == 0
+flag = torch.tensor([1 if ok else 0], device="cuda")
+dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+dist.destroy_process_group()
+sys.exit(0 if flag.item() == 1 else 1)
+"""
+
+
+def test_two_ranks_equal_one_rank(cuda_lib, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER % ROOT)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
