@@ -289,7 +289,6 @@ def main():
         torch.cuda.synchronize()
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---- the dominant kernel alone: the Q4_K gate/up product of every layer, back to back in one
     # CUDA graph (36 launches, each on its own layer's matrices: cold), timed with events
@@ -395,6 +394,7 @@ def main():
                "exchange": "NCCL all-to-all of Q8_K rows out (1.14 B/value), fp32 rows back" if world > 1 else "none (one GPU)"}
         del pool, ce
 
+    clocks = sampler.stop() if rank == 0 else None  # sampled over every timed region above
     status = D.device_status()
     tmax = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
