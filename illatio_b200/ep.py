@@ -87,8 +87,11 @@ def exchange_rows(rows, send_counts, recv_counts, group=None):
     total = int(sum(recv_counts))
     out = torch.empty((total,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_counts),
-                               input_split_sizes=list(send_counts), group=group)
+        # rows travel as bytes: NCCL has no 16-bit integer type, and the payload is opaque to it anyway
+        src = rows.contiguous().view(rows.shape[0], -1).view(torch.uint8)
+        dst = out.view(total, -1).view(torch.uint8)
+        dist.all_to_all_single(dst, src, output_split_sizes=list(recv_counts), input_split_sizes=list(send_counts),
+                               group=group)
     else:
         out.copy_(rows)
     return out

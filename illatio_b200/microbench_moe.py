@@ -32,10 +32,9 @@ def make_pool(cfg, n_local=None, first=0, seed=0, device="cuda"):
     pv = pool.view(n_local, slot)
     for i, (fmt, rows, cols, off, nb) in enumerate([(cfg["gate_fmt"], ff, d, 0, gb), (cfg["gate_fmt"], ff, d, gb, gb),
                                                     (B.Q2_K, d, ff, 2 * gb, db)]):
-        for e0 in range(0, n_local, 32):
-            k = min(32, n_local - e0)
-            m = B.synth_matrix_torch(fmt, k * rows, cols, seed=seed + 1000 * i + first + e0, device=device)
-            pv[e0:e0 + k, off:off + nb] = m.view(k, nb)
+        for e in range(n_local):  # one stream of numbers per (tensor, expert): any slice of the layer is the same bytes
+            m = B.synth_matrix_torch(fmt, rows, cols, seed=seed + 1000003 * i + first + e, device=device)
+            pv[e, off:off + nb] = m
     base = pool.data_ptr()
     ptrs = torch.tensor([base + e * slot for e in range(n_local)], dtype=torch.int64, device=device)
     return M.ExpertPool(d, ff, cfg["gate_fmt"], B.Q2_K, n_local, pool, slot, gb, db, ptrs)

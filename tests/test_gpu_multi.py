@@ -58,6 +58,8 @@ want = P.dk_ffn_routed_chunk(full, norms, logits, cfg["nu"], 10.0, sc)
 lo, hi = rank * n // world, (rank + 1) * n // world
 got = EP.CudaExperts(mine, cfg["nu"], 10.0).chunk(norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"])
 ok = torch.equal(got, want[lo:hi]) and D.device_status() == 0
+if not ok:
+    print("rank", rank, "max abs difference", (got - want[lo:hi]).abs().max().item(), file=sys.stderr)
 flag = torch.tensor([1 if ok else 0], device="cuda")
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 dist.destroy_process_group()
