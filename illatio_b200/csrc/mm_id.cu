@@ -9,13 +9,13 @@
 // reference's CPU kernels multiply, rounded once to fp16).  W_e is expert e's matrix
 // of raw IQ2_XXS or Q2_K blocks at ptrs[e] + add.
 //
-// One CTA computes a 128 (rows of X) x 128 (rows of W_e) tile, K in steps of 64:
+// A persistent grid (a CTA per SM) walks 128 (rows of X) x 128 (rows of W_e) tiles, K in steps of 64:
 //   warp 0      one lane issues the TMA loads of the X tile (128-byte swizzle)
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128x128x16, fp16 in,
 //               fp32 accumulate) and commits each stage back to the producers
-//   warps 2-5   dequantize W_e's blocks straight into the swizzled shared-memory operand
-//               tile (one weight row per thread), then read the accumulators back
-//               (tcgen05.ld) and store the tile's valid rows
+//   warps 2-17  turn W_e's blocks into the swizzled shared-memory operand tile (four threads a
+//               weight row, one K step each), and drain the accumulators block by block
+//               (tcgen05.ld), scaling each block's sum; then store the tile's valid rows
 // Every mbarrier wait is bounded; on a time-out the kernel records a code in the status
 // word, skips what depends on the wait, frees its tensor memory and returns.
 //
@@ -30,7 +30,8 @@
 namespace ill {
 
 constexpr int MM_BM = 128, MM_BN = 128, MM_BK = 64, MM_STAGES = 6;
-constexpr int MM_THREADS = 320;                        // TMA warp, MMA warp, 8 dequantize / drain warps
+constexpr int MM_THREADS = 576;                        // TMA warp, MMA warp, 16 dequantize / drain warps
+constexpr int MM_DQ_WARPS = 16;
 constexpr uint32_t MM_TILE_BYTES = MM_BM * MM_BK * 2;  // 16 KB, A or B
 
 struct MmParams {
@@ -137,76 +138,80 @@ __device__ __forceinline__ uint32_t h2_of(float a) {
   return *(const uint32_t*)&h;
 }
 
-// A thread's raw share of one block, prefetched a block ahead: half H of the block's quants (32
-// bytes: IQ2_XXS sub-blocks 4h..4h+3; Q2_K quant bytes 32h..32h+31), Q2_K's 8 scale bytes of that
-// half, and the block's fp16 scale(s).
-struct RawBlk { uint32_t w[8]; uint32_t s[2]; uint32_t dd; };
+// A thread's raw share of one block, prefetched a block ahead.  Thread (row, j) makes K step j
+// (64 columns) of its row: IQ2_XXS sub-blocks 2j and 2j+1 (16 bytes); Q2_K the 32 quant bytes of
+// half j/2, the four scale bytes of shifts 2(j&1) and 2(j&1)+1, and (j < 2) the eight scale
+// bytes of half j for the mins; and the block's fp16 scale(s).
+struct RawBlk { uint32_t w[8]; uint32_t s; uint32_t m[2]; uint32_t dd; };
 
 template <int FMT>
-__device__ __forceinline__ void load_raw(RawBlk& r, const u8* blk, int h) {
+__device__ __forceinline__ void load_raw(RawBlk& r, const u8* blk, int j) {
   if constexpr (FMT == ILL_IQ2_XXS) {
-    ldg_words<8>(blk + 2 + 32 * h, r.w);
+    uint32_t v[4];
+    ldg_words<4>(blk + 2 + 16 * j, v);
+    r.w[0] = v[0]; r.w[1] = v[1]; r.w[2] = v[2]; r.w[3] = v[3];
     r.dd = __ldg((const u16*)blk);
-    r.s[0] = r.s[1] = 0;
   } else {
-    const uint4* q = (const uint4*)(blk + 16 + 32 * h);  // a block is 4-byte aligned; 16-byte loads need more
-    const uint32_t* q32 = (const uint32_t*)q;
+    const uint32_t* q32 = (const uint32_t*)(blk + 16 + 32 * (j >> 1));  // a block is 4-byte aligned
 #pragma unroll
     for (int i = 0; i < 8; ++i) r.w[i] = __ldg(q32 + i);
-    r.s[0] = __ldg((const uint32_t*)(blk + 8 * h));
-    r.s[1] = __ldg((const uint32_t*)(blk + 8 * h + 4));
+    r.s = __ldg((const uint32_t*)(blk + 8 * (j >> 1) + 4 * (j & 1)));
+    if (j < 2) { r.m[0] = __ldg((const uint32_t*)(blk + 8 * j)); r.m[1] = __ldg((const uint32_t*)(blk + 8 * j + 4)); }
     r.dd = __ldg((const uint32_t*)(blk + 80));
   }
 }
 
-// IQ2_XXS: one sub-block (IDX, AUX) as the 32 integers grid * sign * (2 LS + 1) (at most 43 * 31:
-// exact in fp16), chunks CB .. CB+3 of the row.  The block's float part is d / 8
-// (src/avx2.lisp:77-110 takes the products this way).
-// GRID and SMASK point at this lane's copy of the tables (eight interleaved copies: entry e of
-// copy c at [8 e + c], so lanes that use different copies never meet in a bank).
-__device__ __forceinline__ void b_iq2xxs(uint32_t idx, uint32_t aux, int cb, u8* tile, int row, const uint2* grid,
+// The four lanes of a row write the same row of four different tiles; each starts ROT = 2j chunks
+// further round the row, so that at any moment they touch different banks.
+//
+// IQ2_XXS: the K step's 64 integers grid * sign * (2 LS + 1) (at most 43 * 31: exact in fp16).  The
+// block's float part is d / 8 (src/avx2.lisp:77-110 takes the products this way).  GRID and SMASK
+// point at this lane's copy of the tables (eight interleaved copies: entry e of copy c at [8 e + c]).
+__device__ __forceinline__ void b_iq2xxs(const RawBlk& r, int rot, u8* tile, int row, const uint2* grid,
                                          const uint2* smask) {
-  const float ls = (float)(2 * (aux >> 28) + 1);
-  const uint32_t s2 = h2_of(ls), bias = h2_of(-1152.0f * ls);  // (1024 + (b + 128)) * s - 1152 s = b * s
+  const float ls0 = (float)(2 * (r.w[1] >> 28) + 1), ls1 = (float)(2 * (r.w[3] >> 28) + 1);
+  // (1024 + (b + 128)) * s - 1152 s = b * s
+  const uint32_t s20 = h2_of(ls0), bias0 = h2_of(-1152.0f * ls0), s21 = h2_of(ls1), bias1 = h2_of(-1152.0f * ls1);
 #pragma unroll
-  for (int l = 0; l < 4; ++l) {
+  for (int i = 0; i < 8; ++i) {
+    const int c = (i + rot) & 7, sb = c >> 2, l = c & 3;
+    const uint32_t idx = sb ? r.w[2] : r.w[0], aux = sb ? r.w[3] : r.w[1];
+    const uint32_t s2 = sb ? s21 : s20, bias = sb ? bias1 : bias0;
     const uint2 g = grid[8 * ((idx >> (8 * l)) & 0xff)];
     const uint2 m = smask[8 * ((aux >> (7 * l)) & 127)];
     // signed bytes: (g ^ m) - m per byte; then + 128 to make them unsigned for the conversion
     const uint32_t lo = ((g.x ^ m.x) + (m.x & 0x01010101u)) ^ 0x80808080u;
     const uint32_t hi = ((g.y ^ m.y) + (m.y & 0x01010101u)) ^ 0x80808080u;
-    store_chunk(tile, row, cb + l,
+    store_chunk(tile, row, c,
                 make_uint4(hfma2(bytes_to_h2_1024(lo, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(lo, 0x4342), s2, bias),
                            hfma2(bytes_to_h2_1024(hi, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(hi, 0x4342), s2, bias)));
   }
 }
 
-// Q2_K: K step JJ (0, 1) of the thread's half block: shifts k = 2 jj, 2 jj + 1; the 64 integers
-// (scale & 15) * q (at most 45) as the row's 8 chunks.
-__device__ __forceinline__ void b_q2k(const RawBlk& r, int jj, int flip, u8* tile, int row) {
+// Q2_K: K step j of the block: shifts k = 2(j&1) + kk, kk = 0, 1; the 64 integers (scale & 15) * q
+// (at most 45); chunk 4 kk + 2 half + c holds bytes 16 half + 8 c .. +7 of the 32 at shift k.
+__device__ __forceinline__ void b_q2k(const RawBlk& r, int j, u8* tile, int row) {
 #pragma unroll
-  for (int kk0 = 0; kk0 < 2; ++kk0) {
-    const int kk = kk0 ^ flip;  // the two lanes of a row write different halves of their tiles at any moment
-    const int k = 2 * jj + kk;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int sb = 2 * k + half;  // scale byte of the half block
-      const float sc = (float)((r.s[sb >> 2] >> (8 * (sb & 3))) & 15u);
-      const uint32_t s2 = h2_of(sc), bias = h2_of(-1024.0f * sc);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const uint32_t w0 = (r.w[4 * half + 2 * c] >> (2 * k)) & 0x03030303u;
-        const uint32_t w1 = (r.w[4 * half + 2 * c + 1] >> (2 * k)) & 0x03030303u;
-        store_chunk(tile, row, 4 * kk + 2 * half + c,
-                    make_uint4(hfma2(bytes_to_h2_1024(w0, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w0, 0x4342), s2, bias),
-                               hfma2(bytes_to_h2_1024(w1, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w1, 0x4342), s2, bias)));
-      }
-    }
+  for (int pi = 0; pi < 4; ++pi) {
+    const int cp = (pi + j) & 3, kk = cp >> 1, half = cp & 1;  // pairs of chunks, rotated by j
+    const int k = 2 * (j & 1) + kk;
+    const float sc = (float)((r.s >> (8 * (2 * kk + half))) & 15u);
+    const uint32_t s2 = h2_of(sc), bias = h2_of(-1024.0f * sc);
+    const uint32_t q0 = half ? r.w[4] : r.w[0], q1 = half ? r.w[5] : r.w[1], q2 = half ? r.w[6] : r.w[2],
+                   q3 = half ? r.w[7] : r.w[3];
+    const uint32_t w0 = (q0 >> (2 * k)) & 0x03030303u, w1 = (q1 >> (2 * k)) & 0x03030303u;
+    const uint32_t w2 = (q2 >> (2 * k)) & 0x03030303u, w3 = (q3 >> (2 * k)) & 0x03030303u;
+    store_chunk(tile, row, 2 * cp,
+                make_uint4(hfma2(bytes_to_h2_1024(w0, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w0, 0x4342), s2, bias),
+                           hfma2(bytes_to_h2_1024(w1, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w1, 0x4342), s2, bias)));
+    store_chunk(tile, row, 2 * cp + 1,
+                make_uint4(hfma2(bytes_to_h2_1024(w2, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w2, 0x4342), s2, bias),
+                           hfma2(bytes_to_h2_1024(w3, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w3, 0x4342), s2, bias)));
   }
 }
-// Q2_K: the half block's eight mins (scale >> 4) as chunk H of the "mins" tile
+// Q2_K: half H's eight mins (scale >> 4) as chunk H of the "mins" tile
 __device__ __forceinline__ void b_q2k_mins(const RawBlk& r, int h, u8* tile, int row) {
-  const uint32_t lo = (r.s[0] >> 4) & 0x0f0f0f0fu, hi = (r.s[1] >> 4) & 0x0f0f0f0fu;
+  const uint32_t lo = (r.m[0] >> 4) & 0x0f0f0f0fu, hi = (r.m[1] >> 4) & 0x0f0f0f0fu;
   const uint32_t k1024 = 0xe400e400u;  // -1024 twice
   uint32_t v[4];
   v[0] = bytes_to_h2_1024(lo, 0x4140); v[1] = bytes_to_h2_1024(lo, 0x4342);
@@ -238,19 +243,18 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   uint64_t* acc_full = empty + MM_STAGES;        // [2] a block's MMAs completed
   uint64_t* acc_free = acc_full + 2;             // [2] the 8 drain warps read the buffer
   uint32_t* tmem_slot = (uint32_t*)(acc_free + 2);
-  int* tile_info = (int*)(tmem_slot + 1);        // expert, row0, rows valid
   float* wsc = (float*)(tail + 256);             // [2 buffers][2: d, dmin][128 rows] of the block
-  uint2* iq_grid = (uint2*)(tail + 256 + 2048);  // eight interleaved copies
+  int* tile_first = (int*)(tail + 256 + 2048);   // [ne + 1] first row tile of each expert; the total
+  uint2* iq_grid = (uint2*)(tail + 256 + 2048 + 2304);  // eight interleaved copies
   uint2* iq_smask = iq_grid + 8 * 256;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nt = blockIdx.x;   // tile along the weights' rows
-  const int mt = blockIdx.y;   // running index of 128-row tiles over all experts
 
-  // which expert does this row tile belong to?  (warp 0 scans the counts)
+  // ---- once per CTA: the experts' row tiles counted (first tile of each expert, in shared memory),
+  // barriers, tables, tensor memory.  The CTA then walks tiles blockIdx.x, + gridDim.x, ...
   if (warp == 0) {
-    int before = 0, found = -1, row0 = 0, nvalid = 0;
-    for (int e0 = 0; e0 < p.ne && found < 0; e0 += 32) {
+    int before = 0;
+    for (int e0 = 0; e0 < p.ne; e0 += 32) {
       const int e = e0 + lane;
       const int c = e < p.ne ? (int)p.counts[e] : 0;
       const int tiles = (c + MM_BM - 1) / MM_BM;
@@ -260,24 +264,14 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         const int v = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += v;
       }
-      const int excl = before + incl - tiles;
-      const bool mine = mt >= excl && mt < excl + tiles;
-      const unsigned who = __ballot_sync(0xffffffffu, mine);
-      if (who) {
-        const int src = __ffs(who) - 1;
-        found = __shfl_sync(0xffffffffu, e, src);
-        const int m_in = mt - __shfl_sync(0xffffffffu, excl, src);
-        const int cnt = __shfl_sync(0xffffffffu, c, src);
-        row0 = (int)p.bases[found] + m_in * MM_BM;
-        nvalid = min(MM_BM, cnt - m_in * MM_BM);
-      }
+      if (e < p.ne) tile_first[e] = before + incl - tiles;
       before += __shfl_sync(0xffffffffu, incl, 31);
     }
-    if (lane == 0) { tile_info[0] = found; tile_info[1] = row0; tile_info[2] = nvalid; }
+    if (lane == 0) tile_first[p.ne] = before;  // row tiles in all
   }
   if (tid == 32) {
-    for (int s = 0; s < MM_STAGES; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 8); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_free[b], 8); }
+    for (int s = 0; s < MM_STAGES; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], MM_DQ_WARPS); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_free[b], MM_DQ_WARPS); }
     mbar_fence_init();
   }
   if (FMT == ILL_IQ2_XXS) {
@@ -296,9 +290,6 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       iq_smask[i] = make_uint2(lo, hi);
     }
   }
-  __syncthreads();
-  const int expert = tile_info[0], row0 = tile_info[1], nvalid = tile_info[2];
-  if (expert < 0) return;  // past the last row tile: nothing allocated, nothing in flight
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -306,20 +297,40 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   const int nkb = p.ncols / 256;
-  const int nsteps = nkb * SPB;
-  const u8* wexp = (const u8*)(uintptr_t)p.ptrs[expert] + p.add;
+  const int ntn = (p.nrows + MM_BN - 1) / MM_BN;
+  const int ntiles = tile_first[p.ne] * ntn;  // weight-row tiles vary fastest: CTAs running together share X
   bool ok = true;
+
+  // tile index -> expert, first row of X, valid rows, weight-row tile
+  auto locate = [&](int tile, int& expert, int& row0, int& nvalid, int& nt) {
+    const int mt = tile / ntn;
+    nt = tile - mt * ntn;
+    int lo = 0, hi = p.ne - 1;  // the last expert whose first tile is <= mt and that has tiles
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (tile_first[mid] <= mt) lo = mid; else hi = mid - 1;
+    }
+    expert = lo;
+    const int m_in = mt - tile_first[lo];
+    row0 = (int)p.bases[lo] + m_in * MM_BM;
+    nvalid = min(MM_BM, (int)p.counts[lo] - m_in * MM_BM);
+  };
 
   if (warp == 0) {
     // ---- TMA producer of the X tiles
     if (lane == 0) {
-      for (int st = 0; st < nsteps; ++st) {
-        const int s = st % MM_STAGES, use = st / MM_STAGES;
-        if (use > 0 && !mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY)) { ok = false; break; }
-        const int kb = st / SPB, j = st - kb * SPB;
-        mbar_expect_tx(&full_a[s], MM_TILE_BYTES);
-        if (j < 4) tma_load_2d(a_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &full_a[s]);
-        else tma_load_2d(a_tiles + s * MM_TILE_BYTES, &emap, kb * MM_BK, row0, &full_a[s]);  // the sums of 16
+      int g_st = 0;  // stages issued so far by this CTA
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        int expert, row0, nvalid, nt;
+        locate(tile, expert, row0, nvalid, nt);
+        for (int st = 0; st < nkb * SPB; ++st, ++g_st) {
+          const int s = g_st % MM_STAGES, use = g_st / MM_STAGES;
+          if (use > 0 && !mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY)) { ok = false; break; }
+          const int kb = st / SPB, j = st - kb * SPB;
+          mbar_expect_tx(&full_a[s], MM_TILE_BYTES);
+          if (j < 4) tma_load_2d(a_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &full_a[s]);
+          else tma_load_2d(a_tiles + s * MM_TILE_BYTES, &emap, kb * MM_BK, row0, &full_a[s]);  // the sums of 16
+        }
       }
     }
   } else if (warp == 1) {
@@ -327,171 +338,185 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     if (lane == 0) {
       // fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
       const uint32_t idesc = (1u << 4) | ((uint32_t)(MM_BN >> 3) << 17) | ((uint32_t)(MM_BM >> 4) << 24);
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int b = kb & 1;
-        if (kb >= 2 && !mbar_wait(&acc_free[b], (uint32_t)(kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d1 = tmem_base + (uint32_t)(b * ACCS * MM_BN);
-        for (int j = 0; j < SPB; ++j) {
-          const int st = kb * SPB + j, s = st % MM_STAGES;
-          const uint32_t par = (uint32_t)(st / MM_STAGES) & 1u;
-          if (!mbar_wait(&full_a[s], par, p.status, ST_MM_WAIT_FULL) ||
-              !mbar_wait(&full_b[s], par, p.status, ST_MM_WAIT_FULL + 1)) { ok = false; break; }
+      int g_st = 0, g_kb = 0;  // stages and blocks consumed so far by this CTA
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
+          const int b = g_kb & 1;
+          if (g_kb >= 2 && !mbar_wait(&acc_free[b], (uint32_t)(g_kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t ad = umma_desc(a_tiles + s * MM_TILE_BYTES), bd = umma_desc(b_tiles + s * MM_TILE_BYTES);
-          if (j < 4) {
+          const uint32_t d1 = tmem_base + (uint32_t)(b * ACCS * MM_BN);
+          for (int j = 0; j < SPB; ++j, ++g_st) {
+            const int s = g_st % MM_STAGES;
+            const uint32_t par = (uint32_t)(g_st / MM_STAGES) & 1u;
+            if (!mbar_wait(&full_a[s], par, p.status, ST_MM_WAIT_FULL) ||
+                !mbar_wait(&full_b[s], par, p.status, ST_MM_WAIT_FULL + 1)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t ad = umma_desc(a_tiles + s * MM_TILE_BYTES), bd = umma_desc(b_tiles + s * MM_TILE_BYTES);
+            if (j < 4) {
 #pragma unroll
-            for (int k = 0; k < MM_BK / 16; ++k)  // 32 bytes further along K inside the swizzle atom each time
-              umma_f16(d1, ad + 2 * k, bd + 2 * k, idesc, (j | k) ? 1u : 0u);
-          } else {
-            umma_f16(d1 + MM_BN, ad, bd, idesc, 0u);  // mins x sums of 16: one K = 16 product
+              for (int k = 0; k < MM_BK / 16; ++k)  // 32 bytes further along K inside the swizzle atom each time
+                umma_f16(d1, ad + 2 * k, bd + 2 * k, idesc, (j | k) ? 1u : 0u);
+            } else {
+              umma_f16(d1 + MM_BN, ad, bd, idesc, 0u);  // mins x sums of 16: one K = 16 product
+            }
+            umma_commit(&empty[s]);  // frees the stage when these MMAs are done
           }
-          umma_commit(&empty[s]);  // frees the stage when these MMAs are done
+          if (ok) umma_commit(&acc_full[b]);
         }
-        if (ok) umma_commit(&acc_full[b]);
       }
     }
   } else {
-    // ---- warps 2..9: the weights' integer parts into the B tiles; the accumulators drained block by
-    // block with the block's float scales; the final store
-    const int t = tid - 64;                        // 0..255
-    const int row = t >> 1, half = t & 1;          // weight row in the tile, half of each K step
-    const int n = nt * MM_BN + row;
-    const bool has_row = n < p.nrows;
-    const u8* wrow = wexp + (long long)(has_row ? n : 0) * p.row_bytes;
+    // ---- warps 2..17: the weights' integer parts into the B tiles; the accumulators drained block by
+    // block with the block's float scales; the tile's store
+    const int t = tid - 64;                        // 0..511
+    const int row = t >> 2, j = t & 3;             // weight row in the tile, K step of each block
     constexpr int BB = FMT == ILL_IQ2_XXS ? 66 : 84;
     const int q = warp & 3;                        // TMEM lanes 32q .. 32q+31 are this warp's
     const int m = q * 32 + lane;                   // accumulator row
-    const int chalf = (warp - 2) >> 2;             // columns 64*chalf .. +63
-    const long long place = (long long)row0 + m;
-    const long long tok = place < p.total_rows ? (p.map ? (long long)p.map[place] : place) : -1;
-    float out[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) out[i] = 0.0f;
+    const int cq = (warp - 2) >> 2;                // columns 32*cq .. +31
+    int g_st = 0, g_kb = 0;                        // stages / blocks produced so far by this CTA
+    int d_kb = 0;                                  // blocks drained so far
+    // per tile
+    bool has_row = false;
+    const u8* wrow = nullptr;
+    int nvalid = 0;
+    long long tok = -1;
+    float out[32];
 
-    // Block KB's B tiles from CUR (its raw words, loaded a block ago); NXT gets block KB+1's.
-    // The thread's half H of the block is K steps 2h and 2h+1 (all 64 columns of its row).
+    // Block KB's B tiles from CUR (its raw words, loaded a block ago); NXT gets the next block's.
     auto produce = [&](int kb, const RawBlk& cur, RawBlk& nxt) -> bool {
-      const int b = kb & 1;
-      if (kb + 1 < nkb && has_row) load_raw<FMT>(nxt, wrow + (long long)(kb + 1) * BB, half);
-      if (kb >= 2) {  // the scales of block kb - 2 have been read by every drain warp
-        bool w_ok = mbar_wait(&acc_free[b], (uint32_t)(kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI + 1);
+      const int b = g_kb & 1;
+      if (kb + 1 < nkb && has_row) load_raw<FMT>(nxt, wrow + (long long)(kb + 1) * BB, j);
+      if (g_kb >= 2) {  // the scales two blocks back have been read by every drain warp
+        bool w_ok = mbar_wait(&acc_free[b], (uint32_t)(g_kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI + 1);
         if (!__all_sync(0xffffffffu, w_ok)) return false;
       }
-      if (half == 0) {
+      if (j == 0) {
         float d = 0.0f, dmin = 0.0f;
         if (has_row) { d = h2f(cur.dd & 0xffff); dmin = h2f(cur.dd >> 16); }
         wsc[b * 256 + row] = d;
         wsc[b * 256 + 128 + row] = dmin;
       }
-#pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        const int st = kb * SPB + 2 * half + jj, s = st % MM_STAGES, use = st / MM_STAGES;
+      {
+        const int st = g_st + j, s = st % MM_STAGES, use = st / MM_STAGES;
         bool w_ok = true;
         if (use > 0) w_ok = mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
         if (!__all_sync(0xffffffffu, w_ok)) return false;
         u8* tile = b_tiles + s * MM_TILE_BYTES;
         if (has_row) {
-          if constexpr (FMT == ILL_IQ2_XXS) {
-            // the two lanes of a row write different halves of their (different) tiles at any moment: no bank meets
-            const uint32_t i0 = half ? cur.w[4 * jj + 2] : cur.w[4 * jj], a0 = half ? cur.w[4 * jj + 3] : cur.w[4 * jj + 1];
-            const uint32_t i1 = half ? cur.w[4 * jj] : cur.w[4 * jj + 2], a1 = half ? cur.w[4 * jj + 1] : cur.w[4 * jj + 3];
-            b_iq2xxs(i0, a0, 4 * half, tile, row, iq_grid + (lane & 7), iq_smask + (lane & 7));
-            b_iq2xxs(i1, a1, 4 - 4 * half, tile, row, iq_grid + (lane & 7), iq_smask + (lane & 7));
-          } else {
-            b_q2k(cur, jj, half, tile, row);
-          }
+          if constexpr (FMT == ILL_IQ2_XXS) b_iq2xxs(cur, 2 * j, tile, row, iq_grid + (lane & 7), iq_smask + (lane & 7));
+          else b_q2k(cur, j, tile, row);
         } else {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) store_chunk(tile, row, c, make_uint4(0, 0, 0, 0));
+          for (int c = 0; c < 8; ++c) store_chunk(tile, row, (c + 2 * j) & 7, make_uint4(0, 0, 0, 0));
         }
         fence_async_smem();  // the tensor core reads the tile through the async proxy
         __syncwarp();
-        if (lane < 2) mbar_arrive(&full_b[s]);  // lane 0 for the h = 0 lanes' stage, lane 1 for the h = 1 lanes'
+        if (lane < 4) mbar_arrive(&full_b[s]);  // lane j for the stage the K-step-j lanes wrote
       }
       if constexpr (SPB == 5) {
-        const int st = kb * SPB + 4, s = st % MM_STAGES, use = st / MM_STAGES;
+        const int st = g_st + 4, s = st % MM_STAGES, use = st / MM_STAGES;
         bool w_ok = true;
         if (use > 0) w_ok = mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
         if (!__all_sync(0xffffffffu, w_ok)) return false;
         u8* tile = b_tiles + s * MM_TILE_BYTES;
-        if (has_row) b_q2k_mins(cur, half, tile, row);
-        else store_chunk(tile, row, half, make_uint4(0, 0, 0, 0));
+        if (j < 2) {
+          if (has_row) b_q2k_mins(cur, j, tile, row);
+          else store_chunk(tile, row, j, make_uint4(0, 0, 0, 0));
+        }
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_b[s]);
       }
+      g_st += SPB;
+      ++g_kb;
       return true;
     };
+    // Block KB of the current tile (the D_KB-th block of this CTA) out of tensor memory into OUT.
     auto drain = [&](int kb) -> bool {
-      const int b = kb & 1;
-      bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(kb / 2) & 1u, p.status, ST_MM_WAIT_ACC);
+      const int b = d_kb & 1;
+      bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC);
       if (!__all_sync(0xffffffffu, e_ok)) return false;
       tc_fence_after();
       if (32 * q < nvalid) {  // a quarter of the tile with no valid row is not read
         const float dx = tok >= 0 ? p.xd[tok * nkb + kb] : 0.0f;
-        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * ACCS * MM_BN + 64 * chalf);
-        const float4* wd = (const float4*)(wsc + b * 256 + 64 * chalf);
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * ACCS * MM_BN + 32 * cq);
+        const float4* wd = (const float4*)(wsc + b * 256 + 32 * cq);
+        uint32_t v[32];
+        tmem_ld32(t0, v);
+        if constexpr (FMT == ILL_IQ2_XXS) {
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(t0 + c0, v);
-          if constexpr (FMT == ILL_IQ2_XXS) {
+          for (int i = 0; i < 32; i += 4) {
+            const float4 dw = wd[i >> 2];
+            // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum; the 1/8 at the end
+            out[i] = fmaf(__fmul_rn(dw.x, dx), __uint_as_float(v[i]), out[i]);
+            out[i + 1] = fmaf(__fmul_rn(dw.y, dx), __uint_as_float(v[i + 1]), out[i + 1]);
+            out[i + 2] = fmaf(__fmul_rn(dw.z, dx), __uint_as_float(v[i + 2]), out[i + 2]);
+            out[i + 3] = fmaf(__fmul_rn(dw.w, dx), __uint_as_float(v[i + 3]), out[i + 3]);
+          }
+        } else {
+          // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins; the sums first,
+          // then the mins through the same registers
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const float4 dw = wd[(c0 + i) >> 2];
-              // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum; the 1/8 at the end
-              out[c0 + i] = fmaf(__fmul_rn(dw.x, dx), __uint_as_float(v[i]), out[c0 + i]);
-              out[c0 + i + 1] = fmaf(__fmul_rn(dw.y, dx), __uint_as_float(v[i + 1]), out[c0 + i + 1]);
-              out[c0 + i + 2] = fmaf(__fmul_rn(dw.z, dx), __uint_as_float(v[i + 2]), out[c0 + i + 2]);
-              out[c0 + i + 3] = fmaf(__fmul_rn(dw.w, dx), __uint_as_float(v[i + 3]), out[c0 + i + 3]);
-            }
-          } else {
-            uint32_t v2[32];
-            tmem_ld32(t0 + MM_BN + c0, v2);
+          for (int i = 0; i < 32; i += 4) {
+            const float4 dw = wd[i >> 2];
+            out[i] = fmaf(__fmul_rn(dx, dw.x), __uint_as_float(v[i]), out[i]);
+            out[i + 1] = fmaf(__fmul_rn(dx, dw.y), __uint_as_float(v[i + 1]), out[i + 1]);
+            out[i + 2] = fmaf(__fmul_rn(dx, dw.z), __uint_as_float(v[i + 2]), out[i + 2]);
+            out[i + 3] = fmaf(__fmul_rn(dx, dw.w), __uint_as_float(v[i + 3]), out[i + 3]);
+          }
+          tmem_ld32(t0 + MM_BN, v);
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const float4 dw = wd[(c0 + i) >> 2], dm = wd[32 + ((c0 + i) >> 2)];
-              const float dws[4] = {dw.x, dw.y, dw.z, dw.w}, dms[4] = {dm.x, dm.y, dm.z, dm.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
-                const float t1 = fmaf(__fmul_rn(dx, dws[e]), __uint_as_float(v[i + e]), out[c0 + i + e]);
-                out[c0 + i + e] = fmaf(-__fmul_rn(dx, dms[e]), __uint_as_float(v2[i + e]), t1);
-              }
-            }
+          for (int i = 0; i < 32; i += 4) {
+            const float4 dm = wd[32 + (i >> 2)];
+            out[i] = fmaf(-__fmul_rn(dx, dm.x), __uint_as_float(v[i]), out[i]);
+            out[i + 1] = fmaf(-__fmul_rn(dx, dm.y), __uint_as_float(v[i + 1]), out[i + 1]);
+            out[i + 2] = fmaf(-__fmul_rn(dx, dm.z), __uint_as_float(v[i + 2]), out[i + 2]);
+            out[i + 3] = fmaf(-__fmul_rn(dx, dm.w), __uint_as_float(v[i + 3]), out[i + 3]);
           }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_free[b]);
+      ++d_kb;
       return true;
     };
 
-    RawBlk r0, r1;
-    if (has_row) load_raw<FMT>(r0, wrow, half);
-    for (int kb = 0; kb < nkb && ok; kb += 2) {
-      ok = produce(kb, r0, r1);
-      if (ok && kb >= 1) ok = drain(kb - 1);
-      if (ok && kb + 1 < nkb) {
-        ok = produce(kb + 1, r1, r0);
-        if (ok) ok = drain(kb);
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      int expert, row0, nt;
+      locate(tile, expert, row0, nvalid, nt);
+      const int n = nt * MM_BN + row;
+      has_row = n < p.nrows;
+      wrow = (const u8*)(uintptr_t)p.ptrs[expert] + p.add + (long long)(has_row ? n : 0) * p.row_bytes;
+      const long long place = (long long)row0 + m;
+      tok = place < p.total_rows ? (p.map ? (long long)p.map[place] : place) : -1;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) out[i] = 0.0f;
+      RawBlk r0, r1;
+      if (has_row) load_raw<FMT>(r0, wrow, j);
+      for (int kb = 0; kb < nkb && ok; kb += 2) {
+        ok = produce(kb, r0, r1);
+        if (ok && kb >= 1) ok = drain(kb - 1);
+        if (ok && kb + 1 < nkb) {
+          ok = produce(kb + 1, r1, r0);
+          if (ok) ok = drain(kb);
+        }
       }
-    }
-    if (ok) ok = drain(nkb - 1);
-    if (ok && m < nvalid) {
-      float* yrow = p.y + place * p.y_stride + (long long)nt * MM_BN + 64 * chalf;
-      const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
+      if (ok) ok = drain(nkb - 1);
+      if (ok && m < nvalid) {
+        float* yrow = p.y + place * p.y_stride + (long long)nt * MM_BN + 32 * cq;
+        const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
 #pragma unroll
-      for (int j = 0; j < 64; j += 4) {
-        const int n0 = nt * MM_BN + 64 * chalf + j;
-        if (n0 + 3 < p.nrows) {
-          *(float4*)(yrow + j) = make_float4(out[j] * fin, out[j + 1] * fin, out[j + 2] * fin, out[j + 3] * fin);
-        } else {
+        for (int jj = 0; jj < 32; jj += 4) {
+          const int n0 = nt * MM_BN + 32 * cq + jj;
+          if (n0 + 3 < p.nrows) {
+            *(float4*)(yrow + jj) = make_float4(out[jj] * fin, out[jj + 1] * fin, out[jj + 2] * fin, out[jj + 3] * fin);
+          } else {
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
-            if (n0 + jj < p.nrows) yrow[j + jj] = out[j + jj] * fin;
+            for (int e = 0; e < 4; ++e)
+              if (n0 + e < p.nrows) yrow[jj + e] = out[jj + e] * fin;
+          }
         }
       }
     }
@@ -621,14 +646,19 @@ extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dpt
   p.y_stride = y_stride;
   p.ne = ne;
   p.status = device_status_word();
-  const int max_mtiles = (int)((total_rows + MM_BM - 1) / MM_BM) + ne;  // every expert may end with a partial tile
-  const size_t smem = 2 * MM_STAGES * MM_TILE_BYTES + 256 + 2048 + 8 * 2048 + 8 * 1024 + 1024;  // tiles, barriers, scales, tables x 8, alignment
+  const long long max_tiles = ((total_rows + MM_BM - 1) / MM_BM + ne) * ((nrows + MM_BN - 1) / MM_BN);  // an upper bound
+  // tiles, barriers, scales, the experts' first tiles, tables x 8, alignment
+  const size_t smem = 2 * MM_STAGES * MM_TILE_BYTES + 256 + 2048 + 2304 + 8 * 2048 + 8 * 1024 + 1024;
+  if (ne > 512) return ILL_ERR_TOO_LARGE;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   const void* k = fmt == ILL_IQ2_XXS ? (const void*)mm_id_kernel<ILL_IQ2_XXS> : (const void*)mm_id_kernel<ILL_Q2_K>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e);
   void* args[] = {&xmap, &emap, &p};
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((nrows + MM_BN - 1) / MM_BN, max_mtiles, 1);
+  cfg.gridDim = dim3((unsigned)(max_tiles < sms ? max_tiles : sms), 1, 1);  // persistent: a CTA an SM, each walks tiles
   cfg.blockDim = dim3(MM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = (cudaStream_t)stream;
