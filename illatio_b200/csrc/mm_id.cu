@@ -13,9 +13,11 @@
 //   warp 0      one lane issues the TMA loads of the X tile (128-byte swizzle)
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128x128x16, fp16 in,
 //               fp32 accumulate) and commits each stage back to the producers
-//   warps 2-17  turn W_e's blocks into the swizzled shared-memory operand tile (four threads a
-//               weight row, one K step each), and drain the accumulators block by block
-//               (tcgen05.ld), scaling each block's sum; then store the tile's valid rows
+//   warps 2-3   copy W_e's raw blocks into a ring in shared memory (cp.async, coalesced)
+//   warps 4-11  drain the accumulators block by block (tcgen05.ld), scaling each block's integer
+//               sums by the block's float scales; then store the tile's valid rows
+//   warps 12-19 turn the raw blocks into the swizzled shared-memory operand tiles (two threads a
+//               weight row, two K steps each)
 // Every mbarrier wait is bounded; on a time-out the kernel records a code in the status
 // word, skips what depends on the wait, frees its tensor memory and returns.
 //
@@ -29,9 +31,12 @@
 
 namespace ill {
 
-constexpr int MM_BM = 128, MM_BN = 128, MM_BK = 64, MM_STAGES = 6;
-constexpr int MM_THREADS = 576;                        // TMA warp, MMA warp, 16 dequantize / drain warps
-constexpr int MM_DQ_WARPS = 16;
+constexpr int MM_BM = 128, MM_BN = 128, MM_BK = 64;
+constexpr int MM_NA = 6;                               // stages of the ring of X tiles
+constexpr int MM_RS = 3;                               // stages of the ring of raw weight blocks
+constexpr int MM_DR_WARPS = 8, MM_DQ_WARPS = 8, MM_LD_WARPS = 2;  // drain, dequantize, raw-load warps
+constexpr int MM_THREADS = 32 * (2 + MM_LD_WARPS + MM_DR_WARPS + MM_DQ_WARPS);  // + the TMA warp and the MMA warp
+constexpr int MM_FULL_B = 8;                           // arrivals that complete a B stage
 constexpr uint32_t MM_TILE_BYTES = MM_BM * MM_BK * 2;  // 16 KB, A or B
 
 struct MmParams {
@@ -109,21 +114,6 @@ __device__ __forceinline__ void store_chunk(u8* tile, int row, int c, uint4 v) {
   *(uint4*)(tile + (row >> 3) * 1024 + (row & 7) * 128 + ((c ^ (row & 7)) << 4)) = v;
 }
 
-// N words at P (any alignment), from global memory
-template <int N>
-__device__ __forceinline__ void ldg_words(const u8* p, uint32_t (&out)[N]) {
-  const uint32_t mis = (uint32_t)(uintptr_t)p & 3u;
-  const uint32_t* b = (const uint32_t*)(p - mis);
-  const uint32_t sh = mis * 8u;
-  uint32_t prev = __ldg(b);
-#pragma unroll
-  for (int i = 0; i < N; ++i) {
-    const uint32_t next = __ldg(b + i + 1);
-    out[i] = __funnelshift_r(prev, next, sh);
-    prev = next;
-  }
-}
-
 // two unsigned bytes (byte positions B0, B1 of V) as the halves 1024 + byte
 __device__ __forceinline__ uint32_t bytes_to_h2_1024(uint32_t v, uint32_t sel) {
   return __byte_perm(v, 0x64646464u, sel);
@@ -138,80 +128,81 @@ __device__ __forceinline__ uint32_t h2_of(float a) {
   return *(const uint32_t*)&h;
 }
 
-// A thread's raw share of one block, prefetched a block ahead.  Thread (row, j) makes K step j
-// (64 columns) of its row: IQ2_XXS sub-blocks 2j and 2j+1 (16 bytes); Q2_K the 32 quant bytes of
-// half j/2, the four scale bytes of shifts 2(j&1) and 2(j&1)+1, and (j < 2) the eight scale
-// bytes of half j for the mins; and the block's fp16 scale(s).
-struct RawBlk { uint32_t w[8]; uint32_t s; uint32_t m[2]; uint32_t dd; };
+// 4 bytes global -> shared, asynchronously (both addresses 4-byte aligned)
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+// BAR gets one arrival (counted in its initial count) once this thread's earlier cp.async have landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <int FMT>
-__device__ __forceinline__ void load_raw(RawBlk& r, const u8* blk, int j) {
-  if constexpr (FMT == ILL_IQ2_XXS) {
-    uint32_t v[4];
-    ldg_words<4>(blk + 2 + 16 * j, v);
-    r.w[0] = v[0]; r.w[1] = v[1]; r.w[2] = v[2]; r.w[3] = v[3];
-    r.dd = __ldg((const u16*)blk);
-  } else {
-    const uint32_t* q32 = (const uint32_t*)(blk + 16 + 32 * (j >> 1));  // a block is 4-byte aligned
-#pragma unroll
-    for (int i = 0; i < 8; ++i) r.w[i] = __ldg(q32 + i);
-    r.s = __ldg((const uint32_t*)(blk + 8 * (j >> 1) + 4 * (j & 1)));
-    if (j < 2) { r.m[0] = __ldg((const uint32_t*)(blk + 8 * j)); r.m[1] = __ldg((const uint32_t*)(blk + 8 * j + 4)); }
-    r.dd = __ldg((const uint32_t*)(blk + 80));
-  }
+// the small integer N (twice, as two halves) without a conversion: 1024 + N has the bits 0x6400 | N
+__device__ __forceinline__ uint32_t small_h2(uint32_t n) {
+  uint32_t v = 0x64006400u | (n * 0x10001u);
+  asm("add.rn.f16x2 %0, %0, %1;" : "+r"(v) : "r"(0xe400e400u));  // - 1024
+  return v;
+}
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
 
-// The four lanes of a row write the same row of four different tiles; each starts ROT = 2j chunks
-// further round the row, so that at any moment they touch different banks.
+// A warp's lanes are 32 consecutive weight rows writing the same 16-byte chunk index: the swizzle
+// spreads every eight rows over all the banks, so the stores do not collide.
 //
-// IQ2_XXS: the K step's 64 integers grid * sign * (2 LS + 1) (at most 43 * 31: exact in fp16).  The
-// block's float part is d / 8 (src/avx2.lisp:77-110 takes the products this way).  GRID and SMASK
-// point at this lane's copy of the tables (eight interleaved copies: entry e of copy c at [8 e + c]).
-__device__ __forceinline__ void b_iq2xxs(const RawBlk& r, int rot, u8* tile, int row, const uint2* grid,
-                                         const uint2* smask) {
-  const float ls0 = (float)(2 * (r.w[1] >> 28) + 1), ls1 = (float)(2 * (r.w[3] >> 28) + 1);
-  // (1024 + (b + 128)) * s - 1152 s = b * s
-  const uint32_t s20 = h2_of(ls0), bias0 = h2_of(-1152.0f * ls0), s21 = h2_of(ls1), bias1 = h2_of(-1152.0f * ls1);
+// IQ2_XXS: one K step = two sub-blocks W[0..3] = (indices, signs + scale) x 2; the 64 integers
+// grid * sign * (2 LS + 1) (at most 43 * 31: exact in fp16).  The block's float part is d / 8
+// (src/avx2.lisp:77-110 takes the products this way).  GRID and SMASK point at this lane's copy of
+// the tables (eight interleaved copies: entry e of copy c at [8 e + c]).
+__device__ __forceinline__ void b_iq2xxs(const uint32_t* w, u8* tile, int row, const uint2* grid, const uint2* smask) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int c = (i + rot) & 7, sb = c >> 2, l = c & 3;
-    const uint32_t idx = sb ? r.w[2] : r.w[0], aux = sb ? r.w[3] : r.w[1];
-    const uint32_t s2 = sb ? s21 : s20, bias = sb ? bias1 : bias0;
-    const uint2 g = grid[8 * ((idx >> (8 * l)) & 0xff)];
-    const uint2 m = smask[8 * ((aux >> (7 * l)) & 127)];
-    // signed bytes: (g ^ m) - m per byte; then + 128 to make them unsigned for the conversion
-    const uint32_t lo = ((g.x ^ m.x) + (m.x & 0x01010101u)) ^ 0x80808080u;
-    const uint32_t hi = ((g.y ^ m.y) + (m.y & 0x01010101u)) ^ 0x80808080u;
-    store_chunk(tile, row, c,
-                make_uint4(hfma2(bytes_to_h2_1024(lo, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(lo, 0x4342), s2, bias),
-                           hfma2(bytes_to_h2_1024(hi, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(hi, 0x4342), s2, bias)));
+  for (int sb = 0; sb < 2; ++sb) {
+    const uint32_t idx = w[2 * sb], aux = w[2 * sb + 1];
+    // (1024 + (b + 128)) * s - 1152 s = b * s
+    const uint32_t s2 = small_h2(2 * (aux >> 28) + 1), bias = hmul2(s2, 0xe480e480u /* -1152 */);
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      const uint2 g = grid[8 * ((idx >> (8 * l)) & 0xff)];
+      const uint2 m = smask[8 * ((aux >> (7 * l)) & 127)];
+      // signed bytes: (g ^ m) - m per byte; then + 128 to make them unsigned for the conversion
+      const uint32_t lo = ((g.x ^ m.x) + (m.x & 0x01010101u)) ^ 0x80808080u;
+      const uint32_t hi = ((g.y ^ m.y) + (m.y & 0x01010101u)) ^ 0x80808080u;
+      store_chunk(tile, row, 4 * sb + l,
+                  make_uint4(hfma2(bytes_to_h2_1024(lo, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(lo, 0x4342), s2, bias),
+                             hfma2(bytes_to_h2_1024(hi, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(hi, 0x4342), s2, bias)));
+    }
   }
 }
 
-// Q2_K: K step j of the block: shifts k = 2(j&1) + kk, kk = 0, 1; the 64 integers (scale & 15) * q
-// (at most 45); chunk 4 kk + 2 half + c holds bytes 16 half + 8 c .. +7 of the 32 at shift k.
-__device__ __forceinline__ void b_q2k(const RawBlk& r, int j, u8* tile, int row) {
+// Q2_K: the K step of half HALF128 (its 32 quant bytes Q) at shifts k = 2h + kk, kk = 0, 1; the 64
+// integers (scale & 15) * q (at most 45); chunk 4 kk + 2 half16 + c holds bytes 16 half16 + 8 c .. +7
+// at shift k.  SC4: the K step's four scale bytes (shift-major, then the half of 16).
+__device__ __forceinline__ void b_q2k(const uint32_t* q, uint32_t sc4, int h, u8* tile, int row) {
 #pragma unroll
-  for (int pi = 0; pi < 4; ++pi) {
-    const int cp = (pi + j) & 3, kk = cp >> 1, half = cp & 1;  // pairs of chunks, rotated by j
-    const int k = 2 * (j & 1) + kk;
-    const float sc = (float)((r.s >> (8 * (2 * kk + half))) & 15u);
-    const uint32_t s2 = h2_of(sc), bias = h2_of(-1024.0f * sc);
-    const uint32_t q0 = half ? r.w[4] : r.w[0], q1 = half ? r.w[5] : r.w[1], q2 = half ? r.w[6] : r.w[2],
-                   q3 = half ? r.w[7] : r.w[3];
-    const uint32_t w0 = (q0 >> (2 * k)) & 0x03030303u, w1 = (q1 >> (2 * k)) & 0x03030303u;
-    const uint32_t w2 = (q2 >> (2 * k)) & 0x03030303u, w3 = (q3 >> (2 * k)) & 0x03030303u;
-    store_chunk(tile, row, 2 * cp,
-                make_uint4(hfma2(bytes_to_h2_1024(w0, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w0, 0x4342), s2, bias),
-                           hfma2(bytes_to_h2_1024(w1, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w1, 0x4342), s2, bias)));
-    store_chunk(tile, row, 2 * cp + 1,
-                make_uint4(hfma2(bytes_to_h2_1024(w2, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w2, 0x4342), s2, bias),
-                           hfma2(bytes_to_h2_1024(w3, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w3, 0x4342), s2, bias)));
+  for (int kk = 0; kk < 2; ++kk) {
+    const int k = 2 * h + kk;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const uint32_t scn = (sc4 >> (8 * (2 * kk + half))) & 15u;
+      const uint32_t s2 = small_h2(scn), bias = hmul2(s2, 0xe400e400u /* -1024 */);
+      const uint32_t w0 = (q[4 * half] >> (2 * k)) & 0x03030303u, w1 = (q[4 * half + 1] >> (2 * k)) & 0x03030303u;
+      const uint32_t w2 = (q[4 * half + 2] >> (2 * k)) & 0x03030303u, w3 = (q[4 * half + 3] >> (2 * k)) & 0x03030303u;
+      const int cp = 2 * kk + half;
+      store_chunk(tile, row, 2 * cp,
+                  make_uint4(hfma2(bytes_to_h2_1024(w0, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w0, 0x4342), s2, bias),
+                             hfma2(bytes_to_h2_1024(w1, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w1, 0x4342), s2, bias)));
+      store_chunk(tile, row, 2 * cp + 1,
+                  make_uint4(hfma2(bytes_to_h2_1024(w2, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w2, 0x4342), s2, bias),
+                             hfma2(bytes_to_h2_1024(w3, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w3, 0x4342), s2, bias)));
+    }
   }
 }
-// Q2_K: half H's eight mins (scale >> 4) as chunk H of the "mins" tile
-__device__ __forceinline__ void b_q2k_mins(const RawBlk& r, int h, u8* tile, int row) {
-  const uint32_t lo = (r.m[0] >> 4) & 0x0f0f0f0fu, hi = (r.m[1] >> 4) & 0x0f0f0f0fu;
+// Q2_K: eight mins (scale bytes M0, M1 >> 4) as chunk H of the "mins" tile
+__device__ __forceinline__ void b_q2k_mins(uint32_t m0, uint32_t m1, int h, u8* tile, int row) {
+  const uint32_t lo = (m0 >> 4) & 0x0f0f0f0fu, hi = (m1 >> 4) & 0x0f0f0f0fu;
   const uint32_t k1024 = 0xe400e400u;  // -1024 twice
   uint32_t v[4];
   v[0] = bytes_to_h2_1024(lo, 0x4140); v[1] = bytes_to_h2_1024(lo, 0x4342);
@@ -224,28 +215,43 @@ __device__ __forceinline__ void b_q2k_mins(const RawBlk& r, int h, u8* tile, int
 // K steps per 256-wide block: four of the quants; for Q2_K a fifth whose A tile holds the
 // activations' sums of 16 and whose B tile holds the mins (one K = 16 MMA into a second
 // accumulator).
-template <int FMT> struct MmGeom { static constexpr int SPB = FMT == ILL_Q2_K ? 5 : 4, ACCS = FMT == ILL_Q2_K ? 2 : 1; };
+// PW: 4-byte words of a row's raw block in shared memory (IQ2_XXS: the 66 bytes from the 4-byte boundary at or
+// before them; an odd count, so that a warp's rows fall in different banks).
+template <int FMT> struct MmGeom {
+  static constexpr int SPB = FMT == ILL_Q2_K ? 5 : 4, ACCS = FMT == ILL_Q2_K ? 2 : 1, PW = FMT == ILL_Q2_K ? 21 : 17;
+  static constexpr int BB = FMT == ILL_Q2_K ? 84 : 66;
+  static constexpr uint32_t RAW_BYTES = 128 * PW * 4;
+  static constexpr size_t SMEM = (size_t)(MM_NA + SPB) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
+                                 512 /* barriers */ + 4096 /* scales */ + 2304 /* experts' first tiles */ +
+                                 (FMT == ILL_IQ2_XXS ? 8 * 2048 + 8 * 1024 : 0) + 1024 /* alignment */;
+};
 
 template <int FMT>
 __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant__ CUtensorMap xmap,
                                                            const __grid_constant__ CUtensorMap emap, const MmParams p) {
-  constexpr int SPB = MmGeom<FMT>::SPB, ACCS = MmGeom<FMT>::ACCS;
+  typedef MmGeom<FMT> G;
+  constexpr int SPB = G::SPB, ACCS = G::ACCS, PW = G::PW, BB = G::BB;
   constexpr uint32_t TMEM_COLS = 2 * ACCS * MM_BN;  // two buffers of accumulators
   extern __shared__ __align__(1024) u8 smem_raw[];
-  // [A stages][B stages] (each tile 1024-byte aligned, as the 128-byte swizzle needs), then barriers, tables
+  // [A ring][B stages: one per K step of a block] (each tile 1024-byte aligned, as the 128-byte swizzle
+  // needs), the ring of raw blocks, then barriers, scales, tables
   u8* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   u8* a_tiles = smem;
-  u8* b_tiles = smem + MM_STAGES * MM_TILE_BYTES;
-  u8* tail = smem + 2 * MM_STAGES * MM_TILE_BYTES;
-  uint64_t* full_a = (uint64_t*)tail;            // TMA bytes landed
-  uint64_t* full_b = full_a + MM_STAGES;         // 8 dequantizing warps arrived
-  uint64_t* empty = full_b + MM_STAGES;          // the MMAs that read the stage completed
-  uint64_t* acc_full = empty + MM_STAGES;        // [2] a block's MMAs completed
-  uint64_t* acc_free = acc_full + 2;             // [2] the 8 drain warps read the buffer
+  u8* b_tiles = smem + MM_NA * MM_TILE_BYTES;
+  uint32_t* raw = (uint32_t*)(smem + (MM_NA + SPB) * MM_TILE_BYTES);
+  u8* tail = (u8*)raw + MM_RS * G::RAW_BYTES + 16;
+  uint64_t* full_a = (uint64_t*)tail;            // [NA] TMA bytes landed
+  uint64_t* empty_a = full_a + MM_NA;            // [NA] the MMAs that read the stage completed
+  uint64_t* full_b = empty_a + MM_NA;            // [SPB] the dequantizing warps arrived (MM_FULL_B arrivals)
+  uint64_t* empty_b = full_b + SPB;              // [SPB] the MMAs that read the stage completed
+  uint64_t* raw_full = empty_b + SPB;            // [RS] the raw-load lanes' copies landed
+  uint64_t* raw_empty = raw_full + MM_RS;        // [RS] the dequantizing warps have read the stage
+  uint64_t* acc_full = raw_empty + MM_RS;        // [2] a block's MMAs completed
+  uint64_t* acc_free = acc_full + 2;             // [2] the drain warps read the buffer
   uint32_t* tmem_slot = (uint32_t*)(acc_free + 2);
-  float* wsc = (float*)(tail + 256);             // [2 buffers][2: d, dmin][128 rows] of the block
-  int* tile_first = (int*)(tail + 256 + 2048);   // [ne + 1] first row tile of each expert; the total
-  uint2* iq_grid = (uint2*)(tail + 256 + 2048 + 2304);  // eight interleaved copies
+  float* wsc = (float*)(tail + 512);             // [4 blocks in flight][2: d, dmin][128 rows]
+  int* tile_first = (int*)(tail + 512 + 4096);   // [ne + 1] first row tile of each expert; the total
+  uint2* iq_grid = (uint2*)(tail + 512 + 4096 + 2304);  // eight interleaved copies
   uint2* iq_smask = iq_grid + 8 * 256;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -270,8 +276,10 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     if (lane == 0) tile_first[p.ne] = before;  // row tiles in all
   }
   if (tid == 32) {
-    for (int s = 0; s < MM_STAGES; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], MM_DQ_WARPS); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_free[b], MM_DQ_WARPS); }
+    for (int s = 0; s < MM_NA; ++s) { mbar_init(&full_a[s], 1); mbar_init(&empty_a[s], 1); }
+    for (int s = 0; s < SPB; ++s) { mbar_init(&full_b[s], MM_FULL_B); mbar_init(&empty_b[s], 1); }
+    for (int s = 0; s < MM_RS; ++s) { mbar_init(&raw_full[s], 32 * MM_LD_WARPS); mbar_init(&raw_empty[s], MM_DQ_WARPS); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_free[b], MM_DR_WARPS); }
     mbar_fence_init();
   }
   if (FMT == ILL_IQ2_XXS) {
@@ -319,13 +327,13 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   if (warp == 0) {
     // ---- TMA producer of the X tiles
     if (lane == 0) {
-      int g_st = 0;  // stages issued so far by this CTA
+      int g_sa = 0;  // A stages issued so far by this CTA
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         int expert, row0, nvalid, nt;
         locate(tile, expert, row0, nvalid, nt);
-        for (int st = 0; st < nkb * SPB; ++st, ++g_st) {
-          const int s = g_st % MM_STAGES, use = g_st / MM_STAGES;
-          if (use > 0 && !mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY)) { ok = false; break; }
+        for (int st = 0; st < nkb * SPB; ++st, ++g_sa) {
+          const int s = g_sa % MM_NA, use = g_sa / MM_NA;
+          if (use > 0 && !mbar_wait(&empty_a[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY)) { ok = false; break; }
           const int kb = st / SPB, j = st - kb * SPB;
           mbar_expect_tx(&full_a[s], MM_TILE_BYTES);
           if (j < 4) tma_load_2d(a_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &full_a[s]);
@@ -338,20 +346,19 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     if (lane == 0) {
       // fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
       const uint32_t idesc = (1u << 4) | ((uint32_t)(MM_BN >> 3) << 17) | ((uint32_t)(MM_BM >> 4) << 24);
-      int g_st = 0, g_kb = 0;  // stages and blocks consumed so far by this CTA
+      int g_sa = 0, g_kb = 0;  // A stages and blocks consumed so far by this CTA
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
           const int b = g_kb & 1;
           if (g_kb >= 2 && !mbar_wait(&acc_free[b], (uint32_t)(g_kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d1 = tmem_base + (uint32_t)(b * ACCS * MM_BN);
-          for (int j = 0; j < SPB; ++j, ++g_st) {
-            const int s = g_st % MM_STAGES;
-            const uint32_t par = (uint32_t)(g_st / MM_STAGES) & 1u;
-            if (!mbar_wait(&full_a[s], par, p.status, ST_MM_WAIT_FULL) ||
-                !mbar_wait(&full_b[s], par, p.status, ST_MM_WAIT_FULL + 1)) { ok = false; break; }
+          for (int j = 0; j < SPB; ++j, ++g_sa) {
+            const int s = g_sa % MM_NA;
+            if (!mbar_wait(&full_a[s], (uint32_t)(g_sa / MM_NA) & 1u, p.status, ST_MM_WAIT_FULL) ||
+                !mbar_wait(&full_b[j], (uint32_t)g_kb & 1u, p.status, ST_MM_WAIT_FULL + 1)) { ok = false; break; }
             tc_fence_after();
-            const uint64_t ad = umma_desc(a_tiles + s * MM_TILE_BYTES), bd = umma_desc(b_tiles + s * MM_TILE_BYTES);
+            const uint64_t ad = umma_desc(a_tiles + s * MM_TILE_BYTES), bd = umma_desc(b_tiles + j * MM_TILE_BYTES);
             if (j < 4) {
 #pragma unroll
               for (int k = 0; k < MM_BK / 16; ++k)  // 32 bytes further along K inside the swizzle atom each time
@@ -359,157 +366,116 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             } else {
               umma_f16(d1 + MM_BN, ad, bd, idesc, 0u);  // mins x sums of 16: one K = 16 product
             }
-            umma_commit(&empty[s]);  // frees the stage when these MMAs are done
+            umma_commit(&empty_a[s]);  // both stages are free when these MMAs are done
+            umma_commit(&empty_b[j]);
           }
           if (ok) umma_commit(&acc_full[b]);
         }
       }
     }
-  } else {
-    // ---- warps 2..17: the weights' integer parts into the B tiles; the accumulators drained block by
-    // block with the block's float scales; the tile's store
-    const int t = tid - 64;                        // 0..511
-    const int row = t >> 2, j = t & 3;             // weight row in the tile, K step of each block
-    constexpr int BB = FMT == ILL_IQ2_XXS ? 66 : 84;
-    const int q = warp & 3;                        // TMEM lanes 32q .. 32q+31 are this warp's
-    const int m = q * 32 + lane;                   // accumulator row
-    const int cq = (warp - 2) >> 2;                // columns 32*cq .. +31
-    int g_st = 0, g_kb = 0;                        // stages / blocks produced so far by this CTA
-    int d_kb = 0;                                  // blocks drained so far
-    // per tile
-    bool has_row = false;
-    const u8* wrow = nullptr;
-    int nvalid = 0;
-    long long tok = -1;
-    float out[32];
-
-    // Block KB's B tiles from CUR (its raw words, loaded a block ago); NXT gets the next block's.
-    auto produce = [&](int kb, const RawBlk& cur, RawBlk& nxt) -> bool {
-      const int b = g_kb & 1;
-      if (kb + 1 < nkb && has_row) load_raw<FMT>(nxt, wrow + (long long)(kb + 1) * BB, j);
-      if (g_kb >= 2) {  // the scales two blocks back have been read by every drain warp
-        bool w_ok = mbar_wait(&acc_free[b], (uint32_t)(g_kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI + 1);
-        if (!__all_sync(0xffffffffu, w_ok)) return false;
-      }
-      if (j == 0) {
-        float d = 0.0f, dmin = 0.0f;
-        if (has_row) { d = h2f(cur.dd & 0xffff); dmin = h2f(cur.dd >> 16); }
-        wsc[b * 256 + row] = d;
-        wsc[b * 256 + 128 + row] = dmin;
-      }
-      {
-        const int st = g_st + j, s = st % MM_STAGES, use = st / MM_STAGES;
-        bool w_ok = true;
-        if (use > 0) w_ok = mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
-        if (!__all_sync(0xffffffffu, w_ok)) return false;
-        u8* tile = b_tiles + s * MM_TILE_BYTES;
-        if (has_row) {
-          if constexpr (FMT == ILL_IQ2_XXS) b_iq2xxs(cur, 2 * j, tile, row, iq_grid + (lane & 7), iq_smask + (lane & 7));
-          else b_q2k(cur, j, tile, row);
-        } else {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) store_chunk(tile, row, (c + 2 * j) & 7, make_uint4(0, 0, 0, 0));
-        }
-        fence_async_smem();  // the tensor core reads the tile through the async proxy
-        __syncwarp();
-        if (lane < 4) mbar_arrive(&full_b[s]);  // lane j for the stage the K-step-j lanes wrote
-      }
-      if constexpr (SPB == 5) {
-        const int st = g_st + 4, s = st % MM_STAGES, use = st / MM_STAGES;
-        bool w_ok = true;
-        if (use > 0) w_ok = mbar_wait(&empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
-        if (!__all_sync(0xffffffffu, w_ok)) return false;
-        u8* tile = b_tiles + s * MM_TILE_BYTES;
-        if (j < 2) {
-          if (has_row) b_q2k_mins(cur, j, tile, row);
-          else store_chunk(tile, row, j, make_uint4(0, 0, 0, 0));
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_b[s]);
-      }
-      g_st += SPB;
-      ++g_kb;
-      return true;
-    };
-    // Block KB of the current tile (the D_KB-th block of this CTA) out of tensor memory into OUT.
-    auto drain = [&](int kb) -> bool {
-      const int b = d_kb & 1;
-      bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC);
-      if (!__all_sync(0xffffffffu, e_ok)) return false;
-      tc_fence_after();
-      if (32 * q < nvalid) {  // a quarter of the tile with no valid row is not read
-        const float dx = tok >= 0 ? p.xd[tok * nkb + kb] : 0.0f;
-        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * ACCS * MM_BN + 32 * cq);
-        const float4* wd = (const float4*)(wsc + b * 256 + 32 * cq);
-        uint32_t v[32];
-        tmem_ld32(t0, v);
-        if constexpr (FMT == ILL_IQ2_XXS) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 dw = wd[i >> 2];
-            // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum; the 1/8 at the end
-            out[i] = fmaf(__fmul_rn(dw.x, dx), __uint_as_float(v[i]), out[i]);
-            out[i + 1] = fmaf(__fmul_rn(dw.y, dx), __uint_as_float(v[i + 1]), out[i + 1]);
-            out[i + 2] = fmaf(__fmul_rn(dw.z, dx), __uint_as_float(v[i + 2]), out[i + 2]);
-            out[i + 3] = fmaf(__fmul_rn(dw.w, dx), __uint_as_float(v[i + 3]), out[i + 3]);
-          }
-        } else {
-          // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins; the sums first,
-          // then the mins through the same registers
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 dw = wd[i >> 2];
-            out[i] = fmaf(__fmul_rn(dx, dw.x), __uint_as_float(v[i]), out[i]);
-            out[i + 1] = fmaf(__fmul_rn(dx, dw.y), __uint_as_float(v[i + 1]), out[i + 1]);
-            out[i + 2] = fmaf(__fmul_rn(dx, dw.z), __uint_as_float(v[i + 2]), out[i + 2]);
-            out[i + 3] = fmaf(__fmul_rn(dx, dw.w), __uint_as_float(v[i + 3]), out[i + 3]);
-          }
-          tmem_ld32(t0 + MM_BN, v);
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 dm = wd[32 + (i >> 2)];
-            out[i] = fmaf(-__fmul_rn(dx, dm.x), __uint_as_float(v[i]), out[i]);
-            out[i + 1] = fmaf(-__fmul_rn(dx, dm.y), __uint_as_float(v[i + 1]), out[i + 1]);
-            out[i + 2] = fmaf(-__fmul_rn(dx, dm.z), __uint_as_float(v[i + 2]), out[i + 2]);
-            out[i + 3] = fmaf(-__fmul_rn(dx, dm.w), __uint_as_float(v[i + 3]), out[i + 3]);
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_free[b]);
-      ++d_kb;
-      return true;
-    };
-
+  } else if (warp < 2 + MM_LD_WARPS) {
+    // ---- warps 2, 3 copy each block's raw bytes (128 rows x PW words) into the raw ring, 4 bytes a
+    // lane at a time so that a warp's requests touch two or three rows, not thirty-two
+    const int L = (warp - 2) * 32 + lane;
+    constexpr int NL = 32 * MM_LD_WARPS, QS = NL / PW, RS_ = NL % PW;  // a step of NL words = QS rows + RS_ words
+    int g_kb = 0;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-      int expert, row0, nt;
+      int expert, row0, nvalid, nt;
       locate(tile, expert, row0, nvalid, nt);
-      const int n = nt * MM_BN + row;
-      has_row = n < p.nrows;
-      wrow = (const u8*)(uintptr_t)p.ptrs[expert] + p.add + (long long)(has_row ? n : 0) * p.row_bytes;
-      const long long place = (long long)row0 + m;
-      tok = place < p.total_rows ? (p.map ? (long long)p.map[place] : place) : -1;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) out[i] = 0.0f;
-      RawBlk r0, r1;
-      if (has_row) load_raw<FMT>(r0, wrow, j);
-      for (int kb = 0; kb < nkb && ok; kb += 2) {
-        ok = produce(kb, r0, r1);
-        if (ok && kb >= 1) ok = drain(kb - 1);
-        if (ok && kb + 1 < nkb) {
-          ok = produce(kb + 1, r1, r0);
-          if (ok) ok = drain(kb);
+      const u8* wbase = (const u8*)(uintptr_t)p.ptrs[expert] + p.add + (long long)nt * MM_BN * p.row_bytes;
+      const int rows_here = min(MM_BN, p.nrows - nt * MM_BN);
+      for (int kb = 0; kb < nkb; ++kb, ++g_kb) {
+        const int s = g_kb % MM_RS, use = g_kb / MM_RS;
+        bool w_ok = true;
+        if (use > 0) w_ok = mbar_wait(&raw_empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 2);
+        if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
+        uint32_t* dst = raw + s * (G::RAW_BYTES / 4);
+        int row = L / PW, word = L % PW;
+#pragma unroll 2
+        for (int n = 0; n < 128 * PW / NL; ++n) {
+          if (row < rows_here) {
+            const uintptr_t blk = (uintptr_t)(wbase + (long long)row * p.row_bytes + kb * BB);
+            cp_async4(dst + row * PW + word, (const void*)((blk & ~(uintptr_t)3) + 4 * word));
+          }
+          row += QS;
+          word += RS_;
+          if (word >= PW) { word -= PW; ++row; }
         }
+        cp_async_arrive(&raw_full[s]);
       }
-      if (ok) ok = drain(nkb - 1);
+    }
+    cp_async_wait_all();
+  } else if (warp < 2 + MM_LD_WARPS + MM_DR_WARPS) {
+    // ---- warps 4..11 drain the accumulators block by block, scaling each block's integer sums by the
+    // block's float scales, and store the finished tile.  A warp reads the 32 tensor-memory lanes
+    // its number gives it (warp % 4) and half of the columns.
+    const int q = warp & 3;
+    const int m = q * 32 + lane;                   // accumulator row = row of X in the tile
+    const int c0 = ((warp - 2 - MM_LD_WARPS) >> 2) * 64;  // columns c0 .. c0 + 63
+    int d_kb = 0;                                  // blocks drained so far by this CTA
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      int expert, row0, nvalid, nt;
+      locate(tile, expert, row0, nvalid, nt);
+      const long long place = (long long)row0 + m;
+      const long long tok = place < p.total_rows ? (p.map ? (long long)p.map[place] : place) : -1;
+      const float* xdr = p.xd + (tok >= 0 ? tok : 0) * nkb;
+      float out[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) out[i] = 0.0f;
+      float dx_next = tok >= 0 ? __ldg(xdr) : 0.0f;
+      for (int kb = 0; kb < nkb; ++kb, ++d_kb) {
+        const float dx = dx_next;
+        if (kb + 1 < nkb && tok >= 0) dx_next = __ldg(xdr + kb + 1);
+        const int b = d_kb & 1;
+        const bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC);
+        if (!__all_sync(0xffffffffu, e_ok)) { ok = false; break; }
+        tc_fence_after();
+        if (32 * q < nvalid) {  // a quarter of the tile with no valid row is not read
+          const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * ACCS * MM_BN + c0);
+          const float* wd = wsc + (d_kb & 3) * 256 + c0;
+#pragma unroll
+          for (int part = 0; part < 2; ++part) {
+            uint32_t v[32];
+            tmem_ld32(t0 + 32 * part, v);
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float4 dw = *(const float4*)(wd + 32 * part + i);
+              // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum, the 1/8 at the end;
+              // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
+              const float s0 = FMT == ILL_IQ2_XXS ? __fmul_rn(dw.x, dx) : __fmul_rn(dx, dw.x);
+              const float s1 = FMT == ILL_IQ2_XXS ? __fmul_rn(dw.y, dx) : __fmul_rn(dx, dw.y);
+              const float s2 = FMT == ILL_IQ2_XXS ? __fmul_rn(dw.z, dx) : __fmul_rn(dx, dw.z);
+              const float s3 = FMT == ILL_IQ2_XXS ? __fmul_rn(dw.w, dx) : __fmul_rn(dx, dw.w);
+              float* o = out + 32 * part + i;
+              o[0] = fmaf(s0, __uint_as_float(v[i]), o[0]);
+              o[1] = fmaf(s1, __uint_as_float(v[i + 1]), o[1]);
+              o[2] = fmaf(s2, __uint_as_float(v[i + 2]), o[2]);
+              o[3] = fmaf(s3, __uint_as_float(v[i + 3]), o[3]);
+            }
+            if constexpr (FMT == ILL_Q2_K) {
+              tmem_ld32(t0 + MM_BN + 32 * part, v);
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                const float4 dm = *(const float4*)(wd + 128 + 32 * part + i);
+                float* o = out + 32 * part + i;
+                o[0] = fmaf(-__fmul_rn(dx, dm.x), __uint_as_float(v[i]), o[0]);
+                o[1] = fmaf(-__fmul_rn(dx, dm.y), __uint_as_float(v[i + 1]), o[1]);
+                o[2] = fmaf(-__fmul_rn(dx, dm.z), __uint_as_float(v[i + 2]), o[2]);
+                o[3] = fmaf(-__fmul_rn(dx, dm.w), __uint_as_float(v[i + 3]), o[3]);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_free[b]);
+      }
       if (ok && m < nvalid) {
-        float* yrow = p.y + place * p.y_stride + (long long)nt * MM_BN + 32 * cq;
+        float* yrow = p.y + place * p.y_stride + (long long)nt * MM_BN + c0;
         const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
 #pragma unroll
-        for (int jj = 0; jj < 32; jj += 4) {
-          const int n0 = nt * MM_BN + 32 * cq + jj;
+        for (int jj = 0; jj < 64; jj += 4) {
+          const int n0 = nt * MM_BN + c0 + jj;
           if (n0 + 3 < p.nrows) {
             *(float4*)(yrow + jj) = make_float4(out[jj] * fin, out[jj + 1] * fin, out[jj + 2] * fin, out[jj + 3] * fin);
           } else {
@@ -517,6 +483,97 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             for (int e = 0; e < 4; ++e)
               if (n0 + e < p.nrows) yrow[jj + e] = out[jj + e] * fin;
           }
+        }
+      }
+    }
+  } else {
+    // ---- warps 12..19 turn the raw blocks into the B tiles: thread (row, h) makes K steps h and
+    // h + 2 of its row, so the warps of h = 0 and of h = 1 fill alternate stages and the tensor core
+    // can start on a block while its second half is still being made.
+    const int t = tid - 32 * (2 + MM_LD_WARPS + MM_DR_WARPS);  // 0..255
+    const int row = t & 127, h = t >> 7;
+    const uint2* grid = iq_grid + (lane & 7);
+    const uint2* smask = iq_smask + (lane & 7);
+    int g_kb = 0;                                  // blocks produced so far by this CTA
+
+    // B stage J (K step J of every block) once the MMAs of the block before are done with it
+    auto stage_wait = [&](int j) -> bool {
+      bool w_ok = true;
+      if (g_kb > 0) w_ok = mbar_wait(&empty_b[j], (uint32_t)(g_kb - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
+      return __all_sync(0xffffffffu, w_ok);
+    };
+
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      int expert, row0, nvalid, nt;
+      locate(tile, expert, row0, nvalid, nt);
+      const int n = nt * MM_BN + row;
+      const bool has_row = n < p.nrows;
+      // the low bits of the row's address: where its blocks start inside their first word
+      const uint32_t rowlow = (uint32_t)(p.ptrs[expert] + (unsigned long long)p.add + (unsigned long long)n * p.row_bytes);
+      for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
+        const int rs = g_kb % MM_RS;
+        const bool r_ok = mbar_wait(&raw_full[rs], (uint32_t)(g_kb / MM_RS) & 1u, p.status, ST_MM_WAIT_FULL + 2);
+        if (!__all_sync(0xffffffffu, r_ok)) { ok = false; break; }
+        const uint32_t* rw = raw + rs * (G::RAW_BYTES / 4) + row * PW;
+        // this thread's words of the block, then the raw stage is free again
+        uint32_t w[FMT == ILL_Q2_K ? 16 : 8], sc[4], dd = 0;
+        if (has_row) {
+          if constexpr (FMT == ILL_IQ2_XXS) {
+            const uint32_t mis = (rowlow + (uint32_t)kb * BB) & 3u;  // 0 or 2
+            dd = (rw[0] >> (8 * mis)) & 0xffffu;
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              const uint32_t o = mis + 2 + 16 * (h + 2 * part), w0 = o >> 2, sh = (o & 3u) * 8u;
+              uint32_t prev = rw[w0];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t next = rw[w0 + i + 1];
+                w[4 * part + i] = __funnelshift_r(prev, next, sh);
+                prev = next;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[i] = rw[i];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) w[i] = rw[4 + i];
+            dd = rw[20];
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[rs]);
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          const int j = h + 2 * part;
+          if (!stage_wait(j)) { ok = false; break; }
+          if (part == 0 && h == 0) {
+            // The drain of four blocks back is over: the MMAs that freed this stage were issued after it.
+            float d = 0.0f, dmin = 0.0f;
+            if (has_row) { d = h2f(dd & 0xffff); dmin = h2f(dd >> 16); }
+            wsc[(g_kb & 3) * 256 + row] = d;
+            if (FMT == ILL_Q2_K) wsc[(g_kb & 3) * 256 + 128 + row] = dmin;
+          }
+          u8* tile_b = b_tiles + j * MM_TILE_BYTES;
+          if (has_row) {
+            if constexpr (FMT == ILL_IQ2_XXS) b_iq2xxs(w + 4 * part, tile_b, row, grid, smask);
+            else b_q2k(w + 8 * part, sc[2 * part + h], h, tile_b, row);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) store_chunk(tile_b, row, c, make_uint4(0, 0, 0, 0));
+          }
+          fence_async_smem();  // the tensor core reads the tile through the async proxy
+          __syncwarp();
+          if (lane < 2) mbar_arrive(&full_b[j]);  // four warps x two arrivals
+        }
+        if constexpr (SPB == 5) {
+          if (!ok) break;
+          if (!stage_wait(4)) { ok = false; break; }
+          u8* tile_b = b_tiles + 4 * MM_TILE_BYTES;
+          if (has_row) b_q2k_mins(sc[2 * h], sc[2 * h + 1], h, tile_b, row);
+          else store_chunk(tile_b, row, h, make_uint4(0, 0, 0, 0));
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_b[4]);  // eight warps x one arrival
         }
       }
     }
@@ -647,8 +704,7 @@ extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dpt
   p.ne = ne;
   p.status = device_status_word();
   const long long max_tiles = ((total_rows + MM_BM - 1) / MM_BM + ne) * ((nrows + MM_BN - 1) / MM_BN);  // an upper bound
-  // tiles, barriers, scales, the experts' first tiles, tables x 8, alignment
-  const size_t smem = 2 * MM_STAGES * MM_TILE_BYTES + 256 + 2048 + 2304 + 8 * 2048 + 8 * 1024 + 1024;
+  const size_t smem = fmt == ILL_IQ2_XXS ? MmGeom<ILL_IQ2_XXS>::SMEM : MmGeom<ILL_Q2_K>::SMEM;
   if (ne > 512) return ILL_ERR_TOO_LARGE;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
