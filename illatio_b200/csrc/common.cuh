@@ -59,14 +59,22 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: gives up ILL_WAIT_NS nanoseconds after it began.  Returns false (and records CODE in
-// the status word, first writer wins) when the phase never completes.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code) {
+// Bounded wait: gives up about ILL_WAIT_NS nanoseconds after it began.  Returns false (and records CODE
+// in the status word, first writer wins) when the phase never completes.  SLEEP_NS > 0 makes the
+// waiter sleep between polls, so that a warp with slack leaves the issue slots to the others; the
+// clock is read once in 64 polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code,
+                                          unsigned sleep_ns = 0) {
   if (mbar_try_wait(bar, parity, 0)) return true;
-  const unsigned long long t0 = global_ns();
-  for (;;) {
+  unsigned long long t0 = 0;
+  for (unsigned it = 1;; ++it) {
+    if (sleep_ns) __nanosleep(sleep_ns);
     if (mbar_try_wait(bar, parity, 20000)) return true;
-    if (global_ns() - t0 > ILL_WAIT_NS) break;
+    if ((it & 63u) == 0) {
+      const unsigned long long now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > ILL_WAIT_NS) break;
+    }
   }
   if (status) atomicCAS(status, 0u, code);
   return false;

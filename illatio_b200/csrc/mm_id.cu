@@ -32,7 +32,7 @@
 namespace ill {
 
 constexpr int MM_BM = 128, MM_BN = 128, MM_BK = 64;
-constexpr int MM_NA = 6;                               // stages of the ring of X tiles
+constexpr int MM_NA = 5;                               // stages of the ring of X tiles
 constexpr int MM_RS = 3;                               // stages of the ring of raw weight blocks
 constexpr int MM_DR_WARPS = 8, MM_DQ_WARPS = 8, MM_LD_WARPS = 2;  // drain, dequantize, raw-load warps
 constexpr int MM_THREADS = 32 * (2 + MM_LD_WARPS + MM_DR_WARPS + MM_DQ_WARPS);  // + the TMA warp and the MMA warp
@@ -155,25 +155,34 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
 //
 // IQ2_XXS: one K step = two sub-blocks W[0..3] = (indices, signs + scale) x 2; the 64 integers
 // grid * sign * (2 LS + 1) (at most 43 * 31: exact in fp16).  The block's float part is d / 8
-// (src/avx2.lisp:77-110 takes the products this way).  GRID and SMASK point at this lane's copy of
-// the tables (eight interleaved copies: entry e of copy c at [8 e + c]).
-__device__ __forceinline__ void b_iq2xxs(const uint32_t* w, u8* tile, int row, const uint2* grid, const uint2* smask) {
+// (src/avx2.lisp:77-110 takes the products this way).  GRID points at this lane's copy of the grid
+// (sixteen interleaved copies: entry e of copy c at [16 e + c], so the sixteen lanes of a 64-bit
+// request never share a bank); SGN at this lane's copy of the table that turns four sign bits into
+// the sign bits of two pairs of halves (entry x of copy c at [32 x + c]).  The eighth sign of a
+// group is the parity of the seven stored ones (ksigns_iq2xs[i] = i | parity(i) << 7).
+// All the look-ups of a sub-block are issued before its first store: the compiler may not move a
+// shared-memory load over a shared-memory store by itself.
+__device__ __forceinline__ void b_iq2xxs(const uint32_t* w, u8* tile, int row, const uint2* grid, const uint2* sgn) {
 #pragma unroll
   for (int sb = 0; sb < 2; ++sb) {
     const uint32_t idx = w[2 * sb], aux = w[2 * sb + 1];
-    // (1024 + (b + 128)) * s - 1152 s = b * s
-    const uint32_t s2 = small_h2(2 * (aux >> 28) + 1), bias = hmul2(s2, 0xe480e480u /* -1152 */);
+    // (1024 + g) * s - 1024 s = g * s
+    const uint32_t s2 = small_h2(2 * (aux >> 28) + 1), bias = hmul2(s2, 0xe400e400u /* -1024 */);
+    uint2 g[4], ml[4], mh[4];
 #pragma unroll
     for (int l = 0; l < 4; ++l) {
-      const uint2 g = grid[8 * ((idx >> (8 * l)) & 0xff)];
-      const uint2 m = smask[8 * ((aux >> (7 * l)) & 127)];
-      // signed bytes: (g ^ m) - m per byte; then + 128 to make them unsigned for the conversion
-      const uint32_t lo = ((g.x ^ m.x) + (m.x & 0x01010101u)) ^ 0x80808080u;
-      const uint32_t hi = ((g.y ^ m.y) + (m.y & 0x01010101u)) ^ 0x80808080u;
-      store_chunk(tile, row, 4 * sb + l,
-                  make_uint4(hfma2(bytes_to_h2_1024(lo, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(lo, 0x4342), s2, bias),
-                             hfma2(bytes_to_h2_1024(hi, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(hi, 0x4342), s2, bias)));
+      const uint32_t s7 = (aux >> (7 * l)) & 127u;
+      g[l] = grid[16 * ((idx >> (8 * l)) & 0xff)];
+      ml[l] = sgn[32 * (s7 & 15u)];
+      mh[l] = sgn[32 * ((s7 >> 4) | ((__popc(s7) & 1u) << 3))];
     }
+#pragma unroll
+    for (int l = 0; l < 4; ++l)
+      store_chunk(tile, row, 4 * sb + l,
+                  make_uint4(hfma2(bytes_to_h2_1024(g[l].x, 0x4140), s2, bias) ^ ml[l].x,
+                             hfma2(bytes_to_h2_1024(g[l].x, 0x4342), s2, bias) ^ ml[l].y,
+                             hfma2(bytes_to_h2_1024(g[l].y, 0x4140), s2, bias) ^ mh[l].x,
+                             hfma2(bytes_to_h2_1024(g[l].y, 0x4342), s2, bias) ^ mh[l].y));
   }
 }
 
@@ -223,7 +232,7 @@ template <int FMT> struct MmGeom {
   static constexpr uint32_t RAW_BYTES = 128 * PW * 4;
   static constexpr size_t SMEM = (size_t)(MM_NA + SPB) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
                                  512 /* barriers */ + 4096 /* scales */ + 2304 /* experts' first tiles */ +
-                                 (FMT == ILL_IQ2_XXS ? 8 * 2048 + 8 * 1024 : 0) + 1024 /* alignment */;
+                                 (FMT == ILL_IQ2_XXS ? 16 * 2048 + 4096 : 0) /* tables */ + 1024 /* alignment */;
 };
 
 template <int FMT>
@@ -251,8 +260,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   uint32_t* tmem_slot = (uint32_t*)(acc_free + 2);
   float* wsc = (float*)(tail + 512);             // [4 blocks in flight][2: d, dmin][128 rows]
   int* tile_first = (int*)(tail + 512 + 4096);   // [ne + 1] first row tile of each expert; the total
-  uint2* iq_grid = (uint2*)(tail + 512 + 4096 + 2304);  // eight interleaved copies
-  uint2* iq_smask = iq_grid + 8 * 256;
+  uint2* iq_grid = (uint2*)(tail + 512 + 4096 + 2304);  // sixteen interleaved copies
+  uint2* iq_sgn = iq_grid + 16 * 256;            // [16 nibbles][32 copies]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -283,19 +292,13 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     mbar_fence_init();
   }
   if (FMT == ILL_IQ2_XXS) {
-    for (int i = tid; i < 8 * 256; i += MM_THREADS) {
-      const uint64_t g = ill_iq2xxs_grid[i >> 3];
+    for (int i = tid; i < 16 * 256; i += MM_THREADS) {
+      const uint64_t g = ill_iq2xxs_grid[i >> 4];
       iq_grid[i] = make_uint2((uint32_t)g, (uint32_t)(g >> 32));
     }
-    for (int i = tid; i < 8 * 128; i += MM_THREADS) {
-      const uint32_t sg = ill_ksigns_iq2xs[i >> 3];
-      uint32_t lo = 0, hi = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if ((sg >> j) & 1) lo |= 0xffu << (8 * j);
-        if ((sg >> (4 + j)) & 1) hi |= 0xffu << (8 * j);
-      }
-      iq_smask[i] = make_uint2(lo, hi);
+    for (int i = tid; i < 16 * 32; i += MM_THREADS) {
+      const uint32_t x = (uint32_t)i >> 5;  // signs of elements 0..3: the sign bits of the halves (0, 1) and (2, 3)
+      iq_sgn[i] = make_uint2(((x & 1u) << 15) | ((x & 2u) << 30), ((x & 4u) << 13) | ((x & 8u) << 28));
     }
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
@@ -333,7 +336,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         locate(tile, expert, row0, nvalid, nt);
         for (int st = 0; st < nkb * SPB; ++st, ++g_sa) {
           const int s = g_sa % MM_NA, use = g_sa / MM_NA;
-          if (use > 0 && !mbar_wait(&empty_a[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY)) { ok = false; break; }
+          if (use > 0 && !mbar_wait(&empty_a[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY, 100)) { ok = false; break; }
           const int kb = st / SPB, j = st - kb * SPB;
           mbar_expect_tx(&full_a[s], MM_TILE_BYTES);
           if (j < 4) tma_load_2d(a_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &full_a[s]);
@@ -376,30 +379,28 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   } else if (warp < 2 + MM_LD_WARPS) {
     // ---- warps 2, 3 copy each block's raw bytes (128 rows x PW words) into the raw ring, 4 bytes a
     // lane at a time so that a warp's requests touch two or three rows, not thirty-two
+    // Lane L < RPS * PW owns word L % PW of rows L / PW, + RPS, + 2 RPS, ...
     const int L = (warp - 2) * 32 + lane;
-    constexpr int NL = 32 * MM_LD_WARPS, QS = NL / PW, RS_ = NL % PW;  // a step of NL words = QS rows + RS_ words
+    constexpr int NL = 32 * MM_LD_WARPS, RPS = NL / PW;  // rows a step
+    const int word = L % PW, r_first = L / PW;
     int g_kb = 0;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int expert, row0, nvalid, nt;
       locate(tile, expert, row0, nvalid, nt);
       const u8* wbase = (const u8*)(uintptr_t)p.ptrs[expert] + p.add + (long long)nt * MM_BN * p.row_bytes;
-      const int rows_here = min(MM_BN, p.nrows - nt * MM_BN);
+      const int rows_here = r_first < RPS ? min(MM_BN, p.nrows - nt * MM_BN) : 0;
       for (int kb = 0; kb < nkb; ++kb, ++g_kb) {
         const int s = g_kb % MM_RS, use = g_kb / MM_RS;
         bool w_ok = true;
-        if (use > 0) w_ok = mbar_wait(&raw_empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 2);
+        if (use > 0) w_ok = mbar_wait(&raw_empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 2, 200);
         if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
-        uint32_t* dst = raw + s * (G::RAW_BYTES / 4);
-        int row = L / PW, word = L % PW;
-#pragma unroll 2
-        for (int n = 0; n < 128 * PW / NL; ++n) {
-          if (row < rows_here) {
-            const uintptr_t blk = (uintptr_t)(wbase + (long long)row * p.row_bytes + kb * BB);
-            cp_async4(dst + row * PW + word, (const void*)((blk & ~(uintptr_t)3) + 4 * word));
-          }
-          row += QS;
-          word += RS_;
-          if (word >= PW) { word -= PW; ++row; }
+        uint32_t* dst = raw + s * (G::RAW_BYTES / 4) + r_first * PW + word;
+        const u8* src = wbase + (long long)r_first * p.row_bytes + kb * BB;
+#pragma unroll 4
+        for (int row = r_first; row < rows_here; row += RPS) {
+          cp_async4(dst, (const void*)(((uintptr_t)src & ~(uintptr_t)3) + 4 * word));
+          dst += RPS * PW;
+          src += (long long)RPS * p.row_bytes;
         }
         cp_async_arrive(&raw_full[s]);
       }
@@ -427,7 +428,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         const float dx = dx_next;
         if (kb + 1 < nkb && tok >= 0) dx_next = __ldg(xdr + kb + 1);
         const int b = d_kb & 1;
-        const bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC);
+        const bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC, 100);
         if (!__all_sync(0xffffffffu, e_ok)) { ok = false; break; }
         tc_fence_after();
         if (32 * q < nvalid) {  // a quarter of the tile with no valid row is not read
@@ -492,14 +493,14 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     // can start on a block while its second half is still being made.
     const int t = tid - 32 * (2 + MM_LD_WARPS + MM_DR_WARPS);  // 0..255
     const int row = t & 127, h = t >> 7;
-    const uint2* grid = iq_grid + (lane & 7);
-    const uint2* smask = iq_smask + (lane & 7);
+    const uint2* grid = iq_grid + (lane & 15);
+    const uint2* sgn = iq_sgn + lane;
     int g_kb = 0;                                  // blocks produced so far by this CTA
 
     // B stage J (K step J of every block) once the MMAs of the block before are done with it
     auto stage_wait = [&](int j) -> bool {
       bool w_ok = true;
-      if (g_kb > 0) w_ok = mbar_wait(&empty_b[j], (uint32_t)(g_kb - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1);
+      if (g_kb > 0) w_ok = mbar_wait(&empty_b[j], (uint32_t)(g_kb - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1, 50);
       return __all_sync(0xffffffffu, w_ok);
     };
 
@@ -512,7 +513,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       const uint32_t rowlow = (uint32_t)(p.ptrs[expert] + (unsigned long long)p.add + (unsigned long long)n * p.row_bytes);
       for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
         const int rs = g_kb % MM_RS;
-        const bool r_ok = mbar_wait(&raw_full[rs], (uint32_t)(g_kb / MM_RS) & 1u, p.status, ST_MM_WAIT_FULL + 2);
+        const bool r_ok = mbar_wait(&raw_full[rs], (uint32_t)(g_kb / MM_RS) & 1u, p.status, ST_MM_WAIT_FULL + 2, 50);
         if (!__all_sync(0xffffffffu, r_ok)) { ok = false; break; }
         const uint32_t* rw = raw + rs * (G::RAW_BYTES / 4) + row * PW;
         // this thread's words of the block, then the raw stage is free again
@@ -555,7 +556,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           }
           u8* tile_b = b_tiles + j * MM_TILE_BYTES;
           if (has_row) {
-            if constexpr (FMT == ILL_IQ2_XXS) b_iq2xxs(w + 4 * part, tile_b, row, grid, smask);
+            if constexpr (FMT == ILL_IQ2_XXS) b_iq2xxs(w + 4 * part, tile_b, row, grid, sgn);
             else b_q2k(w + 8 * part, sc[2 * part + h], h, tile_b, row);
           } else {
 #pragma unroll
