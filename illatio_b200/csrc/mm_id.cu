@@ -1,23 +1,28 @@
 // mm_id.cu -- the routed experts' product for a chunk of tokens, on the 5th-generation
-// tensor cores (tcgen05, accumulators in tensor memory).
+// tensor cores (tcgen05, operands and accumulators in tensor memory).
 //
 //   Y[place, n] = sum_k X[place, k] * W_e[n, k]      for every expert e and every row
 //                                                    `place` in [bases[e], bases[e] + counts[e])
 //
 // X is the chunk's activations already grouped by expert (ill_moe_group), as fp16
-// (ill_act_f16: the Q8_K quants times their block scale, i.e. exactly the values the
-// reference's CPU kernels multiply, rounded once to fp16).  W_e is expert e's matrix
-// of raw IQ2_XXS or Q2_K blocks at ptrs[e] + add.
+// (ill_act_f16: the Q8_K quants, exact in fp16).  W_e is expert e's matrix of raw IQ2_XXS
+// or Q2_K blocks at ptrs[e] + add.
 //
-// A persistent grid (a CTA per SM) walks 128 (rows of X) x 128 (rows of W_e) tiles, K in steps of 64:
-//   warp 0      one lane issues the TMA loads of the X tile (128-byte swizzle)
-//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128x128x16, fp16 in,
-//               fp32 accumulate) and commits each stage back to the producers
-//   warps 2-3   copy W_e's raw blocks into a ring in shared memory (cp.async, coalesced)
+// A persistent grid (a CTA per SM) walks tiles of 128 weight rows x up to 128 rows of X.  The
+// weights are the tensor core's A operand and live in tensor memory: the dequantizing warps write
+// their integer parts (exact in fp16) there with tcgen05.st, so they never pass through shared
+// memory; X is the B operand, brought by TMA (128-byte swizzle).  The accumulator
+// D[weight row, row of X] is drained once per 256-wide block of K and scaled by the block's two
+// float scales, which is the order the reference's CPU kernels multiply in.
+//   warp 0      one lane issues the TMA loads of the X tiles
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x N x 16, fp16 in,
+//               fp32 accumulate) and commits each step back to the producers
+//   warps 2-3   copy W_e's raw blocks and the X rows' block scales into rings in shared memory
+//               (cp.async, coalesced)
 //   warps 4-11  drain the accumulators block by block (tcgen05.ld), scaling each block's integer
-//               sums by the block's float scales; then store the tile's valid rows
-//   warps 12-19 turn the raw blocks into the swizzled shared-memory operand tiles (two threads a
-//               weight row, two K steps each)
+//               sums by the block's float scales; then store the tile (a lane = a weight row, so
+//               the 32 lanes of a warp write 128 contiguous bytes of a row of Y)
+//   warps 12-19 turn the raw blocks into the A operand (two threads a weight row, two K steps each)
 // Every mbarrier wait is bounded; on a time-out the kernel records a code in the status
 // word, skips what depends on the wait, frees its tensor memory and returns.
 //
@@ -31,13 +36,15 @@
 
 namespace ill {
 
-constexpr int MM_BM = 128, MM_BN = 128, MM_BK = 64;
-constexpr int MM_NA = 5;                               // stages of the ring of X tiles
+constexpr int MM_BM = 128;                             // rows of X a tile (the MMA's N)
+constexpr int MM_BN = 128;                             // weight rows a tile (the MMA's M)
+constexpr int MM_BK = 64;                              // K step: one 128-byte row of the swizzled X tile
+constexpr int MM_NX = 8;                               // stages of the ring of X tiles
 constexpr int MM_RS = 3;                               // stages of the ring of raw weight blocks
+constexpr int MM_XSC = 16;                             // blocks of X scales kept (the loader runs < 16 blocks ahead of the drain)
 constexpr int MM_DR_WARPS = 8, MM_DQ_WARPS = 8, MM_LD_WARPS = 2;  // drain, dequantize, raw-load warps
 constexpr int MM_THREADS = 32 * (2 + MM_LD_WARPS + MM_DR_WARPS + MM_DQ_WARPS);  // + the TMA warp and the MMA warp
-constexpr int MM_FULL_B = 8;                           // arrivals that complete a B stage
-constexpr uint32_t MM_TILE_BYTES = MM_BM * MM_BK * 2;  // 16 KB, A or B
+constexpr uint32_t MM_TILE_BYTES = MM_BM * MM_BK * 2;  // 16 KB
 
 struct MmParams {
   int ncols, nrows;            // K and N of every expert matrix
@@ -73,14 +80,14 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// D[tmem] (+)= A[smem] * B[smem]^T, 128 x 128 x 16, fp16 operands, fp32 accumulate
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+// D[tmem] (+)= A[tmem] * B[smem]^T, 128 x N x 16, fp16 operands, fp32 accumulate.  A: 128 lanes x 8
+// columns (two halves a column, K ascending); B: N rows of X, K-major.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
       : "memory");
 }
 // arrive on BAR once every tcgen05.mma issued so far by this thread has completed
@@ -106,13 +113,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-
-// ---- the weights' integer parts into the swizzled B tile ---------------------------------
-// A thread owns half of a weight row's 64-wide K step: 32 weights = 4 chunks of 8 halves;
-// chunk c of the row goes to 16-byte slot c ^ (row % 8) of the row's 128 bytes.
-__device__ __forceinline__ void store_chunk(u8* tile, int row, int c, uint4 v) {
-  *(uint4*)(tile + (row >> 3) * 1024 + (row & 7) * 128 + ((c ^ (row & 7)) << 4)) = v;
+// this lane's 16 (4) words into 16 (4) consecutive columns of its tensor-memory lane
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
 }
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+               "r"(v[3])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // two unsigned bytes (byte positions B0, B1 of V) as the halves 1024 + byte
 __device__ __forceinline__ uint32_t bytes_to_h2_1024(uint32_t v, uint32_t sel) {
@@ -123,9 +137,16 @@ __device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
   asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
-__device__ __forceinline__ uint32_t h2_of(float a) {
-  const __half2 h = __float2half2_rn(a);
-  return *(const uint32_t*)&h;
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// the small integer N (twice, as two halves) without a conversion: 1024 + N has the bits 0x6400 | N
+__device__ __forceinline__ uint32_t small_h2(uint32_t n) {
+  uint32_t v = 0x64006400u | (n * 0x10001u);
+  asm("add.rn.f16x2 %0, %0, %1;" : "+r"(v) : "r"(0xe400e400u));  // - 1024
+  return v;
 }
 
 // 4 bytes global -> shared, asynchronously (both addresses 4-byte aligned)
@@ -138,129 +159,105 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// the small integer N (twice, as two halves) without a conversion: 1024 + N has the bits 0x6400 | N
-__device__ __forceinline__ uint32_t small_h2(uint32_t n) {
-  uint32_t v = 0x64006400u | (n * 0x10001u);
-  asm("add.rn.f16x2 %0, %0, %1;" : "+r"(v) : "r"(0xe400e400u));  // - 1024
-  return v;
-}
-__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-// A warp's lanes are 32 consecutive weight rows writing the same 16-byte chunk index: the swizzle
-// spreads every eight rows over all the banks, so the stores do not collide.
-//
-// IQ2_XXS: one K step = two sub-blocks W[0..3] = (indices, signs + scale) x 2; the 64 integers
-// grid * sign * (2 LS + 1) (at most 43 * 31: exact in fp16).  The block's float part is d / 8
-// (src/avx2.lisp:77-110 takes the products this way).  GRID points at this lane's copy of the grid
-// (sixteen interleaved copies: entry e of copy c at [16 e + c], so the sixteen lanes of a 64-bit
-// request never share a bank); SGN at this lane's copy of the table that turns four sign bits into
-// the sign bits of two pairs of halves (entry x of copy c at [32 x + c]).  The eighth sign of a
-// group is the parity of the seven stored ones (ksigns_iq2xs[i] = i | parity(i) << 7).
-// All the look-ups of a sub-block are issued before its first store: the compiler may not move a
-// shared-memory load over a shared-memory store by itself.
-__device__ __forceinline__ void b_iq2xxs(const uint32_t* w, u8* tile, int row, const uint2* grid, const uint2* sgn) {
+// ---- the weights' integer parts, 32 at a time, as 16 words of two halves -----------------
+// IQ2_XXS: one sub-block (IDX: four grid indices; AUX: four groups of seven signs, and the scale):
+// the 32 integers grid * sign * (2 LS + 1) (at most 43 * 31: exact in fp16).  The block's float
+// part is d / 8 (src/avx2.lisp:77-110 takes the products this way).  GRID points at this lane's copy
+// of the grid (sixteen interleaved copies: entry e of copy c at [16 e + c], so the sixteen lanes of
+// a 64-bit request never share a bank); SGN at this lane's copy of the table that turns four sign
+// bits into the sign bits of two pairs of halves (entry x of copy c at [32 x + c]).  The eighth
+// sign of a group is the parity of the seven stored ones (ksigns_iq2xs[i] = i | parity(i) << 7).
+__device__ __forceinline__ void w_iq2xxs(uint32_t idx, uint32_t aux, const uint2* grid, const uint2* sgn, uint32_t* out) {
+  // (1024 + g) * s - 1024 s = g * s
+  const uint32_t s2 = small_h2(2 * (aux >> 28) + 1), bias = hmul2(s2, 0xe400e400u /* -1024 */);
+  uint2 g[4], ml[4], mh[4];
 #pragma unroll
-  for (int sb = 0; sb < 2; ++sb) {
-    const uint32_t idx = w[2 * sb], aux = w[2 * sb + 1];
-    // (1024 + g) * s - 1024 s = g * s
-    const uint32_t s2 = small_h2(2 * (aux >> 28) + 1), bias = hmul2(s2, 0xe400e400u /* -1024 */);
-    uint2 g[4], ml[4], mh[4];
+  for (int l = 0; l < 4; ++l) {
+    const uint32_t s7 = (aux >> (7 * l)) & 127u;
+    g[l] = grid[16 * ((idx >> (8 * l)) & 0xff)];
+    ml[l] = sgn[32 * (s7 & 15u)];
+    mh[l] = sgn[32 * ((s7 >> 4) | ((__popc(s7) & 1u) << 3))];
+  }
 #pragma unroll
-    for (int l = 0; l < 4; ++l) {
-      const uint32_t s7 = (aux >> (7 * l)) & 127u;
-      g[l] = grid[16 * ((idx >> (8 * l)) & 0xff)];
-      ml[l] = sgn[32 * (s7 & 15u)];
-      mh[l] = sgn[32 * ((s7 >> 4) | ((__popc(s7) & 1u) << 3))];
-    }
-#pragma unroll
-    for (int l = 0; l < 4; ++l)
-      store_chunk(tile, row, 4 * sb + l,
-                  make_uint4(hfma2(bytes_to_h2_1024(g[l].x, 0x4140), s2, bias) ^ ml[l].x,
-                             hfma2(bytes_to_h2_1024(g[l].x, 0x4342), s2, bias) ^ ml[l].y,
-                             hfma2(bytes_to_h2_1024(g[l].y, 0x4140), s2, bias) ^ mh[l].x,
-                             hfma2(bytes_to_h2_1024(g[l].y, 0x4342), s2, bias) ^ mh[l].y));
+  for (int l = 0; l < 4; ++l) {
+    out[4 * l] = hfma2(bytes_to_h2_1024(g[l].x, 0x4140), s2, bias) ^ ml[l].x;
+    out[4 * l + 1] = hfma2(bytes_to_h2_1024(g[l].x, 0x4342), s2, bias) ^ ml[l].y;
+    out[4 * l + 2] = hfma2(bytes_to_h2_1024(g[l].y, 0x4140), s2, bias) ^ mh[l].x;
+    out[4 * l + 3] = hfma2(bytes_to_h2_1024(g[l].y, 0x4342), s2, bias) ^ mh[l].y;
   }
 }
 
-// Q2_K: the K step of half HALF128 (its 32 quant bytes Q) at shifts k = 2h + kk, kk = 0, 1; the 64
-// integers (scale & 15) * q (at most 45); chunk 4 kk + 2 half16 + c holds bytes 16 half16 + 8 c .. +7
-// at shift k.  SC4: the K step's four scale bytes (shift-major, then the half of 16).
-__device__ __forceinline__ void b_q2k(const uint32_t* q, uint32_t sc4, int h, u8* tile, int row) {
+// Q2_K: the 32 weights at shift K of a half's 32 quant bytes Q: (scale & 15) * q (at most 45), the
+// scales SC_LO for the first sixteen and SC_HI for the rest (src/kquant.lisp:DEQUANTIZE-ROW-Q2-K order).
+__device__ __forceinline__ void w_q2k(const uint32_t* q, int k, uint32_t sc_lo, uint32_t sc_hi, uint32_t* out) {
 #pragma unroll
-  for (int kk = 0; kk < 2; ++kk) {
-    const int k = 2 * h + kk;
+  for (int half = 0; half < 2; ++half) {
+    const uint32_t s2 = small_h2((half ? sc_hi : sc_lo) & 15u), bias = hmul2(s2, 0xe400e400u /* -1024 */);
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const uint32_t scn = (sc4 >> (8 * (2 * kk + half))) & 15u;
-      const uint32_t s2 = small_h2(scn), bias = hmul2(s2, 0xe400e400u /* -1024 */);
-      const uint32_t w0 = (q[4 * half] >> (2 * k)) & 0x03030303u, w1 = (q[4 * half + 1] >> (2 * k)) & 0x03030303u;
-      const uint32_t w2 = (q[4 * half + 2] >> (2 * k)) & 0x03030303u, w3 = (q[4 * half + 3] >> (2 * k)) & 0x03030303u;
-      const int cp = 2 * kk + half;
-      store_chunk(tile, row, 2 * cp,
-                  make_uint4(hfma2(bytes_to_h2_1024(w0, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w0, 0x4342), s2, bias),
-                             hfma2(bytes_to_h2_1024(w1, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w1, 0x4342), s2, bias)));
-      store_chunk(tile, row, 2 * cp + 1,
-                  make_uint4(hfma2(bytes_to_h2_1024(w2, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w2, 0x4342), s2, bias),
-                             hfma2(bytes_to_h2_1024(w3, 0x4140), s2, bias), hfma2(bytes_to_h2_1024(w3, 0x4342), s2, bias)));
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t v = (q[4 * half + i] >> (2 * k)) & 0x03030303u;
+      out[8 * half + 2 * i] = hfma2(bytes_to_h2_1024(v, 0x4140), s2, bias);
+      out[8 * half + 2 * i + 1] = hfma2(bytes_to_h2_1024(v, 0x4342), s2, bias);
     }
   }
 }
-// Q2_K: eight mins (scale bytes M0, M1 >> 4) as chunk H of the "mins" tile
-__device__ __forceinline__ void b_q2k_mins(uint32_t m0, uint32_t m1, int h, u8* tile, int row) {
+// Q2_K: eight mins (scale bytes M0, M1 >> 4) as four words
+__device__ __forceinline__ void w_q2k_mins(uint32_t m0, uint32_t m1, uint32_t* v) {
   const uint32_t lo = (m0 >> 4) & 0x0f0f0f0fu, hi = (m1 >> 4) & 0x0f0f0f0fu;
   const uint32_t k1024 = 0xe400e400u;  // -1024 twice
-  uint32_t v[4];
   v[0] = bytes_to_h2_1024(lo, 0x4140); v[1] = bytes_to_h2_1024(lo, 0x4342);
   v[2] = bytes_to_h2_1024(hi, 0x4140); v[3] = bytes_to_h2_1024(hi, 0x4342);
 #pragma unroll
   for (int i = 0; i < 4; ++i) asm("add.rn.f16x2 %0, %0, %1;" : "+r"(v[i]) : "r"(k1024));
-  store_chunk(tile, row, h, make_uint4(v[0], v[1], v[2], v[3]));
 }
 
-// K steps per 256-wide block: four of the quants; for Q2_K a fifth whose A tile holds the
-// activations' sums of 16 and whose B tile holds the mins (one K = 16 MMA into a second
-// accumulator).
-// PW: 4-byte words of a row's raw block in shared memory (IQ2_XXS: the 66 bytes from the 4-byte boundary at or
-// before them; an odd count, so that a warp's rows fall in different banks).
+// Per format.  SPB: X tiles per 256-wide block: four K steps; for Q2_K a fifth that holds the
+// activations' sums of 16, multiplied with the mins (one K = 16 MMA into a second accumulator).
+// PW: 4-byte words of a row's raw block in shared memory (IQ2_XXS: the 66 bytes from the 4-byte
+// boundary at or before them; an odd count, so that a warp's rows fall in different banks).
+// Tensor memory, 512 columns: accumulators D[2] at 0 and 128 (a column = a row of X); then
+//   IQ2_XXS  the A ring, 8 K steps x 32 columns, at 256
+//   Q2_K     the mins' accumulator at 256; the A ring, 3 K steps, at 384; the mins' A, 2 x 8 columns, at 480
 template <int FMT> struct MmGeom {
-  static constexpr int SPB = FMT == ILL_Q2_K ? 5 : 4, ACCS = FMT == ILL_Q2_K ? 2 : 1, PW = FMT == ILL_Q2_K ? 21 : 17;
-  static constexpr int BB = FMT == ILL_Q2_K ? 84 : 66;
+  static constexpr int SPB = FMT == ILL_Q2_K ? 5 : 4, PW = FMT == ILL_Q2_K ? 21 : 17, BB = FMT == ILL_Q2_K ? 84 : 66;
+  static constexpr int NSLOT = FMT == ILL_Q2_K ? 3 : 8;
+  static constexpr uint32_t A_COL = FMT == ILL_Q2_K ? 384 : 256, DM_COL = 256, AM_COL = 480;
   static constexpr uint32_t RAW_BYTES = 128 * PW * 4;
-  static constexpr size_t SMEM = (size_t)(MM_NA + SPB) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
-                                 512 /* barriers */ + 4096 /* scales */ + 2304 /* experts' first tiles */ +
-                                 (FMT == ILL_IQ2_XXS ? 16 * 2048 + 4096 : 0) /* tables */ + 1024 /* alignment */;
+  static constexpr size_t SMEM = (size_t)MM_NX * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
+                                 512 /* barriers */ + 4 * 256 * 4 /* weight scales */ + MM_XSC * 128 * 4 /* X scales */ +
+                                 2304 /* experts' first tiles */ + (FMT == ILL_IQ2_XXS ? 16 * 2048 + 4096 : 0) /* tables */ +
+                                 1024 /* alignment */;
 };
 
 template <int FMT>
 __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant__ CUtensorMap xmap,
                                                            const __grid_constant__ CUtensorMap emap, const MmParams p) {
   typedef MmGeom<FMT> G;
-  constexpr int SPB = G::SPB, ACCS = G::ACCS, PW = G::PW, BB = G::BB;
-  constexpr uint32_t TMEM_COLS = 2 * ACCS * MM_BN;  // two buffers of accumulators
+  constexpr int SPB = G::SPB, PW = G::PW, BB = G::BB, NSLOT = G::NSLOT;
+  constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ __align__(1024) u8 smem_raw[];
-  // [A ring][B stages: one per K step of a block] (each tile 1024-byte aligned, as the 128-byte swizzle
-  // needs), the ring of raw blocks, then barriers, scales, tables
+  // [X ring] (each tile 1024-byte aligned, as the 128-byte swizzle needs), the ring of raw blocks, then
+  // barriers, scales, tables
   u8* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  u8* a_tiles = smem;
-  u8* b_tiles = smem + MM_NA * MM_TILE_BYTES;
-  uint32_t* raw = (uint32_t*)(smem + (MM_NA + SPB) * MM_TILE_BYTES);
+  u8* x_tiles = smem;
+  uint32_t* raw = (uint32_t*)(smem + MM_NX * MM_TILE_BYTES);
   u8* tail = (u8*)raw + MM_RS * G::RAW_BYTES + 16;
-  uint64_t* full_a = (uint64_t*)tail;            // [NA] TMA bytes landed
-  uint64_t* empty_a = full_a + MM_NA;            // [NA] the MMAs that read the stage completed
-  uint64_t* full_b = empty_a + MM_NA;            // [SPB] the dequantizing warps arrived (MM_FULL_B arrivals)
-  uint64_t* empty_b = full_b + SPB;              // [SPB] the MMAs that read the stage completed
-  uint64_t* raw_full = empty_b + SPB;            // [RS] the raw-load lanes' copies landed
+  uint64_t* full_x = (uint64_t*)tail;            // [NX] TMA bytes landed
+  uint64_t* empty_x = full_x + MM_NX;            // [NX] the MMAs that read the stage completed
+  uint64_t* full_t = empty_x + MM_NX;            // [NSLOT] a K step of A is in tensor memory (4 warps)
+  uint64_t* empty_t = full_t + NSLOT;            // [NSLOT] the MMAs that read it completed
+  uint64_t* full_m = empty_t + NSLOT;            // [2] Q2_K: a block's mins are in tensor memory (8 warps)
+  uint64_t* empty_m = full_m + 2;                // [2] the MMA that read them completed
+  uint64_t* raw_full = empty_m + 2;              // [RS] the raw-load lanes' copies landed
   uint64_t* raw_empty = raw_full + MM_RS;        // [RS] the dequantizing warps have read the stage
   uint64_t* acc_full = raw_empty + MM_RS;        // [2] a block's MMAs completed
   uint64_t* acc_free = acc_full + 2;             // [2] the drain warps read the buffer
-  uint32_t* tmem_slot = (uint32_t*)(acc_free + 2);
-  float* wsc = (float*)(tail + 512);             // [4 blocks in flight][2: d, dmin][128 rows]
-  int* tile_first = (int*)(tail + 512 + 4096);   // [ne + 1] first row tile of each expert; the total
-  uint2* iq_grid = (uint2*)(tail + 512 + 4096 + 2304);  // sixteen interleaved copies
+  uint64_t* accm_free = acc_free + 2;            // [1] Q2_K: the drain warps read the mins' accumulator
+  uint32_t* tmem_slot = (uint32_t*)(accm_free + 1);
+  float* wsc = (float*)(tail + 512);             // [4 blocks in flight][2: d, dmin][128 weight rows]
+  float* xsc = wsc + 4 * 256;                    // [XSC blocks][128 rows of X] the activations' block scales
+  int* tile_first = (int*)(xsc + MM_XSC * 128);  // [ne + 1] first row tile of each expert; the total
+  uint2* iq_grid = (uint2*)((u8*)tile_first + 2304);  // sixteen interleaved copies
   uint2* iq_sgn = iq_grid + 16 * 256;            // [16 nibbles][32 copies]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -285,10 +282,12 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     if (lane == 0) tile_first[p.ne] = before;  // row tiles in all
   }
   if (tid == 32) {
-    for (int s = 0; s < MM_NA; ++s) { mbar_init(&full_a[s], 1); mbar_init(&empty_a[s], 1); }
-    for (int s = 0; s < SPB; ++s) { mbar_init(&full_b[s], MM_FULL_B); mbar_init(&empty_b[s], 1); }
+    for (int s = 0; s < MM_NX; ++s) { mbar_init(&full_x[s], 1); mbar_init(&empty_x[s], 1); }
+    for (int s = 0; s < NSLOT; ++s) { mbar_init(&full_t[s], MM_DQ_WARPS / 2); mbar_init(&empty_t[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&full_m[s], MM_DQ_WARPS); mbar_init(&empty_m[s], 1); }
     for (int s = 0; s < MM_RS; ++s) { mbar_init(&raw_full[s], 32 * MM_LD_WARPS); mbar_init(&raw_empty[s], MM_DQ_WARPS); }
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_free[b], MM_DR_WARPS); }
+    mbar_init(accm_free, MM_DR_WARPS);
     mbar_fence_init();
   }
   if (FMT == ILL_IQ2_XXS) {
@@ -330,55 +329,68 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   if (warp == 0) {
     // ---- TMA producer of the X tiles
     if (lane == 0) {
-      int g_sa = 0;  // A stages issued so far by this CTA
+      int g_sx = 0;  // X stages issued so far by this CTA
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         int expert, row0, nvalid, nt;
         locate(tile, expert, row0, nvalid, nt);
-        for (int st = 0; st < nkb * SPB; ++st, ++g_sa) {
-          const int s = g_sa % MM_NA, use = g_sa / MM_NA;
-          if (use > 0 && !mbar_wait(&empty_a[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY, 100)) { ok = false; break; }
+        for (int st = 0; st < nkb * SPB; ++st, ++g_sx) {
+          const int s = g_sx % MM_NX, use = g_sx / MM_NX;
+          if (use > 0 && !mbar_wait(&empty_x[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY, 100)) { ok = false; break; }
           const int kb = st / SPB, j = st - kb * SPB;
-          mbar_expect_tx(&full_a[s], MM_TILE_BYTES);
-          if (j < 4) tma_load_2d(a_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &full_a[s]);
-          else tma_load_2d(a_tiles + s * MM_TILE_BYTES, &emap, kb * MM_BK, row0, &full_a[s]);  // the sums of 16
+          mbar_expect_tx(&full_x[s], MM_TILE_BYTES);
+          if (j < 4) tma_load_2d(x_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &full_x[s]);
+          else tma_load_2d(x_tiles + s * MM_TILE_BYTES, &emap, kb * MM_BK, row0, &full_x[s]);  // the sums of 16
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer
     if (lane == 0) {
-      // fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
-      const uint32_t idesc = (1u << 4) | ((uint32_t)(MM_BN >> 3) << 17) | ((uint32_t)(MM_BM >> 4) << 24);
-      int g_sa = 0, g_kb = 0;  // A stages and blocks consumed so far by this CTA
+      int g_sx = 0, g_st = 0, g_kb = 0;  // X stages, K steps of A and blocks consumed so far by this CTA
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        int expert, row0, nvalid, nt;
+        locate(tile, expert, row0, nvalid, nt);
+        // fp32 accumulate, fp16 A and B, both K-major, M = 128 weight rows, N = the tile's rows of X up to 16
+        const int nmma = max(16, (nvalid + 15) & ~15);
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(nmma >> 3) << 17) | ((uint32_t)(MM_BN >> 4) << 24);
         for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
           const int b = g_kb & 1;
           if (g_kb >= 2 && !mbar_wait(&acc_free[b], (uint32_t)(g_kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t d1 = tmem_base + (uint32_t)(b * ACCS * MM_BN);
-          for (int j = 0; j < SPB; ++j, ++g_sa) {
-            const int s = g_sa % MM_NA;
-            if (!mbar_wait(&full_a[s], (uint32_t)(g_sa / MM_NA) & 1u, p.status, ST_MM_WAIT_FULL) ||
-                !mbar_wait(&full_b[j], (uint32_t)g_kb & 1u, p.status, ST_MM_WAIT_FULL + 1)) { ok = false; break; }
+          const uint32_t d1 = tmem_base + (uint32_t)(b * MM_BM);
+          for (int j = 0; j < 4; ++j, ++g_sx, ++g_st) {
+            const int s = g_sx % MM_NX, slot = g_st % NSLOT;
+            if (!mbar_wait(&full_x[s], (uint32_t)(g_sx / MM_NX) & 1u, p.status, ST_MM_WAIT_FULL) ||
+                !mbar_wait(&full_t[slot], (uint32_t)(g_st / NSLOT) & 1u, p.status, ST_MM_WAIT_FULL + 1)) { ok = false; break; }
             tc_fence_after();
-            const uint64_t ad = umma_desc(a_tiles + s * MM_TILE_BYTES), bd = umma_desc(b_tiles + j * MM_TILE_BYTES);
-            if (j < 4) {
+            const uint64_t xdsc = umma_desc(x_tiles + s * MM_TILE_BYTES);
+            const uint32_t a0 = tmem_base + G::A_COL + 32u * slot;
 #pragma unroll
-              for (int k = 0; k < MM_BK / 16; ++k)  // 32 bytes further along K inside the swizzle atom each time
-                umma_f16(d1, ad + 2 * k, bd + 2 * k, idesc, (j | k) ? 1u : 0u);
-            } else {
-              umma_f16(d1 + MM_BN, ad, bd, idesc, 0u);  // mins x sums of 16: one K = 16 product
-            }
-            umma_commit(&empty_a[s]);  // both stages are free when these MMAs are done
-            umma_commit(&empty_b[j]);
+            for (int k = 0; k < MM_BK / 16; ++k)  // 16 of K: 8 columns of A, 32 bytes inside X's swizzle atom
+              umma_f16_ts(d1, a0 + 8 * k, xdsc + 2 * k, idesc, (j | k) ? 1u : 0u);
+            umma_commit(&empty_x[s]);  // the X stage and the A slot are free when these MMAs are done
+            umma_commit(&empty_t[slot]);
           }
-          if (ok) umma_commit(&acc_full[b]);
+          if (!ok) break;
+          if constexpr (FMT == ILL_Q2_K) {
+            const int s = g_sx % MM_NX, sm = g_kb & 1;
+            if (!mbar_wait(&full_x[s], (uint32_t)(g_sx / MM_NX) & 1u, p.status, ST_MM_WAIT_FULL) ||
+                !mbar_wait(&full_m[sm], (uint32_t)(g_kb >> 1) & 1u, p.status, ST_MM_WAIT_FULL + 3) ||
+                (g_kb >= 1 && !mbar_wait(accm_free, (uint32_t)(g_kb - 1) & 1u, p.status, ST_MM_WAIT_EPI + 2))) { ok = false; break; }
+            tc_fence_after();
+            // mins x sums of 16: one K = 16 product into the mins' accumulator
+            umma_f16_ts(tmem_base + G::DM_COL, tmem_base + G::AM_COL + 8u * sm, umma_desc(x_tiles + s * MM_TILE_BYTES), idesc, 0u);
+            umma_commit(&empty_x[s]);
+            umma_commit(&empty_m[sm]);
+            ++g_sx;
+          }
+          umma_commit(&acc_full[b]);
         }
       }
     }
   } else if (warp < 2 + MM_LD_WARPS) {
-    // ---- warps 2, 3 copy each block's raw bytes (128 rows x PW words) into the raw ring, 4 bytes a
-    // lane at a time so that a warp's requests touch two or three rows, not thirty-two
+    // ---- warps 2, 3 copy each block's raw bytes (128 weight rows x PW words) into the raw ring, 4
+    // bytes a lane at a time so that a warp's requests touch two or three rows, not thirty-two; and
+    // the block's scale of each of the tile's rows of X.
     // Lane L < RPS * PW owns word L % PW of rows L / PW, + RPS, + 2 RPS, ...
     const int L = (warp - 2) * 32 + lane;
     constexpr int NL = 32 * MM_LD_WARPS, RPS = NL / PW;  // rows a step
@@ -389,11 +401,21 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       locate(tile, expert, row0, nvalid, nt);
       const u8* wbase = (const u8*)(uintptr_t)p.ptrs[expert] + p.add + (long long)nt * MM_BN * p.row_bytes;
       const int rows_here = r_first < RPS ? min(MM_BN, p.nrows - nt * MM_BN) : 0;
+      // the tokens of the tile's rows L, L + NL of X (a row past the tile's last takes the first row's)
+      const float* xdp[128 / NL];
+#pragma unroll
+      for (int i = 0; i < 128 / NL; ++i) {
+        const long long place = (long long)row0 + (L + i * NL < nvalid ? L + i * NL : 0);
+        const long long tok = p.map ? (long long)p.map[place] : place;
+        xdp[i] = p.xd + tok * nkb;
+      }
       for (int kb = 0; kb < nkb; ++kb, ++g_kb) {
         const int s = g_kb % MM_RS, use = g_kb / MM_RS;
         bool w_ok = true;
         if (use > 0) w_ok = mbar_wait(&raw_empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 2, 200);
         if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
+#pragma unroll
+        for (int i = 0; i < 128 / NL; ++i) cp_async4(xsc + (g_kb % MM_XSC) * 128 + L + i * NL, xdp[i] + kb);
         uint32_t* dst = raw + s * (G::RAW_BYTES / 4) + r_first * PW + word;
         const u8* src = wbase + (long long)r_first * p.row_bytes + kb * BB;
 #pragma unroll 4
@@ -409,61 +431,62 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   } else if (warp < 2 + MM_LD_WARPS + MM_DR_WARPS) {
     // ---- warps 4..11 drain the accumulators block by block, scaling each block's integer sums by the
     // block's float scales, and store the finished tile.  A warp reads the 32 tensor-memory lanes
-    // its number gives it (warp % 4) and half of the columns.
+    // its number gives it (warp % 4: 32 weight rows) and half of the columns (64 rows of X).
     const int q = warp & 3;
-    const int m = q * 32 + lane;                   // accumulator row = row of X in the tile
-    const int c0 = ((warp - 2 - MM_LD_WARPS) >> 2) * 64;  // columns c0 .. c0 + 63
+    const int m = q * 32 + lane;                   // accumulator lane = weight row in the tile
+    const int c0 = ((warp - 2 - MM_LD_WARPS) >> 2) * 64;  // columns (rows of X) c0 .. c0 + 63
     int d_kb = 0;                                  // blocks drained so far by this CTA
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int expert, row0, nvalid, nt;
       locate(tile, expert, row0, nvalid, nt);
-      const long long place = (long long)row0 + m;
-      const long long tok = place < p.total_rows ? (p.map ? (long long)p.map[place] : place) : -1;
-      const float* xdr = p.xd + (tok >= 0 ? tok : 0) * nkb;
       float out[64];
 #pragma unroll
       for (int i = 0; i < 64; ++i) out[i] = 0.0f;
-      float dx_next = tok >= 0 ? __ldg(xdr) : 0.0f;
       for (int kb = 0; kb < nkb; ++kb, ++d_kb) {
-        const float dx = dx_next;
-        if (kb + 1 < nkb && tok >= 0) dx_next = __ldg(xdr + kb + 1);
         const int b = d_kb & 1;
         const bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC, 100);
         if (!__all_sync(0xffffffffu, e_ok)) { ok = false; break; }
         tc_fence_after();
-        if (32 * q < nvalid) {  // a quarter of the tile with no valid row is not read
-          const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * ACCS * MM_BN + c0);
-          const float* wd = wsc + (d_kb & 3) * 256 + c0;
+        const float dw = wsc[(d_kb & 3) * 256 + m];
+        const float* xs = xsc + (d_kb % MM_XSC) * 128 + c0;
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        if constexpr (FMT == ILL_Q2_K) {
+          // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
+          const float dm = wsc[(d_kb & 3) * 256 + 128 + m];
 #pragma unroll
           for (int part = 0; part < 2; ++part) {
-            uint32_t v[32];
-            tmem_ld32(t0 + 32 * part, v);
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const float4 dw = *(const float4*)(wd + 32 * part + i);
-              // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum, the 1/8 at the end;
-              // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
-              const float s0 = FMT == ILL_IQ2_XXS ? __fmul_rn(dw.x, dx) : __fmul_rn(dx, dw.x);
-              const float s1 = FMT == ILL_IQ2_XXS ? __fmul_rn(dw.y, dx) : __fmul_rn(dx, dw.y);
-              const float s2 = FMT == ILL_IQ2_XXS ? __fmul_rn(dw.z, dx) : __fmul_rn(dx, dw.z);
-              const float s3 = FMT == ILL_IQ2_XXS ? __fmul_rn(dw.w, dx) : __fmul_rn(dx, dw.w);
-              float* o = out + 32 * part + i;
-              o[0] = fmaf(s0, __uint_as_float(v[i]), o[0]);
-              o[1] = fmaf(s1, __uint_as_float(v[i + 1]), o[1]);
-              o[2] = fmaf(s2, __uint_as_float(v[i + 2]), o[2]);
-              o[3] = fmaf(s3, __uint_as_float(v[i + 3]), o[3]);
-            }
-            if constexpr (FMT == ILL_Q2_K) {
-              tmem_ld32(t0 + MM_BN + 32 * part, v);
+            if (c0 + 32 * part < nvalid) {  // columns past the tile's last row of X were not computed
+              uint32_t v[32];
+              tmem_ld32(t0 + G::DM_COL + 32 * part, v);
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
-                const float4 dm = *(const float4*)(wd + 128 + 32 * part + i);
+                const float4 dx = *(const float4*)(xs + 32 * part + i);
                 float* o = out + 32 * part + i;
-                o[0] = fmaf(-__fmul_rn(dx, dm.x), __uint_as_float(v[i]), o[0]);
-                o[1] = fmaf(-__fmul_rn(dx, dm.y), __uint_as_float(v[i + 1]), o[1]);
-                o[2] = fmaf(-__fmul_rn(dx, dm.z), __uint_as_float(v[i + 2]), o[2]);
-                o[3] = fmaf(-__fmul_rn(dx, dm.w), __uint_as_float(v[i + 3]), o[3]);
+                o[0] = fmaf(-__fmul_rn(dx.x, dm), __uint_as_float(v[i]), o[0]);
+                o[1] = fmaf(-__fmul_rn(dx.y, dm), __uint_as_float(v[i + 1]), o[1]);
+                o[2] = fmaf(-__fmul_rn(dx.z, dm), __uint_as_float(v[i + 2]), o[2]);
+                o[3] = fmaf(-__fmul_rn(dx.w, dm), __uint_as_float(v[i + 3]), o[3]);
               }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(accm_free);
+        }
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          if (c0 + 32 * part < nvalid) {
+            uint32_t v[32];
+            tmem_ld32(t0 + b * MM_BM + 32 * part, v);
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float4 dx = *(const float4*)(xs + 32 * part + i);
+              // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum, the 1/8 at the end
+              float* o = out + 32 * part + i;
+              o[0] = fmaf(__fmul_rn(dw, dx.x), __uint_as_float(v[i]), o[0]);
+              o[1] = fmaf(__fmul_rn(dw, dx.y), __uint_as_float(v[i + 1]), o[1]);
+              o[2] = fmaf(__fmul_rn(dw, dx.z), __uint_as_float(v[i + 2]), o[2]);
+              o[3] = fmaf(__fmul_rn(dw, dx.w), __uint_as_float(v[i + 3]), o[3]);
             }
           }
         }
@@ -471,38 +494,25 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_free[b]);
       }
-      if (ok && m < nvalid) {
-        float* yrow = p.y + place * p.y_stride + (long long)nt * MM_BN + c0;
+      const int n = nt * MM_BN + m;
+      if (ok && n < p.nrows) {
+        float* ycol = p.y + ((long long)row0 + c0) * p.y_stride + n;
         const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
 #pragma unroll
-        for (int jj = 0; jj < 64; jj += 4) {
-          const int n0 = nt * MM_BN + c0 + jj;
-          if (n0 + 3 < p.nrows) {
-            *(float4*)(yrow + jj) = make_float4(out[jj] * fin, out[jj + 1] * fin, out[jj + 2] * fin, out[jj + 3] * fin);
-          } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (n0 + e < p.nrows) yrow[jj + e] = out[jj + e] * fin;
-          }
-        }
+        for (int i = 0; i < 64; ++i)
+          if (c0 + i < nvalid) ycol[(long long)i * p.y_stride] = out[i] * fin;
       }
     }
   } else {
-    // ---- warps 12..19 turn the raw blocks into the B tiles: thread (row, h) makes K steps h and
-    // h + 2 of its row, so the warps of h = 0 and of h = 1 fill alternate stages and the tensor core
-    // can start on a block while its second half is still being made.
+    // ---- warps 12..19 turn the raw blocks into the A operand in tensor memory: thread (row, h) makes
+    // K steps h and h + 2 of its weight row, so the warps of h = 0 and of h = 1 fill alternate K
+    // steps and the tensor core can start on a block while its second half is still being made.
     const int t = tid - 32 * (2 + MM_LD_WARPS + MM_DR_WARPS);  // 0..255
     const int row = t & 127, h = t >> 7;
+    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's lanes: rows (warp % 4) * 32 ..
     const uint2* grid = iq_grid + (lane & 15);
     const uint2* sgn = iq_sgn + lane;
     int g_kb = 0;                                  // blocks produced so far by this CTA
-
-    // B stage J (K step J of every block) once the MMAs of the block before are done with it
-    auto stage_wait = [&](int j) -> bool {
-      bool w_ok = true;
-      if (g_kb > 0) w_ok = mbar_wait(&empty_b[j], (uint32_t)(g_kb - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1, 50);
-      return __all_sync(0xffffffffu, w_ok);
-    };
 
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int expert, row0, nvalid, nt;
@@ -518,6 +528,9 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         const uint32_t* rw = raw + rs * (G::RAW_BYTES / 4) + row * PW;
         // this thread's words of the block, then the raw stage is free again
         uint32_t w[FMT == ILL_Q2_K ? 16 : 8], sc[4], dd = 0;
+#pragma unroll
+        for (int i = 0; i < (FMT == ILL_Q2_K ? 16 : 8); ++i) w[i] = 0;
+        sc[0] = sc[1] = sc[2] = sc[3] = 0;
         if (has_row) {
           if constexpr (FMT == ILL_IQ2_XXS) {
             const uint32_t mis = (rowlow + (uint32_t)kb * BB) & 3u;  // 0 or 2
@@ -545,36 +558,52 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         if (lane == 0) mbar_arrive(&raw_empty[rs]);
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
-          const int j = h + 2 * part;
-          if (!stage_wait(j)) { ok = false; break; }
+          const int st = 4 * g_kb + h + 2 * part, slot = st % NSLOT, use = st / NSLOT;
+          bool w_ok = true;
+          if (use > 0) w_ok = mbar_wait(&empty_t[slot], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1, 50);
+          if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
+          tc_fence_after();
           if (part == 0 && h == 0) {
-            // The drain of four blocks back is over: the MMAs that freed this stage were issued after it.
-            float d = 0.0f, dmin = 0.0f;
-            if (has_row) { d = h2f(dd & 0xffff); dmin = h2f(dd >> 16); }
-            wsc[(g_kb & 3) * 256 + row] = d;
-            if (FMT == ILL_Q2_K) wsc[(g_kb & 3) * 256 + 128 + row] = dmin;
+            // The drain of four blocks back is over: the MMAs that freed this slot were issued after it.
+            wsc[(g_kb & 3) * 256 + row] = h2f(dd & 0xffff);
+            if (FMT == ILL_Q2_K) wsc[(g_kb & 3) * 256 + 128 + row] = h2f(dd >> 16);
           }
-          u8* tile_b = b_tiles + j * MM_TILE_BYTES;
-          if (has_row) {
-            if constexpr (FMT == ILL_IQ2_XXS) b_iq2xxs(w + 4 * part, tile_b, row, grid, sgn);
-            else b_q2k(w + 8 * part, sc[2 * part + h], h, tile_b, row);
-          } else {
+          const uint32_t a0 = lane_base + G::A_COL + 32u * slot;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) store_chunk(tile_b, row, c, make_uint4(0, 0, 0, 0));
+          for (int sb = 0; sb < 2; ++sb) {  // 32 weights = 16 columns at a time
+            uint32_t v[16];
+            if constexpr (FMT == ILL_IQ2_XXS) {
+              w_iq2xxs(w[4 * part + 2 * sb], w[4 * part + 2 * sb + 1], grid, sgn, v);
+              if (!has_row) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = 0;
+              }
+            } else {
+              // K step h + 2 part: half `part` of the block's quants at shifts 2h and 2h + 1
+              const uint32_t s4 = sc[2 * part + h];
+              w_q2k(w + 8 * part, 2 * h + sb, s4 >> (16 * sb), s4 >> (16 * sb + 8), v);
+            }
+            tmem_st16(a0 + 16 * sb, v);
           }
-          fence_async_smem();  // the tensor core reads the tile through the async proxy
+          tmem_st_wait();
+          tc_fence_before();
           __syncwarp();
-          if (lane < 2) mbar_arrive(&full_b[j]);  // four warps x two arrivals
+          if (lane == 0) mbar_arrive(&full_t[slot]);
         }
-        if constexpr (SPB == 5) {
+        if constexpr (FMT == ILL_Q2_K) {
           if (!ok) break;
-          if (!stage_wait(4)) { ok = false; break; }
-          u8* tile_b = b_tiles + 4 * MM_TILE_BYTES;
-          if (has_row) b_q2k_mins(sc[2 * h], sc[2 * h + 1], h, tile_b, row);
-          else store_chunk(tile_b, row, h, make_uint4(0, 0, 0, 0));
-          fence_async_smem();
+          const int sm = g_kb & 1;
+          bool w_ok = true;
+          if (g_kb >= 2) w_ok = mbar_wait(&empty_m[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 50);
+          if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
+          tc_fence_after();
+          uint32_t v[4];
+          w_q2k_mins(sc[2 * h], sc[2 * h + 1], v);  // half h's eight mins: K = 8h .. 8h + 7 of the 16
+          tmem_st4(lane_base + G::AM_COL + 8u * sm + 4u * h, v);
+          tmem_st_wait();
+          tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&full_b[4]);  // eight warps x one arrival
+          if (lane == 0) mbar_arrive(&full_m[sm]);
         }
       }
     }
