@@ -126,6 +126,12 @@ __device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t* v) {
                "r"(v[3])
                : "memory");
 }
+// true in one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // two unsigned bytes (byte positions B0, B1 of V) as the halves 1024 + byte
@@ -260,7 +266,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   uint2* iq_grid = (uint2*)((u8*)tile_first + 2304);  // sixteen interleaved copies
   uint2* iq_sgn = iq_grid + 16 * 256;            // [16 nibbles][32 copies]
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // the warp number through a shuffle: the compiler then knows that the role branches are warp-uniform
+  const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
 
   // ---- once per CTA: the experts' row tiles counted (first tile of each expert, in shared memory),
   // barriers, tables, tensor memory.  The CTA then walks tiles blockIdx.x, + gridDim.x, ...
@@ -304,7 +311,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
   const int nkb = p.ncols / 256;
   const int ntn = (p.nrows + MM_BN - 1) / MM_BN;
@@ -344,46 +351,58 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer
-    if (lane == 0) {
+    // ---- MMA issuer: the whole warp walks the loop (so that addresses and descriptors stay in uniform
+    // registers) and one elected lane issues
+    {
       int g_sx = 0, g_st = 0, g_kb = 0;  // X stages, K steps of A and blocks consumed so far by this CTA
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         int expert, row0, nvalid, nt;
         locate(tile, expert, row0, nvalid, nt);
+        nvalid = __shfl_sync(0xffffffffu, nvalid, 0);
         // fp32 accumulate, fp16 A and B, both K-major, M = 128 weight rows, N = the tile's rows of X up to 16
         const int nmma = max(16, (nvalid + 15) & ~15);
         const uint32_t idesc = (1u << 4) | ((uint32_t)(nmma >> 3) << 17) | ((uint32_t)(MM_BN >> 4) << 24);
         for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
           const int b = g_kb & 1;
-          if (g_kb >= 2 && !mbar_wait(&acc_free[b], (uint32_t)(g_kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI)) { ok = false; break; }
+          if (g_kb >= 2) ok = __all_sync(0xffffffffu, mbar_wait(&acc_free[b], (uint32_t)(g_kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI));
+          if (!ok) break;
           const uint32_t d1 = tmem_base + (uint32_t)(b * MM_BM);
           for (int j = 0; j < 4; ++j, ++g_sx, ++g_st) {
             const int s = g_sx % MM_NX, slot = g_st % NSLOT;
-            if (!mbar_wait(&full_x[s], (uint32_t)(g_sx / MM_NX) & 1u, p.status, ST_MM_WAIT_FULL) ||
-                !mbar_wait(&full_t[slot], (uint32_t)(g_st / NSLOT) & 1u, p.status, ST_MM_WAIT_FULL + 1)) { ok = false; break; }
+            ok = __all_sync(0xffffffffu, mbar_wait(&full_x[s], (uint32_t)(g_sx / MM_NX) & 1u, p.status, ST_MM_WAIT_FULL) &&
+                                             mbar_wait(&full_t[slot], (uint32_t)(g_st / NSLOT) & 1u, p.status, ST_MM_WAIT_FULL + 1));
+            if (!ok) break;
             tc_fence_after();
             const uint64_t xdsc = umma_desc(x_tiles + s * MM_TILE_BYTES);
             const uint32_t a0 = tmem_base + G::A_COL + 32u * slot;
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < MM_BK / 16; ++k)  // 16 of K: 8 columns of A, 32 bytes inside X's swizzle atom
-              umma_f16_ts(d1, a0 + 8 * k, xdsc + 2 * k, idesc, (j | k) ? 1u : 0u);
-            umma_commit(&empty_x[s]);  // the X stage and the A slot are free when these MMAs are done
-            umma_commit(&empty_t[slot]);
+              for (int k = 0; k < MM_BK / 16; ++k)  // 16 of K: 8 columns of A, 32 bytes inside X's swizzle atom
+                umma_f16_ts(d1, a0 + 8 * k, xdsc + 2 * k, idesc, (j | k) ? 1u : 0u);
+              umma_commit(&empty_x[s]);  // the X stage and the A slot are free when these MMAs are done
+              umma_commit(&empty_t[slot]);
+            }
+            __syncwarp();
           }
           if (!ok) break;
           if constexpr (FMT == ILL_Q2_K) {
             const int s = g_sx % MM_NX, sm = g_kb & 1;
-            if (!mbar_wait(&full_x[s], (uint32_t)(g_sx / MM_NX) & 1u, p.status, ST_MM_WAIT_FULL) ||
-                !mbar_wait(&full_m[sm], (uint32_t)(g_kb >> 1) & 1u, p.status, ST_MM_WAIT_FULL + 3) ||
-                (g_kb >= 1 && !mbar_wait(accm_free, (uint32_t)(g_kb - 1) & 1u, p.status, ST_MM_WAIT_EPI + 2))) { ok = false; break; }
+            ok = __all_sync(0xffffffffu, mbar_wait(&full_x[s], (uint32_t)(g_sx / MM_NX) & 1u, p.status, ST_MM_WAIT_FULL) &&
+                                             mbar_wait(&full_m[sm], (uint32_t)(g_kb >> 1) & 1u, p.status, ST_MM_WAIT_FULL + 3) &&
+                                             (g_kb < 1 || mbar_wait(accm_free, (uint32_t)(g_kb - 1) & 1u, p.status, ST_MM_WAIT_EPI + 2)));
+            if (!ok) break;
             tc_fence_after();
             // mins x sums of 16: one K = 16 product into the mins' accumulator
-            umma_f16_ts(tmem_base + G::DM_COL, tmem_base + G::AM_COL + 8u * sm, umma_desc(x_tiles + s * MM_TILE_BYTES), idesc, 0u);
-            umma_commit(&empty_x[s]);
-            umma_commit(&empty_m[sm]);
+            if (elect_one()) {
+              umma_f16_ts(tmem_base + G::DM_COL, tmem_base + G::AM_COL + 8u * sm, umma_desc(x_tiles + s * MM_TILE_BYTES), idesc, 0u);
+              umma_commit(&empty_x[s]);
+              umma_commit(&empty_m[sm]);
+            }
+            __syncwarp();
             ++g_sx;
           }
-          umma_commit(&acc_full[b]);
+          if (elect_one()) umma_commit(&acc_full[b]);
+          __syncwarp();
         }
       }
     }
