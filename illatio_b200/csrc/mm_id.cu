@@ -19,10 +19,11 @@
 //               fp32 accumulate) and commits each step back to the producers
 //   warps 2-3   copy W_e's raw blocks and the X rows' block scales into rings in shared memory
 //               (cp.async, coalesced)
-//   warps 4-11  drain the accumulators block by block (tcgen05.ld), scaling each block's integer
+//   warps 4-7   drain the accumulators block by block (tcgen05.ld), scaling each block's integer
 //               sums by the block's float scales; then store the tile (a lane = a weight row, so
 //               the 32 lanes of a warp write 128 contiguous bytes of a row of Y)
-//   warps 12-19 turn the raw blocks into the A operand (two threads a weight row, two K steps each)
+//   warps 8-23  turn the raw blocks into the A operand (four threads a weight row, a K step each)
+// The roles' register needs differ widely, so the warp groups trade registers (setmaxnreg).
 // Every mbarrier wait is bounded; on a time-out the kernel records a code in the status
 // word, skips what depends on the wait, frees its tensor memory and returns.
 //
@@ -42,7 +43,10 @@ constexpr int MM_BK = 64;                              // K step: one 128-byte r
 constexpr int MM_NX = 8;                               // stages of the ring of X tiles
 constexpr int MM_RS = 3;                               // stages of the ring of raw weight blocks
 constexpr int MM_XSC = 16;                             // blocks of X scales kept (the loader runs < 16 blocks ahead of the drain)
-constexpr int MM_DR_WARPS = 8, MM_DQ_WARPS = 8, MM_LD_WARPS = 2;  // drain, dequantize, raw-load warps
+constexpr int MM_DR_WARPS = 4, MM_DQ_WARPS = 16, MM_LD_WARPS = 2;  // drain, dequantize, raw-load warps
+// Registers a thread after the roles part: the four warps of TMA / MMA / raw loads give theirs up, the
+// drain warps (a whole tile's row of 128 sums each) take them
+constexpr int MM_REGS_AUX = 40, MM_REGS_DRAIN = 176, MM_REGS_DQ = 64;
 constexpr int MM_THREADS = 32 * (2 + MM_LD_WARPS + MM_DR_WARPS + MM_DQ_WARPS);  // + the TMA warp and the MMA warp
 constexpr uint32_t MM_TILE_BYTES = MM_BM * MM_BK * 2;  // 16 KB
 
@@ -89,6 +93,19 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
       : "memory");
+}
+// the same with A in shared memory (K-major, 128-byte swizzle)
+__device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// 16-byte chunk C of row ROW of a K-major tile with the 128-byte swizzle
+__device__ __forceinline__ void store_chunk(u8* tile, int row, int c, uint4 v) {
+  *(uint4*)(tile + (row >> 3) * 1024 + (row & 7) * 128 + ((c ^ (row & 7)) << 4)) = v;
 }
 // arrive on BAR once every tcgen05.mma issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -223,13 +240,14 @@ __device__ __forceinline__ void w_q2k_mins(uint32_t m0, uint32_t m1, uint32_t* v
 // boundary at or before them; an odd count, so that a warp's rows fall in different banks).
 // Tensor memory, 512 columns: accumulators D[2] at 0 and 128 (a column = a row of X); then
 //   IQ2_XXS  the A ring, 8 K steps x 32 columns, at 256
-//   Q2_K     the mins' accumulator at 256; the A ring, 3 K steps, at 384; the mins' A, 2 x 8 columns, at 480
+//   Q2_K     the mins' accumulator at 256; the A ring, 4 K steps, at 384 (the mins themselves, a
+//            128 x 16 operand, go through two tiles in shared memory)
 template <int FMT> struct MmGeom {
   static constexpr int SPB = FMT == ILL_Q2_K ? 5 : 4, PW = FMT == ILL_Q2_K ? 21 : 17, BB = FMT == ILL_Q2_K ? 84 : 66;
-  static constexpr int NSLOT = FMT == ILL_Q2_K ? 3 : 8;
-  static constexpr uint32_t A_COL = FMT == ILL_Q2_K ? 384 : 256, DM_COL = 256, AM_COL = 480;
+  static constexpr int NSLOT = FMT == ILL_Q2_K ? 4 : 8;  // a multiple of four: a slot is always written by the same warps
+  static constexpr uint32_t A_COL = FMT == ILL_Q2_K ? 384 : 256, DM_COL = 256;
   static constexpr uint32_t RAW_BYTES = 128 * PW * 4;
-  static constexpr size_t SMEM = (size_t)MM_NX * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
+  static constexpr size_t SMEM = (size_t)(MM_NX + (FMT == ILL_Q2_K ? 2 : 0)) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
                                  512 /* barriers */ + 4 * 256 * 4 /* weight scales */ + MM_XSC * 128 * 4 /* X scales */ +
                                  2304 /* experts' first tiles */ + (FMT == ILL_IQ2_XXS ? 16 * 2048 + 4096 : 0) /* tables */ +
                                  1024 /* alignment */;
@@ -246,13 +264,14 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   // barriers, scales, tables
   u8* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   u8* x_tiles = smem;
-  uint32_t* raw = (uint32_t*)(smem + MM_NX * MM_TILE_BYTES);
+  u8* m_tiles = smem + MM_NX * MM_TILE_BYTES;    // Q2_K: two tiles for the mins
+  uint32_t* raw = (uint32_t*)(smem + (MM_NX + (FMT == ILL_Q2_K ? 2 : 0)) * MM_TILE_BYTES);
   u8* tail = (u8*)raw + MM_RS * G::RAW_BYTES + 16;
   uint64_t* full_x = (uint64_t*)tail;            // [NX] TMA bytes landed
   uint64_t* empty_x = full_x + MM_NX;            // [NX] the MMAs that read the stage completed
   uint64_t* full_t = empty_x + MM_NX;            // [NSLOT] a K step of A is in tensor memory (4 warps)
   uint64_t* empty_t = full_t + NSLOT;            // [NSLOT] the MMAs that read it completed
-  uint64_t* full_m = empty_t + NSLOT;            // [2] Q2_K: a block's mins are in tensor memory (8 warps)
+  uint64_t* full_m = empty_t + NSLOT;            // [2] Q2_K: a block's mins are in their tile (8 warps)
   uint64_t* empty_m = full_m + 2;                // [2] the MMA that read them completed
   uint64_t* raw_full = empty_m + 2;              // [RS] the raw-load lanes' copies landed
   uint64_t* raw_empty = raw_full + MM_RS;        // [RS] the dequantizing warps have read the stage
@@ -290,8 +309,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   }
   if (tid == 32) {
     for (int s = 0; s < MM_NX; ++s) { mbar_init(&full_x[s], 1); mbar_init(&empty_x[s], 1); }
-    for (int s = 0; s < NSLOT; ++s) { mbar_init(&full_t[s], MM_DQ_WARPS / 2); mbar_init(&empty_t[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&full_m[s], MM_DQ_WARPS); mbar_init(&empty_m[s], 1); }
+    for (int s = 0; s < NSLOT; ++s) { mbar_init(&full_t[s], MM_DQ_WARPS / 4); mbar_init(&empty_t[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&full_m[s], MM_DQ_WARPS / 2); mbar_init(&empty_m[s], 1); }
     for (int s = 0; s < MM_RS; ++s) { mbar_init(&raw_full[s], 32 * MM_LD_WARPS); mbar_init(&raw_empty[s], MM_DQ_WARPS); }
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_free[b], MM_DR_WARPS); }
     mbar_init(accm_free, MM_DR_WARPS);
@@ -333,6 +352,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     nvalid = min(MM_BM, (int)p.counts[lo] - m_in * MM_BM);
   };
 
+  if (warp < 2 + MM_LD_WARPS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(MM_REGS_AUX));
   if (warp == 0) {
     // ---- TMA producer of the X tiles
     if (lane == 0) {
@@ -394,7 +414,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             tc_fence_after();
             // mins x sums of 16: one K = 16 product into the mins' accumulator
             if (elect_one()) {
-              umma_f16_ts(tmem_base + G::DM_COL, tmem_base + G::AM_COL + 8u * sm, umma_desc(x_tiles + s * MM_TILE_BYTES), idesc, 0u);
+              umma_f16_ss(tmem_base + G::DM_COL, umma_desc(m_tiles + sm * MM_TILE_BYTES), umma_desc(x_tiles + s * MM_TILE_BYTES), idesc, 0u);
               umma_commit(&empty_x[s]);
               umma_commit(&empty_m[sm]);
             }
@@ -448,33 +468,33 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     }
     cp_async_wait_all();
   } else if (warp < 2 + MM_LD_WARPS + MM_DR_WARPS) {
-    // ---- warps 4..11 drain the accumulators block by block, scaling each block's integer sums by the
+    // ---- warps 4..7 drain the accumulators block by block, scaling each block's integer sums by the
     // block's float scales, and store the finished tile.  A warp reads the 32 tensor-memory lanes
-    // its number gives it (warp % 4: 32 weight rows) and half of the columns (64 rows of X).
+    // its number gives it (warp % 4: 32 weight rows) and all the columns (rows of X).
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(MM_REGS_DRAIN));
     const int q = warp & 3;
     const int m = q * 32 + lane;                   // accumulator lane = weight row in the tile
-    const int c0 = ((warp - 2 - MM_LD_WARPS) >> 2) * 64;  // columns (rows of X) c0 .. c0 + 63
     int d_kb = 0;                                  // blocks drained so far by this CTA
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int expert, row0, nvalid, nt;
       locate(tile, expert, row0, nvalid, nt);
-      float out[64];
+      float out[128];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) out[i] = 0.0f;
+      for (int i = 0; i < 128; ++i) out[i] = 0.0f;
       for (int kb = 0; kb < nkb; ++kb, ++d_kb) {
         const int b = d_kb & 1;
         const bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC, 100);
         if (!__all_sync(0xffffffffu, e_ok)) { ok = false; break; }
         tc_fence_after();
         const float dw = wsc[(d_kb & 3) * 256 + m];
-        const float* xs = xsc + (d_kb % MM_XSC) * 128 + c0;
-        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        const float* xs = xsc + (d_kb % MM_XSC) * 128;
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16);
         if constexpr (FMT == ILL_Q2_K) {
           // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
           const float dm = wsc[(d_kb & 3) * 256 + 128 + m];
 #pragma unroll
-          for (int part = 0; part < 2; ++part) {
-            if (c0 + 32 * part < nvalid) {  // columns past the tile's last row of X were not computed
+          for (int part = 0; part < 4; ++part) {
+            if (32 * part < nvalid) {  // columns past the tile's last row of X were not computed
               uint32_t v[32];
               tmem_ld32(t0 + G::DM_COL + 32 * part, v);
 #pragma unroll
@@ -493,8 +513,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           if (lane == 0) mbar_arrive(accm_free);
         }
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          if (c0 + 32 * part < nvalid) {
+        for (int part = 0; part < 4; ++part) {
+          if (32 * part < nvalid) {
             uint32_t v[32];
             tmem_ld32(t0 + b * MM_BM + 32 * part, v);
 #pragma unroll
@@ -515,19 +535,20 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       }
       const int n = nt * MM_BN + m;
       if (ok && n < p.nrows) {
-        float* ycol = p.y + ((long long)row0 + c0) * p.y_stride + n;
+        float* ycol = p.y + (long long)row0 * p.y_stride + n;
         const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (c0 + i < nvalid) ycol[(long long)i * p.y_stride] = out[i] * fin;
+        for (int i = 0; i < 128; ++i)
+          if (i < nvalid) ycol[(long long)i * p.y_stride] = out[i] * fin;
       }
     }
   } else {
-    // ---- warps 12..19 turn the raw blocks into the A operand in tensor memory: thread (row, h) makes
-    // K steps h and h + 2 of its weight row, so the warps of h = 0 and of h = 1 fill alternate K
-    // steps and the tensor core can start on a block while its second half is still being made.
-    const int t = tid - 32 * (2 + MM_LD_WARPS + MM_DR_WARPS);  // 0..255
-    const int row = t & 127, h = t >> 7;
+    // ---- warps 8..23 turn the raw blocks into the A operand in tensor memory: thread (row, j) makes K
+    // step j of its weight row in every block, so the tensor core can start on a block's first K
+    // step while the others are still being made.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(MM_REGS_DQ));
+    const int t = tid - 32 * (2 + MM_LD_WARPS + MM_DR_WARPS);  // 0..511
+    const int row = t & 127, j = t >> 7;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's lanes: rows (warp % 4) * 32 ..
     const uint2* grid = iq_grid + (lane & 15);
     const uint2* sgn = iq_sgn + lane;
@@ -546,43 +567,39 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         if (!__all_sync(0xffffffffu, r_ok)) { ok = false; break; }
         const uint32_t* rw = raw + rs * (G::RAW_BYTES / 4) + row * PW;
         // this thread's words of the block, then the raw stage is free again
-        uint32_t w[FMT == ILL_Q2_K ? 16 : 8], sc[4], dd = 0;
+        uint32_t w[FMT == ILL_Q2_K ? 8 : 4], sc4 = 0, m0 = 0, m1 = 0, dd = 0;
 #pragma unroll
-        for (int i = 0; i < (FMT == ILL_Q2_K ? 16 : 8); ++i) w[i] = 0;
-        sc[0] = sc[1] = sc[2] = sc[3] = 0;
+        for (int i = 0; i < (FMT == ILL_Q2_K ? 8 : 4); ++i) w[i] = 0;
         if (has_row) {
           if constexpr (FMT == ILL_IQ2_XXS) {
             const uint32_t mis = (rowlow + (uint32_t)kb * BB) & 3u;  // 0 or 2
             dd = (rw[0] >> (8 * mis)) & 0xffffu;
+            const uint32_t o = mis + 2 + 16 * j, w0 = o >> 2, sh = (o & 3u) * 8u;
+            uint32_t prev = rw[w0];
 #pragma unroll
-            for (int part = 0; part < 2; ++part) {
-              const uint32_t o = mis + 2 + 16 * (h + 2 * part), w0 = o >> 2, sh = (o & 3u) * 8u;
-              uint32_t prev = rw[w0];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const uint32_t next = rw[w0 + i + 1];
-                w[4 * part + i] = __funnelshift_r(prev, next, sh);
-                prev = next;
-              }
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t next = rw[w0 + i + 1];
+              w[i] = __funnelshift_r(prev, next, sh);
+              prev = next;
             }
           } else {
+            // K step j: half j / 2 of the block's quants at shifts 2 (j % 2) and 2 (j % 2) + 1; its four scale bytes
+            sc4 = rw[j];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) sc[i] = rw[i];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) w[i] = rw[4 + i];
+            for (int i = 0; i < 8; ++i) w[i] = rw[4 + 8 * (j >> 1) + i];
+            if (j < 2) { m0 = rw[2 * j]; m1 = rw[2 * j + 1]; }
             dd = rw[20];
           }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&raw_empty[rs]);
-#pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          const int st = 4 * g_kb + h + 2 * part, slot = st % NSLOT, use = st / NSLOT;
+        {
+          const int st = 4 * g_kb + j, slot = st % NSLOT, use = st / NSLOT;
           bool w_ok = true;
           if (use > 0) w_ok = mbar_wait(&empty_t[slot], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1, 50);
           if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
           tc_fence_after();
-          if (part == 0 && h == 0) {
+          if (j == 0) {
             // The drain of four blocks back is over: the MMAs that freed this slot were issued after it.
             wsc[(g_kb & 3) * 256 + row] = h2f(dd & 0xffff);
             if (FMT == ILL_Q2_K) wsc[(g_kb & 3) * 256 + 128 + row] = h2f(dd >> 16);
@@ -592,15 +609,13 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           for (int sb = 0; sb < 2; ++sb) {  // 32 weights = 16 columns at a time
             uint32_t v[16];
             if constexpr (FMT == ILL_IQ2_XXS) {
-              w_iq2xxs(w[4 * part + 2 * sb], w[4 * part + 2 * sb + 1], grid, sgn, v);
+              w_iq2xxs(w[2 * sb], w[2 * sb + 1], grid, sgn, v);
               if (!has_row) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[i] = 0;
               }
             } else {
-              // K step h + 2 part: half `part` of the block's quants at shifts 2h and 2h + 1
-              const uint32_t s4 = sc[2 * part + h];
-              w_q2k(w + 8 * part, 2 * h + sb, s4 >> (16 * sb), s4 >> (16 * sb + 8), v);
+              w_q2k(w, 2 * (j & 1) + sb, sc4 >> (16 * sb), sc4 >> (16 * sb + 8), v);
             }
             tmem_st16(a0 + 16 * sb, v);
           }
@@ -610,19 +625,18 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           if (lane == 0) mbar_arrive(&full_t[slot]);
         }
         if constexpr (FMT == ILL_Q2_K) {
-          if (!ok) break;
-          const int sm = g_kb & 1;
-          bool w_ok = true;
-          if (g_kb >= 2) w_ok = mbar_wait(&empty_m[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 50);
-          if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
-          tc_fence_after();
-          uint32_t v[4];
-          w_q2k_mins(sc[2 * h], sc[2 * h + 1], v);  // half h's eight mins: K = 8h .. 8h + 7 of the 16
-          tmem_st4(lane_base + G::AM_COL + 8u * sm + 4u * h, v);
-          tmem_st_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full_m[sm]);
+          if (j < 2) {  // warp-uniform: the eight warps of K steps 0 and 1 also make the mins
+            const int sm = g_kb & 1;
+            bool w_ok = true;
+            if (g_kb >= 2) w_ok = mbar_wait(&empty_m[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 50);
+            if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
+            uint32_t v[4];
+            w_q2k_mins(m0, m1, v);  // half j's eight mins: K = 8j .. 8j + 7 of the 16, chunk j of the row
+            store_chunk(m_tiles + sm * MM_TILE_BYTES, row, j, make_uint4(v[0], v[1], v[2], v[3]));
+            fence_async_smem();  // the tensor core reads the tile through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_m[sm]);
+          }
         }
       }
     }
@@ -761,6 +775,12 @@ extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dpt
   const void* k = fmt == ILL_IQ2_XXS ? (const void*)mm_id_kernel<ILL_IQ2_XXS> : (const void*)mm_id_kernel<ILL_Q2_K>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e);
+  // The warp groups trade registers after launch; what they ask for together must fit in what the
+  // CTA was given, or the drain warps would wait for registers for ever.
+  cudaFuncAttributes fa;
+  e = cudaFuncGetAttributes(&fa, k);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (fa.numRegs * MM_THREADS < 128 * (MM_REGS_AUX + MM_REGS_DRAIN) + 32 * MM_DQ_WARPS * MM_REGS_DQ) return ILL_ERR_UNSUPPORTED;
   void* args[] = {&xmap, &emap, &p};
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(max_tiles < sms ? max_tiles : sms), 1, 1);  // persistent: a CTA an SM, each walks tiles
