@@ -40,7 +40,6 @@ namespace ill {
 constexpr int MM_BM = 128;                             // rows of X a tile (the MMA's N)
 constexpr int MM_BN = 128;                             // weight rows a tile (the MMA's M)
 constexpr int MM_BK = 64;                              // K step: one 128-byte row of the swizzled X tile
-constexpr int MM_NX = 8;                               // stages of the ring of X tiles
 constexpr int MM_RS = 3;                               // stages of the ring of raw weight blocks
 constexpr int MM_XSC = 16;                             // blocks of X scales kept (the loader runs < 16 blocks ahead of the drain)
 constexpr int MM_DR_WARPS = 4, MM_DQ_WARPS = 16, MM_LD_WARPS = 2;  // drain, dequantize, raw-load warps
@@ -234,8 +233,8 @@ __device__ __forceinline__ void w_q2k_mins(uint32_t m0, uint32_t m1, uint32_t* v
   for (int i = 0; i < 4; ++i) asm("add.rn.f16x2 %0, %0, %1;" : "+r"(v[i]) : "r"(k1024));
 }
 
-// Per format.  SPB: X tiles per 256-wide block: four K steps; for Q2_K a fifth that holds the
-// activations' sums of 16, multiplied with the mins (one K = 16 MMA into a second accumulator).
+// Per format.  A 256-wide block is four K steps; for Q2_K it also has a tile of the activations' sums
+// of 16, multiplied with the mins (one K = 16 MMA into a second accumulator).
 // PW: 4-byte words of a row's raw block in shared memory (IQ2_XXS: the 66 bytes from the 4-byte
 // boundary at or before them; an odd count, so that a warp's rows fall in different banks).
 // Tensor memory, 512 columns: accumulators D[2] at 0 and 128 (a column = a row of X); then
@@ -243,11 +242,13 @@ __device__ __forceinline__ void w_q2k_mins(uint32_t m0, uint32_t m1, uint32_t* v
 //   Q2_K     the mins' accumulator at 256; the A ring, 4 K steps, at 384 (the mins themselves, a
 //            128 x 16 operand, go through two tiles in shared memory)
 template <int FMT> struct MmGeom {
-  static constexpr int SPB = FMT == ILL_Q2_K ? 5 : 4, PW = FMT == ILL_Q2_K ? 21 : 17, BB = FMT == ILL_Q2_K ? 84 : 66;
+  static constexpr int PW = FMT == ILL_Q2_K ? 21 : 17, BB = FMT == ILL_Q2_K ? 84 : 66;
   static constexpr int NSLOT = FMT == ILL_Q2_K ? 4 : 8;  // a multiple of four: a slot is always written by the same warps
+  static constexpr int NX = FMT == ILL_Q2_K ? 6 : 8;     // stages of the ring of X tiles = K steps in flight
+  static constexpr int NE = FMT == ILL_Q2_K ? 4 : 0;     // Q2_K: two tiles of X's sums of 16, two of the mins
   static constexpr uint32_t A_COL = FMT == ILL_Q2_K ? 384 : 256, DM_COL = 256;
   static constexpr uint32_t RAW_BYTES = 128 * PW * 4;
-  static constexpr size_t SMEM = (size_t)(MM_NX + (FMT == ILL_Q2_K ? 2 : 0)) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
+  static constexpr size_t SMEM = (size_t)(NX + NE) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
                                  512 /* barriers */ + 4 * 256 * 4 /* weight scales */ + MM_XSC * 128 * 4 /* X scales */ +
                                  2304 /* experts' first tiles */ + (FMT == ILL_IQ2_XXS ? 16 * 2048 + 4096 : 0) /* tables */ +
                                  1024 /* alignment */;
@@ -257,23 +258,24 @@ template <int FMT>
 __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant__ CUtensorMap xmap,
                                                            const __grid_constant__ CUtensorMap emap, const MmParams p) {
   typedef MmGeom<FMT> G;
-  constexpr int SPB = G::SPB, PW = G::PW, BB = G::BB, NSLOT = G::NSLOT;
+  constexpr int PW = G::PW, BB = G::BB, NSLOT = G::NSLOT, NX = G::NX;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ __align__(1024) u8 smem_raw[];
-  // [X ring] (each tile 1024-byte aligned, as the 128-byte swizzle needs), the ring of raw blocks, then
-  // barriers, scales, tables
+  // [X ring][Q2_K: sums of 16 x 2, mins x 2] (each tile 1024-byte aligned, as the 128-byte swizzle needs), the
+  // ring of raw blocks, then barriers, scales, tables
   u8* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   u8* x_tiles = smem;
-  u8* m_tiles = smem + MM_NX * MM_TILE_BYTES;    // Q2_K: two tiles for the mins
-  uint32_t* raw = (uint32_t*)(smem + (MM_NX + (FMT == ILL_Q2_K ? 2 : 0)) * MM_TILE_BYTES);
+  u8* e_tiles = smem + NX * MM_TILE_BYTES;       // Q2_K: the sums of 16 of the tile's rows of X
+  u8* m_tiles = e_tiles + 2 * MM_TILE_BYTES;     // Q2_K: the mins
+  uint32_t* raw = (uint32_t*)(smem + (NX + G::NE) * MM_TILE_BYTES);
   u8* tail = (u8*)raw + MM_RS * G::RAW_BYTES + 16;
-  uint64_t* full_x = (uint64_t*)tail;            // [NX] TMA bytes landed
-  uint64_t* empty_x = full_x + MM_NX;            // [NX] the MMAs that read the stage completed
-  uint64_t* full_t = empty_x + MM_NX;            // [NSLOT] a K step of A is in tensor memory (4 warps)
-  uint64_t* empty_t = full_t + NSLOT;            // [NSLOT] the MMAs that read it completed
-  uint64_t* full_m = empty_t + NSLOT;            // [2] Q2_K: a block's mins are in their tile (8 warps)
-  uint64_t* empty_m = full_m + 2;                // [2] the MMA that read them completed
-  uint64_t* raw_full = empty_m + 2;              // [RS] the raw-load lanes' copies landed
+  // K step st of this CTA (four a block, counted over all its tiles) uses X stage st % NX, A slot st % NSLOT
+  // and the pair of barriers st % NX
+  uint64_t* kfull = (uint64_t*)tail;             // [NX] the X tile landed (TMA) and the K step of A is in tensor memory (4 warps)
+  uint64_t* kempty = kfull + NX;                 // [NX] the MMAs of the K step completed
+  uint64_t* mfull = kempty + NX;                 // [2] Q2_K: the block's sums of 16 landed and its mins are in their tile (8 warps)
+  uint64_t* mempty = mfull + 2;                  // [2] the MMA that read them completed
+  uint64_t* raw_full = mempty + 2;               // [RS] the raw-load lanes' copies landed
   uint64_t* raw_empty = raw_full + MM_RS;        // [RS] the dequantizing warps have read the stage
   uint64_t* acc_full = raw_empty + MM_RS;        // [2] a block's MMAs completed
   uint64_t* acc_free = acc_full + 2;             // [2] the drain warps read the buffer
@@ -308,9 +310,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     if (lane == 0) tile_first[p.ne] = before;  // row tiles in all
   }
   if (tid == 32) {
-    for (int s = 0; s < MM_NX; ++s) { mbar_init(&full_x[s], 1); mbar_init(&empty_x[s], 1); }
-    for (int s = 0; s < NSLOT; ++s) { mbar_init(&full_t[s], MM_DQ_WARPS / 4); mbar_init(&empty_t[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&full_m[s], MM_DQ_WARPS / 2); mbar_init(&empty_m[s], 1); }
+    for (int s = 0; s < NX; ++s) { mbar_init(&kfull[s], 1 + MM_DQ_WARPS / 4); mbar_init(&kempty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&mfull[s], 1 + MM_DQ_WARPS / 2); mbar_init(&mempty[s], 1); }
     for (int s = 0; s < MM_RS; ++s) { mbar_init(&raw_full[s], 32 * MM_LD_WARPS); mbar_init(&raw_empty[s], MM_DQ_WARPS); }
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_free[b], MM_DR_WARPS); }
     mbar_init(accm_free, MM_DR_WARPS);
@@ -356,17 +357,23 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   if (warp == 0) {
     // ---- TMA producer of the X tiles
     if (lane == 0) {
-      int g_sx = 0;  // X stages issued so far by this CTA
+      int g_st = 0, g_kb = 0;  // K steps and blocks issued so far by this CTA
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         int expert, row0, nvalid, nt;
         locate(tile, expert, row0, nvalid, nt);
-        for (int st = 0; st < nkb * SPB; ++st, ++g_sx) {
-          const int s = g_sx % MM_NX, use = g_sx / MM_NX;
-          if (use > 0 && !mbar_wait(&empty_x[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY, 100)) { ok = false; break; }
-          const int kb = st / SPB, j = st - kb * SPB;
-          mbar_expect_tx(&full_x[s], MM_TILE_BYTES);
-          if (j < 4) tma_load_2d(x_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &full_x[s]);
-          else tma_load_2d(x_tiles + s * MM_TILE_BYTES, &emap, kb * MM_BK, row0, &full_x[s]);  // the sums of 16
+        for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
+          for (int j = 0; j < 4; ++j, ++g_st) {
+            const int s = g_st % NX;
+            if (g_st >= NX && !mbar_wait(&kempty[s], (uint32_t)(g_st / NX - 1) & 1u, p.status, ST_MM_WAIT_EMPTY, 100)) { ok = false; break; }
+            mbar_expect_tx(&kfull[s], MM_TILE_BYTES);
+            tma_load_2d(x_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &kfull[s]);
+          }
+          if (FMT == ILL_Q2_K && ok) {
+            const int sm = g_kb & 1;
+            if (g_kb >= 2 && !mbar_wait(&mempty[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 100)) { ok = false; break; }
+            mbar_expect_tx(&mfull[sm], MM_TILE_BYTES);
+            tma_load_2d(e_tiles + sm * MM_TILE_BYTES, &emap, kb * MM_BK, row0, &mfull[sm]);  // the sums of 16
+          }
         }
       }
     }
@@ -374,7 +381,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     // ---- MMA issuer: the whole warp walks the loop (so that addresses and descriptors stay in uniform
     // registers) and one elected lane issues
     {
-      int g_sx = 0, g_st = 0, g_kb = 0;  // X stages, K steps of A and blocks consumed so far by this CTA
+      int g_st = 0, g_kb = 0;  // K steps and blocks consumed so far by this CTA
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         int expert, row0, nvalid, nt;
         locate(tile, expert, row0, nvalid, nt);
@@ -387,10 +394,9 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           if (g_kb >= 2) ok = __all_sync(0xffffffffu, mbar_wait(&acc_free[b], (uint32_t)(g_kb / 2 - 1) & 1u, p.status, ST_MM_WAIT_EPI));
           if (!ok) break;
           const uint32_t d1 = tmem_base + (uint32_t)(b * MM_BM);
-          for (int j = 0; j < 4; ++j, ++g_sx, ++g_st) {
-            const int s = g_sx % MM_NX, slot = g_st % NSLOT;
-            ok = __all_sync(0xffffffffu, mbar_wait(&full_x[s], (uint32_t)(g_sx / MM_NX) & 1u, p.status, ST_MM_WAIT_FULL) &&
-                                             mbar_wait(&full_t[slot], (uint32_t)(g_st / NSLOT) & 1u, p.status, ST_MM_WAIT_FULL + 1));
+          for (int j = 0; j < 4; ++j, ++g_st) {
+            const int s = g_st % NX, slot = g_st % NSLOT;
+            ok = __all_sync(0xffffffffu, mbar_wait(&kfull[s], (uint32_t)(g_st / NX) & 1u, p.status, ST_MM_WAIT_FULL));
             if (!ok) break;
             tc_fence_after();
             const uint64_t xdsc = umma_desc(x_tiles + s * MM_TILE_BYTES);
@@ -399,27 +405,23 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
 #pragma unroll
               for (int k = 0; k < MM_BK / 16; ++k)  // 16 of K: 8 columns of A, 32 bytes inside X's swizzle atom
                 umma_f16_ts(d1, a0 + 8 * k, xdsc + 2 * k, idesc, (j | k) ? 1u : 0u);
-              umma_commit(&empty_x[s]);  // the X stage and the A slot are free when these MMAs are done
-              umma_commit(&empty_t[slot]);
+              umma_commit(&kempty[s]);  // the X stage and the A slot are free when these MMAs are done
             }
             __syncwarp();
           }
           if (!ok) break;
           if constexpr (FMT == ILL_Q2_K) {
-            const int s = g_sx % MM_NX, sm = g_kb & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(&full_x[s], (uint32_t)(g_sx / MM_NX) & 1u, p.status, ST_MM_WAIT_FULL) &&
-                                             mbar_wait(&full_m[sm], (uint32_t)(g_kb >> 1) & 1u, p.status, ST_MM_WAIT_FULL + 3) &&
+            const int sm = g_kb & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(&mfull[sm], (uint32_t)(g_kb >> 1) & 1u, p.status, ST_MM_WAIT_FULL + 3) &&
                                              (g_kb < 1 || mbar_wait(accm_free, (uint32_t)(g_kb - 1) & 1u, p.status, ST_MM_WAIT_EPI + 2)));
             if (!ok) break;
             tc_fence_after();
             // mins x sums of 16: one K = 16 product into the mins' accumulator
             if (elect_one()) {
-              umma_f16_ss(tmem_base + G::DM_COL, umma_desc(m_tiles + sm * MM_TILE_BYTES), umma_desc(x_tiles + s * MM_TILE_BYTES), idesc, 0u);
-              umma_commit(&empty_x[s]);
-              umma_commit(&empty_m[sm]);
+              umma_f16_ss(tmem_base + G::DM_COL, umma_desc(m_tiles + sm * MM_TILE_BYTES), umma_desc(e_tiles + sm * MM_TILE_BYTES), idesc, 0u);
+              umma_commit(&mempty[sm]);
             }
             __syncwarp();
-            ++g_sx;
           }
           if (elect_one()) umma_commit(&acc_full[b]);
           __syncwarp();
@@ -594,9 +596,10 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive(&raw_empty[rs]);
         {
-          const int st = 4 * g_kb + j, slot = st % NSLOT, use = st / NSLOT;
+          // the slot's last K step was st - NSLOT: its MMAs must be done
+          const int st = 4 * g_kb + j, slot = st % NSLOT, sp = st - NSLOT;
           bool w_ok = true;
-          if (use > 0) w_ok = mbar_wait(&empty_t[slot], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 1, 50);
+          if (sp >= 0) w_ok = mbar_wait(&kempty[sp % NX], (uint32_t)(sp / NX) & 1u, p.status, ST_MM_WAIT_EMPTY + 1, 50);
           if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
           tc_fence_after();
           if (j == 0) {
@@ -622,20 +625,20 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&full_t[slot]);
+          if (lane == 0) mbar_arrive(&kfull[st % NX]);
         }
         if constexpr (FMT == ILL_Q2_K) {
           if (j < 2) {  // warp-uniform: the eight warps of K steps 0 and 1 also make the mins
             const int sm = g_kb & 1;
             bool w_ok = true;
-            if (g_kb >= 2) w_ok = mbar_wait(&empty_m[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 50);
+            if (g_kb >= 2) w_ok = mbar_wait(&mempty[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 50);
             if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
             uint32_t v[4];
             w_q2k_mins(m0, m1, v);  // half j's eight mins: K = 8j .. 8j + 7 of the 16, chunk j of the row
             store_chunk(m_tiles + sm * MM_TILE_BYTES, row, j, make_uint4(v[0], v[1], v[2], v[3]));
             fence_async_smem();  // the tensor core reads the tile through the async proxy
             __syncwarp();
-            if (lane == 0) mbar_arrive(&full_m[sm]);
+            if (lane == 0) mbar_arrive(&mfull[sm]);
           }
         }
       }
