@@ -45,7 +45,7 @@ constexpr int MM_XSC = 16;                             // blocks of X scales kep
 constexpr int MM_DR_WARPS = 4, MM_DQ_WARPS = 16, MM_LD_WARPS = 2;  // drain, dequantize, raw-load warps
 // Registers a thread after the roles part: the four warps of TMA / MMA / raw loads give theirs up, the
 // drain warps (a whole tile's row of 128 sums each) take them
-constexpr int MM_REGS_AUX = 40, MM_REGS_DRAIN = 176, MM_REGS_DQ = 64;
+constexpr int MM_REGS_AUX = 40, MM_REGS_DRAIN = 184, MM_REGS_DQ = 64;
 constexpr int MM_THREADS = 32 * (2 + MM_LD_WARPS + MM_DR_WARPS + MM_DQ_WARPS);  // + the TMA warp and the MMA warp
 constexpr uint32_t MM_TILE_BYTES = MM_BM * MM_BK * 2;  // 16 KB
 
@@ -169,6 +169,24 @@ __device__ __forceinline__ uint32_t small_h2(uint32_t n) {
   uint32_t v = 0x64006400u | (n * 0x10001u);
   asm("add.rn.f16x2 %0, %0, %1;" : "+r"(v) : "r"(0xe400e400u));  // - 1024
   return v;
+}
+
+// pairs of fp32 in a 64-bit register, and the packed multiply / fused multiply-add of sm_100
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) { return pack2u(__float_as_uint(lo), __float_as_uint(hi)); }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
 }
 
 // 4 bytes global -> shared, asynchronously (both addresses 4-byte aligned)
@@ -480,20 +498,24 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int expert, row0, nvalid, nt;
       locate(tile, expert, row0, nvalid, nt);
-      float out[128];
+      uint64_t out[64];  // pairs of fp32: this weight row against the tile's 128 rows of X
 #pragma unroll
-      for (int i = 0; i < 128; ++i) out[i] = 0.0f;
+      for (int i = 0; i < 64; ++i) out[i] = 0ull;
       for (int kb = 0; kb < nkb; ++kb, ++d_kb) {
         const int b = d_kb & 1;
         const bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC, 100);
         if (!__all_sync(0xffffffffu, e_ok)) { ok = false; break; }
         tc_fence_after();
+        // Two fp32 at a time (fma.rn.f32x2: each half rounds as the scalar instruction does).
+        // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum, the 1/8 at the end;
+        // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
         const float dw = wsc[(d_kb & 3) * 256 + m];
+        const uint64_t dw2 = pack2(dw, dw);
         const float* xs = xsc + (d_kb % MM_XSC) * 128;
         const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16);
         if constexpr (FMT == ILL_Q2_K) {
-          // Q2K-DOT-AVX2 (src/avx2.lisp:147-150): y.d * d * sum - y.d * dmin * mins
-          const float dm = wsc[(d_kb & 3) * 256 + 128 + m];
+          const float dm = -wsc[(d_kb & 3) * 256 + 128 + m];
+          const uint64_t dm2 = pack2(dm, dm);
 #pragma unroll
           for (int part = 0; part < 4; ++part) {
             if (32 * part < nvalid) {  // columns past the tile's last row of X were not computed
@@ -501,12 +523,10 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
               tmem_ld32(t0 + G::DM_COL + 32 * part, v);
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
-                const float4 dx = *(const float4*)(xs + 32 * part + i);
-                float* o = out + 32 * part + i;
-                o[0] = fmaf(-__fmul_rn(dx.x, dm), __uint_as_float(v[i]), o[0]);
-                o[1] = fmaf(-__fmul_rn(dx.y, dm), __uint_as_float(v[i + 1]), o[1]);
-                o[2] = fmaf(-__fmul_rn(dx.z, dm), __uint_as_float(v[i + 2]), o[2]);
-                o[3] = fmaf(-__fmul_rn(dx.w, dm), __uint_as_float(v[i + 3]), o[3]);
+                const ulonglong2 dx = *(const ulonglong2*)(xs + 32 * part + i);
+                uint64_t* o = out + (32 * part + i) / 2;
+                o[0] = fma2(mul2(dx.x, dm2), pack2u(v[i], v[i + 1]), o[0]);
+                o[1] = fma2(mul2(dx.y, dm2), pack2u(v[i + 2], v[i + 3]), o[1]);
               }
             }
           }
@@ -521,13 +541,10 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             tmem_ld32(t0 + b * MM_BM + 32 * part, v);
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
-              const float4 dx = *(const float4*)(xs + 32 * part + i);
-              // IQ2XXS-DOT-AVX2 (src/avx2.lisp:107-110): total += d * y.d * sum, the 1/8 at the end
-              float* o = out + 32 * part + i;
-              o[0] = fmaf(__fmul_rn(dw, dx.x), __uint_as_float(v[i]), o[0]);
-              o[1] = fmaf(__fmul_rn(dw, dx.y), __uint_as_float(v[i + 1]), o[1]);
-              o[2] = fmaf(__fmul_rn(dw, dx.z), __uint_as_float(v[i + 2]), o[2]);
-              o[3] = fmaf(__fmul_rn(dw, dx.w), __uint_as_float(v[i + 3]), o[3]);
+              const ulonglong2 dx = *(const ulonglong2*)(xs + 32 * part + i);
+              uint64_t* o = out + (32 * part + i) / 2;
+              o[0] = fma2(mul2(dw2, dx.x), pack2u(v[i], v[i + 1]), o[0]);
+              o[1] = fma2(mul2(dw2, dx.y), pack2u(v[i + 2], v[i + 3]), o[1]);
             }
           }
         }
@@ -541,7 +558,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
 #pragma unroll
         for (int i = 0; i < 128; ++i)
-          if (i < nvalid) ycol[(long long)i * p.y_stride] = out[i] * fin;
+          if (i < nvalid) ycol[(long long)i * p.y_stride] = __uint_as_float((uint32_t)(out[i >> 1] >> (32 * (i & 1)))) * fin;
       }
     }
   } else {
