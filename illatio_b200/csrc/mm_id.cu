@@ -17,8 +17,8 @@
 //   warp 0      one lane issues the TMA loads of the X tiles
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x N x 16, fp16 in,
 //               fp32 accumulate) and commits each step back to the producers
-//   warps 2-3   copy W_e's raw blocks and the X rows' block scales into rings in shared memory
-//               (cp.async, coalesced)
+//   warps 2-3   bring W_e's raw blocks and the X rows' block scales into rings in shared memory
+//               (cp.async)
 //   warps 4-7   drain the accumulators block by block (tcgen05.ld), scaling each block's integer
 //               sums by the block's float scales; then store the tile (a lane = a weight row, so
 //               the 32 lanes of a warp write 128 contiguous bytes of a row of Y)
@@ -193,6 +193,9 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {  // both 16-byte aligned
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
 // BAR gets one arrival (counted in its initial count) once this thread's earlier cp.async have landed
 __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -253,19 +256,20 @@ __device__ __forceinline__ void w_q2k_mins(uint32_t m0, uint32_t m1, uint32_t* v
 
 // Per format.  A 256-wide block is four K steps; for Q2_K it also has a tile of the activations' sums
 // of 16, multiplied with the mins (one K = 16 MMA into a second accumulator).
-// PW: 4-byte words of a row's raw block in shared memory (IQ2_XXS: the 66 bytes from the 4-byte
-// boundary at or before them; an odd count, so that a warp's rows fall in different banks).
 // Tensor memory, 512 columns: accumulators D[2] at 0 and 128 (a column = a row of X); then
 //   IQ2_XXS  the A ring, 8 K steps x 32 columns, at 256
 //   Q2_K     the mins' accumulator at 256; the A ring, 4 K steps, at 384 (the mins themselves, a
 //            128 x 16 operand, go through two tiles in shared memory)
 template <int FMT> struct MmGeom {
-  static constexpr int PW = FMT == ILL_Q2_K ? 21 : 17, BB = FMT == ILL_Q2_K ? 84 : 66;
+  static constexpr int BB = FMT == ILL_Q2_K ? 84 : 66;
   static constexpr int NSLOT = FMT == ILL_Q2_K ? 4 : 8;  // a multiple of four: a slot is always written by the same warps
   static constexpr int NX = FMT == ILL_Q2_K ? 6 : 8;     // stages of the ring of X tiles = K steps in flight
   static constexpr int NE = FMT == ILL_Q2_K ? 4 : 0;     // Q2_K: two tiles of X's sums of 16, two of the mins
   static constexpr uint32_t A_COL = FMT == ILL_Q2_K ? 384 : 256, DM_COL = 256;
-  static constexpr uint32_t RAW_BYTES = 128 * PW * 4;
+  // A row's raw block reaches shared memory as the WIN bytes from the 16-byte boundary at or before it,
+  // PITCH bytes apart
+  static constexpr uint32_t WIN = FMT == ILL_Q2_K ? 96 : 80, PITCH = FMT == ILL_Q2_K ? 112 : 80;
+  static constexpr uint32_t RAW_BYTES = 128 * PITCH;
   static constexpr size_t SMEM = (size_t)(NX + NE) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
                                  512 /* barriers */ + 4 * 256 * 4 /* weight scales */ + MM_XSC * 128 * 4 /* X scales */ +
                                  2304 /* experts' first tiles */ + (FMT == ILL_IQ2_XXS ? 16 * 2048 + 4096 : 0) /* tables */ +
@@ -276,7 +280,7 @@ template <int FMT>
 __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant__ CUtensorMap xmap,
                                                            const __grid_constant__ CUtensorMap emap, const MmParams p) {
   typedef MmGeom<FMT> G;
-  constexpr int PW = G::PW, BB = G::BB, NSLOT = G::NSLOT, NX = G::NX;
+  constexpr int BB = G::BB, NSLOT = G::NSLOT, NX = G::NX;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ __align__(1024) u8 smem_raw[];
   // [X ring][Q2_K: sums of 16 x 2, mins x 2] (each tile 1024-byte aligned, as the 128-byte swizzle needs), the
@@ -447,19 +451,17 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       }
     }
   } else if (warp < 2 + MM_LD_WARPS) {
-    // ---- warps 2, 3 copy each block's raw bytes (128 weight rows x PW words) into the raw ring, 4
-    // bytes a lane at a time so that a warp's requests touch two or three rows, not thirty-two; and
-    // the block's scale of each of the tile's rows of X.
-    // Lane L < RPS * PW owns word L % PW of rows L / PW, + RPS, + 2 RPS, ...
+    // ---- warps 2, 3 bring each block's raw bytes (for every weight row the 16-byte-aligned window
+    // around the row's block, 16 bytes a lane at a time: a warp's requests touch six or seven rows) and
+    // the block's scale of each of the tile's rows of X into shared memory
     const int L = (warp - 2) * 32 + lane;
-    constexpr int NL = 32 * MM_LD_WARPS, RPS = NL / PW;  // rows a step
-    const int word = L % PW, r_first = L / PW;
+    constexpr int NL = 32 * MM_LD_WARPS, CPR = G::WIN / 16;  // chunks of a row's window
     int g_kb = 0;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int expert, row0, nvalid, nt;
       locate(tile, expert, row0, nvalid, nt);
       const u8* wbase = (const u8*)(uintptr_t)p.ptrs[expert] + p.add + (long long)nt * MM_BN * p.row_bytes;
-      const int rows_here = r_first < RPS ? min(MM_BN, p.nrows - nt * MM_BN) : 0;
+      const int rows_here = min(MM_BN, p.nrows - nt * MM_BN);
       // the tokens of the tile's rows L, L + NL of X (a row past the tile's last takes the first row's)
       const float* xdp[128 / NL];
 #pragma unroll
@@ -475,13 +477,14 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
 #pragma unroll
         for (int i = 0; i < 128 / NL; ++i) cp_async4(xsc + (g_kb % MM_XSC) * 128 + L + i * NL, xdp[i] + kb);
-        uint32_t* dst = raw + s * (G::RAW_BYTES / 4) + r_first * PW + word;
-        const u8* src = wbase + (long long)r_first * p.row_bytes + kb * BB;
+        u8* dst = (u8*)raw + s * G::RAW_BYTES;
 #pragma unroll 4
-        for (int row = r_first; row < rows_here; row += RPS) {
-          cp_async4(dst, (const void*)(((uintptr_t)src & ~(uintptr_t)3) + 4 * word));
-          dst += RPS * PW;
-          src += (long long)RPS * p.row_bytes;
+        for (int c = L; c < 128 * CPR; c += NL) {
+          const int row = c / CPR, ch = c - row * CPR;
+          if (row < rows_here) {
+            const uintptr_t blk = (uintptr_t)(wbase + (long long)row * p.row_bytes + kb * BB);
+            cp_async16(dst + row * G::PITCH + 16 * ch, (const void*)((blk & ~(uintptr_t)15) + 16 * ch));
+          }
         }
         cp_async_arrive(&raw_full[s]);
       }
@@ -584,16 +587,17 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         const int rs = g_kb % MM_RS;
         const bool r_ok = mbar_wait(&raw_full[rs], (uint32_t)(g_kb / MM_RS) & 1u, p.status, ST_MM_WAIT_FULL + 2, 50);
         if (!__all_sync(0xffffffffu, r_ok)) { ok = false; break; }
-        const uint32_t* rw = raw + rs * (G::RAW_BYTES / 4) + row * PW;
-        // this thread's words of the block, then the raw stage is free again
+        // this thread's words of the block (it starts O16 bytes into the row's window), then the raw
+        // stage is free again
+        const uint32_t o16 = (rowlow + (uint32_t)kb * BB) & 15u;
+        const uint32_t* rw = raw + rs * (G::RAW_BYTES / 4) + row * (G::PITCH / 4);
         uint32_t w[FMT == ILL_Q2_K ? 8 : 4], sc4 = 0, m0 = 0, m1 = 0, dd = 0;
 #pragma unroll
         for (int i = 0; i < (FMT == ILL_Q2_K ? 8 : 4); ++i) w[i] = 0;
         if (has_row) {
           if constexpr (FMT == ILL_IQ2_XXS) {
-            const uint32_t mis = (rowlow + (uint32_t)kb * BB) & 3u;  // 0 or 2
-            dd = (rw[0] >> (8 * mis)) & 0xffffu;
-            const uint32_t o = mis + 2 + 16 * j, w0 = o >> 2, sh = (o & 3u) * 8u;
+            dd = (rw[o16 >> 2] >> (8 * (o16 & 2u))) & 0xffffu;
+            const uint32_t o = o16 + 2 + 16 * j, w0 = o >> 2, sh = (o & 3u) * 8u;
             uint32_t prev = rw[w0];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -603,11 +607,12 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             }
           } else {
             // K step j: half j / 2 of the block's quants at shifts 2 (j % 2) and 2 (j % 2) + 1; its four scale bytes
-            sc4 = rw[j];
+            const uint32_t* bw = rw + (o16 >> 2);  // a Q2_K block is 4-byte aligned
+            sc4 = bw[j];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) w[i] = rw[4 + 8 * (j >> 1) + i];
-            if (j < 2) { m0 = rw[2 * j]; m1 = rw[2 * j + 1]; }
-            dd = rw[20];
+            for (int i = 0; i < 8; ++i) w[i] = bw[4 + 8 * (j >> 1) + i];
+            if (j < 2) { m0 = bw[2 * j]; m1 = bw[2 * j + 1]; }
+            dd = bw[20];
           }
         }
         __syncwarp();
