@@ -58,6 +58,7 @@ struct MmParams {
   const unsigned* bases;
   const float* xd;             // the activations' block scales, [token][K/256]
   const unsigned* map;         // token of each row of X (null: the row itself)
+  const unsigned* ymap;        // row of Y each row of X is written to (null: the same row)
   long long total_rows;
   float* y;
   long long y_stride;          // floats between rows of Y
@@ -557,11 +558,13 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       }
       const int n = nt * MM_BN + m;
       if (ok && n < p.nrows) {
-        float* ycol = p.y + (long long)row0 * p.y_stride + n;
         const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
 #pragma unroll
         for (int i = 0; i < 128; ++i)
-          if (i < nvalid) ycol[(long long)i * p.y_stride] = __uint_as_float((uint32_t)(out[i >> 1] >> (32 * (i & 1)))) * fin;
+          if (i < nvalid) {
+            const long long yr = p.ymap ? (long long)__ldg(p.ymap + row0 + i) : (long long)row0 + i;
+            p.y[yr * p.y_stride + n] = __uint_as_float((uint32_t)(out[i >> 1] >> (32 * (i & 1)))) * fin;
+          }
       }
     }
   } else {
@@ -761,13 +764,13 @@ static int encode_map(CUtensorMap* map, ill_dptr base, int64_t inner, int64_t ro
 }
 
 extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases,
-                             int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr y,
-                             int64_t y_stride, ill_stream stream) {
+                             int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap,
+                             ill_dptr y, int64_t y_stride, ill_stream stream) {
   if (fmt != ILL_IQ2_XXS && fmt != ILL_Q2_K) return ILL_ERR_UNSUPPORTED;
   if (ncols <= 0 || ncols % 256 || nrows <= 0 || ne <= 0 || ne > 65535 || total_rows < 0 || y_stride < nrows)
     return ILL_ERR_ARG;
   if (!ptrs || !counts || !bases || !xh || !xd || !y || (fmt == ILL_Q2_K && !xe)) return ILL_ERR_ARG;
-  if ((ptrs & 7) || (counts & 3) || (bases & 3) || (xh & 15) || (xe & 15) || (xd & 3) || (map & 3) || (y & 15) ||
+  if ((ptrs & 7) || (counts & 3) || (bases & 3) || (xh & 15) || (xe & 15) || (xd & 3) || (map & 3) || (ymap & 3) || (y & 15) ||
       (y_stride & 3) || (add & 3))
     return ILL_ERR_ALIGN;
   if (total_rows == 0) return ILL_OK;
@@ -786,6 +789,7 @@ extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dpt
   p.bases = (const unsigned*)(uintptr_t)bases;
   p.xd = (const float*)(uintptr_t)xd;
   p.map = (const unsigned*)(uintptr_t)map;
+  p.ymap = (const unsigned*)(uintptr_t)ymap;
   p.total_rows = total_rows;
   p.y = (float*)(uintptr_t)y;
   p.y_stride = y_stride;

@@ -214,6 +214,31 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(long long rows, int ro
   dst[gid] = src[(long long)map[r] * row_vec + j];
 }
 
+// the same for rows that are a whole number of 4-byte words only
+__global__ void __launch_bounds__(256) gather_rows4_kernel(long long rows, int row_words, const uint32_t* __restrict__ src,
+                                                           const unsigned* __restrict__ map, uint32_t* __restrict__ dst) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= rows * row_words) return;
+  const long long r = gid / row_words;
+  const int j = (int)(gid - r * row_words);
+  dst[gid] = src[(long long)map[r] * row_words + j];
+}
+
+// One block a segment (rows of one expert from one source): arrival index <-> place of each row.
+__global__ void __launch_bounds__(128) ep_plan_rows_kernel(const int* __restrict__ seg_arrival, const int* __restrict__ seg_place,
+                                                           const int* __restrict__ seg_len, unsigned* __restrict__ p2r,
+                                                           unsigned* __restrict__ r2p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int a = seg_arrival[blockIdx.x], pl = seg_place[blockIdx.x], n = seg_len[blockIdx.x];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    p2r[pl + i] = (unsigned)(a + i);
+    r2p[a + i] = (unsigned)(pl + i);
+  }
+}
+
 }  // namespace ill
 
 using namespace ill;
@@ -403,15 +428,39 @@ extern "C" int ill_moe_group_static(int64_t rows, int ne, int nu, ill_dptr sel, 
 
 extern "C" int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,
                                ill_stream stream) {
-  if (rows < 0 || row_bytes <= 0 || (row_bytes & 15) || !check_ptr(src, 16) || !check_ptr(dst, 16) || !check_ptr(map, 4))
-    return ILL_ERR_ARG;
+  if (rows < 0 || row_bytes <= 0 || (row_bytes & 3) || !check_ptr(map, 4)) return ILL_ERR_ARG;
+  const unsigned align = (row_bytes & 15) ? 4 : 16;
+  if (!check_ptr(src, align) || !check_ptr(dst, align)) return ILL_ERR_ARG;
   if (rows == 0) return ILL_OK;
   long long nrows = rows;
+  const unsigned* mp = (const unsigned*)(uintptr_t)map;
+  if (align == 4) {
+    int row_words = (int)(row_bytes / 4);
+    const uint32_t* sp = (const uint32_t*)(uintptr_t)src;
+    uint32_t* dp = (uint32_t*)(uintptr_t)dst;
+    void* args[] = {&nrows, &row_words, &sp, &mp, &dp};
+    return launch_kernel((const void*)gather_rows4_kernel, dim3((unsigned)((rows * row_words + 255) / 256)), dim3(256), 0,
+                         args, (cudaStream_t)stream);
+  }
   int row_vec = (int)(row_bytes / 16);
   const uint4* sp = (const uint4*)(uintptr_t)src;
-  const unsigned* mp = (const unsigned*)(uintptr_t)map;
   uint4* dp = (uint4*)(uintptr_t)dst;
   void* args[] = {&nrows, &row_vec, &sp, &mp, &dp};
   return launch_kernel((const void*)gather_rows_kernel, dim3((unsigned)((rows * row_vec + 255) / 256)), dim3(256), 0,
                        args, (cudaStream_t)stream);
+}
+
+extern "C" int ill_ep_plan_rows(int nseg, ill_dptr seg_arrival, ill_dptr seg_place, ill_dptr seg_len, ill_dptr p2r,
+                                ill_dptr r2p, ill_stream stream) {
+  if (nseg < 0 || !check_ptr(seg_arrival, 4) || !check_ptr(seg_place, 4) || !check_ptr(seg_len, 4) || !check_ptr(p2r, 4) ||
+      !check_ptr(r2p, 4))
+    return ILL_ERR_ARG;
+  if (nseg == 0) return ILL_OK;
+  const int* sa = (const int*)(uintptr_t)seg_arrival;
+  const int* sp = (const int*)(uintptr_t)seg_place;
+  const int* sl = (const int*)(uintptr_t)seg_len;
+  unsigned* pp = (unsigned*)(uintptr_t)p2r;
+  unsigned* rp = (unsigned*)(uintptr_t)r2p;
+  void* args[] = {&sa, &sp, &sl, &pp, &rp};
+  return launch_kernel((const void*)ep_plan_rows_kernel, dim3((unsigned)nseg), dim3(128), 0, args, (cudaStream_t)stream);
 }

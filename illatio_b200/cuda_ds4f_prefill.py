@@ -75,7 +75,7 @@ def act_f16(act, cols, rows, rmap, xh, xe):
 def mm_id(pool, fmt, ncols, nrows, add, sc, xh, xe, xd, rmap, y):
     """d4_mm_id_<fmt> (src/cuda-ds4f-prefill.lisp:345-347); every expert is resident."""
     _lib.call("ill_moe_mm_id", fmt, ncols, nrows, add, _ptr(pool.ptrs_all), _ptr(sc.counts), _ptr(sc.bases),
-              pool.n_expert, sc.rows, _ptr(xh), _ptr(xe), _ptr(xd), _ptr(rmap), _ptr(y), nrows, _stream())
+              pool.n_expert, sc.rows, _ptr(xh), _ptr(xe), _ptr(xd), _ptr(rmap), 0, _ptr(y), nrows, _stream())
 
 
 def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, scale=1.0, shared=None):

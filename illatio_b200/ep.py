@@ -168,7 +168,7 @@ class CudaExperts:
         g, u = torch.empty(rows, ff, **f32), torch.empty(rows, ff, **f32)
         for add, y in ((0, g), (pool.gate_bytes, u)):
             _lib.call("ill_moe_mm_id", pool.gate_fmt, d, ff, add, ptr(pool.ptrs_all), ptr(plan.counts), ptr(plan.bases),
-                      pool.n_expert, rows, ptr(xh), ptr(xe), ptr(xd), ptr(p2r), ptr(y), ff, st)
+                      pool.n_expert, rows, ptr(xh), ptr(xe), ptr(xd), ptr(p2r), 0, ptr(y), ff, st)
         wplace = wrow[p2r.long()].contiguous()
         mid = torch.empty(rows, ff, **f32)
         swiglu_w(g, u, wplace, mid, ff, self.clamp)
@@ -179,7 +179,7 @@ class CudaExperts:
         _lib.call("ill_act_f16", rows, ff, ptr(midq.xq), ptr(midq.xsum), 0, ptr(mh), ptr(me), st)
         down = torch.empty(rows, d, **f32)
         _lib.call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(plan.counts),
-                  ptr(plan.bases), pool.n_expert, rows, ptr(mh), ptr(me), ptr(midq.xs), 0, ptr(down), d, st)
+                  ptr(plan.bases), pool.n_expert, rows, ptr(mh), ptr(me), ptr(midq.xs), 0, 0, ptr(down), d, st)
         out = torch.empty_like(down)
         _lib.call("ill_gather_rows", rows, d * 4, ptr(down), ptr(plan.recv_to_place), ptr(out), st)
         return out
@@ -195,6 +195,147 @@ class CudaExperts:
     def chunk(self, norms, logits, n_expert_total, group=None):
         return moe_chunk_ep(norms, logits, self.nu, self.route, self.quantize, self.experts, self.sum, n_expert_total,
                             group)
+
+
+class EpScratch:
+    """Buffers of CudaExperts.chunk_fast for chunks of up to N tokens a rank: nothing
+    is allocated per chunk.  A rank may receive every row of the chunk (CAP)."""
+
+    def __init__(self, pool, n, nu, n_expert_total, world, device="cuda"):
+        from . import _lib
+        from .blocks import Q2_K
+        d, ff = pool.d, pool.ff
+        rows, cap = n * nu, n * nu * world
+        per = n_expert_total // world
+        dev = dict(device=device)
+        f32, i32, u8 = dict(dtype=torch.float32, **dev), dict(dtype=torch.int32, **dev), dict(dtype=torch.uint8, **dev)
+        self.n, self.nu, self.rows, self.cap, self.per, self.world = n, nu, rows, cap, per, world
+        self.sel, self.w = torch.empty(n, nu, **i32), torch.empty(n, nu, **f32)
+        self.counts, self.bases = torch.empty(n_expert_total, **i32), torch.empty(n_expert_total, **i32)
+        self.rmap, self.smap, self.wrow = torch.empty(rows, **i32), torch.empty(rows, **i32), torch.empty(rows, **f32)
+        self.group = torch.empty(_lib.lib().ill_moe_group_scratch_bytes(rows, n_expert_total), **u8)
+        self.cmat = torch.empty(world, n_expert_total, **i32)
+        self.cmat_host = torch.empty(world, n_expert_total, dtype=torch.int32).pin_memory()
+        nseg = world * per
+        self.plan_host = torch.empty(3 * nseg + 2 * per, dtype=torch.int32).pin_memory()
+        self.plan = torch.empty(3 * nseg + 2 * per, **i32)
+        self.p2r, self.r2p = torch.empty(cap, **i32), torch.empty(cap, **i32)
+        self.xq = torch.empty(n * d, dtype=torch.int8, **dev)
+        self.xs, self.xsum = torch.empty(n * d // 256, **f32), torch.empty(n * d // 16, dtype=torch.int16, **dev)
+        # what a row carries, in the order it is sent / as it arrives
+        self.s_xq, self.s_xs = torch.empty(rows, d, dtype=torch.int8, **dev), torch.empty(rows, d // 256, **f32)
+        self.s_xsum = torch.empty(rows, d // 16, dtype=torch.int16, **dev)
+        if world > 1:
+            self.r_xq, self.r_xs = torch.empty(cap, d, dtype=torch.int8, **dev), torch.empty(cap, d // 256, **f32)
+            self.r_xsum, self.r_w = torch.empty(cap, d // 16, dtype=torch.int16, **dev), torch.empty(cap, **f32)
+            self.back = torch.empty(rows, d, **f32)
+        self.xh = torch.empty(cap, d, dtype=torch.float16, **dev)
+        self.xe = torch.empty(cap, d // 256, 64, dtype=torch.float16, **dev) if pool.gate_fmt == Q2_K else None
+        self.g, self.u, self.mid = torch.empty(cap, ff, **f32), torch.empty(cap, ff, **f32), torch.empty(cap, ff, **f32)
+        self.wplace = torch.empty(cap, **f32)
+        self.mq = torch.empty(cap * ff, dtype=torch.int8, **dev)
+        self.ms, self.msum = torch.empty(cap * ff // 256, **f32), torch.empty(cap * ff // 16, dtype=torch.int16, **dev)
+        self.mh = torch.empty(cap, ff, dtype=torch.float16, **dev)
+        self.me = torch.empty(cap, ff // 256, 64, dtype=torch.float16, **dev) if pool.down_fmt == Q2_K else None
+        self.down = torch.empty(cap, d, **f32)
+        self.moe = torch.empty(n, d, **f32)
+
+
+def host_plan(cm, me, per):
+    """The plan of rank ME from every rank's rows per expert CM [world, E] (numpy):
+    send and receive counts per rank, the rows and first place of each local
+    expert, and per segment (source, local expert) where its rows arrive and where
+    they are placed -- place order is (expert, source, order of arrival), as
+    plan_dispatch has it."""
+    import numpy as np
+    world = cm.shape[0]
+    cm = cm.astype(np.int64)
+    send_counts = cm[me].reshape(world, per).sum(1)
+    rc = cm[:, me * per:(me + 1) * per]
+    recv_counts = rc.sum(1)
+    counts = rc.sum(0)
+    bases = np.cumsum(counts) - counts
+    src_off = np.cumsum(recv_counts) - recv_counts
+    in_src = np.cumsum(rc, 1) - rc
+    before = np.cumsum(rc, 0) - rc
+    return (send_counts, recv_counts, counts, bases, (src_off[:, None] + in_src).ravel(),
+            (bases[None, :] + before).ravel(), rc.ravel())
+
+
+def _a2a_bytes(dst, src, recv_counts, send_counts, group):
+    dist.all_to_all_single(dst.view(dst.shape[0], -1).view(torch.uint8), src.view(src.shape[0], -1).view(torch.uint8),
+                           output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+
+
+def chunk_fast(ex, sc, norms, logits, n_expert_total, group=None):
+    """CudaExperts.chunk with every step a kernel of the library, no allocation and
+    one host synchronisation (the ranks' rows per expert, which size the
+    exchanges).  Same result, bit for bit."""
+    import numpy as np
+    from . import _lib
+    pool = ex.pool
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    me = dist.get_rank(group) if dist.is_initialized() else 0
+    n, d = norms.shape
+    ff, nu, per = pool.ff, ex.nu, sc.per
+    rows = n * nu
+    E = n_expert_total
+    st = torch.cuda.current_stream().cuda_stream
+    ptr = lambda t: 0 if t is None else t.data_ptr()  # noqa: E731
+    call = _lib.call
+    call("ill_moe_route", E, nu, ex.mode, float(ex.scale), n, ptr(logits), 0, ptr(sc.sel), ptr(sc.w), st)
+    call("ill_moe_group", rows, E, nu, ptr(sc.sel), ptr(sc.w), ptr(sc.group), ptr(sc.counts), ptr(sc.bases), ptr(sc.rmap),
+         ptr(sc.smap), ptr(sc.wrow), st)
+    if world > 1:
+        dist.all_gather_into_tensor(sc.cmat.view(-1), sc.counts, group=group)
+    else:
+        sc.cmat.view(-1).copy_(sc.counts)
+    sc.cmat_host.copy_(sc.cmat, non_blocking=True)
+    # while the counts travel: what each row carries, in sending order
+    call("ill_quant_q8_k", ptr(norms), ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), n * d // 256, st)
+    call("ill_gather_rows", rows, d, ptr(sc.xq), ptr(sc.rmap), ptr(sc.s_xq), st)
+    call("ill_gather_rows", rows, d // 256 * 4, ptr(sc.xs), ptr(sc.rmap), ptr(sc.s_xs), st)
+    call("ill_gather_rows", rows, d // 16 * 2, ptr(sc.xsum), ptr(sc.rmap), ptr(sc.s_xsum), st)
+    torch.cuda.current_stream().synchronize()
+    send_counts, recv_counts, counts, bases, seg_a, seg_p, seg_l = host_plan(sc.cmat_host.numpy(), me, per)
+    nseg = world * per
+    ph = sc.plan_host.numpy()
+    ph[0:nseg], ph[nseg:2 * nseg], ph[2 * nseg:3 * nseg] = seg_a, seg_p, seg_l
+    ph[3 * nseg:3 * nseg + per], ph[3 * nseg + per:] = counts, bases
+    sc.plan.copy_(sc.plan_host, non_blocking=True)
+    total = int(recv_counts.sum())
+    if total > sc.cap:
+        raise ValueError("more rows than the scratch holds")
+    lcounts, lbases = sc.plan[3 * nseg:3 * nseg + per], sc.plan[3 * nseg + per:]
+    call("ill_ep_plan_rows", nseg, ptr(sc.plan), ptr(sc.plan) + 4 * nseg, ptr(sc.plan) + 8 * nseg, ptr(sc.p2r), ptr(sc.r2p), st)
+    if world > 1:
+        sl, rl = [int(x) for x in send_counts], [int(x) for x in recv_counts]
+        _a2a_bytes(sc.r_xq[:total], sc.s_xq, rl, sl, group)
+        _a2a_bytes(sc.r_xs[:total], sc.s_xs, rl, sl, group)
+        _a2a_bytes(sc.r_xsum[:total], sc.s_xsum, rl, sl, group)
+        _a2a_bytes(sc.r_w[:total].view(-1, 1), sc.wrow.view(-1, 1), rl, sl, group)
+        r_xq, r_xs, r_xsum, r_w = sc.r_xq, sc.r_xs, sc.r_xsum, sc.r_w
+    else:
+        r_xq, r_xs, r_xsum, r_w = sc.s_xq, sc.s_xs, sc.s_xsum, sc.wrow
+    if total:
+        call("ill_act_f16", total, d, ptr(r_xq), ptr(r_xsum), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), st)
+        for add, y in ((0, sc.g), (pool.gate_bytes, sc.u)):
+            call("ill_moe_mm_id", pool.gate_fmt, d, ff, add, ptr(pool.ptrs_all), ptr(lcounts), ptr(lbases), pool.n_expert, total,
+                 ptr(sc.xh), ptr(sc.xe), ptr(r_xs), ptr(sc.p2r), 0, ptr(y), ff, st)
+        call("ill_gather_rows", total, 4, ptr(r_w), ptr(sc.p2r), ptr(sc.wplace), st)
+        call("ill_swiglu_w", total * ff, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mid), st)
+        call("ill_quant_q8_k", ptr(sc.mid), ptr(sc.mq), ptr(sc.ms), ptr(sc.msum), total * ff // 256, st)
+        call("ill_act_f16", total, ff, ptr(sc.mq), ptr(sc.msum), 0, ptr(sc.mh), ptr(sc.me), st)
+        # the down rows leave in the order their inputs arrived
+        call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(lcounts), ptr(lbases),
+             pool.n_expert, total, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.p2r), ptr(sc.down), d, st)
+    if world > 1:
+        _a2a_bytes(sc.back, sc.down[:total], sl, rl, group)
+        back = sc.back
+    else:
+        back = sc.down
+    call("ill_moe_sum", d, nu, n, ptr(back), ptr(sc.smap), 0, ptr(sc.moe), st)
+    return sc.moe
 
 
 def head_rows(rows, world, rank):

@@ -230,8 +230,9 @@ ILL_API int ill_moe_group(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w
 ILL_API int ill_moe_group_static(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w, ill_dptr counts, ill_dptr bases,
                                  ill_dptr rmap, ill_dptr smap, ill_dptr wrow, ill_stream stream);
 
-/* DST row r = SRC row MAP[r], rows of ROW_BYTES bytes (a multiple of 16; both
- * 16-byte aligned).  Replaces d4_gather_rows (src/cuda/ds4f_chunk.cu:393). */
+/* DST row r = SRC row MAP[r], rows of ROW_BYTES bytes: a multiple of 16 with
+ * both 16-byte aligned, or a multiple of 4 with both 4-byte aligned.  Replaces
+ * d4_gather_rows (src/cuda/ds4f_chunk.cu:393). */
 ILL_API int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,
                             ill_stream stream);
 
@@ -251,18 +252,32 @@ ILL_API int ill_act_f16(int64_t rows, int cols, ill_dptr xq, ill_dptr bsums, ill
  * + ADD, X the Q8_K activations XH (+ XE for Q2_K) of ill_act_f16 with block
  * scales XD[t*(ncols/256) + kb], t = MAP[place] (MAP = 0: t = place).  COUNTS /
  * BASES are read on the device (no host synchronisation); TOTAL_ROWS is the
- * number of rows of XH and Y.
+ * number of rows of XH and Y.  With YMAP given, row `place` is written to row
+ * YMAP[place] of Y instead (expert parallelism: the rows leave in the order they
+ * arrived).
  *
- * tcgen05 MMA, 128 x 128 tiles: the operands are the integers of both sides as
- * fp16 (exact), accumulated per 256-wide block in tensor memory (fp32, two
- * buffers), and each block's sum is scaled by d_w * d_x in fp32 as it is
- * drained -- the arithmetic of the reference's CPU kernels (src/avx2.lisp:
+ * tcgen05 MMA, tiles of 128 weight rows x up to 128 rows of X: the operands are
+ * the integers of both sides as fp16 (exact; the weights' go straight from the
+ * dequantizing warps into tensor memory), accumulated per 256-wide block in
+ * tensor memory (fp32, two buffers), and each block's sum is scaled by d_w * d_x
+ * in fp32 as it is drained -- the arithmetic of the reference's CPU kernels (src/avx2.lisp:
  * 77-150), so results agree with them to fp32 rounding.  Replaces
  * d4_mm_id_iq2_xxs / d4_mm_id_q2_k (src/cuda/ds4f_mm.cu:229-257) behind
  * DK-FFN-ROUTED-CHUNK (src/cuda-ds4f-prefill.lisp:345-351). */
 ILL_API int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases,
-                          int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr y,
-                          int64_t y_stride, ill_stream stream);
+                          int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap,
+                          ill_dptr y, int64_t y_stride, ill_stream stream);
+
+/* Expert parallelism: the two row orders of a rank that receives rows from
+ * several sources.  Rows arrive source by source, each source's rows grouped by
+ * expert; the products want them expert by expert.  Segment i (one source, one
+ * expert) is SEG_LEN[i] rows that arrive at SEG_ARRIVAL[i] .. and are placed at
+ * SEG_PLACE[i] ..: fills P2R[place] = arrival index and R2P[arrival] = place
+ * (uint32).  The three tables (int32, NSEG each) come from the host, which knows
+ * every rank's counts after one small exchange.  No counterpart in the
+ * reference, whose experts never leave their GPU. */
+ILL_API int ill_ep_plan_rows(int nseg, ill_dptr seg_arrival, ill_dptr seg_place, ill_dptr seg_len, ill_dptr p2r,
+                             ill_dptr r2p, ill_stream stream);
 
 #ifdef __cplusplus
 }

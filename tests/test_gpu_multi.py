@@ -31,9 +31,41 @@ def test_world_of_one_equals_chunk_driver(cuda_lib):
     logits = torch.randn(n, CFG["ne"], device="cuda", generator=g)
     sc = P.make_chunk_scratch(pool, n, CFG["nu"])
     want = P.dk_ffn_routed_chunk(pool, norms, logits, CFG["nu"], 10.0, sc).clone()
-    got = EP.CudaExperts(pool, CFG["nu"], 10.0).chunk(norms, logits, CFG["ne"])
+    ce = EP.CudaExperts(pool, CFG["nu"], 10.0)
+    got = ce.chunk(norms, logits, CFG["ne"])
     assert torch.equal(got, want)
+    # the path without allocations or torch index arithmetic, twice over the same scratch
+    esc = EP.EpScratch(pool, n, CFG["nu"], CFG["ne"], 1)
+    for _ in range(2):
+        assert torch.equal(EP.chunk_fast(ce, esc, norms, logits, CFG["ne"]), want)
     assert D.device_status() == 0
+
+
+def test_plan_rows_and_gather_words(cuda_lib):
+    from illatio_b200 import _lib
+    rng = np.random.default_rng(5)
+    world, per = 3, 4
+    cm = rng.integers(0, 9, size=(world, world * per))
+    cm[1, :] = 0  # a source with nothing to send
+    send, recv, counts, bases, seg_a, seg_p, seg_l = EP.host_plan(cm, 2, per)
+    total = int(recv.sum())
+    tab = torch.tensor(np.concatenate([seg_a, seg_p, seg_l]).astype(np.int32), device="cuda")
+    nseg = world * per
+    p2r = torch.full((total,), -1, dtype=torch.int32, device="cuda")
+    r2p = torch.full((total,), -1, dtype=torch.int32, device="cuda")
+    _lib.call("ill_ep_plan_rows", nseg, tab.data_ptr(), tab.data_ptr() + 4 * nseg, tab.data_ptr() + 8 * nseg,
+              p2r.data_ptr(), r2p.data_ptr(), None)
+    p2r, r2p = p2r.cpu().numpy(), r2p.cpu().numpy()
+    # arrival order: source, then expert; place order: expert, then source
+    arrival = [(s, e, i) for s in range(world) for e in range(per) for i in range(cm[s, 2 * per + e])]
+    place = sorted(range(total), key=lambda a: (arrival[a][1], arrival[a][0], arrival[a][2]))
+    assert np.array_equal(p2r, np.array(place)) and np.array_equal(r2p[p2r], np.arange(total))
+    assert np.array_equal(counts, cm[:, 2 * per:3 * per].sum(0)) and send.sum() == cm[2].sum()
+    src = torch.arange(total * 3, dtype=torch.float32, device="cuda").view(total, 3)  # rows of 12 bytes
+    dst = torch.empty_like(src)
+    m = torch.as_tensor(p2r.astype(np.int32), device="cuda")
+    _lib.call("ill_gather_rows", total, 12, src.data_ptr(), m.data_ptr(), dst.data_ptr(), None)
+    assert torch.equal(dst, src[m.long()])
 
 
 WORKER = r"""
@@ -56,8 +88,11 @@ logits = torch.randn(n, cfg["ne"], device="cuda", generator=g)
 sc = P.make_chunk_scratch(full, n, cfg["nu"])
 want = P.dk_ffn_routed_chunk(full, norms, logits, cfg["nu"], 10.0, sc)
 lo, hi = rank * n // world, (rank + 1) * n // world
-got = EP.CudaExperts(mine, cfg["nu"], 10.0).chunk(norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"])
-ok = torch.equal(got, want[lo:hi]) and D.device_status() == 0
+ce = EP.CudaExperts(mine, cfg["nu"], 10.0)
+got = ce.chunk(norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"])
+esc = EP.EpScratch(mine, hi - lo, cfg["nu"], cfg["ne"], world)
+fast = [EP.chunk_fast(ce, esc, norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"]).clone() for _ in range(2)]
+ok = torch.equal(got, want[lo:hi]) and all(torch.equal(f, want[lo:hi]) for f in fast) and D.device_status() == 0
 if not ok:
     print("rank", rank, "max abs difference", (got - want[lo:hi]).abs().max().item(), file=sys.stderr)
 flag = torch.tensor([1 if ok else 0], device="cuda")

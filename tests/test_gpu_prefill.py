@@ -64,7 +64,7 @@ def test_mm_id_matches_oracle_rows(oracle, fmt, rows_w, cols, counts):
     bases = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.int32)
     dcounts, dbases = to_dev(np.array(counts, np.int32)), to_dev(bases)
     _lib.call("ill_moe_mm_id", fmt, cols, rows_w, 0, ptrs.data_ptr(), dcounts.data_ptr(), dbases.data_ptr(), ne, total,
-              xh.data_ptr(), xe.data_ptr(), dxd.data_ptr(), 0, y.data_ptr(), rows_w, None)
+              xh.data_ptr(), xe.data_ptr(), dxd.data_ptr(), 0, 0, y.data_ptr(), rows_w, None)
     got = y.cpu().numpy()
     assert (got[total:] == 7.0).all()
     want = np.empty((total, rows_w), np.float32)
