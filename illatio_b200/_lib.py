@@ -43,6 +43,9 @@ SIGNATURES = {
     "ill_act_f16": (_I, [_L, _I, _P, _P, _P, _P, _P, _S]),
     "ill_moe_mm_id": (_I, [_I, _I, _I, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),
     "ill_ep_plan_rows": (_I, [_I, _P, _P, _P, _P, _P, _S]),
+    "ill_ep_row_bytes": (_L, [_I]),
+    "ill_ep_pack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _S]),
+    "ill_ep_unpack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _S]),
 }
 
 

@@ -207,27 +207,24 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // IQ2_XXS: one sub-block (IDX: four grid indices; AUX: four groups of seven signs, and the scale):
 // the 32 integers grid * sign * (2 LS + 1) (at most 43 * 31: exact in fp16).  The block's float
 // part is d / 8 (src/avx2.lisp:77-110 takes the products this way).  GRID points at this lane's copy
-// of the grid (sixteen interleaved copies: entry e of copy c at [16 e + c], so the sixteen lanes of
-// a 64-bit request never share a bank); SGN at this lane's copy of the table that turns four sign
-// bits into the sign bits of two pairs of halves (entry x of copy c at [32 x + c]).  The eighth
-// sign of a group is the parity of the seven stored ones (ksigns_iq2xs[i] = i | parity(i) << 7).
-__device__ __forceinline__ void w_iq2xxs(uint32_t idx, uint32_t aux, const uint2* grid, const uint2* sgn, uint32_t* out) {
-  // (1024 + g) * s - 1024 s = g * s
-  const uint32_t s2 = small_h2(2 * (aux >> 28) + 1), bias = hmul2(s2, 0xe400e400u /* -1024 */);
-  uint2 g[4], ml[4], mh[4];
+// of the grid as halves (16 bytes an entry, eight interleaved copies: entry e of copy c at [8 e + c],
+// so the eight lanes of a 128-bit request's quarter never share a bank); SGN likewise at the table
+// that gives, for the seven stored sign bits, the sign bits of the eight halves (the eighth sign is
+// the parity of the seven: ksigns_iq2xs[i] = i | parity(i) << 7).
+__device__ __forceinline__ void w_iq2xxs(uint32_t idx, uint32_t aux, const uint4* grid, const uint4* sgn, uint32_t* out) {
+  const uint32_t s2 = small_h2(2 * (aux >> 28) + 1);
+  uint4 g[4], m[4];
 #pragma unroll
   for (int l = 0; l < 4; ++l) {
-    const uint32_t s7 = (aux >> (7 * l)) & 127u;
-    g[l] = grid[16 * ((idx >> (8 * l)) & 0xff)];
-    ml[l] = sgn[32 * (s7 & 15u)];
-    mh[l] = sgn[32 * ((s7 >> 4) | ((__popc(s7) & 1u) << 3))];
+    g[l] = grid[8 * ((idx >> (8 * l)) & 0xff)];
+    m[l] = sgn[8 * ((aux >> (7 * l)) & 127u)];
   }
 #pragma unroll
   for (int l = 0; l < 4; ++l) {
-    out[4 * l] = hfma2(bytes_to_h2_1024(g[l].x, 0x4140), s2, bias) ^ ml[l].x;
-    out[4 * l + 1] = hfma2(bytes_to_h2_1024(g[l].x, 0x4342), s2, bias) ^ ml[l].y;
-    out[4 * l + 2] = hfma2(bytes_to_h2_1024(g[l].y, 0x4140), s2, bias) ^ mh[l].x;
-    out[4 * l + 3] = hfma2(bytes_to_h2_1024(g[l].y, 0x4342), s2, bias) ^ mh[l].y;
+    out[4 * l] = hmul2(g[l].x, s2) ^ m[l].x;
+    out[4 * l + 1] = hmul2(g[l].y, s2) ^ m[l].y;
+    out[4 * l + 2] = hmul2(g[l].z, s2) ^ m[l].z;
+    out[4 * l + 3] = hmul2(g[l].w, s2) ^ m[l].w;
   }
 }
 
@@ -265,6 +262,9 @@ template <int FMT> struct MmGeom {
   static constexpr int BB = FMT == ILL_Q2_K ? 84 : 66;
   static constexpr int NSLOT = FMT == ILL_Q2_K ? 4 : 8;  // a multiple of four: a slot is always written by the same warps
   static constexpr int NX = FMT == ILL_Q2_K ? 6 : 8;     // stages of the ring of X tiles = K steps in flight
+  // A dequantizing warp waits for K step st - NSLOT on barrier (st - NSLOT) % NX; the barrier's next phase (K step
+  // st - NSLOT + NX) must not be able to complete before that warp has passed, or the parity it waits for comes round again
+  static_assert(NX >= NSLOT, "the ring of K-step barriers must be at least as long as the ring of A slots");
   static constexpr int NE = FMT == ILL_Q2_K ? 4 : 0;     // Q2_K: two tiles of X's sums of 16, two of the mins
   static constexpr uint32_t A_COL = FMT == ILL_Q2_K ? 384 : 256, DM_COL = 256;
   // A row's raw block reaches shared memory as the WIN bytes from the 16-byte boundary at or before it,
@@ -273,7 +273,7 @@ template <int FMT> struct MmGeom {
   static constexpr uint32_t RAW_BYTES = 128 * PITCH;
   static constexpr size_t SMEM = (size_t)(NX + NE) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
                                  512 /* barriers */ + 4 * 256 * 4 /* weight scales */ + MM_XSC * 128 * 4 /* X scales */ +
-                                 2304 /* experts' first tiles */ + (FMT == ILL_IQ2_XXS ? 16 * 2048 + 4096 : 0) /* tables */ +
+                                 2304 /* experts' first tiles */ + (FMT == ILL_IQ2_XXS ? 8 * 4096 + 8 * 2048 : 0) /* tables */ +
                                  1024 /* alignment */;
 };
 
@@ -307,8 +307,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   float* wsc = (float*)(tail + 512);             // [4 blocks in flight][2: d, dmin][128 weight rows]
   float* xsc = wsc + 4 * 256;                    // [XSC blocks][128 rows of X] the activations' block scales
   int* tile_first = (int*)(xsc + MM_XSC * 128);  // [ne + 1] first row tile of each expert; the total
-  uint2* iq_grid = (uint2*)((u8*)tile_first + 2304);  // sixteen interleaved copies
-  uint2* iq_sgn = iq_grid + 16 * 256;            // [16 nibbles][32 copies]
+  uint4* iq_grid = (uint4*)((u8*)tile_first + 2304);  // [256 entries][8 copies] the grid as halves
+  uint4* iq_sgn = iq_grid + 8 * 256;             // [128 entries][8 copies] sign bits of the eight halves
 
   // the warp number through a shuffle: the compiler then knows that the role branches are warp-uniform
   const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
@@ -341,13 +341,22 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     mbar_fence_init();
   }
   if (FMT == ILL_IQ2_XXS) {
-    for (int i = tid; i < 16 * 256; i += MM_THREADS) {
-      const uint64_t g = ill_iq2xxs_grid[i >> 4];
-      iq_grid[i] = make_uint2((uint32_t)g, (uint32_t)(g >> 32));
+    for (int i = tid; i < 8 * 256; i += MM_THREADS) {
+      const uint64_t g = ill_iq2xxs_grid[i >> 3];
+      uint32_t h[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const __half2 hh = __floats2half2_rn((float)((g >> (16 * k)) & 0xff), (float)((g >> (16 * k + 8)) & 0xff));
+        h[k] = *(const uint32_t*)&hh;
+      }
+      iq_grid[i] = make_uint4(h[0], h[1], h[2], h[3]);
     }
-    for (int i = tid; i < 16 * 32; i += MM_THREADS) {
-      const uint32_t x = (uint32_t)i >> 5;  // signs of elements 0..3: the sign bits of the halves (0, 1) and (2, 3)
-      iq_sgn[i] = make_uint2(((x & 1u) << 15) | ((x & 2u) << 30), ((x & 4u) << 13) | ((x & 8u) << 28));
+    for (int i = tid; i < 8 * 128; i += MM_THREADS) {
+      const uint32_t s7 = (uint32_t)i >> 3, sg = s7 | ((__popc(s7) & 1u) << 7);
+      uint32_t h[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) h[k] = (((sg >> (2 * k)) & 1u) << 15) | (((sg >> (2 * k + 1)) & 1u) << 31);
+      iq_sgn[i] = make_uint4(h[0], h[1], h[2], h[3]);
     }
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
@@ -477,7 +486,10 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         if (use > 0) w_ok = mbar_wait(&raw_empty[s], (uint32_t)(use - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 2, 200);
         if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
 #pragma unroll
-        for (int i = 0; i < 128 / NL; ++i) cp_async4(xsc + (g_kb % MM_XSC) * 128 + L + i * NL, xdp[i] + kb);
+        for (int i = 0; i < 128 / NL; ++i) {
+          cp_async4(xsc + (g_kb % MM_XSC) * 128 + L + i * NL, xdp[i] + kb);
+
+        }
         u8* dst = (u8*)raw + s * G::RAW_BYTES;
 #pragma unroll 4
         for (int c = L; c < 128 * CPR; c += NL) {
@@ -559,12 +571,30 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       const int n = nt * MM_BN + m;
       if (ok && n < p.nrows) {
         const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
+        float* ycol = p.y + n;
+        const unsigned ys = (unsigned)p.y_stride;
+        if (p.ymap) {
+          const unsigned* ym = p.ymap + row0;
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i < nvalid) {
-            const long long yr = p.ymap ? (long long)__ldg(p.ymap + row0 + i) : (long long)row0 + i;
-            p.y[yr * p.y_stride + n] = __uint_as_float((uint32_t)(out[i >> 1] >> (32 * (i & 1)))) * fin;
+          for (int i0 = 0; i0 < 128; i0 += 8) {
+            if (i0 < nvalid) {
+              unsigned yr[8];  // the rows first, then the stores: a load does not wait for the store before it
+#pragma unroll
+              for (int i = 0; i < 8; ++i) yr[i] = i0 + i < nvalid ? __ldg(ym + i0 + i) : 0u;
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                if (i0 + i < nvalid)
+                  ycol[(size_t)yr[i] * ys] = __uint_as_float((uint32_t)(out[(i0 + i) >> 1] >> (32 * (i & 1)))) * fin;
+            }
           }
+        } else {
+          ycol += (size_t)row0 * ys;
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            if (i < nvalid) *ycol = __uint_as_float((uint32_t)(out[i >> 1] >> (32 * (i & 1)))) * fin;
+            ycol += ys;
+          }
+        }
       }
     }
   } else {
@@ -575,8 +605,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     const int t = tid - 32 * (2 + MM_LD_WARPS + MM_DR_WARPS);  // 0..511
     const int row = t & 127, j = t >> 7;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's lanes: rows (warp % 4) * 32 ..
-    const uint2* grid = iq_grid + (lane & 15);
-    const uint2* sgn = iq_sgn + lane;
+    const uint4* grid = iq_grid + (lane & 7);
+    const uint4* sgn = iq_sgn + (lane & 7);
     int g_kb = 0;                                  // blocks produced so far by this CTA
 
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
@@ -677,10 +707,15 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
 // The Q8_K activations as the tensor cores take them, in expert order: XH[place, k] = fp16(q[t, k])
 // (exact), t = MAP[place] (or place when MAP is null); and, when XE is given, the sums of 16 as
 // XE[place, kb, 0..15] = fp16(bsums[t, 16 kb ..]) (exact: at most 2032), the other 48 of each 64 zero.
-__global__ void __launch_bounds__(256) act_f16_kernel(long long rows, int cols, const i8* __restrict__ xq,
-                                                      const int16_t* __restrict__ bsums,
+// Row t's quants are at XQ + t * XQ_STRIDE bytes and its sums at BSUMS + t * BS_STRIDE bytes.  With XD_OUT,
+// the row also carries its block scales (SC + t * XQ_STRIDE) and a weight (WT + t * XQ_STRIDE), copied
+// to XD_OUT[place, kb] and W_OUT[place]: the rows of an expert-parallel exchange, unpacked.
+__global__ void __launch_bounds__(256) act_f16_kernel(long long rows, int cols, const u8* __restrict__ xq, long long xq_stride,
+                                                      const u8* __restrict__ bsums, long long bs_stride,
                                                       const unsigned* __restrict__ map, __half* __restrict__ xh,
-                                                      __half* __restrict__ xe) {
+                                                      __half* __restrict__ xe, const u8* __restrict__ sc,
+                                                      const u8* __restrict__ wt, float* __restrict__ xd_out,
+                                                      float* __restrict__ w_out) {
   pdl_launch_dependents();
   pdl_wait();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread: 16 values
@@ -689,7 +724,7 @@ __global__ void __launch_bounds__(256) act_f16_kernel(long long rows, int cols, 
   const long long place = gid / per_row;
   const int j = (int)(gid - place * per_row);
   const long long t = map ? (long long)map[place] : place;
-  const uint4 q = *(const uint4*)(xq + t * cols + 16 * j);
+  const uint4 q = *(const uint4*)(xq + t * xq_stride + 16 * j);
   const uint32_t w[4] = {q.x, q.y, q.z, q.w};
   uint32_t h[8];
 #pragma unroll
@@ -706,10 +741,37 @@ __global__ void __launch_bounds__(256) act_f16_kernel(long long rows, int cols, 
     // this thread's 16 quants are one sum of 16: element j%16 of block j/16; it also clears 3 of the 48 zeros
     const int kb = j >> 4, g = j & 15;
     __half* e = xe + (place * (cols / 256) + kb) * 64;
-    e[g] = __float2half_rn((float)bsums[t * (cols / 16) + j]);
+    e[g] = __float2half_rn((float)((const int16_t*)(bsums + t * bs_stride))[j]);
     e[16 + 3 * g] = __float2half_rn(0.0f);
     e[16 + 3 * g + 1] = __float2half_rn(0.0f);
     e[16 + 3 * g + 2] = __float2half_rn(0.0f);
+  }
+  if (xd_out) {
+    if (j < cols / 256) xd_out[place * (cols / 256) + j] = ((const float*)(sc + t * xq_stride))[j];
+    if (j == per_row - 1) w_out[place] = *(const float*)(wt + t * xq_stride);
+  }
+}
+
+// A row of an expert-parallel exchange: the token's Q8_K form and its routing weight in one piece,
+//   [cols int8 quants][cols/256 float scales][cols/16 int16 sums][float weight][pad to 16 bytes]
+// PACKED[place] from token MAP[place]'s quantized activations and W[place].  One block a row.
+__global__ void __launch_bounds__(128) ep_pack_kernel(int cols, long long row_bytes, const uint32_t* __restrict__ xq,
+                                                      const uint32_t* __restrict__ xs, const uint32_t* __restrict__ xsum,
+                                                      const uint32_t* __restrict__ w, const unsigned* __restrict__ map,
+                                                      uint32_t* __restrict__ packed) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long place = blockIdx.x;
+  const long long t = map[place];
+  const int nq = cols / 4, ns = cols / 256, nb = cols / 32;  // words of quants, scales, sums
+  uint32_t* dst = packed + place * (row_bytes / 4);
+  for (int i = threadIdx.x; i < nq + ns + nb + 1; i += blockDim.x) {
+    uint32_t v;
+    if (i < nq) v = xq[t * nq + i];
+    else if (i < nq + ns) v = xs[t * ns + (i - nq)];
+    else if (i < nq + ns + nb) v = xsum[t * nb + (i - nq - ns)];
+    else v = w[place];
+    dst[i] = v;
   }
 }
 
@@ -733,21 +795,60 @@ static EncodeTiledFn encode_tiled_fn() {
 
 using namespace ill;
 
+static int act_f16_launch(int64_t rows, int cols, const u8* qp, long long qs, const u8* bp, long long bs, ill_dptr map,
+                          ill_dptr xh, ill_dptr xe, const u8* sc, const u8* wt, ill_dptr xd_out, ill_dptr w_out,
+                          ill_stream stream) {
+  long long nrows = rows;
+  const unsigned* mp = (const unsigned*)(uintptr_t)map;
+  __half* hp = (__half*)(uintptr_t)xh;
+  __half* ep = (__half*)(uintptr_t)xe;
+  float* xo = (float*)(uintptr_t)xd_out;
+  float* wo = (float*)(uintptr_t)w_out;
+  void* args[] = {&nrows, &cols, &qp, &qs, &bp, &bs, &mp, &hp, &ep, &sc, &wt, &xo, &wo};
+  const long long threads = rows * (cols / 16);
+  return launch_kernel((const void*)act_f16_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, args,
+                       (cudaStream_t)stream);
+}
+
 extern "C" int ill_act_f16(int64_t rows, int cols, ill_dptr xq, ill_dptr bsums, ill_dptr map, ill_dptr xh, ill_dptr xe,
                            ill_stream stream) {
   if (rows < 0 || cols <= 0 || cols % 256 || !xq || !xh || (xe && !bsums)) return ILL_ERR_ARG;
   if ((xq & 15) || (bsums & 1) || (map & 3) || (xh & 15) || (xe & 15)) return ILL_ERR_ALIGN;
   if (rows == 0) return ILL_OK;
-  long long nrows = rows;
-  const i8* qp = (const i8*)(uintptr_t)xq;
-  const int16_t* bp = (const int16_t*)(uintptr_t)bsums;
+  return act_f16_launch(rows, cols, (const u8*)(uintptr_t)xq, cols, (const u8*)(uintptr_t)bsums, cols / 8, map, xh, xe, nullptr,
+                        nullptr, 0, 0, stream);
+}
+
+extern "C" int64_t ill_ep_row_bytes(int cols) {
+  if (cols <= 0 || cols % 256) return 0;
+  return ((int64_t)cols + cols / 256 * 4 + cols / 16 * 2 + 4 + 15) / 16 * 16;
+}
+
+extern "C" int ill_ep_pack(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr w, ill_dptr map,
+                           ill_dptr packed, ill_stream stream) {
+  if (rows < 0 || cols <= 0 || cols % 256 || !xq || !xs || !xsum || !w || !map || !packed) return ILL_ERR_ARG;
+  if ((xq & 3) || (xs & 3) || (xsum & 3) || (w & 3) || (map & 3) || (packed & 15)) return ILL_ERR_ALIGN;
+  if (rows == 0) return ILL_OK;
+  long long rb = ill_ep_row_bytes(cols);
+  const uint32_t* qp = (const uint32_t*)(uintptr_t)xq;
+  const uint32_t* sp = (const uint32_t*)(uintptr_t)xs;
+  const uint32_t* bp = (const uint32_t*)(uintptr_t)xsum;
+  const uint32_t* wp = (const uint32_t*)(uintptr_t)w;
   const unsigned* mp = (const unsigned*)(uintptr_t)map;
-  __half* hp = (__half*)(uintptr_t)xh;
-  __half* ep = (__half*)(uintptr_t)xe;
-  void* args[] = {&nrows, &cols, &qp, &bp, &mp, &hp, &ep};
-  const long long threads = rows * (cols / 16);
-  return launch_kernel((const void*)act_f16_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, args,
-                       (cudaStream_t)stream);
+  uint32_t* pp = (uint32_t*)(uintptr_t)packed;
+  void* args[] = {&cols, &rb, &qp, &sp, &bp, &wp, &mp, &pp};
+  return launch_kernel((const void*)ep_pack_kernel, dim3((unsigned)rows), dim3(128), 0, args, (cudaStream_t)stream);
+}
+
+extern "C" int ill_ep_unpack(int64_t rows, int cols, ill_dptr packed, ill_dptr map, ill_dptr xh, ill_dptr xe, ill_dptr xd,
+                             ill_dptr w, ill_stream stream) {
+  if (rows < 0 || cols <= 0 || cols % 256 || !packed || !xh || !xd || !w) return ILL_ERR_ARG;
+  if ((packed & 15) || (map & 3) || (xh & 15) || (xe & 15) || (xd & 3) || (w & 3)) return ILL_ERR_ALIGN;
+  if (rows == 0) return ILL_OK;
+  const long long rb = ill_ep_row_bytes(cols);
+  const u8* base = (const u8*)(uintptr_t)packed;
+  return act_f16_launch(rows, cols, base, rb, base + cols + cols / 256 * 4, rb, map, xh, xe, base + cols,
+                        base + cols + cols / 256 * 4 + cols / 16 * 2, xd, w, stream);
 }
 
 static int encode_map(CUtensorMap* map, ill_dptr base, int64_t inner, int64_t rows) {
@@ -767,7 +868,8 @@ extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dpt
                              int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap,
                              ill_dptr y, int64_t y_stride, ill_stream stream) {
   if (fmt != ILL_IQ2_XXS && fmt != ILL_Q2_K) return ILL_ERR_UNSUPPORTED;
-  if (ncols <= 0 || ncols % 256 || nrows <= 0 || ne <= 0 || ne > 65535 || total_rows < 0 || y_stride < nrows)
+  if (ncols <= 0 || ncols % 256 || nrows <= 0 || ne <= 0 || ne > 65535 || total_rows < 0 || y_stride < nrows ||
+      y_stride > 0xffffffffll)
     return ILL_ERR_ARG;
   if (!ptrs || !counts || !bases || !xh || !xd || !y || (fmt == ILL_Q2_K && !xe)) return ILL_ERR_ARG;
   if ((ptrs & 7) || (counts & 3) || (bases & 3) || (xh & 15) || (xe & 15) || (xd & 3) || (map & 3) || (ymap & 3) || (y & 15) ||

@@ -222,13 +222,13 @@ class EpScratch:
         self.p2r, self.r2p = torch.empty(cap, **i32), torch.empty(cap, **i32)
         self.xq = torch.empty(n * d, dtype=torch.int8, **dev)
         self.xs, self.xsum = torch.empty(n * d // 256, **f32), torch.empty(n * d // 16, dtype=torch.int16, **dev)
-        # what a row carries, in the order it is sent / as it arrives
-        self.s_xq, self.s_xs = torch.empty(rows, d, dtype=torch.int8, **dev), torch.empty(rows, d // 256, **f32)
-        self.s_xsum = torch.empty(rows, d // 16, dtype=torch.int16, **dev)
+        # the rows as they are sent (a token's Q8_K form and the slot's weight in one piece) and as they arrive
+        self.row_bytes = _lib.lib().ill_ep_row_bytes(d)
+        self.s_rows = torch.empty(rows, self.row_bytes, **u8)
         if world > 1:
-            self.r_xq, self.r_xs = torch.empty(cap, d, dtype=torch.int8, **dev), torch.empty(cap, d // 256, **f32)
-            self.r_xsum, self.r_w = torch.empty(cap, d // 16, dtype=torch.int16, **dev), torch.empty(cap, **f32)
+            self.r_rows = torch.empty(cap, self.row_bytes, **u8)
             self.back = torch.empty(rows, d, **f32)
+        self.xd = torch.empty(cap, d // 256, **f32)
         self.xh = torch.empty(cap, d, dtype=torch.float16, **dev)
         self.xe = torch.empty(cap, d // 256, 64, dtype=torch.float16, **dev) if pool.gate_fmt == Q2_K else None
         self.g, self.u, self.mid = torch.empty(cap, ff, **f32), torch.empty(cap, ff, **f32), torch.empty(cap, ff, **f32)
@@ -263,6 +263,7 @@ def host_plan(cm, me, per):
 
 
 def _a2a_bytes(dst, src, recv_counts, send_counts, group):
+    """All-to-all of rows as bytes (NCCL has no 16-bit integer type, and the payload is opaque to it anyway)."""
     dist.all_to_all_single(dst.view(dst.shape[0], -1).view(torch.uint8), src.view(src.shape[0], -1).view(torch.uint8),
                            output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
 
@@ -293,9 +294,7 @@ def chunk_fast(ex, sc, norms, logits, n_expert_total, group=None):
     sc.cmat_host.copy_(sc.cmat, non_blocking=True)
     # while the counts travel: what each row carries, in sending order
     call("ill_quant_q8_k", ptr(norms), ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), n * d // 256, st)
-    call("ill_gather_rows", rows, d, ptr(sc.xq), ptr(sc.rmap), ptr(sc.s_xq), st)
-    call("ill_gather_rows", rows, d // 256 * 4, ptr(sc.xs), ptr(sc.rmap), ptr(sc.s_xs), st)
-    call("ill_gather_rows", rows, d // 16 * 2, ptr(sc.xsum), ptr(sc.rmap), ptr(sc.s_xsum), st)
+    call("ill_ep_pack", rows, d, ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.s_rows), st)
     torch.cuda.current_stream().synchronize()
     send_counts, recv_counts, counts, bases, seg_a, seg_p, seg_l = host_plan(sc.cmat_host.numpy(), me, per)
     nseg = world * per
@@ -310,19 +309,16 @@ def chunk_fast(ex, sc, norms, logits, n_expert_total, group=None):
     call("ill_ep_plan_rows", nseg, ptr(sc.plan), ptr(sc.plan) + 4 * nseg, ptr(sc.plan) + 8 * nseg, ptr(sc.p2r), ptr(sc.r2p), st)
     if world > 1:
         sl, rl = [int(x) for x in send_counts], [int(x) for x in recv_counts]
-        _a2a_bytes(sc.r_xq[:total], sc.s_xq, rl, sl, group)
-        _a2a_bytes(sc.r_xs[:total], sc.s_xs, rl, sl, group)
-        _a2a_bytes(sc.r_xsum[:total], sc.s_xsum, rl, sl, group)
-        _a2a_bytes(sc.r_w[:total].view(-1, 1), sc.wrow.view(-1, 1), rl, sl, group)
-        r_xq, r_xs, r_xsum, r_w = sc.r_xq, sc.r_xs, sc.r_xsum, sc.r_w
+        dist.all_to_all_single(sc.r_rows[:total], sc.s_rows, output_split_sizes=rl, input_split_sizes=sl, group=group)
+        r_rows = sc.r_rows
     else:
-        r_xq, r_xs, r_xsum, r_w = sc.s_xq, sc.s_xs, sc.s_xsum, sc.wrow
+        r_rows = sc.s_rows
     if total:
-        call("ill_act_f16", total, d, ptr(r_xq), ptr(r_xsum), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), st)
+        # the arrived rows as the products want them, expert by expert
+        call("ill_ep_unpack", total, d, ptr(r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), st)
         for add, y in ((0, sc.g), (pool.gate_bytes, sc.u)):
             call("ill_moe_mm_id", pool.gate_fmt, d, ff, add, ptr(pool.ptrs_all), ptr(lcounts), ptr(lbases), pool.n_expert, total,
-                 ptr(sc.xh), ptr(sc.xe), ptr(r_xs), ptr(sc.p2r), 0, ptr(y), ff, st)
-        call("ill_gather_rows", total, 4, ptr(r_w), ptr(sc.p2r), ptr(sc.wplace), st)
+                 ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, 0, ptr(y), ff, st)
         call("ill_swiglu_w", total * ff, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mid), st)
         call("ill_quant_q8_k", ptr(sc.mid), ptr(sc.mq), ptr(sc.ms), ptr(sc.msum), total * ff // 256, st)
         call("ill_act_f16", total, ff, ptr(sc.mq), ptr(sc.msum), 0, ptr(sc.mh), ptr(sc.me), st)

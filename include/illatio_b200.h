@@ -246,6 +246,22 @@ ILL_API int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_d
 ILL_API int ill_act_f16(int64_t rows, int cols, ill_dptr xq, ill_dptr bsums, ill_dptr map, ill_dptr xh, ill_dptr xe,
                         ill_stream stream);
 
+/* Expert parallelism: a (token, slot) row travels to the rank that holds its
+ * expert as one piece, the token's Q8_K form and the slot's weight:
+ *   [cols int8 quants][cols/256 float scales][cols/16 int16 sums][float weight]
+ * padded to a multiple of 16 bytes = ill_ep_row_bytes(cols).  ill_ep_pack fills
+ * PACKED[place] from token MAP[place] of XQ / XS / XSUM (ill_quant_q8_k) and
+ * W[place] (the WROW of ill_moe_group).  ill_ep_unpack is ill_act_f16 on rows that
+ * arrived packed: XH / XE as there, plus XD[place, kb] (the scales
+ * ill_moe_mm_id wants, so that it needs no MAP) and W[place]; MAP[place] is the
+ * arrival index of the row placed at `place` (the P2R of ill_ep_plan_rows; 0:
+ * the same).  No counterpart in the reference. */
+ILL_API int64_t ill_ep_row_bytes(int cols);
+ILL_API int ill_ep_pack(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr w, ill_dptr map,
+                        ill_dptr packed, ill_stream stream);
+ILL_API int ill_ep_unpack(int64_t rows, int cols, ill_dptr packed, ill_dptr map, ill_dptr xh, ill_dptr xe, ill_dptr xd,
+                          ill_dptr w, ill_stream stream);
+
 /* The routed experts' product for a chunk: for each expert e < NE and each row
  * `place` in [BASES[e], BASES[e] + COUNTS[e]): Y[place*y_stride + n] = W_e[n] .
  * X[place], n < NROWS, W_e the FMT (ILL_IQ2_XXS or ILL_Q2_K) matrix at PTRS[e]
