@@ -433,9 +433,11 @@ def main():
             "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": HIDDEN * 4,
                     "d2h_bytes_per_step": VOCAB * 4},
             "gpu_launches": launches_per_step[0] * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "mv_kernel<Q4_K, GLU> (gate/up 2 x 9728x2560)",
+            "roofline": {"bound": "hbm", "kernel": "mvw_kernel<Q4_K, gated> (gate/up 2 x 9728x2560)",
                          "achieved": achieved, "peak": peak, "peak_source": which + " (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else which,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "unit": "GB/s", "frac": achieved / peak,
+                         # dram__bytes_read + write of one launch, from the ncu capture summarised under profiles/
+                         "traffic": 28053760.0,
                          "us_per_launch": glu_us, "algorithmic_bytes_per_launch": glu_bytes},
             "clocks": clocks, "formats": formats, "device_status": status,
             "head_rowsplit": {"rows_per_gpu": end_row - first_row, "us_per_token": head_us,
