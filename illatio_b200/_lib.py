@@ -27,6 +27,7 @@ SIGNATURES = {
     "ill_device_status": (_I, [_c.POINTER(_c.c_uint), _S]),
     "ill_quant_q8_0": (_I, [_P, _P, _P, _P, _L, _I, _S]),
     "ill_quant_q8_k": (_I, [_P, _P, _P, _P, _L, _S]),
+    "ill_rmsnorm_q8": (_I, [_I, _P, _P, _P, _P, _P, _P, _I, _F, _L, _I, _S]),
     "ill_dequant_rows": (_I, [_I, _P, _I, _P, _L, _I, _P, _S]),
     "ill_mv": (_I, [_I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _S]),
     "ill_mv_3": (_I, [_I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _S]),
@@ -35,6 +36,7 @@ SIGNATURES = {
     "ill_moe_glu": (_I, [_I, _I, _I, _L, _L, _P, _I, _P, _P, _P, _I, _F, _P, _P, _L, _S]),
     "ill_swiglu_w": (_I, [_L, _I, _F, _P, _P, _P, _P, _S]),
     "ill_moe_sum": (_I, [_I, _I, _L, _P, _P, _P, _P, _S]),
+    "ill_swiglu_q8k_f16": (_I, [_L, _I, _F, _P, _P, _P, _P, _P, _P, _S]),
     "ill_moe_route": (_I, [_I, _I, _I, _F, _L, _P, _P, _P, _P, _S]),
     "ill_moe_group_scratch_bytes": (_L, [_L, _I]),
     "ill_moe_group": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _S]),

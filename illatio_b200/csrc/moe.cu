@@ -214,6 +214,75 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(long long rows, int ro
   dst[gid] = src[(long long)map[r] * row_vec + j];
 }
 
+// d4_swiglu_w, the Q8_K quantizer and the conversion to the tensor cores' operands in one pass: a warp a
+// 256-wide block of a row's middle values, lane l its elements 8l .. 8l+7.  Every step is the arithmetic of
+// swiglu_w_kernel, quant_q8_k_kernel and act_f16_kernel in turn, so the results are theirs bit for bit; the
+// middle values and their int8 form never go to memory.
+__global__ void __launch_bounds__(256) swiglu_q8k_f16_kernel(long long nblocks, int ff, float clamp,
+                                                             const float* __restrict__ g, const float* __restrict__ u,
+                                                             const float* __restrict__ w, __half* __restrict__ mh,
+                                                             __half* __restrict__ me, float* __restrict__ ms) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= nblocks) return;
+  const float wv = w ? w[b / (ff / 256)] : 1.0f;
+  const float4 g0 = ((const float4*)(g + b * 256))[2 * lane], g1 = ((const float4*)(g + b * 256))[2 * lane + 1];
+  const float4 u0 = ((const float4*)(u + b * 256))[2 * lane], u1 = ((const float4*)(u + b * 256))[2 * lane + 1];
+  const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+  const float us[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float gv = gs[j], uv = us[j];
+    if (clamp > 1e-6f) { gv = fminf(gv, clamp); uv = fmaxf(-clamp, fminf(uv, clamp)); }
+    v[j] = __fmul_rn(__fmul_rn(__fmul_rn(gv, d4_sigmoid(gv)), uv), wv);
+  }
+  // QUANTIZE-Q8K! (src/kquant.lisp:130-167): the largest magnitude, the first of equal ones, and its value
+  float amax = 0.0f, mx = 0.0f;
+  int idx = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float a = fabsf(v[j]);
+    if (a > amax) { amax = a; mx = v[j]; idx = 8 * lane + j; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float oa = __shfl_xor_sync(0xffffffffu, amax, o), om = __shfl_xor_sync(0xffffffffu, mx, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (oa > amax || (oa == amax && oi < idx)) { amax = oa; mx = om; idx = oi; }
+  }
+  int q[8];
+  float d = 0.0f;
+  if (amax == 0.0f) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = 0;
+  } else {
+    const float iscale = __fdiv_rn(-127.0f, mx);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = min(127, __float2int_rn(__fmul_rn(iscale, v[j])));
+    d = __fdiv_rn(1.0f, iscale);
+  }
+  uint32_t h[4];
+  int s = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    s += q[2 * j] + q[2 * j + 1];
+    const __half2 hh = __floats2half2_rn((float)q[2 * j], (float)q[2 * j + 1]);
+    h[j] = *(const uint32_t*)&hh;
+  }
+  ((uint4*)(mh + b * 256))[lane] = make_uint4(h[0], h[1], h[2], h[3]);
+  if (lane == 0) ms[b] = d;
+  if (me) {
+    // the block's sixteen sums of 16 as halves, then 48 zeros (the rest of the 64-wide K step of the mins' product)
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    __half* e = me + b * 64;
+    if (!(lane & 1)) e[lane >> 1] = __float2half_rn((float)s);
+    if (lane < 24) ((uint32_t*)(e + 16))[lane] = 0u;
+  }
+}
+
 // the same for rows that are a whole number of 4-byte words only
 __global__ void __launch_bounds__(256) gather_rows4_kernel(long long rows, int row_words, const uint32_t* __restrict__ src,
                                                            const unsigned* __restrict__ map, uint32_t* __restrict__ dst) {
@@ -424,6 +493,23 @@ extern "C" int ill_moe_group_static(int64_t rows, int ne, int nu, ill_dptr sel, 
   const unsigned* bs = bp;
   void* args[] = {&nrows, &ne, &nu, &selp, &rk, &bc, &bs, &wp, &rp, &sp, &wr};
   return launch_kernel((const void*)group_scatter_kernel, dim3((unsigned)((rows + 255) / 256)), dim3(256), 0, args, st);
+}
+
+extern "C" int ill_swiglu_q8k_f16(int64_t rows, int ff, float clamp, ill_dptr g, ill_dptr u, ill_dptr w, ill_dptr mh,
+                                  ill_dptr me, ill_dptr ms, ill_stream stream) {
+  if (rows < 0 || ff <= 0 || ff % 256 || !g || !u || !mh || !ms) return ILL_ERR_ARG;
+  if ((g & 15) || (u & 15) || (w & 3) || (mh & 15) || (me & 15) || (ms & 3)) return ILL_ERR_ALIGN;
+  if (rows == 0) return ILL_OK;
+  long long nb = rows * (ff / 256);
+  const float* gp = (const float*)(uintptr_t)g;
+  const float* up = (const float*)(uintptr_t)u;
+  const float* wp = (const float*)(uintptr_t)w;
+  __half* hp = (__half*)(uintptr_t)mh;
+  __half* ep = (__half*)(uintptr_t)me;
+  float* sp = (float*)(uintptr_t)ms;
+  void* args[] = {&nb, &ff, &clamp, &gp, &up, &wp, &hp, &ep, &sp};
+  return launch_kernel((const void*)swiglu_q8k_f16_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, args,
+                       (cudaStream_t)stream);
 }
 
 extern "C" int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,

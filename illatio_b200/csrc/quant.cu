@@ -12,15 +12,9 @@
 
 namespace ill {
 
-__global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict__ x, i8* __restrict__ xq,
-                                                         float* __restrict__ xs, int* __restrict__ xsum,
-                                                         long long nblocks, int f16_scale) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (b >= nblocks) return;
-  const float v = x[b * 32 + lane];
+// One Q8_0 block: lane l holds element l.
+__device__ __forceinline__ void quant_block_q8_0(float v, int lane, long long b, i8* __restrict__ xq, float* __restrict__ xs,
+                                                 int* __restrict__ xsum, int f16_scale) {
   float amax = fabsf(v);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -37,17 +31,9 @@ __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict
   if (lane == 0) xs[b] = f16_scale ? __half2float(__float2half_rn(d)) : d;
 }
 
-// A warp a super-block; lane l holds elements 8l .. 8l+7.
-__global__ void __launch_bounds__(256) quant_q8_k_kernel(const float* __restrict__ x, i8* __restrict__ xq,
-                                                         float* __restrict__ xd, int16_t* __restrict__ bsums,
-                                                         long long nblocks) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (b >= nblocks) return;
-  const float4 v0 = ((const float4*)(x + b * 256))[2 * lane], v1 = ((const float4*)(x + b * 256))[2 * lane + 1];
-  const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+// One Q8_K super-block: lane l holds elements 8l .. 8l+7.
+__device__ __forceinline__ void quant_block_q8_k(const float (&v)[8], int lane, long long b, i8* __restrict__ xq,
+                                                 float* __restrict__ xd, int16_t* __restrict__ bsums) {
   // the largest magnitude, the first of equal ones, and the value that has it
   float amax = 0.0f, mx = 0.0f;
   int idx = 0;
@@ -85,6 +71,84 @@ __global__ void __launch_bounds__(256) quant_q8_k_kernel(const float* __restrict
   s += __shfl_xor_sync(0xffffffffu, s, 1);
   if (!(lane & 1)) bsums[b * 16 + (lane >> 1)] = (int16_t)s;
   if (lane == 0) xd[b] = d;
+}
+
+__global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict__ x, i8* __restrict__ xq,
+                                                         float* __restrict__ xs, int* __restrict__ xsum,
+                                                         long long nblocks, int f16_scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= nblocks) return;
+  quant_block_q8_0(x[b * 32 + lane], lane, b, xq, xs, xsum, f16_scale);
+}
+
+// A warp a super-block; lane l holds elements 8l .. 8l+7.
+__global__ void __launch_bounds__(256) quant_q8_k_kernel(const float* __restrict__ x, i8* __restrict__ xq,
+                                                         float* __restrict__ xd, int16_t* __restrict__ bsums,
+                                                         long long nblocks) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= nblocks) return;
+  const float4 v0 = ((const float4*)(x + b * 256))[2 * lane], v1 = ((const float4*)(x + b * 256))[2 * lane + 1];
+  const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  quant_block_q8_k(v, lane, b, xq, xd, bsums);
+}
+
+// RMSNORM! (src/model.lisp:205-216) fused with the activation quantizer, as the reference's rmsnorm_q8
+// launch is (src/cuda/dense.cu:144-160, RMSNORM-Q8 src/cuda-dense.lisp:260-264): the squares (rounded to
+// float) summed in double, scale = 1 / sqrt(float(sum / d + eps)), value = (x * scale) * w, then the
+// blocks quantized as the stand-alone quantizers do.  Grid (slices, rows): every CTA of a row works the
+// row's scale out for itself (the row comes from L2) and takes a slice of its blocks, so that one token's
+// norm is not one CTA's serial work.  The double sum is taken in a different order than the CPU's loop;
+// the two agree until the float the sum is rounded to sits within 1e-16 of a rounding boundary.
+template <int K8K>
+__global__ void __launch_bounds__(256) rmsnorm_q8_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                         float* __restrict__ h, i8* __restrict__ xq, float* __restrict__ xs,
+                                                         void* __restrict__ xsum, int d, float eps, int f16_scale) {
+  __shared__ double part[8];
+  __shared__ float scale_s;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const long long base = (long long)blockIdx.y * d;
+  const float* xr = x + base;
+  double acc = 0.0;
+  for (int i = tid; i < d; i += 256) acc += (double)__fmul_rn(xr[i], xr[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) part[warp] = acc;
+  __syncthreads();
+  if (tid == 0) {
+    double t = 0.0;
+    for (int i = 0; i < 8; ++i) t += part[i];
+    scale_s = __fdiv_rn(1.0f, __fsqrt_rn((float)(t / (double)d + (double)eps)));
+  }
+  __syncthreads();
+  const float sc = scale_s;
+  constexpr int BW = K8K ? 256 : 32;
+  const int nb = d / BW;
+  for (int b = blockIdx.x * 8 + warp; b < nb; b += gridDim.x * 8) {
+    const long long gb = base / BW + b;
+    if constexpr (K8K) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = b * 256 + 8 * lane + j;
+        v[j] = __fmul_rn(__fmul_rn(xr[i], sc), w[i]);
+        if (h) h[base + i] = v[j];
+      }
+      quant_block_q8_k(v, lane, gb, xq, xs, (int16_t*)xsum);
+    } else {
+      const int i = b * 32 + lane;
+      const float v = __fmul_rn(__fmul_rn(xr[i], sc), w[i]);
+      if (h) h[base + i] = v;
+      quant_block_q8_0(v, lane, gb, xq, xs, (int*)xsum, f16_scale);
+    }
+  }
 }
 
 template <int FMT>
@@ -130,6 +194,27 @@ extern "C" int ill_quant_q8_k(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsu
   void* args[] = {&xp, &qp, &dp, &bp, &nb};
   return launch_kernel((const void*)quant_q8_k_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), 0, args,
                        (cudaStream_t)stream);
+}
+
+extern "C" int ill_rmsnorm_q8(int kind, ill_dptr x, ill_dptr w, ill_dptr h, ill_dptr xq, ill_dptr xs, ill_dptr xsum, int d,
+                              float eps, int64_t n, int f16_scale, ill_stream stream) {
+  const int bw = kind == 1 ? 256 : 32;
+  if ((kind != 0 && kind != 1) || d <= 0 || d % bw || n < 0 || n > 65535 || !x || !w || !xq || !xs || (kind == 1 && !xsum))
+    return ILL_ERR_ARG;
+  if ((x & 3) || (w & 3) || (h & 3) || (xs & 3) || (xsum & (kind == 1 ? 1 : 3)) || (kind == 1 && (xq & 7))) return ILL_ERR_ALIGN;
+  if (n == 0) return ILL_OK;
+  const float* xp = (const float*)(uintptr_t)x;
+  const float* wp = (const float*)(uintptr_t)w;
+  float* hp = (float*)(uintptr_t)h;
+  i8* qp = (i8*)(uintptr_t)xq;
+  float* sp = (float*)(uintptr_t)xs;
+  void* bp = (void*)(uintptr_t)xsum;
+  void* args[] = {&xp, &wp, &hp, &qp, &sp, &bp, &d, &eps, &f16_scale};
+  // a single row is spread over its blocks; many rows take a CTA each
+  const int nb = d / bw;
+  const unsigned slices = n == 1 ? (unsigned)((nb + 7) / 8) : 1u;
+  const void* k = kind == 1 ? (const void*)rmsnorm_q8_kernel<1> : (const void*)rmsnorm_q8_kernel<0>;
+  return launch_kernel(k, dim3(slices, (unsigned)n), dim3(256), 0, args, (cudaStream_t)stream);
 }
 
 extern "C" int ill_dequant_rows(int fmt, ill_dptr w, int cols, ill_dptr row_ids, int64_t first_row, int nrows,

@@ -99,6 +99,14 @@ def quant_q8(x, act, f16_scale=True):
     return act
 
 
+def rmsnorm_q8(x, w, act, d, eps, n=1, h=None, f16_scale=True):
+    """RMSNORM-Q8 (src/cuda-dense.lisp:260-264): RMSNORM! of N rows of X (D wide) by
+    W, quantized into ACT in the kind it holds; H, when given, also gets the floats."""
+    _lib.call("ill_rmsnorm_q8", 1 if act.kind == "q8k" else 0, _ptr(x), _ptr(w), _ptr(h), _ptr(act.xq), _ptr(act.xs),
+              _ptr(act.xsum), d, float(eps), n, 1 if f16_scale else 0, _stream())
+    return act
+
+
 def cmat_mul(w, act, y, n=1, bias=None, acc=False):
     """CMAT-MUL (src/cuda-dense.lisp:220-248): Y = W X for N tokens (token t's X
     at t*cols, its Y at t*rows), or Y += it when ACC."""

@@ -78,7 +78,7 @@ def mm_id(pool, fmt, ncols, nrows, add, sc, xh, xe, xd, rmap, y):
               pool.n_expert, sc.rows, _ptr(xh), _ptr(xe), _ptr(xd), _ptr(rmap), 0, _ptr(y), nrows, _stream())
 
 
-def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, scale=1.0, shared=None):
+def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, scale=1.0, shared=None, fused=True):
     """DK-FFN-ROUTED-CHUNK (src/cuda-ds4f-prefill.lisp:315-356): the chunk's N
     tokens (NORMS [n, d] floats, LOGITS [n, ne] router logits) through their
     routed experts; returns MOE [n, d] (plus SHARED [n, d] when given)."""
@@ -92,9 +92,13 @@ def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, s
     act_f16(sc.xq, d, sc.rows, sc.rmap, sc.xh, sc.xe)
     mm_id(pool, pool.gate_fmt, d, ff, 0, sc, sc.xh, sc.xe, sc.xq.xs, sc.rmap, sc.g)
     mm_id(pool, pool.gate_fmt, d, ff, pool.gate_bytes, sc, sc.xh, sc.xe, sc.xq.xs, sc.rmap, sc.u)
-    swiglu_w(sc.g, sc.u, sc.wrow, sc.mid, ff, clamp)
-    D.quant_q8(sc.mid, sc.midq)                                    # per (token, slot) row, as the CPU path does
-    act_f16(sc.midq, ff, sc.rows, None, sc.mh, sc.me)
+    if fused:  # the three steps below in one pass (same results bit for bit; sc.mid and sc.midq.xq stay unwritten)
+        _lib.call("ill_swiglu_q8k_f16", sc.rows, ff, float(clamp), _ptr(sc.g), _ptr(sc.u), _ptr(sc.wrow), _ptr(sc.mh),
+                  _ptr(sc.me), _ptr(sc.midq.xs), st)
+    else:
+        swiglu_w(sc.g, sc.u, sc.wrow, sc.mid, ff, clamp)
+        D.quant_q8(sc.mid, sc.midq)                                # per (token, slot) row, as the CPU path does
+        act_f16(sc.midq, ff, sc.rows, None, sc.mh, sc.me)
     mm_id(pool, pool.down_fmt, ff, d, 2 * pool.gate_bytes, sc, sc.mh, sc.me, sc.midq.xs, None, sc.down)
     _lib.call("ill_moe_sum", d, nu, n, _ptr(sc.down), _ptr(sc.smap), _ptr(shared), _ptr(sc.moe), st)
     return sc.moe

@@ -231,10 +231,9 @@ class EpScratch:
         self.xd = torch.empty(cap, d // 256, **f32)
         self.xh = torch.empty(cap, d, dtype=torch.float16, **dev)
         self.xe = torch.empty(cap, d // 256, 64, dtype=torch.float16, **dev) if pool.gate_fmt == Q2_K else None
-        self.g, self.u, self.mid = torch.empty(cap, ff, **f32), torch.empty(cap, ff, **f32), torch.empty(cap, ff, **f32)
+        self.g, self.u = torch.empty(cap, ff, **f32), torch.empty(cap, ff, **f32)
         self.wplace = torch.empty(cap, **f32)
-        self.mq = torch.empty(cap * ff, dtype=torch.int8, **dev)
-        self.ms, self.msum = torch.empty(cap * ff // 256, **f32), torch.empty(cap * ff // 16, dtype=torch.int16, **dev)
+        self.ms = torch.empty(cap * ff // 256, **f32)
         self.mh = torch.empty(cap, ff, dtype=torch.float16, **dev)
         self.me = torch.empty(cap, ff // 256, 64, dtype=torch.float16, **dev) if pool.down_fmt == Q2_K else None
         self.down = torch.empty(cap, d, **f32)
@@ -319,9 +318,8 @@ def chunk_fast(ex, sc, norms, logits, n_expert_total, group=None):
         for add, y in ((0, sc.g), (pool.gate_bytes, sc.u)):
             call("ill_moe_mm_id", pool.gate_fmt, d, ff, add, ptr(pool.ptrs_all), ptr(lcounts), ptr(lbases), pool.n_expert, total,
                  ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, 0, ptr(y), ff, st)
-        call("ill_swiglu_w", total * ff, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mid), st)
-        call("ill_quant_q8_k", ptr(sc.mid), ptr(sc.mq), ptr(sc.ms), ptr(sc.msum), total * ff // 256, st)
-        call("ill_act_f16", total, ff, ptr(sc.mq), ptr(sc.msum), 0, ptr(sc.mh), ptr(sc.me), st)
+        call("ill_swiglu_q8k_f16", total, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mh), ptr(sc.me),
+             ptr(sc.ms), st)
         # the down rows leave in the order their inputs arrived
         call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(lcounts), ptr(lbases),
              pool.n_expert, total, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.p2r), ptr(sc.down), d, st)

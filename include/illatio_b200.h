@@ -112,6 +112,16 @@ ILL_API int ill_quant_q8_0(ill_dptr x, ill_dptr xq, ill_dptr xs, ill_dptr xsum, 
  * its CPU path and these do not. */
 ILL_API int ill_quant_q8_k(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums, int64_t nblocks, ill_stream stream);
 
+/* RMSNORM! (src/model.lisp:205-216) of N rows of X (D wide) by W, fused with the
+ * activation quantizer: value = (x * scale) * w with scale = 1 / sqrt(float(sum
+ * of squares in double / d + eps)), then quantized as ill_quant_q8_0 (KIND 0;
+ * XSUM int32 per block or 0; F16_SCALE as there) or ill_quant_q8_k (KIND 1; XSUM
+ * int16 per 16, required).  H, when not 0, also receives the normalized floats.
+ * Replaces the rmsnorm_q8 launch (RMSNORM-Q8, src/cuda-dense.lisp:260-264;
+ * src/cuda/dense.cu:144-160), which quantizes to Q8_0 only. */
+ILL_API int ill_rmsnorm_q8(int kind, ill_dptr x, ill_dptr w, ill_dptr h, ill_dptr xq, ill_dptr xs, ill_dptr xsum, int d,
+                           float eps, int64_t n, int f16_scale, ill_stream stream);
+
 /* ---- rows as floats --------------------------------------------------------- */
 
 /* OUT[i*cols ..] = row ROW_IDS[i] (int32, on the device) of the FMT matrix W
@@ -177,6 +187,17 @@ ILL_API int ill_moe_glu(int fmt, int ncols, int nrows, int64_t gate_add, int64_t
  * with ill_quant_q8_0 / ill_quant_q8_k. */
 ILL_API int ill_swiglu_w(int64_t n, int ff, float clamp, ill_dptr g, ill_dptr u, ill_dptr w, ill_dptr mid,
                          ill_stream stream);
+
+/* ill_swiglu_w, ill_quant_q8_k and ill_act_f16 of the middle values in one
+ * pass, for the chunk path: MH[r*ff + j] = fp16 of the Q8_K quant of row r's
+ * j-th middle value, MS[r*(ff/256) + kb] its block scales, and with ME given
+ * (Q2_K down weights) ME[(r*(ff/256) + kb)*64 + i] the sums of 16 as ill_act_f16
+ * lays them out.  Bit for bit what the three calls produce; the middle values
+ * and their int8 form are not written.  (The reference keeps d4_swiglu_w and
+ * the quantizer apart, src/cuda-ds4f-prefill.lisp:348-349; fusing them is its own
+ * open item, TODO.md:16-21.) */
+ILL_API int ill_swiglu_q8k_f16(int64_t rows, int ff, float clamp, ill_dptr g, ill_dptr u, ill_dptr w, ill_dptr mh,
+                               ill_dptr me, ill_dptr ms, ill_stream stream);
 
 /* MOE[t*d + r] = sum over slots s < NU, in slot order, of DOWN[row(t,s)*d + r]
  * (+ SHARED[t*d + r] unless 0); row(t,s) = MAP[t*nu + s], or t*nu + s when MAP

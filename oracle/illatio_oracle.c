@@ -167,6 +167,18 @@ void orc_dequant_row(int fmt, const uint8_t* w, int ncols, float* out) {
 /* QUANTIZE-Q8!, src/tensor.lisp:245-262.  f16_scale: *Q8-F16-SCALE* (ggml's
  * rounding of the stored scale); 0 keeps the float, as ds4's path does
  * (src/ds4f.lisp:1052-1053). */
+/* RMSNORM! (src/model.lisp:205-216): the squares (each rounded to float) summed in double in index order, the
+ * scale a float, x scaled before it is weighted. */
+void orc_rmsnorm(const float* x, const float* w, int64_t n, float eps, float* out) {
+  double sum = 0.0;
+  for (int64_t i = 0; i < n; ++i) {
+    const float p = x[i] * x[i];
+    sum += (double)p;
+  }
+  const float scale = 1.0f / sqrtf((float)(sum / (double)n + (double)eps));
+  for (int64_t i = 0; i < n; ++i) out[i] = (x[i] * scale) * w[i];
+}
+
 void orc_quantize_q8_0(const float* x, int64_t n, int8_t* q, float* s, int f16_scale) {
   for (int64_t b = 0; b < n / 32; ++b) {
     const float* xb = x + b * 32;

@@ -62,6 +62,27 @@ def test_quant_q8_k_bit_exact(oracle):
     assert np.array_equal(act.xsum.cpu().numpy().astype(np.int32), bs)
 
 
+@pytest.mark.parametrize("kind,d,n", [("q8", 896, 1), ("q8k", 2560, 1), ("q8k", 5120, 5), ("q8", 4864, 3)])
+def test_rmsnorm_q8_matches_oracle(oracle, kind, d, n):
+    """RMSNorm fused with the quantizer: the normalized floats, the quants and the scales of the CPU routines."""
+    rng = np.random.default_rng(d + n)
+    x = (rng.standard_normal((n, d)) * rng.uniform(0.01, 30.0, (n, 1))).astype(np.float32)
+    w = rng.standard_normal(d).astype(np.float32)
+    act = D.make_qact(n * d, kind, want_xsum=True)
+    h = torch.empty(n, d, device="cuda")
+    D.rmsnorm_q8(to_dev(x), to_dev(w), act, d, 1e-6, n, h=h)
+    want = np.stack([oracle.rmsnorm(x[t], w, 1e-6) for t in range(n)])
+    assert np.array_equal(h.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    if kind == "q8":
+        q, s = oracle.quantize_q8_0(want)
+        assert np.array_equal(act.xsum.cpu().numpy(), q.reshape(-1, 32).astype(np.int32).sum(1))
+    else:
+        q, s, bs = oracle.quantize_q8k(want)
+        assert np.array_equal(act.xsum.cpu().numpy().astype(np.int32), bs)
+    assert np.array_equal(act.xq.cpu().numpy(), q)
+    assert np.array_equal(act.xs.cpu().numpy().view(np.uint32), s.view(np.uint32))
+
+
 @pytest.mark.parametrize("fmt", FMTS)
 def test_dequant_rows_bit_exact_golden(fmt):
     z = np.load(os.path.join(GOLD, "dequant_%s.npz" % B.NAMES[fmt]))

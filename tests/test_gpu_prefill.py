@@ -96,3 +96,19 @@ def test_chunk_matches_oracle_small(oracle, d, ff, ne, nu, n, gate_fmt, clamp):
                      for t in range(n)])
     a, _ = rel_errors(got, want)
     assert a < TOL_SPEC and a < 2e-4, a
+
+
+@pytest.mark.parametrize("gate_fmt", [B.IQ2_XXS, B.Q2_K])
+def test_fused_middle_equals_three_steps(gate_fmt):
+    """SwiGLU + Q8_K + operand conversion in one pass: the same bits as the three separate launches."""
+    d, ff, ne, nu, n = 512, 512, 4, 2, 70
+    _, pool = _pool(d, ff, ne, gate_fmt, seed=9)
+    rng = np.random.default_rng(4)
+    norms, logits = to_dev(rng.standard_normal((n, d)).astype(np.float32)), to_dev(rng.standard_normal((n, ne)).astype(np.float32))
+    sc = P.make_chunk_scratch(pool, n, nu)
+    apart = P.dk_ffn_routed_chunk(pool, norms, logits, nu, 7.0, sc, fused=False).clone()
+    mh, me, ms = sc.mh.clone(), sc.me.clone(), sc.midq.xs.clone()
+    sc.mh.zero_(), sc.me.fill_(3.0), sc.midq.xs.zero_()
+    fused = P.dk_ffn_routed_chunk(pool, norms, logits, nu, 7.0, sc, fused=True)
+    assert torch.equal(sc.mh, mh) and torch.equal(sc.me, me) and torch.equal(sc.midq.xs, ms)
+    assert torch.equal(fused, apart)

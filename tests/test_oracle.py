@@ -68,6 +68,18 @@ def test_half_conversions(oracle):
     assert np.array_equal(got16, want16)
 
 
+def test_rmsnorm(oracle):
+    """RMSNORM! (src/model.lisp:205-216): float squares summed in double, float scale, x scaled then weighted."""
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal(2560).astype(np.float32) * 7
+    w = rng.standard_normal(2560).astype(np.float32)
+    eps = np.float32(1e-6)
+    scale = np.float32(1) / np.sqrt(np.float32((x * x).astype(np.float64).sum() / 2560 + np.float64(eps)))
+    assert np.array_equal(oracle.rmsnorm(x, w, eps), (x * scale) * w)
+    assert np.allclose(oracle.rmsnorm(x, w, eps), x.astype(np.float64) / np.sqrt((x.astype(np.float64) ** 2).mean() + 1e-6) * w,
+                       rtol=1e-6, atol=1e-6)
+
+
 def test_quantize_q8_0(oracle):
     rng = np.random.default_rng(5)
     x = rng.standard_normal(32 * 64).astype(np.float32)
