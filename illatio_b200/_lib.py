@@ -37,6 +37,7 @@ SIGNATURES = {
     "ill_swiglu_w": (_I, [_L, _I, _F, _P, _P, _P, _P, _S]),
     "ill_moe_sum": (_I, [_I, _I, _L, _P, _P, _P, _P, _S]),
     "ill_swiglu_q8k_f16": (_I, [_L, _I, _F, _P, _P, _P, _P, _P, _P, _S]),
+    "ill_mv_dense": (_I, [_I, _P, _I, _I, _P, _P, _I, _L, _S]),
     "ill_moe_route": (_I, [_I, _I, _I, _F, _L, _P, _P, _P, _P, _S]),
     "ill_moe_group_scratch_bytes": (_L, [_L, _I]),
     "ill_moe_group": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _S]),

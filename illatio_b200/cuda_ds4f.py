@@ -74,6 +74,18 @@ def dk_q8mv(w, x, y, q=None):
     return q
 
 
+F32, F16, BF16 = 0, 1, 2
+_DENSE_TYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+
+def dk_mv16(w, x, y, n=1):
+    """DK-MV16 (src/cuda-ds4f.lisp:767-771): Y = W X for an unquantized tensor W [rows, cols]
+    (float32, float16 or bfloat16 on the device) and N tokens' float activations."""
+    rows, cols = w.shape
+    _lib.call("ill_mv_dense", _DENSE_TYPES[w.dtype], _ptr(w), rows, cols, _ptr(x), _ptr(y), n, rows, _stream())
+    return y
+
+
 def swiglu_w(g, u, w, mid, ff, clamp):
     """d4_swiglu_w (src/cuda-ds4f.lisp:939): MID = silu(min(G,c)) * clamp(U) * W[row]."""
     _lib.call("ill_swiglu_w", g.numel(), ff, float(clamp), _ptr(g), _ptr(u), _ptr(w), _ptr(mid), _stream())

@@ -217,6 +217,21 @@ ILL_API int ill_moe_sum(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map
 ILL_API int ill_moe_route(int ne, int nu, int mode, float scale, int64_t ntok, ill_dptr logits, ill_dptr bias,
                           ill_dptr sel, ill_dptr weights, ill_stream stream);
 
+/* Element types of the unquantized tensors ill_mv_dense takes. */
+#define ILL_F32 0
+#define ILL_F16 1
+#define ILL_BF16 2
+
+/* Y[t*y_stride + r] = W[r] . X[t] for the ROWS x COLS matrix W of F32 / F16 /
+ * BF16 values (row-major, as in the file) and N <= 16 tokens' float
+ * activations X [n, cols]; fp32 accumulate.  The router's logits and the other
+ * small unquantized tensors between the quantized products: DK-MV16
+ * (src/cuda-ds4f.lisp:767-771; d4_mv_f16 src/cuda/ds4f.cu:145, g53_mv_bf16,
+ * d41_mv_f32 and their several-token forms).  The CPU path is F32MV!
+ * (src/ds4f.lisp:256-276) on weights widened to float. */
+ILL_API int ill_mv_dense(int type, ill_dptr w, int rows, int cols, ill_dptr x, ill_dptr y, int n, int64_t y_stride,
+                         ill_stream stream);
+
 /* Bytes of scratch ill_moe_group needs for ROWS (token, slot) rows and NE experts. */
 ILL_API int64_t ill_moe_group_scratch_bytes(int64_t rows, int ne);
 

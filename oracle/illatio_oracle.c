@@ -167,6 +167,17 @@ void orc_dequant_row(int fmt, const uint8_t* w, int ncols, float* out) {
 /* QUANTIZE-Q8!, src/tensor.lisp:245-262.  f16_scale: *Q8-F16-SCALE* (ggml's
  * rounding of the stored scale); 0 keeps the float, as ds4's path does
  * (src/ds4f.lisp:1052-1053). */
+/* F32MV! (src/ds4f.lisp:256-276), the plain loop: a float accumulator a row, columns in order.  W is already
+ * widened to float (the CPU path keeps the F16 / BF16 tensors that way, src/ds4f.lisp:102-108). */
+void orc_f32mv(const float* w, int rows, int cols, const float* x, float* out) {
+  for (int r = 0; r < rows; ++r) {
+    float acc = 0.0f;
+    const float* row = w + (int64_t)r * cols;
+    for (int j = 0; j < cols; ++j) acc += row[j] * x[j];
+    out[r] = acc;
+  }
+}
+
 /* RMSNORM! (src/model.lisp:205-216): the squares (each rounded to float) summed in double in index order, the
  * scale a float, x scaled before it is weighted. */
 void orc_rmsnorm(const float* x, const float* w, int64_t n, float eps, float* out) {

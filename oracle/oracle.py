@@ -48,6 +48,7 @@ def lib():
         L.orc_dequant_row.argtypes = [_c.c_int, _u8p, _c.c_int, _f32p]
         L.orc_quantize_q8_0.argtypes = [_f32p, _c.c_int64, _i8p, _f32p, _c.c_int]
         L.orc_rmsnorm.argtypes = [_f32p, _f32p, _c.c_int64, _c.c_float, _f32p]
+        L.orc_f32mv.argtypes = [_f32p, _c.c_int, _c.c_int, _f32p, _f32p]
         L.orc_quantize_q8k.argtypes = [_f32p, _c.c_int64, _i8p, _f32p, _i32p]
         L.orc_row_dot.restype = _c.c_float
         L.orc_row_dot.argtypes = [_c.c_int, _u8p, _c.c_int, _i8p, _f32p, _i32p]
@@ -100,6 +101,15 @@ def dequant(fmt, w, rows, cols):
     L = lib()
     for r in range(rows):
         L.orc_dequant_row(fmt, _p(w[r * rb:], _u8p), cols, _p(out[r], _f32p))
+    return out
+
+
+def f32mv(w, x):
+    """F32MV!: out[r] = row r of W (floats, [rows, cols]) . x."""
+    w, x = _c_(w, np.float32), _c_(x, np.float32).reshape(-1)
+    rows, cols = w.shape
+    out = np.empty(rows, np.float32)
+    lib().orc_f32mv(_p(w, _f32p), rows, cols, _p(x, _f32p), _p(out, _f32p))
     return out
 
 

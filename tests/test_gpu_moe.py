@@ -108,3 +108,25 @@ def test_shared_expert_matches_oracle(oracle):
     want = oracle.moe_shared(d, ff, mats[0], mats[1], mats[2], x, clamp, threads=4)
     a, _ = rel_errors(out.cpu().numpy(), want)
     assert a < TOL_SPEC, a
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols,n", [(256, 4096, 1), (37, 1000, 3), (5, 250, 16)])
+def test_mv_dense_matches_f32mv(oracle, dtype, rows, cols, n):
+    """The router's matvec and its kin: unquantized weights, float activations, the CPU's float dot as the check."""
+    rng = np.random.default_rng(rows + cols)
+    w = torch.as_tensor(rng.standard_normal((rows, cols)).astype(np.float32)).to(dtype)
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    y = torch.full((n, rows + 3), 5.0, device="cuda")
+    wd, xd = w.cuda(), to_dev(x)
+    _lib.call("ill_mv_dense", M._DENSE_TYPES[dtype], wd.data_ptr(), rows, cols, xd.data_ptr(), y.data_ptr(), n, rows + 3, None)
+    got = y.cpu().numpy()
+    assert (got[:, rows:] == 5.0).all()
+    wf = w.to(torch.float32).numpy()  # the CPU path's widened copy
+    for t in range(n):
+        want = oracle.f32mv(wf, x[t])
+        terms = np.abs(wf.astype(np.float64) * x[t].astype(np.float64)).sum(1)
+        assert (np.abs(got[t, :rows] - want) <= 1e-6 * terms + 1e-30).all()
+    y1 = torch.empty(rows, device="cuda")
+    M.dk_mv16(wd, xd[:1], y1)
+    assert torch.equal(y1, y[0, :rows])

@@ -210,3 +210,18 @@ def test_moe_routed_composition(oracle):
         dn = oracle.matvec(B.Q2_K, down[e * d * drb:(e + 1) * d * drb], d, ff, oracle.quantize_q8k(m))[0]
         want = (want + dn).astype(np.float32)
     assert np.array_equal(moe, want)
+
+
+def test_f32mv(oracle):
+    """F32MV!'s plain loop: a float accumulator, columns in order."""
+    rng = np.random.default_rng(12)
+    w = rng.standard_normal((7, 300)).astype(np.float32)
+    x = rng.standard_normal(300).astype(np.float32)
+    got = oracle.f32mv(w, x)
+    want = np.empty(7, np.float32)
+    for r in range(7):
+        acc = np.float32(0)
+        for j in range(300):
+            acc = np.float32(acc + np.float32(w[r, j] * x[j]))
+        want[r] = acc
+    assert np.array_equal(got, want)
