@@ -775,6 +775,88 @@ __global__ void __launch_bounds__(128) ep_pack_kernel(int cols, long long row_by
   }
 }
 
+// ep_pack_kernel for exchanges of a fixed size: rank g's rows go to slab g of PACKED, CAP rows a slab, in the
+// order of their places; PSLOT[place] = the row's slot (g * cap + index in the slab).  BASES[e] = first place
+// of expert e on this rank (ill_moe_group), so destination g's rows are places [bases[g * per], bases[(g + 1) *
+// per]).  A slab that would overflow sets *OVERFLOW and drops the rows past CAP.
+__global__ void __launch_bounds__(128) ep_pack_cap_kernel(int cols, long long row_bytes, const uint32_t* __restrict__ xq,
+                                                          const uint32_t* __restrict__ xs, const uint32_t* __restrict__ xsum,
+                                                          const uint32_t* __restrict__ w, const unsigned* __restrict__ map,
+                                                          const unsigned* __restrict__ bases, int per, int world, int cap,
+                                                          long long rows, uint32_t* __restrict__ packed,
+                                                          unsigned* __restrict__ pslot, unsigned* __restrict__ overflow) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long place = blockIdx.x;
+  __shared__ long long slot_s;
+  if (threadIdx.x == 0) {
+    int g = 0;
+    while (g + 1 < world && (long long)bases[(g + 1) * per] <= place) ++g;
+    const long long idx = place - (long long)bases[g * per];
+    if (idx >= cap) { atomicOr(overflow, 1u); slot_s = -1; pslot[place] = 0; }
+    else { slot_s = (long long)g * cap + idx; pslot[place] = (unsigned)slot_s; }
+  }
+  __syncthreads();
+  const long long slot = slot_s;
+  if (slot < 0) return;
+  const long long t = map[place];
+  const int nq = cols / 4, ns = cols / 256, nb = cols / 32;  // words of quants, scales, sums
+  uint32_t* dst = packed + slot * (row_bytes / 4);
+  for (int i = threadIdx.x; i < nq + ns + nb + 1; i += blockDim.x) {
+    uint32_t v;
+    if (i < nq) v = xq[t * nq + i];
+    else if (i < nq + ns) v = xs[t * ns + (i - nq)];
+    else if (i < nq + ns + nb) v = xsum[t * nb + (i - nq - ns)];
+    else v = w[place];
+    dst[i] = v;
+  }
+}
+
+// The receiving rank's plan, on the device, for exchanges of a fixed size: RC[s * per + e] = rows source s sent
+// for local expert e; they sit at slots s * cap + (rows of s's earlier experts) ...  Fills COUNTS / BASES of the
+// local experts (what ill_moe_mm_id reads), P2R[place] = slot of the row placed there (expert by expert, source
+// after source), R2P its inverse on the slots in use, P2R of the places past the last row = 0 (a row that exists,
+// so that element-wise steps over all CAP * WORLD places read valid memory), and TOTAL[0] = rows in all.  One CTA.
+__global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, int cap, const unsigned* __restrict__ rc,
+                                                          unsigned* __restrict__ counts, unsigned* __restrict__ bases,
+                                                          unsigned* __restrict__ p2r, unsigned* __restrict__ r2p,
+                                                          unsigned* __restrict__ total) {
+  extern __shared__ unsigned plan_s[];
+  unsigned* in_src = plan_s;                 // [world][per] rows of the source's earlier experts
+  unsigned* before = plan_s + world * per;   // [world][per] rows of the expert from earlier sources
+  unsigned* lb = before + world * per;       // [per + 1] first place of each local expert; the total
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  for (int s = tid; s < world; s += blockDim.x) {
+    unsigned a = 0;
+    for (int e = 0; e < per; ++e) { in_src[s * per + e] = a; a += rc[s * per + e]; }
+  }
+  for (int e = tid; e < per; e += blockDim.x) {
+    unsigned a = 0;
+    for (int s = 0; s < world; ++s) { before[s * per + e] = a; a += rc[s * per + e]; }
+    counts[e] = a;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    unsigned a = 0;
+    for (int e = 0; e < per; ++e) { lb[e] = a; bases[e] = a; a += counts[e]; }
+    lb[per] = a;
+    total[0] = a;
+  }
+  __syncthreads();
+  const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+  for (int seg = warp; seg < world * per; seg += nw) {
+    const int s = seg / per, e = seg - s * per;
+    const unsigned n = rc[seg], a0 = (unsigned)s * cap + in_src[seg], p0 = lb[e] + before[seg];
+    for (unsigned i = lane; i < n; i += 32) {
+      if (in_src[seg] + i < (unsigned)cap) { p2r[p0 + i] = a0 + i; r2p[a0 + i] = p0 + i; }
+      else p2r[p0 + i] = 0;  // the sender dropped it (and raised its overflow flag)
+    }
+  }
+  for (unsigned p = lb[per] + tid; p < (unsigned)(world * cap); p += blockDim.x) p2r[p] = 0;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -838,6 +920,50 @@ extern "C" int ill_ep_pack(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill
   uint32_t* pp = (uint32_t*)(uintptr_t)packed;
   void* args[] = {&cols, &rb, &qp, &sp, &bp, &wp, &mp, &pp};
   return launch_kernel((const void*)ep_pack_kernel, dim3((unsigned)rows), dim3(128), 0, args, (cudaStream_t)stream);
+}
+
+extern "C" int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr w, ill_dptr map,
+                               ill_dptr bases, int per, int world, int cap, ill_dptr packed, ill_dptr pslot, ill_dptr overflow,
+                               ill_stream stream) {
+  if (rows < 0 || cols <= 0 || cols % 256 || per < 1 || world < 1 || cap < 1 || !xq || !xs || !xsum || !w || !map || !bases ||
+      !packed || !pslot || !overflow)
+    return ILL_ERR_ARG;
+  if ((xq & 3) || (xs & 3) || (xsum & 3) || (w & 3) || (map & 3) || (bases & 3) || (packed & 15) || (pslot & 3) || (overflow & 3))
+    return ILL_ERR_ALIGN;
+  if (rows == 0) return ILL_OK;
+  long long rb = ill_ep_row_bytes(cols), nrows = rows;
+  const uint32_t* qp = (const uint32_t*)(uintptr_t)xq;
+  const uint32_t* sp = (const uint32_t*)(uintptr_t)xs;
+  const uint32_t* bp = (const uint32_t*)(uintptr_t)xsum;
+  const uint32_t* wp = (const uint32_t*)(uintptr_t)w;
+  const unsigned* mp = (const unsigned*)(uintptr_t)map;
+  const unsigned* bs = (const unsigned*)(uintptr_t)bases;
+  uint32_t* pp = (uint32_t*)(uintptr_t)packed;
+  unsigned* ps = (unsigned*)(uintptr_t)pslot;
+  unsigned* ov = (unsigned*)(uintptr_t)overflow;
+  void* args[] = {&cols, &rb, &qp, &sp, &bp, &wp, &mp, &bs, &per, &world, &cap, &nrows, &pp, &ps, &ov};
+  return launch_kernel((const void*)ep_pack_cap_kernel, dim3((unsigned)rows), dim3(128), 0, args, (cudaStream_t)stream);
+}
+
+extern "C" int ill_ep_plan_dev(int world, int per, int cap, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
+                               ill_dptr r2p, ill_dptr total, ill_stream stream) {
+  if (world < 1 || per < 1 || cap < 1 || (long long)world * per > 8192 || !rc || !counts || !bases || !p2r || !r2p || !total)
+    return ILL_ERR_ARG;
+  if ((rc & 3) || (counts & 3) || (bases & 3) || (p2r & 3) || (r2p & 3) || (total & 3)) return ILL_ERR_ALIGN;
+  const unsigned* rp = (const unsigned*)(uintptr_t)rc;
+  unsigned* cp = (unsigned*)(uintptr_t)counts;
+  unsigned* bp = (unsigned*)(uintptr_t)bases;
+  unsigned* pp = (unsigned*)(uintptr_t)p2r;
+  unsigned* ip = (unsigned*)(uintptr_t)r2p;
+  unsigned* tp = (unsigned*)(uintptr_t)total;
+  void* args[] = {&world, &per, &cap, &rp, &cp, &bp, &pp, &ip, &tp};
+  const size_t smem = ((size_t)2 * world * per + per + 1) * 4;
+  const void* k = (const void*)ep_plan_dev_kernel;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  return launch_kernel(k, dim3(1), dim3(256), smem, args, (cudaStream_t)stream);
 }
 
 extern "C" int ill_ep_unpack(int64_t rows, int cols, ill_dptr packed, ill_dptr map, ill_dptr xh, ill_dptr xe, ill_dptr xd,

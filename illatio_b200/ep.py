@@ -332,6 +332,94 @@ def chunk_fast(ex, sc, norms, logits, n_expert_total, group=None):
     return sc.moe
 
 
+class EpCapScratch:
+    """Buffers of chunk_capacity: exchanges of a fixed size, CAP rows from every rank to every rank."""
+
+    def __init__(self, pool, n, nu, n_expert_total, world, cap=None, device="cuda"):
+        from . import _lib
+        from .blocks import Q2_K
+        d, ff = pool.d, pool.ff
+        rows = n * nu
+        per = n_expert_total // world
+        if cap is None:  # half again the even share, and room for small chunks' spread
+            cap = rows if world == 1 else min(rows, (rows // world * 3 // 2 + 63) // 64 * 64 + 64)
+        tot = cap * world
+        dev = dict(device=device)
+        f32, i32, u8 = dict(dtype=torch.float32, **dev), dict(dtype=torch.int32, **dev), dict(dtype=torch.uint8, **dev)
+        self.n, self.nu, self.rows, self.cap, self.tot, self.per, self.world = n, nu, rows, cap, tot, per, world
+        self.sel, self.w = torch.empty(n, nu, **i32), torch.empty(n, nu, **f32)
+        self.counts, self.bases = torch.empty(n_expert_total, **i32), torch.empty(n_expert_total, **i32)
+        self.rmap, self.smap, self.wrow = torch.empty(rows, **i32), torch.empty(rows, **i32), torch.empty(rows, **f32)
+        self.group = torch.empty(_lib.lib().ill_moe_group_scratch_bytes(rows, n_expert_total), **u8)
+        self.rc = torch.empty(world, per, **i32)
+        self.lcounts, self.lbases, self.total = torch.empty(per, **i32), torch.empty(per, **i32), torch.zeros(1, **i32)
+        self.overflow = torch.zeros(1, **i32)
+        self.pslot, self.smap2 = torch.empty(rows, **i32), torch.empty(rows, **i32)
+        self.p2r, self.r2p = torch.zeros(tot, **i32), torch.zeros(tot, **i32)
+        self.xq = torch.empty(n * d, dtype=torch.int8, **dev)
+        self.xs, self.xsum = torch.empty(n * d // 256, **f32), torch.empty(n * d // 16, dtype=torch.int16, **dev)
+        self.row_bytes = _lib.lib().ill_ep_row_bytes(d)
+        self.s_rows = torch.zeros(tot, self.row_bytes, **u8)
+        self.r_rows = torch.zeros(tot, self.row_bytes, **u8) if world > 1 else self.s_rows
+        self.xh = torch.empty(tot, d, dtype=torch.float16, **dev)
+        self.xe = torch.empty(tot, d // 256, 64, dtype=torch.float16, **dev) if pool.gate_fmt == Q2_K else None
+        self.xd, self.wplace = torch.empty(tot, d // 256, **f32), torch.empty(tot, **f32)
+        self.g, self.u = torch.zeros(tot, ff, **f32), torch.zeros(tot, ff, **f32)
+        self.ms = torch.empty(tot * ff // 256, **f32)
+        self.mh = torch.empty(tot, ff, dtype=torch.float16, **dev)
+        self.me = torch.empty(tot, ff // 256, 64, dtype=torch.float16, **dev) if pool.down_fmt == Q2_K else None
+        self.down = torch.zeros(tot, d, **f32)
+        self.back = torch.zeros(tot, d, **f32) if world > 1 else self.down
+        self.moe = torch.empty(n, d, **f32)
+
+
+def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
+    """The chunk with exchanges of a fixed size (sc.cap rows from every rank to every
+    rank): nothing on the host depends on the routing, so the whole chunk is
+    enqueued without a synchronisation.  Returns (moe, overflow): OVERFLOW is a
+    device flag, set when some slab was too small -- the result is then void and
+    the caller repeats the chunk with chunk_fast.  Otherwise the same bits as
+    chunk_fast."""
+    from . import _lib
+    pool = ex.pool
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    n, d = norms.shape
+    ff, nu, per, cap, tot = pool.ff, ex.nu, sc.per, sc.cap, sc.tot
+    rows = n * nu
+    E = n_expert_total
+    st = torch.cuda.current_stream().cuda_stream
+    ptr = lambda t: 0 if t is None else t.data_ptr()  # noqa: E731
+    call = _lib.call
+    call("ill_moe_route", E, nu, ex.mode, float(ex.scale), n, ptr(logits), 0, ptr(sc.sel), ptr(sc.w), st)
+    call("ill_moe_group", rows, E, nu, ptr(sc.sel), ptr(sc.w), ptr(sc.group), ptr(sc.counts), ptr(sc.bases), ptr(sc.rmap),
+         ptr(sc.smap), ptr(sc.wrow), st)
+    if world > 1:  # my rows per expert, to each expert's rank: [world, per] both ways
+        dist.all_to_all_single(sc.rc.view(-1), sc.counts, group=group)
+    else:
+        sc.rc.view(-1).copy_(sc.counts)
+    call("ill_quant_q8_k", ptr(norms), ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), n * d // 256, st)
+    sc.overflow.zero_()
+    call("ill_ep_pack_cap", rows, d, ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), per, world,
+         cap, ptr(sc.s_rows), ptr(sc.pslot), ptr(sc.overflow), st)
+    if world > 1:
+        dist.all_to_all_single(sc.r_rows, sc.s_rows, group=group)
+    call("ill_ep_plan_dev", world, per, cap, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p), ptr(sc.total), st)
+    call("ill_ep_unpack", tot, d, ptr(sc.r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), st)
+    for add, y in ((0, sc.g), (pool.gate_bytes, sc.u)):
+        call("ill_moe_mm_id", pool.gate_fmt, d, ff, add, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases), pool.n_expert, tot,
+             ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, 0, ptr(y), ff, st)
+    call("ill_swiglu_q8k_f16", tot, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mh), ptr(sc.me), ptr(sc.ms),
+         st)
+    call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases),
+         pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.p2r), ptr(sc.down), d, st)
+    if world > 1:
+        dist.all_to_all_single(sc.back, sc.down, group=group)
+    # a (token, slot) row's result is at its slot of the slab it left in
+    call("ill_gather_rows", rows, 4, ptr(sc.pslot), ptr(sc.smap), ptr(sc.smap2), st)
+    call("ill_moe_sum", d, nu, n, ptr(sc.back), ptr(sc.smap2), 0, ptr(sc.moe), st)
+    return sc.moe, sc.overflow
+
+
 def head_rows(rows, world, rank):
     """[first, end) of the output head's rows on RANK: equal slices (the last takes the remainder)."""
     per = rows // world

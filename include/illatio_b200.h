@@ -298,6 +298,21 @@ ILL_API int ill_ep_pack(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dp
 ILL_API int ill_ep_unpack(int64_t rows, int cols, ill_dptr packed, ill_dptr map, ill_dptr xh, ill_dptr xe, ill_dptr xd,
                           ill_dptr w, ill_stream stream);
 
+/* The same exchange with slabs of a fixed size, so that the host never waits for
+ * counts: every rank sends every rank CAP rows' worth (ill_ep_pack_cap: rank g's
+ * rows, in place order, in slab g; PSLOT[place] = g*cap + index; *OVERFLOW is
+ * set, and the rows past CAP dropped, if a slab is too small -- the caller then
+ * repeats the chunk with exact sizes), and the per-expert counts travel as a
+ * [world, per] table.  ill_ep_plan_dev turns the received table RC[s*per + e]
+ * into the local experts' COUNTS / BASES, the two row orders (P2R over all
+ * world*cap places, those past the last row pointing at slot 0) and TOTAL[0],
+ * on the device.  No counterpart in the reference. */
+ILL_API int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr w, ill_dptr map,
+                            ill_dptr bases, int per, int world, int cap, ill_dptr packed, ill_dptr pslot, ill_dptr overflow,
+                            ill_stream stream);
+ILL_API int ill_ep_plan_dev(int world, int per, int cap, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
+                            ill_dptr r2p, ill_dptr total, ill_stream stream);
+
 /* The routed experts' product for a chunk: for each expert e < NE and each row
  * `place` in [BASES[e], BASES[e] + COUNTS[e]): Y[place*y_stride + n] = W_e[n] .
  * X[place], n < NROWS, W_e the FMT (ILL_IQ2_XXS or ILL_Q2_K) matrix at PTRS[e]

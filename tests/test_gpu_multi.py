@@ -38,6 +38,14 @@ def test_world_of_one_equals_chunk_driver(cuda_lib):
     esc = EP.EpScratch(pool, n, CFG["nu"], CFG["ne"], 1)
     for _ in range(2):
         assert torch.equal(EP.chunk_fast(ce, esc, norms, logits, CFG["ne"]), want)
+    # exchanges of a fixed size: the same bits without a host synchronisation; a slab too small raises the flag
+    csc = EP.EpCapScratch(pool, n, CFG["nu"], CFG["ne"], 1)
+    for _ in range(2):
+        moe, flag = EP.chunk_capacity(ce, csc, norms, logits, CFG["ne"])
+        assert torch.equal(moe, want) and flag.item() == 0
+    small = EP.EpCapScratch(pool, n, CFG["nu"], CFG["ne"], 1, cap=n * CFG["nu"] - 5)
+    _, flag = EP.chunk_capacity(ce, small, norms, logits, CFG["ne"])
+    assert flag.item() == 1
     assert D.device_status() == 0
 
 
@@ -92,6 +100,11 @@ ce = EP.CudaExperts(mine, cfg["nu"], 10.0)
 got = ce.chunk(norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"])
 esc = EP.EpScratch(mine, hi - lo, cfg["nu"], cfg["ne"], world)
 fast = [EP.chunk_fast(ce, esc, norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"]).clone() for _ in range(2)]
+csc = EP.EpCapScratch(mine, hi - lo, cfg["nu"], cfg["ne"], world)
+for _ in range(2):
+    moe, flag = EP.chunk_capacity(ce, csc, norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"])
+    fast.append(moe.clone())
+    assert flag.item() == 0
 ok = torch.equal(got, want[lo:hi]) and all(torch.equal(f, want[lo:hi]) for f in fast) and D.device_status() == 0
 if not ok:
     print("rank", rank, "max abs difference", (got - want[lo:hi]).abs().max().item(), file=sys.stderr)
