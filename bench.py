@@ -373,19 +373,28 @@ def main():
         norms_l, logits_l = norms_all[lo:hi].contiguous(), logits_all[lo:hi].contiguous()
         del norms_all, logits_all
         ce = EP.CudaExperts(pool, cfg["nu"], 10.0)
-        # A stream of independent chunks, alternating between two lanes (a CUDA stream and a scratch
-        # each): one chunk's exchanges and host synchronisation overlap the other's products.
-        lanes = [(torch.cuda.Stream(device=dev), EP.EpScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev))
-                 for _ in range(2)]
+        # A stream of independent chunks, alternating between lanes (a CUDA stream and a scratch each): one
+        # chunk's exchanges overlap the other's products.  The exchanges have a fixed size (half again the
+        # even share of rows from every rank to every rank), so nothing on the host waits for the routing;
+        # a slab that turned out too small would raise a flag, checked after the timed region.
+        nlanes = int(os.environ.get("ILL_EP_LANES", "2"))
+        exact = os.environ.get("ILL_EP_MODE", "capacity") == "exact"
+        mk = (lambda: EP.EpScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev)) if exact else \
+             (lambda: EP.EpCapScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev))
+        lanes = [(torch.cuda.Stream(device=dev), mk()) for _ in range(nlanes)]
+        flags = []
 
         def run_chunks(k):
             main = torch.cuda.current_stream()
             for s_, _ in lanes:
                 s_.wait_stream(main)
             for i in range(k):
-                s_, esc = lanes[i % 2]
+                s_, esc = lanes[i % nlanes]
                 with torch.cuda.stream(s_):
-                    EP.chunk_fast(ce, esc, norms_l, logits_l, cfg["ne"])
+                    if exact:
+                        EP.chunk_fast(ce, esc, norms_l, logits_l, cfg["ne"])
+                    else:
+                        flags.append(EP.chunk_capacity(ce, esc, norms_l, logits_l, cfg["ne"])[1].clone())
             for s_, _ in lanes:
                 main.wait_stream(s_)
 
@@ -403,7 +412,9 @@ def main():
         moe_ms, head_us = mt.tolist()
         flop = 2.0 * n_tok * cfg["nu"] * 3 * cfg["d"] * cfg["ff"]
         moe = {"workload": "configs[3]: hidden 4096, 256 experts of FFN 2048, top-6, IQ2_XXS gate/up, Q2_K down; one 4096-token chunk through the routed experts",
-               "n_gpus": world, "experts_per_gpu": per, "tokens": n_tok, "ms_per_chunk": moe_ms, "chunks_in_flight": 2,
+               "n_gpus": world, "experts_per_gpu": per, "tokens": n_tok, "ms_per_chunk": moe_ms, "chunks_in_flight": nlanes,
+               "exchange_sizes": "exact (one host synchronisation a chunk)" if exact else "fixed slabs, no host synchronisation",
+               "slab_overflows": int(sum(int(f.item()) for f in flags)),
                "tok_per_s": n_tok / moe_ms * 1e3, "tflops": flop / moe_ms / 1e9, "scaling": "strong",
                "exchange": "NCCL all-to-all of Q8_K rows out (1.14 B/value), fp32 rows back" if world > 1 else "none (one GPU)"}
         del pool, ce, lanes
