@@ -373,11 +373,12 @@ def main():
         norms_l, logits_l = norms_all[lo:hi].contiguous(), logits_all[lo:hi].contiguous()
         del norms_all, logits_all
         ce = EP.CudaExperts(pool, cfg["nu"], 10.0)
-        # A stream of independent chunks, alternating between lanes (a CUDA stream and a scratch each): one
-        # chunk's exchanges overlap the other's products.  The exchanges have a fixed size (half again the
-        # even share of rows from every rank to every rank), so nothing on the host waits for the routing;
-        # a slab that turned out too small would raise a flag, checked after the timed region.
-        nlanes = int(os.environ.get("ILL_EP_LANES", "2"))
+        # A stream of independent chunks.  The exchanges have a fixed size (half again the even share of rows
+        # from every rank to every rank), so nothing on the host waits for the routing; a slab that turned out
+        # too small would raise a flag, checked after the timed region.  (ILL_EP_LANES=2 alternates the chunks
+        # between two CUDA streams; measured, it gains nothing: the persistent product kernel holds every SM, so
+        # the other stream's exchange kernels do not run beside it.)
+        nlanes = int(os.environ.get("ILL_EP_LANES", "1"))
         exact = os.environ.get("ILL_EP_MODE", "capacity") == "exact"
         mk = (lambda: EP.EpScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev)) if exact else \
              (lambda: EP.EpCapScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev))
