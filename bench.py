@@ -380,8 +380,9 @@ def main():
         # the other stream's exchange kernels do not run beside it.)
         nlanes = int(os.environ.get("ILL_EP_LANES", "1"))
         exact = os.environ.get("ILL_EP_MODE", "capacity") == "exact"
+        peer_combine = world > 1 and not exact and os.environ.get("ILL_EP_COMBINE", "peer") == "peer"
         mk = (lambda: EP.EpScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev)) if exact else \
-             (lambda: EP.EpCapScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev))
+             (lambda: EP.EpCapScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev, peer=peer_combine))
         lanes = [(torch.cuda.Stream(device=dev), mk()) for _ in range(nlanes)]
         flags = []
 
@@ -416,6 +417,8 @@ def main():
                "n_gpus": world, "experts_per_gpu": per, "tokens": n_tok, "ms_per_chunk": moe_ms, "chunks_in_flight": nlanes,
                "exchange_sizes": "exact (one host synchronisation a chunk)" if exact else "fixed slabs, no host synchronisation",
                "slab_overflows": int(sum(int(f.item()) for f in flags)),
+               "combine": ("fused into the down product: stores into the owners' memory over NVLink" if peer_combine
+                           else "NCCL all-to-all of fp32 rows" if world > 1 else "none (one GPU)"),
                "tok_per_s": n_tok / moe_ms * 1e3, "tflops": flop / moe_ms / 1e9, "scaling": "strong",
                "exchange": "NCCL all-to-all of Q8_K rows out (1.14 B/value), fp32 rows back" if world > 1 else "none (one GPU)"}
         del pool, ce, lanes

@@ -59,6 +59,7 @@ struct MmParams {
   const float* xd;             // the activations' block scales, [token][K/256]
   const unsigned* map;         // token of each row of X (null: the row itself)
   const unsigned* ymap;        // row of Y each row of X is written to (null: the same row)
+  const unsigned long long* ypeers;  // with YMAP: Y of every rank (peer memory); YMAP[place] = rank << 24 | row there
   long long total_rows;
   float* y;
   long long y_stride;          // floats between rows of Y
@@ -581,10 +582,21 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
               unsigned yr[8];  // the rows first, then the stores: a load does not wait for the store before it
 #pragma unroll
               for (int i = 0; i < 8; ++i) yr[i] = i0 + i < nvalid ? __ldg(ym + i0 + i) : 0u;
+              if (p.ypeers) {
+                // the combine of an expert-parallel chunk, fused: the row goes straight into the memory of the
+                // rank that owns its token (a plain store over NVLink), tile by tile as the products finish
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                if (i0 + i < nvalid)
-                  ycol[(size_t)yr[i] * ys] = __uint_as_float((uint32_t)(out[(i0 + i) >> 1] >> (32 * (i & 1)))) * fin;
+                for (int i = 0; i < 8; ++i)
+                  if (i0 + i < nvalid) {
+                    float* dst = (float*)(uintptr_t)__ldg(p.ypeers + (yr[i] >> 24)) + (size_t)(yr[i] & 0xffffffu) * ys + n;
+                    *dst = __uint_as_float((uint32_t)(out[(i0 + i) >> 1] >> (32 * (i & 1)))) * fin;
+                  }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  if (i0 + i < nvalid)
+                    ycol[(size_t)yr[i] * ys] = __uint_as_float((uint32_t)(out[(i0 + i) >> 1] >> (32 * (i & 1)))) * fin;
+              }
             }
           }
         } else {
@@ -817,10 +829,10 @@ __global__ void __launch_bounds__(128) ep_pack_cap_kernel(int cols, long long ro
 // local experts (what ill_moe_mm_id reads), P2R[place] = slot of the row placed there (expert by expert, source
 // after source), R2P its inverse on the slots in use, P2R of the places past the last row = 0 (a row that exists,
 // so that element-wise steps over all CAP * WORLD places read valid memory), and TOTAL[0] = rows in all.  One CTA.
-__global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, int cap, const unsigned* __restrict__ rc,
+__global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, int cap, int rank, const unsigned* __restrict__ rc,
                                                           unsigned* __restrict__ counts, unsigned* __restrict__ bases,
                                                           unsigned* __restrict__ p2r, unsigned* __restrict__ r2p,
-                                                          unsigned* __restrict__ total) {
+                                                          unsigned* __restrict__ pdst, unsigned* __restrict__ total) {
   extern __shared__ unsigned plan_s[];
   unsigned* in_src = plan_s;                 // [world][per] rows of the source's earlier experts
   unsigned* before = plan_s + world * per;   // [world][per] rows of the expert from earlier sources
@@ -850,11 +862,21 @@ __global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, in
     const int s = seg / per, e = seg - s * per;
     const unsigned n = rc[seg], a0 = (unsigned)s * cap + in_src[seg], p0 = lb[e] + before[seg];
     for (unsigned i = lane; i < n; i += 32) {
-      if (in_src[seg] + i < (unsigned)cap) { p2r[p0 + i] = a0 + i; r2p[a0 + i] = p0 + i; }
-      else p2r[p0 + i] = 0;  // the sender dropped it (and raised its overflow flag)
+      if (in_src[seg] + i < (unsigned)cap) {
+        p2r[p0 + i] = a0 + i;
+        r2p[a0 + i] = p0 + i;
+        // where the row's result goes: rank s, row (this rank's slab there) * cap + its index in the slab
+        if (pdst) pdst[p0 + i] = ((unsigned)s << 24) | ((unsigned)rank * cap + in_src[seg] + i);
+      } else {
+        p2r[p0 + i] = 0;  // the sender dropped it (and raised its overflow flag)
+        if (pdst) pdst[p0 + i] = ((unsigned)s << 24) | ((unsigned)rank * cap);
+      }
     }
   }
-  for (unsigned p = lb[per] + tid; p < (unsigned)(world * cap); p += blockDim.x) p2r[p] = 0;
+  for (unsigned p = lb[per] + tid; p < (unsigned)(world * cap); p += blockDim.x) {
+    p2r[p] = 0;
+    if (pdst) pdst[p] = (unsigned)rank << 24 | ((unsigned)rank * cap);
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -945,18 +967,20 @@ extern "C" int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs,
   return launch_kernel((const void*)ep_pack_cap_kernel, dim3((unsigned)rows), dim3(128), 0, args, (cudaStream_t)stream);
 }
 
-extern "C" int ill_ep_plan_dev(int world, int per, int cap, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
-                               ill_dptr r2p, ill_dptr total, ill_stream stream) {
-  if (world < 1 || per < 1 || cap < 1 || (long long)world * per > 8192 || !rc || !counts || !bases || !p2r || !r2p || !total)
+extern "C" int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
+                               ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_stream stream) {
+  if (world < 1 || world > 255 || per < 1 || cap < 1 || (long long)world * cap > 0xffffff || rank < 0 || rank >= world ||
+      (long long)world * per > 8192 || !rc || !counts || !bases || !p2r || !r2p || !total)
     return ILL_ERR_ARG;
-  if ((rc & 3) || (counts & 3) || (bases & 3) || (p2r & 3) || (r2p & 3) || (total & 3)) return ILL_ERR_ALIGN;
+  if ((rc & 3) || (counts & 3) || (bases & 3) || (p2r & 3) || (r2p & 3) || (pdst & 3) || (total & 3)) return ILL_ERR_ALIGN;
   const unsigned* rp = (const unsigned*)(uintptr_t)rc;
   unsigned* cp = (unsigned*)(uintptr_t)counts;
   unsigned* bp = (unsigned*)(uintptr_t)bases;
   unsigned* pp = (unsigned*)(uintptr_t)p2r;
   unsigned* ip = (unsigned*)(uintptr_t)r2p;
   unsigned* tp = (unsigned*)(uintptr_t)total;
-  void* args[] = {&world, &per, &cap, &rp, &cp, &bp, &pp, &ip, &tp};
+  unsigned* dp = (unsigned*)(uintptr_t)pdst;
+  void* args[] = {&world, &per, &cap, &rank, &rp, &cp, &bp, &pp, &ip, &dp, &tp};
   const size_t smem = ((size_t)2 * world * per + per + 1) * 4;
   const void* k = (const void*)ep_plan_dev_kernel;
   if (smem > 48 * 1024) {
@@ -990,9 +1014,29 @@ static int encode_map(CUtensorMap* map, ill_dptr base, int64_t inner, int64_t ro
   return r == CUDA_SUCCESS ? ILL_OK : cuda_fail(cudaErrorInvalidValue);
 }
 
+static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int ne,
+                        int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap, ill_dptr ypeers,
+                        ill_dptr y, int64_t y_stride, ill_stream stream);
+
 extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases,
                              int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap,
                              ill_dptr y, int64_t y_stride, ill_stream stream) {
+  if (!y) return ILL_ERR_ARG;
+  return mm_id_launch(fmt, ncols, nrows, add, ptrs, counts, bases, ne, total_rows, xh, xe, xd, map, ymap, 0, y, y_stride, stream);
+}
+
+extern "C" int ill_moe_mm_id_peers(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases,
+                                   int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ydst,
+                                   ill_dptr ypeers, int64_t y_stride, ill_stream stream) {
+  if (!ydst || !ypeers || (ypeers & 7)) return ILL_ERR_ARG;
+  // Y is only named through YPEERS; any aligned non-null value keeps the common checks happy
+  return mm_id_launch(fmt, ncols, nrows, add, ptrs, counts, bases, ne, total_rows, xh, xe, xd, map, ydst, ypeers, 16, y_stride,
+                      stream);
+}
+
+static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int ne,
+                        int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap, ill_dptr ypeers,
+                        ill_dptr y, int64_t y_stride, ill_stream stream) {
   if (fmt != ILL_IQ2_XXS && fmt != ILL_Q2_K) return ILL_ERR_UNSUPPORTED;
   if (ncols <= 0 || ncols % 256 || nrows <= 0 || ne <= 0 || ne > 65535 || total_rows < 0 || y_stride < nrows ||
       y_stride > 0xffffffffll)
@@ -1018,6 +1062,7 @@ extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dpt
   p.xd = (const float*)(uintptr_t)xd;
   p.map = (const unsigned*)(uintptr_t)map;
   p.ymap = (const unsigned*)(uintptr_t)ymap;
+  p.ypeers = (const unsigned long long*)(uintptr_t)ypeers;
   p.total_rows = total_rows;
   p.y = (float*)(uintptr_t)y;
   p.y_stride = y_stride;

@@ -335,7 +335,10 @@ def chunk_fast(ex, sc, norms, logits, n_expert_total, group=None):
 class EpCapScratch:
     """Buffers of chunk_capacity: exchanges of a fixed size, CAP rows from every rank to every rank."""
 
-    def __init__(self, pool, n, nu, n_expert_total, world, cap=None, device="cuda"):
+    def __init__(self, pool, n, nu, n_expert_total, world, cap=None, device="cuda", peer=False, group=None):
+        """PEER (several ranks only; every rank must construct it at the same point): the buffer the down rows
+        come back in is a symmetric allocation that every rank maps, so that the down product stores each row
+        straight into its owner's memory instead of an all-to-all after it."""
         from . import _lib
         from .blocks import Q2_K
         d, ff = pool.d, pool.ff
@@ -369,7 +372,16 @@ class EpCapScratch:
         self.mh = torch.empty(tot, ff, dtype=torch.float16, **dev)
         self.me = torch.empty(tot, ff // 256, 64, dtype=torch.float16, **dev) if pool.down_fmt == Q2_K else None
         self.down = torch.zeros(tot, d, **f32)
-        self.back = torch.zeros(tot, d, **f32) if world > 1 else self.down
+        self.pdst = torch.zeros(tot, **i32)
+        self.hdl, self.peers = None, None
+        if world > 1 and peer:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.back = symm_mem.empty((tot, d), dtype=torch.float32, device=device)
+            self.back.zero_()
+            self.hdl = symm_mem.rendezvous(self.back, group if group is not None else dist.group.WORLD)
+            self.peers = torch.tensor(list(self.hdl.buffer_ptrs), dtype=torch.int64, device=device)
+        else:
+            self.back = torch.zeros(tot, d, **f32) if world > 1 else self.down
         self.moe = torch.empty(n, d, **f32)
 
 
@@ -403,17 +415,26 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
          cap, ptr(sc.s_rows), ptr(sc.pslot), ptr(sc.overflow), st)
     if world > 1:
         dist.all_to_all_single(sc.r_rows, sc.s_rows, group=group)
-    call("ill_ep_plan_dev", world, per, cap, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p), ptr(sc.total), st)
+    me = dist.get_rank(group) if dist.is_initialized() else 0
+    call("ill_ep_plan_dev", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
+         ptr(sc.pdst), ptr(sc.total), st)
     call("ill_ep_unpack", tot, d, ptr(sc.r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), st)
     for add, y in ((0, sc.g), (pool.gate_bytes, sc.u)):
         call("ill_moe_mm_id", pool.gate_fmt, d, ff, add, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases), pool.n_expert, tot,
              ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, 0, ptr(y), ff, st)
     call("ill_swiglu_q8k_f16", tot, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mh), ptr(sc.me), ptr(sc.ms),
          st)
-    call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases),
-         pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.p2r), ptr(sc.down), d, st)
-    if world > 1:
-        dist.all_to_all_single(sc.back, sc.down, group=group)
+    if sc.peers is not None:
+        # the combine fused into the down product: rows go straight to their owners over NVLink; then the ranks
+        # meet, so that every owner's rows are in before it sums them
+        call("ill_moe_mm_id_peers", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts),
+             ptr(sc.lbases), pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.pdst), ptr(sc.peers), d, st)
+        sc.hdl.barrier()
+    else:
+        call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases),
+             pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.p2r), ptr(sc.down), d, st)
+        if world > 1:
+            dist.all_to_all_single(sc.back, sc.down, group=group)
     # a (token, slot) row's result is at its slot of the slab it left in
     call("ill_gather_rows", rows, 4, ptr(sc.pslot), ptr(sc.smap), ptr(sc.smap2), st)
     call("ill_moe_sum", d, nu, n, ptr(sc.back), ptr(sc.smap2), 0, ptr(sc.moe), st)

@@ -305,13 +305,27 @@ ILL_API int ill_ep_unpack(int64_t rows, int cols, ill_dptr packed, ill_dptr map,
  * repeats the chunk with exact sizes), and the per-expert counts travel as a
  * [world, per] table.  ill_ep_plan_dev turns the received table RC[s*per + e]
  * into the local experts' COUNTS / BASES, the two row orders (P2R over all
- * world*cap places, those past the last row pointing at slot 0) and TOTAL[0],
- * on the device.  No counterpart in the reference. */
+ * world*cap places, those past the last row pointing at slot 0), TOTAL[0], and
+ * with PDST given where each place's result goes (for ill_moe_mm_id_peers), on
+ * the device.  No counterpart in the reference. */
 ILL_API int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr w, ill_dptr map,
                             ill_dptr bases, int per, int world, int cap, ill_dptr packed, ill_dptr pslot, ill_dptr overflow,
                             ill_stream stream);
-ILL_API int ill_ep_plan_dev(int world, int per, int cap, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
-                            ill_dptr r2p, ill_dptr total, ill_stream stream);
+ILL_API int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
+                            ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_stream stream);
+
+/* ill_moe_mm_id with the combine of an expert-parallel chunk fused into it: the
+ * row computed for `place` is stored straight into the memory of the rank that
+ * owns its token, YPEERS[r] being the address of rank r's Y (peer memory: a
+ * symmetric allocation, every rank's the same shape) and YDST[place] = r << 24 |
+ * row of that Y (the PDST of ill_ep_plan_dev, RANK the caller's).  Plain stores
+ * over NVLink, tile by tile as the products finish, instead of an all-to-all
+ * after them; the owner may read its Y once every rank's call has completed (a
+ * barrier between the ranks' streams).  No TMA and no multicast touch peer
+ * memory.  No counterpart in the reference. */
+ILL_API int ill_moe_mm_id_peers(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases,
+                                int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ydst,
+                                ill_dptr ypeers, int64_t y_stride, ill_stream stream);
 
 /* The routed experts' product for a chunk: for each expert e < NE and each row
  * `place` in [BASES[e], BASES[e] + COUNTS[e]): Y[place*y_stride + n] = W_e[n] .

@@ -100,11 +100,12 @@ ce = EP.CudaExperts(mine, cfg["nu"], 10.0)
 got = ce.chunk(norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"])
 esc = EP.EpScratch(mine, hi - lo, cfg["nu"], cfg["ne"], world)
 fast = [EP.chunk_fast(ce, esc, norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"]).clone() for _ in range(2)]
-csc = EP.EpCapScratch(mine, hi - lo, cfg["nu"], cfg["ne"], world)
-for _ in range(2):
-    moe, flag = EP.chunk_capacity(ce, csc, norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"])
-    fast.append(moe.clone())
-    assert flag.item() == 0
+for peer in (False, True):  # the combine as an all-to-all, and fused into the down product over peer memory
+    csc = EP.EpCapScratch(mine, hi - lo, cfg["nu"], cfg["ne"], world, peer=peer)
+    for _ in range(3):
+        moe, flag = EP.chunk_capacity(ce, csc, norms[lo:hi].contiguous(), logits[lo:hi].contiguous(), cfg["ne"])
+        fast.append(moe.clone())
+        assert flag.item() == 0
 ok = torch.equal(got, want[lo:hi]) and all(torch.equal(f, want[lo:hi]) for f in fast) and D.device_status() == 0
 if not ok:
     print("rank", rank, "max abs difference", (got - want[lo:hi]).abs().max().item(), file=sys.stderr)
