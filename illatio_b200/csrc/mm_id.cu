@@ -796,21 +796,29 @@ __global__ void __launch_bounds__(128) ep_pack_cap_kernel(int cols, long long ro
                                                           const uint32_t* __restrict__ w, const unsigned* __restrict__ map,
                                                           const unsigned* __restrict__ bases, int per, int world, int cap,
                                                           long long rows, uint32_t* __restrict__ packed,
-                                                          unsigned* __restrict__ pslot, unsigned* __restrict__ overflow) {
+                                                          unsigned* __restrict__ pslot, unsigned* __restrict__ overflow,
+                                                          const unsigned long long* __restrict__ peers, int rank) {
   pdl_launch_dependents();
   pdl_wait();
   const long long place = blockIdx.x;
   __shared__ long long slot_s;
+  __shared__ int dest_s;
   if (threadIdx.x == 0) {
     int g = 0;
     while (g + 1 < world && (long long)bases[(g + 1) * per] <= place) ++g;
     const long long idx = place - (long long)bases[g * per];
+    dest_s = g;
     if (idx >= cap) { atomicOr(overflow, 1u); slot_s = -1; pslot[place] = 0; }
     else { slot_s = (long long)g * cap + idx; pslot[place] = (unsigned)slot_s; }
   }
   __syncthreads();
-  const long long slot = slot_s;
+  long long slot = slot_s;
   if (slot < 0) return;
+  if (peers) {
+    // the dispatch without a collective: the row is stored into slab RANK of the receiving rank's buffer
+    packed = (uint32_t*)(uintptr_t)peers[dest_s];
+    slot = (long long)rank * cap + (slot - (long long)dest_s * cap);
+  }
   const long long t = map[place];
   const int nq = cols / 4, ns = cols / 256, nb = cols / 32;  // words of quants, scales, sums
   uint32_t* dst = packed + slot * (row_bytes / 4);
@@ -876,6 +884,18 @@ __global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, in
   for (unsigned p = lb[per] + tid; p < (unsigned)(world * cap); p += blockDim.x) {
     p2r[p] = 0;
     if (pdst) pdst[p] = (unsigned)rank << 24 | ((unsigned)rank * cap);
+  }
+}
+
+// This rank's rows per expert to the experts' ranks, without a collective: COUNTS[g * per + e] into row RANK of
+// rank g's [world, per] table (peer memory).
+__global__ void __launch_bounds__(256) ep_put_counts_kernel(int world, int per, int rank, const unsigned* __restrict__ counts,
+                                                            const unsigned long long* __restrict__ peers) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < world * per; i += gridDim.x * blockDim.x) {
+    const int g = i / per, e = i - g * per;
+    ((unsigned*)(uintptr_t)peers[g])[rank * per + e] = counts[i];
   }
 }
 
@@ -946,11 +966,12 @@ extern "C" int ill_ep_pack(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill
 
 extern "C" int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr w, ill_dptr map,
                                ill_dptr bases, int per, int world, int cap, ill_dptr packed, ill_dptr pslot, ill_dptr overflow,
-                               ill_stream stream) {
+                               ill_dptr peers, int rank, ill_stream stream) {
   if (rows < 0 || cols <= 0 || cols % 256 || per < 1 || world < 1 || cap < 1 || !xq || !xs || !xsum || !w || !map || !bases ||
-      !packed || !pslot || !overflow)
+      (!packed && !peers) || !pslot || !overflow || rank < 0 || rank >= world)
     return ILL_ERR_ARG;
-  if ((xq & 3) || (xs & 3) || (xsum & 3) || (w & 3) || (map & 3) || (bases & 3) || (packed & 15) || (pslot & 3) || (overflow & 3))
+  if ((xq & 3) || (xs & 3) || (xsum & 3) || (w & 3) || (map & 3) || (bases & 3) || (packed & 15) || (pslot & 3) || (overflow & 3) ||
+      (peers & 7))
     return ILL_ERR_ALIGN;
   if (rows == 0) return ILL_OK;
   long long rb = ill_ep_row_bytes(cols), nrows = rows;
@@ -963,8 +984,19 @@ extern "C" int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs,
   uint32_t* pp = (uint32_t*)(uintptr_t)packed;
   unsigned* ps = (unsigned*)(uintptr_t)pslot;
   unsigned* ov = (unsigned*)(uintptr_t)overflow;
-  void* args[] = {&cols, &rb, &qp, &sp, &bp, &wp, &mp, &bs, &per, &world, &cap, &nrows, &pp, &ps, &ov};
+  const unsigned long long* pr = (const unsigned long long*)(uintptr_t)peers;
+  void* args[] = {&cols, &rb, &qp, &sp, &bp, &wp, &mp, &bs, &per, &world, &cap, &nrows, &pp, &ps, &ov, &pr, &rank};
   return launch_kernel((const void*)ep_pack_cap_kernel, dim3((unsigned)rows), dim3(128), 0, args, (cudaStream_t)stream);
+}
+
+extern "C" int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill_dptr peers, ill_stream stream) {
+  if (world < 1 || per < 1 || rank < 0 || rank >= world || !counts || !peers) return ILL_ERR_ARG;
+  if ((counts & 3) || (peers & 7)) return ILL_ERR_ALIGN;
+  const unsigned* cp = (const unsigned*)(uintptr_t)counts;
+  const unsigned long long* pr = (const unsigned long long*)(uintptr_t)peers;
+  void* args[] = {&world, &per, &rank, &cp, &pr};
+  return launch_kernel((const void*)ep_put_counts_kernel, dim3((unsigned)((world * per + 255) / 256)), dim3(256), 0, args,
+                       (cudaStream_t)stream);
 }
 
 extern "C" int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,

@@ -373,13 +373,20 @@ class EpCapScratch:
         self.me = torch.empty(tot, ff // 256, 64, dtype=torch.float16, **dev) if pool.down_fmt == Q2_K else None
         self.down = torch.zeros(tot, d, **f32)
         self.pdst = torch.zeros(tot, **i32)
-        self.hdl, self.peers = None, None
+        self.hdl, self.peers, self.peers_rows, self.peers_rc = None, None, None, None
         if world > 1 and peer:
             import torch.distributed._symmetric_memory as symm_mem
-            self.back = symm_mem.empty((tot, d), dtype=torch.float32, device=device)
-            self.back.zero_()
-            self.hdl = symm_mem.rendezvous(self.back, group if group is not None else dist.group.WORLD)
-            self.peers = torch.tensor(list(self.hdl.buffer_ptrs), dtype=torch.int64, device=device)
+            grp = group if group is not None else dist.group.WORLD
+
+            def shared(shape, dtype):
+                t = symm_mem.empty(shape, dtype=dtype, device=device)
+                t.zero_()
+                h = symm_mem.rendezvous(t, grp)
+                return t, h, torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device)
+
+            self.back, self.hdl, self.peers = shared((tot, d), torch.float32)
+            self.r_rows, _, self.peers_rows = shared((tot, self.row_bytes), torch.uint8)
+            self.rc, _, self.peers_rc = shared((world, per), torch.int32)
         else:
             self.back = torch.zeros(tot, d, **f32) if world > 1 else self.down
         self.moe = torch.empty(n, d, **f32)
@@ -405,17 +412,25 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
     call("ill_moe_route", E, nu, ex.mode, float(ex.scale), n, ptr(logits), 0, ptr(sc.sel), ptr(sc.w), st)
     call("ill_moe_group", rows, E, nu, ptr(sc.sel), ptr(sc.w), ptr(sc.group), ptr(sc.counts), ptr(sc.bases), ptr(sc.rmap),
          ptr(sc.smap), ptr(sc.wrow), st)
-    if world > 1:  # my rows per expert, to each expert's rank: [world, per] both ways
-        dist.all_to_all_single(sc.rc.view(-1), sc.counts, group=group)
-    else:
-        sc.rc.view(-1).copy_(sc.counts)
+    me = dist.get_rank(group) if dist.is_initialized() else 0
     call("ill_quant_q8_k", ptr(norms), ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), n * d // 256, st)
     sc.overflow.zero_()
-    call("ill_ep_pack_cap", rows, d, ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), per, world,
-         cap, ptr(sc.s_rows), ptr(sc.pslot), ptr(sc.overflow), st)
-    if world > 1:
-        dist.all_to_all_single(sc.r_rows, sc.s_rows, group=group)
-    me = dist.get_rank(group) if dist.is_initialized() else 0
+    if sc.peers is not None:
+        # the dispatch without a collective: counts and rows are stored straight into the receivers' buffers
+        # over NVLink, then the ranks meet
+        call("ill_ep_put_counts", world, per, me, ptr(sc.counts), ptr(sc.peers_rc), st)
+        call("ill_ep_pack_cap", rows, d, ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), per,
+             world, cap, 0, ptr(sc.pslot), ptr(sc.overflow), ptr(sc.peers_rows), me, st)
+        sc.hdl.barrier()
+    else:
+        if world > 1:  # my rows per expert, to each expert's rank: [world, per] both ways
+            dist.all_to_all_single(sc.rc.view(-1), sc.counts, group=group)
+        else:
+            sc.rc.view(-1).copy_(sc.counts)
+        call("ill_ep_pack_cap", rows, d, ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), per,
+             world, cap, ptr(sc.s_rows), ptr(sc.pslot), ptr(sc.overflow), 0, me, st)
+        if world > 1:
+            dist.all_to_all_single(sc.r_rows, sc.s_rows, group=group)
     call("ill_ep_plan_dev", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
          ptr(sc.pdst), ptr(sc.total), st)
     call("ill_ep_unpack", tot, d, ptr(sc.r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), st)

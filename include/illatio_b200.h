@@ -310,7 +310,14 @@ ILL_API int ill_ep_unpack(int64_t rows, int cols, ill_dptr packed, ill_dptr map,
  * the device.  No counterpart in the reference. */
 ILL_API int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr w, ill_dptr map,
                             ill_dptr bases, int per, int world, int cap, ill_dptr packed, ill_dptr pslot, ill_dptr overflow,
-                            ill_stream stream);
+                            ill_dptr peers, int rank, ill_stream stream);
+/* With PEERS given (the address of every rank's receive buffer: peer memory)
+ * ill_ep_pack_cap stores each row straight into slab RANK of its destination's
+ * buffer and PACKED is not used; ill_ep_put_counts does the same for the table
+ * of counts (row RANK of every rank's [world, per] table).  The dispatch then
+ * needs no collective, only a barrier between the ranks' streams before the
+ * receivers read. */
+ILL_API int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill_dptr peers, ill_stream stream);
 ILL_API int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
                             ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_stream stream);
 
