@@ -51,6 +51,7 @@ SIGNATURES = {
     "ill_ep_pack_cap": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _S]),
     "ill_ep_put_counts": (_I, [_I, _I, _I, _P, _P, _S]),
     "ill_ep_plan_dev": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _S]),
+    "ill_moe_mm_id2": (_I, [_I, _I, _I, _L, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),
     "ill_moe_mm_id_peers": (_I, [_I, _I, _I, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),
     "ill_ep_unpack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _S]),
 }

@@ -52,7 +52,7 @@ constexpr uint32_t MM_TILE_BYTES = MM_BM * MM_BK * 2;  // 16 KB
 struct MmParams {
   int ncols, nrows;            // K and N of every expert matrix
   int row_bytes;
-  long long add;
+  long long add, add2;         // a second matrix of every expert (gate and up in one launch) when Y2 is given
   const unsigned long long* ptrs;
   const unsigned* counts;
   const unsigned* bases;
@@ -62,6 +62,7 @@ struct MmParams {
   const unsigned long long* ypeers;  // with YMAP: Y of every rank (peer memory); YMAP[place] = rank << 24 | row there
   long long total_rows;
   float* y;
+  float* y2;
   long long y_stride;          // floats between rows of Y
   int ne;
   unsigned int* status;
@@ -367,11 +368,13 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
   const int nkb = p.ncols / 256;
-  const int ntn = (p.nrows + MM_BN - 1) / MM_BN;
+  const int ntn1 = (p.nrows + MM_BN - 1) / MM_BN;
+  const int ntn = p.y2 ? 2 * ntn1 : ntn1;     // the second matrix's weight-row tiles follow the first's
   const int ntiles = tile_first[p.ne] * ntn;  // weight-row tiles vary fastest: CTAs running together share X
   bool ok = true;
 
   // tile index -> expert, first row of X, valid rows, weight-row tile
+  // (NT >= ntn1: tile NT - ntn1 of the second matrix)
   auto locate = [&](int tile, int& expert, int& row0, int& nvalid, int& nt) {
     const int mt = tile / ntn;
     nt = tile - mt * ntn;
@@ -471,7 +474,9 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int expert, row0, nvalid, nt;
       locate(tile, expert, row0, nvalid, nt);
-      const u8* wbase = (const u8*)(uintptr_t)p.ptrs[expert] + p.add + (long long)nt * MM_BN * p.row_bytes;
+      const bool second = nt >= ntn1;
+      if (second) nt -= ntn1;
+      const u8* wbase = (const u8*)(uintptr_t)p.ptrs[expert] + (second ? p.add2 : p.add) + (long long)nt * MM_BN * p.row_bytes;
       const int rows_here = min(MM_BN, p.nrows - nt * MM_BN);
       // the tokens of the tile's rows L, L + NL of X (a row past the tile's last takes the first row's)
       const float* xdp[128 / NL];
@@ -569,10 +574,12 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_free[b]);
       }
+      const bool second = nt >= ntn1;
+      if (second) nt -= ntn1;
       const int n = nt * MM_BN + m;
       if (ok && n < p.nrows) {
         const float fin = FMT == ILL_IQ2_XXS ? 0.125f : 1.0f;
-        float* ycol = p.y + n;
+        float* ycol = (second ? p.y2 : p.y) + n;
         const unsigned ys = (unsigned)p.y_stride;
         if (p.ymap) {
           const unsigned* ym = p.ymap + row0;
@@ -624,10 +631,12 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int expert, row0, nvalid, nt;
       locate(tile, expert, row0, nvalid, nt);
+      const bool second = nt >= ntn1;
+      if (second) nt -= ntn1;
       const int n = nt * MM_BN + row;
       const bool has_row = n < p.nrows;
       // the low bits of the row's address: where its blocks start inside their first word
-      const uint32_t rowlow = (uint32_t)(p.ptrs[expert] + (unsigned long long)p.add + (unsigned long long)n * p.row_bytes);
+      const uint32_t rowlow = (uint32_t)(p.ptrs[expert] + (unsigned long long)(second ? p.add2 : p.add) + (unsigned long long)n * p.row_bytes);
       for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
         const int rs = g_kb % MM_RS;
         const bool r_ok = mbar_wait(&raw_full[rs], (uint32_t)(g_kb / MM_RS) & 1u, p.status, ST_MM_WAIT_FULL + 2, 50);
@@ -1048,7 +1057,15 @@ static int encode_map(CUtensorMap* map, ill_dptr base, int64_t inner, int64_t ro
 
 static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int ne,
                         int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap, ill_dptr ypeers,
-                        ill_dptr y, int64_t y_stride, ill_stream stream);
+                        ill_dptr y, int64_t y_stride, ill_stream stream, int64_t add2 = 0, ill_dptr y2 = 0);
+
+extern "C" int ill_moe_mm_id2(int fmt, int ncols, int nrows, int64_t add, int64_t add2, ill_dptr ptrs, ill_dptr counts,
+                              ill_dptr bases, int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map,
+                              ill_dptr y, ill_dptr y2, int64_t y_stride, ill_stream stream) {
+  if (!y || !y2 || (y2 & 15) || (add2 & 3)) return ILL_ERR_ARG;
+  return mm_id_launch(fmt, ncols, nrows, add, ptrs, counts, bases, ne, total_rows, xh, xe, xd, map, 0, 0, y, y_stride, stream, add2,
+                      y2);
+}
 
 extern "C" int ill_moe_mm_id(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases,
                              int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap,
@@ -1068,7 +1085,7 @@ extern "C" int ill_moe_mm_id_peers(int fmt, int ncols, int nrows, int64_t add, i
 
 static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int ne,
                         int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap, ill_dptr ypeers,
-                        ill_dptr y, int64_t y_stride, ill_stream stream) {
+                        ill_dptr y, int64_t y_stride, ill_stream stream, int64_t add2, ill_dptr y2) {
   if (fmt != ILL_IQ2_XXS && fmt != ILL_Q2_K) return ILL_ERR_UNSUPPORTED;
   if (ncols <= 0 || ncols % 256 || nrows <= 0 || ne <= 0 || ne > 65535 || total_rows < 0 || y_stride < nrows ||
       y_stride > 0xffffffffll)
@@ -1088,6 +1105,7 @@ static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptr
   p.nrows = nrows;
   p.row_bytes = ncols / 256 * fmt_block_bytes(fmt);
   p.add = add;
+  p.add2 = add2;
   p.ptrs = (const unsigned long long*)(uintptr_t)ptrs;
   p.counts = (const unsigned*)(uintptr_t)counts;
   p.bases = (const unsigned*)(uintptr_t)bases;
@@ -1097,10 +1115,11 @@ static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptr
   p.ypeers = (const unsigned long long*)(uintptr_t)ypeers;
   p.total_rows = total_rows;
   p.y = (float*)(uintptr_t)y;
+  p.y2 = (float*)(uintptr_t)y2;
   p.y_stride = y_stride;
   p.ne = ne;
   p.status = device_status_word();
-  const long long max_tiles = ((total_rows + MM_BM - 1) / MM_BM + ne) * ((nrows + MM_BN - 1) / MM_BN);  // an upper bound
+  const long long max_tiles = ((total_rows + MM_BM - 1) / MM_BM + ne) * ((nrows + MM_BN - 1) / MM_BN) * (y2 ? 2 : 1);  // an upper bound
   const size_t smem = fmt == ILL_IQ2_XXS ? MmGeom<ILL_IQ2_XXS>::SMEM : MmGeom<ILL_Q2_K>::SMEM;
   if (ne > 512) return ILL_ERR_TOO_LARGE;
   int dev = 0, sms = 148;

@@ -90,8 +90,12 @@ def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, s
               _ptr(sc.bases), _ptr(sc.rmap), _ptr(sc.smap), _ptr(sc.wrow), st)
     D.quant_q8(norms, sc.xq)                                       # each token's Q8_K, once
     act_f16(sc.xq, d, sc.rows, sc.rmap, sc.xh, sc.xe)
-    mm_id(pool, pool.gate_fmt, d, ff, 0, sc, sc.xh, sc.xe, sc.xq.xs, sc.rmap, sc.g)
-    mm_id(pool, pool.gate_fmt, d, ff, pool.gate_bytes, sc, sc.xh, sc.xe, sc.xq.xs, sc.rmap, sc.u)
+    if fused:  # gate and up in one launch
+        _lib.call("ill_moe_mm_id2", pool.gate_fmt, d, ff, 0, pool.gate_bytes, _ptr(pool.ptrs_all), _ptr(sc.counts), _ptr(sc.bases),
+                  pool.n_expert, sc.rows, _ptr(sc.xh), _ptr(sc.xe), _ptr(sc.xq.xs), _ptr(sc.rmap), _ptr(sc.g), _ptr(sc.u), ff, st)
+    else:
+        mm_id(pool, pool.gate_fmt, d, ff, 0, sc, sc.xh, sc.xe, sc.xq.xs, sc.rmap, sc.g)
+        mm_id(pool, pool.gate_fmt, d, ff, pool.gate_bytes, sc, sc.xh, sc.xe, sc.xq.xs, sc.rmap, sc.u)
     if fused:  # the three steps below in one pass (same results bit for bit; sc.mid and sc.midq.xq stay unwritten)
         _lib.call("ill_swiglu_q8k_f16", sc.rows, ff, float(clamp), _ptr(sc.g), _ptr(sc.u), _ptr(sc.wrow), _ptr(sc.mh),
                   _ptr(sc.me), _ptr(sc.midq.xs), st)

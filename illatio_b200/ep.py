@@ -315,9 +315,8 @@ def chunk_fast(ex, sc, norms, logits, n_expert_total, group=None):
     if total:
         # the arrived rows as the products want them, expert by expert
         call("ill_ep_unpack", total, d, ptr(r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), st)
-        for add, y in ((0, sc.g), (pool.gate_bytes, sc.u)):
-            call("ill_moe_mm_id", pool.gate_fmt, d, ff, add, ptr(pool.ptrs_all), ptr(lcounts), ptr(lbases), pool.n_expert, total,
-                 ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, 0, ptr(y), ff, st)
+        call("ill_moe_mm_id2", pool.gate_fmt, d, ff, 0, pool.gate_bytes, ptr(pool.ptrs_all), ptr(lcounts), ptr(lbases),
+             pool.n_expert, total, ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, ptr(sc.g), ptr(sc.u), ff, st)
         call("ill_swiglu_q8k_f16", total, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mh), ptr(sc.me),
              ptr(sc.ms), st)
         # the down rows leave in the order their inputs arrived
@@ -434,9 +433,8 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
     call("ill_ep_plan_dev", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
          ptr(sc.pdst), ptr(sc.total), st)
     call("ill_ep_unpack", tot, d, ptr(sc.r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), st)
-    for add, y in ((0, sc.g), (pool.gate_bytes, sc.u)):
-        call("ill_moe_mm_id", pool.gate_fmt, d, ff, add, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases), pool.n_expert, tot,
-             ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, 0, ptr(y), ff, st)
+    call("ill_moe_mm_id2", pool.gate_fmt, d, ff, 0, pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases),
+         pool.n_expert, tot, ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, ptr(sc.g), ptr(sc.u), ff, st)  # gate and up in one launch
     call("ill_swiglu_q8k_f16", tot, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mh), ptr(sc.me), ptr(sc.ms),
          st)
     if sc.peers is not None:

@@ -321,6 +321,14 @@ ILL_API int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill
 ILL_API int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
                             ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_stream stream);
 
+/* Two matrices of every expert against the same rows in one launch (gate and up:
+ * W_e at PTRS[e] + ADD into Y, at PTRS[e] + ADD2 into Y2; no YMAP).  The same
+ * results as two calls of ill_moe_mm_id; one launch fills the SMs better when a
+ * rank holds few experts. */
+ILL_API int ill_moe_mm_id2(int fmt, int ncols, int nrows, int64_t add, int64_t add2, ill_dptr ptrs, ill_dptr counts,
+                           ill_dptr bases, int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map,
+                           ill_dptr y, ill_dptr y2, int64_t y_stride, ill_stream stream);
+
 /* ill_moe_mm_id with the combine of an expert-parallel chunk fused into it: the
  * row computed for `place` is stored straight into the memory of the rank that
  * owns its token, YPEERS[r] being the address of rank r's Y (peer memory: a
