@@ -420,7 +420,9 @@ def main():
                "combine": ("fused into the down product: stores into the owners' memory over NVLink" if peer_combine
                            else "NCCL all-to-all of fp32 rows" if world > 1 else "none (one GPU)"),
                "tok_per_s": n_tok / moe_ms * 1e3, "tflops": flop / moe_ms / 1e9, "scaling": "strong",
-               "exchange": "NCCL all-to-all of Q8_K rows out (1.14 B/value), fp32 rows back" if world > 1 else "none (one GPU)"}
+               "exchange": ("none (one GPU)" if world == 1 else
+                            "peer stores over NVLink: packed Q8_K rows out (1.14 B/value), fp32 rows back from the down product's epilogue"
+                            if peer_combine else "NCCL all-to-all of packed Q8_K rows out (1.14 B/value), fp32 rows back")}
         del pool, ce, lanes
 
     clocks = sampler.stop() if rank == 0 else None  # sampled over every timed region above
