@@ -100,6 +100,11 @@ __device__ __forceinline__ int dp2a_lo(int a, int b, int c) {
 
 // The IQ2_XXS codebook (256 x 8 magnitudes) and the sign patterns expanded to
 // byte masks (0xFF where the weight is negative), in shared memory.
+// IQ2_XXS tables in shared memory, IQ_COPIES interleaved copies each (entry e of copy c at [IQ_COPIES e + c]):
+// a lane reads copy lane % IQ_COPIES, so that the sixteen lanes of a 64-bit request spread over the banks
+// instead of piling onto the ones their random entries happen to share.  GRID / SMASK point at the lane's copy.
+constexpr int IQ_COPIES = 8;
+constexpr int IQ_TABLE_BYTES = IQ_COPIES * (256 + 128) * 8;
 struct IqTables { const uint2* grid; const uint2* smask; };
 
 template <int FMT> struct XReg;  // one token's activations for a unit
@@ -279,10 +284,12 @@ __device__ __forceinline__ float dot(const WReg<ILL_Q2_K>& w, const XReg<ILL_Q2_
   int isum = 0, mins = 0;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
+    // the 2-bit fields are masked where they sit (unsigned bytes up to 192 against signed ones): the dot comes
+    // out 4^k times too large, exactly, and one shift a group puts that right instead of one a word
     int d = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) d = __dp4a((int)((w.q[j] >> (2 * k)) & 0x03030303u), (int)x.q[4 * k + j], d);
-    isum += (int)(w.sc[k] & 15) * d;
+    for (int j = 0; j < 4; ++j) d = dp4a_us(w.q[j] & (0x03030303u << (2 * k)), (int)x.q[4 * k + j], d);
+    isum += (int)(w.sc[k] & 15) * (d >> (2 * k));
     mins += (int)(w.sc[k] >> 4) * x.bs[k];
   }
   return (x.d * w.d) * (float)isum - (x.d * w.dmin) * (float)mins;
@@ -309,8 +316,8 @@ __device__ __forceinline__ void load_w(WReg<ILL_IQ2_XXS>& w, const u8* row, cons
   const uint32_t idx = v[0], aux = v[1];
 #pragma unroll
   for (int l = 0; l < 4; ++l) {
-    const uint2 g = t.grid[(idx >> (8 * l)) & 0xff];
-    const uint2 m = t.smask[(aux >> (7 * l)) & 127];
+    const uint2 g = t.grid[IQ_COPIES * ((idx >> (8 * l)) & 0xff)];
+    const uint2 m = t.smask[IQ_COPIES * ((aux >> (7 * l)) & 127)];
     // (g ^ m) - m per byte; g <= 43, so adding 1 to a flipped byte never carries
     w.q[2 * l] = (g.x ^ m.x) + (m.x & 0x01010101u);
     w.q[2 * l + 1] = (g.y ^ m.y) + (m.y & 0x01010101u);
@@ -411,12 +418,12 @@ __device__ __forceinline__ void load_x_planes(XReg<FMT>& x, const ActP& a, int u
 
 // Fills the IQ2_XXS tables in shared memory (call from all threads, then sync).
 __device__ __forceinline__ void iq_tables_fill(uint2* grid, uint2* smask, const uint64_t* ggrid, const u8* gsigns) {
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-    const uint64_t g = ggrid[i];
+  for (int i = threadIdx.x; i < IQ_COPIES * 256; i += blockDim.x) {
+    const uint64_t g = ggrid[i / IQ_COPIES];
     grid[i] = make_uint2((uint32_t)g, (uint32_t)(g >> 32));
   }
-  for (int i = threadIdx.x; i < 128; i += blockDim.x) {
-    const uint32_t s = gsigns[i];
+  for (int i = threadIdx.x; i < IQ_COPIES * 128; i += blockDim.x) {
+    const uint32_t s = gsigns[i / IQ_COPIES];
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {

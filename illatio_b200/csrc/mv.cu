@@ -92,8 +92,8 @@ __global__ void __launch_bounds__(MV_THREADS) mvn_kernel(const MvParams p) {
   const uint32_t stage_stride = p.stage_bytes * (GLU ? 2u : 1u);
   u8* after = stage0 + (size_t)stage_stride * p.nstages;
   uint2* iq_grid = (uint2*)after;
-  uint2* iq_smask = iq_grid + 256;
-  uint64_t* full = (uint64_t*)(after + (IQ ? 3072 : 0));
+  uint2* iq_smask = iq_grid + IQ_COPIES * 256;
+  uint64_t* full = (uint64_t*)(after + (IQ ? IQ_TABLE_BYTES : 0));
 
   // this segment's matrices
   const u8* wbase[MV_MAX_MATS];
@@ -164,8 +164,8 @@ __global__ void __launch_bounds__(MV_THREADS) mvn_kernel(const MvParams p) {
   const int group = tid / L, lane_in = tid % L, ngroups = MV_THREADS / L;
   const int nsc = FMT == ILL_Q8_0 ? p.cols / 32 : p.cols / 256;
   IqTables iqt;
-  iqt.grid = iq_grid;
-  iqt.smask = iq_smask;
+  iqt.grid = iq_grid + (threadIdx.x & (IQ_COPIES - 1));
+  iqt.smask = iq_smask + (threadIdx.x & (IQ_COPIES - 1));
 
   int it = 0;
   bool failed = false;
@@ -300,9 +300,9 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
   u8* wstage = smem + (size_t)warp * p.stage_bytes * p.nstages;
   u8* after = smem + (size_t)WARPS * p.stage_bytes * p.nstages;
   uint2* iq_grid = (uint2*)after;
-  uint2* iq_smask = iq_grid + 256;
-  uint64_t* full = (uint64_t*)(after + (IQ ? 3072 : 0)) + warp * p.nstages;
-  u8* xsm = after + (IQ ? 3072 : 0) + 8 * WARPS * p.nstages;  // XS: the activations (16-byte aligned)
+  uint2* iq_smask = iq_grid + IQ_COPIES * 256;
+  uint64_t* full = (uint64_t*)(after + (IQ ? IQ_TABLE_BYTES : 0)) + warp * p.nstages;
+  u8* xsm = after + (IQ ? IQ_TABLE_BYTES : 0) + 8 * WARPS * p.nstages;  // XS: the activations (16-byte aligned)
 
   const u8* wbase[MV_MAX_MATS];
   if (p.ptrs) {
@@ -385,8 +385,8 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
   if (IQ || XS) __syncthreads();  // tables / activations staged
   else __syncwarp();
   IqTables iqt;
-  iqt.grid = iq_grid;
-  iqt.smask = iq_smask;
+  iqt.grid = iq_grid + (threadIdx.x & (IQ_COPIES - 1));
+  iqt.smask = iq_smask + (threadIdx.x & (IQ_COPIES - 1));
 
   int s = 0;
   uint32_t parity = 0;
@@ -605,12 +605,12 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
     }
   }
   // stages: four if two CTAs still fit an SM, else three (two CTAs, else one), else two
-  const uint32_t fixed = (fmt == ILL_IQ2_XXS ? 3072 : 0) + 8 * 8 * pl->warps + pl->x_bytes + 64 + 1024;
+  const uint32_t fixed = (fmt == ILL_IQ2_XXS ? IQ_TABLE_BYTES : 0) + 8 * 8 * pl->warps + pl->x_bytes + 64 + 1024;
   const uint32_t per_stage = pl->stage_bytes * pl->warps;
   const uint32_t two = 113 * 1024;  // half an SM's shared memory
   pl->nstages = per_stage * 4 + fixed <= two ? 4 : per_stage * 3 + fixed <= two ? 3 : per_stage * 3 + fixed <= 200 * 1024 ? 3 : 2;
   if (g_env_NST) pl->nstages = g_env_NST;
-  pl->smem = pl->stage_bytes * pl->nstages * pl->warps + (fmt == ILL_IQ2_XXS ? 3072 : 0) + 8 * pl->nstages * pl->warps +
+  pl->smem = pl->stage_bytes * pl->nstages * pl->warps + (fmt == ILL_IQ2_XXS ? IQ_TABLE_BYTES : 0) + 8 * pl->nstages * pl->warps +
              pl->x_bytes + 64;
   return pl->smem > 220 * 1024 ? ILL_ERR_UNSUPPORTED : ILL_OK;
 }
@@ -641,7 +641,7 @@ static int plan_many(int fmt, long long total_rows, int cols, int ntok, int nseg
   pl->xs_off = align_up((uint32_t)ntok * cols, 16);
   pl->bs_off = align_up(pl->xs_off + 4u * ntok * nsc, 16);
   pl->x_bytes = align_up(pl->bs_off + 2u * ntok * (cols / 16), 128);
-  pl->smem = pl->x_bytes + pl->stage_bytes * pl->nstages + (fmt == ILL_IQ2_XXS ? 3072 : 0) + 64;
+  pl->smem = pl->x_bytes + pl->stage_bytes * pl->nstages + (fmt == ILL_IQ2_XXS ? IQ_TABLE_BYTES : 0) + 64;
   return pl->smem > 227 * 1024 ? ILL_ERR_UNSUPPORTED : ILL_OK;
 }
 
