@@ -540,7 +540,11 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
   const int bb = fmt_block_bytes(fmt), bw = fmt_block_weights(fmt), uw = unit_weights(fmt);
   const long long row_bytes = (long long)(cols / bw) * bb;
   const int units = cols / uw;
-  const int upt_max = uw == 32 ? 5 : 3;
+  // Units a lane keeps in registers, at most.  More of them lets fewer lanes share a row with none idle (80 units:
+  // 16 lanes x 5 instead of 32 x 3 with five lanes idle) at the price of registers, i.e. of resident warps.
+  // Measured on 151936-row matrices and the 4B model's shapes: five pays for Q6_K and Q2_K rows and for the gated
+  // Q4_K product, three for the rest.
+  const int upt_max = uw == 32 ? 5 : ((fmt == ILL_Q6_K || fmt == ILL_Q2_K) && !glu) || (fmt == ILL_Q4_K && glu) ? 5 : 3;
   int bestL = 0, bestU = 0;
   double best = -1.0;
   for (int L = 32; L >= 8; L >>= 1) {
@@ -658,7 +662,7 @@ static int launch_k(K k, const MvParams& p, const MvPlan& pl, int gx, int gy, cu
 
 template <int FMT, int MODE, int AL>
 static int launch_one_u(const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
-  constexpr int UMAX = (FMT == ILL_Q8_0 || FMT == ILL_IQ2_XXS) ? 5 : 3;
+  constexpr int UMAX = 5;
   if (pl.xs) {
     switch (pl.upt) {
       case 1: return launch_k(mvw_kernel<FMT, MODE, 1, AL, true>, p, pl, gx, gy, st);
