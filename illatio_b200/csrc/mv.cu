@@ -542,12 +542,13 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
   const int units = cols / uw;
   // Units a lane keeps in registers, at most.  More of them lets fewer lanes share a row with none idle (80 units:
   // 16 lanes x 5 instead of 32 x 3 with five lanes idle) at the price of registers, i.e. of resident warps.
-  // Measured on 151936-row matrices and the 4B model's shapes: five pays for Q6_K and Q2_K rows and for the gated
-  // Q4_K product, three for the rest.
-  const int upt_max = uw == 32 ? 5 : ((fmt == ILL_Q6_K || fmt == ILL_Q2_K) && !glu) || (fmt == ILL_Q4_K && glu) ? 5 : 3;
+  // Measured on 151936-row matrices and the 4B model's shapes: five pays for Q6_K and Q2_K rows, for the gated
+  // Q4_K product and for large Q4_K matrices, three for the rest; Q8_0's 32-wide units go up to seven, four lanes a row.
+  const bool big = total_rows * row_bytes * nseg >= (16ll << 20);  // Q4_K rows: five only pays once the launch is long
+  const int upt_max = fmt == ILL_Q8_0 ? 7 : uw == 32 ? 5 : (fmt == ILL_Q4_K && !glu) ? (big ? 5 : 3) : ((fmt == ILL_Q6_K || fmt == ILL_Q2_K) && !glu) || (fmt == ILL_Q4_K && glu) ? 5 : 3;
   int bestL = 0, bestU = 0;
   double best = -1.0;
-  for (int L = 32; L >= 8; L >>= 1) {
+  for (int L = 32; L >= (fmt == ILL_Q8_0 ? 4 : 8); L >>= 1) {
     const int upt = (units + L - 1) / L;
     if (upt > upt_max) continue;
     const double eff = (double)units / ((double)L * upt) + (L == 16 ? 0.02 : L == 32 ? 0.01 : 0.0);  // ties: 16, then 32
@@ -608,11 +609,14 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
       default: pl->x_bytes = plane_bytes<ILL_IQ2_XXS>(units, nsc); break;
     }
   }
-  // stages: four if two CTAs still fit an SM, else three (two CTAs, else one), else two
+  // stages: four if two CTAs still fit an SM, else three or two with two CTAs, else three or two with one
   const uint32_t fixed = (fmt == ILL_IQ2_XXS ? IQ_TABLE_BYTES : 0) + 8 * 8 * pl->warps + pl->x_bytes + 64 + 1024;
   const uint32_t per_stage = pl->stage_bytes * pl->warps;
   const uint32_t two = 113 * 1024;  // half an SM's shared memory
-  pl->nstages = per_stage * 4 + fixed <= two ? 4 : per_stage * 3 + fixed <= two ? 3 : per_stage * 3 + fixed <= 200 * 1024 ? 3 : 2;
+  // (plain products: two CTAs with two stages each beat one CTA with three, residency hides more latency than
+  // depth; a gated product's group is two stages, so it needs the third to fetch ahead at all)
+  pl->nstages = per_stage * 4 + fixed <= two ? 4 : per_stage * 3 + fixed <= two ? 3 : (!glu && per_stage * 2 + fixed <= two) ? 2
+                : per_stage * 3 + fixed <= 200 * 1024 ? 3 : 2;
   if (g_env_NST) pl->nstages = g_env_NST;
   pl->smem = pl->stage_bytes * pl->nstages * pl->warps + (fmt == ILL_IQ2_XXS ? IQ_TABLE_BYTES : 0) + 8 * pl->nstages * pl->warps +
              pl->x_bytes + 64;
@@ -678,6 +682,8 @@ static int launch_one_u(const MvParams& p, const MvPlan& pl, int gx, int gy, cud
     case 3: return launch_k(mvw_kernel<FMT, MODE, 3, AL, false>, p, pl, gx, gy, st);
     case 4: if constexpr (UMAX >= 4) return launch_k(mvw_kernel<FMT, MODE, 4, AL, false>, p, pl, gx, gy, st); break;
     case 5: if constexpr (UMAX >= 5) return launch_k(mvw_kernel<FMT, MODE, 5, AL, false>, p, pl, gx, gy, st); break;
+    case 6: if constexpr (FMT == ILL_Q8_0) return launch_k(mvw_kernel<FMT, MODE, 6, AL, false>, p, pl, gx, gy, st); break;
+    case 7: if constexpr (FMT == ILL_Q8_0) return launch_k(mvw_kernel<FMT, MODE, 7, AL, false>, p, pl, gx, gy, st); break;
   }
   return ILL_ERR_UNSUPPORTED;
 }
