@@ -112,7 +112,8 @@ def test_dequant_rows_bit_exact_random_and_embed(oracle, fmt):
 # block / super-block per row, one row, rows not a multiple of anything
 SHAPES = {
     B.Q8_0: [(896, 896), (128, 896), (4864, 896), (896, 4864), (1, 32), (5, 64), (1031, 160)],
-    B.Q4_K: [(4096, 2560), (1024, 2560), (2560, 4096), (1, 256), (3, 512), (777, 768)],
+    B.Q4_K: [(4096, 2560), (1024, 2560), (2560, 4096), (1, 256), (3, 512), (777, 768),
+             (11700, 2560)],  # past 16 MB the plan changes (eight lanes a row, five units a lane)
     B.Q6_K: [(1024, 2560), (2560, 9728), (5120, 5120), (1, 256), (5, 256), (333, 1280), (64, 17408)],
     B.Q2_K: [(4096, 2048), (1536, 5120), (5120, 1536), (1, 256), (7, 512)],
     B.IQ2_XXS: [(2048, 4096), (1, 256), (9, 512), (515, 1024)],
