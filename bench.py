@@ -383,7 +383,18 @@ def main():
         peer_combine = world > 1 and not exact and os.environ.get("ILL_EP_COMBINE", "peer") == "peer"
         mk = (lambda: EP.EpScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev)) if exact else \
              (lambda: EP.EpCapScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev, peer=peer_combine))
-        lanes = [(torch.cuda.Stream(device=dev), mk()) for _ in range(nlanes)]
+        try:
+            lanes = [(torch.cuda.Stream(device=dev), mk()) for _ in range(nlanes)]
+            made = 1
+        except Exception as exc:  # no peer mapping on this box: the same exchanges over NCCL
+            print("rank %d: symmetric memory unavailable (%s)" % (rank, exc), file=sys.stderr)
+            made = 0
+        if peer_combine:  # every rank takes the same path
+            agree = torch.tensor([made], device=dev)
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            if agree.item() == 0:
+                peer_combine = False
+                lanes = [(torch.cuda.Stream(device=dev), mk()) for _ in range(nlanes)]
         flags = []
 
         def run_chunks(k):
