@@ -36,7 +36,7 @@ SIGNATURES = {
     "ill_moe_glu": (_I, [_I, _I, _I, _L, _L, _P, _I, _P, _P, _P, _I, _F, _P, _P, _L, _S]),
     "ill_swiglu_w": (_I, [_L, _I, _F, _P, _P, _P, _P, _S]),
     "ill_moe_sum": (_I, [_I, _I, _L, _P, _P, _P, _P, _S]),
-    "ill_swiglu_q8k_f16": (_I, [_L, _I, _F, _P, _P, _P, _P, _P, _P, _S]),
+    "ill_swiglu_q8k_f16": (_I, [_L, _I, _F, _P, _P, _P, _P, _P, _P, _P, _S]),
     "ill_mv_dense": (_I, [_I, _P, _I, _I, _P, _P, _I, _L, _S]),
     "ill_moe_route": (_I, [_I, _I, _I, _F, _L, _P, _P, _P, _P, _S]),
     "ill_moe_group_scratch_bytes": (_L, [_L, _I]),
@@ -49,11 +49,11 @@ SIGNATURES = {
     "ill_ep_row_bytes": (_L, [_I]),
     "ill_ep_pack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _S]),
     "ill_ep_pack_cap": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _S]),
-    "ill_ep_put_counts": (_I, [_I, _I, _I, _P, _P, _S]),
+    "ill_ep_put_counts": (_I, [_I, _I, _I, _P, _P, _P, _S]),
     "ill_ep_plan_dev": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _S]),
     "ill_moe_mm_id2": (_I, [_I, _I, _I, _L, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),
     "ill_moe_mm_id_peers": (_I, [_I, _I, _I, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),
-    "ill_ep_unpack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _S]),
+    "ill_ep_unpack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _S]),
 }
 
 

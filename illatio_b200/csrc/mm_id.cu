@@ -736,13 +736,14 @@ __global__ void __launch_bounds__(256) act_f16_kernel(long long rows, int cols, 
                                                       const unsigned* __restrict__ map, __half* __restrict__ xh,
                                                       __half* __restrict__ xe, const u8* __restrict__ sc,
                                                       const u8* __restrict__ wt, float* __restrict__ xd_out,
-                                                      float* __restrict__ w_out) {
+                                                      float* __restrict__ w_out, const unsigned* __restrict__ rows_dev) {
   pdl_launch_dependents();
   pdl_wait();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread: 16 values
   const int per_row = cols / 16;
   if (gid >= rows * per_row) return;
   const long long place = gid / per_row;
+  if (rows_dev && place >= (long long)*rows_dev) return;  // the rows in use, known on the device only
   const int j = (int)(gid - place * per_row);
   const long long t = map ? (long long)map[place] : place;
   const uint4 q = *(const uint4*)(xq + t * xq_stride + 16 * j);
@@ -899,9 +900,11 @@ __global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, in
 // This rank's rows per expert to the experts' ranks, without a collective: COUNTS[g * per + e] into row RANK of
 // rank g's [world, per] table (peer memory).
 __global__ void __launch_bounds__(256) ep_put_counts_kernel(int world, int per, int rank, const unsigned* __restrict__ counts,
-                                                            const unsigned long long* __restrict__ peers) {
+                                                            const unsigned long long* __restrict__ peers,
+                                                            unsigned* __restrict__ overflow) {
   pdl_launch_dependents();
   pdl_wait();
+  if (overflow && blockIdx.x == 0 && threadIdx.x == 0) *overflow = 0;  // for the pack that follows in the stream
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < world * per; i += gridDim.x * blockDim.x) {
     const int g = i / per, e = i - g * per;
     ((unsigned*)(uintptr_t)peers[g])[rank * per + e] = counts[i];
@@ -930,14 +933,15 @@ using namespace ill;
 
 static int act_f16_launch(int64_t rows, int cols, const u8* qp, long long qs, const u8* bp, long long bs, ill_dptr map,
                           ill_dptr xh, ill_dptr xe, const u8* sc, const u8* wt, ill_dptr xd_out, ill_dptr w_out,
-                          ill_stream stream) {
+                          ill_stream stream, ill_dptr rows_dev = 0) {
   long long nrows = rows;
   const unsigned* mp = (const unsigned*)(uintptr_t)map;
   __half* hp = (__half*)(uintptr_t)xh;
   __half* ep = (__half*)(uintptr_t)xe;
   float* xo = (float*)(uintptr_t)xd_out;
   float* wo = (float*)(uintptr_t)w_out;
-  void* args[] = {&nrows, &cols, &qp, &qs, &bp, &bs, &mp, &hp, &ep, &sc, &wt, &xo, &wo};
+  const unsigned* rd = (const unsigned*)(uintptr_t)rows_dev;
+  void* args[] = {&nrows, &cols, &qp, &qs, &bp, &bs, &mp, &hp, &ep, &sc, &wt, &xo, &wo, &rd};
   const long long threads = rows * (cols / 16);
   return launch_kernel((const void*)act_f16_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, args,
                        (cudaStream_t)stream);
@@ -998,12 +1002,14 @@ extern "C" int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs,
   return launch_kernel((const void*)ep_pack_cap_kernel, dim3((unsigned)rows), dim3(128), 0, args, (cudaStream_t)stream);
 }
 
-extern "C" int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill_dptr peers, ill_stream stream) {
+extern "C" int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill_dptr peers, ill_dptr overflow,
+                                 ill_stream stream) {
   if (world < 1 || per < 1 || rank < 0 || rank >= world || !counts || !peers) return ILL_ERR_ARG;
-  if ((counts & 3) || (peers & 7)) return ILL_ERR_ALIGN;
+  if ((counts & 3) || (peers & 7) || (overflow & 3)) return ILL_ERR_ALIGN;
   const unsigned* cp = (const unsigned*)(uintptr_t)counts;
   const unsigned long long* pr = (const unsigned long long*)(uintptr_t)peers;
-  void* args[] = {&world, &per, &rank, &cp, &pr};
+  unsigned* ov = (unsigned*)(uintptr_t)overflow;
+  void* args[] = {&world, &per, &rank, &cp, &pr, &ov};
   return launch_kernel((const void*)ep_put_counts_kernel, dim3((unsigned)((world * per + 255) / 256)), dim3(256), 0, args,
                        (cudaStream_t)stream);
 }
@@ -1032,14 +1038,14 @@ extern "C" int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr r
 }
 
 extern "C" int ill_ep_unpack(int64_t rows, int cols, ill_dptr packed, ill_dptr map, ill_dptr xh, ill_dptr xe, ill_dptr xd,
-                             ill_dptr w, ill_stream stream) {
+                             ill_dptr w, ill_dptr rows_dev, ill_stream stream) {
   if (rows < 0 || cols <= 0 || cols % 256 || !packed || !xh || !xd || !w) return ILL_ERR_ARG;
-  if ((packed & 15) || (map & 3) || (xh & 15) || (xe & 15) || (xd & 3) || (w & 3)) return ILL_ERR_ALIGN;
+  if ((packed & 15) || (map & 3) || (xh & 15) || (xe & 15) || (xd & 3) || (w & 3) || (rows_dev & 3)) return ILL_ERR_ALIGN;
   if (rows == 0) return ILL_OK;
   const long long rb = ill_ep_row_bytes(cols);
   const u8* base = (const u8*)(uintptr_t)packed;
   return act_f16_launch(rows, cols, base, rb, base + cols + cols / 256 * 4, rb, map, xh, xe, base + cols,
-                        base + cols + cols / 256 * 4 + cols / 16 * 2, xd, w, stream);
+                        base + cols + cols / 256 * 4 + cols / 16 * 2, xd, w, stream, rows_dev);
 }
 
 static int encode_map(CUtensorMap* map, ill_dptr base, int64_t inner, int64_t rows) {

@@ -221,12 +221,14 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(long long rows, int ro
 __global__ void __launch_bounds__(256) swiglu_q8k_f16_kernel(long long nblocks, int ff, float clamp,
                                                              const float* __restrict__ g, const float* __restrict__ u,
                                                              const float* __restrict__ w, __half* __restrict__ mh,
-                                                             __half* __restrict__ me, float* __restrict__ ms) {
+                                                             __half* __restrict__ me, float* __restrict__ ms,
+                                                             const unsigned* __restrict__ rows_dev) {
   pdl_launch_dependents();
   pdl_wait();
   const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (b >= nblocks) return;
+  if (rows_dev && b >= (long long)*rows_dev * (ff / 256)) return;  // the rows in use, known on the device only
   const float wv = w ? w[b / (ff / 256)] : 1.0f;
   const float4 g0 = ((const float4*)(g + b * 256))[2 * lane], g1 = ((const float4*)(g + b * 256))[2 * lane + 1];
   const float4 u0 = ((const float4*)(u + b * 256))[2 * lane], u1 = ((const float4*)(u + b * 256))[2 * lane + 1];
@@ -496,9 +498,9 @@ extern "C" int ill_moe_group_static(int64_t rows, int ne, int nu, ill_dptr sel, 
 }
 
 extern "C" int ill_swiglu_q8k_f16(int64_t rows, int ff, float clamp, ill_dptr g, ill_dptr u, ill_dptr w, ill_dptr mh,
-                                  ill_dptr me, ill_dptr ms, ill_stream stream) {
+                                  ill_dptr me, ill_dptr ms, ill_dptr rows_dev, ill_stream stream) {
   if (rows < 0 || ff <= 0 || ff % 256 || !g || !u || !mh || !ms) return ILL_ERR_ARG;
-  if ((g & 15) || (u & 15) || (w & 3) || (mh & 15) || (me & 15) || (ms & 3)) return ILL_ERR_ALIGN;
+  if ((g & 15) || (u & 15) || (w & 3) || (mh & 15) || (me & 15) || (ms & 3) || (rows_dev & 3)) return ILL_ERR_ALIGN;
   if (rows == 0) return ILL_OK;
   long long nb = rows * (ff / 256);
   const float* gp = (const float*)(uintptr_t)g;
@@ -507,7 +509,8 @@ extern "C" int ill_swiglu_q8k_f16(int64_t rows, int ff, float clamp, ill_dptr g,
   __half* hp = (__half*)(uintptr_t)mh;
   __half* ep = (__half*)(uintptr_t)me;
   float* sp = (float*)(uintptr_t)ms;
-  void* args[] = {&nb, &ff, &clamp, &gp, &up, &wp, &hp, &ep, &sp};
+  const unsigned* rd = (const unsigned*)(uintptr_t)rows_dev;
+  void* args[] = {&nb, &ff, &clamp, &gp, &up, &wp, &hp, &ep, &sp, &rd};
   return launch_kernel((const void*)swiglu_q8k_f16_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, args,
                        (cudaStream_t)stream);
 }

@@ -98,7 +98,7 @@ def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, s
         mm_id(pool, pool.gate_fmt, d, ff, pool.gate_bytes, sc, sc.xh, sc.xe, sc.xq.xs, sc.rmap, sc.u)
     if fused:  # the three steps below in one pass (same results bit for bit; sc.mid and sc.midq.xq stay unwritten)
         _lib.call("ill_swiglu_q8k_f16", sc.rows, ff, float(clamp), _ptr(sc.g), _ptr(sc.u), _ptr(sc.wrow), _ptr(sc.mh),
-                  _ptr(sc.me), _ptr(sc.midq.xs), st)
+                  _ptr(sc.me), _ptr(sc.midq.xs), 0, st)
     else:
         swiglu_w(sc.g, sc.u, sc.wrow, sc.mid, ff, clamp)
         D.quant_q8(sc.mid, sc.midq)                                # per (token, slot) row, as the CPU path does

@@ -314,11 +314,11 @@ def chunk_fast(ex, sc, norms, logits, n_expert_total, group=None):
         r_rows = sc.s_rows
     if total:
         # the arrived rows as the products want them, expert by expert
-        call("ill_ep_unpack", total, d, ptr(r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), st)
+        call("ill_ep_unpack", total, d, ptr(r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), 0, st)
         call("ill_moe_mm_id2", pool.gate_fmt, d, ff, 0, pool.gate_bytes, ptr(pool.ptrs_all), ptr(lcounts), ptr(lbases),
              pool.n_expert, total, ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, ptr(sc.g), ptr(sc.u), ff, st)
         call("ill_swiglu_q8k_f16", total, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mh), ptr(sc.me),
-             ptr(sc.ms), st)
+             ptr(sc.ms), 0, st)
         # the down rows leave in the order their inputs arrived
         call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(lcounts), ptr(lbases),
              pool.n_expert, total, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.p2r), ptr(sc.down), d, st)
@@ -413,15 +413,15 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
          ptr(sc.smap), ptr(sc.wrow), st)
     me = dist.get_rank(group) if dist.is_initialized() else 0
     call("ill_quant_q8_k", ptr(norms), ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), n * d // 256, st)
-    sc.overflow.zero_()
     if sc.peers is not None:
         # the dispatch without a collective: counts and rows are stored straight into the receivers' buffers
         # over NVLink, then the ranks meet
-        call("ill_ep_put_counts", world, per, me, ptr(sc.counts), ptr(sc.peers_rc), st)
+        call("ill_ep_put_counts", world, per, me, ptr(sc.counts), ptr(sc.peers_rc), ptr(sc.overflow), st)
         call("ill_ep_pack_cap", rows, d, ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), per,
              world, cap, 0, ptr(sc.pslot), ptr(sc.overflow), ptr(sc.peers_rows), me, st)
         sc.hdl.barrier()
     else:
+        sc.overflow.zero_()
         if world > 1:  # my rows per expert, to each expert's rank: [world, per] both ways
             dist.all_to_all_single(sc.rc.view(-1), sc.counts, group=group)
         else:
@@ -432,11 +432,13 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
             dist.all_to_all_single(sc.r_rows, sc.s_rows, group=group)
     call("ill_ep_plan_dev", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
          ptr(sc.pdst), ptr(sc.total), st)
-    call("ill_ep_unpack", tot, d, ptr(sc.r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), st)
+    # the element-wise steps stop at the rows in use (sc.total, written by the plan), not at the slabs' capacity
+    call("ill_ep_unpack", tot, d, ptr(sc.r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), ptr(sc.total),
+         st)
     call("ill_moe_mm_id2", pool.gate_fmt, d, ff, 0, pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases),
          pool.n_expert, tot, ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), 0, ptr(sc.g), ptr(sc.u), ff, st)  # gate and up in one launch
     call("ill_swiglu_q8k_f16", tot, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mh), ptr(sc.me), ptr(sc.ms),
-         st)
+         ptr(sc.total), st)
     if sc.peers is not None:
         # the combine fused into the down product: rows go straight to their owners over NVLink; then the ranks
         # meet, so that every owner's rows are in before it sums them

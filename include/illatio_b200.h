@@ -195,9 +195,9 @@ ILL_API int ill_swiglu_w(int64_t n, int ff, float clamp, ill_dptr g, ill_dptr u,
  * lays them out.  Bit for bit what the three calls produce; the middle values
  * and their int8 form are not written.  (The reference keeps d4_swiglu_w and
  * the quantizer apart, src/cuda-ds4f-prefill.lisp:348-349; fusing them is its own
- * open item, TODO.md:16-21.) */
+ * open item, TODO.md:16-21.)  ROWS_DEV as for ill_ep_unpack (0: all ROWS). */
 ILL_API int ill_swiglu_q8k_f16(int64_t rows, int ff, float clamp, ill_dptr g, ill_dptr u, ill_dptr w, ill_dptr mh,
-                               ill_dptr me, ill_dptr ms, ill_stream stream);
+                               ill_dptr me, ill_dptr ms, ill_dptr rows_dev, ill_stream stream);
 
 /* MOE[t*d + r] = sum over slots s < NU, in slot order, of DOWN[row(t,s)*d + r]
  * (+ SHARED[t*d + r] unless 0); row(t,s) = MAP[t*nu + s], or t*nu + s when MAP
@@ -291,12 +291,14 @@ ILL_API int ill_act_f16(int64_t rows, int cols, ill_dptr xq, ill_dptr bsums, ill
  * arrived packed: XH / XE as there, plus XD[place, kb] (the scales
  * ill_moe_mm_id wants, so that it needs no MAP) and W[place]; MAP[place] is the
  * arrival index of the row placed at `place` (the P2R of ill_ep_plan_rows; 0:
- * the same).  No counterpart in the reference. */
+ * the same).  ROWS_DEV, when not 0, points at the number of rows in use (a
+ * uint32 on the device, e.g. the TOTAL of ill_ep_plan_dev): places from there
+ * up to ROWS are skipped.  No counterpart in the reference. */
 ILL_API int64_t ill_ep_row_bytes(int cols);
 ILL_API int ill_ep_pack(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr w, ill_dptr map,
                         ill_dptr packed, ill_stream stream);
 ILL_API int ill_ep_unpack(int64_t rows, int cols, ill_dptr packed, ill_dptr map, ill_dptr xh, ill_dptr xe, ill_dptr xd,
-                          ill_dptr w, ill_stream stream);
+                          ill_dptr w, ill_dptr rows_dev, ill_stream stream);
 
 /* The same exchange with slabs of a fixed size, so that the host never waits for
  * counts: every rank sends every rank CAP rows' worth (ill_ep_pack_cap: rank g's
@@ -316,8 +318,10 @@ ILL_API int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, il
  * buffer and PACKED is not used; ill_ep_put_counts does the same for the table
  * of counts (row RANK of every rank's [world, per] table).  The dispatch then
  * needs no collective, only a barrier between the ranks' streams before the
- * receivers read. */
-ILL_API int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill_dptr peers, ill_stream stream);
+ * receivers read.  OVERFLOW, when not 0, is cleared (the flag of the
+ * ill_ep_pack_cap that follows in the stream). */
+ILL_API int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill_dptr peers, ill_dptr overflow,
+                              ill_stream stream);
 ILL_API int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
                             ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_stream stream);
 
