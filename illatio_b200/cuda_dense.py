@@ -122,6 +122,17 @@ def cmat_mul(w, act, y, n=1, bias=None, acc=False):
     return y
 
 
+_SIDE = {}
+
+
+def _side_stream(device):
+    """A second stream per device for products that may run beside the current stream's."""
+    s = _SIDE.get(device)
+    if s is None:
+        s = _SIDE[device] = torch.cuda.Stream(device=device)
+    return s
+
+
 def qkv_mul(wq, wk, wv, act, q, k, v, bq=None, bk=None, bv=None, n=1):
     """QKV-MUL (src/cuda-dense.lisp:309-324): one launch when the three formats
     agree and there is one token, else three products."""
@@ -130,11 +141,17 @@ def qkv_mul(wq, wk, wv, act, q, k, v, bq=None, bk=None, bv=None, n=1):
                   _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum) if act.kind == "q8k" else 0,
                   _ptr(q), _ptr(k), _ptr(v), _ptr(bq), _ptr(bk), _ptr(bv), _stream())
     elif n == 1 and wq.type == wk.type:
-        # Q4_K_M files keep V in Q6_K: Q and K in one launch, V in its own
+        # Q4_K_M files keep V in Q6_K: Q and K in one launch, V in its own -- beside it, on a second
+        # stream (both read the same activations; in a captured graph this is a fork and a join)
+        cur = torch.cuda.current_stream()
+        side = _side_stream(cur.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            cmat_mul(wv, act, v, n, bias=bv)
         _lib.call("ill_mv_3", wq.type, _ptr(wq.qs), _ptr(wk.qs), 0, wq.rows, wk.rows, 0, wq.cols,
                   _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum) if act.kind == "q8k" else 0,
                   _ptr(q), _ptr(k), 0, _ptr(bq), _ptr(bk), 0, _stream())
-        cmat_mul(wv, act, v, n, bias=bv)
+        cur.wait_stream(side)
     else:
         cmat_mul(wq, act, q, n, bias=bq)
         cmat_mul(wk, act, k, n, bias=bk)
