@@ -55,7 +55,9 @@ def emit(grid, signs, qual_grid, qual_signs, guard):
 
 
 def main():
-    src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src/iquant.lisp"
+    if len(sys.argv) != 2:
+        sys.exit("usage: gen_iq2xxs_tables.py <the reference's src/iquant.lisp>")
+    src = sys.argv[1]
     grid, signs = parse(src)
     here = os.path.dirname(os.path.abspath(__file__))
     with open(os.path.join(here, "iq2xxs_tables.h"), "w") as f:
