@@ -554,6 +554,8 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
     const double eff = (double)units / ((double)L * upt) + (L == 16 ? 0.02 : L == 32 ? 0.01 : 0.0);  // ties: 16, then 32
     if (eff > best) { best = eff; bestL = L; bestU = upt; }
   }
+  // a row too long for that many units still beats staging it in column chunks if 32 lanes x 5 units hold it
+  if (!bestL && !g_env_XS && uw == 64 && (units + 31) / 32 <= 5) { bestL = 32; bestU = (units + 31) / 32; }
   if (g_env_L && (units + g_env_L - 1) / g_env_L <= upt_max) { bestL = g_env_L; bestU = (units + g_env_L - 1) / g_env_L; }
   pl->one = true;
   pl->xs = false;
