@@ -47,6 +47,14 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def tensor_peak():
+    """Measured dense bf16 / fp16 TFLOP/s of this pool's B200s (the burst figure), else the fallback."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -431,6 +439,9 @@ def main():
                "combine": ("fused into the down product: stores into the owners' memory over NVLink" if peer_combine
                            else "NCCL all-to-all of fp32 rows" if world > 1 else "none (one GPU)"),
                "tok_per_s": n_tok / moe_ms * 1e3, "tflops": flop / moe_ms / 1e9, "scaling": "strong",
+               "roofline": {"bound": "tensor", "achieved": flop / moe_ms / 1e9 / world, "peak": tensor_peak()[0],
+                            "peak_source": tensor_peak()[1], "unit": "TFLOP/s per GPU, whole chunk (products and all the steps around them)",
+                            "frac": flop / moe_ms / 1e9 / world / tensor_peak()[0]},
                "exchange": ("none (one GPU)" if world == 1 else
                             "peer stores over NVLink: packed Q8_K rows out (1.14 B/value), fp32 rows back from the down product's epilogue"
                             if peer_combine else "NCCL all-to-all of packed Q8_K rows out (1.14 B/value), fp32 rows back")}
