@@ -832,10 +832,11 @@ __global__ void __launch_bounds__(128) ep_pack_cap_kernel(int cols, long long ro
   const long long t = map[place];
   const int nq = cols / 4, ns = cols / 256, nb = cols / 32;  // words of quants, scales, sums
   uint32_t* dst = packed + slot * (row_bytes / 4);
-  for (int i = threadIdx.x; i < nq + ns + nb + 1; i += blockDim.x) {
+  // the quants 16 bytes at a time (a token's quants and a packed row both start on 16-byte boundaries), the rest by words
+  for (int i = threadIdx.x; i < nq / 4; i += blockDim.x) ((uint4*)dst)[i] = ((const uint4*)(xq + t * nq))[i];
+  for (int i = nq + threadIdx.x; i < nq + ns + nb + 1; i += blockDim.x) {
     uint32_t v;
-    if (i < nq) v = xq[t * nq + i];
-    else if (i < nq + ns) v = xs[t * ns + (i - nq)];
+    if (i < nq + ns) v = xs[t * ns + (i - nq)];
     else if (i < nq + ns + nb) v = xsum[t * nb + (i - nq - ns)];
     else v = w[place];
     dst[i] = v;
@@ -983,7 +984,7 @@ extern "C" int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs,
   if (rows < 0 || cols <= 0 || cols % 256 || per < 1 || world < 1 || cap < 1 || !xq || !xs || !xsum || !w || !map || !bases ||
       (!packed && !peers) || !pslot || !overflow || rank < 0 || rank >= world)
     return ILL_ERR_ARG;
-  if ((xq & 3) || (xs & 3) || (xsum & 3) || (w & 3) || (map & 3) || (bases & 3) || (packed & 15) || (pslot & 3) || (overflow & 3) ||
+  if ((xq & 15) || (xs & 3) || (xsum & 3) || (w & 3) || (map & 3) || (bases & 3) || (packed & 15) || (pslot & 3) || (overflow & 3) ||
       (peers & 7))
     return ILL_ERR_ALIGN;
   if (rows == 0) return ILL_OK;
