@@ -73,6 +73,20 @@ def _worker(rank, world, port, q):
             return out
 
         got = ep.moe_chunk_ep(norms, logits, NU, _route, lambda x: (x,), experts, summed, E)
+        # the plan the GPU drivers derive on the host from every rank's counts is the one plan_dispatch exchanges for
+        sel, _ = _route(logits)
+        mine = torch.bincount(sel.reshape(-1).long(), minlength=E)
+        allc = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allc, mine)
+        plan = ep.plan_dispatch(mine, world)
+        send, recv, counts, bases, seg_a, seg_p, seg_l = ep.host_plan(torch.stack(allc).numpy(), rank, per)
+        assert send.tolist() == plan.send_counts and recv.tolist() == plan.recv_counts
+        assert counts.tolist() == plan.counts.tolist() and bases.tolist() == plan.bases.tolist()
+        p2r = [0] * int(recv.sum())
+        for a, pl, n in zip(seg_a, seg_p, seg_l):
+            for i in range(int(n)):
+                p2r[int(pl) + i] = int(a) + i
+        assert p2r == plan.place_to_recv.tolist()
         q.put((rank, torch.allclose(got, _expected(norms, logits), atol=1e-6), None))
     except Exception as exc:  # report instead of hanging the other rank
         q.put((rank, False, repr(exc)))
