@@ -22,8 +22,7 @@ SIGNATURES = {
     "ill_last_cuda_error": (_I, []),
     "ill_block_bytes": (_I, [_I]),
     "ill_block_weights": (_I, [_I]),
-    "ill_set_pdl": (_I, [_I]),
-    "ill_set_tuning": (_I, [_I, _I, _I, _I]),
+    "ill_test_wait_timeout": (_I, [_L, _P, _S]),
     "ill_device_status": (_I, [_c.POINTER(_c.c_uint), _S]),
     "ill_quant_q8_0": (_I, [_P, _P, _P, _P, _L, _I, _S]),
     "ill_quant_q8_k": (_I, [_P, _P, _P, _P, _L, _S]),
@@ -50,7 +49,7 @@ SIGNATURES = {
     "ill_ep_pack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _S]),
     "ill_ep_pack_cap": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _S]),
     "ill_ep_put_counts": (_I, [_I, _I, _I, _P, _P, _P, _S]),
-    "ill_ep_plan_dev": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _S]),
+    "ill_ep_plan_dev": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _S]),
     "ill_moe_mm_id2": (_I, [_I, _I, _I, _L, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),
     "ill_moe_mm_id_peers": (_I, [_I, _I, _I, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),
     "ill_ep_unpack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _S]),

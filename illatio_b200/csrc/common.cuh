@@ -22,7 +22,10 @@ typedef unsigned short u16;
 
 // device status codes (written once, first writer wins)
 enum { ST_OK = 0, ST_MV_WAIT = 0x100, ST_MM_WAIT_FULL = 0x200, ST_MM_WAIT_EMPTY = 0x300,
-       ST_MM_WAIT_ACC = 0x400, ST_MM_WAIT_EPI = 0x500 };
+       ST_MM_WAIT_ACC = 0x400, ST_MM_WAIT_EPI = 0x500,
+       ST_GROUP_SEL = 0x600 /* an expert number out of range in ill_moe_group's SEL */,
+       ST_BARRIER_WAIT = 0x700 /* a barrier between CTAs or ranks never completed */,
+       ST_TEST_WAIT = 0x800 /* ill_test_wait_timeout: the wait that is meant to run out */ };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -59,12 +62,12 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: gives up about ILL_WAIT_NS nanoseconds after it began.  Returns false (and records CODE
+// Bounded wait: gives up about LIMIT_NS (by default ILL_WAIT_NS) nanoseconds after it began.  Returns false (and records CODE
 // in the status word, first writer wins) when the phase never completes.  SLEEP_NS > 0 makes the
 // waiter sleep between polls, so that a warp with slack leaves the issue slots to the others; the
 // clock is read once in 64 polls.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code,
-                                          unsigned sleep_ns = 0) {
+                                          unsigned sleep_ns = 0, unsigned long long limit_ns = ILL_WAIT_NS) {
   if (mbar_try_wait(bar, parity, 0)) return true;
   unsigned long long t0 = 0;
   for (unsigned it = 1;; ++it) {
@@ -73,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
     if ((it & 63u) == 0) {
       const unsigned long long now = global_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > ILL_WAIT_NS) break;
+      else if (now - t0 > limit_ns) break;
     }
   }
   if (status) atomicCAS(status, 0u, code);

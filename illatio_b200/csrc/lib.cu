@@ -3,6 +3,8 @@
 #include "formats.cuh"
 #include "host.h"
 
+#include <stdlib.h>
+
 namespace ill {
 
 // Written by a kernel that gave up a bounded wait (first code wins).
@@ -25,8 +27,13 @@ unsigned int* device_status_word() {
   return p;
 }
 
-static int g_pdl = 1;
-bool pdl_enabled() { return g_pdl != 0; }
+// Programmatic dependent launch is on unless the environment says ILL_PDL=0 when the library is
+// loaded; it cannot be changed afterwards (the library keeps no mutable process-wide state).
+static const bool g_pdl = [] {
+  const char* v = getenv("ILL_PDL");
+  return !(v && v[0] == '0');
+}();
+bool pdl_enabled() { return g_pdl; }
 
 int launch_kernel(const void* fn, dim3 grid, dim3 block, size_t smem, void** args, cudaStream_t st) {
   cudaLaunchConfig_t cfg = {};
@@ -43,14 +50,27 @@ int launch_kernel(const void* fn, dim3 grid, dim3 block, size_t smem, void** arg
   return e == cudaSuccess ? ILL_OK : cuda_fail(e);
 }
 
+// A wait that is meant to run out: one warp waits LIMIT_NS for a phase of an mbarrier nobody arrives at, through
+// the same bounded wait every kernel of the library uses.  It records ST_TEST_WAIT and returns.
+__global__ void __launch_bounds__(32) test_wait_kernel(unsigned long long limit_ns, unsigned int* status, unsigned int* gave_up) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+  __syncwarp();
+  const bool ok = mbar_wait(&bar, 0u, status, ST_TEST_WAIT, 0, limit_ns);
+  if (threadIdx.x == 0 && gave_up) *gave_up = ok ? 0u : 1u;
+}
+
 }  // namespace ill
 
 using namespace ill;
 
-extern "C" int ill_set_pdl(int on) {
-  const int prev = g_pdl;
-  g_pdl = on ? 1 : 0;
-  return prev;
+extern "C" int ill_test_wait_timeout(int64_t limit_ns, ill_dptr gave_up, ill_stream stream) {
+  if (limit_ns < 1000 || limit_ns > 100000000ll || (gave_up & 3)) return ILL_ERR_ARG;  // 1 us .. 100 ms
+  unsigned long long lim = (unsigned long long)limit_ns;
+  unsigned int* st = device_status_word();
+  unsigned int* gu = (unsigned int*)(uintptr_t)gave_up;
+  void* args[] = {&lim, &st, &gu};
+  return launch_kernel((const void*)test_wait_kernel, dim3(1), dim3(32), 0, args, (cudaStream_t)stream);
 }
 
 extern "C" int ill_b200_version(void) { return 100; }

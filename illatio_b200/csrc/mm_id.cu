@@ -387,6 +387,9 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     const int m_in = mt - tile_first[lo];
     row0 = (int)p.bases[lo] + m_in * MM_BM;
     nvalid = min(MM_BM, (int)p.counts[lo] - m_in * MM_BM);
+    // counts / bases come from the caller: a tile never reaches past the TOTAL_ROWS rows X and Y have
+    if ((long long)row0 >= p.total_rows) { row0 = 0; nvalid = 0; }
+    else nvalid = min(nvalid, (int)(p.total_rows - row0));
   };
 
   if (warp < 2 + MM_LD_WARPS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(MM_REGS_AUX));
@@ -843,53 +846,64 @@ __global__ void __launch_bounds__(128) ep_pack_cap_kernel(int cols, long long ro
   }
 }
 
-// The receiving rank's plan, on the device, for exchanges of a fixed size: RC[s * per + e] = rows source s sent
-// for local expert e; they sit at slots s * cap + (rows of s's earlier experts) ...  Fills COUNTS / BASES of the
-// local experts (what ill_moe_mm_id reads), P2R[place] = slot of the row placed there (expert by expert, source
-// after source), R2P its inverse on the slots in use, P2R of the places past the last row = 0 (a row that exists,
-// so that element-wise steps over all CAP * WORLD places read valid memory), and TOTAL[0] = rows in all.  One CTA.
+// The receiving rank's plan, on the device, for exchanges of a fixed size: RC[s * per + e] = rows source s counted
+// for local expert e.  The sender keeps, per destination, only the first CAP rows of its expert order, so of
+// those RC rows the ones that arrived are GOT = min(RC, max(0, cap - rows of s's earlier experts)), at slots
+// s * cap + (rows of s's earlier experts) ...  Everything below is built from GOT, never from RC, so that the rows
+// planned are at most WORLD * CAP whatever the counts say: COUNTS / BASES of the local experts (what ill_moe_mm_id
+// reads), P2R[place] = slot of the row placed there (expert by expert, source after source), R2P its inverse on the
+// slots in use, P2R of the places past the last row = 0 (a row that exists, so that element-wise steps over all
+// CAP * WORLD places read valid memory), TOTAL[0] = rows in all, and *OVERFLOW |= 1 when some source's rows were
+// cut (its own flag is up too: that chunk's result is void).  One CTA.
 __global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, int cap, int rank, const unsigned* __restrict__ rc,
                                                           unsigned* __restrict__ counts, unsigned* __restrict__ bases,
                                                           unsigned* __restrict__ p2r, unsigned* __restrict__ r2p,
-                                                          unsigned* __restrict__ pdst, unsigned* __restrict__ total) {
+                                                          unsigned* __restrict__ pdst, unsigned* __restrict__ total,
+                                                          unsigned* __restrict__ overflow) {
   extern __shared__ unsigned plan_s[];
-  unsigned* in_src = plan_s;                 // [world][per] rows of the source's earlier experts
-  unsigned* before = plan_s + world * per;   // [world][per] rows of the expert from earlier sources
-  unsigned* lb = before + world * per;       // [per + 1] first place of each local expert; the total
+  unsigned* in_src = plan_s;                 // [world][per] rows of the source's earlier experts (as counted)
+  unsigned* before = plan_s + world * per;   // [world][per] rows of the expert that arrived from earlier sources
+  unsigned* got = before + world * per;      // [world][per] rows of the segment that arrived
+  unsigned* lb = got + world * per;          // [per + 1] first place of each local expert; the total
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x;
   for (int s = tid; s < world; s += blockDim.x) {
     unsigned a = 0;
-    for (int e = 0; e < per; ++e) { in_src[s * per + e] = a; a += rc[s * per + e]; }
+    bool cut = false;
+    for (int e = 0; e < per; ++e) {
+      const unsigned n = rc[s * per + e];
+      const unsigned room = a < (unsigned)cap ? (unsigned)cap - a : 0u;
+      in_src[s * per + e] = a;
+      got[s * per + e] = n < room ? n : room;
+      cut |= n > room;
+      a = a + n < a ? 0xffffffffu : a + n;   // saturate: counts are the caller's, not trusted
+    }
+    if (cut && overflow) atomicOr(overflow, 1u);
   }
+  __syncthreads();
   for (int e = tid; e < per; e += blockDim.x) {
     unsigned a = 0;
-    for (int s = 0; s < world; ++s) { before[s * per + e] = a; a += rc[s * per + e]; }
+    for (int s = 0; s < world; ++s) { before[s * per + e] = a; a += got[s * per + e]; }
     counts[e] = a;
   }
   __syncthreads();
   if (tid == 0) {
     unsigned a = 0;
     for (int e = 0; e < per; ++e) { lb[e] = a; bases[e] = a; a += counts[e]; }
-    lb[per] = a;
+    lb[per] = a;                             // <= world * cap: every source contributes at most cap rows
     total[0] = a;
   }
   __syncthreads();
   const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
   for (int seg = warp; seg < world * per; seg += nw) {
     const int s = seg / per, e = seg - s * per;
-    const unsigned n = rc[seg], a0 = (unsigned)s * cap + in_src[seg], p0 = lb[e] + before[seg];
-    for (unsigned i = lane; i < n; i += 32) {
-      if (in_src[seg] + i < (unsigned)cap) {
-        p2r[p0 + i] = a0 + i;
-        r2p[a0 + i] = p0 + i;
-        // where the row's result goes: rank s, row (this rank's slab there) * cap + its index in the slab
-        if (pdst) pdst[p0 + i] = ((unsigned)s << 24) | ((unsigned)rank * cap + in_src[seg] + i);
-      } else {
-        p2r[p0 + i] = 0;  // the sender dropped it (and raised its overflow flag)
-        if (pdst) pdst[p0 + i] = ((unsigned)s << 24) | ((unsigned)rank * cap);
-      }
+    const unsigned n = got[seg], a0 = (unsigned)s * cap + in_src[seg], p0 = lb[e] + before[seg];
+    for (unsigned i = lane; i < n; i += 32) {  // in_src + i < cap for every i < got
+      p2r[p0 + i] = a0 + i;
+      r2p[a0 + i] = p0 + i;
+      // where the row's result goes: rank s, row (this rank's slab there) * cap + its index in the slab
+      if (pdst) pdst[p0 + i] = ((unsigned)s << 24) | ((unsigned)rank * cap + in_src[seg] + i);
     }
   }
   for (unsigned p = lb[per] + tid; p < (unsigned)(world * cap); p += blockDim.x) {
@@ -1016,11 +1030,11 @@ extern "C" int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, 
 }
 
 extern "C" int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
-                               ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_stream stream) {
+                               ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_stream stream) {
   if (world < 1 || world > 255 || per < 1 || cap < 1 || (long long)world * cap > 0xffffff || rank < 0 || rank >= world ||
       (long long)world * per > 8192 || !rc || !counts || !bases || !p2r || !r2p || !total)
     return ILL_ERR_ARG;
-  if ((rc & 3) || (counts & 3) || (bases & 3) || (p2r & 3) || (r2p & 3) || (pdst & 3) || (total & 3)) return ILL_ERR_ALIGN;
+  if ((rc & 3) || (counts & 3) || (bases & 3) || (p2r & 3) || (r2p & 3) || (pdst & 3) || (total & 3) || (overflow & 3)) return ILL_ERR_ALIGN;
   const unsigned* rp = (const unsigned*)(uintptr_t)rc;
   unsigned* cp = (unsigned*)(uintptr_t)counts;
   unsigned* bp = (unsigned*)(uintptr_t)bases;
@@ -1028,8 +1042,9 @@ extern "C" int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr r
   unsigned* ip = (unsigned*)(uintptr_t)r2p;
   unsigned* tp = (unsigned*)(uintptr_t)total;
   unsigned* dp = (unsigned*)(uintptr_t)pdst;
-  void* args[] = {&world, &per, &cap, &rank, &rp, &cp, &bp, &pp, &ip, &dp, &tp};
-  const size_t smem = ((size_t)2 * world * per + per + 1) * 4;
+  unsigned* ov = (unsigned*)(uintptr_t)overflow;
+  void* args[] = {&world, &per, &cap, &rank, &rp, &cp, &bp, &pp, &ip, &dp, &tp, &ov};
+  const size_t smem = ((size_t)3 * world * per + per + 1) * 4;
   const void* k = (const void*)ep_plan_dev_kernel;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

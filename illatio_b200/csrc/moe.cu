@@ -126,9 +126,10 @@ __global__ void __launch_bounds__(128) route_kernel(int ne, int nu, int mode, fl
 constexpr int GROUP_BLOCK = 1024;
 
 // pass 1: per block, each expert's count; each row's rank inside its block
+// An expert number >= NE (the caller's SEL is not trusted) is left out of every count and recorded in the status word.
 __global__ void __launch_bounds__(GROUP_BLOCK) group_count_kernel(long long rows, int ne, const unsigned* __restrict__ sel,
                                                                   unsigned* __restrict__ block_counts,
-                                                                  unsigned* __restrict__ rank) {
+                                                                  unsigned* __restrict__ rank, unsigned* __restrict__ status) {
   extern __shared__ unsigned gsm[];  // ne counters, then 32 * ne per-warp counters
   pdl_launch_dependents();
   pdl_wait();
@@ -137,8 +138,13 @@ __global__ void __launch_bounds__(GROUP_BLOCK) group_count_kernel(long long rows
   for (int i = tid; i < 32 * ne; i += GROUP_BLOCK) warp_counts[i] = 0;
   __syncthreads();
   const long long row = (long long)blockIdx.x * GROUP_BLOCK + tid;
-  const bool valid = row < rows;
-  const unsigned e = valid ? sel[row] : 0xffffffffu;
+  bool valid = row < rows;
+  unsigned e = valid ? sel[row] : 0xffffffffu;
+  if (valid && e >= (unsigned)ne) {
+    if (status) atomicCAS(status, 0u, (unsigned)ST_GROUP_SEL);
+    valid = false;
+    e = 0xffffffffu;
+  }
   // rank within the warp: lanes below with the same expert
   const unsigned same = __match_any_sync(0xffffffffu, e);
   const unsigned below = same & ((1u << lane) - 1u);
@@ -195,6 +201,7 @@ __global__ void __launch_bounds__(256) group_scatter_kernel(long long rows, int 
   const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
   const unsigned e = sel[row];
+  if (e >= (unsigned)ne) { smap[row] = 0; return; }  // not an expert (flagged by the counting pass): the row has no place
   const unsigned place = bases[e] + block_counts[(row / GROUP_BLOCK) * ne + e] + rank[row];
   rmap[place] = (unsigned)(row / nu);
   smap[row] = place;
@@ -406,7 +413,8 @@ extern "C" int ill_moe_group(int64_t rows, int ne, int nu, ill_dptr sel, ill_dpt
     if (e != cudaSuccess) return cuda_fail(e);
   }
   {
-    void* args[] = {&nrows, &ne, &selp, &block_counts, &rank};
+    unsigned* stw = device_status_word();
+    void* args[] = {&nrows, &ne, &selp, &block_counts, &rank, &stw};
     int rc = launch_kernel((const void*)group_count_kernel, dim3(nblocks), dim3(GROUP_BLOCK), smem, args, st);
     if (rc) return rc;
   }
@@ -480,7 +488,8 @@ extern "C" int ill_moe_group_static(int64_t rows, int ne, int nu, ill_dptr sel, 
     if (e != cudaSuccess) return cuda_fail(e);
   }
   {
-    void* args[] = {&nrows, &ne, &selp, &block_counts, &rank};
+    unsigned* stw = device_status_word();
+    void* args[] = {&nrows, &ne, &selp, &block_counts, &rank, &stw};
     rc = launch_kernel((const void*)group_count_kernel, dim3(nblocks), dim3(GROUP_BLOCK), smem, args, st);
     if (rc) return rc;
   }

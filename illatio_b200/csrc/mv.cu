@@ -1,14 +1,15 @@
 // mv.cu -- dequant-fused quantized matrix x vector products (decode path).
 //
-// HBM-bound: one pass over the raw GGUF bytes.  A persistent grid walks the
-// matrix in tiles of whole rows.  Thread 0 of each CTA streams tiles into a ring
-// of shared-memory stages with 1-D bulk asynchronous copies (cp.async.bulk,
-// completion counted on an mbarrier per stage); all threads then unpack the
-// blocks from shared memory, take exact integer dots against the quantized
-// activations (also staged in shared memory) with dp4a, scale in fp32 and
-// reduce across the lanes that share a row with shuffles.  A copy covers the
-// 16-byte aligned superset of the tile's byte range, so rows of any byte length
-// and base alignment are read where they lie (no repacking or padding).
+// HBM-bound: one pass over the raw GGUF bytes.  One token (mvw_kernel): every warp
+// streams its own tiles of whole rows through its own ring of shared-memory stages
+// with 1-D bulk asynchronous copies (cp.async.bulk, completion counted on an
+// mbarrier per stage; no CTA-wide barrier in the loop), the lanes that share a row
+// keep that row's activations in registers, unpack the blocks from shared memory,
+// take exact integer dots with dp4a, scale in fp32 and meet with shuffles.  Several
+// tokens (mvn_kernel): a CTA-wide ring, the activations in shared memory, each
+// weight read once.  A copy covers the 16-byte aligned superset of the tile's byte
+// range, so rows of any byte length and base alignment are read where they lie (no
+// repacking or padding).
 //
 // Replaces mv_q8 / mv_q8_3 / mv_q8_glu (src/cuda/dense.cu:194-250), mv_k /
 // mv_k_glu (src/cuda/kquant.cu:169-193), d4_mvq8 / d4_mvq8n (src/cuda/ds4f.cu:
@@ -346,9 +347,11 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
 
   // the warp's stages in order: (group, g) for i = 0, 1, ...
   int i_grp = first, i_g = 0;  // next stage to issue
+  int n_issued = 0, n_done = 0;  // stages issued (lane 0 counts) and consumed by this warp
   auto issue_next = [&](int s) {
     if (i_grp < ngroups) {
       issue(i_grp, i_g, s);
+      ++n_issued;
       if (++i_g == G) { i_g = 0; i_grp += step; }
     }
   };
@@ -445,6 +448,7 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
       }
       __syncwarp();  // every lane is done with the stage
       if (lane == 0) issue_next(s);
+      ++n_done;
       if (++s == p.nstages) { s = 0; parity ^= 1u; }
     }
     if constexpr (GLU || XS) {
@@ -479,6 +483,13 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
       }
     }
   }
+  if (dead) {
+    // copies issued after the one that never landed may still be in flight into this warp's stages: give each a
+    // bounded time to land before the CTA's shared memory is released
+    const int issued = __shfl_sync(0xffffffffu, n_issued, 0);
+    for (int k = n_done + 1; k < issued; ++k)
+      mbar_wait(&full[k % p.nstages], (uint32_t)(k / p.nstages) & 1u, nullptr, 0);
+  }
 }
 
 // ---- host side ----------------------------------------------------------------
@@ -495,15 +506,18 @@ static unsigned int* status_ptr() {
   return cached;
 }
 
-static int g_sm_count = 0;
+// SMs of the current device (looked up once per device and thread).
 static int sm_count() {
-  if (!g_sm_count) {
-    int dev = 0, n = 148;
-    cudaGetDevice(&dev);
+  static thread_local int cached_dev = -1, cached = 148;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != cached_dev) {
+    int n = 148;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    g_sm_count = n;
+    cached = n;
+    cached_dev = dev;
   }
-  return g_sm_count;
+  return cached;
 }
 
 static uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
@@ -528,9 +542,14 @@ static long long tile_target(long long total_bytes, uint32_t cap) {
   return t;
 }
 
-// Tuning overrides for experiments (ill_set_tuning): lanes a row, rows a warp
-// tile, stages, CTAs per SM.  0 = planned.
+// Overrides of the plan for sweeps: lanes a row, rows a warp tile, stages, CTAs per SM (0 = planned).  They
+// exist only in builds made with -DILL_TUNING (an entry point ill_set_tuning sets them); the shipped library has
+// no mutable plan state.
+#ifdef ILL_TUNING
 static int g_env_L = 0, g_env_TR = 0, g_env_NST = 0, g_env_CTAS = 0, g_env_XS = 0;
+#else
+constexpr int g_env_L = 0, g_env_TR = 0, g_env_NST = 0, g_env_CTAS = 0, g_env_XS = 0;
+#endif
 
 // One-token plan.  Whole rows: L lanes a row and UPT units a lane in registers,
 // chosen for the fewest idle lanes; a warp's stage holds (32/L) * k rows, about
@@ -813,7 +832,8 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
 
 using namespace ill;
 
-extern "C" int ill_set_tuning(int lanes, int tile_rows, int stages, int ctas_per_sm) {
+#ifdef ILL_TUNING
+extern "C" __attribute__((visibility("default"))) int ill_set_tuning(int lanes, int tile_rows, int stages, int ctas_per_sm) {
   g_env_XS = 0;
   if (lanes == 1) { g_env_XS = 1; lanes = 0; }  // 1: stage rows in column chunks whatever their length
   if (lanes && lanes != 8 && lanes != 16 && lanes != 32) return ILL_ERR_ARG;
@@ -824,6 +844,7 @@ extern "C" int ill_set_tuning(int lanes, int tile_rows, int stages, int ctas_per
   g_env_CTAS = ctas_per_sm;
   return ILL_OK;
 }
+#endif
 
 extern "C" int ill_mv(int fmt, ill_dptr w, int rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y,
                       ill_dptr bias, int acc, int n, ill_stream stream) {

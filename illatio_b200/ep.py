@@ -431,7 +431,7 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
         if world > 1:
             dist.all_to_all_single(sc.r_rows, sc.s_rows, group=group)
     call("ill_ep_plan_dev", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
-         ptr(sc.pdst), ptr(sc.total), st)
+         ptr(sc.pdst), ptr(sc.total), ptr(sc.overflow), st)
     # the element-wise steps stop at the rows in use (sc.total, written by the plan), not at the slabs' capacity
     call("ill_ep_unpack", tot, d, ptr(sc.r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), ptr(sc.total),
          st)

@@ -79,20 +79,20 @@ ILL_API int ill_block_weights(int fmt);
  * src/cuda.lisp:41-49.) */
 ILL_API int ill_device_status(unsigned int* out, ill_stream stream);
 
-/* Programmatic dependent launch: when ON (the default), each kernel is launched
- * so that it may start streaming its weights while the previous kernel of the
- * stream drains; it still waits for that kernel's results before it reads its
- * activations or writes.  OFF launches plainly.  Returns the previous setting.
- * (No counterpart in the reference, which launches with cuLaunchKernel,
- * src/cuda.lisp:345-350.) */
-ILL_API int ill_set_pdl(int on);
+/* Exercises the library's bounded wait: a one-warp kernel waits LIMIT_NS
+ * nanoseconds (1000 .. 100000000) for an mbarrier phase that never completes, gives
+ * up, records a code in the status word (ill_device_status then returns
+ * ILL_ERR_DEVICE_WAIT) and writes 1 to *GAVE_UP (a uint32 on the device; may be 0).
+ * The device and the context stay usable.  For tests of the failure path; no
+ * counterpart in the reference, which has no device-side waits. */
+ILL_API int ill_test_wait_timeout(int64_t limit_ns, ill_dptr gave_up, ill_stream stream);
 
-/* Overrides the one-token product's launch plan, for tuning experiments: lanes
- * that share a row (8, 16 or 32; 1 = stage rows in column chunks), rows per warp tile, pipeline stages, CTAs per
- * SM.  0 leaves a value to the planner; (0,0,0,0) restores the defaults.  Not
- * for production use.  (No counterpart in the reference, whose launch shapes
- * are fixed at each Lisp call site.) */
-ILL_API int ill_set_tuning(int lanes, int tile_rows, int stages, int ctas_per_sm);
+/* Launches use programmatic dependent launch: a kernel may start streaming its
+ * weights while the previous kernel of the stream drains; it still waits for that
+ * kernel's results before it reads its activations or writes.  Setting ILL_PDL=0 in
+ * the environment before the library is loaded makes every launch a plain one; there
+ * is no run-time switch (the library keeps no mutable process-wide state).  (The
+ * reference launches with cuLaunchKernel, src/cuda.lisp:345-350.) */
 
 /* ---- activations ----------------------------------------------------------- */
 
@@ -309,7 +309,10 @@ ILL_API int ill_ep_unpack(int64_t rows, int cols, ill_dptr packed, ill_dptr map,
  * into the local experts' COUNTS / BASES, the two row orders (P2R over all
  * world*cap places, those past the last row pointing at slot 0), TOTAL[0], and
  * with PDST given where each place's result goes (for ill_moe_mm_id_peers), on
- * the device.  No counterpart in the reference. */
+ * the device.  Only the rows a sender kept are planned (a source's first CAP in
+ * its expert order), so the plan never names more than world*cap rows whatever RC
+ * holds; when some were cut, *OVERFLOW (may be 0) is or-ed with 1.  No counterpart
+ * in the reference. */
 ILL_API int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr w, ill_dptr map,
                             ill_dptr bases, int per, int world, int cap, ill_dptr packed, ill_dptr pslot, ill_dptr overflow,
                             ill_dptr peers, int rank, ill_stream stream);
@@ -323,7 +326,7 @@ ILL_API int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs, il
 ILL_API int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill_dptr peers, ill_dptr overflow,
                               ill_stream stream);
 ILL_API int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
-                            ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_stream stream);
+                            ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_stream stream);
 
 /* Two matrices of every expert against the same rows in one launch (gate and up:
  * W_e at PTRS[e] + ADD into Y, at PTRS[e] + ADD2 into Y2; no YMAP).  The same

@@ -107,6 +107,23 @@ for peer in (False, True):  # the combine as an all-to-all, and fused into the d
         fast.append(moe.clone())
         assert flag.item() == 0
 ok = torch.equal(got, want[lo:hi]) and all(torch.equal(f, want[lo:hi]) for f in fast) and D.device_status() == 0
+# slabs too small: every token routed to rank 0's experts, so rank 0 is sent more rows than a slab holds.  The
+# flags go up, the plan names only the rows that were kept, canary rows after the buffers stay untouched.
+skew = logits[lo:hi].clone()
+skew[:, :per] += 100.0
+for peer in (False, True):
+    osc = EP.EpCapScratch(mine, hi - lo, cfg["nu"], cfg["ne"], world, cap=64, peer=peer)
+    bigs = {}
+    for name in ("p2r", "pdst", "g", "u", "down"):
+        t = getattr(osc, name)
+        big = torch.full((t.shape[0] + 8,) + tuple(t.shape[1:]), -7, dtype=t.dtype, device=t.device)
+        bigs[name] = big
+        setattr(osc, name, big[:t.shape[0]])
+    _, flag = EP.chunk_capacity(ce, osc, norms[lo:hi].contiguous(), skew, cfg["ne"])
+    torch.cuda.synchronize()
+    dist.barrier()
+    ok = ok and flag.item() == 1 and osc.total.item() <= world * 64 and osc.lcounts.sum().item() == osc.total.item()
+    ok = ok and all((b[-8:] == -7).all().item() for b in bigs.values()) and D.device_status() == 0
 if not ok:
     print("rank", rank, "max abs difference", (got - want[lo:hi]).abs().max().item(), file=sys.stderr)
 flag = torch.tensor([1 if ok else 0], device="cuda")

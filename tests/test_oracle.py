@@ -100,6 +100,30 @@ def test_quantize_q8_0(oracle):
     assert list(q[:5]) == [127, 0, 2, 2, -2]
 
 
+def test_quantize_q8_0_pinned_by_gguf_py(oracle):
+    """QUANTIZE-Q8! with the fp16-rounded scale against gguf-py's Q8_0 `quantize` (the same ggml routine the
+    reference's quantizer restates, src/tensor.lisp:245-262): identical fp16 scales, and identical quants
+    except on exact .5 ties, which ggml rounds away from zero and the reference to even."""
+    gguf = pytest.importorskip("gguf")
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal(32 * 4000) * rng.uniform(1e-3, 50.0, 32 * 4000)).astype(np.float32)
+    x[:32] = 0.0
+    x[32:64] = np.arange(32, dtype=np.float32) * 0.5 - 8.0  # a block full of exact ties (amax 8 -> id 15.875)
+    blk = gguf.quants.quantize(x.reshape(-1, 32), gguf.GGMLQuantizationType.Q8_0).reshape(-1, 34)
+    q, s = oracle.quantize_q8_0(x, f16_scale=True)
+    want_d = blk[:, :2].copy().view(np.float16).astype(np.float32).reshape(-1)
+    assert np.array_equal(s.view(np.uint32), want_d.view(np.uint32))
+    want_q = blk[:, 2:].copy().view(np.int8).reshape(-1)
+    d = np.abs(x.reshape(-1, 32)).max(1, keepdims=True) / np.float32(127)
+    with np.errstate(divide="ignore"):
+        inv = np.where(d == 0, np.float32(0), np.float32(1) / d).astype(np.float32)
+    scaled = (x.reshape(-1, 32) * inv).reshape(-1)
+    tie = np.abs(scaled - np.trunc(scaled)) == 0.5
+    assert np.array_equal(q[~tie], want_q[~tie])
+    assert tie.sum() < 64 and (np.abs(q[tie].astype(np.int32) - want_q[tie]) <= 1).all()
+    assert (q[tie] % 2 == 0).all()  # the reference's ties go to even
+
+
 def test_quantize_q8k(oracle):
     rng = np.random.default_rng(6)
     x = rng.standard_normal(256 * 8).astype(np.float32)

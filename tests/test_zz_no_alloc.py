@@ -49,6 +49,33 @@ def test_static_grouping_matches_on_two_calls_in_a_row(cuda_lib):
     assert D.device_status() == 0
 
 
+def test_static_grouping_leaves_device_memory_as_it_found_it(cuda_lib):
+    """The property in the entry point's name: the device's free memory is the same after the calls as
+    before them.  One call comes first, so that the driver's lazy loading of the kernels (which is not
+    an allocation of the entry point's) is over before the figure is taken; the inputs and outputs are
+    allocated before it too."""
+    assert torch.cuda.is_available()
+    n, ne, nu = 3000, 256, 6
+    rng = np.random.default_rng(3)
+    sel = torch.as_tensor(np.stack([rng.choice(ne, size=nu, replace=False) for _ in range(n)]).astype(np.int32)).cuda()
+    w = torch.rand(n, nu, device="cuda")
+    rows = n * nu
+    i32 = dict(dtype=torch.int32, device="cuda")
+    counts, bases, rmap, smap = (torch.empty(k, **i32) for k in (ne, ne, rows, rows))
+    wrow = torch.empty(rows, device="cuda")
+    args = (rows, ne, nu, sel.data_ptr(), w.data_ptr(), counts.data_ptr(), bases.data_ptr(), rmap.data_ptr(), smap.data_ptr(),
+            wrow.data_ptr(), None)
+    _lib.call("ill_moe_group_static", *args)
+    torch.cuda.synchronize()
+    free0, total0 = torch.cuda.mem_get_info()
+    for _ in range(2):
+        _lib.call("ill_moe_group_static", *args)
+    torch.cuda.synchronize()
+    free1, total1 = torch.cuda.mem_get_info()
+    assert (free1, total1) == (free0, total0)
+    assert counts.sum().item() == rows
+
+
 def test_static_grouping_rejects_sizes_beyond_its_array(cuda_lib):
     assert torch.cuda.is_available()
     z = torch.zeros(8, dtype=torch.int32, device="cuda")
