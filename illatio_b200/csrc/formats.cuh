@@ -12,7 +12,9 @@
 // Integer dots are exact (dp4a); the float steps per unit follow the reference
 // CPU kernels' formulas (src/tensor.lisp:321-336, src/kquant.lisp:171-236,
 // src/iquant.lisp:126-215), so results differ from them only by the order in
-// which fp32 partial sums are added.
+// which fp32 partial sums are added.  Every float step is written with the
+// rounding intrinsics (no multiply-add contraction), so that a unit's value is
+// the same bits in every kernel that includes this file.
 //
 // Weights are read from a shared-memory copy of the raw row bytes at any byte
 // alignment; activations from a shared-memory copy laid out by x_layout().
@@ -134,7 +136,7 @@ __device__ __forceinline__ float dot(const WReg<ILL_Q8_0>& w, const XReg<ILL_Q8_
     a0 = __dp4a((int)w.q[i], (int)x.q[i], a0);
     a1 = __dp4a((int)w.q[4 + i], (int)x.q[4 + i], a1);
   }
-  return (float)(a0 + a1) * (w.d * x.s);
+  return __fmul_rn((float)(a0 + a1), __fmul_rn(w.d, x.s));
 }
 
 // ---- Q4_K: unit = 64 weights (groups 2k and 2k+1 of a super-block) ------------
@@ -184,7 +186,7 @@ __device__ __forceinline__ float dot(const WReg<ILL_Q4_K>& w, const XReg<ILL_Q4_
   }
   const int isum = lo * (int)(w.sc & 0xff) + (hi >> 4) * (int)(w.sc >> 8);
   const int imin = dp2a_lo(x.bsp, (int)w.mn, 0);
-  return (x.d * w.d) * (float)isum - (x.d * w.dmin) * (float)imin;
+  return __fsub_rn(__fmul_rn(__fmul_rn(x.d, w.d), (float)isum), __fmul_rn(__fmul_rn(x.d, w.dmin), (float)imin));
 }
 
 // ---- Q6_K: unit = half c, 16-weight column hq of each 32: four groups of 16 ------
@@ -242,7 +244,7 @@ __device__ __forceinline__ float dot(const WReg<ILL_Q6_K>& w, const XReg<ILL_Q6_
     for (int j = 0; j < 4; ++j) d = __dp4a((int)w.q[4 * g + j], (int)x.q[4 * g + j], d);
     isum += w.sc[g] * d;
   }
-  return (w.d * x.d) * (float)isum;
+  return __fmul_rn(__fmul_rn(w.d, x.d), (float)isum);
 }
 
 // ---- Q2_K: unit = half h, 16-byte half: four groups of 16 ---------------------
@@ -292,7 +294,7 @@ __device__ __forceinline__ float dot(const WReg<ILL_Q2_K>& w, const XReg<ILL_Q2_
     isum += (int)(w.sc[k] & 15) * (d >> (2 * k));
     mins += (int)(w.sc[k] >> 4) * x.bs[k];
   }
-  return (x.d * w.d) * (float)isum - (x.d * w.dmin) * (float)mins;
+  return __fsub_rn(__fmul_rn(__fmul_rn(x.d, w.d), (float)isum), __fmul_rn(__fmul_rn(x.d, w.dmin), (float)mins));
 }
 
 // ---- IQ2_XXS: unit = sub-block of 32 -------------------------------------------
@@ -329,7 +331,7 @@ __device__ __forceinline__ float dot(const WReg<ILL_IQ2_XXS>& w, const XReg<ILL_
   int acc = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc = __dp4a((int)w.q[i], (int)x.q[i], acc);
-  return ((w.d * x.d) * ((float)acc * w.ls)) * 0.25f;
+  return __fmul_rn(__fmul_rn(__fmul_rn(w.d, x.d), __fmul_rn((float)acc, w.ls)), 0.25f);
 }
 
 // ---- activations staged in shared memory as planes ---------------------------------

@@ -28,4 +28,8 @@ int mv_common(int fmt, int mode, int nmat, const uint64_t* w, const int* rows, i
               uint64_t xsum, const uint64_t* y, const uint64_t* bias, int acc, int n, uint64_t ptrs, int nseg,
               long long add, long long up_add, int x_seg, long long y_seg, uint64_t seg_w, float clamp, void* stream);
 
+// Lanes a row and units a lane of the one-token product for rows of UNITS units (mv.cu); false when a row does
+// not fit in registers.  BIG: the launch moves 16 MB or more.
+bool mv_pick_lanes(int fmt, int units, bool glu, bool big, int* lanes, int* upt);
+
 }  // namespace ill

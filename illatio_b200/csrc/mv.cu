@@ -207,8 +207,8 @@ __global__ void __launch_bounds__(MV_THREADS) mvn_kernel(const MvParams p) {
             a.bs = (const int16_t*)(xreg + p.bs_off);
             XReg<FMT> x;
             load_x(x, a, u);
-            sum[0] += dot(w, x);
-            sum2[0] += dot(w2, x);
+            sum[0] = __fadd_rn(sum[0], dot(w, x));
+            sum2[0] = __fadd_rn(sum2[0], dot(w2, x));
           } else {
 #pragma unroll
             for (int k = 0; k < NT; ++k) {
@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(MV_THREADS) mvn_kernel(const MvParams p) {
                 a.bs = (const int16_t*)(xreg + p.bs_off) + (size_t)k * (p.cols / 16);
                 XReg<FMT> x;
                 load_x(x, a, u);
-                sum[k] += dot(w, x);
+                sum[k] = __fadd_rn(sum[k], dot(w, x));
               }
             }
           }
@@ -425,7 +425,7 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
               if constexpr (XS) load_x_planes<FMT>(x[0], xa, u);
               WReg<FMT> w;
               load_w<AL>(w, rowp, up[k], iqt);
-              sum += dot(w, x[XS ? 0 : k]);
+              sum = __fadd_rn(sum, dot(w, x[XS ? 0 : k]));
             }
           }
         }
@@ -551,19 +551,16 @@ static int g_env_L = 0, g_env_TR = 0, g_env_NST = 0, g_env_CTAS = 0, g_env_XS = 
 constexpr int g_env_L = 0, g_env_TR = 0, g_env_NST = 0, g_env_CTAS = 0, g_env_XS = 0;
 #endif
 
-// One-token plan.  Whole rows: L lanes a row and UPT units a lane in registers,
-// chosen for the fewest idle lanes; a warp's stage holds (32/L) * k rows, about
-// 3 KB.  Rows too long for that (or FORCE_XS): 32 lanes a row, the row staged in
-// column chunks of whole blocks, the activations in shared memory.
-static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu, MvPlan* pl) {
-  const int bb = fmt_block_bytes(fmt), bw = fmt_block_weights(fmt), uw = unit_weights(fmt);
-  const long long row_bytes = (long long)(cols / bw) * bb;
-  const int units = cols / uw;
+// Lanes that share a row (L) and units a lane keeps in registers (UPT) for rows of UNITS units; false when the
+// row is too long for registers.  The order in which a row's partial sums are added follows from the pair, so
+// every kernel that wants the one-token product's bits picks it here.
+bool mv_pick_lanes(int fmt, int units, bool glu, bool big, int* L_out, int* upt_out) {
+  const int uw = unit_weights(fmt);
   // Units a lane keeps in registers, at most.  More of them lets fewer lanes share a row with none idle (80 units:
   // 16 lanes x 5 instead of 32 x 3 with five lanes idle) at the price of registers, i.e. of resident warps.
   // Measured on 151936-row matrices and the 4B model's shapes: five pays for Q6_K and Q2_K rows, for the gated
-  // Q4_K product and for large Q4_K matrices, three for the rest; Q8_0's 32-wide units go up to seven, four lanes a row.
-  const bool big = total_rows * row_bytes * nseg >= (16ll << 20);  // Q4_K rows: five only pays once the launch is long
+  // Q4_K product and for large Q4_K matrices (BIG: past 16 MB), three for the rest; Q8_0's 32-wide units go up to
+  // seven, four lanes a row.
   const int upt_max = fmt == ILL_Q8_0 ? 7 : uw == 32 ? 5 : (fmt == ILL_Q4_K && !glu) ? (big ? 5 : 3) : ((fmt == ILL_Q6_K || fmt == ILL_Q2_K) && !glu) || (fmt == ILL_Q4_K && glu) ? 5 : 3;
   int bestL = 0, bestU = 0;
   double best = -1.0;
@@ -574,15 +571,31 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
     if (eff > best) { best = eff; bestL = L; bestU = upt; }
   }
   // a row too long for that many units still beats staging it in column chunks if 32 lanes x 5 units hold it
-  if (!bestL && !g_env_XS && uw == 64 && (units + 31) / 32 <= 5) { bestL = 32; bestU = (units + 31) / 32; }
-  if (g_env_L && (units + g_env_L - 1) / g_env_L <= upt_max) { bestL = g_env_L; bestU = (units + g_env_L - 1) / g_env_L; }
+  if (!bestL && uw == 64 && (units + 31) / 32 <= 5) { bestL = 32; bestU = (units + 31) / 32; }
+  *L_out = bestL;
+  *upt_out = bestU;
+  return bestL != 0;
+}
+
+// One-token plan.  Whole rows: L lanes a row and UPT units a lane in registers,
+// chosen for the fewest idle lanes; a warp's stage holds (32/L) * k rows, about
+// 3 KB.  Rows too long for that (or FORCE_XS): 32 lanes a row, the row staged in
+// column chunks of whole blocks, the activations in shared memory.
+static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu, MvPlan* pl) {
+  const int bb = fmt_block_bytes(fmt), bw = fmt_block_weights(fmt), uw = unit_weights(fmt);
+  const long long row_bytes = (long long)(cols / bw) * bb;
+  const int units = cols / uw;
+  const bool big = total_rows * row_bytes * nseg >= (16ll << 20);
+  int bestL = 0, bestU = 0;
+  if (!mv_pick_lanes(fmt, units, glu, big, &bestL, &bestU) || g_env_XS) bestL = 0;
+  if (g_env_L && (units + g_env_L - 1) / g_env_L <= 7) { bestL = g_env_L; bestU = (units + g_env_L - 1) / g_env_L; }
   pl->one = true;
   pl->xs = false;
   pl->nchunks = 1;
   pl->chunk_units = units;
   pl->chunk_bytes = (uint32_t)row_bytes;
   long long tr;
-  if (!bestL || g_env_XS) {
+  if (!bestL) {
     // blocks per chunk: a multiple that makes the chunk's units a multiple of 32, near 3 KB
     const int upb = bw / uw;                  // units per block
     int bpc = 32 / upb > 0 ? 32 / upb : 1;    // 32 units
