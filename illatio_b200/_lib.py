@@ -16,7 +16,17 @@ _I = _c.c_int
 _L = _c.c_int64
 _F = _c.c_float
 
+class DecodeOp(_c.Structure):
+    """ill_decode_op of include/illatio_b200.h."""
+    _fields_ = [("w", _P), ("w2", _P), ("x", _P), ("norm_w", _P), ("y", _P), ("bias", _P),
+                ("fmt", _c.c_int32), ("kind", _c.c_int32), ("rows", _c.c_int32), ("cols", _c.c_int32),
+                ("acc", _c.c_int32), ("after", _c.c_int32), ("f16_scale", _c.c_int32), ("eps", _c.c_float)]
+
+
 SIGNATURES = {
+    "ill_decode_plan_bytes": (_L, [_I]),
+    "ill_decode_plan": (_I, [_c.POINTER(DecodeOp), _I, _P, _L, _c.POINTER(_c.c_int32), _S]),
+    "ill_decode_run": (_I, [_P, _c.POINTER(_c.c_int32), _S]),
     "ill_b200_version": (_I, []),
     "ill_error_string": (_c.c_char_p, [_I]),
     "ill_last_cuda_error": (_I, []),

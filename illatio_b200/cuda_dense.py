@@ -172,6 +172,45 @@ def glu_mul(g, u, act, fa, n=1, fb=None):
     return fa
 
 
+OP_MV, OP_GLU = 0, 1
+
+
+def decode_op(w, x, y, w2=None, norm_w=None, eps=1e-6, bias=None, acc=False, after=True, f16_scale=True):
+    """One product of a token's chain for DecodePlan: Y (+)= W X' (+ BIAS), or Y = silu(W X') * (W2 X') when W2 is
+    given; X' = X (floats on the device) after RMSNORM! by NORM_W (when given) and the quantizer W's format takes.
+    AFTER: the product reads or adds into what an earlier one of the chain writes."""
+    import ctypes
+    op = _lib.DecodeOp()
+    op.w, op.w2, op.x, op.norm_w, op.y, op.bias = _ptr(w.qs), _ptr(w2.qs) if w2 is not None else 0, _ptr(x), _ptr(norm_w), _ptr(y), _ptr(bias)
+    op.fmt, op.kind, op.rows, op.cols = w.type, OP_GLU if w2 is not None else OP_MV, w.rows, w.cols
+    op.acc, op.after, op.f16_scale, op.eps = int(bool(acc)), int(bool(after)), int(bool(f16_scale)), float(eps)
+    if w2 is not None and (w2.type, w2.rows, w2.cols) != (w.type, w.rows, w.cols):
+        raise ValueError("a gated product's two matrices must agree in format and shape")
+    return op
+
+
+class DecodePlan:
+    """A token's chain of products run as ONE launch (ill_decode_plan / ill_decode_run): what CUDA-FORWARD-N
+    (src/cuda-dense.lisp:380-432) issues as a launch per product and per quantization.  OPS: decode_op()s in
+    order.  The plan lives in device memory this object owns; run() enqueues one token on the current stream."""
+
+    def __init__(self, ops, device="cuda"):
+        import ctypes
+        self.n = len(ops)
+        arr = (_lib.DecodeOp * self.n)(*ops)
+        nbytes = _lib.lib().ill_decode_plan_bytes(self.n)
+        if nbytes <= 0:
+            raise ValueError("a chain holds 1 to 1024 products")
+        self.plan = torch.zeros(nbytes + 128, dtype=torch.uint8, device=device)
+        self.base = (self.plan.data_ptr() + 127) // 128 * 128
+        self.launch = (ctypes.c_int32 * 8)()
+        with torch.cuda.device(self.plan.device):
+            _lib.call("ill_decode_plan", arr, self.n, self.base, nbytes, self.launch, _stream())
+
+    def run(self):
+        _lib.call("ill_decode_run", self.base, self.launch, _stream())
+
+
 def embed(emb, tokens, x):
     """EMBED (src/cuda-dense.lisp:302-307): rows TOKENS (int32 on the device) of
     EMB as floats in X."""

@@ -160,6 +160,46 @@ ILL_API int ill_mv_3(int fmt, ill_dptr w0, ill_dptr w1, ill_dptr w2, int rows0, 
 ILL_API int ill_mv_glu(int fmt, ill_dptr wg, ill_dptr wu, int rows, int cols, ill_dptr xq, ill_dptr xs,
                        ill_dptr xsum, ill_dptr y, ill_stream stream);
 
+/* ---- a decoded token's chain of products in one launch ---------------------------- */
+
+/* One product of the chain.  KIND ILL_OP_MV: Y (+)= W X' (+ BIAS), ACC != 0 adds
+ * into Y; ILL_OP_GLU: Y = silu(W X') * (W2 X') (no ACC, no BIAS).  X' is the
+ * product's activations, made from the COLS floats at X inside the launch:
+ * RMSNORM! of them by NORM_W with EPS when NORM_W is given (as ill_rmsnorm_q8),
+ * then quantized the way FMT's products take them (Q8_0 blocks for ILL_Q8_0, with
+ * the scale rounded through fp16 when F16_SCALE; Q8_K super-blocks otherwise) --
+ * bit for bit what ill_quant_q8_0 / ill_quant_q8_k / ill_rmsnorm_q8 write.  AFTER
+ * != 0: the product reads (X) or adds into (Y) what an earlier product of the list
+ * writes, so every earlier product is complete before it starts; products without
+ * it may run beside their predecessors.  W, W2 and X are 16-byte aligned. */
+#define ILL_OP_MV 0
+#define ILL_OP_GLU 1
+typedef struct ill_decode_op {
+  ill_dptr w, w2, x, norm_w, y, bias;
+  int32_t fmt, kind, rows, cols;
+  int32_t acc, after, f16_scale;
+  float eps;
+} ill_decode_op;
+
+/* A token's products in one launch, in place of a launch per product and a launch
+ * per quantization (CUDA-FORWARD-N, src/cuda-dense.lisp:380-432; the reference's
+ * own note on what its ~1,700 launches a token cost: TODO.md:16-21).
+ * ill_decode_plan turns the NOPS products at OPS (host memory) into the list the
+ * kernel walks, written to PLAN (device memory the caller owns, 128-byte aligned,
+ * ill_decode_plan_bytes(nops) bytes; it also holds the barrier the CTAs meet at),
+ * and fills LAUNCH (8 ints the caller keeps beside PLAN).  It synchronises STREAM.
+ * ill_decode_run enqueues the token: one cooperative launch of one CTA per SM.
+ * The same PLAN runs any number of tokens, one at a time (two runs of one PLAN
+ * must not overlap).  Results are the same bits ill_mv / ill_mv_glu give on the
+ * same activations.  Rows too long for a lane's registers (more than 160 units of
+ * 64 weights, 224 Q8_0 blocks) are ILL_ERR_UNSUPPORTED: use ill_mv for those.
+ * After a time-out (ILL_ERR_DEVICE_WAIT from ill_device_status) plan again before
+ * the next run: the barrier's count may be left mid-way. */
+ILL_API int64_t ill_decode_plan_bytes(int nops);
+ILL_API int ill_decode_plan(const ill_decode_op* ops, int nops, ill_dptr plan, int64_t plan_bytes, int32_t* launch,
+                            ill_stream stream);
+ILL_API int ill_decode_run(ill_dptr plan, const int32_t* launch, ill_stream stream);
+
 /* ---- routed experts: one decoded token ------------------------------------------ */
 
 /* Y[z*y_stride + r] = W_z[r] . X_z for each expert z < NZ: W_z's NROWS rows of
