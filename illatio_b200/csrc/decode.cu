@@ -8,18 +8,23 @@
 //   * The weights never depend on earlier products, so every warp streams the tiles it will
 //     multiply -- of this product and of the ones after it -- through its own ring in shared memory
 //     with bulk asynchronous copies, as far ahead as the ring has room.  HBM keeps streaming across
-//     the boundaries between products.
+//     the boundaries between products.  A tile is a few whole rows, or, for rows too long for that,
+//     one row's next run of columns (the row's sum is carried from tile to tile).
 //   * Where a product reads what an earlier one wrote (AFTER), the CTAs meet at a barrier in global
 //     memory (one arrival a CTA, a generation counter; the wait is bounded and ends in a status code).
 //   * The activation quantizer -- and the RMSNorm before it -- runs in the consumer's prologue: every
 //     CTA quantizes the vector it is about to multiply (at most 40 KB, from L2) into its own shared
 //     memory, bit for bit as ill_quant_q8_0 / ill_quant_q8_k / ill_rmsnorm_q8 do.  No quantize launches.
+//   * The quantized activations stay in shared memory (in planes, so that the lanes' 16-byte reads do
+//     not share banks) and are read from there unit by unit: no per-product preload into registers,
+//     which at one token would cost a warp as much as the one or two rows it multiplies.
 //   * A row's arithmetic is the one-token product's (mv.cu): the same lanes a row, units a lane and
-//     order of additions, so the results are the same bits as ill_mv / ill_mv_glu give.
+//     order of additions, so the results are the same bits as ill_mv / ill_mv_glu give (for rows
+//     those keep in registers).
 //
-// The ring is allocated by bytes, not by slots: a tile takes the 16-byte aligned span of its rows (a
-// gated product's tile is its gate rows and its up rows), so the bytes in flight stay near the ring's
-// size whatever the tile size, and up to DEC_NBAR tiles (an mbarrier each) are outstanding per warp.
+// The ring is allocated by bytes, not by slots: a tile takes the 16-byte aligned span of its bytes, so
+// the bytes in flight stay near the ring's size whatever the tile size, and up to DEC_NBAR tiles (an
+// mbarrier each) are outstanding per warp.
 #include "formats.cuh"
 #include "iq2xxs_tables.cuh"
 #include "quantdev.cuh"
@@ -29,13 +34,17 @@
 
 namespace ill {
 
-constexpr int DEC_THREADS = 256;
-constexpr int DEC_WARPS = DEC_THREADS / 32;
+#ifndef DEC_WARPS
+#define DEC_WARPS 11   // 352 threads: three warps a scheduler (two on one), up to 184 registers a thread
+#endif
+constexpr int DEC_THREADS = 32 * DEC_WARPS;
 constexpr int DEC_NBAR = 8;          // tiles in flight per warp, at most
 constexpr int DEC_MAX_OPS = 1024;
 constexpr int DEC_MAX_COLS = 32768;  // activations staged in shared memory: 1.25 bytes a column
 
-// One product as the kernel reads it (global memory, 128 bytes).
+// One product as the kernel reads it: global memory, copied to shared memory when the kernel starts (112 bytes).
+// Its rows are taken in groups of TR (a warp's unit of work); a group is NCH tiles for each of the product's one or
+// two matrices: whole rows (NCH = 1), or a single row in NCH runs of CU units.
 struct __align__(16) DecOp {
   const u8* w;
   const u8* w2;            // the "up" matrix of a gated product, else null
@@ -44,27 +53,21 @@ struct __align__(16) DecOp {
   const float* x;          // the activations as floats
   const float* norm_w;     // RMSNorm weights, or null
   float eps;
-  int fmt, acc, f16_scale;
   int rows, cols, row_bytes, units;
-  int lanes, upt, tr;      // lanes a row, units a lane, rows a tile
-  int tile0, ntiles;       // the product's tiles among all the list's tiles
-  int after, restage;      // meet the other CTAs first; quantize X into shared memory first
-  int pad[4];
+  int tr;                  // rows a group
+  int g0, ng;              // the product's groups among all the list's groups
+  int nch, cu, chunk_bytes;
+  u8 fmt, acc, f16_scale, lanes, kc;   // lanes a row; units a lane in a tile
+  u8 after, restage;       // meet the other CTAs first; quantize X into shared memory first
+  u8 pad[9];
 };
-static_assert(sizeof(DecOp) == 128, "DecOp is 128 bytes");
-
-// What the issuing lane needs of a product, in shared memory.
-struct DecSrc {
-  const u8* w;
-  const u8* w2;
-  int tile0, ntiles, rows, tr, row_bytes, pad;
-};
+static_assert(sizeof(DecOp) == 112, "DecOp is 112 bytes");
 
 struct DecParams {
   const DecOp* ops;
   int nops;
-  unsigned* bar;           // [0] arrivals, [1] generation
-  int total_tiles;
+  unsigned* bar;           // arrivals at the barrier between CTAs, counted up for ever
+  unsigned bar_base;       // its value when this launch began
   int ring_bytes;          // per warp
   int max_cols;            // the staged activations' capacity
   int has_iq;
@@ -72,28 +75,28 @@ struct DecParams {
 };
 
 // What every warp of the CTA shares, written once at the start (shared memory).
-struct DecShared {
-  const DecSrc* srcs;      // [nops] in shared memory
+struct __align__(16) DecShared {
+  const DecOp* ops;        // [nops] in shared memory
   unsigned* status;
-  int total_tiles, ring_bytes, gstep, pad;
-  const i8* xq;            // the staged activations
+  int nops, ring_bytes, gstep, pad;
+  const u8* xq;            // the staged activations: planes of quants, scales, planes of sums
   const float* xs;
   const int16_t* bs;
   const uint2* iq_grid;
   const uint2* iq_smask;
 };
 
-// A warp's state (shared memory): the product it is on, and its ring of tiles.  C counts the tiles consumed; the
-// fields after it belong to the issuing lane.  The ring's bytes lie elsewhere (RING of the functions below).
+// A warp's ring (shared memory).  C counts the tiles consumed; the fields after it are the issuing lane's: the next
+// tile to issue is sub-tile ISS_S of group ISS_G (of product ISS_OP).  The ring's bytes lie elsewhere.
 struct __align__(16) DecWarp {
-  DecOp op;
   uint64_t bars[DEC_NBAR];
   int offs[DEC_NBAR];      // where tile i % DEC_NBAR starts in the ring
   int c;
   int issued, head;
-  int iss_t, iss_op;
-  int pad[3];
+  int iss_g, iss_s, iss_op;
+  int pad[2];
 };
+static_assert(sizeof(DecWarp) == 128, "DecWarp is 128 bytes");
 
 // bytes of the 16-byte aligned span that covers [SRC, SRC + LEN)
 __device__ __forceinline__ uint32_t span16(const u8* src, uint32_t len) {
@@ -101,23 +104,30 @@ __device__ __forceinline__ uint32_t span16(const u8* src, uint32_t len) {
   return (uint32_t)((((uintptr_t)src + len + 15) & ~(uintptr_t)15) - a0);
 }
 
+// where sub-tile S of group G of product O lies, and how long it is
+__device__ __forceinline__ const u8* dec_tile_src(const DecOp& o, int g, int s, uint32_t& len) {
+  const long long row0 = (long long)(g - o.g0) * o.tr;
+  if (o.nch == 1) {
+    len = (uint32_t)min(o.tr, o.rows - (int)row0) * (uint32_t)o.row_bytes;
+    return (s ? o.w2 : o.w) + row0 * o.row_bytes;
+  }
+  const int part = s >= o.nch ? 1 : 0, ch = s - part * o.nch;
+  len = (uint32_t)min(o.chunk_bytes, o.row_bytes - ch * o.chunk_bytes);
+  return (part ? o.w2 : o.w) + row0 * o.row_bytes + (long long)ch * o.chunk_bytes;
+}
+
 // Lane 0: issue this warp's next tiles while a barrier and contiguous room in the ring are free.
-__device__ __forceinline__ void dec_issue(DecWarp* cw, u8* ring, const DecShared* sh) {
-  const DecSrc* srcs = sh->srcs;
-  const int total_tiles = sh->total_tiles, gstep = sh->gstep, ring_bytes = sh->ring_bytes;
-  int issued = cw->issued, head = cw->head, iss_t = cw->iss_t, iss_op = cw->iss_op;
-  const int c = cw->c;
-  while (iss_t < total_tiles && issued - c < DEC_NBAR) {
-    while (iss_t >= srcs[iss_op].tile0 + srcs[iss_op].ntiles) ++iss_op;
-    const DecSrc o = srcs[iss_op];
-    const long long row0 = (long long)(iss_t - o.tile0) * o.tr;
-    const int nrows = min(o.tr, o.rows - (int)row0);
-    const uint32_t len = (uint32_t)nrows * (uint32_t)o.row_bytes;
-    const u8* s0 = o.w + row0 * o.row_bytes;
-    const uint32_t b0 = span16(s0, len);
-    const u8* s1 = o.w2 ? o.w2 + row0 * o.row_bytes : nullptr;
-    const uint32_t b1 = s1 ? span16(s1, len) : 0u;
-    const int need = (int)(b0 + b1);
+__device__ __forceinline__ void dec_issue(DecWarp* cw, u8* ring, const DecShared* sh, int c) {
+  const DecOp* ops = sh->ops;
+  const int nops = sh->nops, gstep = sh->gstep, ring_bytes = sh->ring_bytes;
+  int issued = cw->issued, head = cw->head, g = cw->iss_g, s = cw->iss_s, io = cw->iss_op;
+  while (issued - c < DEC_NBAR) {
+    while (io < nops && g >= ops[io].g0 + ops[io].ng) ++io;
+    if (io >= nops) break;
+    const DecOp& o = ops[io];
+    uint32_t len;
+    const u8* src = dec_tile_src(o, g, s, len);
+    const int need = (int)span16(src, len);
     int off;
     if (issued == c) off = 0;  // nothing outstanding: start over at the ring's base
     else {
@@ -134,288 +144,344 @@ __device__ __forceinline__ void dec_issue(DecWarp* cw, u8* ring, const DecShared
     const int b = issued % DEC_NBAR;
     cw->offs[b] = off;
     mbar_expect_tx(&cw->bars[b], (uint32_t)need);
-    bulk_g2s(ring + off, (const void*)((uintptr_t)s0 & ~(uintptr_t)15), b0, &cw->bars[b]);
-    if (s1) bulk_g2s(ring + off + b0, (const void*)((uintptr_t)s1 & ~(uintptr_t)15), b1, &cw->bars[b]);
+    bulk_g2s(ring + off, (const void*)((uintptr_t)src & ~(uintptr_t)15), (uint32_t)need, &cw->bars[b]);
     ++issued;
     head = off + need;
-    iss_t += gstep;
+    if (++s == (o.w2 ? 2 : 1) * o.nch) { s = 0; g += gstep; }
   }
-  cw->issued = issued; cw->head = head; cw->iss_t = iss_t; cw->iss_op = iss_op;
+  cw->issued = issued; cw->head = head; cw->iss_g = g; cw->iss_s = s; cw->iss_op = io;
 }
 
-// The CTAs meet (thread 0 of each, between two __syncthreads).  False after a bounded wait.
-__device__ __forceinline__ bool dec_grid_barrier(unsigned* bar, unsigned nctas, unsigned* status) {
-  volatile unsigned* gen = bar + 1;
-  const unsigned g = *gen;  // read before arriving: the generation cannot move until this CTA has arrived
-  __threadfence();
-  const unsigned old = atomicAdd(bar, 1u);
-  if (old == nctas - 1) {
-    atomicExch(bar, 0u);
-    __threadfence();
-    atomicAdd(bar + 1, 1u);
+// The CTAs meet: thread 0 of each, between two barriers of its CTA.  Arrivals are counted up for ever; the K-th
+// meeting of a launch is complete when the count has reached BASE + K * NCTAS.  False after a bounded wait.
+__device__ __forceinline__ bool dec_grid_barrier(unsigned* bar, unsigned target, unsigned* status) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(bar) : "memory");
+  unsigned long long t0 = 0;
+  for (unsigned it = 1;; ++it) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bar) : "memory");
+    if ((int)(v - target) >= 0) return true;
+    if ((it & 1023u) == 0) {
+      const unsigned long long now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > ILL_WAIT_NS) {
+        if (status) atomicCAS(status, 0u, (unsigned)ST_BARRIER_WAIT);
+        return false;
+      }
+    }
+  }
+}
+
+// ---- the activations, quantized into planes in shared memory ---------------------------------
+// Where piece P (the token's quants 16 P .. 16 P + 15) lies in FMT's planes of U units (formats.cuh: piece j of
+// unit u at (j U + u) 16): the inverse of plane_src.
+template <int FMT>
+__device__ __forceinline__ int plane_dst(int p, int U) {
+  if constexpr (FMT == ILL_Q6_K || FMT == ILL_Q2_K) {
+    const int rem = p & 15, u = 4 * (p >> 4) + 2 * (rem >> 3) + (rem & 1), j = (rem & 7) >> 1;
+    return (j * U + u) * 16;
   } else {
-    unsigned long long t0 = 0;
-    for (unsigned it = 1; *gen == g; ++it) {
-      if ((it & 1023u) == 0) {
-        const unsigned long long now = global_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > ILL_WAIT_NS) {
-          if (status) atomicCAS(status, 0u, (unsigned)ST_BARRIER_WAIT);
-          return false;
+    constexpr int PPU = PlaneGeom<FMT>::PPU;
+    return ((p % PPU) * U + p / PPU) * 16;
+  }
+}
+
+// One Q8_K super-block B of the row (lane l holds values 8l .. 8l+7) into FMT's planes.
+template <int FMT>
+__device__ __forceinline__ void stage_block_q8k(const float (&v)[8], int lane, int b, int U, u8* xq, float* xs, int16_t* bs) {
+  int q[8];
+  float d;
+  q8k_values(v, lane, q, d);
+  uint32_t w0, w1;
+  int s = q8k_pack(q, w0, w1);
+  *(uint2*)(xq + plane_dst<FMT>(16 * b + (lane >> 1), U) + 8 * (lane & 1)) = make_uint2(w0, w1);
+  if (lane == 0) xs[b] = d;
+  s += __shfl_xor_sync(0xffffffffu, s, 1);  // the sum of 16: number m = lane / 2 of the block's sixteen
+  if constexpr (FMT == ILL_Q6_K || FMT == ILL_Q2_K) {
+    const int m = lane >> 1, u = 4 * b + 2 * (m >> 3) + (m & 1), g = (m & 7) >> 1;
+    if (!(lane & 1)) bs[g * U + u] = (int16_t)s;
+  } else if constexpr (FMT == ILL_Q4_K) {
+    // unit k of the block = its sums 4k .. 4k+3 (lanes 8k .. 8k+7), packed as two sums of 32
+    int s32 = s + __shfl_xor_sync(0xffffffffu, s, 2);
+    const int hi = __shfl_down_sync(0xffffffffu, s32, 4);
+    if (!(lane & 7)) ((int*)bs)[4 * b + (lane >> 3)] = (s32 & 0xffff) | (hi << 16);
+  }
+}
+
+// Every CTA quantizes the product's activations into its own shared memory, in the planes the product's format
+// reads (all threads; ends with a __syncthreads).  The arithmetic is rmsnorm_q8_kernel's and the quantizer
+// kernels' (quant.cu, quantdev.cuh), the sum of squares in the order quantdev.cuh fixes.  X is read around L1
+// (ld.cg): an earlier product of this same launch may have written it.  The loads of all the blocks a warp handles
+// are issued before any is used (the vector comes from L2: one latency, not one per block); rows longer than HOLD
+// blocks a warp take them in rounds.
+constexpr int DEC_HOLD8 = 4;    // 256-wide groups a warp keeps in registers at a time (32 values a lane)
+constexpr int DEC_HOLD0 = 16;   // Q8_0 blocks a warp keeps at a time (16 values a lane)
+
+template <int FMT>
+__device__ __noinline__ void dec_stage_fmt(const DecOp& op, u8* xq, float* xs, int16_t* bs, double* group_s) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* x = op.x;
+  const float* nw = op.norm_w;
+  const int d = op.cols, ng = (d + 255) / 256, U = op.units;
+  constexpr bool k8 = FMT != ILL_Q8_0;
+  float sc = 1.0f;
+  // Q8_K rows of up to HOLD8 groups a warp: the values loaded for the sum of squares are the ones quantized
+  const bool held = k8 && ng <= DEC_HOLD8 * DEC_WARPS;
+  float v[DEC_HOLD8][8];
+  if (nw || held) {
+    for (int g0 = 0; g0 < ng; g0 += DEC_HOLD8 * DEC_WARPS) {
+#pragma unroll
+      for (int j = 0; j < DEC_HOLD8; ++j) {
+        const int g = g0 + warp + j * DEC_WARPS;
+        if (g < ng) rms_load8<true>(x, d, g * 256 + 8 * lane, v[j]);
+      }
+      if (nw) {
+#pragma unroll
+        for (int j = 0; j < DEC_HOLD8; ++j) {
+          const int g = g0 + warp + j * DEC_WARPS;
+          if (g < ng) {
+            const double s = rms_group_sum(v[j]);
+            if (lane == 0) group_s[g] = s;
+          }
         }
       }
     }
   }
-  __threadfence();
-  return true;
-}
-
-// Every CTA quantizes the product's activations into its own shared memory (all threads; ends with a
-// __syncthreads).  The arithmetic and its order are rmsnorm_q8_kernel's and the quantizer kernels' (quant.cu).
-// X is read around L1 (ld.cg): an earlier product of this same launch may have written it.
-__device__ __forceinline__ void dec_stage_x(const DecOp& op, i8* xq, float* xs, int16_t* bs, double* part, float* scale_s) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const float* x = op.x;
-  float sc = 1.0f;
-  if (op.norm_w) {
-    double acc = 0.0;
-    if (tid < 256)
-      for (int i = tid; i < op.cols; i += 256) {
-        const float v = __ldcg(x + i);
-        acc += (double)__fmul_rn(v, v);
-      }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0 && warp < 8) part[warp] = acc;
+  if (nw) {
     __syncthreads();
-    if (tid == 0) {
-      double t = 0.0;
-      for (int i = 0; i < 8; ++i) t += part[i];
-      *scale_s = __fdiv_rn(1.0f, __fsqrt_rn((float)(t / (double)op.cols + (double)op.eps)));
-    }
-    __syncthreads();
-    sc = *scale_s;
+    sc = rms_scale(rms_total(group_s, ng, lane), d, op.eps);
   }
-  if (op.fmt != ILL_Q8_0) {
-    for (int b = warp; b < op.cols / 256; b += DEC_WARPS) {
-      const float4 v0 = __ldcg((const float4*)(x + b * 256) + 2 * lane), v1 = __ldcg((const float4*)(x + b * 256) + 2 * lane + 1);
-      float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-      if (op.norm_w) {
+  if constexpr (k8) {
+    for (int b0 = 0; b0 < ng; b0 += DEC_HOLD8 * DEC_WARPS) {
+      if (!held) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], sc), op.norm_w[b * 256 + 8 * lane + j]);
+        for (int j = 0; j < DEC_HOLD8; ++j) {
+          const int b = b0 + warp + j * DEC_WARPS;
+          if (b < ng) rms_load8<true>(x, d, b * 256 + 8 * lane, v[j]);
+        }
       }
-      quant_block_q8_k(v, lane, b, xq, xs, bs);
+#pragma unroll
+      for (int j = 0; j < DEC_HOLD8; ++j) {
+        const int b = b0 + warp + j * DEC_WARPS;
+        if (b < ng) {
+          if (nw) {
+            const float4 w0 = ((const float4*)(nw + b * 256))[2 * lane], w1 = ((const float4*)(nw + b * 256))[2 * lane + 1];
+            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[j][i] = __fmul_rn(__fmul_rn(v[j][i], sc), ww[i]);
+          }
+          stage_block_q8k<FMT>(v[j], lane, b, U, xq, xs, bs);
+        }
+      }
     }
   } else {
-    for (int b = warp; b < op.cols / 32; b += DEC_WARPS) {
-      float v = __ldcg(x + b * 32 + lane);
-      if (op.norm_w) v = __fmul_rn(__fmul_rn(v, sc), op.norm_w[b * 32 + lane]);
-      quant_block_q8_0(v, lane, b, xq, xs, nullptr, op.f16_scale);
+    const int nb = d / 32;
+    for (int b0 = 0; b0 < nb; b0 += DEC_HOLD0 * DEC_WARPS) {
+      float u[DEC_HOLD0];
+#pragma unroll
+      for (int j = 0; j < DEC_HOLD0; ++j) {
+        const int b = b0 + warp + j * DEC_WARPS;
+        if (b < nb) u[j] = __ldcg(x + b * 32 + lane);
+      }
+#pragma unroll
+      for (int j = 0; j < DEC_HOLD0; ++j) {
+        const int b = b0 + warp + j * DEC_WARPS;
+        if (b < nb) {
+          float t = u[j];
+          if (nw) t = __fmul_rn(__fmul_rn(t, sc), nw[b * 32 + lane]);
+          float ds;
+          const int q = q8_0_value(t, op.f16_scale, ds);
+          xq[plane_dst<ILL_Q8_0>(2 * b + (lane >> 4), U) + (lane & 15)] = (u8)(i8)q;
+          if (lane == 0) xs[b] = ds;
+        }
+      }
     }
   }
   __syncthreads();
 }
 
-// This warp's tiles T_FIRST, T_FIRST + GSTEP, ... of the product in CW->OP.  False when a copy never landed.
-// A function of its own per variant (not inlined): each gets the registers it needs, not the sum of them all.
-template <int FMT, bool GLU, int UPT, int AL>
-__device__ __noinline__ bool dec_run(DecWarp* cw, u8* ring, const DecShared* sh, int t_first) {
+__device__ __forceinline__ void dec_stage_x(const DecOp& op, u8* xq, float* xs, int16_t* bs, double* group_s) {
+  switch (op.fmt) {
+    case ILL_Q8_0: dec_stage_fmt<ILL_Q8_0>(op, xq, xs, bs, group_s); break;
+    case ILL_Q4_K: dec_stage_fmt<ILL_Q4_K>(op, xq, xs, bs, group_s); break;
+    case ILL_Q6_K: dec_stage_fmt<ILL_Q6_K>(op, xq, xs, bs, group_s); break;
+    case ILL_Q2_K: dec_stage_fmt<ILL_Q2_K>(op, xq, xs, bs, group_s); break;
+    default: dec_stage_fmt<ILL_IQ2_XXS>(op, xq, xs, bs, group_s); break;
+  }
+}
+
+// This warp's groups G_FIRST, G_FIRST + GSTEP, ... of the product OP.  False when a copy never landed.
+// KC: units a lane multiplies in a tile (all of the lane's units when rows are taken whole).
+template <int FMT, int KC, int AL>
+__device__ __forceinline__ bool dec_run(const DecOp* op, DecWarp* cw, u8* ring, const DecShared* sh, int g_first) {
   const int lane = threadIdx.x & 31;
-  const int L = cw->op.lanes, units = cw->op.units, tr = cw->op.tr, rows = cw->op.rows, row_bytes = cw->op.row_bytes;
-  const int tile0 = cw->op.tile0, tend = tile0 + cw->op.ntiles, gstep = sh->gstep, acc = cw->op.acc;
-  const u8* const wg = cw->op.w;
-  const u8* const wu = cw->op.w2;
-  float* const y = cw->op.y;
-  const float* const bias = cw->op.bias;
+  const int L = op->lanes, units = op->units, tr = op->tr, rows = op->rows, row_bytes = op->row_bytes;
+  const int g0 = op->g0, gend = g0 + op->ng, gstep = sh->gstep, acc = op->acc, nch = op->nch, cu = op->cu;
+  const int chunk_bytes = op->chunk_bytes;
+  const u8* const wg = op->w;
+  const u8* const wu = op->w2;
+  float* const y = op->y;
+  const float* const bias = op->bias;
   const int sub = lane / L, sl = lane - sub * L, nsub = 32 / L;
+  const int nparts = wu ? 2 : 1;
   IqTables iqt;
   iqt.grid = sh->iq_grid + (threadIdx.x & (IQ_COPIES - 1));
   iqt.smask = sh->iq_smask + (threadIdx.x & (IQ_COPIES - 1));
-  XReg<FMT> x[UPT];
-  UPos<FMT> up[UPT];
-  {
-    ActS xa;
-    xa.q = sh->xq; xa.s = sh->xs; xa.bs = sh->bs;
-#pragma unroll
-    for (int k = 0; k < UPT; ++k) {
-      const int u = sl + k * L;
-      unit_pos(up[k], u);
-      if (u < units) load_x(x[k], xa, u);
-    }
-  }
+  ActP xa;
+  xa.q = sh->xq; xa.s = sh->xs; xa.bs = sh->bs; xa.U = units;
   int c = cw->c;
   bool all_ok = true;
-  for (int t = t_first; t < tend; t += gstep) {
-    const int b = c % DEC_NBAR;
-    bool ok = mbar_wait(&cw->bars[b], (uint32_t)(c / DEC_NBAR) & 1u, sh->status, ST_MV_WAIT + 0x10 + FMT);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) { all_ok = false; break; }
-    const int off = cw->offs[b];  // written by lane 0 before it issued the copy this wait has just seen land
-    const long long row0 = (long long)(t - tile0) * tr;
+  for (int g = g_first; g < gend && all_ok; g += gstep) {
+    const long long row0 = (long long)(g - g0) * tr;
     const int nrows = min(tr, rows - (int)row0);
-    const u8* s0 = wg + row0 * row_bytes;
-    const u8* rows_g = ring + off + ((uintptr_t)s0 & 15);
-    const u8* rows_u = nullptr;
-    if constexpr (GLU) {
-      const u8* s1 = wu + row0 * row_bytes;
-      rows_u = ring + off + span16(s0, (uint32_t)nrows * (uint32_t)row_bytes) + ((uintptr_t)s1 & 15);
-    }
+    float car0 = 0.0f, car1 = 0.0f;  // a group taken in several tiles: the row's sums so far (gate, up)
+    for (int s = 0; s < nparts * nch; ++s) {
+      const int b = c % DEC_NBAR;
+      bool ok = mbar_wait(&cw->bars[b], (uint32_t)(c / DEC_NBAR) & 1u, sh->status, ST_MV_WAIT + 0x10 + FMT);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { all_ok = false; break; }
+      const int off = cw->offs[b];  // written by lane 0 before it issued the copy this wait has just seen land
+      const int part = s >= nch ? 1 : 0, ch = s - part * nch;
+      const u8* src = (part ? wu : wg) + row0 * row_bytes + (nch > 1 ? (long long)ch * chunk_bytes : 0ll);
+      // the tile's rows in the ring; a run of columns starts CH * CHUNK_BYTES into its row, and the unit offsets
+      // below are taken from the row's start
+      const u8* rows_s = ring + off + ((uintptr_t)src & 15) - (nch > 1 ? (size_t)ch * chunk_bytes : 0);
+      const int ubase = ch * cu;
+      const bool single = nparts * nch == 1;
 #pragma unroll 1
-    for (int r0 = 0; r0 < nrows; r0 += nsub) {
-      const int rr = r0 + sub;
-      const bool valid = rr < nrows;
-      float sum = 0.0f, sum2 = 0.0f;
-      if (valid) {
-        const u8* rowp = rows_g + (size_t)rr * row_bytes;
+      for (int r0 = 0; r0 < nrows; r0 += nsub) {
+        const int rr = r0 + sub;
+        const bool valid = rr < nrows;
+        float sum = single ? 0.0f : (part ? car1 : car0);
+        if (valid) {
+          const u8* rowp = rows_s + (size_t)rr * row_bytes;
 #pragma unroll
-        for (int k = 0; k < UPT; ++k) {
-          const int u = sl + k * L;
-          if (k < UPT - 1 || u < units) {
-            WReg<FMT> w;
-            load_w<AL>(w, rowp, up[k], iqt);
-            sum = __fadd_rn(sum, dot(w, x[k]));
+          for (int k = 0; k < KC; ++k) {
+            const int u = ubase + sl + k * L;
+            if (u < units && (nch == 1 || u < ubase + cu)) {
+              UPos<FMT> up;
+              unit_pos(up, u);
+              XReg<FMT> x;
+              load_x_planes<FMT>(x, xa, u);
+              WReg<FMT> w;
+              load_w<AL>(w, rowp, up, iqt);
+              sum = __fadd_rn(sum, dot(w, x));
+            }
           }
         }
-        if constexpr (GLU) {
-          const u8* rowu = rows_u + (size_t)rr * row_bytes;
-#pragma unroll
-          for (int k = 0; k < UPT; ++k) {
-            const int u = sl + k * L;
-            if (k < UPT - 1 || u < units) {
-              WReg<FMT> w;
-              load_w<AL>(w, rowu, up[k], iqt);
-              sum2 = __fadd_rn(sum2, dot(w, x[k]));
+        if (!single) { if (part) car1 = sum; else car0 = sum; }  // one row iteration a group then (the plan sees to it)
+        if (single || s == nparts * nch - 1) {
+          float v = single ? sum : car0, v2 = car1;
+          for (int o = L >> 1; o > 0; o >>= 1) {
+            v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (nparts == 2) v2 += __shfl_xor_sync(0xffffffffu, v2, o);
+          }
+          if (valid && sl == 0) {
+            const long long row = row0 + rr;
+            if (nparts == 2) {
+              y[row] = (v / (1.0f + expf(-v))) * v2;
+            } else {
+              if (bias) v += bias[row];
+              y[row] = acc ? __ldcg(y + row) + v : v;
             }
           }
         }
       }
-      for (int o = L >> 1; o > 0; o >>= 1) {
-        sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if constexpr (GLU) sum2 += __shfl_xor_sync(0xffffffffu, sum2, o);
+      __syncwarp();  // every lane is done with the tile
+      ++c;
+      if (lane == 0) {
+        cw->c = c;
+        dec_issue(cw, ring, sh, c);
       }
-      if (valid && sl == 0) {
-        const long long row = row0 + rr;
-        if constexpr (GLU) {
-          y[row] = (sum / (1.0f + expf(-sum))) * sum2;
-        } else {
-          float v = sum;
-          if (bias) v += bias[row];
-          y[row] = acc ? __ldcg(y + row) + v : v;
-        }
-      }
-    }
-    __syncwarp();  // every lane is done with the tile
-    ++c;
-    if (lane == 0) {
-      cw->c = c;
-      dec_issue(cw, ring, sh);
     }
   }
-  __syncwarp();  // lane 0's state is the warp's
+  __syncwarp();
   return all_ok;
 }
 
-// The variant for a product, as a pointer: the kernel then has one call site (a call site each would give every
-// one of them its own save area in the kernel's stack frame).
-typedef bool (*DecFn)(DecWarp*, u8*, const DecShared*, int);
-
-template <int FMT, bool GLU, int AL>
-__device__ __forceinline__ DecFn dec_pick_u(int upt) {
-  switch (upt) {
-    case 1: return dec_run<FMT, GLU, 1, AL>;
-    case 2: return dec_run<FMT, GLU, 2, AL>;
-    case 3: return dec_run<FMT, GLU, 3, AL>;
-    case 4: return dec_run<FMT, GLU, 4, AL>;
-    case 5: return dec_run<FMT, GLU, 5, AL>;
-    case 6: if constexpr (FMT == ILL_Q8_0) return dec_run<FMT, GLU, 6, AL>; break;
-    case 7: if constexpr (FMT == ILL_Q8_0) return dec_run<FMT, GLU, 7, AL>; break;
-  }
-  return nullptr;  // not reached: the plan only holds 1..5 (Q8_0: ..7)
-}
-
 template <int FMT, int AL>
-__device__ __forceinline__ DecFn dec_pick_f(bool glu, int upt) {
-  return glu ? dec_pick_u<FMT, true, AL>(upt) : dec_pick_u<FMT, false, AL>(upt);
+__device__ __forceinline__ bool dec_run_k(int kc, const DecOp* op, DecWarp* cw, u8* ring, const DecShared* sh, int g_first) {
+  switch (kc) {
+    case 1: return dec_run<FMT, 1, AL>(op, cw, ring, sh, g_first);
+    case 2: return dec_run<FMT, 2, AL>(op, cw, ring, sh, g_first);
+    case 3: return dec_run<FMT, 3, AL>(op, cw, ring, sh, g_first);
+    case 4: return dec_run<FMT, 4, AL>(op, cw, ring, sh, g_first);
+    case 5: return dec_run<FMT, 5, AL>(op, cw, ring, sh, g_first);
+    case 6: if constexpr (FMT == ILL_Q8_0) return dec_run<FMT, 6, AL>(op, cw, ring, sh, g_first); break;
+    case 7: if constexpr (FMT == ILL_Q8_0) return dec_run<FMT, 7, AL>(op, cw, ring, sh, g_first); break;
+  }
+  return false;  // not reached: the plan only holds 1..5 (Q8_0: ..7)
 }
 
 __global__ void __launch_bounds__(DEC_THREADS, 1) decode_kernel(const DecParams p) {
   extern __shared__ __align__(128) u8 smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // [rings][staged activations: quants, scales, sums of 16][IQ2_XXS tables][the products' sources][warps' state][misc]
+  // [rings][staged activations: planes of quants, scales, planes of sums][IQ2_XXS tables][the products][warps' state]
+  // [misc]; every region is a multiple of 16 bytes
   u8* at = smem + (size_t)DEC_WARPS * p.ring_bytes;
-  i8* xq_s = (i8*)at;                      at += p.max_cols;
+  u8* xq_s = at;                           at += p.max_cols;
   float* xs_s = (float*)at;                at += p.max_cols / 32 * 4;
   int16_t* bs_s = (int16_t*)at;            at += p.max_cols / 16 * 2;
   uint2* iq_grid = (uint2*)at;
   uint2* iq_smask = iq_grid + IQ_COPIES * 256;
   if (p.has_iq) at += IQ_TABLE_BYTES;
-  DecSrc* srcs = (DecSrc*)at;              at += (size_t)p.nops * sizeof(DecSrc);
+  DecOp* ops_s = (DecOp*)at;               at += (size_t)p.nops * sizeof(DecOp);
   DecWarp* warps = (DecWarp*)at;           at += DEC_WARPS * sizeof(DecWarp);
   DecShared* sh = (DecShared*)at;          at += sizeof(DecShared);
-  double* part = (double*)at;              at += 8 * 8;
-  float* scale_s = (float*)at;
+  double* group_s = (double*)at;           // [RMS_MAX_GROUPS]
+
+  for (int i = tid; i < p.nops * (int)(sizeof(DecOp) / 16); i += DEC_THREADS) ((uint4*)ops_s)[i] = ((const uint4*)p.ops)[i];
+  const int gstep = gridDim.x * DEC_WARPS, gw = blockIdx.x * DEC_WARPS + warp;
   DecWarp* cw = warps + warp;
   u8* ring = smem + (size_t)warp * p.ring_bytes;
-
-  for (int i = tid; i < p.nops; i += DEC_THREADS) {
-    const DecOp* o = p.ops + i;
-    DecSrc s;
-    s.w = o->w; s.w2 = o->w2; s.tile0 = o->tile0; s.ntiles = o->ntiles; s.rows = o->rows; s.tr = o->tr;
-    s.row_bytes = o->row_bytes; s.pad = 0;
-    srcs[i] = s;
-  }
-  const int gw = blockIdx.x * DEC_WARPS + warp, gstep = gridDim.x * DEC_WARPS;
   if (lane == 0) {
     for (int b = 0; b < DEC_NBAR; ++b) mbar_init(&cw->bars[b], 1);
     mbar_fence_init();
-    cw->c = 0; cw->issued = 0; cw->head = 0; cw->iss_t = gw; cw->iss_op = 0;
+    cw->c = 0; cw->issued = 0; cw->head = 0; cw->iss_g = gw; cw->iss_s = 0; cw->iss_op = 0;
   }
   if (tid == 0) {
-    sh->srcs = srcs; sh->status = p.status; sh->total_tiles = p.total_tiles; sh->ring_bytes = p.ring_bytes; sh->gstep = gstep;
+    sh->ops = ops_s; sh->status = p.status; sh->nops = p.nops; sh->ring_bytes = p.ring_bytes; sh->gstep = gstep;
     sh->xq = xq_s; sh->xs = xs_s; sh->bs = bs_s; sh->iq_grid = iq_grid; sh->iq_smask = iq_smask;
   }
   if (p.has_iq) iq_tables_fill(iq_grid, iq_smask, ill_iq2xxs_grid, ill_ksigns_iq2xs);
   __syncthreads();
-  if (lane == 0) dec_issue(cw, ring, sh);  // the weights depend on nothing: start streaming
+  if (lane == 0) dec_issue(cw, ring, sh, 0);  // the weights depend on nothing: start streaming
   __syncwarp();
 
   // LOST: this warp gave up a wait.  It keeps walking the list (the CTA's barriers count on it) but does no more
   // work; the CTA learns of it at the next point where its warps meet and leaves the list there, all warps together.
   bool lost = false, broke = false;
+  unsigned meetings = 0;
   for (int oi = 0; oi < p.nops; ++oi) {
-    // the warp's copy of the product: a lane a word
-    __syncwarp();
-    ((uint32_t*)&cw->op)[lane] = ((const uint32_t*)(p.ops + oi))[lane];
-    __syncwarp();
+    const DecOp* op = ops_s + oi;
     bool synced = false;
-    if (cw->op.after) {
+    if (op->after) {
       __syncthreads();  // this CTA's part of everything before is written
+      ++meetings;
       bool bad = false;
-      if (tid == 0) bad = !dec_grid_barrier(p.bar, gridDim.x, p.status);
+      if (tid == 0) bad = !dec_grid_barrier(p.bar, p.bar_base + meetings * gridDim.x, p.status);
       if (__syncthreads_or(bad || lost)) { broke = true; break; }
       synced = true;
     }
-    if (cw->op.restage) {
-      // every warp has taken its registers from the activations staged before
+    if (op->restage) {
+      // every warp is done with the activations staged before
       if (!synced && __syncthreads_or(lost)) { broke = true; break; }
-      dec_stage_x(cw->op, xq_s, xs_s, bs_s, part, scale_s);
+      dec_stage_x(*op, xq_s, xs_s, bs_s, group_s);
     }
-    const int tile0 = cw->op.tile0;
-    int d = (gw - tile0) % gstep;
+    const int g0 = op->g0;
+    int d = (gw - g0) % gstep;
     if (d < 0) d += gstep;
-    const int t_first = tile0 + d;
-    if (!lost && t_first < tile0 + cw->op.ntiles) {
-      const bool glu = cw->op.w2 != nullptr;
-      const int upt = cw->op.upt;
-      DecFn fn = nullptr;
-      switch (cw->op.fmt) {
-        case ILL_Q8_0: fn = dec_pick_f<ILL_Q8_0, 1>(glu, upt); break;
-        case ILL_Q4_K: fn = dec_pick_f<ILL_Q4_K, 16>(glu, upt); break;
-        case ILL_Q6_K: fn = dec_pick_f<ILL_Q6_K, 1>(glu, upt); break;
-        case ILL_Q2_K: fn = dec_pick_f<ILL_Q2_K, 4>(glu, upt); break;
-        case ILL_IQ2_XXS: fn = dec_pick_f<ILL_IQ2_XXS, 1>(glu, upt); break;
+    const int g_first = g0 + d;
+    if (!lost && g_first < g0 + op->ng) {
+      const int kc = op->kc;
+      bool ok = false;
+      switch (op->fmt) {
+        case ILL_Q8_0: ok = dec_run_k<ILL_Q8_0, 1>(kc, op, cw, ring, sh, g_first); break;
+        case ILL_Q4_K: ok = dec_run_k<ILL_Q4_K, 16>(kc, op, cw, ring, sh, g_first); break;
+        case ILL_Q6_K: ok = dec_run_k<ILL_Q6_K, 1>(kc, op, cw, ring, sh, g_first); break;
+        case ILL_Q2_K: ok = dec_run_k<ILL_Q2_K, 4>(kc, op, cw, ring, sh, g_first); break;
+        case ILL_IQ2_XXS: ok = dec_run_k<ILL_IQ2_XXS, 1>(kc, op, cw, ring, sh, g_first); break;
       }
-      const bool ok = fn ? fn(cw, ring, sh, t_first) : false;
       if (!ok) lost = true;
     }
   }
@@ -434,8 +500,9 @@ static uint32_t up_to(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 using namespace ill;
 
 // launch[]: what ill_decode_plan hands to ill_decode_run
-enum { DL_NOPS = 0, DL_GRID, DL_SMEM, DL_TILES, DL_RING, DL_MAXCOLS, DL_IQ, DL_MAGIC };
+enum { DL_NOPS = 0, DL_GRID, DL_SMEM, DL_TILES, DL_RING, DL_MAXCOLS, DL_IQ, DL_MEETINGS, DL_EPOCH, DL_MAGIC, DL_WORDS };
 constexpr int DL_MAGIC_VALUE = 0x1d1ec0de;
+static_assert(DL_WORDS <= ILL_DECODE_LAUNCH_WORDS, "the caller's array holds the launch words");
 
 extern "C" int64_t ill_decode_plan_bytes(int nops) {
   if (nops < 1 || nops > DEC_MAX_OPS) return 0;
@@ -460,25 +527,28 @@ extern "C" int ill_decode_plan(const ill_decode_op* ops, int nops, ill_dptr plan
         o.cols > DEC_MAX_COLS || !o.w || !o.x || !o.y || (o.kind == ILL_OP_GLU && (!o.w2 || o.acc || o.bias)) ||
         (o.kind == ILL_OP_MV && o.w2))
       return ILL_ERR_ARG;
-    if ((o.w & 15) || (o.w2 & 15) || (o.x & 15) || (o.norm_w & 3) || (o.y & 3) || (o.bias & 3)) return ILL_ERR_ALIGN;
+    if ((o.w & 15) || (o.w2 & 15) || (o.x & 15) || (o.norm_w & 15) || (o.y & 3) || (o.bias & 3)) return ILL_ERR_ALIGN;
     if (o.cols > max_cols) max_cols = o.cols;
     if (o.fmt == ILL_IQ2_XXS) has_iq = 1;
   }
   max_cols = (int)up_to((uint32_t)max_cols, 256);
   // shared memory: everything but the rings first, the rings get the rest
   const uint32_t fixed = (uint32_t)max_cols + (uint32_t)max_cols / 32 * 4 + (uint32_t)max_cols / 16 * 2 + (has_iq ? IQ_TABLE_BYTES : 0) +
-                         (uint32_t)nops * (uint32_t)sizeof(DecSrc) + DEC_WARPS * (uint32_t)sizeof(DecWarp) + (uint32_t)sizeof(DecShared) + 64 + 16;
+                         (uint32_t)nops * (uint32_t)sizeof(DecOp) + DEC_WARPS * (uint32_t)sizeof(DecWarp) + (uint32_t)sizeof(DecShared) +
+                         RMS_MAX_GROUPS * 8;
   const int budget = smem_max - 1024;
   if ((int)fixed + DEC_WARPS * 8192 > budget) return ILL_ERR_TOO_LARGE;
   const int ring = (int)((((uint32_t)budget - fixed) / DEC_WARPS) & ~127u);
+  const int limit = ring / 2 - 32;  // a tile's bytes at most: the next one fits beside it
   std::vector<DecOp> dev_ops((size_t)nops);
-  long long tiles = 0;
+  long long groups = 0;
+  int meetings = 0;
   const long long gwarps = (long long)sms * DEC_WARPS;
   for (int i = 0; i < nops; ++i) {
     const ill_decode_op& o = ops[i];
     DecOp& d = dev_ops[(size_t)i];
     d = DecOp();
-    const int bw = fmt_block_weights(o.fmt), uw = (o.fmt == ILL_Q8_0 || o.fmt == ILL_IQ2_XXS) ? 32 : 64;
+    const int bw = fmt_block_weights(o.fmt), bb = fmt_block_bytes(o.fmt), uw = (o.fmt == ILL_Q8_0 || o.fmt == ILL_IQ2_XXS) ? 32 : 64;
     const bool glu = o.kind == ILL_OP_GLU;
     d.w = (const u8*)(uintptr_t)o.w;
     d.w2 = (const u8*)(uintptr_t)o.w2;
@@ -487,36 +557,63 @@ extern "C" int ill_decode_plan(const ill_decode_op* ops, int nops, ill_dptr plan
     d.x = (const float*)(uintptr_t)o.x;
     d.norm_w = (const float*)(uintptr_t)o.norm_w;
     d.eps = o.eps;
-    d.fmt = o.fmt;
+    d.fmt = (u8)o.fmt;
     d.acc = o.acc ? 1 : 0;
     d.f16_scale = o.f16_scale ? 1 : 0;
     d.rows = o.rows;
     d.cols = o.cols;
-    d.row_bytes = o.cols / bw * fmt_block_bytes(o.fmt);
+    d.row_bytes = o.cols / bw * bb;
     d.units = o.cols / uw;
+    // lanes a row and units a lane as the one-token product picks them (the order of a row's additions follows from
+    // the pair); rows it would not keep in registers: 32 lanes, as many units a lane as it takes
     const bool big = (long long)o.rows * d.row_bytes >= (16ll << 20);
-    if (!mv_pick_lanes(o.fmt, d.units, glu, big, &d.lanes, &d.upt)) return ILL_ERR_UNSUPPORTED;  // rows too long for registers
-    // rows a tile: a multiple of the rows a warp has in progress; about 4 KB, cut finer when the product is
-    // small (every warp should get a tile), and never more than a third of the ring
-    const int nsub = 32 / d.lanes, parts = glu ? 2 : 1;
-    long long target = (long long)o.rows * d.row_bytes * parts / (2 * gwarps);
-    if (target > 4096) target = 4096;
-    if (target < 1024) target = 1024;
-    if (target > ring / 3) target = ring / 3;
-    long long tr = target / ((long long)d.row_bytes * parts) / nsub * nsub;
-    if (tr < nsub) tr = nsub;
-    if (tr > o.rows) tr = (o.rows + nsub - 1) / nsub * nsub;
-    if ((tr * d.row_bytes + 32) * parts > ring / 2) return ILL_ERR_UNSUPPORTED;  // a tile must leave room for the next
-    d.tr = (int)tr;
-    d.ntiles = (int)((o.rows + tr - 1) / tr);
-    d.tile0 = (int)tiles;
-    tiles += d.ntiles;
-    if (tiles > 0x7fffffffll / 2) return ILL_ERR_TOO_LARGE;
+    int lanes = 0, upt = 0;
+    if (!mv_pick_lanes(o.fmt, d.units, glu, big, &lanes, &upt)) { lanes = 32; upt = (d.units + 31) / 32; }
+    int nsub = 32 / lanes;
+    const int kmax = o.fmt == ILL_Q8_0 ? 7 : 5;
+    if ((long long)nsub * d.row_bytes > limit && lanes < 32 && d.row_bytes > limit) { lanes = 32; upt = (d.units + 31) / 32; nsub = 1; }
+    d.lanes = (u8)lanes;
+    if (d.row_bytes <= limit && upt <= kmax) {
+      // whole rows.  A gated product's group is one pass of the warp (its gate rows' sums are carried to its up
+      // rows); a plain product's is about 4 KB, cut finer when the product is small (every warp should get some).
+      // Rows that do not fit side by side: fewer a group, and the lanes past them idle.
+      long long tr = nsub;
+      if (!glu) {
+        long long target = (long long)o.rows * d.row_bytes / (2 * gwarps);
+        if (target > 4096) target = 4096;
+        if (target < 1024) target = 1024;
+        tr = target / d.row_bytes / nsub * nsub;
+        if (tr < nsub) tr = nsub;
+      }
+      while (tr > 1 && tr * d.row_bytes > limit) tr = tr > nsub ? tr - nsub : tr - 1;
+      if (tr > o.rows) tr = o.rows;
+      d.tr = (int)tr;
+      d.nch = 1;
+      d.cu = d.units;
+      d.kc = (u8)upt;
+      d.chunk_bytes = d.row_bytes;
+    } else {
+      // a row at a time, in runs of KC * 32 units (whole blocks): about 4 KB a tile
+      const int upb = bw / uw;  // units a block
+      int kc = kmax < upt ? kmax : upt;
+      while (kc > 1 && ((long long)kc * 32 / upb * bb > limit || (long long)kc * 32 / upb * bb > 4096)) --kc;
+      if ((long long)kc * 32 / upb * bb > limit) return ILL_ERR_UNSUPPORTED;
+      d.tr = 1;
+      d.cu = kc * 32;
+      d.kc = (u8)kc;
+      d.nch = (d.units + d.cu - 1) / d.cu;
+      d.chunk_bytes = d.cu / upb * bb;
+    }
+    d.ng = (int)((o.rows + d.tr - 1) / d.tr);
+    d.g0 = (int)groups;
+    groups += d.ng;
+    if (groups > 0x7fffffffll / 2) return ILL_ERR_TOO_LARGE;
     d.after = (i > 0 && o.after) ? 1 : 0;
+    meetings += d.after;
+    // the activations are staged again when they change -- or the planes they are laid out in do
     const ill_decode_op* pv = i ? &ops[i - 1] : nullptr;
-    const bool k8 = o.fmt != ILL_Q8_0, pk8 = pv && pv->fmt != ILL_Q8_0;
-    d.restage = (!pv || d.after || pv->x != o.x || pv->norm_w != o.norm_w || pv->eps != o.eps || pv->cols != o.cols || pk8 != k8 ||
-                 (!k8 && (pv->f16_scale != 0) != (o.f16_scale != 0)))
+    d.restage = (!pv || d.after || pv->x != o.x || pv->norm_w != o.norm_w || pv->eps != o.eps || pv->cols != o.cols || pv->fmt != o.fmt ||
+                 (o.fmt == ILL_Q8_0 && (pv->f16_scale != 0) != (o.f16_scale != 0)))
                     ? 1 : 0;
   }
   unsigned char head[128] = {0};
@@ -536,22 +633,24 @@ extern "C" int ill_decode_plan(const ill_decode_op* ops, int nops, ill_dptr plan
   launch[DL_NOPS] = nops;
   launch[DL_GRID] = sms;
   launch[DL_SMEM] = (int)smem;
-  launch[DL_TILES] = (int)tiles;
+  launch[DL_TILES] = (int)groups;
   launch[DL_RING] = ring;
   launch[DL_MAXCOLS] = max_cols;
   launch[DL_IQ] = has_iq;
+  launch[DL_MEETINGS] = meetings;
+  launch[DL_EPOCH] = 0;   // arrivals at the barrier so far (the count in PLAN starts at 0 with it)
   launch[DL_MAGIC] = DL_MAGIC_VALUE;
   return ILL_OK;
 }
 
-extern "C" int ill_decode_run(ill_dptr plan, const int32_t* launch, ill_stream stream) {
+extern "C" int ill_decode_run(ill_dptr plan, int32_t* launch, ill_stream stream) {
   if (!plan || !launch || launch[DL_MAGIC] != DL_MAGIC_VALUE || launch[DL_NOPS] < 1 || launch[DL_GRID] < 1) return ILL_ERR_ARG;
   if (plan & 127) return ILL_ERR_ALIGN;
   DecParams p;
   p.ops = (const DecOp*)(uintptr_t)(plan + 128);
   p.nops = launch[DL_NOPS];
   p.bar = (unsigned*)(uintptr_t)plan;
-  p.total_tiles = launch[DL_TILES];
+  p.bar_base = (unsigned)launch[DL_EPOCH];
   p.ring_bytes = launch[DL_RING];
   p.max_cols = launch[DL_MAXCOLS];
   p.has_iq = launch[DL_IQ];
@@ -572,5 +671,8 @@ extern "C" int ill_decode_run(ill_dptr plan, const int32_t* launch, ill_stream s
   cfg.numAttrs = 1;
   void* args[] = {&p};
   e = cudaLaunchKernelExC(&cfg, (const void*)decode_kernel, args);
-  return e == cudaSuccess ? ILL_OK : cuda_fail(e);
+  if (e != cudaSuccess) return cuda_fail(e);
+  // this token's meetings are counted on from here: the next run's first target lies past them
+  launch[DL_EPOCH] = (int32_t)((unsigned)launch[DL_EPOCH] + (unsigned)launch[DL_MEETINGS] * (unsigned)launch[DL_GRID]);
+  return ILL_OK;
 }

@@ -43,32 +43,27 @@ __global__ void __launch_bounds__(256) quant_q8_k_kernel(const float* __restrict
 // float) summed in double, scale = 1 / sqrt(float(sum / d + eps)), value = (x * scale) * w, then the
 // blocks quantized as the stand-alone quantizers do.  Grid (slices, rows): every CTA of a row works the
 // row's scale out for itself (the row comes from L2) and takes a slice of its blocks, so that one token's
-// norm is not one CTA's serial work.  The double sum is taken in a different order than the CPU's loop;
-// the two agree until the float the sum is rounded to sits within 1e-16 of a rounding boundary.
+// norm is not one CTA's serial work.  The double sum is taken in the order quantdev.cuh fixes, not in the
+// CPU loop's; the two agree until the float the sum is rounded to sits within 1e-16 of a rounding boundary.
 template <int K8K>
 __global__ void __launch_bounds__(256) rmsnorm_q8_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                          float* __restrict__ h, i8* __restrict__ xq, float* __restrict__ xs,
                                                          void* __restrict__ xsum, int d, float eps, int f16_scale) {
-  __shared__ double part[8];
-  __shared__ float scale_s;
+  __shared__ double group_s[RMS_MAX_GROUPS];
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const long long base = (long long)blockIdx.y * d;
   const float* xr = x + base;
-  double acc = 0.0;
-  for (int i = tid; i < d; i += 256) acc += (double)__fmul_rn(xr[i], xr[i]);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) part[warp] = acc;
-  __syncthreads();
-  if (tid == 0) {
-    double t = 0.0;
-    for (int i = 0; i < 8; ++i) t += part[i];
-    scale_s = __fdiv_rn(1.0f, __fsqrt_rn((float)(t / (double)d + (double)eps)));
+  const int ng = (d + 255) / 256;
+  for (int g = warp; g < ng; g += 8) {
+    float v[8];
+    rms_load8<false>(xr, d, g * 256 + 8 * lane, v);
+    const double s = rms_group_sum(v);
+    if (lane == 0) group_s[g] = s;
   }
   __syncthreads();
-  const float sc = scale_s;
+  const float sc = rms_scale(rms_total(group_s, ng, lane), d, eps);
   constexpr int BW = K8K ? 256 : 32;
   const int nb = d / BW;
   for (int b = blockIdx.x * 8 + warp; b < nb; b += gridDim.x * 8) {
@@ -141,6 +136,7 @@ extern "C" int ill_rmsnorm_q8(int kind, ill_dptr x, ill_dptr w, ill_dptr h, ill_
   const int bw = kind == 1 ? 256 : 32;
   if ((kind != 0 && kind != 1) || d <= 0 || d % bw || n < 0 || n > 65535 || !x || !w || !xq || !xs || (kind == 1 && !xsum))
     return ILL_ERR_ARG;
+  if (d > 256 * RMS_MAX_GROUPS) return ILL_ERR_TOO_LARGE;
   if ((x & 3) || (w & 3) || (h & 3) || (xs & 3) || (xsum & (kind == 1 ? 1 : 3)) || (kind == 1 && (xq & 7))) return ILL_ERR_ALIGN;
   if (n == 0) return ILL_OK;
   const float* xp = (const float*)(uintptr_t)x;

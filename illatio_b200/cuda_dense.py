@@ -203,7 +203,7 @@ class DecodePlan:
             raise ValueError("a chain holds 1 to 1024 products")
         self.plan = torch.zeros(nbytes + 128, dtype=torch.uint8, device=device)
         self.base = (self.plan.data_ptr() + 127) // 128 * 128
-        self.launch = (ctypes.c_int32 * 8)()
+        self.launch = (ctypes.c_int32 * 16)()
         with torch.cuda.device(self.plan.device):
             _lib.call("ill_decode_plan", arr, self.n, self.base, nbytes, self.launch, _stream())
 

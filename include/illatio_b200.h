@@ -171,7 +171,7 @@ ILL_API int ill_mv_glu(int fmt, ill_dptr wg, ill_dptr wu, int rows, int cols, il
  * bit for bit what ill_quant_q8_0 / ill_quant_q8_k / ill_rmsnorm_q8 write.  AFTER
  * != 0: the product reads (X) or adds into (Y) what an earlier product of the list
  * writes, so every earlier product is complete before it starts; products without
- * it may run beside their predecessors.  W, W2 and X are 16-byte aligned. */
+ * it may run beside their predecessors.  W, W2, X and NORM_W are 16-byte aligned. */
 #define ILL_OP_MV 0
 #define ILL_OP_GLU 1
 typedef struct ill_decode_op {
@@ -187,18 +187,21 @@ typedef struct ill_decode_op {
  * ill_decode_plan turns the NOPS products at OPS (host memory) into the list the
  * kernel walks, written to PLAN (device memory the caller owns, 128-byte aligned,
  * ill_decode_plan_bytes(nops) bytes; it also holds the barrier the CTAs meet at),
- * and fills LAUNCH (8 ints the caller keeps beside PLAN).  It synchronises STREAM.
- * ill_decode_run enqueues the token: one cooperative launch of one CTA per SM.
- * The same PLAN runs any number of tokens, one at a time (two runs of one PLAN
- * must not overlap).  Results are the same bits ill_mv / ill_mv_glu give on the
+ * and fills LAUNCH (ILL_DECODE_LAUNCH_WORDS ints the caller keeps beside PLAN; the
+ * library keeps nothing itself).  It synchronises STREAM.  ill_decode_run enqueues
+ * the token: one cooperative launch of one CTA per SM; it updates LAUNCH (the
+ * barrier's arrivals are counted on from token to token).  The same PLAN runs any
+ * number of tokens, one at a time, in the order ill_decode_run was called (two runs
+ * of one PLAN must not overlap).  Results are the same bits ill_mv / ill_mv_glu give on the
  * same activations.  Rows too long for a lane's registers (more than 160 units of
  * 64 weights, 224 Q8_0 blocks) are ILL_ERR_UNSUPPORTED: use ill_mv for those.
  * After a time-out (ILL_ERR_DEVICE_WAIT from ill_device_status) plan again before
  * the next run: the barrier's count may be left mid-way. */
+#define ILL_DECODE_LAUNCH_WORDS 16
 ILL_API int64_t ill_decode_plan_bytes(int nops);
 ILL_API int ill_decode_plan(const ill_decode_op* ops, int nops, ill_dptr plan, int64_t plan_bytes, int32_t* launch,
                             ill_stream stream);
-ILL_API int ill_decode_run(ill_dptr plan, const int32_t* launch, ill_stream stream);
+ILL_API int ill_decode_run(ill_dptr plan, int32_t* launch, ill_stream stream);
 
 /* ---- routed experts: one decoded token ------------------------------------------ */
 

@@ -118,7 +118,8 @@ def test_chain_against_the_oracle(oracle):
     nw = (rng.random(hidden) + 0.5).astype(np.float32)
     h, fa = to_dev(h0), torch.empty(ffn, device="cuda")
     G, U, DN = (D.upload_gmat(m, f, r, c) for m, f, r, c in ((g, B.Q4_K, ffn, hidden), (u, B.Q4_K, ffn, hidden), (dn, B.Q6_K, hidden, ffn)))
-    plan = D.DecodePlan([D.decode_op(G, h, fa, w2=U, norm_w=to_dev(nw), eps=EPS, after=False),
+    nwd = to_dev(nw)   # the plan keeps addresses only: every buffer it names must outlive it
+    plan = D.DecodePlan([D.decode_op(G, h, fa, w2=U, norm_w=nwd, eps=EPS, after=False),
                          D.decode_op(DN, fa, h, acc=True, after=True)])
     plan.run()
     torch.cuda.synchronize()
@@ -132,15 +133,29 @@ def test_chain_against_the_oracle(oracle):
     assert np.abs(h.cpu().numpy() - want_h).max() / np.abs(want_h).max() < 1e-5
 
 
+def test_long_rows_are_taken_in_runs_of_columns():
+    """Rows too long to fit a tile whole (and for ill_mv to keep in registers): 17408 columns, Q6_K and Q8_0.
+    The chain takes such a row in runs of columns and carries its sum; against ill_mv, whose order of additions
+    differs for such rows, to fp32 reassociation."""
+    for fmt in (B.Q6_K, B.Q8_0, B.Q4_K):
+        w = _mat(fmt, 300, 17408, 1)
+        x = torch.randn(17408, device="cuda", generator=torch.Generator(device="cuda").manual_seed(2))
+        y, want = torch.zeros(300, device="cuda"), torch.zeros(300, device="cuda")
+        D.DecodePlan([D.decode_op(w, x, y, after=False)]).run()
+        D.cmat_mul(w, D.quant_q8(x, D.make_qact(17408, D.matrix_act_kind(w))), want, 1)
+        torch.cuda.synchronize()
+        assert ((y - want).abs().max() / want.abs().max()).item() < 1e-5
+
+
 def test_plan_refuses_what_it_cannot_run():
     from illatio_b200 import _lib
-    w = _mat(B.Q6_K, 64, 17408, 1)     # 272 units a row: more than a lane's registers hold
-    x, y = torch.zeros(17408, device="cuda"), torch.zeros(64, device="cuda")
-    with pytest.raises(_lib.IllatioError) as e:
-        D.DecodePlan([D.decode_op(w, x, y)])
-    assert e.value.code == 3
     w = _mat(B.Q4_K, 64, 512, 1)
     op = D.decode_op(w, torch.zeros(516, device="cuda")[1:513], torch.zeros(64, device="cuda"))   # X not 16-byte aligned
     with pytest.raises(_lib.IllatioError) as e:
         D.DecodePlan([op])
     assert e.value.code == 2
+    op = D.decode_op(w, torch.zeros(512, device="cuda"), torch.zeros(64, device="cuda"))
+    op.cols = 500                                                                                # not whole blocks
+    with pytest.raises(_lib.IllatioError) as e:
+        D.DecodePlan([op])
+    assert e.value.code == 1
