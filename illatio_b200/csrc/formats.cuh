@@ -100,12 +100,12 @@ __device__ __forceinline__ int dp2a_lo(int a, int b, int c) {
   return d;
 }
 
-// The IQ2_XXS codebook (256 x 8 magnitudes) and the sign patterns expanded to
-// byte masks (0xFF where the weight is negative), in shared memory.
-// IQ2_XXS tables in shared memory, IQ_COPIES interleaved copies each (entry e of copy c at [IQ_COPIES e + c]):
-// a lane reads copy lane % IQ_COPIES, so that the sixteen lanes of a 64-bit request spread over the banks
-// instead of piling onto the ones their random entries happen to share.  GRID / SMASK point at the lane's copy.
-constexpr int IQ_COPIES = 8;
+// The IQ2_XXS codebook (256 x 8 magnitudes) and the sign patterns expanded to byte masks (0xFF where the weight
+// is negative), in shared memory, IQ_COPIES interleaved copies each (entry e of copy c at [IQ_COPIES e + c]).  A
+// lane reads copy lane % 16: a 64-bit request is served half a warp at a time, and the sixteen lanes of a half then
+// sit on sixteen different pairs of banks whatever entries they ask for -- no bank conflicts, where eight copies
+// still left 60% of the wavefronts to them.  GRID / SMASK point at the lane's copy.
+constexpr int IQ_COPIES = 16;
 constexpr int IQ_TABLE_BYTES = IQ_COPIES * (256 + 128) * 8;
 struct IqTables { const uint2* grid; const uint2* smask; };
 
@@ -248,8 +248,8 @@ __device__ __forceinline__ float dot(const WReg<ILL_Q6_K>& w, const XReg<ILL_Q6_
 }
 
 // ---- Q2_K: unit = half h, 16-byte half: four groups of 16 ---------------------
-template <> struct XReg<ILL_Q2_K> { uint32_t q[16]; float d; int bs[4]; };
-template <> struct WReg<ILL_Q2_K> { uint32_t q[4]; float d, dmin; uint32_t sc[4]; };
+template <> struct XReg<ILL_Q2_K> { uint32_t q[16]; float d; int bs01, bs23; };  // the four sums of 16 as int16 pairs
+template <> struct WReg<ILL_Q2_K> { uint32_t q[4]; float d, dmin; uint32_t sc4; };  // the unit's four scale bytes
 template <> struct UPos<ILL_Q2_K> { int offs, offq, offd, sh; };
 
 __device__ __forceinline__ void unit_pos(UPos<ILL_Q2_K>& o, int u) {
@@ -264,11 +264,16 @@ __device__ __forceinline__ void load_x(XReg<ILL_Q2_K>& x, const ActS& a, int u) 
   const i8* q = a.q + 256 * i + 128 * h + 16 * half;
   const int16_t* bs = a.bs + 16 * i + 8 * h + half;
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    ld_x128<1>(q + 32 * k, x.q + 4 * k);
-    x.bs[k] = bs[2 * k];
-  }
+  for (int k = 0; k < 4; ++k) ld_x128<1>(q + 32 * k, x.q + 4 * k);
+  x.bs01 = ((int)bs[0] & 0xffff) | ((int)bs[2] << 16);
+  x.bs23 = ((int)bs[4] & 0xffff) | ((int)bs[6] << 16);
   x.d = a.s[i];
+}
+// two signed 16-bit halves of A times the two high signed bytes of B, accumulated
+__device__ __forceinline__ int dp2a_hi(int a, int b, int c) {
+  int d;
+  asm("dp2a.hi.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
 }
 template <int AL = 1>
 __device__ __forceinline__ void load_w(WReg<ILL_Q2_K>& w, const u8* row, const UPos<ILL_Q2_K>& o, const IqTables&) {
@@ -277,23 +282,28 @@ __device__ __forceinline__ void load_w(WReg<ILL_Q2_K>& w, const u8* row, const U
   ld_words_al<2, A>(row + o.offs, s);  // the half's eight scale bytes
   ld_words_al<4, A>(row + o.offq, w.q);
   ld_words_al<1, A>(row + o.offd, dd);
-  const uint32_t lo = s[0] >> o.sh, hi = s[1] >> o.sh;
-  w.sc[0] = lo & 0xff; w.sc[1] = (lo >> 16) & 0xff; w.sc[2] = hi & 0xff; w.sc[3] = (hi >> 16) & 0xff;
+  // the unit's groups use scale bytes half, half + 2, half + 4, half + 6 of the eight: gathered into one word
+  w.sc4 = __byte_perm(s[0], s[1], o.sh ? 0x7531 : 0x6420);
   w.d = h2f(dd[0] & 0xffff);
   w.dmin = h2f(dd[0] >> 16);
 }
 __device__ __forceinline__ float dot(const WReg<ILL_Q2_K>& w, const XReg<ILL_Q2_K>& x) {
-  int isum = 0, mins = 0;
+  // The 2-bit fields are masked where they sit (unsigned bytes up to 192 against signed ones): group k's dot comes out
+  // 4^k times too large, exactly, and one shift a group puts that right.  A group's dot is at most 16 * 3 * 128 in
+  // magnitude, so the four fit 16 bits and meet their four scales (the low nibbles of the scale bytes) in two dp2a;
+  // the mins (the high nibbles) meet the activations' sums of 16 the same way.
+  int d[4];
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    // the 2-bit fields are masked where they sit (unsigned bytes up to 192 against signed ones): the dot comes
-    // out 4^k times too large, exactly, and one shift a group puts that right instead of one a word
-    int d = 0;
+    d[k] = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) d = dp4a_us(w.q[j] & (0x03030303u << (2 * k)), (int)x.q[4 * k + j], d);
-    isum += (int)(w.sc[k] & 15) * (d >> (2 * k));
-    mins += (int)(w.sc[k] >> 4) * x.bs[k];
+    for (int j = 0; j < 4; ++j) d[k] = dp4a_us(w.q[j] & (0x03030303u << (2 * k)), (int)x.q[4 * k + j], d[k]);
   }
+  const int p01 = (int)__byte_perm((uint32_t)d[0], (uint32_t)(d[1] >> 2), 0x5410);
+  const int p23 = (int)__byte_perm((uint32_t)(d[2] >> 4), (uint32_t)(d[3] >> 6), 0x5410);
+  const int sc = (int)(w.sc4 & 0x0f0f0f0fu), mn = (int)((w.sc4 >> 4) & 0x0f0f0f0fu);
+  const int isum = dp2a_hi(p23, sc, dp2a_lo(p01, sc, 0));
+  const int mins = dp2a_hi(x.bs23, mn, dp2a_lo(x.bs01, mn, 0));
   return __fsub_rn(__fmul_rn(__fmul_rn(x.d, w.d), (float)isum), __fmul_rn(__fmul_rn(x.d, w.dmin), (float)mins));
 }
 
@@ -320,7 +330,7 @@ __device__ __forceinline__ void load_w(WReg<ILL_IQ2_XXS>& w, const u8* row, cons
   for (int l = 0; l < 4; ++l) {
     const uint2 g = t.grid[IQ_COPIES * ((idx >> (8 * l)) & 0xff)];
     const uint2 m = t.smask[IQ_COPIES * ((aux >> (7 * l)) & 127)];
-    // (g ^ m) - m per byte; g <= 43, so adding 1 to a flipped byte never carries
+    // (g ^ m) - m per byte; g is 8, 25 or 43, never 0, so adding 1 to a flipped byte never carries
     w.q[2 * l] = (g.x ^ m.x) + (m.x & 0x01010101u);
     w.q[2 * l + 1] = (g.y ^ m.y) + (m.y & 0x01010101u);
   }
@@ -412,8 +422,8 @@ __device__ __forceinline__ void load_x_planes(XReg<FMT>& x, const ActP& a, int u
 #pragma unroll
       for (int g = 0; g < 4; ++g) x.bs[g] = 32 * (int)a.bs[g * a.U + u];
     } else {
-#pragma unroll
-      for (int g = 0; g < 4; ++g) x.bs[g] = (int)a.bs[g * a.U + u];
+      x.bs01 = ((int)a.bs[u] & 0xffff) | ((int)a.bs[a.U + u] << 16);
+      x.bs23 = ((int)a.bs[2 * a.U + u] & 0xffff) | ((int)a.bs[3 * a.U + u] << 16);
     }
   }
 }

@@ -558,10 +558,11 @@ bool mv_pick_lanes(int fmt, int units, bool glu, bool big, int* L_out, int* upt_
   const int uw = unit_weights(fmt);
   // Units a lane keeps in registers, at most.  More of them lets fewer lanes share a row with none idle (80 units:
   // 16 lanes x 5 instead of 32 x 3 with five lanes idle) at the price of registers, i.e. of resident warps.
-  // Measured on 151936-row matrices and the 4B model's shapes: five pays for Q6_K and Q2_K rows, for the gated
-  // Q4_K product and for large Q4_K matrices (BIG: past 16 MB), three for the rest; Q8_0's 32-wide units go up to
-  // seven, four lanes a row.
-  const int upt_max = fmt == ILL_Q8_0 ? 7 : uw == 32 ? 5 : (fmt == ILL_Q4_K && !glu) ? (big ? 5 : 3) : ((fmt == ILL_Q6_K || fmt == ILL_Q2_K) && !glu) || (fmt == ILL_Q4_K && glu) ? 5 : 3;
+  // Measured on 151936-row matrices and the 4B model's shapes: five pays for Q6_K rows, for the gated Q4_K product
+  // and for large Q4_K matrices (BIG: past 16 MB), three for the rest -- Q2_K too, which is bound by instructions
+  // and at five units (154 registers) keeps one CTA resident where three units keep two (81 us against 62 on
+  // 151936 x 5120); Q8_0's 32-wide units go up to seven, four lanes a row.
+  const int upt_max = fmt == ILL_Q8_0 ? 7 : uw == 32 ? 5 : (fmt == ILL_Q4_K && !glu) ? (big ? 5 : 3) : (fmt == ILL_Q6_K && !glu) || (fmt == ILL_Q4_K && glu) ? 5 : 3;
   int bestL = 0, bestU = 0;
   double best = -1.0;
   for (int L = 32; L >= (fmt == ILL_Q8_0 ? 4 : 8); L >>= 1) {
@@ -615,7 +616,9 @@ static int plan_one(int fmt, long long total_rows, int cols, int nseg, bool glu,
     // rows per warp tile: about 3 KB a stage (small stages keep more CTAs resident, which is what
     // hides the copy latency), and small matrices are cut finer so that every warp gets some
     const long long warps = (long long)sm_count() * 16;
-    tr = 3072 / row_bytes;
+    // (Q2_K is bound by instructions, not by HBM: twice the stage halves what a tile costs it in waits, address
+    // arithmetic and copies issued; IQ2_XXS, with 48 KB of tables a CTA, does better with two small CTAs resident)
+    tr = (fmt == ILL_Q2_K ? 6144 : 3072) / row_bytes;
     const long long share = (total_rows * nseg + warps - 1) / warps;
     if (tr > share) tr = share;
     if (g_env_TR) tr = g_env_TR;
