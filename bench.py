@@ -1,19 +1,27 @@
 #!/usr/bin/env python
-"""bench.py -- quantized matvec weight GB/s on the Qwen3-4B Q4_K_M decode shapes.
+"""bench.py -- quantized matvec weight GB/s on the Qwen3-4B Q4_K_M decode shapes, and the rest of the path's
+configurations beside it.
 
-One "step" is every in-scope kernel of one decoded token of the Qwen3-4B
-architecture (36 layers; Q/K/O/gate/up in Q4_K, V/down in Q6_K, a Q6_K output
-head of 151936 rows): activation quantization and the dequant-fused matrix x
-vector products, in the order the reference's CUDA-FORWARD-N issues them
-(src/cuda-dense.lisp:380-432), on seeded synthetic blocks.  Attention, RoPE and
-normalisation are not part of the path and are not run.
+One "step" is every in-scope kernel of one decoded token of the Qwen3-4B architecture (36 layers; Q/K/O/gate/up
+in Q4_K, V/down in Q6_K, a Q6_K output head of 151936 rows): activation quantization and the dequant-fused matrix
+x vector products, in the order the reference's CUDA-FORWARD-N issues them (src/cuda-dense.lisp:380-432), on
+seeded synthetic blocks.  Attention, RoPE and normalisation are not part of the path and are not run.
 
-  value     weight bytes of a step / device time of a step, weights resident
-            in HBM, every step reading all 2.6 GB cold (far larger than L2)
-  e2e       the same through host buffers: the token's activations go up from
-            pinned memory and the logits come back, inside the timed region
-  roofline  the Q4_K gate/up product (the kernel most of the bytes go through)
-  formats   each of the five formats on one large matrix, cold
+  value / ms_per_step  weight bytes of a step / device time of a step, weights resident in HBM, every step
+                       reading all 2.6 GB cold (far larger than L2); one replica per GPU (the decode products do
+                       not shard), so across N this key is weak scaling of independent copies
+  e2e                  the same through host buffers: the token's activations go up from pinned memory and the
+                       logits come back, inside the timed region
+  roofline             the Q4_K gate/up product (the kernel most of the bytes go through)
+  formats              each of the five formats on one 151936-row matrix, cold
+  configs              the other configurations: c1 (Q8_0 0.5B token), c2_chain (the 4B token with RMSNorm and
+                       every quantization fused, product by product and as one launch), c2_prefill_512, c3 (Q6_K
+                       27B-scale matrices at batch 1 / 4 / 16), c4_decode (one token through an MoE layer)
+  sharded              THE CURVES THAT SCALE WITH N: moe_prefill (c4, one 4096-token chunk, experts placed
+                       expert-parallel), c5 (288 experts, Zipf: 64-sequence decode and an 8192-token prefill),
+                       head_rowsplit (the 151936 x 5120 Q6_K head split by rows) -- each with `vs_1gpu` (the same
+                       work timed on rank 0 alone in the same run) and `parity` (checked against the CPU oracle or
+                       the one-GPU product, outside the timed regions)
 
 Usage: python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 """
@@ -38,6 +46,8 @@ LAYER_MATS = [("q", Q4_K, QDIM, HIDDEN), ("k", Q4_K, KVDIM, HIDDEN), ("v", Q6_K,
               ("o", Q4_K, HIDDEN, QDIM), ("gate", Q4_K, FFN, HIDDEN), ("up", Q4_K, FFN, HIDDEN),
               ("down", Q6_K, HIDDEN, FFN)]
 HEAD = ("head", Q6_K, VOCAB, HIDDEN)
+C1 = dict(hidden=896, qdim=896, kvdim=128, ffn=4864, vocab=151936, layers=24)
+EPS = 1e-6
 
 
 def peaks():
@@ -53,6 +63,15 @@ def tensor_peak():
     if os.path.exists(p):
         return float(json.load(open(p))["bf16_tflops"]), "measured"
     return 1590.0, "fallback"
+
+
+def profiled_traffic(name):
+    """dram bytes read + written per launch, from the JSON beside the ncu summary under profiles/ (None if absent)."""
+    p = os.path.join(ROOT, "profiles", name)
+    if not os.path.exists(p):
+        return None
+    d = json.load(open(p))
+    return float(d["dram_bytes_read"]) + float(d["dram_bytes_written"])
 
 
 class ClockSampler:
@@ -109,73 +128,222 @@ def weight_bytes():
     return per_layer * LAYERS + matrix_bytes(HEAD[1], HEAD[2], HEAD[3]), per_layer
 
 
-# ------------------------------------------------------------------ reference arm
+# ------------------------------------------------------------------ the CPU legs (the oracle, timed)
 
-def run_reference(args, rank, world):
-    """The reference's CPU path (its C restatement, oracle/) on the host cores:
-    a step is one layer's seven products plus their activation quantization."""
-    if rank != 0:
-        return
+def cpu_layer_gbs(fast, seconds, cores):
+    """One layer of the workload (its seven products and their activation quantization) on the host cores:
+    FAST = the AVX2 row dots on pinned threads, else the portable loops.  (GB/s, repetitions, seconds, bytes)."""
     from oracle import oracle as O
     from illatio_b200 import blocks as B
     O.build()
-    cores = len(os.sched_getaffinity(0))
-    mats = [(n, f, r, c, B.synth_matrix(f, r, c, seed=10 + i)) for i, (n, f, r, c) in enumerate(LAYER_MATS)]
-    rng = np.random.default_rng(0)
-    xs = {c: rng.standard_normal(c).astype(np.float32) for c in (HIDDEN, QDIM, FFN)}
-    nbytes = sum(m[4].size for m in mats)
-
-    def step():
-        for _, f, r, c, w in mats:
-            act = O.quantize_act(f, xs[c])
-            O.matvec(f, w, r, c, act, threads=cores)
-
-    for _ in range(max(1, min(args.warmup, 2))):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    dt = (time.perf_counter() - t0) / args.steps
-    gbs = nbytes / dt / 1e9
-    sample = "one layer of the workload (7 products, %.1f MB of blocks) per step, portable-order C port, rows split over %d threads" % (nbytes / 1e6, cores)
-    print(json.dumps({
-        "impl": "reference", "metric": "quant matvec weight GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 dots, fp32 accumulate",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
-
-
-# ------------------------------------------------------------------ our arm
-
-def cpu_baseline_sample(seconds=10.0):
-    """The oracle timed on this box's host cores on one layer of the workload."""
-    from oracle import oracle as O
-    from illatio_b200 import blocks as B
-    O.build()
-    cores = len(os.sched_getaffinity(0))
     mats = [(f, r, c, B.synth_matrix(f, r, c, seed=10 + i)) for i, (_, f, r, c) in enumerate(LAYER_MATS)]
     rng = np.random.default_rng(0)
     xs = {c: rng.standard_normal(c).astype(np.float32) for c in (HIDDEN, QDIM, FFN)}
     nbytes = sum(m[3].size for m in mats)
-
-    def step():
-        for f, r, c, w in mats:
-            O.matvec(f, w, r, c, O.quantize_act(f, xs[c]), threads=cores)
-
-    step()
-    t0 = time.perf_counter()
-    reps = 0
-    while True:
+    prev = O.set_fast(fast)
+    try:
+        def step():
+            for f, r, c, w in mats:
+                O.matvec(f, w, r, c, O.quantize_act(f, xs[c]), threads=cores)
         step()
-        reps += 1
-        if time.perf_counter() - t0 > seconds or reps >= 100000:
-            break
-    dt = (time.perf_counter() - t0) / reps
-    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": "one layer of the workload (%.1f MB of blocks), %d repetitions, %.1f s" % (nbytes / 1e6, reps, dt * reps)}
+        t0 = time.perf_counter()
+        reps = 0
+        while True:
+            step()
+            reps += 1
+            if time.perf_counter() - t0 > seconds or reps >= 100000:
+                break
+        dt = (time.perf_counter() - t0) / reps
+    finally:
+        O.set_fast(prev)
+    return nbytes / dt / 1e9, reps, dt * reps, nbytes
+
+
+def cpu_moe_layer(seconds, cores):
+    """One token through the c4 layer's routed experts (6 of them) on the host cores, AVX2 on pinned threads:
+    the reference's own CPU fast path for these formats (src/avx2.lisp:77-150; "80 us an expert across the cores")."""
+    from oracle import oracle as O
+    from illatio_b200 import blocks as B
+    d, ff, nu = 4096, 2048, 6
+    gate, up = (B.synth_matrix(B.IQ2_XXS, nu * ff, d, seed=s) for s in (41, 42))
+    down = B.synth_matrix(B.Q2_K, nu * d, ff, seed=43)
+    x = np.random.default_rng(1).standard_normal(d).astype(np.float32)
+    sel, w = np.arange(nu, dtype=np.int32), np.full(nu, 1.0 / nu, np.float32)
+    nbytes = gate.size + up.size + down.size
+    out = {}
+    for name, fast in (("avx2_pinned", True), ("portable", False)):
+        if fast and not O.simd_available():
+            continue
+        prev = O.set_fast(fast)
+        try:
+            O.moe_routed(d, ff, B.IQ2_XXS, B.Q2_K, gate, up, down, x, sel, w, 10.0, threads=cores)
+            t0, reps = time.perf_counter(), 0
+            while time.perf_counter() - t0 < seconds:
+                O.moe_routed(d, ff, B.IQ2_XXS, B.Q2_K, gate, up, down, x, sel, w, 10.0, threads=cores)
+                reps += 1
+            dt = (time.perf_counter() - t0) / reps
+        finally:
+            O.set_fast(prev)
+        out[name] = {"us_per_token_layer": dt * 1e6, "GBps": nbytes / dt / 1e9, "us_per_expert": dt * 1e6 / nu}
+    out["sample"] = "6 experts (IQ2_XXS gate / up, Q2_K down, %.1f MB) of one token, %d threads" % (nbytes / 1e6, cores)
+    return out
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU path (its C restatement, oracle/) on the host cores: a step is one layer's seven
+    products plus their activation quantization.  The line's value is the fast form -- AVX2 integer dots on a
+    pool of pinned threads, how the reference runs its own CPU share -- and the portable loops are timed beside it."""
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    cores = len(os.sched_getaffinity(0))
+    fast = O.simd_available()
+    budget = max(2.0, min(20.0, 0.5 * args.steps))
+    gbs, reps, secs, nbytes = cpu_layer_gbs(fast, budget, cores)
+    port_gbs = cpu_layer_gbs(False, 3.0, cores)[0] if fast else gbs
+    sample = ("one layer of the workload (7 products, %.1f MB of blocks) per step, %s, rows split over %d threads"
+              % (nbytes / 1e6, "AVX2 row dots on pinned threads" if fast else "portable-order C port", cores))
+    print(json.dumps({
+        "impl": "reference", "metric": "quant matvec weight GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": nbytes / gbs / 1e6, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 dots, fp32 accumulate",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample, "repetitions": reps, "seconds": secs},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
+                         "portable_scalar_GBps": port_gbs},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------ helpers of the GPU arm
+
+def graph_of(fn, torch):
+    """FN captured in a CUDA graph (after one eager run)."""
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    return g
+
+
+def time_us(fn, reps, torch, warm=3):
+    """Microseconds per call of FN, CUDA events on the current stream."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def build_chain_model(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed):
+    """The in-scope products of a dense transformer with the attention stood in for by its query vector: per
+    layer q / k / v <- rmsnorm(h); h += o(q); fa <- glu(rmsnorm(h)); h += down(fa); then the head on rmsnorm(h)."""
+    hidden, qdim, kvdim, ffn, vocab = dims
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+
+    def mat(fmt, rows, cols, s):
+        return D.CMat("m", fmt, rows, cols, B.synth_matrix_torch(fmt, rows, cols, seed=s, device=dev))
+    m = {"dims": dims, "layers": []}
+    for li in range(layers):
+        s = 100 * li + seed
+        m["layers"].append(dict(q=mat(fmt_main, qdim, hidden, s + 1), k=mat(fmt_main, kvdim, hidden, s + 2),
+                                v=mat(fmt_alt, kvdim, hidden, s + 3), o=mat(fmt_main, hidden, qdim, s + 4),
+                                gate=mat(fmt_main, ffn, hidden, s + 5), up=mat(fmt_main, ffn, hidden, s + 6),
+                                down=mat(fmt_alt, hidden, ffn, s + 7),
+                                nw1=torch.rand(hidden, device=dev, generator=g) + 0.5,
+                                nw2=torch.rand(hidden, device=dev, generator=g) + 0.5))
+    m["head"] = mat(fmt_alt, vocab, hidden, seed + 99)
+    m["nwf"] = torch.rand(hidden, device=dev, generator=g) + 0.5
+    f = dict(dtype=torch.float32, device=dev)
+    m["h"], m["q"], m["k"], m["v"] = torch.empty(hidden, **f), torch.empty(qdim, **f), torch.empty(kvdim, **f), torch.empty(kvdim, **f)
+    m["fa"], m["logits"] = torch.empty(ffn, **f), torch.empty(vocab, **f)
+    m["x0"] = torch.randn(hidden, device=dev, generator=g)
+    m["bytes"] = sum(w.nbytes for L in m["layers"] for w in L.values() if isinstance(w, D.CMat)) + m["head"].nbytes
+    return m
+
+
+def chain_ops(D, m):
+    ops = []
+    for L in m["layers"]:
+        ops += [D.decode_op(L["q"], m["h"], m["q"], norm_w=L["nw1"], eps=EPS, after=True),
+                D.decode_op(L["k"], m["h"], m["k"], norm_w=L["nw1"], eps=EPS, after=False),
+                D.decode_op(L["v"], m["h"], m["v"], norm_w=L["nw1"], eps=EPS, after=False),
+                D.decode_op(L["o"], m["q"], m["h"], acc=True, after=True),
+                D.decode_op(L["gate"], m["h"], m["fa"], w2=L["up"], norm_w=L["nw2"], eps=EPS, after=True),
+                D.decode_op(L["down"], m["fa"], m["h"], acc=True, after=True)]
+    ops.append(D.decode_op(m["head"], m["h"], m["logits"], norm_w=m["nwf"], eps=EPS, after=True))
+    return ops
+
+
+def chain_per_product(D, m, acts):
+    """The same chain, a launch per product and per quantization (RMSNorm fused with the quantizer)."""
+    hidden, qdim, kvdim, ffn, vocab = m["dims"]
+    n = 0
+    for L in m["layers"]:
+        a = D.rmsnorm_q8(m["h"], L["nw1"], acts[("h", D.matrix_act_kind(L["q"]))], hidden, EPS)
+        D.cmat_mul(L["q"], a, m["q"], 1)
+        D.cmat_mul(L["k"], a, m["k"], 1)
+        n += 3
+        if D.matrix_act_kind(L["v"]) != a.kind:
+            a = D.rmsnorm_q8(m["h"], L["nw1"], acts[("h", D.matrix_act_kind(L["v"]))], hidden, EPS)
+            n += 1
+        D.cmat_mul(L["v"], a, m["v"], 1)
+        D.cmat_mul(L["o"], D.quant_q8(m["q"], acts[("q", D.matrix_act_kind(L["o"]))]), m["h"], 1, acc=True)
+        a = D.rmsnorm_q8(m["h"], L["nw2"], acts[("h", D.matrix_act_kind(L["gate"]))], hidden, EPS)
+        D.glu_mul(L["gate"], L["up"], a, m["fa"])
+        D.cmat_mul(L["down"], D.quant_q8(m["fa"], acts[("fa", D.matrix_act_kind(L["down"]))]), m["h"], 1, acc=True)
+        n += 7
+    a = D.rmsnorm_q8(m["h"], m["nwf"], acts[("h", D.matrix_act_kind(m["head"]))], hidden, EPS)
+    D.cmat_mul(m["head"], a, m["logits"], 1)
+    return n + 2
+
+
+def chain_leg(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed, peak, name):
+    """A token's chain both ways, timed; and that the two give the same logits."""
+    m = build_chain_model(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed)
+    hidden, qdim, kvdim, ffn, vocab = dims
+    acts = {(k, kind): D.make_qact(n, kind, device=dev) for k, n in (("h", hidden), ("q", qdim), ("fa", ffn)) for kind in ("q8", "q8k")}
+    launches = [0]
+
+    def per_product():
+        m["h"].copy_(m["x0"])
+        launches[0] = chain_per_product(D, m, acts) + 1
+    plan = D.DecodePlan(chain_ops(D, m), device=dev)
+
+    def one_launch():
+        m["h"].copy_(m["x0"])
+        plan.run()
+    per_product()
+    torch.cuda.synchronize()
+    want = m["logits"].clone()
+    m["logits"].zero_()
+    one_launch()
+    torch.cuda.synchronize()
+    same = bool(torch.equal(m["logits"], want)) and bool(torch.isfinite(want).all())
+    g = graph_of(per_product, torch)
+    us_pp = time_us(g.replay, 10, torch)
+    us_one = time_us(one_launch, 10, torch)
+    out = {"workload": name, "weight_MB": m["bytes"] / 1e6,
+           "per_product": {"us_per_token": us_pp, "GBps": m["bytes"] / us_pp / 1e3, "frac_of_hbm": m["bytes"] / us_pp / 1e3 / peak,
+                           "launches": launches[0], "how": "one CUDA graph of the token's launches"},
+           "one_launch": {"us_per_token": us_one, "GBps": m["bytes"] / us_one / 1e3, "frac_of_hbm": m["bytes"] / us_one / 1e3 / peak,
+                          "launches": 1, "products": plan.n, "how": "ill_decode_run: one cooperative launch, a barrier between dependent products"},
+           "parity": {"one_launch_equals_per_product_bits": same}}
+    del m, plan, g
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -184,9 +352,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-formats", action="store_true", help="skip the per-format sweep")
-    ap.add_argument("--no-moe", action="store_true", help="skip the mixture-of-experts layer")
+    ap.add_argument("--no-moe", action="store_true", help="skip the mixture-of-experts legs")
+    ap.add_argument("--no-configs", action="store_true", help="skip the c1 / c2_chain / c3 / c4_decode legs")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -205,8 +374,23 @@ def main():
     _lib.lib()  # fails loudly if the CUDA library is missing
     torch.cuda.set_device(local_rank)
     if world > 1:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
+    peak, which = peaks()
+    tpeak, twhich = tensor_peak()
+    cores = len(os.sched_getaffinity(0))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(vals):
+        t = torch.tensor(vals, device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
 
     # ---- the model's matrices (random-init, seeded), resident in HBM
     layers = []
@@ -238,6 +422,7 @@ def main():
     # hidden state is quantized once per step and stands for each layer's normed input, and the
     # attention output is quantized before the timed region.  The quantization after the gated
     # product is the reference's own stand-alone quant_q8 launch (src/cuda-dense.lisp:417).
+    # (configs.c2_chain runs the same token with the norms and every quantization inside.)
     D.quant_q8(att, act_q)
 
     def token_step():
@@ -252,24 +437,11 @@ def main():
         D.cmat_mul(head, act_d, logits, 1); n += 1
         launches_per_step[0] = n
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     # eager warm-up, then one CUDA graph of a step (removes host launch cost from the device number)
     for _ in range(args.warmup):
         h.zero_()
         token_step()
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(graph, stream=side):
-            token_step()
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
+    graph = graph_of(token_step, torch)
     for _ in range(args.warmup):
         graph.replay()
     barrier()
@@ -302,24 +474,13 @@ def main():
     # CUDA graph (36 launches, each on its own layer's matrices: cold), timed with events
     glu_bytes = 2 * B.matrix_bytes(Q4_K, FFN, HIDDEN) + HIDDEN * (1 + 4 / 256 + 2 / 16) + 4 * FFN
     D.quant_q8(x, act_d)
-    torch.cuda.synchronize()
-    ggraph = torch.cuda.CUDAGraph()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(ggraph, stream=side):
-            for L in layers:
-                D.glu_mul(L["gate"], L["up"], act_d, fa)
-    torch.cuda.synchronize()
-    for _ in range(3):
-        ggraph.replay()
-    torch.cuda.synchronize()
-    reps = 10
-    e0.record()
-    for _ in range(reps):
-        ggraph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    glu_us = e0.elapsed_time(e1) * 1e3 / (reps * LAYERS)
+
+    def all_glu():
+        for L in layers:
+            D.glu_mul(L["gate"], L["up"], act_d, fa)
+    ggraph = graph_of(all_glu, torch)
+    glu_us = time_us(ggraph.replay, 10, torch) / LAYERS
+    del ggraph
 
     # ---- each format on one large matrix, cold (two copies, alternating, each larger than L2)
     formats = {}
@@ -332,163 +493,384 @@ def main():
             act = D.make_qact(cols, D.matrix_act_kind(ms_[0]), device=dev)
             D.quant_q8(xx, act)
             y = torch.empty(rows, device=dev)
-            for i in range(4):
-                D.cmat_mul(ms_[i & 1], act, y, 1)
-            torch.cuda.synchronize()
-            e0.record()
-            for i in range(10):
-                D.cmat_mul(ms_[i & 1], act, y, 1)
-            e1.record()
-            torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / 10
+            it = [0]
+
+            def one():
+                D.cmat_mul(ms_[it[0] & 1], act, y, 1)
+                it[0] += 1
+            us = time_us(one, 10, torch, warm=4)
             nb = ms_[0].nbytes
-            formats[B.NAMES[fmt]] = {"rows": rows, "cols": cols, "MB": nb / 1e6, "us": us, "GBps": nb / us / 1e3}
+            formats[B.NAMES[fmt]] = {"rows": rows, "cols": cols, "MB": nb / 1e6, "us": us, "GBps": nb / us / 1e3,
+                                     "frac_of_%s_hbm" % which: nb / us / 1e3 / peak}
             del ms_
             torch.cuda.empty_cache()
 
-    # free the sweep's matrices before the mixture-of-experts layer is built
+    clocks = sampler.stop() if rank == 0 else None  # sampled over the headline's timed regions and the kernels above
+    ms, e2e_ms = max_over_ranks([ms, e2e_ms])
+    # the headline's buffers are done with: make room for the other configurations
+    del layers, head, graph
     torch.cuda.empty_cache()
 
-    # ---- the sharded paths: (1) the row-split output head with an all-gather of the logits,
-    # (2) one DeepSeek-V4-Flash-shaped MoE layer (configs[3]) over a 4096-token chunk, experts placed
-    # expert-parallel (256 / N per rank), tokens split by position (strong scaling)
-    from illatio_b200 import ep as EP
-    from illatio_b200 import microbench_moe as MB
-    first_row, end_row = EP.head_rows(VOCAB, world, rank)
-    rb = B.row_bytes(HEAD[1], HIDDEN)
-    head_slice = D.CMat("head_slice", HEAD[1], end_row - first_row, HIDDEN, head.qs[first_row * rb:end_row * rb])
-    for _ in range(3):
-        EP.head_mul_allgather(head_slice, act_d, logits, VOCAB)
-    barrier()
-    e0.record()
-    for _ in range(20):
-        EP.head_mul_allgather(head_slice, act_d, logits, VOCAB)
-    e1.record()
-    barrier()
-    head_us = e0.elapsed_time(e1) * 1e3 / 20
+    # ---- the other configurations, one GPU's worth each (rank 0 reports; every rank runs them, replicas)
+    configs = {}
+    if not args.no_configs:
+        configs["c2_chain"] = chain_leg(D, B, torch, dev, (HIDDEN, QDIM, KVDIM, FFN, VOCAB), LAYERS, Q4_K, Q6_K, 1 + rank, peak,
+                                        "configs[1] with RMSNorm and every activation quantization inside: q/k/v <- norm(h); h += o(q); "
+                                        "fa <- glu(norm(h)); h += down(fa); head(norm(h))")
+        configs["c1_token"] = chain_leg(D, B, torch, dev, (C1["hidden"], C1["qdim"], C1["kvdim"], C1["ffn"], C1["vocab"]), C1["layers"],
+                                        Q8_0, Q8_0, 3 + rank, peak, "configs[0]: qwen2.5-0.5b, all Q8_0, one token (same chain)")
+        configs["c2_prefill_512"] = {"status": "not built",
+                                     "why": "the dense prefill GEMMs for Q8_0 / Q4_K / Q6_K (mm_q8_mma2, mm_q4k_mma, mm_q6k_mma: "
+                                            "src/cuda/dense.cu:885, src/cuda/kquant.cu:316-466) have no tensor-core kernel here yet; "
+                                            "the several-token matvec stops at 16 tokens"}
+        configs["c3_q6k_sweep"] = c3_sweep(D, B, torch, dev, peak, which)
+        configs["c4_decode"] = c4_decode(D, B, torch, dev, peak)
 
-    moe = None
+    # ---- the sharded paths
+    sharded = {}
     if not args.no_moe:
-        cfg = MB.CONFIGS["c4"]
-        n_tok = 4096
-        per = cfg["ne"] // world
-        pool = MB.make_pool(cfg, n_local=per, first=rank * per, seed=7, device=dev)
-        gm = torch.Generator(device=dev)
-        gm.manual_seed(11)  # the same chunk on every rank; each takes its slice of the tokens
-        norms_all = torch.randn(n_tok, cfg["d"], device=dev, generator=gm)
-        logits_all = MB.router_logits(cfg, n_tok, seed=12, device=dev)
-        lo, hi = rank * n_tok // world, (rank + 1) * n_tok // world
-        norms_l, logits_l = norms_all[lo:hi].contiguous(), logits_all[lo:hi].contiguous()
-        del norms_all, logits_all
-        ce = EP.CudaExperts(pool, cfg["nu"], 10.0)
-        # A stream of independent chunks.  The exchanges have a fixed size (half again the even share of rows
-        # from every rank to every rank), so nothing on the host waits for the routing; a slab that turned out
-        # too small would raise a flag, checked after the timed region.  (ILL_EP_LANES=2 alternates the chunks
-        # between two CUDA streams; measured, it gains nothing: the persistent product kernel holds every SM, so
-        # the other stream's exchange kernels do not run beside it.)
-        nlanes = int(os.environ.get("ILL_EP_LANES", "1"))
-        exact = os.environ.get("ILL_EP_MODE", "capacity") == "exact"
-        peer_combine = world > 1 and not exact and os.environ.get("ILL_EP_COMBINE", "peer") == "peer"
-        mk = (lambda: EP.EpScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev)) if exact else \
-             (lambda: EP.EpCapScratch(pool, hi - lo, cfg["nu"], cfg["ne"], world, device=dev, peer=peer_combine))
-        try:
-            lanes = [(torch.cuda.Stream(device=dev), mk()) for _ in range(nlanes)]
-            made = 1
-        except Exception as exc:  # no peer mapping on this box: the same exchanges over NCCL
-            print("rank %d: symmetric memory unavailable (%s)" % (rank, exc), file=sys.stderr)
-            made = 0
-        if peer_combine:  # every rank takes the same path
-            agree = torch.tensor([made], device=dev)
-            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
-            if agree.item() == 0:
-                peer_combine = False
-                lanes = [(torch.cuda.Stream(device=dev), mk()) for _ in range(nlanes)]
-        flags = []
+        from illatio_b200 import ep as EP
+        from illatio_b200 import microbench_moe as MB
+        sharded["head_rowsplit"] = head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_over_ranks)
+        sharded["moe_prefill"] = moe_leg(D, B, EP, MB, torch, dist, dev, rank, world, cores, "c4", 4096, tpeak, twhich, barrier,
+                                         max_over_ranks, interleave=False)
+        sharded["c5_prefill"] = moe_leg(D, B, EP, MB, torch, dist, dev, rank, world, cores, "c5", 8192, tpeak, twhich, barrier,
+                                        max_over_ranks, interleave=True)
+        sharded["c5_decode_64"] = moe_leg(D, B, EP, MB, torch, dist, dev, rank, world, cores, "c5", 64, tpeak, twhich, barrier,
+                                          max_over_ranks, interleave=True, check=False)
 
-        def run_chunks(k):
-            main = torch.cuda.current_stream()
-            for s_, _ in lanes:
-                s_.wait_stream(main)
-            for i in range(k):
-                s_, esc = lanes[i % nlanes]
-                with torch.cuda.stream(s_):
-                    if exact:
-                        EP.chunk_fast(ce, esc, norms_l, logits_l, cfg["ne"])
-                    else:
-                        flags.append(EP.chunk_capacity(ce, esc, norms_l, logits_l, cfg["ne"])[1].clone())
-            for s_, _ in lanes:
-                main.wait_stream(s_)
-
-        run_chunks(4)
-        barrier()
-        reps = 12
-        e0.record()
-        run_chunks(reps)
-        e1.record()
-        barrier()
-        moe_ms = e0.elapsed_time(e1) / reps
-        mt = torch.tensor([moe_ms, head_us], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(mt, op=dist.ReduceOp.MAX)
-        moe_ms, head_us = mt.tolist()
-        flop = 2.0 * n_tok * cfg["nu"] * 3 * cfg["d"] * cfg["ff"]
-        moe = {"workload": "configs[3]: hidden 4096, 256 experts of FFN 2048, top-6, IQ2_XXS gate/up, Q2_K down; one 4096-token chunk through the routed experts",
-               "n_gpus": world, "experts_per_gpu": per, "tokens": n_tok, "ms_per_chunk": moe_ms, "chunks_in_flight": nlanes,
-               "exchange_sizes": "exact (one host synchronisation a chunk)" if exact else "fixed slabs, no host synchronisation",
-               "slab_overflows": int(sum(int(f.item()) for f in flags)),
-               "combine": ("fused into the down product: stores into the owners' memory over NVLink" if peer_combine
-                           else "NCCL all-to-all of fp32 rows" if world > 1 else "none (one GPU)"),
-               "tok_per_s": n_tok / moe_ms * 1e3, "tflops": flop / moe_ms / 1e9, "scaling": "strong",
-               "roofline": {"bound": "tensor", "achieved": flop / moe_ms / 1e9 / world, "peak": tensor_peak()[0],
-                            "peak_source": tensor_peak()[1], "unit": "TFLOP/s per GPU, whole chunk (products and all the steps around them)",
-                            "frac": flop / moe_ms / 1e9 / world / tensor_peak()[0]},
-               "exchange": ("none (one GPU)" if world == 1 else
-                            "peer stores over NVLink: packed Q8_K rows out (1.14 B/value), fp32 rows back from the down product's epilogue"
-                            if peer_combine else "NCCL all-to-all of packed Q8_K rows out (1.14 B/value), fp32 rows back")}
-        del pool, ce, lanes
-
-    clocks = sampler.stop() if rank == 0 else None  # sampled over every timed region above
     status = D.device_status()
-    tmax = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = tmax.tolist()
     if rank == 0:
-        peak, which = peaks()
         value = world * total_bytes / (ms * 1e-3) / 1e9
         e2e = world * total_bytes / (e2e_ms * 1e-3) / 1e9
         achieved = glu_bytes / (glu_us * 1e-6) / 1e9
-        for f in formats.values():
-            f["frac_of_%s_hbm" % which] = f["GBps"] / peak
         out = {
             "metric": "quant matvec weight GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 x int8 -> int32 dots, fp32 accumulate", "data": "synthetic",
             "config": {"workload": WORKLOAD, "weight_bytes_per_step": total_bytes,
                        "l2": "every step reads 2.6 GB of distinct weights, far larger than the 126 MB L2",
-                       "replicas": "each rank decodes its own token on its own copy (the decode products do not shard)",
+                       "replicas": "each rank decodes its own token on its own copy (the decode products do not shard): across N "
+                                   "`value` is weak scaling of independent copies.  The curves that scale with N are under `sharded`: "
+                                   "moe_prefill.tok_per_s, c5_prefill.tok_per_s and head_rowsplit.n1.us_per_token, each with vs_1gpu and parity",
                        "launch": "one CUDA graph of the step's %d kernel launches" % launches_per_step[0]},
             "frac_of_%s_hbm" % which: value / world / peak,
             "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": HIDDEN * 4,
                     "d2h_bytes_per_step": VOCAB * 4},
             "gpu_launches": launches_per_step[0] * args.steps,
             "roofline": {"bound": "hbm", "kernel": "mvw_kernel<Q4_K, gated> (gate/up 2 x 9728x2560)",
-                         "achieved": achieved, "peak": peak, "peak_source": which + " (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else which,
+                         "achieved": achieved, "peak": peak,
+                         "peak_source": which + " (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else which,
                          "unit": "GB/s", "frac": achieved / peak,
-                         # dram__bytes_read + write of one launch, from the ncu capture summarised under profiles/
-                         "traffic": 28059904.0,
+                         "traffic": profiled_traffic("mvw_q4k_glu_9728x2560.json"),
                          "us_per_launch": glu_us, "algorithmic_bytes_per_launch": glu_bytes},
-            "clocks": clocks, "formats": formats, "device_status": status,
-            "head_rowsplit": {"rows_per_gpu": end_row - first_row, "us_per_token": head_us,
-                              "GBps": B.matrix_bytes(HEAD[1], VOCAB, HIDDEN) / head_us / 1e3,
-                              "collective": "in-place all-gather of fp32 logits" if world > 1 else "none (one GPU)"},
-            "moe_prefill": moe,
+            "clocks": clocks, "formats": formats, "device_status": status, "configs": configs, "sharded": sharded,
         }
         if not args.no_cpu:
-            out["cpu_baseline"] = cpu_baseline_sample()
+            fast_ok = False
+            try:
+                from oracle import oracle as O
+                O.build()
+                fast_ok = O.simd_available()
+            except Exception:
+                pass
+            pg, preps, psecs, nb = cpu_layer_gbs(False, 6.0, cores)
+            out["cpu_baseline"] = {"value": pg, "unit": "GB/s", "cores": cores, "kind": "port",
+                                   "sample": "one layer of the workload (%.1f MB of blocks), portable scalar loops, %d repetitions, %.1f s"
+                                             % (nb / 1e6, preps, psecs)}
+            if fast_ok:
+                fg, freps, fsecs, _ = cpu_layer_gbs(True, 6.0, cores)
+                out["cpu_baseline"]["avx2"] = {"value": fg, "unit": "GB/s", "cores": cores, "kind": "port",
+                                               "sample": "the same layer, AVX2 row dots on a pool of pinned threads, %d repetitions, %.1f s" % (freps, fsecs)}
+            out["cpu_baseline"]["c4_moe_layer"] = cpu_moe_layer(3.0, cores)
         print(json.dumps(out))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------ configuration legs
+
+def c3_sweep(D, B, torch, dev, peak, which):
+    """configs[2]: the Q6_K matrices of a 27B-scale model at batch 1, 4 and 16, cold (a rotation of copies whose
+    total is larger than twice the L2)."""
+    out = {"format": "q6_k", "protocol": "copies rotated so that every launch reads its weights from HBM"}
+    for name, rows, cols in (("5120x5120", 5120, 5120), ("17408x5120", 17408, 5120), ("5120x17408", 5120, 17408),
+                             ("151936x5120", 151936, 5120)):
+        nb = B.matrix_bytes(Q6_K, rows, cols)
+        copies = max(2, int(-(-300e6 // nb)))
+        ms_ = [D.CMat("w", Q6_K, rows, cols, B.synth_matrix_torch(Q6_K, rows, cols, seed=70 + i, device=dev)) for i in range(copies)]
+        res = {"MB": nb / 1e6, "copies": copies}
+        for n in (1, 4, 16):
+            xx = torch.randn(n * cols, device=dev)
+            act = D.make_qact(n * cols, "q8k", device=dev)
+            D.quant_q8(xx, act)
+            y = torch.empty(n * rows, device=dev)
+
+            def sweep():
+                for w in ms_:
+                    D.cmat_mul(w, act, y, n)
+            gph = graph_of(sweep, torch)
+            us = time_us(gph.replay, 5, torch) / copies
+            res["n%d" % n] = {"us": us, "GBps": nb / us / 1e3, "frac_of_%s_hbm" % which: nb / us / 1e3 / peak}
+            del gph
+        out[name] = res
+        del ms_
+        torch.cuda.empty_cache()
+    return out
+
+
+def c4_decode(D, B, torch, dev, peak):
+    """configs[3] as decode: one token through one MoE layer (router given; 6 routed experts of 256 + the shared
+    Q8_0 expert), 16 tokens with different routings back to back; the shared expert rotates over six copies."""
+    from illatio_b200 import cuda_ds4f as M
+    from illatio_b200 import microbench_moe as MB
+    cfg = MB.CONFIGS["c4"]
+    d, ff, nu = cfg["d"], cfg["ff"], cfg["nu"]
+    pool = MB.make_pool(cfg, seed=7, device=dev)
+    shared = [[D.CMat("s", Q8_0, r, c, B.synth_matrix_torch(Q8_0, r, c, seed=500 + 3 * i + j, device=dev))
+               for j, (r, c) in enumerate(((ff, d), (ff, d), (d, ff)))] for i in range(6)]
+    T = 16
+    gg = torch.Generator(device=dev)
+    gg.manual_seed(21)
+    norms = torch.randn(T, d, device=dev, generator=gg)
+    logits = torch.randn(T, cfg["ne"], device=dev, generator=gg)
+    sel, w = M.route(logits, nu, mode=2)
+    sh_out, moe = torch.empty(d, device=dev), torch.empty(d, device=dev)
+
+    def tokens():
+        for t in range(T):
+            sg, su, sd = shared[t % 6]
+            M.dk_shared(sg, su, sd, norms[t], 10.0, sh_out)
+            M.dk_ffn_tail(pool, norms[t], sel[t], w[t], 10.0, shared=sh_out, moe=moe)
+    tokens()
+    us = time_us(tokens, 5, torch) / T
+    routed = nu * (2 * B.matrix_bytes(IQ2_XXS, ff, d) + B.matrix_bytes(Q2_K, d, ff))
+    sh_bytes = 3 * B.matrix_bytes(Q8_0, ff, d)
+    out = {"workload": "one token through the layer: shared expert (3 Q8_0 products) + 6 routed experts (IQ2_XXS gate / up fused, Q2_K down) + slot-order sum",
+           "us_per_token_layer": us, "MB": (routed + sh_bytes) / 1e6, "GBps": (routed + sh_bytes) / us / 1e3,
+           "frac_of_hbm": (routed + sh_bytes) / us / 1e3 / peak, "launches_per_token_layer": 12,
+           "how": "eager launches (allocations included), 16 tokens with different routings"}
+    del pool, shared
+    torch.cuda.empty_cache()
+    return out
+
+
+def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_over_ranks):
+    """configs[2]'s output head, 151936 x 5120 Q6_K, split by rows over the ranks, then an all-gather of the logits;
+    batch 1, 4 and 16.  Two copies of the rank's slice alternate so that the weights come from HBM.  The product
+    and the collective are also timed apart.  Parity: the gathered logits against rank 0's product of the whole
+    matrix (exact: a row's arithmetic does not depend on which rank multiplies it)."""
+    rows, cols = VOCAB, 5120
+    first, end = EP.head_rows(rows, world, rank)
+    rb = B.row_bytes(Q6_K, cols)
+
+    def slice_of(copy):
+        # every rank draws the whole matrix's stream and keeps its rows: any split is the same matrix
+        full = B.synth_matrix_torch(Q6_K, rows, cols, seed=880 + copy, device=dev)
+        s = full[first * rb:end * rb].clone()
+        del full
+        return D.CMat("head_slice", Q6_K, end - first, cols, s)
+    slices = [slice_of(0), slice_of(1)]
+    torch.cuda.empty_cache()
+    out = {"matrix": "151936 x 5120 Q6_K (638 MB)", "rows_per_gpu": end - first,
+           "collective": "in-place all-gather of fp32 logits (NCCL)" if world > 1 else "none (one GPU)",
+           "GBps_is": "the whole matrix's bytes over the time of the slowest rank: an aggregate over the ranks"}
+    nb = B.matrix_bytes(Q6_K, rows, cols)
+    for n in (1, 4, 16):
+        xx = torch.randn(n * cols, device=dev, generator=torch.Generator(device=dev).manual_seed(5))
+        act = D.make_qact(n * cols, "q8k", device=dev)
+        D.quant_q8(xx, act)
+        # the logits as [rank, token, the rank's rows]: every rank's product writes its own block, one in-place
+        # all-gather fills the rest (token t's logits are the ranks' blocks [:, t, :] side by side)
+        gathered = torch.zeros(world, n, end - first, device=dev)
+        part = gathered[rank]
+        it = [0]
+
+        def product_only():
+            w = slices[it[0] & 1]
+            it[0] += 1
+            D.cmat_mul(w, act, part, n)
+
+        def gather_only():
+            dist.all_gather_into_tensor(gathered, part)
+
+        def both():
+            product_only()
+            if world > 1:
+                gather_only()
+        barrier()
+        us_both = time_us(both, 20, torch)
+        barrier()
+        us_prod = time_us(product_only, 20, torch)
+        us_gather = 0.0
+        if world > 1:
+            barrier()
+            us_gather = time_us(gather_only, 20, torch)
+        us_both, us_prod, us_gather = max_over_ranks([us_both, us_prod, us_gather])
+        res = {"us_per_token": us_both, "GBps": nb / us_both / 1e3, "us_product": us_prod, "us_all_gather": us_gather,
+               "product_frac_of_hbm_per_gpu": (nb / world) / us_prod / 1e3 / peak}
+        if n == 1:
+            # parity and the one-GPU time, on rank 0 (the whole matrix, copy 0)
+            it[0] = 0
+            both()
+            torch.cuda.synchronize()
+            got = gathered.reshape(-1).clone()
+            vs = None
+            ok = None
+            if rank == 0:
+                full = D.CMat("head", Q6_K, rows, cols, B.synth_matrix_torch(Q6_K, rows, cols, seed=880, device=dev))
+                full2 = D.CMat("head", Q6_K, rows, cols, B.synth_matrix_torch(Q6_K, rows, cols, seed=881, device=dev))
+                want = torch.empty(rows, device=dev)
+                D.cmat_mul(full, act, want, 1)
+                torch.cuda.synchronize()
+                ok = bool(torch.equal(got, want))
+                j = [0]
+
+                def alone():
+                    D.cmat_mul((full, full2)[j[0] & 1], act, want, 1)
+                    j[0] += 1
+                us1 = time_us(alone, 20, torch)
+                vs = us1 / us_both
+                res["us_one_gpu_same_run"] = us1
+                del full, full2
+                torch.cuda.empty_cache()
+            barrier()
+            res["vs_1gpu"] = vs
+            res["parity"] = {"gathered_logits_equal_one_gpu_product": ok, "ranks": world}
+        out["n%d" % n] = res
+    del slices
+    torch.cuda.empty_cache()
+    return out
+
+
+def moe_leg(D, B, EP, MB, torch, dist, dev, rank, world, cores, cfg_name, n_tok, tpeak, twhich, barrier, max_over_ranks,
+            interleave, check=True):
+    """One chunk of N_TOK tokens through a layer's routed experts, experts placed expert-parallel over the ranks
+    (tokens split by position): time, tokens/s, rows per rank, slab overflows; the same chunk on rank 0 alone
+    (vs_1gpu); and 8 of every rank's tokens against the CPU oracle (parity)."""
+    from illatio_b200 import cuda_ds4f_prefill as P
+    cfg = MB.CONFIGS[cfg_name]
+    ne, nu, d, ff = cfg["ne"], cfg["nu"], cfg["d"], cfg["ff"]
+    per = ne // world
+    seed = 7
+    mine = MB.interleaved_experts(ne, world, rank) if interleave else list(range(rank * per, (rank + 1) * per))
+    order = MB.virtual_order(ne, world) if interleave else list(range(ne))
+    pool = MB.make_pool(cfg, seed=seed, device=dev, experts=mine)
+    gm = torch.Generator(device=dev)
+    gm.manual_seed(11)  # the same chunk on every rank; each takes its slice of the tokens
+    norms_all = torch.randn(n_tok, d, device=dev, generator=gm)
+    # the router's logits in the order the ranks hold the experts (its rows are permuted once, when a model is loaded)
+    logits_all = MB.router_logits(cfg, n_tok, seed=12, device=dev)[:, torch.tensor(order, device=dev)].contiguous()
+    lo, hi = rank * n_tok // world, (rank + 1) * n_tok // world
+    norms_l, logits_l = norms_all[lo:hi].contiguous(), logits_all[lo:hi].contiguous()
+    ce = EP.CudaExperts(pool, nu, 10.0)
+    peer = world > 1 and os.environ.get("ILL_EP_COMBINE", "peer") == "peer"
+    made = 1
+    try:
+        esc = EP.EpCapScratch(pool, hi - lo, nu, ne, world, device=dev, peer=peer)
+    except Exception as exc:  # no peer mapping on this box: the same exchanges over NCCL
+        print("rank %d: symmetric memory unavailable (%s)" % (rank, exc), file=sys.stderr)
+        made = 0
+    if peer:  # every rank takes the same path
+        agree = torch.tensor([made], device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if agree.item() == 0:
+            peer = False
+            esc = EP.EpCapScratch(pool, hi - lo, nu, ne, world, device=dev, peer=False)
+    flags = []
+
+    def chunk():
+        flags.append(EP.chunk_capacity(ce, esc, norms_l, logits_l, ne)[1].clone())
+    for _ in range(3):
+        chunk()
+    barrier()
+    reps = 12 if n_tok >= 1024 else 40
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        chunk()
+    e1.record()
+    barrier()
+    ms = max_over_ranks([e0.elapsed_time(e1) / reps])[0]
+    overflows = int(sum(int(f.item()) for f in flags))
+    rows_here = float(esc.total.item())
+    rmax = max_over_ranks([rows_here])[0]
+    rsum = torch.tensor([rows_here], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(rsum)
+    flop = 2.0 * n_tok * nu * 3 * d * ff
+    out = {"workload": "%s: hidden %d, %d experts of FFN %d, top-%d, %s gate/up, Q2_K down%s; one %d-token chunk through the routed experts"
+                       % (cfg_name, d, ne, ff, nu, B.NAMES[cfg["gate_fmt"]], ", Zipf(1.1) popularity" if cfg["zipf"] else "", n_tok),
+           "n_gpus": world, "experts_per_gpu": per, "tokens": n_tok, "ms_per_chunk": ms,
+           "placement": "interleaved (rank r holds experts r, r + N, ...; the router's rows permuted to match at load time)" if interleave
+                        else "contiguous blocks of experts",
+           "rows_per_rank": {"max": rmax, "mean": rsum.item() / world, "slab_rows": esc.cap * world},
+           "slab_overflows": overflows, "exchange_sizes": "fixed slabs, no host synchronisation",
+           "exchange": ("none (one GPU)" if world == 1 else
+                        "peer stores over NVLink: packed Q8_K rows out (1.14 B/value), fp32 rows back from the down product's epilogue"
+                        if peer else "NCCL all-to-all of packed Q8_K rows out (1.14 B/value), fp32 rows back"),
+           "tok_per_s": n_tok / ms * 1e3, "tflops": flop / ms / 1e9, "scaling": "strong",
+           "roofline": {"bound": "tensor", "achieved": flop / ms / 1e9 / world, "peak": tpeak, "peak_source": twhich,
+                        "unit": "TFLOP/s per GPU, whole chunk (products and all the steps around them)",
+                        "frac": flop / ms / 1e9 / world / tpeak}}
+    if n_tok < 1024:
+        out["note"] = ("batched decode run through the chunk driver (tensor-core products on few rows an expert); the "
+                       "matvec-path form with counts / bases (DK-FFN-SMALL, src/cuda-ds4f-spec.lisp:31-132) is not built")
+    got_l = esc.moe.clone()
+    sel_l = esc.sel.clone()
+    # ---- parity: 8 of this rank's tokens against the CPU oracle, which is given those tokens' experts only
+    # (any expert's bytes can be drawn again from its seed)
+    if check:
+        from oracle import oracle as O
+        O.build()
+        rng = np.random.default_rng(100 + rank)
+        toks = np.unique(np.concatenate([[0, hi - lo - 1], rng.integers(0, hi - lo, 6)]))
+        lg = logits_l[torch.as_tensor(toks, device=dev)].cpu().numpy()
+        osel, ow = O.route(lg, nu, mode=2)
+        sel_h = sel_l[torch.as_tensor(toks, device=dev)].cpu().numpy()
+        got = got_l[torch.as_tensor(toks, device=dev)].cpu().numpy()
+        nm = norms_l[torch.as_tensor(toks, device=dev)].cpu().numpy()
+        worst, checked = 0.0, 0
+        threads = max(1, cores // world)
+        for i in range(len(toks)):
+            if not np.array_equal(sel_h[i], osel[i]):
+                continue  # expf's last place swapped two near-equal experts: not this token
+            parts = []
+            for tensor, (fmt, rows, cols) in enumerate(((cfg["gate_fmt"], ff, d), (cfg["gate_fmt"], ff, d), (B.Q2_K, d, ff))):
+                parts.append(np.concatenate([B.synth_matrix_torch(fmt, rows, cols, seed=MB.expert_seed(seed, tensor, order[int(v)]),
+                                                                  device=dev).cpu().numpy() for v in osel[i]]))
+            want = O.moe_routed(d, ff, cfg["gate_fmt"], B.Q2_K, parts[0], parts[1], parts[2], nm[i], np.arange(nu, dtype=np.int32),
+                                ow[i], 10.0, threads=threads)
+            worst = max(worst, float(np.abs(got[i] - want).max() / np.abs(want).max()))
+            checked += 1
+        worst, nchecked = max_over_ranks([worst, -float(checked)])
+        tot = torch.tensor([float(checked)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tot)
+        out["parity"] = {"max_rel_err": worst, "tokens_checked": int(tot.item()), "ranks": world, "bound": 2e-3,
+                         "ok": bool(worst < 2e-3 and tot.item() >= 4 * world and overflows == 0)}
+    del esc, ce, pool
+    torch.cuda.empty_cache()
+    # ---- the same chunk on rank 0 alone, every expert on its GPU
+    vs = None
+    if world > 1:
+        if rank == 0:
+            full = MB.make_pool(cfg, seed=seed, device=dev, experts=order)
+            sc = P.make_chunk_scratch(full, n_tok, nu, device=dev)
+
+            def alone():
+                P.dk_ffn_routed_chunk(full, norms_all, logits_all, nu, 10.0, sc)
+            ms1 = time_us(alone, 6, torch) / 1e3
+            vs = ms1 / ms
+            out["ms_one_gpu_same_run"] = ms1
+            del full, sc
+            torch.cuda.empty_cache()
+        barrier()
+    else:
+        vs = 1.0
+    out["vs_1gpu"] = vs
+    return out
 
 
 if __name__ == "__main__":

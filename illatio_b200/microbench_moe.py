@@ -21,10 +21,33 @@ CONFIGS = {
 }
 
 
-def make_pool(cfg, n_local=None, first=0, seed=0, device="cuda"):
-    """Experts FIRST .. FIRST+N_LOCAL-1 of the layer, drawn on the device."""
+def expert_seed(seed, tensor, expert):
+    """The seed expert EXPERT's tensor (0 gate, 1 up, 2 down) is drawn from: any slice of the layer, on any rank,
+    is the same bytes."""
+    return seed + 1000003 * tensor + expert
+
+
+def interleaved_experts(ne, world, rank):
+    """Expert placement that spreads popular experts over the ranks: rank r holds experts r, r + world, ...
+    (a skewed router, e.g. Zipf popularity by expert number, then loads the ranks evenly).  The products see the
+    rank's experts as local numbers 0 .. ne/world - 1 in this order; the router's rows are permuted to match when
+    the model is loaded (virtual_order), which costs nothing per token."""
+    return list(range(rank, ne, world))
+
+
+def virtual_order(ne, world):
+    """Expert numbers in the order the ranks hold them with interleaved placement: entry v is the expert that is
+    rank v // (ne/world)'s local expert v % (ne/world)."""
+    return [e for r in range(world) for e in interleaved_experts(ne, world, r)]
+
+
+def make_pool(cfg, n_local=None, first=0, seed=0, device="cuda", experts=None):
+    """Experts FIRST .. FIRST+N_LOCAL-1 of the layer (or the listed EXPERTS), drawn on the device."""
     d, ff, ne = cfg["d"], cfg["ff"], cfg["ne"]
     n_local = ne if n_local is None else n_local
+    if experts is None:
+        experts = list(range(first, first + n_local))
+    n_local = len(experts)
     gb = ff * B.row_bytes(cfg["gate_fmt"], d)
     db = d * B.row_bytes(B.Q2_K, ff)
     slot = (2 * gb + db + 255) // 256 * 256
@@ -32,8 +55,8 @@ def make_pool(cfg, n_local=None, first=0, seed=0, device="cuda"):
     pv = pool.view(n_local, slot)
     for i, (fmt, rows, cols, off, nb) in enumerate([(cfg["gate_fmt"], ff, d, 0, gb), (cfg["gate_fmt"], ff, d, gb, gb),
                                                     (B.Q2_K, d, ff, 2 * gb, db)]):
-        for e in range(n_local):  # one stream of numbers per (tensor, expert): any slice of the layer is the same bytes
-            m = B.synth_matrix_torch(fmt, rows, cols, seed=seed + 1000003 * i + first + e, device=device)
+        for e, real in enumerate(experts):  # one stream of numbers per (tensor, expert)
+            m = B.synth_matrix_torch(fmt, rows, cols, seed=expert_seed(seed, i, real), device=device)
             pv[e, off:off + nb] = m
     base = pool.data_ptr()
     ptrs = torch.tensor([base + e * slot for e in range(n_local)], dtype=torch.int64, device=device)

@@ -29,6 +29,11 @@
 
 #define QK_K 256
 
+/* illatio_oracle_simd.c: the same row dots with AVX2 integer instructions, and a pool of pinned threads */
+float orc_row_dot_simd(int fmt, const uint8_t* w, int ncols, const int8_t* xq, const float* xs, const int32_t* bs);
+int orc_simd_available(void);
+void orc_pool_run(void* (*fn)(void*), void* jobs, size_t job_size, int n);
+
 enum { ORC_Q8_0 = 0, ORC_Q4_K = 1, ORC_Q6_K = 2, ORC_Q2_K = 3, ORC_IQ2_XXS = 4 };
 
 /* ---- src/half.lisp ------------------------------------------------------- */
@@ -401,7 +406,19 @@ float orc_q2k_row_dot_x86(const uint8_t* w, int nb, const int8_t* qs, const floa
 /* One row against one token's quantized activations.  For Q8_0, XS is the
  * per-32 scales and BS is unused; otherwise XS is the per-256 scale d and BS
  * the per-16 sums (a Q8KVEC, src/kquant.lisp:117-128). */
+/* How the timed CPU baseline runs (orc_set_fast): 0, the default and what every parity check uses -- the portable
+ * loops above, a thread created per share; 1 -- the AVX2 row dots (IQ2_XXS and Q2_K then in the x86 float order, as
+ * the reference's own AVX2 kernels, src/avx2.lisp:77-150) on a pool of threads pinned one to a core, which is how
+ * the reference runs its CPU share (src/cuda-ds4f.lisp:666-699). */
+static int g_fast = 0;
+int orc_set_fast(int on) {
+  int prev = g_fast;
+  g_fast = on && orc_simd_available();
+  return prev;
+}
+
 float orc_row_dot(int fmt, const uint8_t* w, int ncols, const int8_t* xq, const float* xs, const int32_t* bs) {
+  if (g_fast) return orc_row_dot_simd(fmt, w, ncols, xq, xs, bs);
   switch (fmt) {
     case ORC_Q8_0: return orc_q8_0_row_dot(w, ncols / 32, xq, xs);
     case ORC_Q4_K: return orc_q4k_row_dot(w, ncols / QK_K, xq, xs, bs);
@@ -456,6 +473,7 @@ void orc_matvec(int fmt, const uint8_t* w, int rows, int cols, const int8_t* xq,
     jobs[i] = j;
   }
   if (nthreads == 1) { mv_worker(&jobs[0]); return; }
+  if (g_fast) { orc_pool_run(mv_worker, jobs, sizeof(mv_job), nthreads); return; }
   for (int i = 0; i < nthreads; ++i) pthread_create(&th[i], 0, mv_worker, &jobs[i]);
   for (int i = 0; i < nthreads; ++i) pthread_join(th[i], 0);
 }
@@ -547,6 +565,7 @@ static void run_moe(moe_job* proto, int phase, int nthreads) {
   moe_job jobs[256]; pthread_t th[256];
   for (int i = 0; i < nthreads; ++i) { jobs[i] = *proto; jobs[i].idx = i; jobs[i].count = nthreads; jobs[i].phase = phase; }
   if (nthreads == 1) { moe_worker(&jobs[0]); return; }
+  if (g_fast) { orc_pool_run(moe_worker, jobs, sizeof(moe_job), nthreads); return; }
   for (int i = 0; i < nthreads; ++i) pthread_create(&th[i], 0, moe_worker, &jobs[i]);
   for (int i = 0; i < nthreads; ++i) pthread_join(th[i], 0);
 }

@@ -24,8 +24,8 @@ _i32p = _c.POINTER(_c.c_int32)
 
 def build(force=False):
     """Compile liboracle.so with the Makefile beside this file."""
-    src = os.path.join(HERE, "illatio_oracle.c")
-    if force or not os.path.exists(LIB) or os.path.getmtime(LIB) < os.path.getmtime(src):
+    srcs = [os.path.join(HERE, f) for f in ("illatio_oracle.c", "illatio_oracle_simd.c", "iq2xxs_tables.h", "Makefile")]
+    if force or not os.path.exists(LIB) or any(os.path.getmtime(LIB) < os.path.getmtime(f) for f in srcs):
         subprocess.check_call(["make", "-C", HERE, "-B", "liboracle.so"], stdout=subprocess.DEVNULL)
     return LIB
 
@@ -62,6 +62,11 @@ def lib():
         L.orc_route.argtypes = [_f32p, _c.c_int, _c.c_int, _c.c_int, _f32p, _c.c_float, _i32p, _f32p]
         L.orc_moe_routed.argtypes = [_c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _u8p, _u8p, _u8p, _f32p,
                                      _i32p, _f32p, _c.c_float, _f32p, _f32p, _c.c_int]
+        L.orc_set_fast.restype = _c.c_int
+        L.orc_set_fast.argtypes = [_c.c_int]
+        L.orc_simd_available.restype = _c.c_int
+        L.orc_row_dot_simd.restype = _c.c_float
+        L.orc_row_dot_simd.argtypes = [_c.c_int, _u8p, _c.c_int, _i8p, _f32p, _i32p]
         L.orc_moe_shared.argtypes = [_c.c_int, _c.c_int, _u8p, _u8p, _u8p, _f32p, _c.c_float, _f32p, _c.c_int]
         _lib = L
     return _lib
@@ -155,6 +160,23 @@ def matvec(fmt, w, rows, cols, act, n=1, bias=None, threads=1):
     lib().orc_matvec(fmt, _p(w, _u8p), rows, cols, _p(xq, _i8p), _p(xs, _f32p), _p(bs, _i32p), n,
                      _p(out, _f32p), _p(b, _f32p), threads)
     return out
+
+
+def simd_available():
+    """Whether this CPU runs the AVX2 row dots."""
+    return bool(lib().orc_simd_available())
+
+
+def set_fast(on):
+    """The timed CPU baseline's form: AVX2 row dots (IQ2_XXS / Q2_K in the x86 float order) on a pool of pinned
+    threads.  Off (the default) for every parity check.  Returns the previous setting."""
+    return lib().orc_set_fast(1 if on else 0)
+
+
+def row_dot_simd(fmt, w_row, cols, act):
+    xq, xs, bs = act
+    w_row = _c_(w_row, np.uint8)
+    return lib().orc_row_dot_simd(fmt, _p(w_row, _u8p), cols, _p(xq, _i8p), _p(xs, _f32p), _p(bs, _i32p))
 
 
 def row_dot_x86(fmt, w_row, cols, act):

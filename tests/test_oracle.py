@@ -177,6 +177,33 @@ def test_x86_order_close_to_portable(oracle, fmt):
     assert (np.abs(port - x86) / terms).max() < 1e-6
 
 
+@pytest.mark.parametrize("fmt", [B.Q8_0, B.Q4_K, B.Q6_K, B.Q2_K, B.IQ2_XXS])
+def test_avx2_row_dots_are_the_scalar_bits(oracle, fmt):
+    """The timed CPU baseline's AVX2 dots: the portable loop's bits for Q8_0 / Q4_K / Q6_K (same float steps, exact
+    integer sums), the x86-order restatement's bits for IQ2_XXS / Q2_K (IQ2XXS-DOT-AVX2 / Q2K-DOT-AVX2,
+    src/avx2.lisp:77-150)."""
+    if not oracle.simd_available():
+        pytest.skip("no AVX2 on this CPU")
+    rows, cols = 64, B.BLOCK_WEIGHTS[fmt] * 8 if fmt != B.Q8_0 else 32 * 19
+    w = B.synth_matrix(fmt, rows, cols, seed=31 + fmt)
+    x = np.random.default_rng(fmt).standard_normal(cols).astype(np.float32)
+    x[:32] = 127.0          # saturated quants
+    act = oracle.quantize_act(fmt, x)
+    rb = B.row_bytes(fmt, cols)
+    want = (oracle.matvec(fmt, w, rows, cols, act)[0] if fmt in (B.Q8_0, B.Q4_K, B.Q6_K)
+            else np.array([oracle.row_dot_x86(fmt, w[r * rb:(r + 1) * rb], cols, act) for r in range(rows)], np.float32))
+    got = np.array([oracle.row_dot_simd(fmt, w[r * rb:(r + 1) * rb], cols, act) for r in range(rows)], np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # the pool of pinned threads gives what created threads give
+    prev = oracle.set_fast(True)
+    try:
+        fast = oracle.matvec(fmt, w, rows, cols, act, threads=4)[0]
+        again = oracle.matvec(fmt, w, rows, cols, act, threads=3)[0]
+    finally:
+        oracle.set_fast(prev)
+    assert np.array_equal(fast.view(np.uint32), got.view(np.uint32)) and np.array_equal(again, fast)
+
+
 def test_matvec_threads_and_bias(oracle):
     rows, cols = 37, 512
     w = B.synth_matrix(B.Q4_K, rows, cols, seed=31)
