@@ -111,13 +111,21 @@ def cmat_mul(w, act, y, n=1, bias=None, acc=False):
     """CMAT-MUL (src/cuda-dense.lisp:220-248): Y = W X for N tokens (token t's X
     at t*cols, its Y at t*rows), or Y += it when ACC."""
     done = 0
-    while done < n:  # the kernel takes up to 16 tokens a launch
-        k = min(16, n - done)
+    kmax = 16  # the kernel takes up to 16 tokens a launch -- fewer when their activations do not fit beside the stages
+    while done < n:
+        k = min(kmax, n - done)
         sc = w.cols // (32 if act.kind == "q8" else 256)
-        _lib.call("ill_mv", w.type, _ptr(w.qs), w.rows, w.cols,
-                  act.xq.data_ptr() + done * w.cols, act.xs.data_ptr() + 4 * done * sc,
-                  0 if act.kind == "q8" else act.xsum.data_ptr() + 2 * done * (w.cols // 16),
-                  y.data_ptr() + 4 * done * w.rows, _ptr(bias), 1 if acc else 0, k, _stream())
+        rc = _lib.status("ill_mv", w.type, _ptr(w.qs), w.rows, w.cols,
+                         act.xq.data_ptr() + done * w.cols, act.xs.data_ptr() + 4 * done * sc,
+                         0 if act.kind == "q8" else act.xsum.data_ptr() + 2 * done * (w.cols // 16),
+                         y.data_ptr() + 4 * done * w.rows, _ptr(bias), 1 if acc else 0, k, _stream())
+        if rc == 3 and k > 1:   # ILL_ERR_UNSUPPORTED: long rows, many tokens
+            kmax = k // 2
+            continue
+        if rc:
+            _lib.call("ill_mv", w.type, _ptr(w.qs), w.rows, w.cols, act.xq.data_ptr() + done * w.cols,
+                      act.xs.data_ptr() + 4 * done * sc, 0 if act.kind == "q8" else act.xsum.data_ptr() + 2 * done * (w.cols // 16),
+                      y.data_ptr() + 4 * done * w.rows, _ptr(bias), 1 if acc else 0, k, _stream())  # raises with the text
         done += k
     return y
 
