@@ -850,6 +850,8 @@ def moe_leg(D, B, EP, MB, torch, dist, dev, rank, world, cores, cfg_name, n_tok,
             dist.all_reduce(tot)
         out["parity"] = {"max_rel_err": worst, "tokens_checked": int(tot.item()), "ranks": world, "bound": 2e-3,
                          "ok": bool(worst < 2e-3 and tot.item() >= 4 * world and overflows == 0)}
+    barrier()
+    esc.close()
     del esc, ce, pool
     torch.cuda.empty_cache()
     # ---- the same chunk on rank 0 alone, every expert on its GPU

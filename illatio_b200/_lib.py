@@ -62,6 +62,13 @@ SIGNATURES = {
     "ill_ep_plan_dev": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _S]),
     "ill_moe_mm_id2": (_I, [_I, _I, _I, _L, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),
     "ill_moe_mm_id_peers": (_I, [_I, _I, _I, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),
+    "ill_ep_ipc_export": (_I, [_P, _c.c_char_p, _c.POINTER(_c.c_int64)]),
+    "ill_ep_ipc_open": (_I, [_c.c_char_p, _L, _c.POINTER(_c.c_uint64)]),
+    "ill_ep_ipc_close": (_I, [_P, _L]),
+    "ill_ep_flags_bytes": (_L, []),
+    "ill_ep_barrier": (_I, [_P, _P, _I, _I, _I, _c.c_uint32, _L, _S]),
+    "ill_ep_plan_dev_sync": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _c.c_uint32, _L, _S]),
+    "ill_moe_sum_sync": (_I, [_I, _I, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _c.c_uint32, _L, _S]),
     "ill_ep_unpack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _S]),
 }
 

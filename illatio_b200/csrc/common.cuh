@@ -83,6 +83,43 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
   return false;
 }
 
+// ---- ranks meet without a collective: flags in peer memory -------------------------------------
+// Every rank owns an array of flags, EP_FLAG_SLOTS x EP_MAX_RANKS words, that its peers can store into
+// (FLAG_PEERS[r] = the address of rank r's array).  A meeting in slot S with number EPOCH (counted up by the
+// caller, the same on every rank): thread t < WORLD of the calling block stores EPOCH into rank t's
+// flags[S][RANK] (after a system-wide fence: what this rank stored into peer memory before is visible to a
+// peer that sees the flag), then waits until its own flags[S][t] has reached EPOCH.  The wait is bounded
+// (WAIT_NS, 0 = ILL_WAIT_NS): on a time-out the status word gets ST_BARRIER_WAIT and the call returns false.
+// No rank waits for anything but stores its peers make unconditionally, so ranks that run their kernels at
+// different times cannot deadlock each other.
+constexpr int EP_MAX_RANKS = 64, EP_FLAG_SLOTS = 4;
+__device__ __forceinline__ bool ep_meet(const unsigned long long* flag_peers, unsigned* flags, int world, int rank, int slot,
+                                        unsigned epoch, bool signal, unsigned long long wait_ns, unsigned int* status) {
+  const int t = threadIdx.x;
+  if (t >= world) return true;
+  if (signal) {
+    __threadfence_system();
+    unsigned* dst = (unsigned*)(uintptr_t)flag_peers[t] + slot * EP_MAX_RANKS + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
+  }
+  const unsigned* mine = flags + slot * EP_MAX_RANKS + t;
+  const unsigned long long limit = wait_ns ? wait_ns : ILL_WAIT_NS;
+  unsigned long long t0 = 0;
+  for (unsigned it = 1;; ++it) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int)(v - epoch) >= 0) return true;
+    if ((it & 255u) == 0) {
+      const unsigned long long now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit) {
+        if (status) atomicCAS(status, 0u, (unsigned)ST_BARRIER_WAIT);
+        return false;
+      }
+    }
+  }
+}
+
 // 1-D bulk copy global -> this CTA's shared memory; 16-byte aligned addresses
 // and size.  No multicast.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {

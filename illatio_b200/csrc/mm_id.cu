@@ -859,7 +859,9 @@ __global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, in
                                                           unsigned* __restrict__ counts, unsigned* __restrict__ bases,
                                                           unsigned* __restrict__ p2r, unsigned* __restrict__ r2p,
                                                           unsigned* __restrict__ pdst, unsigned* __restrict__ total,
-                                                          unsigned* __restrict__ overflow) {
+                                                          unsigned* __restrict__ overflow, const unsigned long long* flag_peers,
+                                                          unsigned* flags, unsigned epoch, unsigned long long wait_ns,
+                                                          unsigned* status) {
   extern __shared__ unsigned plan_s[];
   unsigned* in_src = plan_s;                 // [world][per] rows of the source's earlier experts (as counted)
   unsigned* before = plan_s + world * per;   // [world][per] rows of the expert that arrived from earlier sources
@@ -868,6 +870,21 @@ __global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, in
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x;
+  if (flag_peers) {
+    // the ranks meet first (slot 0): this rank's rows and counts are in its peers' buffers (the kernels before this
+    // one in the stream stored them), and what RC and the slabs hold is complete once every peer has said the same.
+    // A meeting that times out leaves a plan of no rows at all.
+    const bool ok = ep_meet(flag_peers, flags, world, rank, 0, epoch, true, wait_ns, status);
+    if (!__syncthreads_and(ok)) {
+      for (int e = tid; e < per; e += blockDim.x) { counts[e] = 0; bases[e] = 0; }
+      for (unsigned p = tid; p < (unsigned)(world * cap); p += blockDim.x) {
+        p2r[p] = 0;
+        if (pdst) pdst[p] = (unsigned)rank << 24 | ((unsigned)rank * cap);
+      }
+      if (tid == 0) total[0] = 0;
+      return;
+    }
+  }
   for (int s = tid; s < world; s += blockDim.x) {
     unsigned a = 0;
     bool cut = false;
@@ -1029,8 +1046,26 @@ extern "C" int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, 
                        (cudaStream_t)stream);
 }
 
+static int ep_plan_dev_launch(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
+                              ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_dptr flag_peers, ill_dptr flags,
+                              uint32_t epoch, int64_t wait_ns, ill_stream stream);
+
 extern "C" int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
                                ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_stream stream) {
+  return ep_plan_dev_launch(world, per, cap, rank, rc, counts, bases, p2r, r2p, pdst, total, overflow, 0, 0, 0, 0, stream);
+}
+
+extern "C" int ill_ep_plan_dev_sync(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
+                                    ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_dptr flag_peers,
+                                    ill_dptr flags, uint32_t epoch, int64_t wait_ns, ill_stream stream) {
+  if (!flag_peers || !flags || (flag_peers & 7) || (flags & 3) || world > EP_MAX_RANKS || wait_ns < 0) return ILL_ERR_ARG;
+  return ep_plan_dev_launch(world, per, cap, rank, rc, counts, bases, p2r, r2p, pdst, total, overflow, flag_peers, flags, epoch,
+                            wait_ns, stream);
+}
+
+static int ep_plan_dev_launch(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
+                              ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_dptr flag_peers, ill_dptr flags,
+                              uint32_t epoch, int64_t wait_ns, ill_stream stream) {
   if (world < 1 || world > 255 || per < 1 || cap < 1 || (long long)world * cap > 0xffffff || rank < 0 || rank >= world ||
       (long long)world * per > 8192 || !rc || !counts || !bases || !p2r || !r2p || !total)
     return ILL_ERR_ARG;
@@ -1043,7 +1078,11 @@ extern "C" int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr r
   unsigned* tp = (unsigned*)(uintptr_t)total;
   unsigned* dp = (unsigned*)(uintptr_t)pdst;
   unsigned* ov = (unsigned*)(uintptr_t)overflow;
-  void* args[] = {&world, &per, &cap, &rank, &rp, &cp, &bp, &pp, &ip, &dp, &tp, &ov};
+  const unsigned long long* fp = (const unsigned long long*)(uintptr_t)flag_peers;
+  unsigned* fl = (unsigned*)(uintptr_t)flags;
+  unsigned long long wn = (unsigned long long)wait_ns;
+  unsigned* stw = device_status_word();
+  void* args[] = {&world, &per, &cap, &rank, &rp, &cp, &bp, &pp, &ip, &dp, &tp, &ov, &fp, &fl, &epoch, &wn, &stw};
   const size_t smem = ((size_t)3 * world * per + per + 1) * 4;
   const void* k = (const void*)ep_plan_dev_kernel;
   if (smem > 48 * 1024) {

@@ -6,6 +6,9 @@
 // Replaces d4_mv_iq2_xxs / d4_mv_q2_k / d4_swiglu_w / d4_moe_sum
 // (src/cuda/ds4f.cu:645,769,837,902) and d4_route / d4_group_* / d4_gather_rows /
 // d4_moe_sum_rows (src/cuda/ds4f_chunk.cu:393-508) of the reference.
+#include <cuda.h>
+#include <string.h>
+
 #include "formats.cuh"
 #include "host.h"
 
@@ -34,19 +37,30 @@ __global__ void __launch_bounds__(256) swiglu_w_kernel(long long n, int ff, floa
 
 // MOE[t*d + r] = sum over the token's NU slots, in slot order, of DOWN[row(t, s)*d + r], plus SHARED
 // (src/ds4f.lisp:1031-1036, 1226-1231).  MAP gives row(t, s) (null: t*nu + s).
+// With MAP2, row(t, s) = MAP2[MAP[t*nu + s]] (an expert-parallel chunk: the slot a row left in, then where that
+// slot's result came back).  With FLAG_PEERS the ranks meet first (slot 1): DOWN then holds rows that peers stored,
+// complete once every peer has said so; block 0 says it for this rank (the kernel before this one in the stream
+// stored this rank's rows into its peers).  DOWN is read around L1 in that case.
 __global__ void __launch_bounds__(256) moe_sum_kernel(int d, int nu, long long ntok, const float* __restrict__ down,
-                                                      const unsigned* __restrict__ map,
-                                                      const float* __restrict__ shared_, float* __restrict__ moe) {
+                                                      const unsigned* __restrict__ map, const unsigned* __restrict__ map2,
+                                                      const float* __restrict__ shared_, float* __restrict__ moe,
+                                                      const unsigned long long* flag_peers, unsigned* flags, int world, int rank,
+                                                      unsigned epoch, unsigned long long wait_ns, unsigned* status) {
   pdl_launch_dependents();
   pdl_wait();
+  if (flag_peers) {
+    const bool ok = ep_meet(flag_peers, flags, world, rank, 1, epoch, blockIdx.x == 0, wait_ns, status);
+    if (!__syncthreads_and(ok)) return;
+  }
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= ntok * d) return;
   const long long t = gid / d;
   const int r = (int)(gid - t * d);
   float acc = 0.0f;
   for (int s = 0; s < nu; ++s) {
-    const long long row = map ? (long long)map[t * nu + s] : t * nu + s;
-    acc = __fadd_rn(acc, down[row * d + r]);
+    long long row = map ? (long long)map[t * nu + s] : t * nu + s;
+    if (map2) row = map2[row];
+    acc = __fadd_rn(acc, flag_peers ? __ldcg(down + row * d + r) : down[row * d + r]);
   }
   moe[gid] = shared_ ? __fadd_rn(acc, shared_[gid]) : acc;
 }
@@ -355,18 +369,103 @@ extern "C" int ill_swiglu_w(int64_t n, int ff, float clamp, ill_dptr g, ill_dptr
                        (cudaStream_t)stream);
 }
 
-extern "C" int ill_moe_sum(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr shared_, ill_dptr moe,
-                           ill_stream stream) {
-  if (d <= 0 || nu <= 0 || ntok < 0 || !check_ptr(down, 4) || !check_ptr(moe, 4) || (map & 3) || (shared_ & 3))
+static int moe_sum_launch(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr map2, ill_dptr shared_, ill_dptr moe,
+                          ill_dptr flag_peers, ill_dptr flags, int world, int rank, uint32_t epoch, int64_t wait_ns,
+                          ill_stream stream) {
+  if (d <= 0 || nu <= 0 || ntok < 0 || !check_ptr(down, 4) || !check_ptr(moe, 4) || (map & 3) || (map2 & 3) || (shared_ & 3))
     return ILL_ERR_ARG;
-  if (ntok == 0) return ILL_OK;
+  if (ntok == 0 && !flag_peers) return ILL_OK;
   long long nt = ntok;
   const float *dp = (const float*)(uintptr_t)down, *sp = (const float*)(uintptr_t)shared_;
-  const unsigned* mp = (const unsigned*)(uintptr_t)map;
+  const unsigned *mp = (const unsigned*)(uintptr_t)map, *m2 = (const unsigned*)(uintptr_t)map2;
   float* op = (float*)(uintptr_t)moe;
-  void* args[] = {&d, &nu, &nt, &dp, &mp, &sp, &op};
-  return launch_kernel((const void*)moe_sum_kernel, dim3((unsigned)((ntok * d + 255) / 256)), dim3(256), 0, args,
-                       (cudaStream_t)stream);
+  const unsigned long long* fp = (const unsigned long long*)(uintptr_t)flag_peers;
+  unsigned* fl = (unsigned*)(uintptr_t)flags;
+  unsigned long long wn = (unsigned long long)wait_ns;
+  unsigned* stw = device_status_word();
+  void* args[] = {&d, &nu, &nt, &dp, &mp, &m2, &sp, &op, &fp, &fl, &world, &rank, &epoch, &wn, &stw};
+  long long blocks = (ntok * d + 255) / 256;
+  if (blocks < 1) blocks = 1;  // a rank without tokens still meets the others
+  return launch_kernel((const void*)moe_sum_kernel, dim3((unsigned)blocks), dim3(256), 0, args, (cudaStream_t)stream);
+}
+
+extern "C" int ill_moe_sum(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr shared_, ill_dptr moe,
+                           ill_stream stream) {
+  return moe_sum_launch(d, nu, ntok, down, map, 0, shared_, moe, 0, 0, 1, 0, 0, 0, stream);
+}
+
+extern "C" int ill_moe_sum_sync(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr map2, ill_dptr shared_,
+                                ill_dptr moe, ill_dptr flag_peers, ill_dptr flags, int world, int rank, uint32_t epoch,
+                                int64_t wait_ns, ill_stream stream) {
+  if (!flag_peers || !flags || (flag_peers & 7) || (flags & 3) || world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world ||
+      wait_ns < 0)
+    return ILL_ERR_ARG;
+  return moe_sum_launch(d, nu, ntok, down, map, map2, shared_, moe, flag_peers, flags, world, rank, epoch, wait_ns, stream);
+}
+
+// The ranks meet (slot SLOT of the flags), nothing else: one block.
+__global__ void __launch_bounds__(64) ep_barrier_kernel(const unsigned long long* flag_peers, unsigned* flags, int world, int rank,
+                                                        int slot, unsigned epoch, unsigned long long wait_ns, unsigned* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  ep_meet(flag_peers, flags, world, rank, slot, epoch, true, wait_ns, status);
+}
+
+extern "C" int64_t ill_ep_flags_bytes(void) { return (int64_t)EP_MAX_RANKS * EP_FLAG_SLOTS * 4; }
+
+extern "C" int ill_ep_barrier(ill_dptr flag_peers, ill_dptr flags, int world, int rank, int slot, uint32_t epoch, int64_t wait_ns,
+                              ill_stream stream) {
+  if (!flag_peers || !flags || (flag_peers & 7) || (flags & 3) || world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world ||
+      slot < 0 || slot >= EP_FLAG_SLOTS || wait_ns < 0)
+    return ILL_ERR_ARG;
+  const unsigned long long* fp = (const unsigned long long*)(uintptr_t)flag_peers;
+  unsigned* fl = (unsigned*)(uintptr_t)flags;
+  unsigned long long wn = (unsigned long long)wait_ns;
+  unsigned* stw = device_status_word();
+  void* args[] = {&fp, &fl, &world, &rank, &slot, &epoch, &wn, &stw};
+  return launch_kernel((const void*)ep_barrier_kernel, dim3(1), dim3(64), 0, args, (cudaStream_t)stream);
+}
+
+// ---- peer mappings for hosts that drive the ranks as processes ----------------------------------
+typedef CUresult (*AddrRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+
+extern "C" int ill_ep_ipc_export(ill_dptr buf, unsigned char* handle, int64_t* offset) {
+  if (!buf || !handle || !offset) return ILL_ERR_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == ILL_EP_IPC_HANDLE_BYTES, "the handle is 64 bytes");
+  static AddrRangeFn range = nullptr;
+  if (!range) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return cuda_fail(cudaErrorNotSupported);
+    range = (AddrRangeFn)p;
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (range(&base, &size, (CUdeviceptr)buf) != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, (void*)(uintptr_t)base);
+  if (e != cudaSuccess) return cuda_fail(e);
+  memcpy(handle, &h, sizeof h);
+  *offset = (int64_t)(buf - (ill_dptr)base);
+  return ILL_OK;
+}
+
+extern "C" int ill_ep_ipc_open(const unsigned char* handle, int64_t offset, ill_dptr* out) {
+  if (!handle || !out || offset < 0) return ILL_ERR_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof h);
+  void* p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail(e);
+  *out = (ill_dptr)(uintptr_t)p + (ill_dptr)offset;
+  return ILL_OK;
+}
+
+extern "C" int ill_ep_ipc_close(ill_dptr mapped, int64_t offset) {
+  if (!mapped || offset < 0) return ILL_ERR_ARG;
+  const cudaError_t e = cudaIpcCloseMemHandle((void*)(uintptr_t)(mapped - (ill_dptr)offset));
+  return e == cudaSuccess ? ILL_OK : cuda_fail(e);
 }
 
 extern "C" int ill_moe_route(int ne, int nu, int mode, float scale, int64_t ntok, ill_dptr logits, ill_dptr bias,

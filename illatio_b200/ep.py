@@ -372,32 +372,72 @@ class EpCapScratch:
         self.me = torch.empty(tot, ff // 256, 64, dtype=torch.float16, **dev) if pool.down_fmt == Q2_K else None
         self.down = torch.zeros(tot, d, **f32)
         self.pdst = torch.zeros(tot, **i32)
-        self.hdl, self.peers, self.peers_rows, self.peers_rc = None, None, None, None
+        self.peers, self.peers_rows, self.peers_rc, self.peers_flags, self.flags = None, None, None, None, None
+        self.epoch, self._mapped = 0, []
         if world > 1 and peer:
-            import torch.distributed._symmetric_memory as symm_mem
+            # One buffer a rank holds everything its peers store into -- the rows that come back, the slabs of packed
+            # rows, the table of counts, the flags the ranks meet at -- mapped into every peer through CUDA IPC
+            # (ill_ep_ipc_export / ill_ep_ipc_open): plain peer pointers, no multicast, no collective library.
+            import ctypes
             grp = group if group is not None else dist.group.WORLD
-
-            def shared(shape, dtype):
-                t = symm_mem.empty(shape, dtype=dtype, device=device)
-                t.zero_()
-                h = symm_mem.rendezvous(t, grp)
-                return t, h, torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device)
-
-            self.back, self.hdl, self.peers = shared((tot, d), torch.float32)
-            self.r_rows, _, self.peers_rows = shared((tot, self.row_bytes), torch.uint8)
-            self.rc, _, self.peers_rc = shared((world, per), torch.int32)
+            me = dist.get_rank(grp)
+            up = lambda v: (v + 255) // 256 * 256  # noqa: E731
+            sizes = [tot * d * 4, tot * self.row_bytes, world * per * 4, int(_lib.lib().ill_ep_flags_bytes())]
+            offs = [0]
+            for sz in sizes:
+                offs.append(offs[-1] + up(sz))
+            self.shared = torch.zeros(offs[-1], dtype=torch.uint8, device=device)
+            base = self.shared.data_ptr()
+            handle = ctypes.create_string_buffer(64)
+            off = ctypes.c_int64(0)
+            with torch.cuda.device(self.shared.device):
+                _lib.call("ill_ep_ipc_export", base, handle, ctypes.byref(off))
+                torch.cuda.synchronize()
+                every = [None] * world
+                dist.all_gather_object(every, (handle.raw, off.value), group=grp)
+                bases = []
+                for r, (h, o) in enumerate(every):
+                    if r == me:
+                        bases.append(base)
+                        continue
+                    out = ctypes.c_uint64(0)
+                    _lib.call("ill_ep_ipc_open", h, o, ctypes.byref(out))
+                    self._mapped.append((out.value, o))
+                    bases.append(out.value)
+            table = lambda k: torch.tensor([b + offs[k] for b in bases], dtype=torch.int64, device=device)  # noqa: E731
+            view = lambda k, dt, shape: self.shared[offs[k]:offs[k] + sizes[k]].view(dt).view(shape)  # noqa: E731
+            self.back, self.peers = view(0, torch.float32, (tot, d)), table(0)
+            self.r_rows, self.peers_rows = view(1, torch.uint8, (tot, self.row_bytes)), table(1)
+            self.rc, self.peers_rc = view(2, torch.int32, (world, per)), table(2)
+            self.flags, self.peers_flags = view(3, torch.int32, (-1,)), table(3)
+            torch.cuda.synchronize()
+            dist.barrier(group=grp)  # every rank's buffer is zeroed and mapped before anybody stores into one
         else:
             self.back = torch.zeros(tot, d, **f32) if world > 1 else self.down
         self.moe = torch.empty(n, d, **f32)
 
+    def close(self):
+        """Unmap the peers' buffers (call on every rank, after the last chunk has completed everywhere)."""
+        for ptr_, off in self._mapped:
+            _lib_close(ptr_, off)
+        self._mapped = []
 
-def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
+
+def _lib_close(ptr_, off):
+    from . import _lib
+    _lib.status("ill_ep_ipc_close", ptr_, off)
+
+
+def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None, wait_ns=0):
     """The chunk with exchanges of a fixed size (sc.cap rows from every rank to every
     rank): nothing on the host depends on the routing, so the whole chunk is
     enqueued without a synchronisation.  Returns (moe, overflow): OVERFLOW is a
     device flag, set when some slab was too small -- the result is then void and
     the caller repeats the chunk with chunk_fast.  Otherwise the same bits as
-    chunk_fast."""
+    chunk_fast.  With peer buffers (EpCapScratch(peer=True)) the chunk uses no collective at all: rows and counts
+    are stored into the owners' buffers, results into the tokens' owners', and the ranks' streams meet twice at
+    flags in peer memory, inside the plan and the sum kernels (WAIT_NS: how long a meeting waits, 0 = two seconds;
+    a meeting that times out shows in device_status() and the chunk's result is void)."""
     from . import _lib
     pool = ex.pool
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -419,7 +459,7 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
         call("ill_ep_put_counts", world, per, me, ptr(sc.counts), ptr(sc.peers_rc), ptr(sc.overflow), st)
         call("ill_ep_pack_cap", rows, d, ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), per,
              world, cap, 0, ptr(sc.pslot), ptr(sc.overflow), ptr(sc.peers_rows), me, st)
-        sc.hdl.barrier()
+        sc.epoch += 1
     else:
         sc.overflow.zero_()
         if world > 1:  # my rows per expert, to each expert's rank: [world, per] both ways
@@ -430,8 +470,14 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
              world, cap, ptr(sc.s_rows), ptr(sc.pslot), ptr(sc.overflow), 0, me, st)
         if world > 1:
             dist.all_to_all_single(sc.r_rows, sc.s_rows, group=group)
-    call("ill_ep_plan_dev", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
-         ptr(sc.pdst), ptr(sc.total), ptr(sc.overflow), st)
+    if sc.peers is not None:
+        # the ranks meet at the start of the plan kernel (flags in peer memory, a bounded wait): the slabs and the
+        # table of counts are complete once every peer has said that its stores are out
+        call("ill_ep_plan_dev_sync", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
+             ptr(sc.pdst), ptr(sc.total), ptr(sc.overflow), ptr(sc.peers_flags), ptr(sc.flags), sc.epoch, wait_ns, st)
+    else:
+        call("ill_ep_plan_dev", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
+             ptr(sc.pdst), ptr(sc.total), ptr(sc.overflow), st)
     # the element-wise steps stop at the rows in use (sc.total, written by the plan), not at the slabs' capacity
     call("ill_ep_unpack", tot, d, ptr(sc.r_rows), ptr(sc.p2r), ptr(sc.xh), ptr(sc.xe), ptr(sc.xd), ptr(sc.wplace), ptr(sc.total),
          st)
@@ -440,16 +486,18 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None):
     call("ill_swiglu_q8k_f16", tot, ff, float(ex.clamp), ptr(sc.g), ptr(sc.u), ptr(sc.wplace), ptr(sc.mh), ptr(sc.me), ptr(sc.ms),
          ptr(sc.total), st)
     if sc.peers is not None:
-        # the combine fused into the down product: rows go straight to their owners over NVLink; then the ranks
-        # meet, so that every owner's rows are in before it sums them
+        # the combine fused into the down product: rows go straight to their owners over NVLink; the ranks meet
+        # again at the start of the sum (every owner's rows are in before it adds them), which also looks each
+        # (token, slot) row up where it came back: at its slot of the slab it left in
         call("ill_moe_mm_id_peers", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts),
              ptr(sc.lbases), pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.pdst), ptr(sc.peers), d, st)
-        sc.hdl.barrier()
-    else:
-        call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases),
-             pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.p2r), ptr(sc.down), d, st)
-        if world > 1:
-            dist.all_to_all_single(sc.back, sc.down, group=group)
+        call("ill_moe_sum_sync", d, nu, n, ptr(sc.back), ptr(sc.smap), ptr(sc.pslot), 0, ptr(sc.moe), ptr(sc.peers_flags),
+             ptr(sc.flags), world, me, sc.epoch, wait_ns, st)
+        return sc.moe, sc.overflow
+    call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases),
+         pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.p2r), ptr(sc.down), d, st)
+    if world > 1:
+        dist.all_to_all_single(sc.back, sc.down, group=group)
     # a (token, slot) row's result is at its slot of the slab it left in
     call("ill_gather_rows", rows, 4, ptr(sc.pslot), ptr(sc.smap), ptr(sc.smap2), st)
     call("ill_moe_sum", d, nu, n, ptr(sc.back), ptr(sc.smap2), 0, ptr(sc.moe), st)

@@ -371,6 +371,48 @@ ILL_API int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill
 ILL_API int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
                             ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_stream stream);
 
+/* ---- expert parallelism without a collective library: peer mappings and meetings ------------
+ * A host that runs one process per GPU (as illatio runs one Lisp thread per device,
+ * src/cuda-ds4f.lisp:594-618) needs two things of its peers: their buffers' addresses,
+ * and a way for the ranks' streams to meet.  Both are here, so that the chunk needs no
+ * NCCL, no torch and no host synchronisation.  No counterpart in the reference, whose
+ * second device exchanges activations through pinned host memory.
+ *
+ * ill_ep_ipc_export gives the 64-byte CUDA IPC handle of the allocation that holds BUF (a
+ * cuMemAlloc'd buffer of the caller's) and BUF's offset inside it; the host passes both to
+ * its peers by any means it has.  ill_ep_ipc_open maps a peer's buffer into this process
+ * (peer access is enabled on first use) and returns its address here; ill_ep_ipc_close
+ * unmaps it.  A rank does not open its own handle: it uses its own address.
+ *
+ * A meeting is made of flags: every rank owns ill_ep_flags_bytes() bytes of zeroed device
+ * memory that its peers have mapped, FLAG_PEERS is a device table of the WORLD addresses
+ * (this rank's own at [RANK]), FLAGS this rank's own array.  Meeting number EPOCH (1, 2, ...
+ * counted by the caller, the same on every rank) in SLOT (0..3): the rank stores EPOCH into
+ * every peer's flags, after a system-wide fence, and waits until every peer's EPOCH has
+ * arrived in its own.  The wait is bounded: WAIT_NS nanoseconds (0: two seconds), after
+ * which the kernel records a code in the status word (ill_device_status) and goes on
+ * without the meeting -- ill_ep_plan_dev_sync then plans no rows, ill_moe_sum_sync sums
+ * nothing; nothing hangs and nothing traps.  ill_ep_barrier is the meeting alone (one
+ * block); ill_ep_plan_dev_sync is ill_ep_plan_dev after a meeting in slot 0 (this rank's
+ * rows and counts are in its peers' buffers; theirs are in its own once they have all said
+ * so); ill_moe_sum_sync is ill_moe_sum after a meeting in slot 1, with row(t, s) =
+ * MAP2[MAP[t*nu + s]] when MAP2 is given.  Two meetings a chunk order everything: a peer
+ * cannot overwrite a buffer this rank still reads, because it passes the chunk's second
+ * meeting only after this rank has enqueued everything before its own. */
+#define ILL_EP_IPC_HANDLE_BYTES 64
+ILL_API int ill_ep_ipc_export(ill_dptr buf, unsigned char* handle, int64_t* offset);
+ILL_API int ill_ep_ipc_open(const unsigned char* handle, int64_t offset, ill_dptr* out);
+ILL_API int ill_ep_ipc_close(ill_dptr mapped, int64_t offset);
+ILL_API int64_t ill_ep_flags_bytes(void);
+ILL_API int ill_ep_barrier(ill_dptr flag_peers, ill_dptr flags, int world, int rank, int slot, uint32_t epoch, int64_t wait_ns,
+                           ill_stream stream);
+ILL_API int ill_ep_plan_dev_sync(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
+                                 ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_dptr flag_peers, ill_dptr flags,
+                                 uint32_t epoch, int64_t wait_ns, ill_stream stream);
+ILL_API int ill_moe_sum_sync(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr map2, ill_dptr shared_, ill_dptr moe,
+                             ill_dptr flag_peers, ill_dptr flags, int world, int rank, uint32_t epoch, int64_t wait_ns,
+                             ill_stream stream);
+
 /* Two matrices of every expert against the same rows in one launch (gate and up:
  * W_e at PTRS[e] + ADD into Y, at PTRS[e] + ADD2 into Y2; no YMAP).  The same
  * results as two calls of ill_moe_mm_id; one launch fills the SMs better when a

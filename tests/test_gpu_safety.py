@@ -52,6 +52,34 @@ def test_bounded_wait_runs_out_and_the_device_stays_usable(cuda_lib):
     assert _lib.status("ill_test_wait_timeout", 10, 0, None) == 1   # limits outside 1 us .. 100 ms are refused
 
 
+def test_meeting_of_ranks_gives_up_when_a_peer_never_arrives(cuda_lib):
+    """The flag barrier of the expert-parallel path, on one GPU: a world of two whose second rank never
+    signals.  The meeting waits its millisecond, records the barrier's code and returns; once the missing
+    flag is there the same meeting passes."""
+    nbytes = _lib.lib().ill_ep_flags_bytes()
+    mine = torch.zeros(nbytes // 4, dtype=torch.int32, device="cuda")
+    other = torch.zeros(nbytes // 4, dtype=torch.int32, device="cuda")     # stands for the absent rank's flags
+    peers = torch.tensor([mine.data_ptr(), other.data_ptr()], dtype=torch.int64, device="cuda")
+    slot, epoch = 2, 1
+    _lib.call("ill_ep_barrier", peers.data_ptr(), mine.data_ptr(), 2, 0, slot, epoch, 1_000_000, None)
+    torch.cuda.synchronize()
+    assert _status() == (5, 0x700)
+    assert mine[slot * 64 + 0].item() == epoch and other[slot * 64 + 0].item() == epoch   # this rank did signal both
+    mine[slot * 64 + 1] = epoch                                                           # the peer's flag, late
+    _lib.call("ill_ep_barrier", peers.data_ptr(), mine.data_ptr(), 2, 0, slot, epoch, 1_000_000, None)
+    torch.cuda.synchronize()
+    assert _status() == (0, 0)
+    # the sum that follows a failed meeting adds nothing and leaves its output alone
+    d, nu, n = 256, 2, 3
+    down = torch.ones(n * nu, d, device="cuda")
+    moe = torch.full((n, d), -7.0, device="cuda")
+    _lib.call("ill_moe_sum_sync", d, nu, n, down.data_ptr(), 0, 0, 0, moe.data_ptr(), peers.data_ptr(), mine.data_ptr(), 2, 0,
+              epoch + 1, 1_000_000, None)
+    torch.cuda.synchronize()
+    assert _status() == (5, 0x700) and (moe == -7.0).all()
+    assert _lib.status("ill_ep_barrier", peers.data_ptr(), mine.data_ptr(), 65, 0, 0, 1, 0, None) == 1   # more ranks than flags
+
+
 def test_group_skips_and_flags_an_expert_out_of_range(cuda_lib):
     ne, nu, n = 8, 2, 700
     rng = np.random.default_rng(1)
