@@ -33,6 +33,7 @@
 
 #include "formats.cuh"
 #include "iq2xxs_tables.cuh"
+#include "quantdev.cuh"
 #include "host.h"
 
 namespace ill {
@@ -846,6 +847,60 @@ __global__ void __launch_bounds__(128) ep_pack_cap_kernel(int cols, long long ro
   }
 }
 
+// The whole dispatch of an expert-parallel chunk in one launch: block PLACE quantizes its token's activations
+// (Q8_K, the arithmetic of quant_q8_k_kernel: the same bits) straight into the packed row it stores into slab RANK
+// of the expert's rank (peer memory) -- the quantized token never passes through this rank's memory, and what
+// ep_pack_cap_kernel, quant_q8_k_kernel and ep_put_counts_kernel do in three launches is done in one; the first
+// blocks also store this rank's rows-per-expert into row RANK of every rank's table.  A slab that would overflow
+// raises *OVERFLOW to EPOCH (never cleared: the chunk with that number overflowed) and drops the rows past CAP.
+__global__ void __launch_bounds__(128) ep_dispatch_kernel(int cols, long long row_bytes, const float* __restrict__ x,
+                                                          const uint32_t* __restrict__ w, const unsigned* __restrict__ map,
+                                                          const unsigned* __restrict__ bases, const unsigned* __restrict__ counts,
+                                                          int per, int world, int cap, unsigned* __restrict__ pslot,
+                                                          unsigned* __restrict__ overflow, unsigned epoch,
+                                                          const unsigned long long* __restrict__ peers_rows,
+                                                          const unsigned long long* __restrict__ peers_rc, int rank) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  {
+    const int i = blockIdx.x * 128 + tid;
+    if (i < world * per) ((unsigned*)(uintptr_t)peers_rc[i / per])[rank * per + (i % per)] = counts[i];
+  }
+  const long long place = blockIdx.x;
+  __shared__ long long slot_s;
+  __shared__ int dest_s;
+  if (tid == 0) {
+    int g = 0;
+    while (g + 1 < world && (long long)bases[(g + 1) * per] <= place) ++g;
+    const long long idx = place - (long long)bases[g * per];
+    dest_s = g;
+    if (idx >= cap) { atomicMax(overflow, epoch); slot_s = -1; pslot[place] = 0; }
+    else { slot_s = (long long)g * cap + idx; pslot[place] = (unsigned)slot_s; }
+  }
+  __syncthreads();
+  if (slot_s < 0) return;
+  u8* dst = (u8*)(uintptr_t)peers_rows[dest_s] + ((long long)rank * cap + (slot_s - (long long)dest_s * cap)) * row_bytes;
+  const float* xr = x + (long long)map[place] * cols;
+  const int nb = cols / 256;
+  float* dscale = (float*)(dst + cols);
+  int16_t* dsum = (int16_t*)(dst + cols + nb * 4);
+  for (int b = warp; b < nb; b += 4) {
+    const float4 v0 = ((const float4*)(xr + b * 256))[2 * lane], v1 = ((const float4*)(xr + b * 256))[2 * lane + 1];
+    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    int q[8];
+    float d;
+    q8k_values(v, lane, q, d);
+    uint32_t w0, w1;
+    int sum = q8k_pack(q, w0, w1);
+    ((uint2*)(dst + b * 256))[lane] = make_uint2(w0, w1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    if (!(lane & 1)) dsum[b * 16 + (lane >> 1)] = (int16_t)sum;
+    if (lane == 0) dscale[b] = d;
+  }
+  if (tid == 0) *(uint32_t*)(dst + cols + nb * 4 + cols / 8) = w[place];
+}
+
 // The receiving rank's plan, on the device, for exchanges of a fixed size: RC[s * per + e] = rows source s counted
 // for local expert e.  The sender keeps, per destination, only the first CAP rows of its expert order, so of
 // those RC rows the ones that arrived are GOT = min(RC, max(0, cap - rows of s's earlier experts)), at slots
@@ -896,7 +951,7 @@ __global__ void __launch_bounds__(256) ep_plan_dev_kernel(int world, int per, in
       cut |= n > room;
       a = a + n < a ? 0xffffffffu : a + n;   // saturate: counts are the caller's, not trusted
     }
-    if (cut && overflow) atomicOr(overflow, 1u);
+    if (cut && overflow) { if (flag_peers) atomicMax(overflow, epoch); else atomicOr(overflow, 1u); }
   }
   __syncthreads();
   for (int e = tid; e < per; e += blockDim.x) {
@@ -1032,6 +1087,31 @@ extern "C" int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs,
   const unsigned long long* pr = (const unsigned long long*)(uintptr_t)peers;
   void* args[] = {&cols, &rb, &qp, &sp, &bp, &wp, &mp, &bs, &per, &world, &cap, &nrows, &pp, &ps, &ov, &pr, &rank};
   return launch_kernel((const void*)ep_pack_cap_kernel, dim3((unsigned)rows), dim3(128), 0, args, (cudaStream_t)stream);
+}
+
+extern "C" int ill_ep_dispatch(int64_t rows, int cols, ill_dptr x, ill_dptr w, ill_dptr map, ill_dptr bases, ill_dptr counts, int per,
+                               int world, int cap, int rank, ill_dptr peers_rows, ill_dptr peers_rc, ill_dptr pslot, ill_dptr overflow,
+                               uint32_t epoch, ill_stream stream) {
+  if (rows < 0 || cols <= 0 || cols % 256 || per < 1 || world < 1 || cap < 1 || !x || !w || !map || !bases || !counts || !peers_rows ||
+      !peers_rc || !pslot || !overflow || rank < 0 || rank >= world || epoch == 0)
+    return ILL_ERR_ARG;
+  if ((x & 15) || (w & 3) || (map & 3) || (bases & 3) || (counts & 3) || (pslot & 3) || (overflow & 3) || (peers_rows & 7) || (peers_rc & 7))
+    return ILL_ERR_ALIGN;
+  long long rb = ill_ep_row_bytes(cols);
+  const float* xp = (const float*)(uintptr_t)x;
+  const uint32_t* wp = (const uint32_t*)(uintptr_t)w;
+  const unsigned* mp = (const unsigned*)(uintptr_t)map;
+  const unsigned* bs = (const unsigned*)(uintptr_t)bases;
+  const unsigned* cp = (const unsigned*)(uintptr_t)counts;
+  unsigned* ps = (unsigned*)(uintptr_t)pslot;
+  unsigned* ov = (unsigned*)(uintptr_t)overflow;
+  const unsigned long long* pr = (const unsigned long long*)(uintptr_t)peers_rows;
+  const unsigned long long* pc = (const unsigned long long*)(uintptr_t)peers_rc;
+  void* args[] = {&cols, &rb, &xp, &wp, &mp, &bs, &cp, &per, &world, &cap, &ps, &ov, &epoch, &pr, &pc, &rank};
+  long long blocks = rows;
+  const long long need = ((long long)world * per + 127) / 128;  // blocks that carry the counts
+  if (blocks < need) return ILL_ERR_UNSUPPORTED;  // fewer rows than that: use ill_ep_put_counts and ill_ep_pack_cap
+  return launch_kernel((const void*)ep_dispatch_kernel, dim3((unsigned)blocks), dim3(128), 0, args, (cudaStream_t)stream);
 }
 
 extern "C" int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill_dptr peers, ill_dptr overflow,

@@ -45,9 +45,12 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(int d, int nu, long long n
                                                       const unsigned* __restrict__ map, const unsigned* __restrict__ map2,
                                                       const float* __restrict__ shared_, float* __restrict__ moe,
                                                       const unsigned long long* flag_peers, unsigned* flags, int world, int rank,
-                                                      unsigned epoch, unsigned long long wait_ns, unsigned* status) {
+                                                      unsigned epoch, unsigned long long wait_ns, unsigned* status,
+                                                      const unsigned* ovf_epoch, unsigned* ovf_flag) {
   pdl_launch_dependents();
   pdl_wait();
+  // the chunk's overflow as 0 / 1: its dispatch and its plan raise OVF_EPOCH to the chunk's number
+  if (ovf_flag && blockIdx.x == 0 && threadIdx.x == 0) *ovf_flag = *ovf_epoch == epoch ? 1u : 0u;
   if (flag_peers) {
     const bool ok = ep_meet(flag_peers, flags, world, rank, 1, epoch, blockIdx.x == 0, wait_ns, status);
     if (!__syncthreads_and(ok)) return;
@@ -371,8 +374,8 @@ extern "C" int ill_swiglu_w(int64_t n, int ff, float clamp, ill_dptr g, ill_dptr
 
 static int moe_sum_launch(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr map2, ill_dptr shared_, ill_dptr moe,
                           ill_dptr flag_peers, ill_dptr flags, int world, int rank, uint32_t epoch, int64_t wait_ns,
-                          ill_stream stream) {
-  if (d <= 0 || nu <= 0 || ntok < 0 || !check_ptr(down, 4) || !check_ptr(moe, 4) || (map & 3) || (map2 & 3) || (shared_ & 3))
+                          ill_dptr ovf_epoch, ill_dptr ovf_flag, ill_stream stream) {
+  if (d <= 0 || nu <= 0 || ntok < 0 || (ovf_epoch & 3) || (ovf_flag & 3) || (ovf_flag && !ovf_epoch) || !check_ptr(down, 4) || !check_ptr(moe, 4) || (map & 3) || (map2 & 3) || (shared_ & 3))
     return ILL_ERR_ARG;
   if (ntok == 0 && !flag_peers) return ILL_OK;
   long long nt = ntok;
@@ -383,7 +386,9 @@ static int moe_sum_launch(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr m
   unsigned* fl = (unsigned*)(uintptr_t)flags;
   unsigned long long wn = (unsigned long long)wait_ns;
   unsigned* stw = device_status_word();
-  void* args[] = {&d, &nu, &nt, &dp, &mp, &m2, &sp, &op, &fp, &fl, &world, &rank, &epoch, &wn, &stw};
+  const unsigned* oe = (const unsigned*)(uintptr_t)ovf_epoch;
+  unsigned* of = (unsigned*)(uintptr_t)ovf_flag;
+  void* args[] = {&d, &nu, &nt, &dp, &mp, &m2, &sp, &op, &fp, &fl, &world, &rank, &epoch, &wn, &stw, &oe, &of};
   long long blocks = (ntok * d + 255) / 256;
   if (blocks < 1) blocks = 1;  // a rank without tokens still meets the others
   return launch_kernel((const void*)moe_sum_kernel, dim3((unsigned)blocks), dim3(256), 0, args, (cudaStream_t)stream);
@@ -391,16 +396,17 @@ static int moe_sum_launch(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr m
 
 extern "C" int ill_moe_sum(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr shared_, ill_dptr moe,
                            ill_stream stream) {
-  return moe_sum_launch(d, nu, ntok, down, map, 0, shared_, moe, 0, 0, 1, 0, 0, 0, stream);
+  return moe_sum_launch(d, nu, ntok, down, map, 0, shared_, moe, 0, 0, 1, 0, 0, 0, 0, 0, stream);
 }
 
 extern "C" int ill_moe_sum_sync(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr map2, ill_dptr shared_,
                                 ill_dptr moe, ill_dptr flag_peers, ill_dptr flags, int world, int rank, uint32_t epoch,
-                                int64_t wait_ns, ill_stream stream) {
+                                int64_t wait_ns, ill_dptr ovf_epoch, ill_dptr ovf_flag, ill_stream stream) {
   if (!flag_peers || !flags || (flag_peers & 7) || (flags & 3) || world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world ||
       wait_ns < 0)
     return ILL_ERR_ARG;
-  return moe_sum_launch(d, nu, ntok, down, map, map2, shared_, moe, flag_peers, flags, world, rank, epoch, wait_ns, stream);
+  return moe_sum_launch(d, nu, ntok, down, map, map2, shared_, moe, flag_peers, flags, world, rank, epoch, wait_ns, ovf_epoch, ovf_flag,
+                        stream);
 }
 
 // The ranks meet (slot SLOT of the flags), nothing else: one block.

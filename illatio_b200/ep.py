@@ -356,6 +356,7 @@ class EpCapScratch:
         self.rc = torch.empty(world, per, **i32)
         self.lcounts, self.lbases, self.total = torch.empty(per, **i32), torch.empty(per, **i32), torch.zeros(1, **i32)
         self.overflow = torch.zeros(1, **i32)
+        self.ovf_epoch, self.ovf1 = torch.zeros(1, **i32), torch.zeros(1, **i32)  # the last chunk that overflowed; a spare flag
         self.pslot, self.smap2 = torch.empty(rows, **i32), torch.empty(rows, **i32)
         self.p2r, self.r2p = torch.zeros(tot, **i32), torch.zeros(tot, **i32)
         self.xq = torch.empty(n * d, dtype=torch.int8, **dev)
@@ -452,15 +453,21 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None, wait_ns=0)
     call("ill_moe_group", rows, E, nu, ptr(sc.sel), ptr(sc.w), ptr(sc.group), ptr(sc.counts), ptr(sc.bases), ptr(sc.rmap),
          ptr(sc.smap), ptr(sc.wrow), st)
     me = dist.get_rank(group) if dist.is_initialized() else 0
-    call("ill_quant_q8_k", ptr(norms), ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), n * d // 256, st)
     if sc.peers is not None:
-        # the dispatch without a collective: counts and rows are stored straight into the receivers' buffers
-        # over NVLink, then the ranks meet
-        call("ill_ep_put_counts", world, per, me, ptr(sc.counts), ptr(sc.peers_rc), ptr(sc.overflow), st)
-        call("ill_ep_pack_cap", rows, d, ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), per,
-             world, cap, 0, ptr(sc.pslot), ptr(sc.overflow), ptr(sc.peers_rows), me, st)
+        # the dispatch without a collective, in one launch: every (token, slot) row is quantized straight into its
+        # packed form in the owner's slab over NVLink, and the counts go into the owners' tables; then the ranks meet
         sc.epoch += 1
+        if rows >= (world * per + 127) // 128:
+            call("ill_ep_dispatch", rows, d, ptr(norms), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), ptr(sc.counts), per, world, cap,
+                 me, ptr(sc.peers_rows), ptr(sc.peers_rc), ptr(sc.pslot), ptr(sc.ovf_epoch), sc.epoch, st)
+        else:  # fewer rows than it takes blocks to carry the counts: the three steps apart
+            call("ill_quant_q8_k", ptr(norms), ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), n * d // 256, st)
+            call("ill_ep_put_counts", world, per, me, ptr(sc.counts), ptr(sc.peers_rc), 0, st)
+            sc.ovf1.zero_()
+            call("ill_ep_pack_cap", rows, d, ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), per,
+                 world, cap, 0, ptr(sc.pslot), ptr(sc.ovf1), ptr(sc.peers_rows), me, st)
     else:
+        call("ill_quant_q8_k", ptr(norms), ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), n * d // 256, st)
         sc.overflow.zero_()
         if world > 1:  # my rows per expert, to each expert's rank: [world, per] both ways
             dist.all_to_all_single(sc.rc.view(-1), sc.counts, group=group)
@@ -474,7 +481,7 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None, wait_ns=0)
         # the ranks meet at the start of the plan kernel (flags in peer memory, a bounded wait): the slabs and the
         # table of counts are complete once every peer has said that its stores are out
         call("ill_ep_plan_dev_sync", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
-             ptr(sc.pdst), ptr(sc.total), ptr(sc.overflow), ptr(sc.peers_flags), ptr(sc.flags), sc.epoch, wait_ns, st)
+             ptr(sc.pdst), ptr(sc.total), ptr(sc.ovf_epoch), ptr(sc.peers_flags), ptr(sc.flags), sc.epoch, wait_ns, st)
     else:
         call("ill_ep_plan_dev", world, per, cap, me, ptr(sc.rc), ptr(sc.lcounts), ptr(sc.lbases), ptr(sc.p2r), ptr(sc.r2p),
              ptr(sc.pdst), ptr(sc.total), ptr(sc.overflow), st)
@@ -492,7 +499,9 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None, wait_ns=0)
         call("ill_moe_mm_id_peers", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts),
              ptr(sc.lbases), pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.pdst), ptr(sc.peers), d, st)
         call("ill_moe_sum_sync", d, nu, n, ptr(sc.back), ptr(sc.smap), ptr(sc.pslot), 0, ptr(sc.moe), ptr(sc.peers_flags),
-             ptr(sc.flags), world, me, sc.epoch, wait_ns, st)
+             ptr(sc.flags), world, me, sc.epoch, wait_ns, ptr(sc.ovf_epoch), ptr(sc.overflow), st)
+        if rows < (world * per + 127) // 128:
+            sc.overflow.bitwise_or_(sc.ovf1)
         return sc.moe, sc.overflow
     call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases),
          pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.p2r), ptr(sc.down), d, st)

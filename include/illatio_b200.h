@@ -396,7 +396,8 @@ ILL_API int ill_ep_plan_dev(int world, int per, int cap, int rank, ill_dptr rc, 
  * block); ill_ep_plan_dev_sync is ill_ep_plan_dev after a meeting in slot 0 (this rank's
  * rows and counts are in its peers' buffers; theirs are in its own once they have all said
  * so); ill_moe_sum_sync is ill_moe_sum after a meeting in slot 1, with row(t, s) =
- * MAP2[MAP[t*nu + s]] when MAP2 is given.  Two meetings a chunk order everything: a peer
+ * MAP2[MAP[t*nu + s]] when MAP2 is given (OVF_EPOCH / OVF_FLAG: see ill_ep_dispatch; both
+ * may be 0).  Two meetings a chunk order everything: a peer
  * cannot overwrite a buffer this rank still reads, because it passes the chunk's second
  * meeting only after this rank has enqueued everything before its own. */
 #define ILL_EP_IPC_HANDLE_BYTES 64
@@ -411,7 +412,22 @@ ILL_API int ill_ep_plan_dev_sync(int world, int per, int cap, int rank, ill_dptr
                                  uint32_t epoch, int64_t wait_ns, ill_stream stream);
 ILL_API int ill_moe_sum_sync(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr map, ill_dptr map2, ill_dptr shared_, ill_dptr moe,
                              ill_dptr flag_peers, ill_dptr flags, int world, int rank, uint32_t epoch, int64_t wait_ns,
-                             ill_stream stream);
+                             ill_dptr ovf_epoch, ill_dptr ovf_flag, ill_stream stream);
+
+/* The dispatch of an expert-parallel chunk in one launch: ill_quant_q8_k, ill_ep_put_counts
+ * and ill_ep_pack_cap (peer form) together.  X holds the tokens' activations as floats
+ * [tokens, cols] (16-byte aligned); row PLACE (of the ROWS (token, slot) rows, in the order
+ * ill_moe_group leaves them: W = its WROW, MAP = its RMAP, BASES / COUNTS its per-expert
+ * tables) is quantized -- the same bits as ill_quant_q8_k -- straight into the packed row
+ * stored in slab RANK of its expert's rank (PEERS_ROWS), and this rank's rows per expert go
+ * into row RANK of every rank's table (PEERS_RC).  A slab too small raises *OVERFLOW to EPOCH
+ * (>= 1, the chunk's number; the word is never cleared -- ill_ep_plan_dev_sync raises it the
+ * same way, and ill_moe_sum_sync turns "equals this chunk's number" into 0 / 1 at *OVF_FLAG
+ * when given OVF_EPOCH = this word).  Needs ROWS >= ceil(world*per / 128), else
+ * ILL_ERR_UNSUPPORTED (use the three calls).  No counterpart in the reference. */
+ILL_API int ill_ep_dispatch(int64_t rows, int cols, ill_dptr x, ill_dptr w, ill_dptr map, ill_dptr bases, ill_dptr counts, int per,
+                            int world, int cap, int rank, ill_dptr peers_rows, ill_dptr peers_rc, ill_dptr pslot, ill_dptr overflow,
+                            uint32_t epoch, ill_stream stream);
 
 /* Two matrices of every expert against the same rows in one launch (gate and up:
  * W_e at PTRS[e] + ADD into Y, at PTRS[e] + ADD2 into Y2; no YMAP).  The same

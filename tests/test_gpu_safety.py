@@ -74,7 +74,7 @@ def test_meeting_of_ranks_gives_up_when_a_peer_never_arrives(cuda_lib):
     down = torch.ones(n * nu, d, device="cuda")
     moe = torch.full((n, d), -7.0, device="cuda")
     _lib.call("ill_moe_sum_sync", d, nu, n, down.data_ptr(), 0, 0, 0, moe.data_ptr(), peers.data_ptr(), mine.data_ptr(), 2, 0,
-              epoch + 1, 1_000_000, None)
+              epoch + 1, 1_000_000, 0, 0, None)
     torch.cuda.synchronize()
     assert _status() == (5, 0x700) and (moe == -7.0).all()
     assert _lib.status("ill_ep_barrier", peers.data_ptr(), mine.data_ptr(), 65, 0, 0, 1, 0, None) == 1   # more ranks than flags
