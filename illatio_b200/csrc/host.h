@@ -32,4 +32,8 @@ int mv_common(int fmt, int mode, int nmat, const uint64_t* w, const int* rows, i
 // not fit in registers.  BIG: the launch moves 16 MB or more.
 bool mv_pick_lanes(int fmt, int units, bool glu, bool big, int* lanes, int* upt);
 
+// The several-token product on the tensor cores (mvt.cu); ILL_ERR_UNSUPPORTED where it has no kernel.
+int mvt_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, uint64_t xsum, uint64_t y, uint64_t bias, int acc,
+            int n, void* stream);
+
 }  // namespace ill

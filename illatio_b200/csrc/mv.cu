@@ -787,6 +787,11 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
   }
   const bool glu = mode != MODE_PLAIN;
   if (glu && n != 1) return ILL_ERR_ARG;
+  if (n >= 2 && !glu && nmat == 1 && !ptrs && !x_seg) {
+    // a few tokens: the tensor cores' int8 path where it is written (Q8_0, Q4_K, Q6_K), else the token loop below
+    const int rc_t = mvt_try(fmt, w[0], rows[0], cols, xq, xs, xsum, y[0], bias ? bias[0] : 0, acc, n, stream);
+    if (rc_t != ILL_ERR_UNSUPPORTED) return rc_t;
+  }
   MvPlan pl;
   int rc = ILL_ERR_UNSUPPORTED;
   if (n == 1) rc = plan_one(fmt, glu ? rows[0] : total_rows, cols, nseg, glu, &pl);
