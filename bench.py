@@ -519,12 +519,11 @@ def main():
                                         "fa <- glu(norm(h)); h += down(fa); head(norm(h))")
         configs["c1_token"] = chain_leg(D, B, torch, dev, (C1["hidden"], C1["qdim"], C1["kvdim"], C1["ffn"], C1["vocab"]), C1["layers"],
                                         Q8_0, Q8_0, 3 + rank, peak, "configs[0]: qwen2.5-0.5b, all Q8_0, one token (same chain)")
-        configs["c2_prefill_512"] = {"status": "not built",
-                                     "why": "the dense prefill GEMMs for Q8_0 / Q4_K / Q6_K (mm_q8_mma2, mm_q4k_mma, mm_q6k_mma: "
-                                            "src/cuda/dense.cu:885, src/cuda/kquant.cu:316-466) have no tensor-core kernel here yet; "
-                                            "the several-token matvec stops at 16 tokens"}
+        configs["c2_prefill_512"] = prefill_leg(D, B, torch, dev, (HIDDEN, QDIM, KVDIM, FFN, VOCAB), LAYERS, Q4_K, Q6_K, 5 + rank, 512,
+                                                tensor_peak())
         configs["c3_q6k_sweep"] = c3_sweep(D, B, torch, dev, peak, which)
         configs["c4_decode"] = c4_decode(D, B, torch, dev, peak)
+        configs["c4_ffn_head_chunk"] = c4_head_chunk(D, B, torch, dev, 4096, tensor_peak())
 
     # ---- the sharded paths
     sharded = {}
@@ -590,6 +589,112 @@ def main():
 
 
 # ------------------------------------------------------------------ configuration legs
+
+def prefill_leg(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed, n, tpeak):
+    """configs[1] as prefill: a chunk of N tokens through every in-scope product of the model (the chain of
+    chain_leg with N rows: RMSNorm fused with the quantizer, q / k / v / o, gate and up, SwiGLU, down), the head for
+    the last token only; one CUDA graph.  Attention itself is out of scope and stood in for by the query rows."""
+    m = build_chain_model(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed)
+    hidden, qdim, kvdim, ffn, vocab = dims
+    f = dict(dtype=torch.float32, device=dev)
+    h0 = torch.randn(n * hidden, **f)
+    h, q, k, v = torch.empty(n * hidden, **f), torch.empty(n * qdim, **f), torch.empty(n * kvdim, **f), torch.empty(n * kvdim, **f)
+    ga, ub = torch.empty(n * ffn, **f), torch.empty(n * ffn, **f)
+    acts = {(name, kind): D.make_qact(n * width, kind, device=dev) for name, width in (("h", hidden), ("q", qdim), ("fa", ffn))
+            for kind in ("q8", "q8k")}
+    last = D.make_qact(hidden, D.matrix_act_kind(m["head"]), device=dev)
+    launches = [0]
+
+    def chunk():
+        h.copy_(h0)
+        c = 1
+        for L in m["layers"]:
+            a = D.rmsnorm_q8(h, L["nw1"], acts[("h", D.matrix_act_kind(L["q"]))], hidden, EPS, n=n)
+            D.cmat_mul(L["q"], a, q, n)
+            D.cmat_mul(L["k"], a, k, n)
+            if D.matrix_act_kind(L["v"]) != a.kind:
+                a = D.rmsnorm_q8(h, L["nw1"], acts[("h", D.matrix_act_kind(L["v"]))], hidden, EPS, n=n)
+                c += 1
+            D.cmat_mul(L["v"], a, v, n)
+            D.cmat_mul(L["o"], D.quant_q8(q, acts[("q", D.matrix_act_kind(L["o"]))]), h, n, acc=True)
+            a = D.rmsnorm_q8(h, L["nw2"], acts[("h", D.matrix_act_kind(L["gate"]))], hidden, EPS, n=n)
+            D.cmat_mul(L["gate"], a, ga, n)
+            D.cmat_mul(L["up"], a, ub, n)
+            D.swiglu(ga, ub, ga, ffn)
+            D.cmat_mul(L["down"], D.quant_q8(ga, acts[("fa", D.matrix_act_kind(L["down"]))]), h, n, acc=True)
+            c += 11
+        D.cmat_mul(m["head"], D.rmsnorm_q8(h[(n - 1) * hidden:], m["nwf"], last, hidden, EPS), m["logits"], 1)
+        launches[0] = c + 2
+    chunk()
+    torch.cuda.synchronize()
+    finite = bool(torch.isfinite(m["logits"]).all()) and bool(torch.isfinite(h).all())
+    # parity, outside the timed region: the chunk product of the first layer's gate matrix against the one-token
+    # product (itself held to the CPU oracle by the tests) for three of the tokens
+    L0 = m["layers"][0]
+    a = D.rmsnorm_q8(h0, L0["nw2"], acts[("h", D.matrix_act_kind(L0["gate"]))], hidden, EPS, n=n)
+    D.cmat_mul(L0["gate"], a, ga, n)
+    worst = 0.0
+    one = D.make_qact(hidden, a.kind, device=dev)
+    y1 = torch.empty(ffn, **f)
+    for t in (0, n // 2 + 1, n - 1):
+        D.rmsnorm_q8(h0[t * hidden:(t + 1) * hidden], L0["nw2"], one, hidden, EPS)
+        D.cmat_mul(L0["gate"], one, y1, 1)
+        worst = max(worst, float(((ga[t * ffn:(t + 1) * ffn] - y1).abs().max() / y1.abs().max()).item()))
+    g = graph_of(chunk, torch)
+    us = time_us(g.replay, 3, torch)
+    body = m["bytes"] - m["head"].nbytes
+    weights = sum(w.rows * w.cols for L in m["layers"] for w in L.values() if isinstance(w, D.CMat))
+    tops = 2.0 * weights * n / us / 1e6
+    out = {"workload": "configs[1], a %d-token chunk through %d layers' products and the last token's head" % (n, layers),
+           "tokens": n, "ms": us / 1e3, "tokens_per_s": n / us * 1e6, "launches": launches[0], "how": "one CUDA graph",
+           "int8_TOPS": tops, "frac_of_bf16_tensor_peak": tops / tpeak[0] if tpeak and tpeak[0] else None,
+           "weight_MB_read_once": body / 1e6,
+           "kernel": "mmd_kernel: mma.sync int8, 128 rows x 128 tokens a CTA, weights by cp.async.bulk rings, activations by cp.async",
+           "parity": {"finite": finite, "chunk_vs_one_token_max_rel": worst, "ok": finite and worst < 2e-6}}
+    del m, g
+    torch.cuda.empty_cache()
+    return out
+
+
+def c4_head_chunk(D, B, torch, dev, n, tpeak):
+    """configs[3]'s chunk before its routing (DK-FFN-HEAD-CHUNK): RMSNorm with the Q8_0 quantizer, the router's
+    logits (F16 [256, 4096]) and the shared Q8_0 expert over N tokens."""
+    from illatio_b200 import cuda_ds4f_prefill as P
+    from illatio_b200 import cuda_ds4f as M
+    d, ff, ne, clamp = 4096, 2048, 256, 10.0
+    ws = [D.CMat("sh", Q8_0, r, c, B.synth_matrix_torch(Q8_0, r, c, seed=90 + i, device=dev)) for i, (r, c) in enumerate(((ff, d), (ff, d), (d, ff)))]
+    g = torch.Generator(device=dev)
+    g.manual_seed(4)
+    router = (torch.randn(ne, d, device=dev, generator=g) * 0.05).to(torch.float16)
+    cur = torch.randn(n, d, device=dev, generator=g)
+    nw = torch.rand(d, device=dev, generator=g) + 0.5
+    hs = P.HeadScratch(n, d, ff, ne, device=dev)
+
+    def head():
+        P.dk_ffn_head_chunk(cur, nw, EPS, router, ws[0], ws[1], ws[2], clamp, hs)
+    head()
+    torch.cuda.synchronize()
+    # parity, outside the timed region: three tokens through the one-token drivers (DK-MV16, the shared expert as
+    # DK-FFN-HEAD runs it), which the tests hold to the CPU oracle
+    worst_l = worst_s = 0.0
+    y1, l1 = torch.empty(d, device=dev), torch.empty(ne, device=dev)
+    for t in (0, n // 2 + 1, n - 1):
+        M.dk_mv16(router, hs.norm2[t], l1)
+        M.dk_shared(ws[0], ws[1], ws[2], hs.norm2[t], clamp, y1)
+        worst_l = max(worst_l, float(((hs.logits[t] - l1).abs().max() / l1.abs().max()).item()))
+        worst_s = max(worst_s, float(((hs.sout[t] - y1).abs().max() / y1.abs().max()).item()))
+    gr = graph_of(head, torch)
+    us = time_us(gr.replay, 5, torch)
+    macs = n * (3.0 * d * ff + ne * d)
+    out = {"workload": "configs[3]: %d tokens, RMSNorm + router logits + shared Q8_0 expert (gate / up / down)" % n, "tokens": n,
+           "ms": us / 1e3, "launches": 8, "how": "one CUDA graph", "TOPS": 2.0 * macs / us / 1e6,
+           "frac_of_bf16_tensor_peak": 2.0 * macs / us / 1e6 / tpeak[0] if tpeak and tpeak[0] else None,
+           "parity": {"logits_vs_one_token_max_rel": worst_l, "shared_vs_one_token_max_rel": worst_s,
+                      "ok": worst_l < 1e-5 and worst_s < 1e-5}}
+    del gr, ws, hs
+    torch.cuda.empty_cache()
+    return out
+
 
 def c3_sweep(D, B, torch, dev, peak, which):
     """configs[2]: the Q6_K matrices of a 27B-scale model at batch 1, 4 and 16, cold (a rotation of copies whose
@@ -677,6 +782,11 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
            "collective": "in-place all-gather of fp32 logits (NCCL)" if world > 1 else "none (one GPU)",
            "GBps_is": "the whole matrix's bytes over the time of the slowest rank: an aggregate over the ranks"}
     nb = B.matrix_bytes(Q6_K, rows, cols)
+    sl = end - first
+    pg = EP.PeerGather(16 * (rows - (world - 1) * (rows // world)) * 4, world, device=dev) if world > 1 else None
+    if pg is not None:
+        out["collective"] = ("peer stores of the rank's logits into every peer's buffer and one flag meeting (ill_peer_put); "
+                             "NCCL's in-place all-gather timed beside it")
     for n in (1, 4, 16):
         xx = torch.randn(n * cols, device=dev, generator=torch.Generator(device=dev).manual_seed(5))
         act = D.make_qact(n * cols, "q8k", device=dev)
@@ -699,6 +809,18 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
             product_only()
             if world > 1:
                 gather_only()
+        us_peer = None
+        if pg is not None:
+            mine = [pg.buffer(i)[rank][:n * sl * 4].view(torch.float32) for i in (0, 1)]
+
+            def both_peer():
+                i = it[0] & 1
+                it[0] += 1
+                D.cmat_mul(slices[i], act, mine[i], n)
+                pg.put(i, n * sl * 4)
+            barrier()
+            us_peer = time_us(both_peer, 20, torch)
+            barrier()
         barrier()
         us_both = time_us(both, 20, torch)
         barrier()
@@ -707,15 +829,27 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
         if world > 1:
             barrier()
             us_gather = time_us(gather_only, 20, torch)
-        us_both, us_prod, us_gather = max_over_ranks([us_both, us_prod, us_gather])
+        us_both, us_prod, us_gather, us_peer_m = max_over_ranks([us_both, us_prod, us_gather, us_peer or 0.0])
+        us_nccl = us_both
+        if pg is not None:
+            us_both = us_peer_m
         res = {"us_per_token": us_both, "GBps": nb / us_both / 1e3, "us_product": us_prod, "us_all_gather": us_gather,
+               "us_with_nccl_all_gather": us_nccl if pg is not None else None,
                "product_frac_of_hbm_per_gpu": (nb / world) / us_prod / 1e3 / peak}
         if n == 1:
             # parity and the one-GPU time, on rank 0 (the whole matrix, copy 0)
             it[0] = 0
-            both()
-            torch.cuda.synchronize()
-            got = gathered.reshape(-1).clone()
+            if pg is not None:
+                both_peer()
+                torch.cuda.synchronize()
+                barrier()
+                per = rows // world
+                got = torch.cat([pg.buffer(0)[r][:(rows - r * per if r == world - 1 else per) * 4].view(torch.float32)
+                                 for r in range(world)]).clone()
+            else:
+                both()
+                torch.cuda.synchronize()
+                got = gathered.reshape(-1).clone()
             vs = None
             ok = None
             if rank == 0:
@@ -739,7 +873,11 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
             res["vs_1gpu"] = vs
             res["parity"] = {"gathered_logits_equal_one_gpu_product": ok, "ranks": world}
         out["n%d" % n] = res
-    del slices
+    if pg is not None:
+        torch.cuda.synchronize()
+        barrier()
+        pg.close()
+    del slices, pg
     torch.cuda.empty_cache()
     return out
 

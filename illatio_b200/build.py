@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libillatio_b200.so")
-SOURCES = ["lib.cu", "quant.cu", "mv.cu", "moe.cu", "mm_id.cu", "mvf.cu", "decode.cu", "mvt.cu"]
+SOURCES = ["lib.cu", "quant.cu", "mv.cu", "moe.cu", "mm_id.cu", "mvf.cu", "decode.cu", "mvt.cu", "mmd.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",

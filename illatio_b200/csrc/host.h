@@ -35,5 +35,8 @@ bool mv_pick_lanes(int fmt, int units, bool glu, bool big, int* lanes, int* upt)
 // The several-token product on the tensor cores (mvt.cu); ILL_ERR_UNSUPPORTED where it has no kernel.
 int mvt_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, uint64_t xsum, uint64_t y, uint64_t bias, int acc,
             int n, void* stream);
+// the same for a chunk of tokens (more than 16): mmd.cu
+int mmd_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, uint64_t xsum, uint64_t y, uint64_t bias, int acc,
+            int n, void* stream);
 
 }  // namespace ill

@@ -417,6 +417,74 @@ __global__ void __launch_bounds__(64) ep_barrier_kernel(const unsigned long long
   ep_meet(flag_peers, flags, world, rank, slot, epoch, true, wait_ns, status);
 }
 
+// ---- an all-gather by peer stores --------------------------------------------------------------
+// Every CTA stores its share of SRC into every peer's buffer, fences, and takes a ticket; the CTA that takes the
+// last one holds the meeting: its signal says that all of this rank's stores are out, and once every peer's
+// signal is in, their blocks are complete in this rank's buffer.
+__device__ unsigned g_put_ticket;  // CTAs of the running peer_put_kernel that have stored their share (one call at a time a device)
+
+__global__ void __launch_bounds__(256) peer_put_kernel(const u8* __restrict__ src, long long nbytes, const unsigned long long* dst_peers,
+                                                       long long dst_off, const unsigned long long* flag_peers, unsigned* flags,
+                                                       int world, int rank, int slot, unsigned epoch, unsigned long long wait_ns,
+                                                       int vec, unsigned* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+  if (vec) {
+    const long long nv = nbytes / 16;
+    for (long long i = tid; i < nv; i += nthr) {
+      const uint4 v = ((const uint4*)src)[i];
+      for (int p = 0; p < world; ++p) {
+        u8* dst = (u8*)(uintptr_t)dst_peers[p] + dst_off;
+        if (dst != src) ((uint4*)dst)[i] = v;
+      }
+    }
+    for (long long i = nv * 4 + tid; i < nbytes / 4; i += nthr) {
+      const uint32_t v = ((const uint32_t*)src)[i];
+      for (int p = 0; p < world; ++p) {
+        u8* dst = (u8*)(uintptr_t)dst_peers[p] + dst_off;
+        if (dst != src) ((uint32_t*)dst)[i] = v;
+      }
+    }
+  } else {
+    for (long long i = tid; i < nbytes / 4; i += nthr) {
+      const uint32_t v = ((const uint32_t*)src)[i];
+      for (int p = 0; p < world; ++p) {
+        u8* dst = (u8*)(uintptr_t)dst_peers[p] + dst_off;
+        if (dst != src) ((uint32_t*)dst)[i] = v;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int last;
+  if (threadIdx.x == 0) last = atomicAdd(&g_put_ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!last) return;
+  if (threadIdx.x == 0) g_put_ticket = 0;
+  ep_meet(flag_peers, flags, world, rank, slot, epoch, true, wait_ns, status);
+}
+
+extern "C" int ill_peer_put(ill_dptr src, int64_t nbytes, ill_dptr dst_peers, int64_t dst_off, ill_dptr flag_peers, ill_dptr flags,
+                            int world, int rank, int slot, uint32_t epoch, int64_t wait_ns, ill_stream stream) {
+  if (!src || nbytes <= 0 || !dst_peers || dst_off < 0 || !flag_peers || !flags || world < 1 || world > EP_MAX_RANKS || rank < 0 ||
+      rank >= world || slot < 0 || slot >= EP_FLAG_SLOTS || wait_ns < 0)
+    return ILL_ERR_ARG;
+  if ((src & 3) || (nbytes & 3) || (dst_off & 3) || (dst_peers & 7) || (flag_peers & 7) || (flags & 3)) return ILL_ERR_ALIGN;
+  const u8* sp = (const u8*)(uintptr_t)src;
+  long long nb = nbytes, off = dst_off;
+  const unsigned long long* dp = (const unsigned long long*)(uintptr_t)dst_peers;
+  const unsigned long long* fp = (const unsigned long long*)(uintptr_t)flag_peers;
+  unsigned* fl = (unsigned*)(uintptr_t)flags;
+  unsigned long long wn = (unsigned long long)wait_ns;
+  int vec = !(src & 15) && !(dst_off & 15);  // the peers' buffers are assumed 16-byte aligned when the offset is
+  unsigned* stw = device_status_word();
+  int grid = (int)((nbytes / 16 + 255) / 256);
+  grid = grid < 1 ? 1 : grid > 512 ? 512 : grid;  // grid-stride loops: a few CTAs an SM are enough to fill the links
+  void* args[] = {&sp, &nb, &dp, &off, &fp, &fl, &world, &rank, &slot, &epoch, &wn, &vec, &stw};
+  return launch_kernel((const void*)peer_put_kernel, dim3(grid), dim3(256), 0, args, (cudaStream_t)stream);
+}
+
 extern "C" int64_t ill_ep_flags_bytes(void) { return (int64_t)EP_MAX_RANKS * EP_FLAG_SLOTS * 4; }
 
 extern "C" int ill_ep_barrier(ill_dptr flag_peers, ill_dptr flags, int world, int rank, int slot, uint32_t epoch, int64_t wait_ns,

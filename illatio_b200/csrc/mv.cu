@@ -774,7 +774,7 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
               ill_stream stream) {
   const int bw = fmt_block_weights(fmt);
   if (!bw || nmat < 1 || nmat > MV_MAX_MATS || cols <= 0 || cols % (bw == 32 ? 32 : 256)) return ILL_ERR_ARG;
-  if (n < 1 || n > MV_MAX_TOK || nseg < 1 || nseg > 65535) return ILL_ERR_ARG;
+  if (n < 1 || nseg < 1 || nseg > 65535) return ILL_ERR_ARG;
   if (!xq || !xs || (needs_bsums(fmt) && !xsum)) return ILL_ERR_ARG;
   if (xq & 15 || xs & 3 || xsum & 7) return ILL_ERR_ALIGN;
   long long total_rows = 0;
@@ -788,10 +788,15 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
   const bool glu = mode != MODE_PLAIN;
   if (glu && n != 1) return ILL_ERR_ARG;
   if (n >= 2 && !glu && nmat == 1 && !ptrs && !x_seg) {
-    // a few tokens: the tensor cores' int8 path where it is written (Q8_0, Q4_K, Q6_K), else the token loop below
-    const int rc_t = mvt_try(fmt, w[0], rows[0], cols, xq, xs, xsum, y[0], bias ? bias[0] : 0, acc, n, stream);
+    // several tokens: the tensor cores' int8 path where it is written (Q8_0, Q4_K, Q6_K; up to 16 tokens with the
+    // activations resident, chunks with them streamed), else the token loop below
+    int rc_t = ILL_ERR_UNSUPPORTED;
+    if (n <= 16) rc_t = mvt_try(fmt, w[0], rows[0], cols, xq, xs, xsum, y[0], bias ? bias[0] : 0, acc, n, stream);
+    // a chunk -- or a few tokens of rows too long for their activations to stay in shared memory
+    if (rc_t == ILL_ERR_UNSUPPORTED) rc_t = mmd_try(fmt, w[0], rows[0], cols, xq, xs, xsum, y[0], bias ? bias[0] : 0, acc, n, stream);
     if (rc_t != ILL_ERR_UNSUPPORTED) return rc_t;
   }
+  if (n > MV_MAX_TOK) return ILL_ERR_UNSUPPORTED;  // the token loop below takes 16 at most: the caller splits the chunk
   MvPlan pl;
   int rc = ILL_ERR_UNSUPPORTED;
   if (n == 1) rc = plan_one(fmt, glu ? rows[0] : total_rows, cols, nseg, glu, &pl);

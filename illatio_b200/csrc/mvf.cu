@@ -48,7 +48,8 @@ __device__ __forceinline__ void dense_vec(const uint4 v, float (&f)[8]) {
 
 constexpr int MVF_MAXN = 16;
 
-// Y[t * y_stride + r] = W[r] . X[t], r < rows, t < n <= 16
+// Y[t * y_stride + r] = W[r] . X[t], r < rows, t < n: blockIdx.y takes the tokens sixteen at a time (a chunk's
+// router logits: the matrix is small and stays in L2 between the token batches)
 template <int TYPE>
 __global__ void __launch_bounds__(256) mv_dense_kernel(const u8* __restrict__ w, int rows, int cols, const float* __restrict__ x,
                                                        float* __restrict__ y, int n, long long y_stride, int vec_ok) {
@@ -57,6 +58,12 @@ __global__ void __launch_bounds__(256) mv_dense_kernel(const u8* __restrict__ w,
   const int lane = threadIdx.x & 31;
   const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= rows) return;
+  {
+    const long long t0 = (long long)blockIdx.y * MVF_MAXN;
+    x += t0 * cols;
+    y += t0 * y_stride;
+    n = min(n - (int)t0, MVF_MAXN);
+  }
   constexpr int EB = DenseElt<TYPE>::BYTES, VE = 16 / EB;  // elements a 16-byte load
   const u8* row = w + (long long)r * cols * EB;
   float sum[MVF_MAXN];
@@ -106,7 +113,7 @@ using namespace ill;
 
 extern "C" int ill_mv_dense(int type, ill_dptr w, int rows, int cols, ill_dptr x, ill_dptr y, int n, int64_t y_stride,
                             ill_stream stream) {
-  if ((type != ILL_F32 && type != ILL_F16 && type != ILL_BF16) || rows <= 0 || cols <= 0 || n < 1 || n > MVF_MAXN || !w || !x ||
+  if ((type != ILL_F32 && type != ILL_F16 && type != ILL_BF16) || rows <= 0 || cols <= 0 || n < 1 || n > 65535 * MVF_MAXN || !w || !x ||
       !y || y_stride < rows)
     return ILL_ERR_ARG;
   const int eb = type == ILL_F32 ? 4 : 2;
@@ -120,5 +127,5 @@ extern "C" int ill_mv_dense(int type, ill_dptr w, int rows, int cols, ill_dptr x
   void* args[] = {&wp, &rows, &cols, &xp, &yp, &n, &ys, &vec_ok};
   const void* k = type == ILL_F32 ? (const void*)mv_dense_kernel<ILL_F32>
                   : type == ILL_F16 ? (const void*)mv_dense_kernel<ILL_F16> : (const void*)mv_dense_kernel<ILL_BF16>;
-  return launch_kernel(k, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, args, (cudaStream_t)stream);
+  return launch_kernel(k, dim3((unsigned)((rows + 7) / 8), (unsigned)((n + MVF_MAXN - 1) / MVF_MAXN)), dim3(256), 0, args, (cudaStream_t)stream);
 }

@@ -22,6 +22,7 @@
 // (src/cuda-dense.lisp:220-255; src/cuda/dense.cu:643-885, src/cuda/kquant.cu:169-466) for Q8_0, Q4_K and Q6_K.
 #include "formats.cuh"
 #include "host.h"
+#include "mma_i8.cuh"
 
 namespace ill {
 
@@ -47,29 +48,6 @@ struct MtParams {
   unsigned* status;
 };
 
-__device__ __forceinline__ void mma_k32(int (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2], bool a_unsigned) {
-  if (a_unsigned)
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-  else
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
-__device__ __forceinline__ void mma_k16_u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-               : "r"(a0), "r"(a1), "r"(b0));
-}
-
-// a 32-bit word at any byte address of shared memory
-__device__ __forceinline__ uint32_t lds32u(const u8* p) {
-  const uint32_t mis = (uint32_t)(uintptr_t)p & 3u;
-  const uint32_t* b = (const uint32_t*)(p - mis);
-  return __funnelshift_r(b[0], b[1], 8u * mis);
-}
-__device__ __forceinline__ float ldh(const u8* p) { return h2f(*(const u16*)p); }  // p is 2-byte aligned
 
 // The tokens' activations in shared memory.
 struct MtX {
@@ -111,12 +89,6 @@ template <int NT8> struct MtBlock<ILL_Q8_0, NT8> {
     }
   }
 };
-
-// get_scale_min_k4 (src/kquant.lisp:64-72) for group J of the 12 packed bytes at Q
-__device__ __forceinline__ void scale_min_k4(const u8* q, int j, int& sc, int& mn) {
-  if (j < 4) { sc = q[j] & 63; mn = q[j + 4] & 63; }
-  else { sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4); mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
-}
 
 template <int NT8> struct MtBlock<ILL_Q4_K, NT8> {
   static constexpr int BS_PER = 8;  // sums of 32 a block
@@ -166,17 +138,6 @@ template <int NT8> struct MtBlock<ILL_Q4_K, NT8> {
       }
   }
 };
-
-__device__ __forceinline__ void mma_k16_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0, bool b_unsigned) {
-  if (b_unsigned)
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(b0));
-  else
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(b0));
-}
 
 template <int NT8> struct MtBlock<ILL_Q6_K, NT8> {
   static constexpr int BS_PER = 16;  // a block's sixteen sums of 16, staged as two bytes each: (sum >> 4, sum & 15)

@@ -111,7 +111,9 @@ def cmat_mul(w, act, y, n=1, bias=None, acc=False):
     """CMAT-MUL (src/cuda-dense.lisp:220-248): Y = W X for N tokens (token t's X
     at t*cols, its Y at t*rows), or Y += it when ACC."""
     done = 0
-    kmax = 16  # the kernel takes up to 16 tokens a launch -- fewer when their activations do not fit beside the stages
+    # Q8_0 / Q4_K / Q6_K take a whole chunk of tokens in one launch; the other formats up to 16 tokens --
+    # fewer when their activations do not fit beside the stages
+    kmax = n
     while done < n:
         k = min(kmax, n - done)
         sc = w.cols // (32 if act.kind == "q8" else 256)
@@ -120,7 +122,7 @@ def cmat_mul(w, act, y, n=1, bias=None, acc=False):
                          0 if act.kind == "q8" else act.xsum.data_ptr() + 2 * done * (w.cols // 16),
                          y.data_ptr() + 4 * done * w.rows, _ptr(bias), 1 if acc else 0, k, _stream())
         if rc == 3 and k > 1:   # ILL_ERR_UNSUPPORTED: long rows, many tokens
-            kmax = k // 2
+            kmax = 16 if k > 16 else k // 2
             continue
         if rc:
             _lib.call("ill_mv", w.type, _ptr(w.qs), w.rows, w.cols, act.xq.data_ptr() + done * w.cols,
@@ -178,6 +180,13 @@ def glu_mul(g, u, act, fa, n=1, fb=None):
     cmat_mul(u, act, fb, n)
     fa.copy_((fa / (1.0 + torch.exp(-fa))) * fb)  # the reference's swiglu kernel; not on the decode path
     return fa
+
+
+def swiglu(g, u, out, ff, clamp=3.0e38):
+    """OUT = silu(G) * U over whole rows of FF values (the reference's swiglu launch between the gate / up and the
+    down products of a prefill chunk, src/cuda-dense.lisp:326-339); CLAMP as d4_swiglu_w clamps, off by default."""
+    _lib.call("ill_swiglu_w", g.numel(), ff, float(clamp), _ptr(g), _ptr(u), 0, _ptr(out), _stream())
+    return out
 
 
 OP_MV, OP_GLU = 0, 1

@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from . import cuda_dense as D
 from .blocks import Q2_K
-from .cuda_ds4f import ExpertPool, swiglu_w
+from .cuda_ds4f import _DENSE_TYPES, ExpertPool, swiglu_w
 
 
 def _ptr(t):
@@ -106,3 +106,34 @@ def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, s
     mm_id(pool, pool.down_fmt, ff, d, 2 * pool.gate_bytes, sc, sc.mh, sc.me, sc.midq.xs, None, sc.down)
     _lib.call("ill_moe_sum", d, nu, n, _ptr(sc.down), _ptr(sc.smap), _ptr(shared), _ptr(sc.moe), st)
     return sc.moe
+
+
+class HeadScratch:
+    """The buffers of DK-FFN-HEAD-CHUNK for up to N tokens: NORM2 [n, d] floats and their Q8_0 quantization, the
+    router's LOGITS [n, ne], the shared expert's gate / up [n, ff], the middle values' quantization, SOUT [n, d]."""
+
+    def __init__(self, n, d, ff, ne, device="cuda"):
+        f = dict(dtype=torch.float32, device=device)
+        self.n, self.d, self.ff, self.ne = n, d, ff, ne
+        self.norm2, self.logits = torch.empty(n, d, **f), torch.empty(n, ne, **f)
+        self.sg, self.su, self.sout = torch.empty(n, ff, **f), torch.empty(n, ff, **f), torch.empty(n, d, **f)
+        self.nq, self.mq = D.make_qact(n * d, "q8", device=device), D.make_qact(n * ff, "q8", device=device)
+
+
+def dk_ffn_head_chunk(cur, norm_w, eps, router, sh_gate, sh_up, sh_down, clamp, hs):
+    """DK-FFN-HEAD-CHUNK (src/cuda-ds4f-prefill.lisp:285-303) past its hyper-connection step: CUR [n, d] -> RMSNorm
+    (NORM2) -> the router's logits (ROUTER: an unquantized [ne, d] tensor) and the shared expert
+    (SH_GATE / SH_UP / SH_DOWN: Q8_0 matrices; d4_swiglu_w with weights of one between them) over the whole chunk.
+    Returns (norm2, logits, sout): what DK-FFN-ROUTED-CHUNK takes as NORMS, LOGITS and SHARED."""
+    n, d = cur.shape
+    ne = router.shape[0]
+    norm2, logits, sout = hs.norm2[:n], hs.logits[:n], hs.sout[:n]
+    sg, su = hs.sg[:n], hs.su[:n]
+    D.rmsnorm_q8(cur, norm_w, hs.nq, d, eps, n=n, h=norm2, f16_scale=False)     # DK-RMS and DK-Q8MM's quantization of NORM2
+    _lib.call("ill_mv_dense", _DENSE_TYPES[router.dtype], _ptr(router), ne, d, _ptr(norm2), _ptr(logits), n, ne, _stream())
+    D.cmat_mul(sh_gate, hs.nq, sg, n)
+    D.cmat_mul(sh_up, hs.nq, su, n)
+    _lib.call("ill_swiglu_w", n * hs.ff, hs.ff, float(clamp), _ptr(sg), _ptr(su), 0, _ptr(sg), _stream())
+    D.quant_q8(sg, hs.mq, f16_scale=False)
+    D.cmat_mul(sh_down, hs.mq, sout, n)
+    return norm2, logits, sout

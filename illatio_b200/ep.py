@@ -424,6 +424,67 @@ class EpCapScratch:
         self._mapped = []
 
 
+class PeerGather:
+    """An all-gather without a collective library, for the row-split head: every rank holds two buffers of WORLD
+    blocks of BLOCK_BYTES (they alternate, so a rank may still read one call's result while its peers store the
+    next call's) and the flags the ranks meet at, all in one allocation that the peers map through CUDA IPC.  A rank
+    writes its block in place (block(i) of its own buffer), and put() stores it into every peer's buffer and holds
+    the meeting (ill_peer_put): when the stream has passed it, the whole buffer is complete on this rank."""
+
+    def __init__(self, block_bytes, world, group=None, device="cuda"):
+        import ctypes
+        from . import _lib
+        grp = group if group is not None else dist.group.WORLD
+        self.world, self.rank = world, dist.get_rank(grp) if world > 1 else 0
+        self.block = (block_bytes + 255) // 256 * 256
+        fb = int(_lib.lib().ill_ep_flags_bytes())
+        self.buf_bytes = self.block * world
+        self.shared = torch.zeros(2 * self.buf_bytes + fb, dtype=torch.uint8, device=device)
+        base = self.shared.data_ptr()
+        bases, self._mapped = [base], []
+        if world > 1:
+            handle = ctypes.create_string_buffer(64)
+            off = ctypes.c_int64(0)
+            with torch.cuda.device(self.shared.device):
+                _lib.call("ill_ep_ipc_export", base, handle, ctypes.byref(off))
+                torch.cuda.synchronize()
+                every = [None] * world
+                dist.all_gather_object(every, (handle.raw, off.value), group=grp)
+                bases = []
+                for r, (h, o) in enumerate(every):
+                    if r == self.rank:
+                        bases.append(base)
+                        continue
+                    out = ctypes.c_uint64(0)
+                    _lib.call("ill_ep_ipc_open", h, o, ctypes.byref(out))
+                    self._mapped.append((out.value, o))
+                    bases.append(out.value)
+        self.peers = [torch.tensor([b + i * self.buf_bytes for b in bases], dtype=torch.int64, device=device) for i in (0, 1)]
+        self.peers_flags = torch.tensor([b + 2 * self.buf_bytes for b in bases], dtype=torch.int64, device=device)
+        self.flags = self.shared[2 * self.buf_bytes:].view(torch.int32)
+        self.epoch = 0
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=grp)  # every rank's buffer is zeroed and mapped before anybody stores into one
+
+    def buffer(self, i):
+        """Buffer I (0 or 1) as bytes [world, block]."""
+        return self.shared[i * self.buf_bytes:(i + 1) * self.buf_bytes].view(self.world, self.block)
+
+    def put(self, i, nbytes, wait_ns=0):
+        """This rank's block of buffer I (its first NBYTES) into every peer's buffer I, and the meeting."""
+        from . import _lib
+        self.epoch += 1
+        mine = self.shared.data_ptr() + i * self.buf_bytes + self.rank * self.block
+        _lib.call("ill_peer_put", mine, nbytes, self.peers[i].data_ptr(), self.rank * self.block, self.peers_flags.data_ptr(),
+                  self.flags.data_ptr(), self.world, self.rank, 2, self.epoch, wait_ns, torch.cuda.current_stream().cuda_stream)
+
+    def close(self):
+        for ptr_, off in self._mapped:
+            _lib_close(ptr_, off)
+        self._mapped = []
+
+
 def _lib_close(ptr_, off):
     from . import _lib
     _lib.status("ill_ep_ipc_close", ptr_, off)

@@ -142,7 +142,15 @@ ILL_API int ill_dequant_rows(int fmt, ill_dptr w, int cols, ill_dptr row_ids, in
  * be 0.  Replaces mv_q8 (src/cuda/dense.cu:194), mv_k (src/cuda/kquant.cu:169)
  * and d4_mvq8 / d4_mvq8n (src/cuda/ds4f.cu:50,66) behind CMAT-MUL
  * (src/cuda-dense.lisp:220) and DK-Q8MV (src/cuda-ds4f.lisp:773).  XQ must be
- * 16-byte aligned and cols a multiple of 256 (32 for Q8_0). */
+ * 16-byte aligned and cols a multiple of 256 (32 for Q8_0).
+ *
+ * N > 16 is a prefill chunk: Q8_0, Q4_K and Q6_K take it in one launch on the
+ * tensor cores' int8 path (any N), replacing mm_q8_mma2 (src/cuda/dense.cu:885)
+ * and mm_q4k_mma / mm_q6k_mma (src/cuda/kquant.cu:316-466) behind CMAT-MUL-N;
+ * that path wants XS (Q8_0: and cols a multiple of 128) or XSUM (others) 16-byte
+ * aligned.  Otherwise ILL_ERR_UNSUPPORTED comes back for N > 16 -- also for N <= 16
+ * when N tokens of COLS columns do not fit a CTA's shared memory -- and the caller
+ * splits the tokens. */
 ILL_API int ill_mv(int fmt, ill_dptr w, int rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y,
                    ill_dptr bias, int acc, int n, ill_stream stream);
 
@@ -266,8 +274,9 @@ ILL_API int ill_moe_route(int ne, int nu, int mode, float scale, int64_t ntok, i
 #define ILL_BF16 2
 
 /* Y[t*y_stride + r] = W[r] . X[t] for the ROWS x COLS matrix W of F32 / F16 /
- * BF16 values (row-major, as in the file) and N <= 16 tokens' float
- * activations X [n, cols]; fp32 accumulate.  The router's logits and the other
+ * BF16 values (row-major, as in the file) and N tokens' float activations
+ * X [n, cols] (one token, a few, or a prefill chunk: DK-F16MM,
+ * src/cuda-ds4f-prefill.lisp:297); fp32 accumulate.  The router's logits and the other
  * small unquantized tensors between the quantized products: DK-MV16
  * (src/cuda-ds4f.lisp:767-771; d4_mv_f16 src/cuda/ds4f.cu:145, g53_mv_bf16,
  * d41_mv_f32 and their several-token forms).  The CPU path is F32MV!
@@ -407,6 +416,16 @@ ILL_API int ill_ep_ipc_close(ill_dptr mapped, int64_t offset);
 ILL_API int64_t ill_ep_flags_bytes(void);
 ILL_API int ill_ep_barrier(ill_dptr flag_peers, ill_dptr flags, int world, int rank, int slot, uint32_t epoch, int64_t wait_ns,
                            ill_stream stream);
+/* An all-gather by peer stores (the row-split head's logits; no counterpart in the reference, which
+ * keeps the head on one device): NBYTES of SRC go to DST_PEERS[p] + DST_OFF of every rank p
+ * (DST_PEERS: a device table of WORLD mapped addresses, this rank's own included; an address
+ * equal to SRC is skipped, so SRC may be this rank's block inside its own buffer), then the
+ * ranks meet in SLOT (see above): when the call's kernel has ended without a status code, every
+ * peer's block is complete in this rank's buffer.  SRC, NBYTES, DST_OFF multiples of 4 (16 for
+ * the fast path).  One call at a time a device.  The caller alternates two buffers (or holds
+ * another meeting) before a block is overwritten that a peer may still be reading. */
+ILL_API int ill_peer_put(ill_dptr src, int64_t nbytes, ill_dptr dst_peers, int64_t dst_off, ill_dptr flag_peers, ill_dptr flags,
+                         int world, int rank, int slot, uint32_t epoch, int64_t wait_ns, ill_stream stream);
 ILL_API int ill_ep_plan_dev_sync(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
                                  ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_dptr flag_peers, ill_dptr flags,
                                  uint32_t epoch, int64_t wait_ns, ill_stream stream);

@@ -41,6 +41,6 @@ def test_argument_checks_need_no_device():
     assert s("ill_mv", 1, 16, 4, 100, 16, 16, 16, 16, 0, 0, 1, None) == 1   # cols not a multiple of 256
     assert s("ill_mv", 1, 16, 4, 256, 16, 16, 0, 16, 0, 0, 1, None) == 1    # Q4_K needs the sums
     assert s("ill_mv", 1, 16, 4, 256, 17, 16, 16, 16, 0, 0, 1, None) == 2   # xq not 16-byte aligned
-    assert s("ill_mv", 0, 16, 4, 256, 16, 16, 0, 16, 0, 0, 17, None) == 1   # more than 16 tokens
+    assert s("ill_mv", 0, 16, 4, 256, 16, 16, 0, 16, 0, 0, 0, None) == 1    # no tokens
     assert s("ill_quant_q8_k", 8, 16, 16, 16, 1, None) == 2
     assert s("ill_dequant_rows", 4, 16, 100, 0, 0, 1, 16, None) == 1

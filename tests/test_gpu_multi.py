@@ -124,6 +124,32 @@ for peer in (False, True):
     dist.barrier()
     ok = ok and flag.item() == 1 and osc.total.item() <= world * 64 and osc.lcounts.sum().item() == osc.total.item()
     ok = ok and all((b[-8:] == -7).all().item() for b in bigs.values()) and D.device_status() == 0
+# the row-split head: each rank multiplies its rows, stores its logits into every peer's buffer (ill_peer_put) and
+# meets them; every rank then holds the product of the whole matrix, bit for bit
+rows, cols = 3000, 1024
+wfull = B.synth_matrix_torch(B.Q6_K, rows, cols, seed=5)
+rb = B.row_bytes(B.Q6_K, cols)
+first, end = EP.head_rows(rows, world, rank)
+wmine = D.CMat("slice", B.Q6_K, end - first, cols, wfull[first * rb:end * rb].clone())
+act = D.quant_q8(torch.randn(cols, device="cuda", generator=g), D.make_qact(cols, "q8k"))
+whole = torch.empty(rows, device="cuda")
+D.cmat_mul(D.CMat("head", B.Q6_K, rows, cols, wfull), act, whole, 1)
+pg = EP.PeerGather((rows - (world - 1) * (rows // world)) * 4, world)
+for it in range(4):   # both buffers, twice
+    i = it & 1
+    D.cmat_mul(wmine, act, pg.buffer(i)[rank][:(end - first) * 4].view(torch.float32), 1)
+    pg.put(i, (end - first) * 4)
+    torch.cuda.synchronize()
+    parts = []
+    for r in range(world):
+        f, e = EP.head_rows(rows, world, r)
+        parts.append(pg.buffer(i)[r][:(e - f) * 4].view(torch.float32))
+    ok = ok and torch.equal(torch.cat(parts), whole) and D.device_status() == 0
+    dist.barrier()
+    pg.buffer(i).zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+pg.close()
 if not ok:
     print("rank", rank, "max abs difference", (got - want[lo:hi]).abs().max().item(), file=sys.stderr)
 flag = torch.tensor([1 if ok else 0], device="cuda")

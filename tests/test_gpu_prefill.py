@@ -1,24 +1,15 @@
-"""The chunk's routed-expert product (tcgen05) against the CPU oracle.
-
-Both sides multiply the same integers exactly (the device as fp16 operands of
-tcgen05 MMAs, block by block) and scale each 256-wide block's sum by d_w * d_x
-in fp32, so the products agree to fp32 rounding; across the whole layer the
-only other difference is expf in the gate, whose last-place differences can
-move a quantized middle value by one step now and then.
-"""
+"""Dense products for a chunk of tokens (CMAT-MUL-N with more than 16 tokens: src/cuda-dense.lisp:220-255) --
+the tensor cores' int8 kernel against the one-token product, token by token (the one-token product is what the
+other tests hold against the CPU oracle, bit for bit in its integer sums), and against the oracle directly."""
 import numpy as np
 import pytest
 import torch
 
-from illatio_b200 import _lib
 from illatio_b200 import blocks as B
 from illatio_b200 import cuda_dense as D
-from illatio_b200 import cuda_ds4f as M
-from illatio_b200 import cuda_ds4f_prefill as P
-from gpu_util import rel_errors, to_dev
+from gpu_util import to_dev
 
 pytestmark = pytest.mark.gpu
-TOL_SPEC = 2e-3
 
 
 @pytest.fixture(autouse=True)
@@ -28,87 +19,78 @@ def _need_gpu(cuda_lib):
     assert D.device_status() == 0
 
 
-def _pool(d, ff, ne, gate_fmt, seed):
-    gate = B.synth_matrix(gate_fmt, ne * ff, d, seed=seed + 1)
-    up = B.synth_matrix(gate_fmt, ne * ff, d, seed=seed + 2)
-    down = B.synth_matrix(B.Q2_K, ne * d, ff, seed=seed + 3)
-    return (gate, up, down), M.make_expert_pool(gate, up, down, d, ff, ne, gate_fmt=gate_fmt)
+def _case(fmt, rows, cols, n, seed=0):
+    w = D.CMat("w", fmt, rows, cols, B.synth_matrix_torch(fmt, rows, cols, seed=seed))
+    x = torch.randn(n * cols, device="cuda", generator=torch.Generator(device="cuda").manual_seed(seed + 1))
+    act = D.quant_q8(x, D.make_qact(n * cols, D.matrix_act_kind(w)))
+    return w, x, act
 
 
-@pytest.mark.parametrize("fmt,rows_w,cols,counts", [
-    (B.IQ2_XXS, 256, 512, [5, 0, 130, 1]),      # empty expert, one row, a partial second tile
-    (B.Q2_K, 384, 256, [128, 129, 0, 0, 3]),    # exact tile, tile + 1
-    (B.IQ2_XXS, 200, 1024, [40]),               # weight rows not a multiple of the tile
+@pytest.mark.parametrize("fmt,rows,cols,n", [
+    (B.Q4_K, 300, 512, 17), (B.Q4_K, 1000, 2560, 33), (B.Q4_K, 2560, 9728, 100), (B.Q4_K, 9728, 2560, 512),
+    (B.Q6_K, 300, 768, 20), (B.Q6_K, 2560, 5120, 64), (B.Q6_K, 1031, 17408, 130), (B.Q6_K, 5120, 5120, 512),
+    (B.Q8_0, 300, 896, 17), (B.Q8_0, 4864, 896, 96), (B.Q8_0, 896, 4864, 200), (B.Q8_0, 151936, 896, 40),
 ])
-def test_mm_id_matches_oracle_rows(oracle, fmt, rows_w, cols, counts):
-    """One indexed product alone: each valid row of Y against the oracle's row dots."""
-    ne = len(counts)
-    rb = B.row_bytes(fmt, cols)
-    w = B.synth_matrix(fmt, ne * rows_w, cols, seed=len(counts))
-    slot = (rows_w * rb + 255) // 256 * 256
-    poolbuf = torch.zeros(ne * slot, dtype=torch.uint8, device="cuda")
-    poolbuf.view(ne, slot)[:, :rows_w * rb] = to_dev(w).view(ne, rows_w * rb)
-    ptrs = torch.tensor([poolbuf.data_ptr() + e * slot for e in range(ne)], dtype=torch.int64, device="cuda")
-    total = sum(counts)
-    rng = np.random.default_rng(1)
-    x = rng.standard_normal((total, cols)).astype(np.float32)
-    xq, xd, bs = oracle.quantize_q8k(x)
-    dxq, dxd, dbs = to_dev(xq), to_dev(xd), to_dev(bs.astype(np.int16))  # named: they must outlive the launches
-    xh = torch.empty(total, cols, dtype=torch.float16, device="cuda")
-    xe = torch.full((total, cols // 256, 64), 9.0, dtype=torch.float16, device="cuda")
-    _lib.call("ill_act_f16", total, cols, dxq.data_ptr(), dbs.data_ptr(), 0, xh.data_ptr(), xe.data_ptr(), None)
-    assert np.array_equal(xh.cpu().numpy().astype(np.int32), xq.reshape(total, cols))
-    xeh = xe.cpu().numpy()
-    assert np.array_equal(xeh[:, :, :16].astype(np.int32), bs.reshape(total, cols // 256, 16)) and (xeh[:, :, 16:] == 0).all()
-    y = torch.full((total + 4, rows_w), 7.0, dtype=torch.float32, device="cuda")
-    bases = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.int32)
-    dcounts, dbases = to_dev(np.array(counts, np.int32)), to_dev(bases)
-    _lib.call("ill_moe_mm_id", fmt, cols, rows_w, 0, ptrs.data_ptr(), dcounts.data_ptr(), dbases.data_ptr(), ne, total,
-              xh.data_ptr(), xe.data_ptr(), dxd.data_ptr(), 0, 0, y.data_ptr(), rows_w, None)
-    got = y.cpu().numpy()
-    assert (got[total:] == 7.0).all()
-    want = np.empty((total, rows_w), np.float32)
-    for e, (b, c) in enumerate(zip(bases, counts)):
-        we = w[e * rows_w * rb:(e + 1) * rows_w * rb]
-        for r in range(b, b + c):
-            act = (xq[r * cols:(r + 1) * cols], xd[r * (cols // 256):(r + 1) * (cols // 256)],
-                   bs[r * (cols // 16):(r + 1) * (cols // 16)])
-            want[r] = oracle.matvec(fmt, we, rows_w, cols, act)[0]
-    a, _ = rel_errors(got[:total], want)
-    assert a < 1e-5, a
+def test_chunk_product_equals_token_by_token(fmt, rows, cols, n):
+    w, x, act = _case(fmt, rows, cols, n)
+    y = torch.full((n * rows,), -3.0, device="cuda")
+    D.cmat_mul(w, act, y, n)
+    want = torch.empty(n * rows, device="cuda")
+    for t in range(n):   # one token at a time through the matvec kernel
+        a1 = D.quant_q8(x[t * cols:(t + 1) * cols], D.make_qact(cols, D.matrix_act_kind(w)))
+        D.cmat_mul(w, a1, want[t * rows:(t + 1) * rows], 1)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y).all()
+    # the integer sums are the same; the blocks' float terms are added in a different order (a row whole here,
+    # lanes' partial sums in the one-token kernel)
+    err = ((y - want).abs().max() / want.abs().max()).item()
+    assert err < 2e-6, err
 
 
-@pytest.mark.parametrize("d,ff,ne,nu,n,gate_fmt,clamp", [
-    (512, 256, 8, 2, 300, B.IQ2_XXS, 10.0),
-    (1024, 512, 6, 3, 257, B.Q2_K, 0.0),
-])
-def test_chunk_matches_oracle_small(oracle, d, ff, ne, nu, n, gate_fmt, clamp):
-    (gate, up, down), pool = _pool(d, ff, ne, gate_fmt, seed=n)
-    rng = np.random.default_rng(3)
-    norms = rng.standard_normal((n, d)).astype(np.float32)
-    logits = rng.standard_normal((n, ne)).astype(np.float32)
-    sc = P.make_chunk_scratch(pool, n, nu)
-    moe = P.dk_ffn_routed_chunk(pool, to_dev(norms), to_dev(logits), nu, clamp, sc)
-    got = moe.cpu().numpy()
-    osel, ow = oracle.route(logits, nu, mode=2)
-    assert np.array_equal(sc.sel.cpu().numpy(), osel)
-    want = np.stack([oracle.moe_routed(d, ff, gate_fmt, B.Q2_K, gate, up, down, norms[t], osel[t], ow[t], clamp, threads=4)
-                     for t in range(n)])
-    a, _ = rel_errors(got, want)
-    assert a < TOL_SPEC and a < 2e-4, a
+@pytest.mark.parametrize("fmt", [B.Q8_0, B.Q4_K, B.Q6_K])
+def test_chunk_product_against_the_oracle(oracle, fmt):
+    rows, cols, n = 200, 1024, 70
+    wb = B.synth_matrix(fmt, rows, cols, seed=4)
+    w = D.upload_gmat(wb, fmt, rows, cols)
+    rng = np.random.default_rng(6)
+    xh = rng.standard_normal((n, cols)).astype(np.float32)
+    act = D.quant_q8(to_dev(xh.reshape(-1)), D.make_qact(n * cols, D.matrix_act_kind(w)))
+    bias = to_dev(rng.standard_normal(rows).astype(np.float32))
+    y = torch.zeros(n * rows, device="cuda")
+    D.cmat_mul(w, act, y, n, bias=bias)
+    torch.cuda.synchronize()
+    got = y.cpu().numpy().reshape(n, rows)
+    for t in (0, 1, 37, n - 1):
+        want = oracle.matvec(fmt, wb, rows, cols, oracle.quantize_act(fmt, xh[t]), bias=bias.cpu().numpy())[0]
+        assert np.abs(got[t] - want).max() / np.abs(want).max() < 2e-6
+    # added into Y when ACC
+    y2 = y.clone()
+    D.cmat_mul(w, act, y2, n, acc=True)
+    torch.cuda.synchronize()
+    assert ((y2 - 2 * y + bias.repeat(n)).abs().max() / y.abs().max()).item() < 1e-5
 
 
-@pytest.mark.parametrize("gate_fmt", [B.IQ2_XXS, B.Q2_K])
-def test_fused_middle_equals_three_steps(gate_fmt):
-    """SwiGLU + Q8_K + operand conversion in one pass: the same bits as the three separate launches."""
-    d, ff, ne, nu, n = 512, 512, 4, 2, 70
-    _, pool = _pool(d, ff, ne, gate_fmt, seed=9)
-    rng = np.random.default_rng(4)
-    norms, logits = to_dev(rng.standard_normal((n, d)).astype(np.float32)), to_dev(rng.standard_normal((n, ne)).astype(np.float32))
-    sc = P.make_chunk_scratch(pool, n, nu)
-    apart = P.dk_ffn_routed_chunk(pool, norms, logits, nu, 7.0, sc, fused=False).clone()
-    mh, me, ms = sc.mh.clone(), sc.me.clone(), sc.midq.xs.clone()
-    sc.mh.zero_(), sc.me.fill_(3.0), sc.midq.xs.zero_()
-    fused = P.dk_ffn_routed_chunk(pool, norms, logits, nu, 7.0, sc, fused=True)
-    assert torch.equal(sc.mh, mh) and torch.equal(sc.me, me) and torch.equal(sc.midq.xs, ms)
-    assert torch.equal(fused, apart)
+def test_ffn_head_chunk_against_the_oracle(oracle):
+    """DK-FFN-HEAD-CHUNK: RMSNorm, the router's logits and the shared expert over a chunk, token by token against
+    the CPU routines (RMSNORM!, F32MV! on the widened router, D4-SHARED!)."""
+    from illatio_b200 import cuda_ds4f_prefill as P
+    n, d, ff, ne, clamp, eps = 70, 1024, 512, 64, 10.0, 1e-6
+    rng = np.random.default_rng(11)
+    mats = [B.synth_matrix(B.Q8_0, r, c, seed=20 + i) for i, (r, c) in enumerate(((ff, d), (ff, d), (d, ff)))]
+    ws = [D.upload_gmat(m, B.Q8_0, r, c) for m, (r, c) in zip(mats, ((ff, d), (ff, d), (d, ff)))]
+    router = torch.as_tensor(rng.standard_normal((ne, d)).astype(np.float32) * 0.05).to(torch.float16)
+    cur = rng.standard_normal((n, d)).astype(np.float32)
+    nw = (rng.random(d) + 0.5).astype(np.float32)
+    hs = P.HeadScratch(n + 3, d, ff, ne)
+    norm2, logits, sout = P.dk_ffn_head_chunk(to_dev(cur), to_dev(nw), eps, router.cuda(), ws[0], ws[1], ws[2], clamp, hs)
+    torch.cuda.synchronize()
+    norm2, logits, sout = norm2.cpu().numpy(), logits.cpu().numpy(), sout.cpu().numpy()
+    rf = router.to(torch.float32).numpy()
+    for t in (0, 16, 33, n - 1):
+        want_n = oracle.rmsnorm(cur[t], nw, eps)
+        assert np.abs(norm2[t] - want_n).max() <= 1e-6 * np.abs(want_n).max()
+        want_l = oracle.f32mv(rf, norm2[t])
+        terms = np.abs(rf.astype(np.float64) * norm2[t].astype(np.float64)).sum(1)
+        assert (np.abs(logits[t] - want_l) <= 1e-6 * terms + 1e-30).all()
+        want_s = oracle.moe_shared(d, ff, mats[0], mats[1], mats[2], norm2[t], clamp, threads=2)
+        assert np.abs(sout[t] - want_s).max() / np.abs(want_s).max() < 2e-3
