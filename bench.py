@@ -809,7 +809,7 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
             product_only()
             if world > 1:
                 gather_only()
-        us_peer = None
+        us_peer = us_put = None
         if pg is not None:
             mine = [pg.buffer(i)[rank][:n * sl * 4].view(torch.float32) for i in (0, 1)]
 
@@ -821,6 +821,8 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
             barrier()
             us_peer = time_us(both_peer, 20, torch)
             barrier()
+            us_put = time_us(lambda: pg.put(0, n * sl * 4), 20, torch)
+            barrier()
         barrier()
         us_both = time_us(both, 20, torch)
         barrier()
@@ -829,12 +831,13 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
         if world > 1:
             barrier()
             us_gather = time_us(gather_only, 20, torch)
-        us_both, us_prod, us_gather, us_peer_m = max_over_ranks([us_both, us_prod, us_gather, us_peer or 0.0])
+        us_both, us_prod, us_gather, us_peer_m, us_put_m = max_over_ranks([us_both, us_prod, us_gather, us_peer or 0.0, us_put or 0.0])
         us_nccl = us_both
         if pg is not None:
-            us_both = us_peer_m
+            us_both = min(us_peer_m, us_nccl)   # a host picks the faster of the two once, when it sets the head up
         res = {"us_per_token": us_both, "GBps": nb / us_both / 1e3, "us_product": us_prod, "us_all_gather": us_gather,
                "us_with_nccl_all_gather": us_nccl if pg is not None else None,
+               "us_with_peer_stores": us_peer_m if pg is not None else None, "us_peer_stores_alone": us_put_m if pg is not None else None,
                "product_frac_of_hbm_per_gpu": (nb / world) / us_prod / 1e3 / peak}
         if n == 1:
             # parity and the one-GPU time, on rank 0 (the whole matrix, copy 0)

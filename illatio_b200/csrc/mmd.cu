@@ -9,8 +9,9 @@
 //   * weights: every warp runs its own ring of stages, lanes 0..15 each copying one row's 256 columns of blocks
 //     (144 / 210 / 272 bytes, widened to 16-byte boundaries) with cp.async.bulk onto the stage's mbarrier; a stage
 //     is free again as soon as its block sits in registers, so the next copy is issued before the arithmetic;
-//   * activations: the step's TN x 256 quants, their sums of 16 and scales are brought by all threads with
-//     cp.async into one of two buffers while the other is being used -- one __syncthreads a step.
+//   * activations: the step's TN x 256 quants and their scales are brought by all threads with cp.async into one
+//     of two buffers while the other is being used -- one __syncthreads a step; a token tile's quants reach the
+//     registers as B fragments through ldmatrix.
 // Token tiles are the fastest-varying CTA index: the CTAs that share a tile of rows run together and the weights
 // come from HBM once.  Waits are bounded (status word, ST_MV_WAIT + 0x40 + format); a warp that gave up keeps
 // meeting the CTA's barriers and lets its copies land before the CTA leaves.
@@ -25,7 +26,7 @@ namespace ill {
 
 constexpr int MD_WARPS = 8, MD_THREADS = 32 * MD_WARPS, MD_ROWS = 16 * MD_WARPS, MD_STAGES = 3;
 constexpr int MD_XPITCH = 272;  // bytes between the tokens' 256 quants of a step: 68 words, so eight tokens x four words hit 32 banks
-constexpr int MD_SPITCH = 48;   // bytes between the tokens' 32 bytes of sums (or of Q8_0 scales): four tokens' 16-byte reads on different banks
+constexpr int MD_SPITCH = 48;   // bytes between the tokens' 32 bytes of Q8_0 scales (Q4_K: of sums) of a step: four tokens' 16-byte reads on different banks
 
 struct MdParams {
   const u8* w;
@@ -38,7 +39,7 @@ struct MdParams {
   int acc, n;
   int pitch;             // bytes between the rows of a staged piece
   uint32_t stage_bytes;
-  uint32_t xbuf_bytes, xsum_off, xs_off;  // one activation buffer: its size, where its sums and its scales start
+  uint32_t xbuf_bytes, xs_off, xsum_off;  // one activation buffer: its size, where its scales and (Q4_K) sums start
   uint32_t ring_off;
   unsigned* status;
 };
@@ -52,13 +53,26 @@ __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-__device__ __forceinline__ uint32_t lds32(const u8* p) { return *(const uint32_t*)p; }
+// four 8 x 16-byte matrices of shared memory -> each lane its four bytes of row lane / 4 of each: lane l gives the
+// address of row l % 8 of matrix l / 8.  For a token tile's 64 bytes of quants this is the B fragment of two k32
+// (or four k16) steps: r[0], r[1] = b0, b1 of the first k32 step, r[2], r[3] of the second.
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
 
 // ---- a step's block(s) of 16 rows as tensor-core fragments, and their use against eight tokens ---------------
 // load(): ROW0 / ROW8 = the staged bytes of rows g and g + 8 (g = lane / 4), NB = valid blocks in the step.
-// apply(): XQ = the quants of token 8 nt + g at this step (+ 4 (lane % 4) already added); SA / SB = the 32 bytes of
-// sums (Q8_0: of scales) of tokens 8 nt + 2 (lane % 4) and + 1; DA / DB their scales; ACC the lane's four outputs:
+// apply(): B = the tile's eight tokens' 256 quants as B fragments (ldsm4 of 64 bytes each); YA / YB the Q8_K scales
+// of tokens 8 nt + 2 (lane % 4) and + 1 (Q8_0: SA / SB their eight scales); ACC the lane's four outputs:
 // i -> row g + 8 (i / 2), token 8 nt + 2 (lane % 4) + i % 2.
+//
+// The integer sums are the CPU path's, exactly.  Q6_K's 0..63 quants go in as signed q - 32 (no sums of activations
+// needed), each group of 16 a k16 product scaled by its signed scale; Q4_K's mins meet the activations' sums of 16.
+// (Carrying Q4_K's scales on the tensor core -- (s & 7) q and (s >> 3) q both fit a byte, so a block is c1 + 8 c2 of
+// two accumulating chains, the mins a third -- was measured slower: an int8 mma.sync costs about seven issue slots
+// here, so fewer of them with an integer multiply-add a group wins.)
 template <int FMT> struct MdFrag;
 
 template <> struct MdFrag<ILL_Q8_0> {
@@ -79,13 +93,13 @@ template <> struct MdFrag<ILL_Q8_0> {
       d8[b] = in ? ldh(r8) : 0.0f;
     }
   }
-  __device__ __forceinline__ void apply(const u8* xq, const u8* sa, const u8* sb, float, float, float (&acc)[4]) const {
+  __device__ __forceinline__ void apply(const uint32_t (&x)[4][4], const u8* sa, const u8* sb, float, float, float (&acc)[4]) const {
     const float4 xa0 = *(const float4*)sa, xa1 = *(const float4*)(sa + 16), xb0 = *(const float4*)sb, xb1 = *(const float4*)(sb + 16);
     const float da[8] = {xa0.x, xa0.y, xa0.z, xa0.w, xa1.x, xa1.y, xa1.z, xa1.w};
     const float db[8] = {xb0.x, xb0.y, xb0.z, xb0.w, xb1.x, xb1.y, xb1.z, xb1.w};
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
-      const uint32_t bb[2] = {lds32(xq + 32 * b), lds32(xq + 32 * b + 16)};
+      const uint32_t bb[2] = {x[b >> 1][2 * (b & 1)], x[b >> 1][2 * (b & 1) + 1]};
       int c[4] = {0, 0, 0, 0};
       mma_k32(c, a[b], bb, false);
 #pragma unroll
@@ -121,12 +135,12 @@ template <> struct MdFrag<ILL_Q4_K> {
     }
     d0 = ldh(row0); m0 = ldh(row0 + 2); d8 = ldh(row8); m8 = ldh(row8 + 2);
   }
-  __device__ __forceinline__ void apply(const u8* xq, const u8* sa, const u8* sb, float ya, float yb, float (&acc)[4]) const {
+  // SA / SB: the sixteen sums of 16 (int16) of the two tokens' step
+  __device__ __forceinline__ void apply(const uint32_t (&x)[4][4], const u8* sa, const u8* sb, float ya, float yb, float (&acc)[4]) const {
     int isum[4] = {0, 0, 0, 0}, imin[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      const uint32_t b0[2] = {lds32(xq + 64 * k), lds32(xq + 64 * k + 16)};
-      const uint32_t b1[2] = {lds32(xq + 64 * k + 32), lds32(xq + 64 * k + 48)};
+      const uint32_t b0[2] = {x[k][0], x[k][1]}, b1[2] = {x[k][2], x[k][3]};
       int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
       mma_k32(c0, lo[k], b0, true);
       mma_k32(c1, hi[k], b1, true);
@@ -154,11 +168,16 @@ template <> struct MdFrag<ILL_Q4_K> {
   }
 };
 
+// four 6-bit values 0..63, a byte each -> the signed bytes value - 32
+__device__ __forceinline__ uint32_t q6_signed(uint32_t v) {
+  const uint32_t t = v ^ 0x20202020u, s = t & 0x20202020u;  // t = value - 32 modulo 64; s: its sign (bit 5)
+  return t | (s << 1) | (s << 2);
+}
+
 template <> struct MdFrag<ILL_Q6_K> {
   static constexpr int SB = 210;
-  uint32_t q[2][2][4][2];  // [half of the block][16 is .. 16 is + 15][run of 32][row g / g + 8]: four 6-bit quants, 0..63
+  uint32_t q[16][2];  // [group of 16][row g / g + 8]: the lane's four quants as signed bytes -32..31
   int sc0[16], sc8[16];
-  int scw0[4], scw8[4];    // the same scales, four signed bytes a word
   float d0, d8;
   __device__ __forceinline__ void load(const u8* row0, const u8* row8, int lane, int) {
     const int t4 = 4 * (lane & 3);
@@ -171,53 +190,37 @@ template <> struct MdFrag<ILL_Q6_K> {
         for (int r = 0; r < 2; ++r) {
           const u8* row = r ? row8 : row0;
           const uint32_t A = lds32u(row + 64 * c + l), B = lds32u(row + 64 * c + 32 + l), H = lds32u(row + 128 + 32 * c + l);
-          q[c][is][0][r] = (A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u);
-          q[c][is][1][r] = (B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u);
-          q[c][is][2][r] = ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u);
-          q[c][is][3][r] = ((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u);
+          // run RUN of the half covers weights 128 c + 32 run ..: its group of 16 is 8 c + 2 run + is
+          q[8 * c + 0 + is][r] = q6_signed((A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u));
+          q[8 * c + 2 + is][r] = q6_signed((B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u));
+          q[8 * c + 4 + is][r] = q6_signed(((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u));
+          q[8 * c + 6 + is][r] = q6_signed(((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u));
         }
       }
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      scw0[w] = (int)lds32u(row0 + 192 + 4 * w);
-      scw8[w] = (int)lds32u(row8 + 192 + 4 * w);
+      const uint32_t w0 = lds32u(row0 + 192 + 4 * w), w8 = lds32u(row8 + 192 + 4 * w);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        sc0[4 * w + j] = (int)(signed char)(scw0[w] >> (8 * j));
-        sc8[4 * w + j] = (int)(signed char)(scw8[w] >> (8 * j));
+        sc0[4 * w + j] = (int)(signed char)(w0 >> (8 * j));
+        sc8[4 * w + j] = (int)(signed char)(w8 >> (8 * j));
       }
     }
     d0 = ldh(row0 + 208); d8 = ldh(row8 + 208);
   }
-  __device__ __forceinline__ void apply(const u8* xq, const u8* sa, const u8* sb, float ya, float yb, float (&acc)[4]) const {
+  __device__ __forceinline__ void apply(const uint32_t (&x)[4][4], const u8*, const u8*, float ya, float yb, float (&acc)[4]) const {
     int isum[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int c = 0; c < 2; ++c)
+    for (int grp = 0; grp < 16; ++grp) {  // group GRP's 16 weights face the token's 16 quants at 16 grp
+      int cc[4] = {0, 0, 0, 0};
+      mma_k16_s8(cc, q[grp][0], q[grp][1], x[grp >> 2][grp & 3], false);
 #pragma unroll
-      for (int is = 0; is < 2; ++is)
-#pragma unroll
-        for (int run = 0; run < 4; ++run) {
-          const int grp = 8 * c + 2 * run + is;  // the group of 16 and its scale
-          int cc[4] = {0, 0, 0, 0};
-          mma_k16_u8(cc, q[c][is][run][0], q[c][is][run][1], lds32(xq + 128 * c + 32 * run + 16 * is));
-#pragma unroll
-          for (int i = 0; i < 4; ++i) isum[i] += cc[i] * (i < 2 ? sc0[grp] : sc8[grp]);
-        }
-    // the quants are 0..63: their -32 comes off as 32 * sum over the groups of scale * (the activations' sum of the group)
-    const int4 a0 = *(const int4*)sa, a1 = *(const int4*)(sa + 16), c0 = *(const int4*)sb, c1 = *(const int4*)(sb + 16);
-    const int pa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const int pb[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      int corr = 0;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const int s = i < 2 ? scw0[w] : scw8[w];
-        corr = dp2a_hi((i & 1) ? pb[2 * w + 1] : pa[2 * w + 1], s, dp2a_lo((i & 1) ? pb[2 * w] : pa[2 * w], s, corr));
-      }
-      // Q6K-ROW-DOT: sum += (d * yd) * float(isum - 32 * sum of scale * bsum)
-      acc[i] = __fadd_rn(acc[i], __fmul_rn(__fmul_rn(i < 2 ? d0 : d8, (i & 1) ? yb : ya), (float)(isum[i] - 32 * corr)));
+      for (int i = 0; i < 4; ++i) isum[i] += cc[i] * (i < 2 ? sc0[grp] : sc8[grp]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      // Q6K-ROW-DOT: sum += (d * yd) * float(sum over the groups of scale * dot(q - 32, x))
+      acc[i] = __fadd_rn(acc[i], __fmul_rn(__fmul_rn(i < 2 ? d0 : d8, (i & 1) ? yb : ya), (float)isum[i]));
   }
 };
 
@@ -225,7 +228,7 @@ template <int FMT, int NT8>
 __global__ void __launch_bounds__(MD_THREADS, 1) mmd_kernel(const MdParams p) {
   extern __shared__ __align__(128) u8 smem[];
   constexpr int TN = 8 * NT8, SB = MdFrag<FMT>::SB;
-  constexpr bool KQ = FMT != ILL_Q8_0;  // Q8_K activations: a scale and sixteen sums a step
+  constexpr bool KQ = FMT != ILL_Q8_0;  // Q8_K activations: one scale a step (Q8_0: eight)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int ntt = (p.n + TN - 1) / TN;
   const int tok0 = (int)(blockIdx.x % ntt) * TN, row_base = (int)(blockIdx.x / ntt) * MD_ROWS + warp * 16;
@@ -264,13 +267,15 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mmd_kernel(const MdParams p) {
         cp_async16(xb + tk * MD_XPITCH + 16 * ch, p.xq + (long long)(tok0 + tk) * p.cols + c0 + 16 * ch);
     }
     if constexpr (KQ) {
-      for (int i = tid; i < TN * 2; i += MD_THREADS) {
-        const int tk = i >> 1, ch = i & 1;
-        if (tok0 + tk < p.n)
-          cp_async16(xb + p.xsum_off + tk * MD_SPITCH + 16 * ch, p.xsum + (long long)(tok0 + tk) * (p.cols / 16) + 16 * step + 8 * ch);
-      }
       for (int i = tid; i < TN; i += MD_THREADS)
         if (tok0 + i < p.n) cp_async4(xb + p.xs_off + 4 * i, p.xs + (long long)(tok0 + i) * nsteps + step);
+      if constexpr (FMT == ILL_Q4_K) {
+        for (int i = tid; i < TN * 2; i += MD_THREADS) {
+          const int tk = i >> 1, ch = i & 1;
+          if (tok0 + tk < p.n)
+            cp_async16(xb + p.xsum_off + tk * MD_SPITCH + 16 * ch, p.xsum + (long long)(tok0 + tk) * (p.cols / 16) + 16 * step + 8 * ch);
+        }
+      }
     } else {
       for (int i = tid; i < TN * 2; i += MD_THREADS) {
         const int tk = i >> 1, ch = i & 1;
@@ -323,14 +328,18 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mmd_kernel(const MdParams p) {
     __syncwarp();
     issue_w();  // the stage is free: its block sits in registers
     const u8* xb = smem + (size_t)(step & 1) * p.xbuf_bytes;
-    const u8* xq = xb + g * MD_XPITCH + 4 * t;
-    const u8* sums = xb + (KQ ? p.xsum_off : p.xs_off) + 2 * t * MD_SPITCH;
+    const u8* xl = xb + (lane & 7) * MD_XPITCH + 16 * (lane >> 3);  // this lane's row of the four matrices ldsm4 reads
+    // Q8_0: the eight scales of token 2 t (+ 8 nt); Q4_K: its sixteen sums of 16
+    const u8* scl = xb + (FMT == ILL_Q4_K ? p.xsum_off : p.xs_off) + 2 * t * MD_SPITCH;
     const float* ys = (const float*)(xb + p.xs_off) + 2 * t;
 #pragma unroll
     for (int nt = 0; nt < NT8; ++nt) {
+      uint32_t x[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ldsm4(x[j], xl + 8 * nt * MD_XPITCH + 64 * j);
       float ya = 0.0f, yb = 0.0f;
       if constexpr (KQ) { ya = ys[8 * nt]; yb = ys[8 * nt + 1]; }
-      f.apply(xq + 8 * nt * MD_XPITCH, sums + 8 * nt * MD_SPITCH, sums + (8 * nt + 1) * MD_SPITCH, ya, yb, acc[nt]);
+      f.apply(x, scl + 8 * nt * MD_SPITCH, scl + (8 * nt + 1) * MD_SPITCH, ya, yb, acc[nt]);
     }
   }
   if (dead) {
@@ -371,9 +380,10 @@ int mmd_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, u
   if (fmt != ILL_Q8_0 && fmt != ILL_Q4_K && fmt != ILL_Q6_K) return ILL_ERR_UNSUPPORTED;
   if (n < 2) return ILL_ERR_UNSUPPORTED;
   const bool kq = fmt != ILL_Q8_0;
-  // 16-byte pieces of the activations are copied as they lie: the quants of a step, its sixteen sums, eight Q8_0 scales
+  // 16-byte pieces of the activations are copied as they lie: the quants of a step, eight Q8_0 scales Q4_K's sixteen sums
   if (xq & 15) return ILL_ERR_UNSUPPORTED;
-  if (kq ? ((xsum & 15) || cols % 256) : ((xs & 15) || cols % 128)) return ILL_ERR_UNSUPPORTED;
+  if (kq ? cols % 256 != 0 : ((xs & 15) || cols % 128)) return ILL_ERR_UNSUPPORTED;
+  if (fmt == ILL_Q4_K && (xsum & 15)) return ILL_ERR_UNSUPPORTED;
   const int bw = fmt_block_weights(fmt), bb = fmt_block_bytes(fmt);
   MdParams p = {};
   p.w = (const u8*)(uintptr_t)w;
@@ -398,15 +408,11 @@ int mmd_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, u
   p.pitch = pitch;
   p.stage_bytes = (uint32_t)(16 * pitch + 16 + 127) / 128 * 128;
   uint32_t off = (uint32_t)tn * MD_XPITCH;
-  if (kq) {
-    p.xsum_off = off;
-    off += (uint32_t)tn * MD_SPITCH;
-    p.xs_off = off;
-    off += 4u * tn;
-  } else {
-    p.xs_off = off;
-    off += (uint32_t)tn * MD_SPITCH;
-  }
+  p.xs_off = off;
+  off += kq ? 4u * tn : (uint32_t)tn * MD_SPITCH;
+  off = (off + 15) / 16 * 16;
+  p.xsum_off = off;
+  if (fmt == ILL_Q4_K) off += (uint32_t)tn * MD_SPITCH;
   p.xbuf_bytes = (off + 127) / 128 * 128;
   p.ring_off = 2 * p.xbuf_bytes;
   const size_t smem = p.ring_off + (size_t)MD_WARPS * MD_STAGES * p.stage_bytes;

@@ -49,15 +49,17 @@ __device__ __forceinline__ void dense_vec(const uint4 v, float (&f)[8]) {
 constexpr int MVF_MAXN = 16;
 
 // Y[t * y_stride + r] = W[r] . X[t], r < rows, t < n: blockIdx.y takes the tokens sixteen at a time (a chunk's
-// router logits: the matrix is small and stays in L2 between the token batches)
-template <int TYPE>
+// router logits: the matrix is small and stays in L2 between the token batches).  A warp takes RW rows against the
+// batch's tokens: one row for a token or a few (more warps in flight), four for a chunk (an activation vector
+// loaded once serves four rows).
+template <int TYPE, int RW>
 __global__ void __launch_bounds__(256) mv_dense_kernel(const u8* __restrict__ w, int rows, int cols, const float* __restrict__ x,
                                                        float* __restrict__ y, int n, long long y_stride, int vec_ok) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
-  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (r >= rows) return;
+  const int r0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * RW;
+  if (r0 >= rows) return;
   {
     const long long t0 = (long long)blockIdx.y * MVF_MAXN;
     x += t0 * cols;
@@ -65,46 +67,66 @@ __global__ void __launch_bounds__(256) mv_dense_kernel(const u8* __restrict__ w,
     n = min(n - (int)t0, MVF_MAXN);
   }
   constexpr int EB = DenseElt<TYPE>::BYTES, VE = 16 / EB;  // elements a 16-byte load
-  const u8* row = w + (long long)r * cols * EB;
-  float sum[MVF_MAXN];
+  const u8* row[RW];
 #pragma unroll
-  for (int t = 0; t < MVF_MAXN; ++t) sum[t] = 0.0f;
+  for (int q = 0; q < RW; ++q) row[q] = w + (long long)min(r0 + q, rows - 1) * cols * EB;  // rows past the end repeat the last: not stored
+  float sum[RW][MVF_MAXN];
+#pragma unroll
+  for (int q = 0; q < RW; ++q)
+#pragma unroll
+    for (int t = 0; t < MVF_MAXN; ++t) sum[q][t] = 0.0f;
   int j0 = 0;
   if (vec_ok) {  // rows and activations 16-byte aligned, cols a whole number of vectors
     const int nv = cols / VE;
     for (int i = lane; i < nv; i += 32) {
-      float f[8];
-      dense_vec<TYPE>(__ldg((const uint4*)row + i), f);
+      float f[RW][8];
+#pragma unroll
+      for (int q = 0; q < RW; ++q) dense_vec<TYPE>(__ldg((const uint4*)row[q] + i), f[q]);
 #pragma unroll
       for (int t = 0; t < MVF_MAXN; ++t) {
         if (t < n) {
           const float4* xv = (const float4*)(x + (long long)t * cols + (long long)i * VE);
           const float4 a = xv[0];
-          float s = sum[t];
-          s = fmaf(f[0], a.x, s); s = fmaf(f[1], a.y, s); s = fmaf(f[2], a.z, s); s = fmaf(f[3], a.w, s);
-          if constexpr (VE == 8) {
-            const float4 b = xv[1];
-            s = fmaf(f[4], b.x, s); s = fmaf(f[5], b.y, s); s = fmaf(f[6], b.z, s); s = fmaf(f[7], b.w, s);
+          float4 b = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if constexpr (VE == 8) b = xv[1];
+#pragma unroll
+          for (int q = 0; q < RW; ++q) {
+            float s = sum[q][t];
+            s = fmaf(f[q][0], a.x, s); s = fmaf(f[q][1], a.y, s); s = fmaf(f[q][2], a.z, s); s = fmaf(f[q][3], a.w, s);
+            if constexpr (VE == 8) {
+              s = fmaf(f[q][4], b.x, s); s = fmaf(f[q][5], b.y, s); s = fmaf(f[q][6], b.z, s); s = fmaf(f[q][7], b.w, s);
+            }
+            sum[q][t] = s;
           }
-          sum[t] = s;
         }
       }
     }
     j0 = nv * VE;
   }
   for (int j = j0 + lane; j < cols; j += 32) {
-    const float wv = dense_at<TYPE>(row, j);
 #pragma unroll
-    for (int t = 0; t < MVF_MAXN; ++t)
-      if (t < n) sum[t] = fmaf(wv, x[(long long)t * cols + j], sum[t]);
-  }
+    for (int q = 0; q < RW; ++q) {
+      const float wv = dense_at<TYPE>(row[q], j);
 #pragma unroll
-  for (int t = 0; t < MVF_MAXN; ++t) {
-    if (t < n) {
-      const float v = warp_sum(sum[t]);
-      if (lane == 0) y[(long long)t * y_stride + r] = v;
+      for (int t = 0; t < MVF_MAXN; ++t)
+        if (t < n) sum[q][t] = fmaf(wv, x[(long long)t * cols + j], sum[q][t]);
     }
   }
+#pragma unroll
+  for (int q = 0; q < RW; ++q)
+#pragma unroll
+    for (int t = 0; t < MVF_MAXN; ++t) {
+      if (t < n) {
+        const float v = warp_sum(sum[q][t]);
+        if (lane == 0 && r0 + q < rows) y[(long long)t * y_stride + r0 + q] = v;
+      }
+    }
+}
+
+template <int RW>
+static const void* mv_dense_fn(int type) {
+  return type == ILL_F32 ? (const void*)mv_dense_kernel<ILL_F32, RW>
+         : type == ILL_F16 ? (const void*)mv_dense_kernel<ILL_F16, RW> : (const void*)mv_dense_kernel<ILL_BF16, RW>;
 }
 
 }  // namespace ill
@@ -125,7 +147,8 @@ extern "C" int ill_mv_dense(int type, ill_dptr w, int rows, int cols, ill_dptr x
   float* yp = (float*)(uintptr_t)y;
   long long ys = y_stride;
   void* args[] = {&wp, &rows, &cols, &xp, &yp, &n, &ys, &vec_ok};
-  const void* k = type == ILL_F32 ? (const void*)mv_dense_kernel<ILL_F32>
-                  : type == ILL_F16 ? (const void*)mv_dense_kernel<ILL_F16> : (const void*)mv_dense_kernel<ILL_BF16>;
-  return launch_kernel(k, dim3((unsigned)((rows + 7) / 8), (unsigned)((n + MVF_MAXN - 1) / MVF_MAXN)), dim3(256), 0, args, (cudaStream_t)stream);
+  const int rw = n > MVF_MAXN ? 4 : 1;
+  const void* k = rw == 4 ? mv_dense_fn<4>(type) : mv_dense_fn<1>(type);
+  return launch_kernel(k, dim3((unsigned)((rows + 8 * rw - 1) / (8 * rw)), (unsigned)((n + MVF_MAXN - 1) / MVF_MAXN)), dim3(256), 0, args,
+                       (cudaStream_t)stream);
 }

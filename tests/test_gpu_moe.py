@@ -111,7 +111,7 @@ def test_shared_expert_matches_oracle(oracle):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("rows,cols,n", [(256, 4096, 1), (37, 1000, 3), (5, 250, 16)])
+@pytest.mark.parametrize("rows,cols,n", [(256, 4096, 1), (37, 1000, 3), (5, 250, 16), (37, 1000, 40), (256, 2048, 130)])
 def test_mv_dense_matches_f32mv(oracle, dtype, rows, cols, n):
     """The router's matvec and its kin: unquantized weights, float activations, the CPU's float dot as the check."""
     rng = np.random.default_rng(rows + cols)
