@@ -37,6 +37,7 @@ struct MdParams {
   float* y;
   const float* bias;
   int acc, n;
+  int warps;             // warps a CTA (16 rows each)
   int pitch;             // bytes between the rows of a staged piece
   uint32_t stage_bytes;
   uint32_t xbuf_bytes, xs_off, xsum_off;  // one activation buffer: its size, where its scales and (Q4_K) sums start
@@ -230,8 +231,8 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mmd_kernel(const MdParams p) {
   constexpr int TN = 8 * NT8, SB = MdFrag<FMT>::SB;
   constexpr bool KQ = FMT != ILL_Q8_0;  // Q8_K activations: one scale a step (Q8_0: eight)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  const int ntt = (p.n + TN - 1) / TN;
-  const int tok0 = (int)(blockIdx.x % ntt) * TN, row_base = (int)(blockIdx.x / ntt) * MD_ROWS + warp * 16;
+  const int ntt = (p.n + TN - 1) / TN, nthreads = blockDim.x;  // eight warps, or fewer when the matrix has few rows
+  const int tok0 = (int)(blockIdx.x % ntt) * TN, row_base = (int)(blockIdx.x / ntt) * (nthreads / 2) + warp * 16;
   const int nsteps = p.nsteps;
   const bool live = row_base < p.rows;  // a warp whose rows are all past the end only helps to bring the activations
   u8* ring = smem + p.ring_off + (size_t)warp * MD_STAGES * p.stage_bytes;
@@ -261,23 +262,23 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mmd_kernel(const MdParams p) {
   auto fill_x = [&](int step) {  // all threads: the step's activations -> buffer step % 2
     u8* xb = smem + (size_t)(step & 1) * p.xbuf_bytes;
     const int c0 = 256 * step;
-    for (int i = tid; i < TN * 16; i += MD_THREADS) {
+    for (int i = tid; i < TN * 16; i += nthreads) {
       const int tk = i >> 4, ch = i & 15;
       if (tok0 + tk < p.n && c0 + 16 * ch < p.cols)
         cp_async16(xb + tk * MD_XPITCH + 16 * ch, p.xq + (long long)(tok0 + tk) * p.cols + c0 + 16 * ch);
     }
     if constexpr (KQ) {
-      for (int i = tid; i < TN; i += MD_THREADS)
+      for (int i = tid; i < TN; i += nthreads)
         if (tok0 + i < p.n) cp_async4(xb + p.xs_off + 4 * i, p.xs + (long long)(tok0 + i) * nsteps + step);
       if constexpr (FMT == ILL_Q4_K) {
-        for (int i = tid; i < TN * 2; i += MD_THREADS) {
+        for (int i = tid; i < TN * 2; i += nthreads) {
           const int tk = i >> 1, ch = i & 1;
           if (tok0 + tk < p.n)
             cp_async16(xb + p.xsum_off + tk * MD_SPITCH + 16 * ch, p.xsum + (long long)(tok0 + tk) * (p.cols / 16) + 16 * step + 8 * ch);
         }
       }
     } else {
-      for (int i = tid; i < TN * 2; i += MD_THREADS) {
+      for (int i = tid; i < TN * 2; i += nthreads) {
         const int tk = i >> 1, ch = i & 1;
         if (tok0 + tk < p.n && c0 + 128 * ch < p.cols)
           cp_async16(xb + p.xs_off + tk * MD_SPITCH + 16 * ch, p.xs + (long long)(tok0 + tk) * (p.cols / 32) + 8 * step + 4 * ch);
@@ -287,7 +288,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mmd_kernel(const MdParams p) {
   };
 
   // both activation buffers start as zeros: the tokens past the last, and the columns past a Q8_0 row's end, stay so
-  for (uint32_t i = 16u * tid; i < 2u * p.xbuf_bytes; i += 16u * MD_THREADS) *(uint4*)(smem + i) = make_uint4(0, 0, 0, 0);
+  for (uint32_t i = 16u * tid; i < 2u * p.xbuf_bytes; i += 16u * nthreads) *(uint4*)(smem + i) = make_uint4(0, 0, 0, 0);
   if (lane == 0) {
     for (int s = 0; s < MD_STAGES; ++s) mbar_init(&full[s], 1);
     mbar_fence_init();
@@ -370,7 +371,7 @@ static int mmd_launch(const MdParams& p, int tn, size_t smem, int grid, cudaStre
   if (e != cudaSuccess) return cuda_fail(e);
   MdParams pp = p;
   void* args[] = {&pp};
-  return launch_kernel(k, dim3(grid), dim3(MD_THREADS), smem, args, st);
+  return launch_kernel(k, dim3(grid), dim3(32 * p.warps), smem, args, st);
 }
 
 // The chunk product on the tensor cores, for the formats and layouts it is written for; ILL_ERR_UNSUPPORTED
@@ -398,9 +399,17 @@ int mmd_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, u
   p.bias = (const float*)(uintptr_t)bias;
   p.acc = acc;
   p.n = n;
-  // tokens a CTA: as many as 128, but not a tile that is mostly padding
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  // Tokens a CTA: 128 amortize a block's unpacking best, but not as a tile that is mostly padding, nor when that
+  // leaves the SMs with fewer than eight warps each (few rows): then 64 or 32, for more CTAs.
   int tn = n <= 32 ? 32 : n <= 64 ? 64 : 128;
   if (tn == 128 && (n + 63) / 64 * 64 < (n + 127) / 128 * 128) tn = 64;
+  while (tn > 32 && (long long)((rows + 15) / 16) * ((n + tn - 1) / tn) < 8ll * sms) tn >>= 1;
+  // Warps a CTA: eight (128 rows), fewer when that would leave SMs without a CTA (few rows of many columns)
+  p.warps = MD_WARPS;
+  while (p.warps > 1 && (long long)((rows + 16 * p.warps - 1) / (16 * p.warps)) * ((n + tn - 1) / tn) < sms) p.warps >>= 1;
   // a row's step: its 16-byte aligned span, the rows an odd multiple of 16 bytes apart (eight rows x four words on 32 banks)
   const int sb = fmt == ILL_Q8_0 ? 272 : bb;
   int pitch = (sb + 15 + 15) / 16 * 16;
@@ -415,10 +424,10 @@ int mmd_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, u
   if (fmt == ILL_Q4_K) off += (uint32_t)tn * MD_SPITCH;
   p.xbuf_bytes = (off + 127) / 128 * 128;
   p.ring_off = 2 * p.xbuf_bytes;
-  const size_t smem = p.ring_off + (size_t)MD_WARPS * MD_STAGES * p.stage_bytes;
+  const size_t smem = p.ring_off + (size_t)p.warps * MD_STAGES * p.stage_bytes;
   if (smem > 226 * 1024) return ILL_ERR_UNSUPPORTED;
   p.status = device_status_word();
-  const long long grid = (long long)((rows + MD_ROWS - 1) / MD_ROWS) * ((n + tn - 1) / tn);
+  const long long grid = (long long)((rows + 16 * p.warps - 1) / (16 * p.warps)) * ((n + tn - 1) / tn);
   if (grid > 0x7fffffffll) return ILL_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
   switch (fmt) {
