@@ -24,9 +24,8 @@
 
 namespace ill {
 
-constexpr int MD_WARPS = 8, MD_THREADS = 32 * MD_WARPS, MD_ROWS = 16 * MD_WARPS, MD_STAGES = 3;
+constexpr int MD_WARPS = 8, MD_THREADS = 32 * MD_WARPS, MD_ROWS = 16 * MD_WARPS, MD_MAX_STAGES = 3;
 constexpr int MD_XPITCH = 272;  // bytes between the tokens' 256 quants of a step: 68 words, so eight tokens x four words hit 32 banks
-constexpr int MD_SPITCH = 48;   // bytes between the tokens' 32 bytes of Q8_0 scales (Q4_K: of sums) of a step: four tokens' 16-byte reads on different banks
 
 struct MdParams {
   const u8* w;
@@ -38,6 +37,7 @@ struct MdParams {
   const float* bias;
   int acc, n;
   int warps;             // warps a CTA (16 rows each)
+  int stages;            // stages of a warp's ring of weights (2 or 3)
   int pitch;             // bytes between the rows of a staged piece
   uint32_t stage_bytes;
   uint32_t xbuf_bytes, xs_off, xsum_off;  // one activation buffer: its size, where its scales and (Q4_K) sums start
@@ -78,6 +78,7 @@ template <int FMT> struct MdFrag;
 
 template <> struct MdFrag<ILL_Q8_0> {
   static constexpr int SB = 272;  // eight blocks of 34 bytes
+  static constexpr int SPITCH = 32;  // bytes between the tokens' eight scales of a step
   uint32_t a[8][4];
   float d0[8], d8[8];
   __device__ __forceinline__ void load(const u8* row0, const u8* row8, int lane, int nb) {
@@ -113,6 +114,7 @@ template <> struct MdFrag<ILL_Q8_0> {
 
 template <> struct MdFrag<ILL_Q4_K> {
   static constexpr int SB = 144;
+  static constexpr int SPITCH = 48;  // bytes between the tokens' sixteen sums of a step: four tokens' 16-byte reads on different banks
   uint32_t lo[4][4], hi[4][4];
   int sc0[8], sc8[8];
   int mn0[4], mn8[4];  // the mins of groups 2 j and 2 j + 1, each in two bytes: dp2a against the group's two sums of 16
@@ -177,6 +179,7 @@ __device__ __forceinline__ uint32_t q6_signed(uint32_t v) {
 
 template <> struct MdFrag<ILL_Q6_K> {
   static constexpr int SB = 210;
+  static constexpr int SPITCH = 0;
   uint32_t q[16][2];  // [group of 16][row g / g + 8]: the lane's four quants as signed bytes -32..31
   int sc0[16], sc8[16];
   float d0, d8;
@@ -225,10 +228,12 @@ template <> struct MdFrag<ILL_Q6_K> {
   }
 };
 
-template <int FMT, int NT8>
-__global__ void __launch_bounds__(MD_THREADS, 1) mmd_kernel(const MdParams p) {
+// MINB = 2 (token tiles of 64): a thread stays within 128 registers and two CTAs share an SM
+template <int FMT, int NT8, int MINB>
+__global__ void __launch_bounds__(MD_THREADS, MINB) mmd_kernel(const MdParams p) {
   extern __shared__ __align__(128) u8 smem[];
-  constexpr int TN = 8 * NT8, SB = MdFrag<FMT>::SB;
+  constexpr int TN = 8 * NT8, SB = MdFrag<FMT>::SB, MD_SPITCH = MdFrag<FMT>::SPITCH;
+  const int MD_STAGES = p.stages;
   constexpr bool KQ = FMT != ILL_Q8_0;  // Q8_K activations: one scale a step (Q8_0: eight)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int ntt = (p.n + TN - 1) / TN, nthreads = blockDim.x;  // eight warps, or fewer when the matrix has few rows
@@ -236,8 +241,8 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mmd_kernel(const MdParams p) {
   const int nsteps = p.nsteps;
   const bool live = row_base < p.rows;  // a warp whose rows are all past the end only helps to bring the activations
   u8* ring = smem + p.ring_off + (size_t)warp * MD_STAGES * p.stage_bytes;
-  __shared__ uint64_t full_s[MD_WARPS * MD_STAGES];
-  uint64_t* full = full_s + warp * MD_STAGES;
+  __shared__ uint64_t full_s[MD_WARPS * MD_MAX_STAGES];
+  uint64_t* full = full_s + warp * MD_MAX_STAGES;
 
   int issued = 0;
   auto issue_w = [&]() {  // all lanes of the warp; lanes 0..15 copy a row's step each
@@ -366,7 +371,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) mmd_kernel(const MdParams p) {
 
 template <int FMT>
 static int mmd_launch(const MdParams& p, int tn, size_t smem, int grid, cudaStream_t st) {
-  const void* k = tn == 32 ? (const void*)mmd_kernel<FMT, 4> : tn == 64 ? (const void*)mmd_kernel<FMT, 8> : (const void*)mmd_kernel<FMT, 16>;
+  const void* k = tn == 32 ? (const void*)mmd_kernel<FMT, 4, 1> : tn == 64 ? (const void*)mmd_kernel<FMT, 8, 2> : (const void*)mmd_kernel<FMT, 16, 1>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e);
   MdParams pp = p;
@@ -402,29 +407,32 @@ int mmd_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, u
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  // Tokens a CTA: 128 amortize a block's unpacking best, but not as a tile that is mostly padding, nor when that
-  // leaves the SMs with fewer than eight warps each (few rows): then 64 or 32, for more CTAs.
+  // Tokens a CTA: 128 amortize a block's unpacking best (one CTA of eight warps an SM, up to 255 registers); tiles
+  // of 64 keep a thread within 128 registers so that two CTAs share an SM -- measured equal to slower where both
+  // fill the machine, so they are for chunks of up to 64 tokens and for matrices with so few rows that tiles of 128
+  // would leave the SMs with fewer than eight warps each; 32 below that.
   int tn = n <= 32 ? 32 : n <= 64 ? 64 : 128;
-  if (tn == 128 && (n + 63) / 64 * 64 < (n + 127) / 128 * 128) tn = 64;
   while (tn > 32 && (long long)((rows + 15) / 16) * ((n + tn - 1) / tn) < 8ll * sms) tn >>= 1;
   // Warps a CTA: eight (128 rows), fewer when that would leave SMs without a CTA (few rows of many columns)
   p.warps = MD_WARPS;
   while (p.warps > 1 && (long long)((rows + 16 * p.warps - 1) / (16 * p.warps)) * ((n + tn - 1) / tn) < sms) p.warps >>= 1;
-  // a row's step: its 16-byte aligned span, the rows an odd multiple of 16 bytes apart (eight rows x four words on 32 banks)
+  // a row's step: its 16-byte aligned span (a block is read from its stage once a step, so the rows' pitch need not
+  // spread them over the banks); 16 bytes after the last row for the unaligned loads' second word
   const int sb = fmt == ILL_Q8_0 ? 272 : bb;
-  int pitch = (sb + 15 + 15) / 16 * 16;
-  if ((pitch / 16) % 2 == 0) pitch += 16;
-  p.pitch = pitch;
-  p.stage_bytes = (uint32_t)(16 * pitch + 16 + 127) / 128 * 128;
+  p.pitch = (sb + 15 + 15) / 16 * 16;
+  p.stage_bytes = (uint32_t)(16 * p.pitch + 16);
   uint32_t off = (uint32_t)tn * MD_XPITCH;
   p.xs_off = off;
-  off += kq ? 4u * tn : (uint32_t)tn * MD_SPITCH;
+  off += kq ? 4u * tn : (uint32_t)tn * MdFrag<ILL_Q8_0>::SPITCH;
   off = (off + 15) / 16 * 16;
   p.xsum_off = off;
-  if (fmt == ILL_Q4_K) off += (uint32_t)tn * MD_SPITCH;
+  if (fmt == ILL_Q4_K) off += (uint32_t)tn * MdFrag<ILL_Q4_K>::SPITCH;
   p.xbuf_bytes = (off + 127) / 128 * 128;
   p.ring_off = 2 * p.xbuf_bytes;
-  const size_t smem = p.ring_off + (size_t)p.warps * MD_STAGES * p.stage_bytes;
+  // three stages a ring where two CTAs still fit an SM with them (or where one CTA has the SM anyway), else two
+  const size_t ring1 = (size_t)p.warps * p.stage_bytes, two_ctas = (233472 / 2 - 1024 - 256);
+  p.stages = (tn == 128 || p.ring_off + 3 * ring1 <= two_ctas) ? 3 : 2;
+  const size_t smem = p.ring_off + (size_t)p.stages * ring1;
   if (smem > 226 * 1024) return ILL_ERR_UNSUPPORTED;
   p.status = device_status_word();
   const long long grid = (long long)((rows + 16 * p.warps - 1) / (16 * p.warps)) * ((n + tn - 1) / tn);
