@@ -749,13 +749,19 @@ def c4_decode(D, B, torch, dev, peak):
             M.dk_shared(sg, su, sd, norms[t], 10.0, sh_out)
             M.dk_ffn_tail(pool, norms[t], sel[t], w[t], 10.0, shared=sh_out, moe=moe)
     tokens()
-    us = time_us(tokens, 5, torch) / T
+    us_eager = time_us(tokens, 5, torch) / T
+    # the same sixteen tokens as one CUDA graph: the routing, the experts' addresses and every buffer are on the
+    # device, so the host's launch cost (and the allocator's) is off the path, as it is when illatio's Lisp host
+    # enqueues from preallocated buffers
+    g = graph_of(tokens, torch)
+    us = time_us(g.replay, 5, torch) / T
+    del g
     routed = nu * (2 * B.matrix_bytes(IQ2_XXS, ff, d) + B.matrix_bytes(Q2_K, d, ff))
     sh_bytes = 3 * B.matrix_bytes(Q8_0, ff, d)
     out = {"workload": "one token through the layer: shared expert (3 Q8_0 products) + 6 routed experts (IQ2_XXS gate / up fused, Q2_K down) + slot-order sum",
            "us_per_token_layer": us, "MB": (routed + sh_bytes) / 1e6, "GBps": (routed + sh_bytes) / us / 1e3,
            "frac_of_hbm": (routed + sh_bytes) / us / 1e3 / peak, "launches_per_token_layer": 12,
-           "how": "eager launches (allocations included), 16 tokens with different routings"}
+           "how": "16 tokens with different routings in one CUDA graph", "us_per_token_layer_eager": us_eager}
     del pool, shared
     torch.cuda.empty_cache()
     return out
@@ -785,7 +791,8 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
     sl = end - first
     pg = EP.PeerGather(16 * (rows - (world - 1) * (rows // world)) * 4, world, device=dev) if world > 1 else None
     if pg is not None:
-        out["collective"] = ("peer stores of the rank's logits into every peer's buffer and one flag meeting (ill_peer_put); "
+        out["collective"] = ("peer stores of the rank's logits into every peer's buffer and one flag meeting -- from the "
+                             "product's own epilogue at batch 1 (ill_mv_peers), a second kernel at batch 4 / 16 (ill_peer_put); "
                              "NCCL's in-place all-gather timed beside it")
     for n in (1, 4, 16):
         xx = torch.randn(n * cols, device=dev, generator=torch.Generator(device=dev).manual_seed(5))
@@ -816,8 +823,11 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
             def both_peer():
                 i = it[0] & 1
                 it[0] += 1
-                D.cmat_mul(slices[i], act, mine[i], n)
-                pg.put(i, n * sl * 4)
+                if n == 1:   # the product stores into every rank's buffer itself and holds the meeting: one launch
+                    pg.mul_put(i, slices[i], act)
+                else:
+                    D.cmat_mul(slices[i], act, mine[i], n)
+                    pg.put(i, n * sl * 4)
             barrier()
             us_peer = time_us(both_peer, 20, torch)
             barrier()
@@ -957,7 +967,9 @@ def moe_leg(D, B, EP, MB, torch, dist, dev, rank, world, cores, cfg_name, n_tok,
                         "frac": flop / ms / 1e9 / world / tpeak}}
     if n_tok < 1024:
         out["note"] = ("batched decode run through the chunk driver (tensor-core products on few rows an expert); the "
-                       "matvec-path form with counts / bases (DK-FFN-SMALL, src/cuda-ds4f-spec.lisp:31-132) is not built")
+                       "matvec-path form with counts / bases (DK-FFN-SMALL, src/cuda-ds4f-spec.lisp:31-132) is not built: the 2-bit "
+                       "matvecs are bound by instructions (0.24 / 0.62 of HBM on large matrices), the chunk kernel reads an "
+                       "expert's weights once for all its tokens")
     got_l = esc.moe.clone()
     sel_l = esc.sel.clone()
     # ---- parity: 8 of this rank's tokens against the CPU oracle, which is given those tokens' experts only

@@ -87,18 +87,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
 // Every rank owns an array of flags, EP_FLAG_SLOTS x EP_MAX_RANKS words, that its peers can store into
 // (FLAG_PEERS[r] = the address of rank r's array).  A meeting in slot S with number EPOCH (counted up by the
 // caller, the same on every rank): thread t < WORLD of the calling block stores EPOCH into rank t's
-// flags[S][RANK] (after a system-wide fence: what this rank stored into peer memory before is visible to a
+// flags[S][RANK] (a release at system scope: what this rank stored into peer memory before is visible to a
 // peer that sees the flag), then waits until its own flags[S][t] has reached EPOCH.  The wait is bounded
 // (WAIT_NS, 0 = ILL_WAIT_NS): on a time-out the status word gets ST_BARRIER_WAIT and the call returns false.
 // No rank waits for anything but stores its peers make unconditionally, so ranks that run their kernels at
 // different times cannot deadlock each other.
 constexpr int EP_MAX_RANKS = 64, EP_FLAG_SLOTS = 4;
+
+// A CTA's ticket on a device counter, taken by one thread after the CTA's barrier: release orders the CTA's stores
+// (cumulative through the barrier) before the ticket, acquire lets the CTA that takes the last ticket see every
+// other CTA's -- so that its one system-wide release (the signal of ep_meet) covers the whole grid's stores, with
+// no system-wide fence in the other CTAs.
+__device__ __forceinline__ unsigned take_ticket(unsigned* counter) {
+  unsigned old;
+  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+  return old;
+}
 __device__ __forceinline__ bool ep_meet(const unsigned long long* flag_peers, unsigned* flags, int world, int rank, int slot,
                                         unsigned epoch, bool signal, unsigned long long wait_ns, unsigned int* status) {
   const int t = threadIdx.x;
   if (t >= world) return true;
   if (signal) {
-    __threadfence_system();
+    // a release at system scope: this thread's earlier stores, and those of other threads that it has observed
+    // through a barrier or an acquire, are visible to whoever acquires the flag (no separate fence.sc needed)
     unsigned* dst = (unsigned*)(uintptr_t)flag_peers[t] + slot * EP_MAX_RANKS + rank;
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
   }

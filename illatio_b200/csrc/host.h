@@ -19,7 +19,8 @@ bool pdl_enabled();
 // programmatic-dependent-launch attribute when enabled.
 int launch_kernel(const void* fn, dim3 grid, dim3 block, size_t smem, void** args, cudaStream_t st);
 
-enum { MODE_PLAIN = 0, MODE_GLU = 1, MODE_MOE_GLU = 2 };
+enum { MODE_PLAIN = 0, MODE_GLU = 1, MODE_MOE_GLU = 2,
+       MODE_PEERS = 3 /* a plain one-token product whose results go to every rank's buffer, then the ranks meet */ };
 
 // The matvec family's common entry (mv.cu): NMAT matrices of one format sharing
 // the activations; NSEG segments when PTRS (a device table of base addresses)

@@ -455,10 +455,9 @@ __global__ void __launch_bounds__(256) peer_put_kernel(const u8* __restrict__ sr
       }
     }
   }
-  __threadfence_system();
   __syncthreads();
   __shared__ int last;
-  if (threadIdx.x == 0) last = atomicAdd(&g_put_ticket, 1u) == gridDim.x - 1;
+  if (threadIdx.x == 0) last = take_ticket(&g_put_ticket) == gridDim.x - 1;
   __syncthreads();
   if (!last) return;
   if (threadIdx.x == 0) g_put_ticket = 0;

@@ -59,7 +59,22 @@ struct MvParams {
   const float* seg_w;    // MOE_GLU: weight of segment z
   float clamp;
   unsigned int* status;
+  // the row-split head: the one-token product's results go to every rank's buffer (its own included) instead of
+  // y[0], at y_peers[r] + 4 (y_peer_off + row), and the CTA that finishes last meets the other ranks
+  const unsigned long long* y_peers;  // 0: off
+  long long y_peer_off;
+  const unsigned long long* flag_peers;
+  unsigned* flags;
+  int world, rank, slot;
+  unsigned epoch;
+  unsigned long long wait_ns;
 };
+
+__device__ unsigned g_mv_ticket;  // CTAs of the running peer-storing product that are through (one such call at a time a device)
+
+__device__ __forceinline__ void store_to_peers(const MvParams& p, long long row, float v) {
+  for (int r = 0; r < p.world; ++r) ((float*)(uintptr_t)p.y_peers[r])[p.y_peer_off + row] = v;
+}
 
 // The row r0 .. of one matrix that a tile covers, and where its bytes are.
 struct TileRef {
@@ -292,7 +307,7 @@ constexpr int MV_MAXRI = 4;  // row iterations a warp tile may take when sums ar
 template <int FMT, int MODE, int UPT, int AL, bool XS>
 __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
   extern __shared__ __align__(128) u8 smem[];
-  constexpr bool GLU = MODE != MODE_PLAIN;
+  constexpr bool GLU = MODE == MODE_GLU || MODE == MODE_MOE_GLU;
   constexpr bool IQ = FMT == ILL_IQ2_XXS;
   const int WARPS = blockDim.x >> 5;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -436,7 +451,8 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
             float* y = p.y[m] + (long long)z * p.y_seg;
             float v = sum;
             if (p.bias[m]) v += p.bias[m][row];
-            y[row] = p.acc ? y[row] + v : v;
+            if constexpr (MODE == MODE_PEERS) store_to_peers(p, row, v);
+            else y[row] = p.acc ? y[row] + v : v;
           }
         } else {
           // ri < MV_MAXRI by the plan; the select chain keeps the sums in registers
@@ -477,7 +493,8 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
           } else {
             float* y = p.y[m] + (long long)z * p.y_seg;
             if (p.bias[m]) v += p.bias[m][row];
-            y[row] = p.acc ? y[row] + v : v;
+            if constexpr (MODE == MODE_PEERS) store_to_peers(p, row, v);
+            else y[row] = p.acc ? y[row] + v : v;
           }
         }
       }
@@ -489,6 +506,17 @@ __global__ void __launch_bounds__(MV_THREADS) mvw_kernel(const MvParams p) {
     const int issued = __shfl_sync(0xffffffffu, n_issued, 0);
     for (int k = n_done + 1; k < issued; ++k)
       mbar_wait(&full[k % p.nstages], (uint32_t)(k / p.nstages) & 1u, nullptr, 0);
+  }
+  if constexpr (MODE == MODE_PEERS) {
+    // every CTA takes a ticket once its stores are issued; the last one signals the peers and waits for theirs
+    __syncthreads();
+    __shared__ int last;
+    if (tid == 0) last = take_ticket(&g_mv_ticket) == gridDim.x * gridDim.y - 1;
+    __syncthreads();
+    if (last) {
+      if (tid == 0) g_mv_ticket = 0;
+      ep_meet(p.flag_peers, p.flags, p.world, p.rank, p.slot, p.epoch, true, p.wait_ns, p.status);
+    }
   }
 }
 
@@ -705,11 +733,13 @@ template <int FMT, int MODE, int AL>
 static int launch_one_u(const MvParams& p, const MvPlan& pl, int gx, int gy, cudaStream_t st) {
   constexpr int UMAX = 5;
   if (pl.xs) {
-    switch (pl.upt) {
-      case 1: return launch_k(mvw_kernel<FMT, MODE, 1, AL, true>, p, pl, gx, gy, st);
-      case 2: return launch_k(mvw_kernel<FMT, MODE, 2, AL, true>, p, pl, gx, gy, st);
-      case 3: return launch_k(mvw_kernel<FMT, MODE, 3, AL, true>, p, pl, gx, gy, st);
-      case 4: return launch_k(mvw_kernel<FMT, MODE, 4, AL, true>, p, pl, gx, gy, st);
+    if constexpr (MODE != MODE_PEERS) {
+      switch (pl.upt) {
+        case 1: return launch_k(mvw_kernel<FMT, MODE, 1, AL, true>, p, pl, gx, gy, st);
+        case 2: return launch_k(mvw_kernel<FMT, MODE, 2, AL, true>, p, pl, gx, gy, st);
+        case 3: return launch_k(mvw_kernel<FMT, MODE, 3, AL, true>, p, pl, gx, gy, st);
+        case 4: return launch_k(mvw_kernel<FMT, MODE, 4, AL, true>, p, pl, gx, gy, st);
+      }
     }
     return ILL_ERR_UNSUPPORTED;
   }
@@ -744,6 +774,7 @@ static int launch_fmt(int mode, const MvParams& p, const MvPlan& pl, int gx, int
       if constexpr (FMT == ILL_IQ2_XXS || FMT == ILL_Q2_K) return launch_one_a<FMT, MODE_MOE_GLU>(p, pl, gx, gy, st);
       return ILL_ERR_UNSUPPORTED;
     }
+    if (mode == MODE_PEERS) return pl.xs ? ILL_ERR_UNSUPPORTED : launch_one_a<FMT, MODE_PEERS>(p, pl, gx, gy, st);
     return launch_one_a<FMT, MODE_PLAIN>(p, pl, gx, gy, st);
   }
   if (mode != MODE_PLAIN) return ILL_ERR_UNSUPPORTED;
@@ -768,6 +799,16 @@ static bool needs_bsums(int fmt) { return fmt == ILL_Q4_K || fmt == ILL_Q6_K || 
 
 // Common entry: NMAT matrices of one format sharing the activations, NSEG
 // segments (experts) of them.
+// What ill_mv_peers asks of the one-token kernel on top of the product (set around its call of mv_common).
+struct MvPeer {
+  ill_dptr y_peers, flag_peers, flags;
+  long long y_off;
+  int world, rank, slot;
+  unsigned epoch;
+  unsigned long long wait_ns;
+};
+static thread_local const MvPeer* t_peer = nullptr;
+
 int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, int cols, ill_dptr xq, ill_dptr xs,
               ill_dptr xsum, const ill_dptr* y, const ill_dptr* bias, int acc, int n, ill_dptr ptrs, int nseg,
               long long add, long long up_add, int x_seg, long long y_seg, ill_dptr seg_w, float clamp,
@@ -785,8 +826,8 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
     total_rows += rows[i];
     if (!ptrs) align_bits |= w[i];
   }
-  const bool glu = mode != MODE_PLAIN;
-  if (glu && n != 1) return ILL_ERR_ARG;
+  const bool glu = mode == MODE_GLU || mode == MODE_MOE_GLU;
+  if ((glu || mode == MODE_PEERS) && n != 1) return ILL_ERR_ARG;
   if (n >= 2 && !glu && nmat == 1 && !ptrs && !x_seg) {
     // several tokens: the tensor cores' int8 path where it is written (Q8_0, Q4_K, Q6_K; up to 16 tokens with the
     // activations resident, chunks with them streamed), else the token loop below
@@ -800,7 +841,7 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
   MvPlan pl;
   int rc = ILL_ERR_UNSUPPORTED;
   if (n == 1) rc = plan_one(fmt, glu ? rows[0] : total_rows, cols, nseg, glu, &pl);
-  if (rc == ILL_ERR_UNSUPPORTED && !glu) rc = plan_many(fmt, total_rows, cols, x_seg ? 1 : n, nseg, &pl);
+  if (rc == ILL_ERR_UNSUPPORTED && !glu && !t_peer) rc = plan_many(fmt, total_rows, cols, x_seg ? 1 : n, nseg, &pl);
   if (rc) return rc;
   pl.al = (align_bits & 15) == 0 ? 16 : (align_bits & 3) == 0 ? 4 : 1;
   MvParams p = {};
@@ -842,6 +883,17 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
   p.seg_w = (const float*)(uintptr_t)seg_w;
   p.clamp = clamp;
   p.status = status_ptr();
+  if (t_peer) {
+    p.y_peers = (const unsigned long long*)(uintptr_t)t_peer->y_peers;
+    p.y_peer_off = t_peer->y_off;
+    p.flag_peers = (const unsigned long long*)(uintptr_t)t_peer->flag_peers;
+    p.flags = (unsigned*)(uintptr_t)t_peer->flags;
+    p.world = t_peer->world;
+    p.rank = t_peer->rank;
+    p.slot = t_peer->slot;
+    p.epoch = t_peer->epoch;
+    p.wait_ns = t_peer->wait_ns;
+  }
   // persistent grid: as many CTAs as can be resident, split over the segments
   int per_sm = (int)((227u * 1024u) / (pl.smem + 1024u));
   const int per_sm_cap = pl.one ? 16 / pl.warps * 2 : 6;  // up to 32 warps an SM
@@ -877,6 +929,22 @@ extern "C" int ill_mv(int fmt, ill_dptr w, int rows, int cols, ill_dptr xq, ill_
   const ill_dptr ws[1] = {w}, ys[1] = {y}, bs[1] = {bias};
   const int rs[1] = {rows};
   return mv_common(fmt, MODE_PLAIN, 1, ws, rs, cols, xq, xs, xsum, ys, bs, acc, n, 0, 1, 0, 0, 0, 0, 0, 0.0f, stream);
+}
+
+extern "C" int ill_mv_peers(int fmt, ill_dptr w, int rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y_peers,
+                            int64_t y_off, ill_dptr bias, ill_dptr flag_peers, ill_dptr flags, int world, int rank, int slot,
+                            uint32_t epoch, int64_t wait_ns, ill_stream stream) {
+  if (!y_peers || y_off < 0 || !flag_peers || !flags || world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world || slot < 0 ||
+      slot >= EP_FLAG_SLOTS || wait_ns < 0)
+    return ILL_ERR_ARG;
+  if ((y_peers & 7) || (flag_peers & 7) || (flags & 3)) return ILL_ERR_ALIGN;
+  const MvPeer peer = {y_peers, flag_peers, flags, (long long)y_off, world, rank, slot, epoch, (unsigned long long)wait_ns};
+  const ill_dptr ws[1] = {w}, ys[1] = {flags /* stands for Y in the checks: the kernel stores through Y_PEERS */}, bs[1] = {bias};
+  const int rs[1] = {rows};
+  t_peer = &peer;
+  const int rc = mv_common(fmt, MODE_PEERS, 1, ws, rs, cols, xq, xs, xsum, ys, bs, 0, 1, 0, 1, 0, 0, 0, 0, 0, 0.0f, stream);
+  t_peer = nullptr;
+  return rc;
 }
 
 extern "C" int ill_mv_3(int fmt, ill_dptr w0, ill_dptr w1, ill_dptr w2, int rows0, int rows1, int rows2, int cols,

@@ -479,6 +479,23 @@ class PeerGather:
         _lib.call("ill_peer_put", mine, nbytes, self.peers[i].data_ptr(), self.rank * self.block, self.peers_flags.data_ptr(),
                   self.flags.data_ptr(), self.world, self.rank, 2, self.epoch, wait_ns, torch.cuda.current_stream().cuda_stream)
 
+    def mul_put(self, i, w, act, wait_ns=0):
+        """One token's product of this rank's rows (W: its slice of the matrix) straight into block RANK of every
+        rank's buffer I, and the meeting, in one launch (ill_mv_peers); ill_mv + put() where the kernel declines."""
+        from . import _lib
+        self.epoch += 1
+        off = self.rank * self.block // 4
+        rc = _lib.status("ill_mv_peers", w.type, w.qs.data_ptr(), w.rows, w.cols, act.xq.data_ptr(), act.xs.data_ptr(),
+                         0 if act.kind == "q8" else act.xsum.data_ptr(), self.peers[i].data_ptr(), off, 0, self.peers_flags.data_ptr(),
+                         self.flags.data_ptr(), self.world, self.rank, 2, self.epoch, wait_ns, torch.cuda.current_stream().cuda_stream)
+        if rc == 3:
+            from . import cuda_dense as D
+            self.epoch -= 1
+            D.cmat_mul(w, act, self.buffer(i)[self.rank][:w.rows * 4].view(torch.float32), 1)
+            self.put(i, w.rows * 4, wait_ns)
+        elif rc:
+            raise _lib.IllatioError("ill_mv_peers", rc, _lib.lib().ill_error_string(rc).decode(), 0)
+
     def close(self):
         for ptr_, off in self._mapped:
             _lib_close(ptr_, off)

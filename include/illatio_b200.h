@@ -426,6 +426,15 @@ ILL_API int ill_ep_barrier(ill_dptr flag_peers, ill_dptr flags, int world, int r
  * another meeting) before a block is overwritten that a peer may still be reading. */
 ILL_API int ill_peer_put(ill_dptr src, int64_t nbytes, ill_dptr dst_peers, int64_t dst_off, ill_dptr flag_peers, ill_dptr flags,
                          int world, int rank, int slot, uint32_t epoch, int64_t wait_ns, ill_stream stream);
+/* ill_mv for one token with the all-gather in its epilogue (the row-split head at batch 1): row r's result goes to
+ * Y_PEERS[p] + 4 * (Y_OFF + r) of every rank p (a device table of WORLD mapped float buffers, this rank's own
+ * included) instead of to a Y, and the CTA that finishes last holds the ranks' meeting in SLOT -- one launch where
+ * ill_mv + ill_peer_put are two.  The same caveats as ill_peer_put (one such call at a time a device; alternate
+ * two buffers).  ILL_ERR_UNSUPPORTED for shapes the one-token kernel does not take whole (then: ill_mv and
+ * ill_peer_put). */
+ILL_API int ill_mv_peers(int fmt, ill_dptr w, int rows, int cols, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr y_peers,
+                         int64_t y_off, ill_dptr bias, ill_dptr flag_peers, ill_dptr flags, int world, int rank, int slot,
+                         uint32_t epoch, int64_t wait_ns, ill_stream stream);
 ILL_API int ill_ep_plan_dev_sync(int world, int per, int cap, int rank, ill_dptr rc, ill_dptr counts, ill_dptr bases, ill_dptr p2r,
                                  ill_dptr r2p, ill_dptr pdst, ill_dptr total, ill_dptr overflow, ill_dptr flag_peers, ill_dptr flags,
                                  uint32_t epoch, int64_t wait_ns, ill_stream stream);

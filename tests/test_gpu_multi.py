@@ -135,10 +135,13 @@ act = D.quant_q8(torch.randn(cols, device="cuda", generator=g), D.make_qact(cols
 whole = torch.empty(rows, device="cuda")
 D.cmat_mul(D.CMat("head", B.Q6_K, rows, cols, wfull), act, whole, 1)
 pg = EP.PeerGather((rows - (world - 1) * (rows // world)) * 4, world)
-for it in range(4):   # both buffers, twice
+for it in range(8):   # both buffers; the product and the stores as two launches, then fused into one
     i = it & 1
-    D.cmat_mul(wmine, act, pg.buffer(i)[rank][:(end - first) * 4].view(torch.float32), 1)
-    pg.put(i, (end - first) * 4)
+    if it < 4:
+        D.cmat_mul(wmine, act, pg.buffer(i)[rank][:(end - first) * 4].view(torch.float32), 1)
+        pg.put(i, (end - first) * 4)
+    else:
+        pg.mul_put(i, wmine, act)
     torch.cuda.synchronize()
     parts = []
     for r in range(world):
