@@ -39,5 +39,8 @@ int mvt_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, u
 // the same for a chunk of tokens (more than 16): mmd.cu
 int mmd_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, uint64_t xsum, uint64_t y, uint64_t bias, int acc,
             int n, void* stream);
+// up to 16 tokens of rows with many columns, the columns dealt to a CTA's warps: mmd.cu
+int mmk_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, uint64_t xsum, uint64_t y, uint64_t bias, int acc,
+            int n, void* stream);
 
 }  // namespace ill

@@ -41,7 +41,7 @@ struct MdParams {
   int pitch;             // bytes between the rows of a staged piece
   uint32_t stage_bytes;
   uint32_t xbuf_bytes, xs_off, xsum_off;  // one activation buffer: its size, where its scales and (Q4_K) sums start
-  uint32_t ring_off;
+  uint32_t ring_off, part_off;
   unsigned* status;
 };
 
@@ -369,6 +369,162 @@ __global__ void __launch_bounds__(MD_THREADS, MINB) mmd_kernel(const MdParams p)
     }
 }
 
+// ---- up to sixteen tokens of rows too long for mvt.cu to keep the activations resident ------------------------
+// One 16-row tile a CTA, its column steps dealt to the eight warps (warp w takes steps w, w + 8, ...): each warp
+// streams its own steps' weights (its ring) AND its own steps' activations (cp.async by its lanes into two buffers of
+// its own), so the warps never wait for one another until the end, where their partial sums meet in shared memory
+// in warp order.  A matrix of few rows and many columns (5120 x 17408) thus fills the machine with rows / 16 CTAs
+// of eight busy warps, where the chunk kernel above would run two warps a CTA through all 68 steps.
+template <int FMT, int NT8>
+__global__ void __launch_bounds__(MD_THREADS, 1) mmk_kernel(const MdParams p) {
+  extern __shared__ __align__(128) u8 smem[];
+  constexpr int TN = 8 * NT8, SB = MdFrag<FMT>::SB, SP = MdFrag<FMT>::SPITCH;
+  constexpr bool KQ = FMT != ILL_Q8_0;
+  const int stages = p.stages;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int ntt = (p.n + TN - 1) / TN;
+  const int tok0 = (int)(blockIdx.x % ntt) * TN, row_base = (int)(blockIdx.x / ntt) * 16;
+  const int nsteps = p.nsteps;
+  u8* xw = smem + (size_t)warp * 2 * p.xbuf_bytes;  // this warp's two activation buffers
+  u8* ring = smem + p.ring_off + (size_t)warp * stages * p.stage_bytes;
+  float* part = (float*)(smem + p.part_off);        // [warp][16 rows][TN]
+  __shared__ uint64_t full_s[MD_WARPS * MD_MAX_STAGES];
+  uint64_t* full = full_s + warp * MD_MAX_STAGES;
+
+  int issued = 0;  // of this warp's steps
+  auto issue_w = [&]() {
+    const int step = warp + MD_WARPS * issued;
+    if (step >= nsteps) return;
+    const int s = issued % stages;
+    const int row = row_base + lane;
+    uint32_t bytes = 0;
+    const u8* src = nullptr;
+    if (lane < 16 && row < p.rows) {
+      src = p.w + (long long)row * p.row_bytes + (long long)step * SB;
+      const uint32_t len = (uint32_t)min(SB, p.row_bytes - step * SB);
+      bytes = (uint32_t)((((uintptr_t)src + len + 15) & ~(uintptr_t)15) - ((uintptr_t)src & ~(uintptr_t)15));
+    }
+    uint32_t total = bytes;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    if (lane == 0) mbar_expect_tx(&full[s], total);
+    __syncwarp();
+    if (bytes) bulk_g2s(ring + (size_t)s * p.stage_bytes + (size_t)lane * p.pitch, (const void*)((uintptr_t)src & ~(uintptr_t)15), bytes, &full[s]);
+    ++issued;
+  };
+  auto fill_x = [&](int k) {  // this warp's K-th step -> its buffer k % 2 (a group of cp.async, possibly empty)
+    const int step = warp + MD_WARPS * k;
+    if (step < nsteps) {
+      u8* xb = xw + (size_t)(k & 1) * p.xbuf_bytes;
+      const int c0 = 256 * step;
+      for (int i = lane; i < TN * 16; i += 32) {
+        const int tk = i >> 4, ch = i & 15;
+        if (tok0 + tk < p.n && c0 + 16 * ch < p.cols)
+          cp_async16(xb + tk * MD_XPITCH + 16 * ch, p.xq + (long long)(tok0 + tk) * p.cols + c0 + 16 * ch);
+      }
+      if constexpr (KQ) {
+        for (int i = lane; i < TN; i += 32)
+          if (tok0 + i < p.n) cp_async4(xb + p.xs_off + 4 * i, p.xs + (long long)(tok0 + i) * nsteps + step);
+        if constexpr (FMT == ILL_Q4_K) {
+          for (int i = lane; i < TN * 2; i += 32) {
+            const int tk = i >> 1, ch = i & 1;
+            if (tok0 + tk < p.n)
+              cp_async16(xb + p.xsum_off + tk * SP + 16 * ch, p.xsum + (long long)(tok0 + tk) * (p.cols / 16) + 16 * step + 8 * ch);
+          }
+        }
+      } else {
+        for (int i = lane; i < TN * 2; i += 32) {
+          const int tk = i >> 1, ch = i & 1;
+          if (tok0 + tk < p.n && c0 + 128 * ch < p.cols)
+            cp_async16(xb + p.xs_off + tk * SP + 16 * ch, p.xs + (long long)(tok0 + tk) * (p.cols / 32) + 8 * step + 4 * ch);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  // the warp's activation buffers start as zeros (tokens past the last, columns past a Q8_0 row's end)
+  for (uint32_t i = 16u * lane; i < 2u * p.xbuf_bytes; i += 16u * 32u) *(uint4*)(xw + i) = make_uint4(0, 0, 0, 0);
+  if (lane == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  for (int s = 0; s < stages; ++s) issue_w();  // the weights do not depend on the previous kernel
+  pdl_launch_dependents();
+  pdl_wait();
+  fill_x(0);
+
+  float acc[NT8][4];
+#pragma unroll
+  for (int nt = 0; nt < NT8; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+  bool dead = false;
+  int done = 0;
+  for (int k = 0; warp + MD_WARPS * k < nsteps && !dead; ++k) {
+    const int step = warp + MD_WARPS * k;
+    fill_x(k + 1);                                          // the other buffer: its readers are through (the __syncwarp below)
+    asm volatile("cp.async.wait_group 1;" ::: "memory");   // all but that newest group: step k's activations are in
+    __syncwarp();
+    const int s = k % stages;
+    bool ok = mbar_wait(&full[s], (uint32_t)(k / stages) & 1u, p.status, ST_MV_WAIT + 0x48 + FMT);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) { dead = true; break; }
+    ++done;
+    MdFrag<FMT> f;
+    {
+      const u8* piece = ring + (size_t)s * p.stage_bytes;
+      const long long o0 = (long long)(row_base + g) * p.row_bytes + (long long)step * SB;
+      const long long o8 = o0 + 8ll * p.row_bytes;
+      const u8* row0 = piece + (size_t)g * p.pitch + (((uintptr_t)p.w + o0) & 15);
+      const u8* row8 = piece + (size_t)(g + 8) * p.pitch + (((uintptr_t)p.w + o8) & 15);
+      f.load(row0, row8, lane, min(8, (p.cols - 256 * step) / 32));
+    }
+    __syncwarp();
+    issue_w();
+    const u8* xb = xw + (size_t)(k & 1) * p.xbuf_bytes;
+    const u8* xl = xb + (lane & 7) * MD_XPITCH + 16 * (lane >> 3);
+    const u8* scl = xb + (FMT == ILL_Q4_K ? p.xsum_off : p.xs_off) + 2 * t * SP;
+    const float* ys = (const float*)(xb + p.xs_off) + 2 * t;
+#pragma unroll
+    for (int nt = 0; nt < NT8; ++nt) {
+      uint32_t x[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ldsm4(x[j], xl + 8 * nt * MD_XPITCH + 64 * j);
+      float ya = 0.0f, yb = 0.0f;
+      if constexpr (KQ) { ya = ys[8 * nt]; yb = ys[8 * nt + 1]; }
+      f.apply(x, scl + 8 * nt * SP, scl + (8 * nt + 1) * SP, ya, yb, acc[nt]);
+    }
+    __syncwarp();  // every lane is through with buffer k % 2 before the next iteration's copies into it are issued
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (dead) {
+    // copies still in flight into this warp's stages get a bounded time to land before shared memory is released
+    for (int k = done; k < issued; ++k) mbar_wait(&full[k % stages], (uint32_t)(k / stages) & 1u, nullptr, 0);
+  }
+  // the warps' partial sums meet: thread (row, token) adds them in warp order
+#pragma unroll
+  for (int nt = 0; nt < NT8; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      part[(warp * 16 + g + 8 * (i >> 1)) * TN + 8 * nt + 2 * t + (i & 1)] = dead ? 0.0f : acc[nt][i];
+  if (__syncthreads_or(dead)) return;  // a warp gave up (status word set): the tile is not stored
+  for (int o = tid; o < 16 * TN; o += MD_THREADS) {
+    const int r = o / TN, tk = o - r * TN;
+    const long long row = row_base + r;
+    const int tok = tok0 + tk;
+    if (row < p.rows && tok < p.n) {
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < MD_WARPS; ++w) v = __fadd_rn(v, part[(w * 16 + r) * TN + tk]);
+      if (p.bias) v += p.bias[row];
+      float* yp = p.y + (long long)tok * p.rows + row;
+      *yp = p.acc ? *yp + v : v;
+    }
+  }
+}
+
 template <int FMT>
 static int mmd_launch(const MdParams& p, int tn, size_t smem, int grid, cudaStream_t st) {
   const void* k = tn == 32 ? (const void*)mmd_kernel<FMT, 4, 1> : tn == 64 ? (const void*)mmd_kernel<FMT, 8, 2> : (const void*)mmd_kernel<FMT, 16, 1>;
@@ -442,6 +598,68 @@ int mmd_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, u
     case ILL_Q8_0: return mmd_launch<ILL_Q8_0>(p, tn, smem, (int)grid, st);
     case ILL_Q4_K: return mmd_launch<ILL_Q4_K>(p, tn, smem, (int)grid, st);
     default: return mmd_launch<ILL_Q6_K>(p, tn, smem, (int)grid, st);
+  }
+}
+
+template <int FMT>
+static int mmk_launch(const MdParams& p, int tn, size_t smem, int grid, cudaStream_t st) {
+  const void* k = tn == 8 ? (const void*)mmk_kernel<FMT, 1> : (const void*)mmk_kernel<FMT, 2>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return cuda_fail(e);
+  MdParams pp = p;
+  void* args[] = {&pp};
+  return launch_kernel(k, dim3(grid), dim3(MD_THREADS), smem, args, st);
+}
+
+// Up to sixteen tokens with the columns dealt to a CTA's warps (mmk_kernel): for rows of many columns.
+int mmk_try(int fmt, uint64_t w, int rows, int cols, uint64_t xq, uint64_t xs, uint64_t xsum, uint64_t y, uint64_t bias, int acc,
+            int n, void* stream) {
+  if (fmt != ILL_Q8_0 && fmt != ILL_Q4_K && fmt != ILL_Q6_K) return ILL_ERR_UNSUPPORTED;
+  if (n < 2 || n > 16) return ILL_ERR_UNSUPPORTED;
+  const bool kq = fmt != ILL_Q8_0;
+  if (xq & 15) return ILL_ERR_UNSUPPORTED;
+  if (kq ? cols % 256 != 0 : ((xs & 15) || cols % 128)) return ILL_ERR_UNSUPPORTED;
+  if (fmt == ILL_Q4_K && (xsum & 15)) return ILL_ERR_UNSUPPORTED;
+  const int bw = fmt_block_weights(fmt), bb = fmt_block_bytes(fmt);
+  MdParams p = {};
+  p.w = (const u8*)(uintptr_t)w;
+  p.rows = rows;
+  p.cols = cols;
+  p.row_bytes = cols / bw * bb;
+  p.nsteps = (cols + 255) / 256;
+  if (p.nsteps < 2 * MD_WARPS) return ILL_ERR_UNSUPPORTED;  // too few steps to deal out
+  p.xq = (const i8*)(uintptr_t)xq;
+  p.xs = (const float*)(uintptr_t)xs;
+  p.xsum = (const int16_t*)(uintptr_t)xsum;
+  p.y = (float*)(uintptr_t)y;
+  p.bias = (const float*)(uintptr_t)bias;
+  p.acc = acc;
+  p.n = n;
+  p.warps = MD_WARPS;
+  const int tn = n <= 8 ? 8 : 16;
+  const int sb = fmt == ILL_Q8_0 ? 272 : bb;
+  p.pitch = (sb + 15 + 15) / 16 * 16;
+  p.stage_bytes = (uint32_t)(16 * p.pitch + 16);
+  uint32_t off = (uint32_t)tn * MD_XPITCH;
+  p.xs_off = off;
+  off += kq ? 4u * tn : (uint32_t)tn * MdFrag<ILL_Q8_0>::SPITCH;
+  off = (off + 15) / 16 * 16;
+  p.xsum_off = off;
+  if (fmt == ILL_Q4_K) off += (uint32_t)tn * MdFrag<ILL_Q4_K>::SPITCH;
+  p.xbuf_bytes = (off + 127) / 128 * 128;
+  p.ring_off = 2 * MD_WARPS * p.xbuf_bytes;
+  p.stages = MD_MAX_STAGES;
+  p.part_off = (uint32_t)((p.ring_off + (size_t)MD_WARPS * p.stages * p.stage_bytes + 127) / 128 * 128);
+  const size_t smem = p.part_off + (size_t)MD_WARPS * 16 * tn * 4;
+  if (smem > 226 * 1024) return ILL_ERR_UNSUPPORTED;
+  p.status = device_status_word();
+  const long long grid = (long long)((rows + 15) / 16) * ((n + tn - 1) / tn);
+  if (grid > 0x7fffffffll) return ILL_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (fmt) {
+    case ILL_Q8_0: return mmk_launch<ILL_Q8_0>(p, tn, smem, (int)grid, st);
+    case ILL_Q4_K: return mmk_launch<ILL_Q4_K>(p, tn, smem, (int)grid, st);
+    default: return mmk_launch<ILL_Q6_K>(p, tn, smem, (int)grid, st);
   }
 }
 

@@ -833,7 +833,9 @@ int mv_common(int fmt, int mode, int nmat, const ill_dptr* w, const int* rows, i
     // activations resident, chunks with them streamed), else the token loop below
     int rc_t = ILL_ERR_UNSUPPORTED;
     if (n <= 16) rc_t = mvt_try(fmt, w[0], rows[0], cols, xq, xs, xsum, y[0], bias ? bias[0] : 0, acc, n, stream);
-    // a chunk -- or a few tokens of rows too long for their activations to stay in shared memory
+    // a few tokens of rows too long for their activations to stay in shared memory
+    if (rc_t == ILL_ERR_UNSUPPORTED && n <= 16) rc_t = mmk_try(fmt, w[0], rows[0], cols, xq, xs, xsum, y[0], bias ? bias[0] : 0, acc, n, stream);
+    // a chunk
     if (rc_t == ILL_ERR_UNSUPPORTED) rc_t = mmd_try(fmt, w[0], rows[0], cols, xq, xs, xsum, y[0], bias ? bias[0] : 0, acc, n, stream);
     if (rc_t != ILL_ERR_UNSUPPORTED) return rc_t;
   }

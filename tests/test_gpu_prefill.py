@@ -30,6 +30,8 @@ def _case(fmt, rows, cols, n, seed=0):
     (B.Q4_K, 300, 512, 17), (B.Q4_K, 1000, 2560, 33), (B.Q4_K, 2560, 9728, 100), (B.Q4_K, 9728, 2560, 512),
     (B.Q6_K, 300, 768, 20), (B.Q6_K, 2560, 5120, 64), (B.Q6_K, 1031, 17408, 130), (B.Q6_K, 5120, 5120, 512),
     (B.Q8_0, 300, 896, 17), (B.Q8_0, 4864, 896, 96), (B.Q8_0, 896, 4864, 200), (B.Q8_0, 151936, 896, 40),
+    # a few tokens of rows too long to keep their activations beside the weights: the columns dealt to a CTA's warps
+    (B.Q6_K, 300, 17408, 4), (B.Q6_K, 1031, 17408, 16), (B.Q4_K, 250, 19456, 9), (B.Q8_0, 300, 17408, 16), (B.Q8_0, 40, 17280, 3),
 ])
 def test_chunk_product_equals_token_by_token(fmt, rows, cols, n):
     w, x, act = _case(fmt, rows, cols, n)
