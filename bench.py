@@ -625,7 +625,21 @@ def prefill_leg(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed, n, tpea
             c += 11
         D.cmat_mul(m["head"], D.rmsnorm_q8(h[(n - 1) * hidden:], m["nwf"], last, hidden, EPS), m["logits"], 1)
         launches[0] = c + 2
-    chunk()
+    from illatio_b200 import _lib as LIB
+    counted, real_call, real_status = [0], LIB.call, LIB.status
+
+    def counting(fn):
+        def wrapped(name, *a):
+            r = fn(name, *a)
+            counted[0] += 1 if r == 0 else 0   # a refusal (the caller then splits the tokens) launched nothing
+            return r
+        return wrapped
+    LIB.call, LIB.status = counting(real_call), counting(real_status)   # every kernel launch goes through one of the two
+    try:
+        chunk()
+    finally:
+        LIB.call, LIB.status = real_call, real_status
+    launches[0] = counted[0] + 1   # + the copy of the hidden states
     torch.cuda.synchronize()
     finite = bool(torch.isfinite(m["logits"]).all()) and bool(torch.isfinite(h).all())
     # parity, outside the timed region: the chunk product of the first layer's gate matrix against the one-token
@@ -649,7 +663,9 @@ def prefill_leg(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed, n, tpea
            "tokens": n, "ms": us / 1e3, "tokens_per_s": n / us * 1e6, "launches": launches[0], "how": "one CUDA graph",
            "int8_TOPS": tops, "frac_of_bf16_tensor_peak": tops / tpeak[0] if tpeak and tpeak[0] else None,
            "weight_MB_read_once": body / 1e6,
-           "kernel": "mmd_kernel: mma.sync int8, 128 rows x 128 tokens a CTA, weights by cp.async.bulk rings, activations by cp.async",
+           "kernel": "Q4_K matrices of 2048 rows and more: mm_id_kernel<Q4_K> (tcgen05, ill_mm_chunk; fp16 integer operands, the "
+                     "activations' fp16 form made once per quantization by ill_act_f16); k (1024 rows) and the Q6_K matrices (v, down): "
+                     "mmd_kernel (int8 mma.sync, 128 rows x 128 tokens a CTA)",
            "parity": {"finite": finite, "chunk_vs_one_token_max_rel": worst, "ok": finite and worst < 2e-6}}
     del m, g
     torch.cuda.empty_cache()

@@ -67,7 +67,15 @@ struct MmParams {
   long long y_stride;          // floats between rows of Y
   int ne;
   unsigned int* status;
+  // a dense product (ill_mm_chunk): no tables on the device -- PTRS is null, the one "expert" is the matrix at
+  // ONE_PTR with all ONE_COUNT rows of X; ACC: add into Y
+  unsigned long long one_ptr;
+  unsigned one_count;
+  int acc;
 };
+__device__ __forceinline__ unsigned long long mm_ptr(const MmParams& p, int e) { return p.ptrs ? p.ptrs[e] : p.one_ptr; }
+__device__ __forceinline__ int mm_count(const MmParams& p, int e) { return p.ptrs ? (int)p.counts[e] : (int)p.one_count; }
+__device__ __forceinline__ int mm_base(const MmParams& p, int e) { return p.ptrs ? (int)p.bases[e] : 0; }
 
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -260,19 +268,48 @@ __device__ __forceinline__ void w_q2k_mins(uint32_t m0, uint32_t m1, uint32_t* v
 // Tensor memory, 512 columns: accumulators D[2] at 0 and 128 (a column = a row of X); then
 //   IQ2_XXS  the A ring, 8 K steps x 32 columns, at 256
 //   Q2_K     the mins' accumulator at 256; the A ring, 4 K steps, at 384 (the mins themselves, a
-//            128 x 16 operand, go through two tiles in shared memory)
+//   Q4_K     128 x 16 operand, go through two tiles in shared memory)
+// Q4_K: byte I (0..11) of the block's packed scales and mins, held as the three words S
+__device__ __forceinline__ uint32_t q4k_sb(const uint32_t* s, int i) { return (s[i >> 2] >> (8 * (i & 3))) & 0xffu; }
+// get_scale_min_k4 (src/kquant.lisp:64-72): group J's 6-bit scale and min
+__device__ __forceinline__ void q4k_scale_min(const uint32_t* s, int j, uint32_t& sc, uint32_t& mn) {
+  if (j < 4) { sc = q4k_sb(s, j) & 63u; mn = q4k_sb(s, j + 4) & 63u; }
+  else { sc = (q4k_sb(s, j + 4) & 0xFu) | ((q4k_sb(s, j - 4) >> 6) << 4); mn = (q4k_sb(s, j + 4) >> 4) | ((q4k_sb(s, j) >> 6) << 4); }
+}
+// Q4_K: the 32 weights of a group -- the low (HI = 0) or high nibbles of the chunk's 32 quant bytes Q -- times the
+// group's scale: at most 15 * 63 = 945, exact in fp16 (the fused multiply-add rounds once)
+__device__ __forceinline__ void w_q4k(const uint32_t* q, int hi, uint32_t sc, uint32_t* out) {
+  const uint32_t s2 = small_h2(sc), bias = hmul2(s2, 0xe400e400u /* -1024 */);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t v = (q[i] >> (4 * hi)) & 0x0f0f0f0fu;
+    out[2 * i] = hfma2(bytes_to_h2_1024(v, 0x4140), s2, bias);
+    out[2 * i + 1] = hfma2(bytes_to_h2_1024(v, 0x4342), s2, bias);
+  }
+}
+// Q4_K: four groups' mins, each twice (a group of 32 faces two of the activations' sums of 16), as four words
+__device__ __forceinline__ void w_q4k_mins(const uint32_t* s, int g0, uint32_t* v) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t sc, mn;
+    q4k_scale_min(s, g0 + i, sc, mn);
+    v[i] = small_h2(mn);
+  }
+}
+
 template <int FMT> struct MmGeom {
-  static constexpr int BB = FMT == ILL_Q2_K ? 84 : 66;
-  static constexpr int NSLOT = FMT == ILL_Q2_K ? 4 : 8;  // a multiple of four: a slot is always written by the same warps
-  static constexpr int NX = FMT == ILL_Q2_K ? 6 : 8;     // stages of the ring of X tiles = K steps in flight
+  static constexpr bool KM = FMT == ILL_Q2_K || FMT == ILL_Q4_K;  // formats with mins: a second, small product a block
+  static constexpr int BB = FMT == ILL_Q2_K ? 84 : FMT == ILL_Q4_K ? 144 : 66;
+  static constexpr int NSLOT = KM ? 4 : 8;  // a multiple of four: a slot is always written by the same warps
+  static constexpr int NX = FMT == ILL_Q4_K ? 5 : KM ? 6 : 8;  // stages of the ring of X tiles = K steps in flight
   // A dequantizing warp waits for K step st - NSLOT on barrier (st - NSLOT) % NX; the barrier's next phase (K step
   // st - NSLOT + NX) must not be able to complete before that warp has passed, or the parity it waits for comes round again
   static_assert(NX >= NSLOT, "the ring of K-step barriers must be at least as long as the ring of A slots");
-  static constexpr int NE = FMT == ILL_Q2_K ? 4 : 0;     // Q2_K: two tiles of X's sums of 16, two of the mins
-  static constexpr uint32_t A_COL = FMT == ILL_Q2_K ? 384 : 256, DM_COL = 256;
+  static constexpr int NE = KM ? 4 : 0;     // Q2_K, Q4_K: two tiles of X's sums of 16, two of the mins
+  static constexpr uint32_t A_COL = KM ? 384 : 256, DM_COL = 256;
   // A row's raw block reaches shared memory as the WIN bytes from the 16-byte boundary at or before it,
-  // PITCH bytes apart
-  static constexpr uint32_t WIN = FMT == ILL_Q2_K ? 96 : 80, PITCH = FMT == ILL_Q2_K ? 112 : 80;
+  // PITCH bytes apart (Q4_K: blocks of 144 bytes in rows that the launcher wants 16-byte aligned)
+  static constexpr uint32_t WIN = FMT == ILL_Q2_K ? 96 : FMT == ILL_Q4_K ? 144 : 80, PITCH = FMT == ILL_Q2_K ? 112 : FMT == ILL_Q4_K ? 160 : 80;
   static constexpr uint32_t RAW_BYTES = 128 * PITCH;
   static constexpr size_t SMEM = (size_t)(NX + NE) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
                                  512 /* barriers */ + 4 * 256 * 4 /* weight scales */ + MM_XSC * 128 * 4 /* X scales */ +
@@ -285,6 +322,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
                                                            const __grid_constant__ CUtensorMap emap, const MmParams p) {
   typedef MmGeom<FMT> G;
   constexpr int BB = G::BB, NSLOT = G::NSLOT, NX = G::NX;
+  constexpr bool KM = G::KM;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ __align__(1024) u8 smem_raw[];
   // [X ring][Q2_K: sums of 16 x 2, mins x 2] (each tile 1024-byte aligned, as the 128-byte swizzle needs), the
@@ -322,7 +360,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     int before = 0;
     for (int e0 = 0; e0 < p.ne; e0 += 32) {
       const int e = e0 + lane;
-      const int c = e < p.ne ? (int)p.counts[e] : 0;
+      const int c = e < p.ne ? mm_count(p, e) : 0;
       const int tiles = (c + MM_BM - 1) / MM_BM;
       int incl = tiles;
 #pragma unroll
@@ -386,8 +424,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     }
     expert = lo;
     const int m_in = mt - tile_first[lo];
-    row0 = (int)p.bases[lo] + m_in * MM_BM;
-    nvalid = min(MM_BM, (int)p.counts[lo] - m_in * MM_BM);
+    row0 = mm_base(p, lo) + m_in * MM_BM;
+    nvalid = min(MM_BM, mm_count(p, lo) - m_in * MM_BM);
     // counts / bases come from the caller: a tile never reaches past the TOTAL_ROWS rows X and Y have
     if ((long long)row0 >= p.total_rows) { row0 = 0; nvalid = 0; }
     else nvalid = min(nvalid, (int)(p.total_rows - row0));
@@ -408,7 +446,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             mbar_expect_tx(&kfull[s], MM_TILE_BYTES);
             tma_load_2d(x_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &kfull[s]);
           }
-          if (FMT == ILL_Q2_K && ok) {
+          if (KM && ok) {
             const int sm = g_kb & 1;
             if (g_kb >= 2 && !mbar_wait(&mempty[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 100)) { ok = false; break; }
             mbar_expect_tx(&mfull[sm], MM_TILE_BYTES);
@@ -450,7 +488,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             __syncwarp();
           }
           if (!ok) break;
-          if constexpr (FMT == ILL_Q2_K) {
+          if constexpr (KM) {
             const int sm = g_kb & 1;
             ok = __all_sync(0xffffffffu, mbar_wait(&mfull[sm], (uint32_t)(g_kb >> 1) & 1u, p.status, ST_MM_WAIT_FULL + 3) &&
                                              (g_kb < 1 || mbar_wait(accm_free, (uint32_t)(g_kb - 1) & 1u, p.status, ST_MM_WAIT_EPI + 2)));
@@ -480,7 +518,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       locate(tile, expert, row0, nvalid, nt);
       const bool second = nt >= ntn1;
       if (second) nt -= ntn1;
-      const u8* wbase = (const u8*)(uintptr_t)p.ptrs[expert] + (second ? p.add2 : p.add) + (long long)nt * MM_BN * p.row_bytes;
+      const u8* wbase = (const u8*)(uintptr_t)mm_ptr(p, expert) + (second ? p.add2 : p.add) + (long long)nt * MM_BN * p.row_bytes;
       const int rows_here = min(MM_BN, p.nrows - nt * MM_BN);
       // the tokens of the tile's rows L, L + NL of X (a row past the tile's last takes the first row's)
       const float* xdp[128 / NL];
@@ -539,7 +577,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         const uint64_t dw2 = pack2(dw, dw);
         const float* xs = xsc + (d_kb % MM_XSC) * 128;
         const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16);
-        if constexpr (FMT == ILL_Q2_K) {
+        if constexpr (KM) {
           const float dm = -wsc[(d_kb & 3) * 256 + 128 + m];
           const uint64_t dm2 = pack2(dm, dm);
 #pragma unroll
@@ -614,7 +652,10 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           ycol += (size_t)row0 * ys;
 #pragma unroll
           for (int i = 0; i < 128; ++i) {
-            if (i < nvalid) *ycol = __uint_as_float((uint32_t)(out[i >> 1] >> (32 * (i & 1)))) * fin;
+            if (i < nvalid) {
+              const float v = __uint_as_float((uint32_t)(out[i >> 1] >> (32 * (i & 1)))) * fin;
+              *ycol = p.acc ? *ycol + v : v;
+            }
             ycol += ys;
           }
         }
@@ -640,7 +681,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       const int n = nt * MM_BN + row;
       const bool has_row = n < p.nrows;
       // the low bits of the row's address: where its blocks start inside their first word
-      const uint32_t rowlow = (uint32_t)(p.ptrs[expert] + (unsigned long long)(second ? p.add2 : p.add) + (unsigned long long)n * p.row_bytes);
+      const uint32_t rowlow = (uint32_t)(mm_ptr(p, expert) + (unsigned long long)(second ? p.add2 : p.add) + (unsigned long long)n * p.row_bytes);
       for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
         const int rs = g_kb % MM_RS;
         const bool r_ok = mbar_wait(&raw_full[rs], (uint32_t)(g_kb / MM_RS) & 1u, p.status, ST_MM_WAIT_FULL + 2, 50);
@@ -649,9 +690,9 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         // stage is free again
         const uint32_t o16 = (rowlow + (uint32_t)kb * BB) & 15u;
         const uint32_t* rw = raw + rs * (G::RAW_BYTES / 4) + row * (G::PITCH / 4);
-        uint32_t w[FMT == ILL_Q2_K ? 8 : 4], sc4 = 0, m0 = 0, m1 = 0, dd = 0;
+        uint32_t w[KM ? 8 : 4], sc4 = 0, m0 = 0, m1 = 0, dd = 0, s12[3] = {0, 0, 0};
 #pragma unroll
-        for (int i = 0; i < (FMT == ILL_Q2_K ? 8 : 4); ++i) w[i] = 0;
+        for (int i = 0; i < (KM ? 8 : 4); ++i) w[i] = 0;
         if (has_row) {
           if constexpr (FMT == ILL_IQ2_XXS) {
             dd = (rw[o16 >> 2] >> (8 * (o16 & 2u))) & 0xffffu;
@@ -663,6 +704,13 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
               w[i] = __funnelshift_r(prev, next, sh);
               prev = next;
             }
+          } else if constexpr (FMT == ILL_Q4_K) {
+            // K step j: the block's chunk j of 32 quant bytes (groups 2j and 2j + 1); the twelve bytes of scales and mins
+            const uint32_t* bw = rw + (o16 >> 2);  // a Q4_K block is 16-byte aligned
+            dd = bw[0];
+            s12[0] = bw[1]; s12[1] = bw[2]; s12[2] = bw[3];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = bw[4 + 8 * j + i];
           } else {
             // K step j: half j / 2 of the block's quants at shifts 2 (j % 2) and 2 (j % 2) + 1; its four scale bytes
             const uint32_t* bw = rw + (o16 >> 2);  // a Q2_K block is 4-byte aligned
@@ -685,7 +733,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           if (j == 0) {
             // The drain of four blocks back is over: the MMAs that freed this slot were issued after it.
             wsc[(g_kb & 3) * 256 + row] = h2f(dd & 0xffff);
-            if (FMT == ILL_Q2_K) wsc[(g_kb & 3) * 256 + 128 + row] = h2f(dd >> 16);
+            if (KM) wsc[(g_kb & 3) * 256 + 128 + row] = h2f(dd >> 16);
           }
           const uint32_t a0 = lane_base + G::A_COL + 32u * slot;
 #pragma unroll
@@ -697,6 +745,10 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[i] = 0;
               }
+            } else if constexpr (FMT == ILL_Q4_K) {
+              uint32_t sc, mn;
+              q4k_scale_min(s12, 2 * j + sb, sc, mn);
+              w_q4k(w, sb, sc, v);
             } else {
               w_q2k(w, 2 * (j & 1) + sb, sc4 >> (16 * sb), sc4 >> (16 * sb + 8), v);
             }
@@ -707,14 +759,16 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           __syncwarp();
           if (lane == 0) mbar_arrive(&kfull[st % NX]);
         }
-        if constexpr (FMT == ILL_Q2_K) {
+        if constexpr (KM) {
           if (j < 2) {  // warp-uniform: the eight warps of K steps 0 and 1 also make the mins
             const int sm = g_kb & 1;
             bool w_ok = true;
             if (g_kb >= 2) w_ok = mbar_wait(&mempty[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 50);
             if (!__all_sync(0xffffffffu, w_ok)) { ok = false; break; }
             uint32_t v[4];
-            w_q2k_mins(m0, m1, v);  // half j's eight mins: K = 8j .. 8j + 7 of the 16, chunk j of the row
+            // half j's eight mins: K = 8j .. 8j + 7 of the 16, chunk j of the row (Q4_K: groups 4j .. 4j + 3, each twice)
+            if constexpr (FMT == ILL_Q4_K) w_q4k_mins(s12, 4 * j, v);
+            else w_q2k_mins(m0, m1, v);
             store_chunk(m_tiles + sm * MM_TILE_BYTES, row, j, make_uint4(v[0], v[1], v[2], v[3]));
             fence_async_smem();  // the tensor core reads the tile through the async proxy
             __syncwarp();
@@ -1198,7 +1252,8 @@ static int encode_map(CUtensorMap* map, ill_dptr base, int64_t inner, int64_t ro
 
 static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int ne,
                         int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap, ill_dptr ypeers,
-                        ill_dptr y, int64_t y_stride, ill_stream stream, int64_t add2 = 0, ill_dptr y2 = 0);
+                        ill_dptr y, int64_t y_stride, ill_stream stream, int64_t add2 = 0, ill_dptr y2 = 0, ill_dptr one_ptr = 0,
+                        int acc = 0);
 
 extern "C" int ill_moe_mm_id2(int fmt, int ncols, int nrows, int64_t add, int64_t add2, ill_dptr ptrs, ill_dptr counts,
                               ill_dptr bases, int ne, int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map,
@@ -1224,22 +1279,33 @@ extern "C" int ill_moe_mm_id_peers(int fmt, int ncols, int nrows, int64_t add, i
                       stream);
 }
 
+extern "C" int ill_mm_chunk(int fmt, ill_dptr w, int rows, int cols, ill_dptr xh, ill_dptr xe, ill_dptr xd, int64_t n, ill_dptr y,
+                            int acc, ill_stream stream) {
+  if (!w || !y || n < 0 || n > 0x7fffffffll) return ILL_ERR_ARG;
+  if (fmt != ILL_Q4_K) return ILL_ERR_UNSUPPORTED;
+  return mm_id_launch(fmt, cols, rows, 0, 0, 0, 0, 1, n, xh, xe, xd, 0, 0, 0, y, rows, stream, 0, 0, w, acc ? 1 : 0);
+}
+
 static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int ne,
                         int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap, ill_dptr ypeers,
-                        ill_dptr y, int64_t y_stride, ill_stream stream, int64_t add2, ill_dptr y2) {
-  if (fmt != ILL_IQ2_XXS && fmt != ILL_Q2_K) return ILL_ERR_UNSUPPORTED;
+                        ill_dptr y, int64_t y_stride, ill_stream stream, int64_t add2, ill_dptr y2, ill_dptr one_ptr, int acc) {
+  if (fmt != ILL_IQ2_XXS && fmt != ILL_Q2_K && fmt != ILL_Q4_K) return ILL_ERR_UNSUPPORTED;
+  const bool km = fmt != ILL_IQ2_XXS;  // formats with mins: the sums of 16 of X come along
   if (ncols <= 0 || ncols % 256 || nrows <= 0 || ne <= 0 || ne > 65535 || total_rows < 0 || y_stride < nrows ||
       y_stride > 0xffffffffll)
     return ILL_ERR_ARG;
-  if (!ptrs || !counts || !bases || !xh || !xd || !y || (fmt == ILL_Q2_K && !xe)) return ILL_ERR_ARG;
+  if (!one_ptr && (!ptrs || !counts || !bases)) return ILL_ERR_ARG;
+  if (!xh || !xd || !y || (km && !xe)) return ILL_ERR_ARG;
+  if (fmt == ILL_Q4_K && (one_ptr & 15)) return ILL_ERR_ALIGN;
   if ((ptrs & 7) || (counts & 3) || (bases & 3) || (xh & 15) || (xe & 15) || (xd & 3) || (map & 3) || (ymap & 3) || (y & 15) ||
       (y_stride & 3) || (add & 3))
     return ILL_ERR_ALIGN;
+  if (fmt == ILL_Q4_K && ((add | add2) & 15)) return ILL_ERR_ALIGN;  // (and every PTRS[e]: the kernel copies 16-byte pieces of the rows as they lie)
   if (total_rows == 0) return ILL_OK;
   CUtensorMap xmap, emap;
   int rc = encode_map(&xmap, xh, ncols, total_rows);
   if (rc) return rc;
-  rc = fmt == ILL_Q2_K ? encode_map(&emap, xe, (int64_t)(ncols / 256) * 64, total_rows) : encode_map(&emap, xh, ncols, total_rows);
+  rc = km ? encode_map(&emap, xe, (int64_t)(ncols / 256) * 64, total_rows) : encode_map(&emap, xh, ncols, total_rows);
   if (rc) return rc;
   MmParams p;
   p.ncols = ncols;
@@ -1259,14 +1325,18 @@ static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptr
   p.y2 = (float*)(uintptr_t)y2;
   p.y_stride = y_stride;
   p.ne = ne;
+  p.one_ptr = one_ptr;
+  p.one_count = (unsigned)total_rows;
+  p.acc = acc;
   p.status = device_status_word();
   const long long max_tiles = ((total_rows + MM_BM - 1) / MM_BM + ne) * ((nrows + MM_BN - 1) / MM_BN) * (y2 ? 2 : 1);  // an upper bound
-  const size_t smem = fmt == ILL_IQ2_XXS ? MmGeom<ILL_IQ2_XXS>::SMEM : MmGeom<ILL_Q2_K>::SMEM;
+  const size_t smem = fmt == ILL_IQ2_XXS ? MmGeom<ILL_IQ2_XXS>::SMEM : fmt == ILL_Q2_K ? MmGeom<ILL_Q2_K>::SMEM : MmGeom<ILL_Q4_K>::SMEM;
   if (ne > 512) return ILL_ERR_TOO_LARGE;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  const void* k = fmt == ILL_IQ2_XXS ? (const void*)mm_id_kernel<ILL_IQ2_XXS> : (const void*)mm_id_kernel<ILL_Q2_K>;
+  const void* k = fmt == ILL_IQ2_XXS ? (const void*)mm_id_kernel<ILL_IQ2_XXS>
+                  : fmt == ILL_Q2_K ? (const void*)mm_id_kernel<ILL_Q2_K> : (const void*)mm_id_kernel<ILL_Q4_K>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e);
   // The warp groups trade registers after launch; what they ask for together must fit in what the

@@ -96,6 +96,7 @@ def quant_q8(x, act, f16_scale=True):
                   1 if f16_scale else 0, _stream())
     else:
         _lib.call("ill_quant_q8_k", _ptr(x), _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum), n // 256, _stream())
+    act._cf_fresh = False
     return act
 
 
@@ -104,12 +105,17 @@ def rmsnorm_q8(x, w, act, d, eps, n=1, h=None, f16_scale=True):
     W, quantized into ACT in the kind it holds; H, when given, also gets the floats."""
     _lib.call("ill_rmsnorm_q8", 1 if act.kind == "q8k" else 0, _ptr(x), _ptr(w), _ptr(h), _ptr(act.xq), _ptr(act.xs),
               _ptr(act.xsum), d, float(eps), n, 1 if f16_scale else 0, _stream())
+    act._cf_fresh = False
     return act
 
 
 def cmat_mul(w, act, y, n=1, bias=None, acc=False):
     """CMAT-MUL (src/cuda-dense.lisp:220-248): Y = W X for N tokens (token t's X
     at t*cols, its Y at t*rows), or Y += it when ACC."""
+    if (w.type == 1 and act.kind == "q8k" and n >= TC_MIN_TOKENS and w.rows >= TC_MIN_ROWS and w.rows % 4 == 0 and bias is None
+            and w.qs.data_ptr() % 16 == 0 and act.xq.numel() == n * w.cols):
+        # a prefill chunk of a Q4_K matrix: the tcgen05 kernel (the activations' fp16 form is made once per quantization)
+        return cmat_mul_tc(w, _chunk_f16_of(act, n, w.cols), y, acc=acc)
     done = 0
     # Q8_0 / Q4_K / Q6_K take a whole chunk of tokens in one launch; the other formats up to 16 tokens --
     # fewer when their activations do not fit beside the stages
@@ -180,6 +186,46 @@ def glu_mul(g, u, act, fa, n=1, fb=None):
     cmat_mul(u, act, fb, n)
     fa.copy_((fa / (1.0 + torch.exp(-fa))) * fb)  # the reference's swiglu kernel; not on the decode path
     return fa
+
+
+class ChunkF16:
+    """A chunk's Q8_K activations as the tcgen05 product takes them (ill_act_f16): XH [n, cols] the quants as fp16
+    (exact), XE [n, cols / 256, 64] the sums of 16 as fp16 (exact; 48 of each 64 zero), XD the block scales."""
+
+    def __init__(self, n, cols, device="cuda"):
+        self.n, self.cols = n, cols
+        self.xh = torch.empty(n, cols, dtype=torch.float16, device=device)
+        self.xe = torch.empty(n, cols // 256, 64, dtype=torch.float16, device=device)
+        self.xd = None
+
+    def fill(self, act):
+        _lib.call("ill_act_f16", self.n, self.cols, _ptr(act.xq), _ptr(act.xsum), 0, _ptr(self.xh), _ptr(self.xe), _stream())
+        self.xd = act.xs
+        return self
+
+
+def cmat_mul_tc(w, cf, y, acc=False):
+    """CMAT-MUL-N for a prefill chunk on the 5th-generation tensor cores (ill_mm_chunk): Y[t*rows + r] (+)= W[r] . X[t]
+    for the chunk CF (a ChunkF16 filled from the chunk's Q8_K activations) and a Q4_K matrix W.  Replaces
+    mm_q4k_mma (src/cuda/kquant.cu:316-390) behind CMAT-MUL-N (src/cuda-dense.lisp:250-255)."""
+    _lib.call("ill_mm_chunk", w.type, _ptr(w.qs), w.rows, w.cols, _ptr(cf.xh), _ptr(cf.xe), _ptr(cf.xd), cf.n, _ptr(y),
+              1 if acc else 0, _stream())
+    return y
+
+
+TC_MIN_TOKENS, TC_MIN_ROWS = 64, 2048   # below these the int8 mma.sync kernel is as fast or faster
+
+
+def _chunk_f16_of(act, n, cols):
+    """ACT's fp16 form for the tcgen05 product, made once per quantization of ACT (quant_q8 / rmsnorm_q8 mark it stale)."""
+    cf = getattr(act, "_cf", None)
+    if cf is None or cf.n != n or cf.cols != cols:
+        cf = act._cf = ChunkF16(n, cols, device=act.xq.device)
+        act._cf_fresh = False
+    if not getattr(act, "_cf_fresh", False):
+        cf.fill(act)
+        act._cf_fresh = True
+    return cf
 
 
 def swiglu(g, u, out, ff, clamp=3.0e38):

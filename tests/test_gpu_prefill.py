@@ -96,3 +96,46 @@ def test_ffn_head_chunk_against_the_oracle(oracle):
         assert (np.abs(logits[t] - want_l) <= 1e-6 * terms + 1e-30).all()
         want_s = oracle.moe_shared(d, ff, mats[0], mats[1], mats[2], norm2[t], clamp, threads=2)
         assert np.abs(sout[t] - want_s).max() / np.abs(want_s).max() < 2e-3
+
+
+@pytest.mark.parametrize("rows,cols,n", [(300, 512, 40), (1000, 2560, 130), (9728, 2560, 512), (2560, 9728, 200)])
+def test_q4k_chunk_on_tcgen05_equals_token_by_token(rows, cols, n):
+    """The same chunk product through the tcgen05 kernel (the expert product with the matrix as its one expert):
+    integer operands exact in fp16, fp32 accumulation in tensor memory, the blocks scaled as they are drained."""
+    w, x, act = _case(B.Q4_K, rows, cols, n, seed=3)
+    cf = D.ChunkF16(n, cols).fill(act)
+    y = torch.full((n * rows,), -3.0, device="cuda")
+    D.cmat_mul_tc(w, cf, y)
+    want = torch.empty(n * rows, device="cuda")
+    one = D.make_qact(cols, "q8k")
+    for t in range(n):   # one token at a time through the matvec kernel
+        D.cmat_mul(w, D.quant_q8(x[t * cols:(t + 1) * cols], one), want[t * rows:(t + 1) * rows], 1)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y).all()
+    err = ((y - want).abs().max() / want.abs().max()).item()
+    assert err < 2e-6, err
+    # added into Y when asked; and cmat_mul takes this path by itself for chunks of large Q4_K matrices
+    y2 = y.clone()
+    D.cmat_mul_tc(w, cf, y2, acc=True)
+    y3 = torch.empty_like(y)
+    D.cmat_mul(w, act, y3, n)
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y + y)
+    if rows >= D.TC_MIN_ROWS and n >= D.TC_MIN_TOKENS:
+        assert torch.equal(y3, y)
+
+
+def test_q4k_chunk_on_tcgen05_against_the_oracle(oracle):
+    rows, cols, n = 200, 1024, 70
+    wb = B.synth_matrix(B.Q4_K, rows, cols, seed=4)
+    w = D.upload_gmat(wb, B.Q4_K, rows, cols)
+    rng = np.random.default_rng(6)
+    xh = rng.standard_normal((n, cols)).astype(np.float32)
+    act = D.quant_q8(to_dev(xh.reshape(-1)), D.make_qact(n * cols, "q8k"))
+    y = torch.zeros(n * rows, device="cuda")
+    D.cmat_mul_tc(w, D.ChunkF16(n, cols).fill(act), y)
+    torch.cuda.synchronize()
+    got = y.cpu().numpy().reshape(n, rows)
+    for t in (0, 1, 37, n - 1):
+        want = oracle.matvec(B.Q4_K, wb, rows, cols, oracle.quantize_act(B.Q4_K, xh[t]))[0]
+        assert np.abs(got[t] - want).max() / np.abs(want).max() < 2e-6
