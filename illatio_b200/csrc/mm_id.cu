@@ -149,6 +149,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
       "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]),
+               "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t* v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
                "r"(v[3])
@@ -297,19 +302,55 @@ __device__ __forceinline__ void w_q4k_mins(const uint32_t* s, int g0, uint32_t* 
   }
 }
 
+// N words starting BYTE_OFF bytes into the row's window RW (any 2-byte alignment of the offset is taken up by funnel shifts)
+template <int N>
+__device__ __forceinline__ void raw_words(const uint32_t* rw, uint32_t byte_off, uint32_t* out) {
+  const uint32_t w0 = byte_off >> 2, sh = (byte_off & 3u) * 8u;
+  uint32_t prev = rw[w0];
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    const uint32_t next = rw[w0 + i + 1];
+    out[i] = __funnelshift_r(prev, next, sh);
+    prev = next;
+  }
+}
+// Q6_K: 16 weights of a K step -- the nibbles at shift 4 ODD of the four words QL, the 2-bit fields at shift QSH of the
+// four words QH -- times their group's signed scale SC.  |SC * (q - 32)| reaches 4064 and fp16 holds only even
+// integers above 2048, so the product goes to the tensor core in two exact parts: EVEN = (SC - SC % 2) * (q - 32), an
+// even integer of at most 4096, and ODD = (SC % 2) * (q - 32); both are multiplied with the same activations into
+// the same accumulator.
+__device__ __forceinline__ void w_q6k(const uint32_t* ql, const uint32_t* qh, int odd, int qsh, int sc, uint32_t* even, uint32_t* oddp) {
+  const int s0 = sc & 1;
+  uint32_t s2 = small_h2((uint32_t)(sc - s0 + 128));
+  asm("add.rn.f16x2 %0, %0, %1;" : "+r"(s2) : "r"(0xd800d800u));  // - 128
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t v = ((ql[i] >> (4 * odd)) & 0x0f0f0f0fu) | (((qh[i] >> qsh) & 0x03030303u) << 4);
+    uint32_t a = bytes_to_h2_1024(v, 0x4140), b = bytes_to_h2_1024(v, 0x4342);
+    asm("add.rn.f16x2 %0, %0, %1;" : "+r"(a) : "r"(0xe420e420u));  // - 1056: q - 32
+    asm("add.rn.f16x2 %0, %0, %1;" : "+r"(b) : "r"(0xe420e420u));
+    even[2 * i] = hmul2(a, s2);
+    even[2 * i + 1] = hmul2(b, s2);
+    oddp[2 * i] = s0 ? a : 0u;
+    oddp[2 * i + 1] = s0 ? b : 0u;
+  }
+}
+
 template <int FMT> struct MmGeom {
   static constexpr bool KM = FMT == ILL_Q2_K || FMT == ILL_Q4_K;  // formats with mins: a second, small product a block
-  static constexpr int BB = FMT == ILL_Q2_K ? 84 : FMT == ILL_Q4_K ? 144 : 66;
-  static constexpr int NSLOT = KM ? 4 : 8;  // a multiple of four: a slot is always written by the same warps
-  static constexpr int NX = FMT == ILL_Q4_K ? 5 : KM ? 6 : 8;  // stages of the ring of X tiles = K steps in flight
+  static constexpr int BB = FMT == ILL_Q2_K ? 84 : FMT == ILL_Q4_K ? 144 : FMT == ILL_Q6_K ? 210 : 66;
+  static constexpr int NSLOT = KM || FMT == ILL_Q6_K ? 4 : 8;  // a multiple of four: a slot is always written by the same warps
+  static constexpr int NX = FMT == ILL_Q4_K ? 5 : KM ? 6 : FMT == ILL_Q6_K ? 6 : 8;  // stages of the ring of X tiles = K steps in flight
   // A dequantizing warp waits for K step st - NSLOT on barrier (st - NSLOT) % NX; the barrier's next phase (K step
   // st - NSLOT + NX) must not be able to complete before that warp has passed, or the parity it waits for comes round again
   static_assert(NX >= NSLOT, "the ring of K-step barriers must be at least as long as the ring of A slots");
   static constexpr int NE = KM ? 4 : 0;     // Q2_K, Q4_K: two tiles of X's sums of 16, two of the mins
   static constexpr uint32_t A_COL = KM ? 384 : 256, DM_COL = 256;
+  static constexpr uint32_t SLOTW = FMT == ILL_Q6_K ? 64 : 32;  // columns of an A slot (Q6_K: the even and the odd part)
   // A row's raw block reaches shared memory as the WIN bytes from the 16-byte boundary at or before it,
   // PITCH bytes apart (Q4_K: blocks of 144 bytes in rows that the launcher wants 16-byte aligned)
-  static constexpr uint32_t WIN = FMT == ILL_Q2_K ? 96 : FMT == ILL_Q4_K ? 144 : 80, PITCH = FMT == ILL_Q2_K ? 112 : FMT == ILL_Q4_K ? 160 : 80;
+  static constexpr uint32_t WIN = FMT == ILL_Q2_K ? 96 : FMT == ILL_Q4_K ? 144 : FMT == ILL_Q6_K ? 224 : 80;
+  static constexpr uint32_t PITCH = FMT == ILL_Q2_K ? 112 : FMT == ILL_Q4_K ? 160 : FMT == ILL_Q6_K ? 240 : 80;
   static constexpr uint32_t RAW_BYTES = 128 * PITCH;
   static constexpr size_t SMEM = (size_t)(NX + NE) * MM_TILE_BYTES + MM_RS * RAW_BYTES + 16 /* a word past the last row is read */ +
                                  512 /* barriers */ + 4 * 256 * 4 /* weight scales */ + MM_XSC * 128 * 4 /* X scales */ +
@@ -478,11 +519,15 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const uint64_t xdsc = umma_desc(x_tiles + s * MM_TILE_BYTES);
-            const uint32_t a0 = tmem_base + G::A_COL + 32u * slot;
+            const uint32_t a0 = tmem_base + G::A_COL + G::SLOTW * slot;
             if (elect_one()) {
 #pragma unroll
               for (int k = 0; k < MM_BK / 16; ++k)  // 16 of K: 8 columns of A, 32 bytes inside X's swizzle atom
                 umma_f16_ts(d1, a0 + 8 * k, xdsc + 2 * k, idesc, (j | k) ? 1u : 0u);
+              if constexpr (FMT == ILL_Q6_K) {  // the weights' odd parts against the same activations
+#pragma unroll
+                for (int k = 0; k < MM_BK / 16; ++k) umma_f16_ts(d1, a0 + 32 + 8 * k, xdsc + 2 * k, idesc, 1u);
+              }
               umma_commit(&kempty[s]);  // the X stage and the A slot are free when these MMAs are done
             }
             __syncwarp();
@@ -704,6 +749,10 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
               w[i] = __funnelshift_r(prev, next, sh);
               prev = next;
             }
+          } else if constexpr (FMT == ILL_Q6_K) {
+            // the block's scale and K step j's four group scales; the quants are read as they are unpacked (below)
+            dd = (rw[(o16 + 208) >> 2] >> (8 * ((o16 + 208) & 2u))) & 0xffffu;
+            raw_words<1>(rw, o16 + 192 + 4 * j, &sc4);
           } else if constexpr (FMT == ILL_Q4_K) {
             // K step j: the block's chunk j of 32 quant bytes (groups 2j and 2j + 1); the twelve bytes of scales and mins
             const uint32_t* bw = rw + (o16 >> 2);  // a Q4_K block is 16-byte aligned
@@ -722,7 +771,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&raw_empty[rs]);
+        if (FMT != ILL_Q6_K && lane == 0) mbar_arrive(&raw_empty[rs]);  // (Q6_K reads its quants from the stage while unpacking)
         {
           // the slot's last K step was st - NSLOT: its MMAs must be done
           const int st = 4 * g_kb + j, slot = st % NSLOT, sp = st - NSLOT;
@@ -735,7 +784,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             wsc[(g_kb & 3) * 256 + row] = h2f(dd & 0xffff);
             if (KM) wsc[(g_kb & 3) * 256 + 128 + row] = h2f(dd >> 16);
           }
-          const uint32_t a0 = lane_base + G::A_COL + 32u * slot;
+          const uint32_t a0 = lane_base + G::A_COL + G::SLOTW * slot;
 #pragma unroll
           for (int sb = 0; sb < 2; ++sb) {  // 32 weights = 16 columns at a time
             uint32_t v[16];
@@ -745,6 +794,24 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[i] = 0;
               }
+            } else if constexpr (FMT == ILL_Q6_K) {
+              // K step j: half j / 2 of the block; columns 32 sb .. of the step are the nibbles at shift 4 (j % 2) of
+              // ql[32 sb ..] with the 2-bit fields at shift 2 (2 (j % 2) + sb) of qh; sixteen weights (a group) at a time
+#pragma unroll
+              for (int hf = 0; hf < 2; ++hf) {
+                uint32_t ev[8], od[8];
+                if (has_row) {
+                  uint32_t ql[4], qh[4];
+                  raw_words<4>(rw, o16 + 64 * (j >> 1) + 32 * sb + 16 * hf, ql);
+                  raw_words<4>(rw, o16 + 128 + 32 * (j >> 1) + 16 * hf, qh);
+                  w_q6k(ql, qh, j & 1, 2 * (2 * (j & 1) + sb), (int)(signed char)((sc4 >> (16 * sb + 8 * hf)) & 0xffu), ev, od);
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) ev[i] = od[i] = 0;
+                }
+                tmem_st8(a0 + 16 * sb + 8 * hf, ev);
+                tmem_st8(a0 + 32 + 16 * sb + 8 * hf, od);
+              }
             } else if constexpr (FMT == ILL_Q4_K) {
               uint32_t sc, mn;
               q4k_scale_min(s12, 2 * j + sb, sc, mn);
@@ -752,12 +819,13 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             } else {
               w_q2k(w, 2 * (j & 1) + sb, sc4 >> (16 * sb), sc4 >> (16 * sb + 8), v);
             }
-            tmem_st16(a0 + 16 * sb, v);
+            if constexpr (FMT != ILL_Q6_K) tmem_st16(a0 + 16 * sb, v);
           }
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&kfull[st % NX]);
+          if (FMT == ILL_Q6_K && lane == 0) mbar_arrive(&raw_empty[rs]);
         }
         if constexpr (KM) {
           if (j < 2) {  // warp-uniform: the eight warps of K steps 0 and 1 also make the mins
@@ -1282,15 +1350,15 @@ extern "C" int ill_moe_mm_id_peers(int fmt, int ncols, int nrows, int64_t add, i
 extern "C" int ill_mm_chunk(int fmt, ill_dptr w, int rows, int cols, ill_dptr xh, ill_dptr xe, ill_dptr xd, int64_t n, ill_dptr y,
                             int acc, ill_stream stream) {
   if (!w || !y || n < 0 || n > 0x7fffffffll) return ILL_ERR_ARG;
-  if (fmt != ILL_Q4_K) return ILL_ERR_UNSUPPORTED;
+  if (fmt != ILL_Q4_K && fmt != ILL_Q6_K) return ILL_ERR_UNSUPPORTED;
   return mm_id_launch(fmt, cols, rows, 0, 0, 0, 0, 1, n, xh, xe, xd, 0, 0, 0, y, rows, stream, 0, 0, w, acc ? 1 : 0);
 }
 
 static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int ne,
                         int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap, ill_dptr ypeers,
                         ill_dptr y, int64_t y_stride, ill_stream stream, int64_t add2, ill_dptr y2, ill_dptr one_ptr, int acc) {
-  if (fmt != ILL_IQ2_XXS && fmt != ILL_Q2_K && fmt != ILL_Q4_K) return ILL_ERR_UNSUPPORTED;
-  const bool km = fmt != ILL_IQ2_XXS;  // formats with mins: the sums of 16 of X come along
+  if (fmt != ILL_IQ2_XXS && fmt != ILL_Q2_K && fmt != ILL_Q4_K && fmt != ILL_Q6_K) return ILL_ERR_UNSUPPORTED;
+  const bool km = fmt == ILL_Q2_K || fmt == ILL_Q4_K;  // formats with mins: the sums of 16 of X come along
   if (ncols <= 0 || ncols % 256 || nrows <= 0 || ne <= 0 || ne > 65535 || total_rows < 0 || y_stride < nrows ||
       y_stride > 0xffffffffll)
     return ILL_ERR_ARG;
@@ -1330,13 +1398,15 @@ static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptr
   p.acc = acc;
   p.status = device_status_word();
   const long long max_tiles = ((total_rows + MM_BM - 1) / MM_BM + ne) * ((nrows + MM_BN - 1) / MM_BN) * (y2 ? 2 : 1);  // an upper bound
-  const size_t smem = fmt == ILL_IQ2_XXS ? MmGeom<ILL_IQ2_XXS>::SMEM : fmt == ILL_Q2_K ? MmGeom<ILL_Q2_K>::SMEM : MmGeom<ILL_Q4_K>::SMEM;
+  const size_t smem = fmt == ILL_IQ2_XXS ? MmGeom<ILL_IQ2_XXS>::SMEM : fmt == ILL_Q2_K ? MmGeom<ILL_Q2_K>::SMEM
+                      : fmt == ILL_Q4_K ? MmGeom<ILL_Q4_K>::SMEM : MmGeom<ILL_Q6_K>::SMEM;
   if (ne > 512) return ILL_ERR_TOO_LARGE;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   const void* k = fmt == ILL_IQ2_XXS ? (const void*)mm_id_kernel<ILL_IQ2_XXS>
-                  : fmt == ILL_Q2_K ? (const void*)mm_id_kernel<ILL_Q2_K> : (const void*)mm_id_kernel<ILL_Q4_K>;
+                  : fmt == ILL_Q2_K ? (const void*)mm_id_kernel<ILL_Q2_K>
+                  : fmt == ILL_Q4_K ? (const void*)mm_id_kernel<ILL_Q4_K> : (const void*)mm_id_kernel<ILL_Q6_K>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e);
   // The warp groups trade registers after launch; what they ask for together must fit in what the

@@ -112,9 +112,9 @@ def rmsnorm_q8(x, w, act, d, eps, n=1, h=None, f16_scale=True):
 def cmat_mul(w, act, y, n=1, bias=None, acc=False):
     """CMAT-MUL (src/cuda-dense.lisp:220-248): Y = W X for N tokens (token t's X
     at t*cols, its Y at t*rows), or Y += it when ACC."""
-    if (w.type == 1 and act.kind == "q8k" and n >= TC_MIN_TOKENS and w.rows >= TC_MIN_ROWS and w.rows % 4 == 0 and bias is None
+    if ((w.type == 1 or (w.type == 2 and TC_Q6K)) and act.kind == "q8k" and n >= TC_MIN_TOKENS and w.rows >= TC_MIN_ROWS and w.rows % 4 == 0 and bias is None
             and w.qs.data_ptr() % 16 == 0 and act.xq.numel() == n * w.cols):
-        # a prefill chunk of a Q4_K matrix: the tcgen05 kernel (the activations' fp16 form is made once per quantization)
+        # a prefill chunk of a Q4_K / Q6_K matrix: the tcgen05 kernel (the activations' fp16 form is made once per quantization)
         return cmat_mul_tc(w, _chunk_f16_of(act, n, w.cols), y, acc=acc)
     done = 0
     # Q8_0 / Q4_K / Q6_K take a whole chunk of tokens in one launch; the other formats up to 16 tokens --
@@ -206,14 +206,17 @@ class ChunkF16:
 
 def cmat_mul_tc(w, cf, y, acc=False):
     """CMAT-MUL-N for a prefill chunk on the 5th-generation tensor cores (ill_mm_chunk): Y[t*rows + r] (+)= W[r] . X[t]
-    for the chunk CF (a ChunkF16 filled from the chunk's Q8_K activations) and a Q4_K matrix W.  Replaces
-    mm_q4k_mma (src/cuda/kquant.cu:316-390) behind CMAT-MUL-N (src/cuda-dense.lisp:250-255)."""
+    for the chunk CF (a ChunkF16 filled from the chunk's Q8_K activations) and a Q4_K or Q6_K matrix W.  Replaces
+    mm_q4k_mma / mm_q6k_mma (src/cuda/kquant.cu:316-466) behind CMAT-MUL-N (src/cuda-dense.lisp:250-255)."""
     _lib.call("ill_mm_chunk", w.type, _ptr(w.qs), w.rows, w.cols, _ptr(cf.xh), _ptr(cf.xe), _ptr(cf.xd), cf.n, _ptr(y),
               1 if acc else 0, _stream())
     return y
 
 
 TC_MIN_TOKENS, TC_MIN_ROWS = 64, 2048   # below these the int8 mma.sync kernel is as fast or faster
+# Q6_K on the tcgen05 path: scale * (q - 32) reaches 4064 and fp16 holds only even integers above 2048, so the kernel
+# multiplies an even part and an odd part of every product (both exact).  False keeps Q6_K chunks on the int8 kernel.
+TC_Q6K = True
 
 
 def _chunk_f16_of(act, n, cols):

@@ -98,11 +98,14 @@ def test_ffn_head_chunk_against_the_oracle(oracle):
         assert np.abs(sout[t] - want_s).max() / np.abs(want_s).max() < 2e-3
 
 
-@pytest.mark.parametrize("rows,cols,n", [(300, 512, 40), (1000, 2560, 130), (9728, 2560, 512), (2560, 9728, 200)])
-def test_q4k_chunk_on_tcgen05_equals_token_by_token(rows, cols, n):
+@pytest.mark.parametrize("fmt,rows,cols,n", [(B.Q4_K, 300, 512, 40), (B.Q4_K, 1000, 2560, 130), (B.Q4_K, 9728, 2560, 512),
+                                             (B.Q4_K, 2560, 9728, 200), (B.Q6_K, 300, 768, 40), (B.Q6_K, 1031 - 3, 2560, 130),
+                                             (B.Q6_K, 2560, 9728, 512), (B.Q6_K, 5120, 5120, 200)])
+def test_chunk_on_tcgen05_equals_token_by_token(fmt, rows, cols, n):
     """The same chunk product through the tcgen05 kernel (the expert product with the matrix as its one expert):
-    integer operands exact in fp16, fp32 accumulation in tensor memory, the blocks scaled as they are drained."""
-    w, x, act = _case(B.Q4_K, rows, cols, n, seed=3)
+    integer operands exact in fp16 (Q6_K's products as an even and an odd part), fp32 accumulation in tensor memory,
+    the blocks scaled as they are drained."""
+    w, x, act = _case(fmt, rows, cols, n, seed=3)
     cf = D.ChunkF16(n, cols).fill(act)
     y = torch.full((n * rows,), -3.0, device="cuda")
     D.cmat_mul_tc(w, cf, y)
@@ -114,7 +117,7 @@ def test_q4k_chunk_on_tcgen05_equals_token_by_token(rows, cols, n):
     assert torch.isfinite(y).all()
     err = ((y - want).abs().max() / want.abs().max()).item()
     assert err < 2e-6, err
-    # added into Y when asked; and cmat_mul takes this path by itself for chunks of large Q4_K matrices
+    # added into Y when asked; and cmat_mul takes this path by itself for chunks of large matrices
     y2 = y.clone()
     D.cmat_mul_tc(w, cf, y2, acc=True)
     y3 = torch.empty_like(y)
@@ -125,10 +128,11 @@ def test_q4k_chunk_on_tcgen05_equals_token_by_token(rows, cols, n):
         assert torch.equal(y3, y)
 
 
-def test_q4k_chunk_on_tcgen05_against_the_oracle(oracle):
+@pytest.mark.parametrize("fmt", [B.Q4_K, B.Q6_K])
+def test_chunk_on_tcgen05_against_the_oracle(oracle, fmt):
     rows, cols, n = 200, 1024, 70
-    wb = B.synth_matrix(B.Q4_K, rows, cols, seed=4)
-    w = D.upload_gmat(wb, B.Q4_K, rows, cols)
+    wb = B.synth_matrix(fmt, rows, cols, seed=4)
+    w = D.upload_gmat(wb, fmt, rows, cols)
     rng = np.random.default_rng(6)
     xh = rng.standard_normal((n, cols)).astype(np.float32)
     act = D.quant_q8(to_dev(xh.reshape(-1)), D.make_qact(n * cols, "q8k"))
@@ -137,5 +141,5 @@ def test_q4k_chunk_on_tcgen05_against_the_oracle(oracle):
     torch.cuda.synchronize()
     got = y.cpu().numpy().reshape(n, rows)
     for t in (0, 1, 37, n - 1):
-        want = oracle.matvec(B.Q4_K, wb, rows, cols, oracle.quantize_act(B.Q4_K, xh[t]))[0]
+        want = oracle.matvec(fmt, wb, rows, cols, oracle.quantize_act(fmt, xh[t]))[0]
         assert np.abs(got[t] - want).max() / np.abs(want).max() < 2e-6
