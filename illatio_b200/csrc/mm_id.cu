@@ -6,7 +6,8 @@
 //
 // X is the chunk's activations already grouped by expert (ill_moe_group), as fp16
 // (ill_act_f16: the Q8_K quants, exact in fp16).  W_e is expert e's matrix of raw IQ2_XXS
-// or Q2_K blocks at ptrs[e] + add.
+// or Q2_K blocks at ptrs[e] + add -- or of Q4_K / Q6_K blocks: the dense prefill products run through the same
+// kernel with the matrix as its one expert (ill_mm_chunk; mm_q4k_mma / mm_q6k_mma, src/cuda/kquant.cu:316-466).
 //
 // A persistent grid (a CTA per SM) walks tiles of 128 weight rows x up to 128 rows of X.  The
 // weights are the tensor core's A operand and live in tensor memory: the dequantizing warps write

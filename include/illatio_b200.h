@@ -479,20 +479,21 @@ ILL_API int ill_moe_mm_id_peers(int fmt, int ncols, int nrows, int64_t add, ill_
                                 ill_dptr ypeers, int64_t y_stride, ill_stream stream);
 
 /* CMAT-MUL-N for a prefill chunk on the 5th-generation tensor cores: Y[t*rows + r] (+)= W[r] . X[t] for N tokens
- * and a ROWS x COLS matrix of Q4_K blocks -- the kernel of ill_moe_mm_id with the matrix as its one expert and
- * no tables on the device.  XH / XE / XD as ill_act_f16 leaves them for the chunk's Q8_K activations (MAP 0):
- * quants and sums of 16 as fp16 integers, and the block scales.  (s * q <= 945 is exact in fp16 and the block's
+ * and a ROWS x COLS matrix of Q4_K or Q6_K blocks -- the kernel of ill_moe_mm_id with the matrix as its one expert
+ * and no tables on the device.  XH / XE / XD as ill_act_f16 leaves them for the chunk's Q8_K activations (MAP 0):
+ * quants and sums of 16 as fp16 integers (XE: Q4_K only, else 0), and the block scales.  The weights go in as
+ * integers exact in fp16 (Q4_K: scale * q <= 945; Q6_K: scale * (q - 32) as an even and an odd part) and a block's
  * sum is taken in fp32 in tensor memory, exact up to 2^24: it could only round if nearly every weight and
- * activation of a block sat at its maximum.)  W 16-byte aligned, ROWS a multiple of 4.  ILL_ERR_UNSUPPORTED for
- * the other formats: ill_mv takes chunks of Q8_0 / Q6_K (and Q4_K) on the int8 mma.sync path.  Replaces
- * mm_q4k_mma (src/cuda/kquant.cu:316-390) behind CMAT-MUL-N (src/cuda-dense.lisp:250-255). */
+ * activation of a block sat at its maximum.  W 16-byte aligned (Q4_K), ROWS a multiple of 4.
+ * ILL_ERR_UNSUPPORTED for the other formats: ill_mv takes chunks of Q8_0 (and of these two) on the int8 mma.sync
+ * path.  Replaces mm_q4k_mma / mm_q6k_mma (src/cuda/kquant.cu:316-466) behind CMAT-MUL-N (src/cuda-dense.lisp:250-255). */
 ILL_API int ill_mm_chunk(int fmt, ill_dptr w, int rows, int cols, ill_dptr xh, ill_dptr xe, ill_dptr xd, int64_t n, ill_dptr y,
                          int acc, ill_stream stream);
 
 /* The routed experts' product for a chunk: for each expert e < NE and each row
  * `place` in [BASES[e], BASES[e] + COUNTS[e]): Y[place*y_stride + n] = W_e[n] .
- * X[place], n < NROWS, W_e the FMT (ILL_IQ2_XXS or ILL_Q2_K) matrix at PTRS[e]
- * + ADD, X the Q8_K activations XH (+ XE for Q2_K) of ill_act_f16 with block
+ * X[place], n < NROWS, W_e the FMT (ILL_IQ2_XXS, ILL_Q2_K; also ILL_Q4_K, ILL_Q6_K) matrix at PTRS[e]
+ * + ADD, X the Q8_K activations XH (+ XE for Q2_K / Q4_K) of ill_act_f16 with block
  * scales XD[t*(ncols/256) + kb], t = MAP[place] (MAP = 0: t = place).  COUNTS /
  * BASES are read on the device (no host synchronisation); TOTAL_ROWS is the
  * number of rows of XH and Y.  With YMAP given, row `place` is written to row
