@@ -282,12 +282,13 @@ __device__ __forceinline__ void q4k_scale_min(const uint32_t* s, int j, uint32_t
   if (j < 4) { sc = q4k_sb(s, j) & 63u; mn = q4k_sb(s, j + 4) & 63u; }
   else { sc = (q4k_sb(s, j + 4) & 0xFu) | ((q4k_sb(s, j - 4) >> 6) << 4); mn = (q4k_sb(s, j + 4) >> 4) | ((q4k_sb(s, j) >> 6) << 4); }
 }
-// Q4_K: the 32 weights of a group -- the low (HI = 0) or high nibbles of the chunk's 32 quant bytes Q -- times the
+// Q4_K: 4 NW weights of a group -- the low (HI = 0) or high nibbles of the NW words of quant bytes Q -- times the
 // group's scale: at most 15 * 63 = 945, exact in fp16 (the fused multiply-add rounds once)
+template <int NW>
 __device__ __forceinline__ void w_q4k(const uint32_t* q, int hi, uint32_t sc, uint32_t* out) {
   const uint32_t s2 = small_h2(sc), bias = hmul2(s2, 0xe400e400u /* -1024 */);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < NW; ++i) {
     const uint32_t v = (q[i] >> (4 * hi)) & 0x0f0f0f0fu;
     out[2 * i] = hfma2(bytes_to_h2_1024(v, 0x4140), s2, bias);
     out[2 * i + 1] = hfma2(bytes_to_h2_1024(v, 0x4342), s2, bias);
@@ -816,11 +817,16 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
             } else if constexpr (FMT == ILL_Q4_K) {
               uint32_t sc, mn;
               q4k_scale_min(s12, 2 * j + sb, sc, mn);
-              w_q4k(w, sb, sc, v);
+#pragma unroll
+              for (int hf = 0; hf < 2; ++hf) {  // sixteen weights at a time: fewer live registers than all 32
+                uint32_t v8[8];
+                w_q4k<4>(w + 4 * hf, sb, sc, v8);
+                tmem_st8(a0 + 16 * sb + 8 * hf, v8);
+              }
             } else {
               w_q2k(w, 2 * (j & 1) + sb, sc4 >> (16 * sb), sc4 >> (16 * sb + 8), v);
             }
-            if constexpr (FMT != ILL_Q6_K) tmem_st16(a0 + 16 * sb, v);
+            if constexpr (FMT != ILL_Q6_K && FMT != ILL_Q4_K) tmem_st16(a0 + 16 * sb, v);
           }
           tmem_st_wait();
           tc_fence_before();
