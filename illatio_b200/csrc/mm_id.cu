@@ -74,9 +74,16 @@ struct MmParams {
   unsigned one_count;
   int acc;
 };
-__device__ __forceinline__ unsigned long long mm_ptr(const MmParams& p, int e) { return p.ptrs ? p.ptrs[e] : p.one_ptr; }
-__device__ __forceinline__ int mm_count(const MmParams& p, int e) { return p.ptrs ? (int)p.counts[e] : (int)p.one_count; }
-__device__ __forceinline__ int mm_base(const MmParams& p, int e) { return p.ptrs ? (int)p.bases[e] : 0; }
+// (DENSE is a template argument of the kernel, so that the experts' launches compile to what they were without it)
+template <bool DENSE> __device__ __forceinline__ unsigned long long mm_ptr(const MmParams& p, int e) {
+  if constexpr (DENSE) return p.one_ptr; else return p.ptrs[e];
+}
+template <bool DENSE> __device__ __forceinline__ int mm_count(const MmParams& p, int e) {
+  if constexpr (DENSE) return (int)p.one_count; else return (int)p.counts[e];
+}
+template <bool DENSE> __device__ __forceinline__ int mm_base(const MmParams& p, int e) {
+  if constexpr (DENSE) return 0; else return (int)p.bases[e];
+}
 
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -360,7 +367,7 @@ template <int FMT> struct MmGeom {
                                  1024 /* alignment */;
 };
 
-template <int FMT>
+template <int FMT, bool DENSE>
 __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant__ CUtensorMap xmap,
                                                            const __grid_constant__ CUtensorMap emap, const MmParams p) {
   typedef MmGeom<FMT> G;
@@ -403,7 +410,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     int before = 0;
     for (int e0 = 0; e0 < p.ne; e0 += 32) {
       const int e = e0 + lane;
-      const int c = e < p.ne ? mm_count(p, e) : 0;
+      const int c = e < p.ne ? mm_count<DENSE>(p, e) : 0;
       const int tiles = (c + MM_BM - 1) / MM_BM;
       int incl = tiles;
 #pragma unroll
@@ -467,8 +474,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
     }
     expert = lo;
     const int m_in = mt - tile_first[lo];
-    row0 = mm_base(p, lo) + m_in * MM_BM;
-    nvalid = min(MM_BM, mm_count(p, lo) - m_in * MM_BM);
+    row0 = mm_base<DENSE>(p, lo) + m_in * MM_BM;
+    nvalid = min(MM_BM, mm_count<DENSE>(p, lo) - m_in * MM_BM);
     // counts / bases come from the caller: a tile never reaches past the TOTAL_ROWS rows X and Y have
     if ((long long)row0 >= p.total_rows) { row0 = 0; nvalid = 0; }
     else nvalid = min(nvalid, (int)(p.total_rows - row0));
@@ -565,7 +572,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       locate(tile, expert, row0, nvalid, nt);
       const bool second = nt >= ntn1;
       if (second) nt -= ntn1;
-      const u8* wbase = (const u8*)(uintptr_t)mm_ptr(p, expert) + (second ? p.add2 : p.add) + (long long)nt * MM_BN * p.row_bytes;
+      const u8* wbase = (const u8*)(uintptr_t)mm_ptr<DENSE>(p, expert) + (second ? p.add2 : p.add) + (long long)nt * MM_BN * p.row_bytes;
       const int rows_here = min(MM_BN, p.nrows - nt * MM_BN);
       // the tokens of the tile's rows L, L + NL of X (a row past the tile's last takes the first row's)
       const float* xdp[128 / NL];
@@ -701,7 +708,8 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
           for (int i = 0; i < 128; ++i) {
             if (i < nvalid) {
               const float v = __uint_as_float((uint32_t)(out[i >> 1] >> (32 * (i & 1)))) * fin;
-              *ycol = p.acc ? *ycol + v : v;
+              if constexpr (DENSE) *ycol = p.acc ? *ycol + v : v;
+              else *ycol = v;
             }
             ycol += ys;
           }
@@ -728,7 +736,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       const int n = nt * MM_BN + row;
       const bool has_row = n < p.nrows;
       // the low bits of the row's address: where its blocks start inside their first word
-      const uint32_t rowlow = (uint32_t)(mm_ptr(p, expert) + (unsigned long long)(second ? p.add2 : p.add) + (unsigned long long)n * p.row_bytes);
+      const uint32_t rowlow = (uint32_t)(mm_ptr<DENSE>(p, expert) + (unsigned long long)(second ? p.add2 : p.add) + (unsigned long long)n * p.row_bytes);
       for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
         const int rs = g_kb % MM_RS;
         const bool r_ok = mbar_wait(&raw_full[rs], (uint32_t)(g_kb / MM_RS) & 1u, p.status, ST_MM_WAIT_FULL + 2, 50);
@@ -1411,9 +1419,10 @@ static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptr
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  const void* k = fmt == ILL_IQ2_XXS ? (const void*)mm_id_kernel<ILL_IQ2_XXS>
-                  : fmt == ILL_Q2_K ? (const void*)mm_id_kernel<ILL_Q2_K>
-                  : fmt == ILL_Q4_K ? (const void*)mm_id_kernel<ILL_Q4_K> : (const void*)mm_id_kernel<ILL_Q6_K>;
+  const void* k = fmt == ILL_IQ2_XXS ? (const void*)mm_id_kernel<ILL_IQ2_XXS, false>
+                  : fmt == ILL_Q2_K ? (const void*)mm_id_kernel<ILL_Q2_K, false>
+                  : fmt == ILL_Q4_K ? (one_ptr ? (const void*)mm_id_kernel<ILL_Q4_K, true> : (const void*)mm_id_kernel<ILL_Q4_K, false>)
+                                    : (one_ptr ? (const void*)mm_id_kernel<ILL_Q6_K, true> : (const void*)mm_id_kernel<ILL_Q6_K, false>);
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e);
   // The warp groups trade registers after launch; what they ask for together must fit in what the
