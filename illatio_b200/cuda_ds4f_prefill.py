@@ -108,6 +108,16 @@ def dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, s
     return sc.moe
 
 
+def dk_ffn_small(pool, norms, logits, nu, clamp, sc, **kw):
+    """DK-FFN-SMALL (src/cuda-ds4f-spec.lisp:31-132): the routed experts for a few tokens at once -- several decode
+    sequences, or the positions of a speculative run -- with the rows grouped by expert so that an expert's weights
+    are read once for all of its tokens.  The reference multiplies with its matvec kernels given COUNTS / BASES
+    (src/cuda/ds4f.cu:769-772); here the grouping and the products are the chunk driver's: the tcgen05 kernel takes
+    tiles of as few as 16 rows, and for the 2-bit expert formats it is the faster of the two forms (their matvecs
+    are bound by instructions, not by the bytes they read).  Same arguments and result as dk_ffn_routed_chunk."""
+    return dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, **kw)
+
+
 class HeadScratch:
     """The buffers of DK-FFN-HEAD-CHUNK for up to N tokens: NORM2 [n, d] floats and their Q8_0 quantization, the
     router's LOGITS [n, ne], the shared expert's gate / up [n, ff], the middle values' quantization, SOUT [n, d]."""

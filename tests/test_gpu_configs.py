@@ -96,7 +96,7 @@ def test_gated_q4k_9728x2560(oracle):
     assert a < TOL_SPEC and a < 1e-5, a
 
 
-def _check_chunk(oracle, cfg, n_tok, n_check, clamp, seed):
+def _check_chunk(oracle, cfg, n_tok, n_check, clamp, seed, driver=None):
     """One chunk of N_TOK tokens through every expert of CFG; N_CHECK sampled tokens against the oracle's
     routed-expert layer, which is given only those tokens' experts (copied back from the device)."""
     pool = MB.make_pool(cfg, seed=seed)
@@ -104,7 +104,7 @@ def _check_chunk(oracle, cfg, n_tok, n_check, clamp, seed):
     norms = torch.randn(n_tok, cfg["d"], device="cuda", generator=g)
     logits = MB.router_logits(cfg, n_tok, seed=seed + 2)
     sc = P.make_chunk_scratch(pool, n_tok, cfg["nu"])
-    moe = P.dk_ffn_routed_chunk(pool, norms, logits, cfg["nu"], clamp, sc)
+    moe = (driver or P.dk_ffn_routed_chunk)(pool, norms, logits, cfg["nu"], clamp, sc)
     torch.cuda.synchronize()
     counts = sc.counts.cpu().numpy()
     sel_d = sc.sel.cpu().numpy()
@@ -149,3 +149,24 @@ def test_c5_chunk_zipf_2048_tokens(oracle):
     assert counts.sum() == 2048 * 8 and counts.max() > 128 and checked >= 24
     assert worst < TOL_SPEC, worst
     print("c5 chunk: worst relative error %.3g over %d tokens, rows per expert max %d" % (worst, checked, counts.max()))
+
+
+def test_c5_small_batch_64_sequences(oracle):
+    """DK-FFN-SMALL at configs[4]'s decode shape: 64 sequences' tokens x top-8 of 288 experts (Zipf), rows grouped by
+    expert; twelve tokens against the oracle, and four against the one-token driver (DK-FFN-TAIL)."""
+    cfg = MB.CONFIGS["c5"]
+    worst, counts, checked = _check_chunk(oracle, cfg, 64, 12, 10.0, seed=8, driver=P.dk_ffn_small)
+    assert counts.sum() == 64 * 8 and checked >= 8
+    assert worst < TOL_SPEC, worst
+    from illatio_b200 import cuda_ds4f as M
+    pool = MB.make_pool(cfg, seed=8)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    norms = torch.randn(64, cfg["d"], device="cuda", generator=g)
+    logits = MB.router_logits(cfg, 64, seed=10)
+    sc = P.make_chunk_scratch(pool, 64, cfg["nu"])
+    moe = P.dk_ffn_small(pool, norms, logits, cfg["nu"], 10.0, sc).clone()
+    sel, w = M.route(logits, cfg["nu"], mode=2)
+    for t in (0, 17, 42, 63):
+        one, _ = M.dk_ffn_tail(pool, norms[t], sel[t], w[t], 10.0)
+        assert ((moe[t] - one).abs().max() / one.abs().max()).item() < TOL_SPEC
+    print("c5 small batch: worst relative error %.3g over %d tokens" % (worst, checked))
