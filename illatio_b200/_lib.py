@@ -72,7 +72,7 @@ SIGNATURES = {
     "ill_peer_put": (_I, [_P, _L, _P, _L, _P, _P, _I, _I, _I, _c.c_uint32, _L, _S]),
     "ill_ep_plan_dev_sync": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _c.c_uint32, _L, _S]),
     "ill_moe_sum_sync": (_I, [_I, _I, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _c.c_uint32, _L, _P, _P, _S]),
-    "ill_ep_dispatch": (_I, [_L, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _c.c_uint32, _S]),
+    "ill_ep_dispatch": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _c.c_uint32, _S]),
     "ill_ep_unpack": (_I, [_L, _I, _P, _P, _P, _P, _P, _P, _P, _S]),
 }
 

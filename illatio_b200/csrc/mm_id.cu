@@ -984,19 +984,24 @@ __global__ void __launch_bounds__(128) ep_pack_cap_kernel(int cols, long long ro
   }
 }
 
-// The whole dispatch of an expert-parallel chunk in one launch: block PLACE quantizes its token's activations
-// (Q8_K, the arithmetic of quant_q8_k_kernel: the same bits) straight into the packed row it stores into slab RANK
-// of the expert's rank (peer memory) -- the quantized token never passes through this rank's memory, and what
-// ep_pack_cap_kernel, quant_q8_k_kernel and ep_put_counts_kernel do in three launches is done in one; the first
-// blocks also store this rank's rows-per-expert into row RANK of every rank's table.  A slab that would overflow
-// raises *OVERFLOW to EPOCH (never cleared: the chunk with that number overflowed) and drops the rows past CAP.
-__global__ void __launch_bounds__(128) ep_dispatch_kernel(int cols, long long row_bytes, const float* __restrict__ x,
-                                                          const uint32_t* __restrict__ w, const unsigned* __restrict__ map,
+// The whole dispatch of an expert-parallel chunk in one launch: block T quantizes token T's activations once (Q8_K,
+// the arithmetic of quant_q8_k_kernel: the same bits) into a packed row in shared memory and stores it, for each of
+// the token's NU slots, into slab RANK of that expert's rank (peer memory) with the slot's weight appended -- the
+// quantized token never passes through this rank's memory, and what ep_pack_cap_kernel, quant_q8_k_kernel and
+// ep_put_counts_kernel do in three launches is done in one; the first blocks also store this rank's rows-per-expert
+// into row RANK of every rank's table.  A slab that would overflow raises *OVERFLOW to EPOCH (never cleared: the
+// chunk with that number overflowed) and drops the rows past CAP.
+constexpr int EP_MAX_NU = 32;
+__global__ void __launch_bounds__(128) ep_dispatch_kernel(int cols, int nu, long long row_bytes, const float* __restrict__ x,
+                                                          const uint32_t* __restrict__ w, const unsigned* __restrict__ smap,
                                                           const unsigned* __restrict__ bases, const unsigned* __restrict__ counts,
                                                           int per, int world, int cap, unsigned* __restrict__ pslot,
                                                           unsigned* __restrict__ overflow, unsigned epoch,
                                                           const unsigned long long* __restrict__ peers_rows,
                                                           const unsigned long long* __restrict__ peers_rc, int rank) {
+  extern __shared__ __align__(16) u8 srow[];  // the token's packed row (without the weight)
+  __shared__ unsigned long long dst_s[EP_MAX_NU];  // where slot s's row goes (0: dropped)
+  __shared__ uint32_t w_s[EP_MAX_NU];
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -1004,24 +1009,23 @@ __global__ void __launch_bounds__(128) ep_dispatch_kernel(int cols, long long ro
     const int i = blockIdx.x * 128 + tid;
     if (i < world * per) ((unsigned*)(uintptr_t)peers_rc[i / per])[rank * per + (i % per)] = counts[i];
   }
-  const long long place = blockIdx.x;
-  __shared__ long long slot_s;
-  __shared__ int dest_s;
-  if (tid == 0) {
+  const long long t = blockIdx.x;
+  if (tid < nu) {
+    const long long place = smap[t * nu + tid];
     int g = 0;
     while (g + 1 < world && (long long)bases[(g + 1) * per] <= place) ++g;
     const long long idx = place - (long long)bases[g * per];
-    dest_s = g;
-    if (idx >= cap) { atomicMax(overflow, epoch); slot_s = -1; pslot[place] = 0; }
-    else { slot_s = (long long)g * cap + idx; pslot[place] = (unsigned)slot_s; }
+    if (idx >= cap) { atomicMax(overflow, epoch); dst_s[tid] = 0; pslot[place] = 0; }
+    else {
+      pslot[place] = (unsigned)((long long)g * cap + idx);
+      dst_s[tid] = peers_rows[g] + (unsigned long long)(((long long)rank * cap + idx) * row_bytes);
+    }
+    w_s[tid] = w[place];
   }
-  __syncthreads();
-  if (slot_s < 0) return;
-  u8* dst = (u8*)(uintptr_t)peers_rows[dest_s] + ((long long)rank * cap + (slot_s - (long long)dest_s * cap)) * row_bytes;
-  const float* xr = x + (long long)map[place] * cols;
+  const float* xr = x + t * cols;
   const int nb = cols / 256;
-  float* dscale = (float*)(dst + cols);
-  int16_t* dsum = (int16_t*)(dst + cols + nb * 4);
+  float* dscale = (float*)(srow + cols);
+  int16_t* dsum = (int16_t*)(srow + cols + nb * 4);
   for (int b = warp; b < nb; b += 4) {
     const float4 v0 = ((const float4*)(xr + b * 256))[2 * lane], v1 = ((const float4*)(xr + b * 256))[2 * lane + 1];
     const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
@@ -1030,12 +1034,22 @@ __global__ void __launch_bounds__(128) ep_dispatch_kernel(int cols, long long ro
     q8k_values(v, lane, q, d);
     uint32_t w0, w1;
     int sum = q8k_pack(q, w0, w1);
-    ((uint2*)(dst + b * 256))[lane] = make_uint2(w0, w1);
+    ((uint2*)(srow + b * 256))[lane] = make_uint2(w0, w1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     if (!(lane & 1)) dsum[b * 16 + (lane >> 1)] = (int16_t)sum;
     if (lane == 0) dscale[b] = d;
   }
-  if (tid == 0) *(uint32_t*)(dst + cols + nb * 4 + cols / 8) = w[place];
+  __syncthreads();
+  // the packed row to each of its destinations, 16 bytes a thread at a time (rows and slabs are 16-byte aligned);
+  // the last word, after the sums, is the slot's weight
+  const int body = cols + nb * 4 + cols / 8, nv = body / 16;
+  for (int s = 0; s < nu; ++s) {
+    u8* dst = (u8*)(uintptr_t)dst_s[s];
+    if (!dst) continue;
+    for (int i = tid; i < nv; i += 128) ((uint4*)dst)[i] = ((const uint4*)srow)[i];
+    for (int i = nv * 4 + tid; i < body / 4; i += 128) ((uint32_t*)dst)[i] = ((const uint32_t*)srow)[i];
+    if (tid == 0) *(uint32_t*)(dst + body) = w_s[s];
+  }
 }
 
 // The receiving rank's plan, on the device, for exchanges of a fixed size: RC[s * per + e] = rows source s counted
@@ -1226,29 +1240,33 @@ extern "C" int ill_ep_pack_cap(int64_t rows, int cols, ill_dptr xq, ill_dptr xs,
   return launch_kernel((const void*)ep_pack_cap_kernel, dim3((unsigned)rows), dim3(128), 0, args, (cudaStream_t)stream);
 }
 
-extern "C" int ill_ep_dispatch(int64_t rows, int cols, ill_dptr x, ill_dptr w, ill_dptr map, ill_dptr bases, ill_dptr counts, int per,
-                               int world, int cap, int rank, ill_dptr peers_rows, ill_dptr peers_rc, ill_dptr pslot, ill_dptr overflow,
-                               uint32_t epoch, ill_stream stream) {
-  if (rows < 0 || cols <= 0 || cols % 256 || per < 1 || world < 1 || cap < 1 || !x || !w || !map || !bases || !counts || !peers_rows ||
-      !peers_rc || !pslot || !overflow || rank < 0 || rank >= world || epoch == 0)
+extern "C" int ill_ep_dispatch(int64_t ntok, int nu, int cols, ill_dptr x, ill_dptr w, ill_dptr smap, ill_dptr bases, ill_dptr counts,
+                               int per, int world, int cap, int rank, ill_dptr peers_rows, ill_dptr peers_rc, ill_dptr pslot,
+                               ill_dptr overflow, uint32_t epoch, ill_stream stream) {
+  if (ntok < 0 || nu < 1 || nu > EP_MAX_NU || cols <= 0 || cols % 256 || per < 1 || world < 1 || cap < 1 || !x || !w || !smap || !bases ||
+      !counts || !peers_rows || !peers_rc || !pslot || !overflow || rank < 0 || rank >= world || epoch == 0)
     return ILL_ERR_ARG;
-  if ((x & 15) || (w & 3) || (map & 3) || (bases & 3) || (counts & 3) || (pslot & 3) || (overflow & 3) || (peers_rows & 7) || (peers_rc & 7))
+  if ((x & 15) || (w & 3) || (smap & 3) || (bases & 3) || (counts & 3) || (pslot & 3) || (overflow & 3) || (peers_rows & 7) || (peers_rc & 7))
     return ILL_ERR_ALIGN;
   long long rb = ill_ep_row_bytes(cols);
+  if (rb % 16 || rb > 64 * 1024) return ILL_ERR_UNSUPPORTED;
   const float* xp = (const float*)(uintptr_t)x;
   const uint32_t* wp = (const uint32_t*)(uintptr_t)w;
-  const unsigned* mp = (const unsigned*)(uintptr_t)map;
+  const unsigned* mp = (const unsigned*)(uintptr_t)smap;
   const unsigned* bs = (const unsigned*)(uintptr_t)bases;
   const unsigned* cp = (const unsigned*)(uintptr_t)counts;
   unsigned* ps = (unsigned*)(uintptr_t)pslot;
   unsigned* ov = (unsigned*)(uintptr_t)overflow;
   const unsigned long long* pr = (const unsigned long long*)(uintptr_t)peers_rows;
   const unsigned long long* pc = (const unsigned long long*)(uintptr_t)peers_rc;
-  void* args[] = {&cols, &rb, &xp, &wp, &mp, &bs, &cp, &per, &world, &cap, &ps, &ov, &epoch, &pr, &pc, &rank};
-  long long blocks = rows;
+  void* args[] = {&cols, &nu, &rb, &xp, &wp, &mp, &bs, &cp, &per, &world, &cap, &ps, &ov, &epoch, &pr, &pc, &rank};
   const long long need = ((long long)world * per + 127) / 128;  // blocks that carry the counts
-  if (blocks < need) return ILL_ERR_UNSUPPORTED;  // fewer rows than that: use ill_ep_put_counts and ill_ep_pack_cap
-  return launch_kernel((const void*)ep_dispatch_kernel, dim3((unsigned)blocks), dim3(128), 0, args, (cudaStream_t)stream);
+  if (ntok < need) return ILL_ERR_UNSUPPORTED;  // fewer tokens than that: use ill_ep_put_counts and ill_ep_pack_cap
+  if (rb > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute((const void*)ep_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rb);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  return launch_kernel((const void*)ep_dispatch_kernel, dim3((unsigned)ntok), dim3(128), (size_t)rb, args, (cudaStream_t)stream);
 }
 
 extern "C" int ill_ep_put_counts(int world, int per, int rank, ill_dptr counts, ill_dptr peers, ill_dptr overflow,

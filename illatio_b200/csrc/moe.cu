@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(int d, int nu, long long n
                                                       const float* __restrict__ shared_, float* __restrict__ moe,
                                                       const unsigned long long* flag_peers, unsigned* flags, int world, int rank,
                                                       unsigned epoch, unsigned long long wait_ns, unsigned* status,
-                                                      const unsigned* ovf_epoch, unsigned* ovf_flag) {
+                                                      const unsigned* ovf_epoch, unsigned* ovf_flag, int vec) {
   pdl_launch_dependents();
   pdl_wait();
   // the chunk's overflow as 0 / 1: its dispatch and its plan raise OVF_EPOCH to the chunk's number
@@ -55,17 +55,41 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(int d, int nu, long long n
     const bool ok = ep_meet(flag_peers, flags, world, rank, 1, epoch, blockIdx.x == 0, wait_ns, status);
     if (!__syncthreads_and(ok)) return;
   }
-  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (gid >= ntok * d) return;
-  const long long t = gid / d;
-  const int r = (int)(gid - t * d);
-  float acc = 0.0f;
-  for (int s = 0; s < nu; ++s) {
-    long long row = map ? (long long)map[t * nu + s] : t * nu + s;
-    if (map2) row = map2[row];
-    acc = __fadd_rn(acc, flag_peers ? __ldcg(down + row * d + r) : down[row * d + r]);
+  // The blocks stride over the outputs (so that a block meets the ranks once, not once per 256 outputs); VEC: four
+  // outputs a thread from 16-byte loads.  Every output is the same chain of additions in slot order either way.
+  const long long nthr = (long long)gridDim.x * blockDim.x, tid0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec) {
+    const int d4 = d / 4;
+    for (long long gid = tid0; gid < ntok * d4; gid += nthr) {
+      const long long t = gid / d4;
+      const int r = (int)(gid - t * d4);
+      float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int s = 0; s < nu; ++s) {
+        long long row = map ? (long long)map[t * nu + s] : t * nu + s;
+        if (map2) row = map2[row];
+        const float4* src = (const float4*)(down + row * d) + r;
+        const float4 v = flag_peers ? __ldcg(src) : *src;
+        acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+      }
+      if (shared_) {
+        const float4 v = ((const float4*)shared_)[gid];
+        acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+      }
+      ((float4*)moe)[gid] = acc;
+    }
+    return;
   }
-  moe[gid] = shared_ ? __fadd_rn(acc, shared_[gid]) : acc;
+  for (long long gid = tid0; gid < ntok * d; gid += nthr) {
+    const long long t = gid / d;
+    const int r = (int)(gid - t * d);
+    float acc = 0.0f;
+    for (int s = 0; s < nu; ++s) {
+      long long row = map ? (long long)map[t * nu + s] : t * nu + s;
+      if (map2) row = map2[row];
+      acc = __fadd_rn(acc, flag_peers ? __ldcg(down + row * d + r) : down[row * d + r]);
+    }
+    moe[gid] = shared_ ? __fadd_rn(acc, shared_[gid]) : acc;
+  }
 }
 
 // ---- routing -----------------------------------------------------------------------
@@ -388,8 +412,10 @@ static int moe_sum_launch(int d, int nu, int64_t ntok, ill_dptr down, ill_dptr m
   unsigned* stw = device_status_word();
   const unsigned* oe = (const unsigned*)(uintptr_t)ovf_epoch;
   unsigned* of = (unsigned*)(uintptr_t)ovf_flag;
-  void* args[] = {&d, &nu, &nt, &dp, &mp, &m2, &sp, &op, &fp, &fl, &world, &rank, &epoch, &wn, &stw, &oe, &of};
-  long long blocks = (ntok * d + 255) / 256;
+  int vec = d % 4 == 0 && !(down & 15) && !(moe & 15) && !(shared_ & 15);
+  void* args[] = {&d, &nu, &nt, &dp, &mp, &m2, &sp, &op, &fp, &fl, &world, &rank, &epoch, &wn, &stw, &oe, &of, &vec};
+  long long blocks = (ntok * (vec ? d / 4 : d) + 255) / 256;
+  if (blocks > 16 * 148) blocks = 16 * 148;  // the blocks stride over the rest
   if (blocks < 1) blocks = 1;  // a rank without tokens still meets the others
   return launch_kernel((const void*)moe_sum_kernel, dim3((unsigned)blocks), dim3(256), 0, args, (cudaStream_t)stream);
 }

@@ -532,13 +532,13 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None, wait_ns=0)
          ptr(sc.smap), ptr(sc.wrow), st)
     me = dist.get_rank(group) if dist.is_initialized() else 0
     if sc.peers is not None:
-        # the dispatch without a collective, in one launch: every (token, slot) row is quantized straight into its
-        # packed form in the owner's slab over NVLink, and the counts go into the owners' tables; then the ranks meet
+        # the dispatch without a collective, in one launch: every token is quantized once and its packed row stored
+        # straight into the slabs of its slots' owners over NVLink, and the counts go into the owners' tables; then the ranks meet
         sc.epoch += 1
-        if rows >= (world * per + 127) // 128:
-            call("ill_ep_dispatch", rows, d, ptr(norms), ptr(sc.wrow), ptr(sc.rmap), ptr(sc.bases), ptr(sc.counts), per, world, cap,
+        if n >= (world * per + 127) // 128:
+            call("ill_ep_dispatch", n, nu, d, ptr(norms), ptr(sc.wrow), ptr(sc.smap), ptr(sc.bases), ptr(sc.counts), per, world, cap,
                  me, ptr(sc.peers_rows), ptr(sc.peers_rc), ptr(sc.pslot), ptr(sc.ovf_epoch), sc.epoch, st)
-        else:  # fewer rows than it takes blocks to carry the counts: the three steps apart
+        else:  # fewer tokens than it takes blocks to carry the counts: the three steps apart
             call("ill_quant_q8_k", ptr(norms), ptr(sc.xq), ptr(sc.xs), ptr(sc.xsum), n * d // 256, st)
             call("ill_ep_put_counts", world, per, me, ptr(sc.counts), ptr(sc.peers_rc), 0, st)
             sc.ovf1.zero_()
@@ -578,7 +578,7 @@ def chunk_capacity(ex, sc, norms, logits, n_expert_total, group=None, wait_ns=0)
              ptr(sc.lbases), pool.n_expert, tot, ptr(sc.mh), ptr(sc.me), ptr(sc.ms), 0, ptr(sc.pdst), ptr(sc.peers), d, st)
         call("ill_moe_sum_sync", d, nu, n, ptr(sc.back), ptr(sc.smap), ptr(sc.pslot), 0, ptr(sc.moe), ptr(sc.peers_flags),
              ptr(sc.flags), world, me, sc.epoch, wait_ns, ptr(sc.ovf_epoch), ptr(sc.overflow), st)
-        if rows < (world * per + 127) // 128:
+        if n < (world * per + 127) // 128:
             sc.overflow.bitwise_or_(sc.ovf1)
         return sc.moe, sc.overflow
     call("ill_moe_mm_id", pool.down_fmt, ff, d, 2 * pool.gate_bytes, ptr(pool.ptrs_all), ptr(sc.lcounts), ptr(sc.lbases),

@@ -443,19 +443,21 @@ ILL_API int ill_moe_sum_sync(int d, int nu, int64_t ntok, ill_dptr down, ill_dpt
                              ill_dptr ovf_epoch, ill_dptr ovf_flag, ill_stream stream);
 
 /* The dispatch of an expert-parallel chunk in one launch: ill_quant_q8_k, ill_ep_put_counts
- * and ill_ep_pack_cap (peer form) together.  X holds the tokens' activations as floats
- * [tokens, cols] (16-byte aligned); row PLACE (of the ROWS (token, slot) rows, in the order
- * ill_moe_group leaves them: W = its WROW, MAP = its RMAP, BASES / COUNTS its per-expert
- * tables) is quantized -- the same bits as ill_quant_q8_k -- straight into the packed row
- * stored in slab RANK of its expert's rank (PEERS_ROWS), and this rank's rows per expert go
- * into row RANK of every rank's table (PEERS_RC).  A slab too small raises *OVERFLOW to EPOCH
- * (>= 1, the chunk's number; the word is never cleared -- ill_ep_plan_dev_sync raises it the
- * same way, and ill_moe_sum_sync turns "equals this chunk's number" into 0 / 1 at *OVF_FLAG
- * when given OVF_EPOCH = this word).  Needs ROWS >= ceil(world*per / 128), else
- * ILL_ERR_UNSUPPORTED (use the three calls).  No counterpart in the reference. */
-ILL_API int ill_ep_dispatch(int64_t rows, int cols, ill_dptr x, ill_dptr w, ill_dptr map, ill_dptr bases, ill_dptr counts, int per,
-                            int world, int cap, int rank, ill_dptr peers_rows, ill_dptr peers_rc, ill_dptr pslot, ill_dptr overflow,
-                            uint32_t epoch, ill_stream stream);
+ * and ill_ep_pack_cap (peer form) together.  X holds the NTOK tokens' activations as floats
+ * [tokens, cols] (16-byte aligned).  Token t is quantized once -- the same bits as
+ * ill_quant_q8_k -- and its packed row stored, for each of its NU slots s, in slab RANK of
+ * the rank that holds the slot's expert (PEERS_ROWS), with the slot's weight: the row's
+ * place among the (token, slot) rows is SMAP[t*nu + s] and its weight W[place], as
+ * ill_moe_group leaves them (its SMAP, WROW, and its per-expert BASES / COUNTS); this rank's
+ * rows per expert go into row RANK of every rank's table (PEERS_RC).  A slab too small raises
+ * *OVERFLOW to EPOCH (>= 1, the chunk's number; the word is never cleared --
+ * ill_ep_plan_dev_sync raises it the same way, and ill_moe_sum_sync turns "equals this
+ * chunk's number" into 0 / 1 at *OVF_FLAG when given OVF_EPOCH = this word).  Needs
+ * NTOK >= ceil(world*per / 128), else ILL_ERR_UNSUPPORTED (use the three calls); NU <= 32.
+ * No counterpart in the reference. */
+ILL_API int ill_ep_dispatch(int64_t ntok, int nu, int cols, ill_dptr x, ill_dptr w, ill_dptr smap, ill_dptr bases, ill_dptr counts,
+                            int per, int world, int cap, int rank, ill_dptr peers_rows, ill_dptr peers_rc, ill_dptr pslot,
+                            ill_dptr overflow, uint32_t epoch, ill_stream stream);
 
 /* Two matrices of every expert against the same rows in one launch (gate and up:
  * W_e at PTRS[e] + ADD into Y, at PTRS[e] + ADD2 into Y2; no YMAP).  The same
