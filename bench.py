@@ -947,6 +947,15 @@ def moe_leg(D, B, EP, MB, torch, dist, dev, rank, world, cores, cfg_name, n_tok,
         flags.append(EP.chunk_capacity(ce, esc, norms_l, logits_l, ne)[1].clone())
     for _ in range(3):
         chunk()
+    if world == 1:
+        # one GPU has nothing to exchange: the timed chunk is the plain chunk driver (DK-FFN-ROUTED-CHUNK; the same bits,
+        # without the slabs' pack / plan / unpack steps) -- the same thing `vs_1gpu` is measured against at N > 1
+        sc1 = P.make_chunk_scratch(pool, n_tok, nu, device=dev)
+
+        def chunk():  # noqa: F811
+            P.dk_ffn_routed_chunk(pool, norms_l, logits_l, nu, 10.0, sc1)
+        for _ in range(2):
+            chunk()
     barrier()
     reps = 12 if n_tok >= 1024 else 40
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
