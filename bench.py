@@ -781,7 +781,7 @@ def c4_decode(D, B, torch, dev, peak):
 
 def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_over_ranks):
     """configs[2]'s output head, 151936 x 5120 Q6_K, split by rows over the ranks, then an all-gather of the logits;
-    batch 1, 4 and 16.  Two copies of the rank's slice alternate so that the weights come from HBM.  The product
+    batch 1, 4 and 16.  Copies of the rank's slice rotate so that the weights come from HBM.  The product
     and the collective are also timed apart.  Parity: the gathered logits against rank 0's product of the whole
     matrix (exact: a row's arithmetic does not depend on which rank multiplies it)."""
     rows, cols = VOCAB, 5120
@@ -794,7 +794,10 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
         s = full[first * rb:end * rb].clone()
         del full
         return D.CMat("head_slice", Q6_K, end - first, cols, s)
-    slices = [slice_of(0), slice_of(1)]
+    # as many copies of the rank's slice as it takes to exceed twice the L2 (two at N <= 2, eight at N = 8): every launch
+    # reads its weights from HBM
+    ncopies = max(2, int(-(-300e6 // ((end - first) * rb))))
+    slices = [slice_of(i) for i in range(ncopies)]
     torch.cuda.empty_cache()
     out = {"matrix": "151936 x 5120 Q6_K (638 MB)", "rows_per_gpu": end - first,
            "collective": "in-place all-gather of fp32 logits (NCCL)" if world > 1 else "none (one GPU)",
@@ -817,7 +820,7 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
         it = [0]
 
         def product_only():
-            w = slices[it[0] & 1]
+            w = slices[it[0] % ncopies]
             it[0] += 1
             D.cmat_mul(w, act, part, n)
 
@@ -833,12 +836,12 @@ def head_rowsplit(D, B, EP, torch, dist, dev, rank, world, peak, barrier, max_ov
             mine = [pg.buffer(i)[rank][:n * sl * 4].view(torch.float32) for i in (0, 1)]
 
             def both_peer():
-                i = it[0] & 1
+                i, w = it[0] & 1, slices[it[0] % ncopies]
                 it[0] += 1
                 if n == 1:   # the product stores into every rank's buffer itself and holds the meeting: one launch
-                    pg.mul_put(i, slices[i], act)
+                    pg.mul_put(i, w, act)
                 else:
-                    D.cmat_mul(slices[i], act, mine[i], n)
+                    D.cmat_mul(w, act, mine[i], n)
                     pg.put(i, n * sl * 4)
             barrier()
             us_peer = time_us(both_peer, 20, torch)
