@@ -604,6 +604,8 @@ def prefill_leg(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed, n, tpea
             for kind in ("q8", "q8k")}
     last = D.make_qact(hidden, D.matrix_act_kind(m["head"]), device=dev)
     launches = [0]
+    down_tc = D.tc_takes(m["layers"][0]["down"], n) and D.matrix_act_kind(m["layers"][0]["down"]) == "q8k"
+    mid_cf = D.ChunkF16(n, ffn, device=dev) if down_tc else None
 
     def chunk():
         h.copy_(h0)
@@ -618,8 +620,11 @@ def prefill_leg(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed, n, tpea
             a = D.rmsnorm_q8(h, L["nw2"], acts[("h", D.matrix_act_kind(L["gate"]))], hidden, EPS, n=n)
             D.cmat_mul(L["gate"], a, ga, n)
             D.cmat_mul(L["up"], a, ub, n)
-            D.swiglu(ga, ub, ga, ffn)
-            D.cmat_mul(L["down"], D.quant_q8(ga, acts[("fa", D.matrix_act_kind(L["down"]))]), h, n, acc=True)
+            if down_tc:   # SwiGLU, Q8_K and the fp16 form in one launch, straight into the tcgen05 product
+                D.cmat_mul_tc(L["down"], D.swiglu_chunk_f16(ga, ub, mid_cf), h, acc=True)
+            else:
+                D.swiglu(ga, ub, ga, ffn)
+                D.cmat_mul(L["down"], D.quant_q8(ga, acts[("fa", D.matrix_act_kind(L["down"]))]), h, n, acc=True)
         D.cmat_mul(m["head"], D.rmsnorm_q8(h[(n - 1) * hidden:], m["nwf"], last, hidden, EPS), m["logits"], 1)
     from illatio_b200 import _lib as LIB
     counted, real_call, real_status = [0], LIB.call, LIB.status

@@ -11,6 +11,7 @@
 
 #include "formats.cuh"
 #include "host.h"
+#include "quantdev.cuh"
 
 namespace ill {
 
@@ -289,31 +290,10 @@ __global__ void __launch_bounds__(256) swiglu_q8k_f16_kernel(long long nblocks, 
     if (clamp > 1e-6f) { gv = fminf(gv, clamp); uv = fmaxf(-clamp, fminf(uv, clamp)); }
     v[j] = __fmul_rn(__fmul_rn(__fmul_rn(gv, d4_sigmoid(gv)), uv), wv);
   }
-  // QUANTIZE-Q8K! (src/kquant.lisp:130-167): the largest magnitude, the first of equal ones, and its value
-  float amax = 0.0f, mx = 0.0f;
-  int idx = 0;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float a = fabsf(v[j]);
-    if (a > amax) { amax = a; mx = v[j]; idx = 8 * lane + j; }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float oa = __shfl_xor_sync(0xffffffffu, amax, o), om = __shfl_xor_sync(0xffffffffu, mx, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (oa > amax || (oa == amax && oi < idx)) { amax = oa; mx = om; idx = oi; }
-  }
+  // QUANTIZE-Q8K! (src/kquant.lisp:130-167), the quantizer kernels' own routine
   int q[8];
-  float d = 0.0f;
-  if (amax == 0.0f) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) q[j] = 0;
-  } else {
-    const float iscale = __fdiv_rn(-127.0f, mx);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) q[j] = min(127, __float2int_rn(__fmul_rn(iscale, v[j])));
-    d = __fdiv_rn(1.0f, iscale);
-  }
+  float d;
+  q8k_values(v, lane, q, d);
   uint32_t h[4];
   int s = 0;
 #pragma unroll

@@ -51,11 +51,13 @@ __device__ __forceinline__ void q8k_values(const float (&v)[8], int lane, int (&
     if (oa > amax || (oa == amax && oi < idx)) { amax = oa; mx = om; idx = oi; }
   }
   d = 0.0f;
-  if (amax == 0.0f) {
+  // A block whose largest magnitude is so small (below 3.8e-37) that -127 / max overflows is taken as zeros: the
+  // reference's arithmetic is not defined there (an infinite scale times zero), and such values add nothing.
+  const float iscale = amax == 0.0f ? 0.0f : __fdiv_rn(-127.0f, mx);
+  if (amax == 0.0f || fabsf(iscale) > 3.402823466e38f) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) q[j] = 0;
   } else {
-    const float iscale = __fdiv_rn(-127.0f, mx);
 #pragma unroll
     for (int j = 0; j < 8; ++j) q[j] = min(127, __float2int_rn(__fmul_rn(iscale, v[j])));
     d = __fdiv_rn(1.0f, iscale);

@@ -213,6 +213,23 @@ def cmat_mul_tc(w, cf, y, acc=False):
     return y
 
 
+def swiglu_chunk_f16(g, u, cf, clamp=3.0e38):
+    """silu(G) * U over a chunk's [n, ff] gate and up products, quantized to Q8_K and left in CF (a ChunkF16 of n x ff)
+    in the form the tcgen05 product takes -- the swiglu, quant_q8 and fp16 steps between a prefill chunk's up and
+    down products in one launch (ill_swiglu_q8k_f16: each step's arithmetic, bit for bit)."""
+    n, ff = cf.n, cf.cols
+    if cf.xd is None or cf.xd.numel() != n * ff // 256:
+        cf.xd = torch.empty(n * ff // 256, dtype=torch.float32, device=cf.xh.device)
+    _lib.call("ill_swiglu_q8k_f16", n, ff, float(clamp), _ptr(g), _ptr(u), 0, _ptr(cf.xh), _ptr(cf.xe), _ptr(cf.xd), 0, _stream())
+    return cf
+
+
+def tc_takes(w, n):
+    """Whether cmat_mul sends N tokens of matrix W to the tcgen05 kernel."""
+    return ((w.type == 1 or (w.type == 2 and TC_Q6K)) and n >= TC_MIN_TOKENS and w.rows >= TC_MIN_ROWS and w.rows % 4 == 0
+            and w.qs.data_ptr() % 16 == 0)
+
+
 TC_MIN_TOKENS, TC_MIN_ROWS = 64, 2048   # below these the int8 mma.sync kernel is as fast or faster
 # Q6_K on the tcgen05 path: scale * (q - 32) reaches 4064 and fp16 holds only even integers above 2048, so the kernel
 # multiplies an even part and an odd part of every product (both exact).  False keeps Q6_K chunks on the int8 kernel.

@@ -19,6 +19,7 @@
  * beyond that criterion their parity is unpinned and this restatement of the
  * source is the pin.
  */
+#include <float.h>
 #include <math.h>
 #include <pthread.h>
 #include <stdint.h>
@@ -213,13 +214,15 @@ void orc_quantize_q8k(const float* x, int64_t n, int8_t* q, float* ds, int32_t* 
     const float* xb = x + b * QK_K;
     float mx = 0.0f, amax = 0.0f;
     for (int j = 0; j < QK_K; ++j) { float v = xb[j], a = fabsf(v); if (a > amax) { amax = a; mx = v; } }
-    if (amax == 0.0f) {
+    /* also a block whose largest magnitude is so small that -127 / max overflows: the reference's arithmetic is
+     * not defined there (an infinite scale times zero); such a block is taken as zeros, as the device takes it */
+    float iscale = amax == 0.0f ? 0.0f : -127.0f / mx;
+    if (amax == 0.0f || !(fabsf(iscale) <= FLT_MAX)) {
       ds[b] = 0.0f;
       memset(q + b * QK_K, 0, QK_K);
       for (int g = 0; g < 16; ++g) bs[b * 16 + g] = 0;
       continue;
     }
-    float iscale = -127.0f / mx;
     for (int g = 0; g < 16; ++g) {
       int sum = 0;
       for (int k = 0; k < 16; ++k) {

@@ -143,3 +143,43 @@ def test_chunk_on_tcgen05_against_the_oracle(oracle, fmt):
     for t in (0, 1, 37, n - 1):
         want = oracle.matvec(fmt, wb, rows, cols, oracle.quantize_act(fmt, xh[t]))[0]
         assert np.abs(got[t] - want).max() / np.abs(want).max() < 2e-6
+
+
+def test_fused_swiglu_into_the_down_product():
+    """SwiGLU, Q8_K and the fp16 form in one launch (swiglu_chunk_f16) feed the tcgen05 down product with the same
+    bits as the three steps apart."""
+    n, ff, rows = 130, 2560, 2048
+    g = torch.Generator(device="cuda").manual_seed(5)
+    ga, ub = torch.randn(n * ff, device="cuda", generator=g), torch.randn(n * ff, device="cuda", generator=g)
+    w = D.CMat("down", B.Q6_K, rows, ff, B.synth_matrix_torch(B.Q6_K, rows, ff, seed=2))
+    assert D.tc_takes(w, n)
+    y1 = torch.zeros(n * rows, device="cuda")
+    D.cmat_mul_tc(w, D.swiglu_chunk_f16(ga, ub, D.ChunkF16(n, ff)), y1)
+    mid = torch.empty_like(ga)
+    D.swiglu(ga, ub, mid, ff)
+    y2 = torch.zeros(n * rows, device="cuda")
+    D.cmat_mul(w, D.quant_q8(mid, D.make_qact(n * ff, "q8k")), y2, n)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y1).all() and torch.equal(y1, y2)
+
+
+def test_vanishing_block_is_quantized_to_zeros(oracle):
+    """A Q8_K block whose largest magnitude is below 3.8e-37 (-127 / max overflows: the reference's arithmetic is not
+    defined there) is taken as zeros by the device quantizers and by the oracle alike -- and the fused SwiGLU step,
+    where such blocks arise (silu of a very negative gate), hands the tcgen05 product finite operands."""
+    x = np.zeros(768, np.float32)
+    x[256:512] = np.float32(1e-40) * np.arange(1, 257, dtype=np.float32)   # denormals
+    x[512:] = np.linspace(-1, 1, 256, dtype=np.float32)
+    act = D.quant_q8(to_dev(x), D.make_qact(768, "q8k"))
+    torch.cuda.synchronize()
+    q, d, bs = oracle.quantize_q8k(x)
+    assert np.array_equal(act.xq.cpu().numpy(), q) and np.array_equal(act.xs.cpu().numpy(), d)
+    assert np.array_equal(act.xsum.cpu().numpy().astype(np.int32), bs)
+    assert d[0] == 0 and d[1] == 0 and d[2] != 0 and not q[:512].any() and q[512:].any()
+    # gates of -95 (e^-95 is a denormal) against ups of one: every middle value is a denormal
+    n, ff = 64, 512
+    g = torch.full((n * ff,), -95.0, device="cuda")
+    u = torch.ones(n * ff, device="cuda")
+    cf = D.swiglu_chunk_f16(g, u, D.ChunkF16(n, ff))
+    torch.cuda.synchronize()
+    assert torch.isfinite(cf.xh.float()).all() and (cf.xh == 0).all() and (cf.xd == 0).all()
