@@ -606,6 +606,8 @@ def prefill_leg(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed, n, tpea
     launches = [0]
     down_tc = D.tc_takes(m["layers"][0]["down"], n) and D.matrix_act_kind(m["layers"][0]["down"]) == "q8k"
     mid_cf = D.ChunkF16(n, ffn, device=dev) if down_tc else None
+    L0_ = m["layers"][0]
+    glu_tc = D.tc_takes(L0_["gate"], n) and L0_["gate"].type == L0_["up"].type and D.matrix_act_kind(L0_["gate"]) == "q8k"
 
     def chunk():
         h.copy_(h0)
@@ -618,8 +620,11 @@ def prefill_leg(D, B, torch, dev, dims, layers, fmt_main, fmt_alt, seed, n, tpea
             D.cmat_mul(L["v"], a, v, n)
             D.cmat_mul(L["o"], D.quant_q8(q, acts[("q", D.matrix_act_kind(L["o"]))]), h, n, acc=True)
             a = D.rmsnorm_q8(h, L["nw2"], acts[("h", D.matrix_act_kind(L["gate"]))], hidden, EPS, n=n)
-            D.cmat_mul(L["gate"], a, ga, n)
-            D.cmat_mul(L["up"], a, ub, n)
+            if glu_tc:   # gate and up in one launch of the tcgen05 kernel
+                D.glu_mul_tc(L["gate"], L["up"], a, n, ga, ub)
+            else:
+                D.cmat_mul(L["gate"], a, ga, n)
+                D.cmat_mul(L["up"], a, ub, n)
             if down_tc:   # SwiGLU, Q8_K and the fp16 form in one launch, straight into the tcgen05 product
                 D.cmat_mul_tc(L["down"], D.swiglu_chunk_f16(ga, ub, mid_cf), h, acc=True)
             else:

@@ -68,6 +68,7 @@ SIGNATURES = {
     "ill_ep_flags_bytes": (_L, []),
     "ill_ep_barrier": (_I, [_P, _P, _I, _I, _I, _c.c_uint32, _L, _S]),
     "ill_mm_chunk": (_I, [_I, _P, _I, _I, _P, _P, _P, _L, _P, _I, _S]),
+    "ill_mm_chunk2": (_I, [_I, _P, _P, _I, _I, _P, _P, _P, _L, _P, _P, _S]),
     "ill_mv_peers": (_I, [_I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _c.c_uint32, _L, _S]),
     "ill_peer_put": (_I, [_P, _L, _P, _L, _P, _P, _I, _I, _I, _c.c_uint32, _L, _S]),
     "ill_ep_plan_dev_sync": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _c.c_uint32, _L, _S]),

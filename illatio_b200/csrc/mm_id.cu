@@ -1387,6 +1387,17 @@ extern "C" int ill_mm_chunk(int fmt, ill_dptr w, int rows, int cols, ill_dptr xh
   return mm_id_launch(fmt, cols, rows, 0, 0, 0, 0, 1, n, xh, xe, xd, 0, 0, 0, y, rows, stream, 0, 0, w, acc ? 1 : 0);
 }
 
+// two matrices of one shape against the same chunk in one launch (a gated FFN's gate and up): twice the tiles for
+// the persistent CTAs to share, so the last round of tiles is fuller than in two launches
+extern "C" int ill_mm_chunk2(int fmt, ill_dptr w, ill_dptr w2, int rows, int cols, ill_dptr xh, ill_dptr xe, ill_dptr xd, int64_t n,
+                             ill_dptr y, ill_dptr y2, ill_stream stream) {
+  if (!w || !w2 || !y || !y2 || (y2 & 15) || n < 0 || n > 0x7fffffffll) return ILL_ERR_ARG;
+  if (fmt != ILL_Q4_K && fmt != ILL_Q6_K) return ILL_ERR_UNSUPPORTED;
+  const int64_t add2 = (int64_t)(w2 - w);  // the second matrix, relative to the first (unsigned wrap-around is intended)
+  if (add2 & (fmt == ILL_Q4_K ? 15 : 3)) return ILL_ERR_ALIGN;
+  return mm_id_launch(fmt, cols, rows, 0, 0, 0, 0, 1, n, xh, xe, xd, 0, 0, 0, y, rows, stream, add2, y2, w, 0);
+}
+
 static int mm_id_launch(int fmt, int ncols, int nrows, int64_t add, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int ne,
                         int64_t total_rows, ill_dptr xh, ill_dptr xe, ill_dptr xd, ill_dptr map, ill_dptr ymap, ill_dptr ypeers,
                         ill_dptr y, int64_t y_stride, ill_stream stream, int64_t add2, ill_dptr y2, ill_dptr one_ptr, int acc) {

@@ -213,6 +213,16 @@ def cmat_mul_tc(w, cf, y, acc=False):
     return y
 
 
+def glu_mul_tc(g, u, act, n, fa, fb):
+    """The gate and up products of a gated FFN over a prefill chunk in one launch of the tcgen05 kernel
+    (ill_mm_chunk2): FA = G X, FB = U X for the chunk's Q8_K activations ACT.  Both matrices of one format and
+    shape, and large enough for tc_takes()."""
+    cf = _chunk_f16_of(act, n, g.cols)
+    _lib.call("ill_mm_chunk2", g.type, _ptr(g.qs), _ptr(u.qs), g.rows, g.cols, _ptr(cf.xh), _ptr(cf.xe), _ptr(cf.xd), n, _ptr(fa),
+              _ptr(fb), _stream())
+    return fa, fb
+
+
 def swiglu_chunk_f16(g, u, cf, clamp=3.0e38):
     """silu(G) * U over a chunk's [n, ff] gate and up products, quantized to Q8_K and left in CF (a ChunkF16 of n x ff)
     in the form the tcgen05 product takes -- the swiglu, quant_q8 and fp16 steps between a prefill chunk's up and

@@ -491,6 +491,10 @@ ILL_API int ill_moe_mm_id_peers(int fmt, int ncols, int nrows, int64_t add, ill_
  * path.  Replaces mm_q4k_mma / mm_q6k_mma (src/cuda/kquant.cu:316-466) behind CMAT-MUL-N (src/cuda-dense.lisp:250-255). */
 ILL_API int ill_mm_chunk(int fmt, ill_dptr w, int rows, int cols, ill_dptr xh, ill_dptr xe, ill_dptr xd, int64_t n, ill_dptr y,
                          int acc, ill_stream stream);
+/* The same for two matrices of one shape against the same chunk (a gated FFN's gate and up) in one launch:
+ * Y = W X, Y2 = W2 X.  Twice the tiles for the kernel's persistent CTAs to share. */
+ILL_API int ill_mm_chunk2(int fmt, ill_dptr w, ill_dptr w2, int rows, int cols, ill_dptr xh, ill_dptr xe, ill_dptr xd, int64_t n,
+                          ill_dptr y, ill_dptr y2, ill_stream stream);
 
 /* The routed experts' product for a chunk: for each expert e < NE and each row
  * `place` in [BASES[e], BASES[e] + COUNTS[e]): Y[place*y_stride + n] = W_e[n] .

@@ -183,3 +183,18 @@ def test_vanishing_block_is_quantized_to_zeros(oracle):
     cf = D.swiglu_chunk_f16(g, u, D.ChunkF16(n, ff))
     torch.cuda.synchronize()
     assert torch.isfinite(cf.xh.float()).all() and (cf.xh == 0).all() and (cf.xd == 0).all()
+
+
+@pytest.mark.parametrize("fmt", [B.Q4_K, B.Q6_K])
+def test_gate_and_up_in_one_launch(fmt):
+    """ill_mm_chunk2: two matrices against the same chunk in one launch give what two launches give, bit for bit."""
+    rows, cols, n = 2048 + 128, 1024, 200
+    wg, x, act = _case(fmt, rows, cols, n, seed=7)
+    wu = D.CMat("u", fmt, rows, cols, B.synth_matrix_torch(fmt, rows, cols, seed=8))
+    fa, fb = torch.empty(n * rows, device="cuda"), torch.empty(n * rows, device="cuda")
+    D.glu_mul_tc(wg, wu, act, n, fa, fb)
+    ya, yb = torch.empty_like(fa), torch.empty_like(fb)
+    D.cmat_mul(wg, act, ya, n)
+    D.cmat_mul(wu, act, yb, n)
+    torch.cuda.synchronize()
+    assert torch.equal(fa, ya) and torch.equal(fb, yb) and torch.isfinite(fa).all()
