@@ -67,6 +67,8 @@ SIGNATURES = {
     "ill_ep_ipc_close": (_I, [_P, _L]),
     "ill_ep_flags_bytes": (_L, []),
     "ill_ep_barrier": (_I, [_P, _P, _I, _I, _I, _c.c_uint32, _L, _S]),
+    "ill_quant_q8_k_f16": (_I, [_P, _P, _P, _P, _P, _P, _L, _S]),
+    "ill_rmsnorm_q8k_f16": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _c.c_float, _L, _S]),
     "ill_mm_chunk": (_I, [_I, _P, _I, _I, _P, _P, _P, _L, _P, _I, _S]),
     "ill_mm_chunk2": (_I, [_I, _P, _P, _I, _I, _P, _P, _P, _L, _P, _P, _S]),
     "ill_mv_peers": (_I, [_I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _c.c_uint32, _L, _S]),

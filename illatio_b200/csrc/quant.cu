@@ -24,10 +24,11 @@ __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict
   quant_block_q8_0(x[b * 32 + lane], lane, b, xq, xs, xsum, f16_scale);
 }
 
-// A warp a super-block; lane l holds elements 8l .. 8l+7.
+// A warp a super-block; lane l holds elements 8l .. 8l+7.  F16: also the block's fp16 forms (XH, XE).
+template <bool F16>
 __global__ void __launch_bounds__(256) quant_q8_k_kernel(const float* __restrict__ x, i8* __restrict__ xq,
                                                          float* __restrict__ xd, int16_t* __restrict__ bsums,
-                                                         long long nblocks) {
+                                                         long long nblocks, __half* __restrict__ xh, __half* __restrict__ xe) {
   pdl_launch_dependents();
   pdl_wait();
   const long long b = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -35,7 +36,8 @@ __global__ void __launch_bounds__(256) quant_q8_k_kernel(const float* __restrict
   if (b >= nblocks) return;
   const float4 v0 = ((const float4*)(x + b * 256))[2 * lane], v1 = ((const float4*)(x + b * 256))[2 * lane + 1];
   const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-  quant_block_q8_k(v, lane, b, xq, xd, bsums);
+  if constexpr (F16) quant_block_q8_k_f16(v, lane, b, xq, xd, bsums, xh, xe);
+  else quant_block_q8_k(v, lane, b, xq, xd, bsums);
 }
 
 // RMSNORM! (src/model.lisp:205-216) fused with the activation quantizer, as the reference's rmsnorm_q8
@@ -45,10 +47,11 @@ __global__ void __launch_bounds__(256) quant_q8_k_kernel(const float* __restrict
 // row's scale out for itself (the row comes from L2) and takes a slice of its blocks, so that one token's
 // norm is not one CTA's serial work.  The double sum is taken in the order quantdev.cuh fixes, not in the
 // CPU loop's; the two agree until the float the sum is rounded to sits within 1e-16 of a rounding boundary.
-template <int K8K>
+template <int K8K, bool F16>
 __global__ void __launch_bounds__(256) rmsnorm_q8_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                          float* __restrict__ h, i8* __restrict__ xq, float* __restrict__ xs,
-                                                         void* __restrict__ xsum, int d, float eps, int f16_scale) {
+                                                         void* __restrict__ xsum, int d, float eps, int f16_scale,
+                                                         __half* __restrict__ xh, __half* __restrict__ xe) {
   __shared__ double group_s[RMS_MAX_GROUPS];
   pdl_launch_dependents();
   pdl_wait();
@@ -76,7 +79,8 @@ __global__ void __launch_bounds__(256) rmsnorm_q8_kernel(const float* __restrict
         v[j] = __fmul_rn(__fmul_rn(xr[i], sc), w[i]);
         if (h) h[base + i] = v[j];
       }
-      quant_block_q8_k(v, lane, gb, xq, xs, (int16_t*)xsum);
+      if constexpr (F16) quant_block_q8_k_f16(v, lane, gb, xq, xs, (int16_t*)xsum, xh, xe);
+      else quant_block_q8_k(v, lane, gb, xq, xs, (int16_t*)xsum);
     } else {
       const int i = b * 32 + lane;
       const float v = __fmul_rn(__fmul_rn(xr[i], sc), w[i]);
@@ -116,23 +120,49 @@ extern "C" int ill_quant_q8_0(ill_dptr x, ill_dptr xq, ill_dptr xs, ill_dptr xsu
                        (cudaStream_t)stream);
 }
 
-extern "C" int ill_quant_q8_k(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums, int64_t nblocks,
-                              ill_stream stream) {
+static int quant_q8_k_launch(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums, int64_t nblocks, ill_dptr xh, ill_dptr xe,
+                             ill_stream stream) {
   if (nblocks < 0 || !x || !xq || !xd || !bsums) return ILL_ERR_ARG;
-  if ((x & 15) || (xq & 7) || (xd & 3) || (bsums & 1)) return ILL_ERR_ALIGN;
+  if ((x & 15) || (xq & 7) || (xd & 3) || (bsums & 1) || (xh & 15) || (xe & 15)) return ILL_ERR_ALIGN;
   if (nblocks == 0) return ILL_OK;
   const float* xp = (const float*)(uintptr_t)x;
   i8* qp = (i8*)(uintptr_t)xq;
   float* dp = (float*)(uintptr_t)xd;
   int16_t* bp = (int16_t*)(uintptr_t)bsums;
+  __half *hp = (__half*)(uintptr_t)xh, *ep = (__half*)(uintptr_t)xe;
   long long nb = nblocks;
-  void* args[] = {&xp, &qp, &dp, &bp, &nb};
-  return launch_kernel((const void*)quant_q8_k_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), 0, args,
-                       (cudaStream_t)stream);
+  void* args[] = {&xp, &qp, &dp, &bp, &nb, &hp, &ep};
+  const void* k = xh ? (const void*)quant_q8_k_kernel<true> : (const void*)quant_q8_k_kernel<false>;
+  return launch_kernel(k, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), 0, args, (cudaStream_t)stream);
 }
+
+extern "C" int ill_quant_q8_k(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums, int64_t nblocks,
+                              ill_stream stream) {
+  return quant_q8_k_launch(x, xq, xd, bsums, nblocks, 0, 0, stream);
+}
+
+extern "C" int ill_quant_q8_k_f16(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums, ill_dptr xh, ill_dptr xe, int64_t nblocks,
+                                  ill_stream stream) {
+  if (!xh || !xe) return ILL_ERR_ARG;
+  return quant_q8_k_launch(x, xq, xd, bsums, nblocks, xh, xe, stream);
+}
+
+static int rmsnorm_q8_launch(int kind, ill_dptr x, ill_dptr w, ill_dptr h, ill_dptr xq, ill_dptr xs, ill_dptr xsum, int d, float eps,
+                             int64_t n, int f16_scale, ill_dptr xh, ill_dptr xe, ill_stream stream);
 
 extern "C" int ill_rmsnorm_q8(int kind, ill_dptr x, ill_dptr w, ill_dptr h, ill_dptr xq, ill_dptr xs, ill_dptr xsum, int d,
                               float eps, int64_t n, int f16_scale, ill_stream stream) {
+  return rmsnorm_q8_launch(kind, x, w, h, xq, xs, xsum, d, eps, n, f16_scale, 0, 0, stream);
+}
+
+extern "C" int ill_rmsnorm_q8k_f16(ill_dptr x, ill_dptr w, ill_dptr h, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr xh, ill_dptr xe,
+                                   int d, float eps, int64_t n, ill_stream stream) {
+  if (!xh || !xe || (xh & 15) || (xe & 15)) return ILL_ERR_ARG;
+  return rmsnorm_q8_launch(1, x, w, h, xq, xs, xsum, d, eps, n, 0, xh, xe, stream);
+}
+
+static int rmsnorm_q8_launch(int kind, ill_dptr x, ill_dptr w, ill_dptr h, ill_dptr xq, ill_dptr xs, ill_dptr xsum, int d, float eps,
+                             int64_t n, int f16_scale, ill_dptr xh, ill_dptr xe, ill_stream stream) {
   const int bw = kind == 1 ? 256 : 32;
   if ((kind != 0 && kind != 1) || d <= 0 || d % bw || n < 0 || n > 65535 || !x || !w || !xq || !xs || (kind == 1 && !xsum))
     return ILL_ERR_ARG;
@@ -145,11 +175,13 @@ extern "C" int ill_rmsnorm_q8(int kind, ill_dptr x, ill_dptr w, ill_dptr h, ill_
   i8* qp = (i8*)(uintptr_t)xq;
   float* sp = (float*)(uintptr_t)xs;
   void* bp = (void*)(uintptr_t)xsum;
-  void* args[] = {&xp, &wp, &hp, &qp, &sp, &bp, &d, &eps, &f16_scale};
+  __half *fhp = (__half*)(uintptr_t)xh, *fep = (__half*)(uintptr_t)xe;
+  void* args[] = {&xp, &wp, &hp, &qp, &sp, &bp, &d, &eps, &f16_scale, &fhp, &fep};
   // a single row is spread over its blocks; many rows take a CTA each
   const int nb = d / bw;
   const unsigned slices = n == 1 ? (unsigned)((nb + 7) / 8) : 1u;
-  const void* k = kind == 1 ? (const void*)rmsnorm_q8_kernel<1> : (const void*)rmsnorm_q8_kernel<0>;
+  const void* k = kind == 1 ? (xh ? (const void*)rmsnorm_q8_kernel<1, true> : (const void*)rmsnorm_q8_kernel<1, false>)
+                            : (const void*)rmsnorm_q8_kernel<0, false>;
   return launch_kernel(k, dim3(slices, (unsigned)n), dim3(256), 0, args, (cudaStream_t)stream);
 }
 

@@ -5,6 +5,8 @@
 // src/kquant.lisp:130-167): IEEE division and round-half-even conversion, no fused multiply-add, the
 // first of equal maxima wins.  The output pointers may be global or shared memory.
 #pragma once
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace ill {
@@ -87,6 +89,32 @@ __device__ __forceinline__ void quant_block_q8_k(const float (&v)[8], int lane, 
   ((uint2*)(xq + b * 256))[lane] = make_uint2(w0, w1);
   s += __shfl_xor_sync(0xffffffffu, s, 1);
   if (!(lane & 1)) bsums[b * 16 + (lane >> 1)] = (int16_t)s;
+  if (lane == 0) xd[b] = d;
+}
+
+// The same, and the block's fp16 forms for the tcgen05 products beside it (what act_f16_kernel makes of the bytes):
+// XH[b*256 ..] the quants as halves, XE[b*64 ..] the sixteen sums of 16 as halves followed by 48 zeros.
+__device__ __forceinline__ void quant_block_q8_k_f16(const float (&v)[8], int lane, long long b, i8* xq, float* xd,
+                                                     int16_t* bsums, __half* xh, __half* xe) {
+  int q[8];
+  float d;
+  q8k_values(v, lane, q, d);
+  uint32_t w0, w1;
+  int s = q8k_pack(q, w0, w1);
+  ((uint2*)(xq + b * 256))[lane] = make_uint2(w0, w1);
+  uint32_t h[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const __half2 hh = __floats2half2_rn((float)q[2 * j], (float)q[2 * j + 1]);
+    h[j] = *(const uint32_t*)&hh;
+  }
+  ((uint4*)(xh + b * 256))[lane] = make_uint4(h[0], h[1], h[2], h[3]);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  if (!(lane & 1)) {
+    bsums[b * 16 + (lane >> 1)] = (int16_t)s;
+    xe[b * 64 + (lane >> 1)] = __float2half_rn((float)s);
+  }
+  if (lane < 24) ((uint32_t*)(xe + b * 64 + 16))[lane] = 0u;
   if (lane == 0) xd[b] = d;
 }
 

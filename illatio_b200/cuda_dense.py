@@ -95,6 +95,14 @@ def quant_q8(x, act, f16_scale=True):
         _lib.call("ill_quant_q8_0", _ptr(x), _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum), n // 32,
                   1 if f16_scale else 0, _stream())
     else:
+        cf = getattr(act, "_cf", None)
+        if cf is not None and cf.n * cf.cols == n:
+            # ACT's fp16 form is in use by the tcgen05 products: renewed in the same launch
+            _lib.call("ill_quant_q8_k_f16", _ptr(x), _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum), _ptr(cf.xh), _ptr(cf.xe), n // 256,
+                      _stream())
+            cf.xd = act.xs
+            act._cf_fresh = True
+            return act
         _lib.call("ill_quant_q8_k", _ptr(x), _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum), n // 256, _stream())
     act._cf_fresh = False
     return act
@@ -103,6 +111,14 @@ def quant_q8(x, act, f16_scale=True):
 def rmsnorm_q8(x, w, act, d, eps, n=1, h=None, f16_scale=True):
     """RMSNORM-Q8 (src/cuda-dense.lisp:260-264): RMSNORM! of N rows of X (D wide) by
     W, quantized into ACT in the kind it holds; H, when given, also gets the floats."""
+    cf = getattr(act, "_cf", None)
+    if act.kind == "q8k" and cf is not None and cf.n == n and cf.cols == d:
+        # ACT's fp16 form is in use by the tcgen05 products: renewed in the same launch
+        _lib.call("ill_rmsnorm_q8k_f16", _ptr(x), _ptr(w), _ptr(h), _ptr(act.xq), _ptr(act.xs), _ptr(act.xsum), _ptr(cf.xh),
+                  _ptr(cf.xe), d, float(eps), n, _stream())
+        cf.xd = act.xs
+        act._cf_fresh = True
+        return act
     _lib.call("ill_rmsnorm_q8", 1 if act.kind == "q8k" else 0, _ptr(x), _ptr(w), _ptr(h), _ptr(act.xq), _ptr(act.xs),
               _ptr(act.xsum), d, float(eps), n, 1 if f16_scale else 0, _stream())
     act._cf_fresh = False

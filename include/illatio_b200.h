@@ -122,6 +122,14 @@ ILL_API int ill_quant_q8_k(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums,
 ILL_API int ill_rmsnorm_q8(int kind, ill_dptr x, ill_dptr w, ill_dptr h, ill_dptr xq, ill_dptr xs, ill_dptr xsum, int d,
                            float eps, int64_t n, int f16_scale, ill_stream stream);
 
+/* ill_quant_q8_k / ill_rmsnorm_q8 (kind 1) that also leave the blocks' fp16 forms for the tcgen05 products, as
+ * ill_act_f16 would make them of the bytes (MAP 0): XH[n*cols] the quants as halves, XE[n*(cols/256)*64] the sums
+ * of 16 as halves, 48 of each 64 zero.  One launch where the quantizer and ill_act_f16 are two. */
+ILL_API int ill_quant_q8_k_f16(ill_dptr x, ill_dptr xq, ill_dptr xd, ill_dptr bsums, ill_dptr xh, ill_dptr xe, int64_t nblocks,
+                               ill_stream stream);
+ILL_API int ill_rmsnorm_q8k_f16(ill_dptr x, ill_dptr w, ill_dptr h, ill_dptr xq, ill_dptr xs, ill_dptr xsum, ill_dptr xh, ill_dptr xe,
+                                int d, float eps, int64_t n, ill_stream stream);
+
 /* ---- rows as floats --------------------------------------------------------- */
 
 /* OUT[i*cols ..] = row ROW_IDS[i] (int32, on the device) of the FMT matrix W

@@ -198,3 +198,32 @@ def test_gate_and_up_in_one_launch(fmt):
     D.cmat_mul(wu, act, yb, n)
     torch.cuda.synchronize()
     assert torch.equal(fa, ya) and torch.equal(fb, yb) and torch.isfinite(fa).all()
+
+
+def test_quantizers_that_also_leave_the_fp16_forms():
+    """Once an activation buffer's fp16 form is in use (a chunk went to the tcgen05 kernel), quant_q8 and rmsnorm_q8
+    renew it in their own launch: the same bytes, the same halves as ill_act_f16 makes."""
+    n, cols = 96, 2048
+    g = torch.Generator(device="cuda").manual_seed(3)
+    w = D.CMat("w", B.Q4_K, 2048, cols, B.synth_matrix_torch(B.Q4_K, 2048, cols, seed=1))
+    nw = torch.rand(cols, device="cuda", generator=g) + 0.5
+    for norm in (False, True):
+        act, ref = D.make_qact(n * cols, "q8k"), D.make_qact(n * cols, "q8k")
+        y = torch.empty(n * 2048, device="cuda")
+        outs = []
+        for it in range(2):   # first pass: the fp16 form is made by ill_act_f16; second: by the quantizer itself
+            x = torch.randn(n * cols, device="cuda", generator=g)
+            if norm:
+                D.rmsnorm_q8(x, nw, act, cols, 1e-6, n=n)
+                D.rmsnorm_q8(x, nw, ref, cols, 1e-6, n=n)
+            else:
+                D.quant_q8(x, act)
+                D.quant_q8(x, ref)
+            assert bool(getattr(act, "_cf_fresh", False)) == (it == 1)
+            D.cmat_mul(w, act, y, n)
+            fresh = D.ChunkF16(n, cols).fill(ref)     # ref never goes to the tensor-core path: plain quantizer + ill_act_f16
+            torch.cuda.synchronize()
+            assert torch.equal(act.xq, ref.xq) and torch.equal(act.xs, ref.xs) and torch.equal(act.xsum, ref.xsum)
+            assert torch.equal(act._cf.xh, fresh.xh) and torch.equal(act._cf.xe, fresh.xe)
+            outs.append(y.clone())
+        assert torch.isfinite(outs[1]).all()
