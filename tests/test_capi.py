@@ -44,3 +44,21 @@ def test_argument_checks_need_no_device():
     assert s("ill_mv", 0, 16, 4, 256, 16, 16, 0, 16, 0, 0, 0, None) == 1    # no tokens
     assert s("ill_quant_q8_k", 8, 16, 16, 16, 1, None) == 2
     assert s("ill_dequant_rows", 4, 16, 100, 0, 0, 1, 16, None) == 1
+
+
+def test_argument_checks_of_the_chunk_and_peer_entry_points():
+    s = _lib.status
+    # ill_mm_chunk: Q8_0 has no tcgen05 form; null pointers; a misaligned Q4_K matrix
+    assert s("ill_mm_chunk", 0, 16, 4, 256, 16, 16, 16, 8, 16, 0, None) == 3
+    assert s("ill_mm_chunk", 1, 0, 4, 256, 16, 16, 16, 8, 16, 0, None) == 1
+    assert s("ill_mm_chunk", 1, 24, 4, 256, 16, 16, 16, 8, 16, 0, None) == 2
+    assert s("ill_mm_chunk", 1, 16, 4, 256, 16, 0, 16, 8, 16, 0, None) == 1      # Q4_K needs the sums' tile
+    assert s("ill_mm_chunk2", 3, 16, 32, 4, 256, 16, 16, 16, 8, 16, 32, None) == 3
+    assert s("ill_mm_chunk2", 1, 16, 24, 4, 256, 16, 16, 16, 8, 16, 32, None) == 2  # the second matrix 8 bytes off
+    # the peer-storing product and the all-gather by peer stores
+    assert s("ill_mv_peers", 2, 16, 4, 256, 16, 16, 16, 0, 0, 0, 16, 16, 2, 0, 2, 1, 0, None) == 1      # no table of buffers
+    assert s("ill_mv_peers", 2, 16, 4, 256, 16, 16, 16, 16, 0, 0, 16, 16, 2, 2, 2, 1, 0, None) == 1     # rank >= world
+    assert s("ill_peer_put", 16, 64, 16, 0, 16, 16, 65, 0, 2, 1, 0, None) == 1                          # more ranks than flags
+    assert s("ill_peer_put", 18, 64, 16, 0, 16, 16, 2, 0, 2, 1, 0, None) == 2                           # SRC not a multiple of 4
+    assert s("ill_ep_dispatch", 4, 33, 256, 16, 16, 16, 16, 16, 1, 2, 8, 0, 16, 16, 16, 16, 1, None) == 1   # more than 32 slots
+    assert s("ill_quant_q8_k_f16", 16, 16, 16, 16, 0, 16, 1, None) == 1
