@@ -16,10 +16,11 @@
 namespace ill {
 
 // D4-SIGMOID (src/ds4f.lisp:248-250), each step rounded as written.
+// (One exponential and one division whatever the sign -- 1 / (1 + e^-x) for x >= 0, e^x / (1 + e^x) below, both with
+// e = exp(-|x|) -- so that a warp whose lanes differ in sign does not run both branches one after the other.)
 __device__ __forceinline__ float d4_sigmoid(float x) {
-  if (x >= 0.0f) return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x)));
-  const float e = expf(x);
-  return __fdiv_rn(e, __fadd_rn(1.0f, e));
+  const float e = expf(-fabsf(x));
+  return __fdiv_rn(x >= 0.0f ? 1.0f : e, __fadd_rn(1.0f, e));
 }
 
 // MID[r*ff + j] = silu(min(G, c)) * clamp(U, +-c) * W[r]  (src/ds4f.lisp:1016-1019)
