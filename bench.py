@@ -1000,10 +1000,20 @@ def moe_leg(D, B, EP, MB, torch, dist, dev, rank, world, cores, cfg_name, n_tok,
                         "unit": "TFLOP/s per GPU, whole chunk (products and all the steps around them)",
                         "frac": flop / ms / 1e9 / world / tpeak}}
     if n_tok < 1024:
-        out["note"] = ("batched decode run through the chunk driver (tensor-core products on few rows an expert); the "
-                       "matvec-path form with counts / bases (DK-FFN-SMALL, src/cuda-ds4f-spec.lisp:31-132) is not built: the 2-bit "
-                       "matvecs are bound by instructions (0.24 / 0.62 of HBM on large matrices), the chunk kernel reads an "
-                       "expert's weights once for all its tokens")
+        out["note"] = ("batched decode (DK-FFN-SMALL, src/cuda-ds4f-spec.lisp:31-132) through the chunk driver: tensor-core "
+                       "products on the few rows an expert has, its weights read and unpacked once for all of them")
+        if world == 1:
+            # the same batch on the one-token kernels, an expert's rows next to each other (ill_moe_row_ptrs): the form the
+            # reference runs, here the slower one (the 2-bit matvecs are bound by instructions, a row at a time)
+            sc2 = P.make_chunk_scratch(pool, n_tok, nu, device=dev)
+
+            def small_mv():
+                P.dk_ffn_small_mv(pool, norms_l, logits_l, nu, 10.0, sc2)
+            mv_us = time_us(small_mv, 20, torch)
+            same = bool(torch.allclose(sc2.moe, sc1.moe, rtol=0, atol=2e-3 * float(sc1.moe.abs().max())))
+            out["matvec_path"] = {"ms_per_chunk": mv_us / 1e3, "tok_per_s": n_tok / mv_us * 1e6, "launches": 9,
+                                  "agrees_with_chunk_driver": same,
+                                  "how": "route, group, row pointers, gather, Q8_K, ill_moe_glu, Q8_K, ill_moe_mv, sum"}
     got_l = esc.moe.clone()
     sel_l = esc.sel.clone()
     # ---- parity: 8 of this rank's tokens against the CPU oracle, which is given those tokens' experts only

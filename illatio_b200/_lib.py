@@ -51,6 +51,7 @@ SIGNATURES = {
     "ill_moe_group_scratch_bytes": (_L, [_L, _I]),
     "ill_moe_group": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _S]),
     "ill_moe_group_static": (_I, [_L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _S]),
+    "ill_moe_row_ptrs": (_I, [_I, _P, _P, _P, _L, _P, _S]),
     "ill_gather_rows": (_I, [_L, _L, _P, _P, _P, _S]),
     "ill_act_f16": (_I, [_L, _I, _P, _P, _P, _P, _P, _S]),
     "ill_moe_mm_id": (_I, [_I, _I, _I, _L, _P, _P, _P, _I, _L, _P, _P, _P, _P, _P, _P, _L, _S]),

@@ -326,6 +326,26 @@ __global__ void __launch_bounds__(256) gather_rows4_kernel(long long rows, int r
   dst[gid] = src[(long long)map[r] * row_words + j];
 }
 
+// ROW_PTRS[place] = PTRS[e] for every place of expert e (block e), so that the one-token kernels, which take an
+// expert per row, run an expert's rows one after the other; block NE gives the places past the last expert's
+// (rows the grouping left out) expert 0's matrix: their products are computed and never read.
+__global__ void __launch_bounds__(128) row_ptrs_kernel(int ne, const unsigned long long* __restrict__ ptrs,
+                                                       const unsigned* __restrict__ counts, const unsigned* __restrict__ bases,
+                                                       long long total_rows, unsigned long long* __restrict__ row_ptrs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = blockIdx.x;
+  if (e < ne) {
+    const unsigned long long pe = ptrs[e];
+    const long long b = bases[e], c = counts[e];
+    for (long long i = threadIdx.x; i < c; i += blockDim.x)
+      if (b + i < total_rows) row_ptrs[b + i] = pe;
+  } else {
+    const unsigned long long p0 = ptrs[0];
+    for (long long i = (long long)bases[ne - 1] + counts[ne - 1] + threadIdx.x; i < total_rows; i += blockDim.x) row_ptrs[i] = p0;
+  }
+}
+
 // One block a segment (rows of one expert from one source): arrival index <-> place of each row.
 __global__ void __launch_bounds__(128) ep_plan_rows_kernel(const int* __restrict__ seg_arrival, const int* __restrict__ seg_place,
                                                            const int* __restrict__ seg_len, unsigned* __restrict__ p2r,
@@ -701,6 +721,21 @@ extern "C" int ill_swiglu_q8k_f16(int64_t rows, int ff, float clamp, ill_dptr g,
   void* args[] = {&nb, &ff, &clamp, &gp, &up, &wp, &hp, &ep, &sp, &rd};
   return launch_kernel((const void*)swiglu_q8k_f16_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, args,
                        (cudaStream_t)stream);
+}
+
+extern "C" int ill_moe_row_ptrs(int ne, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int64_t total_rows, ill_dptr row_ptrs,
+                                ill_stream stream) {
+  if (ne < 1 || ne > 65535 || total_rows < 0 || !check_ptr(ptrs, 8) || !check_ptr(counts, 4) || !check_ptr(bases, 4) ||
+      !check_ptr(row_ptrs, 8))
+    return ILL_ERR_ARG;
+  if (total_rows == 0) return ILL_OK;
+  const unsigned long long* pp = (const unsigned long long*)(uintptr_t)ptrs;
+  const unsigned* cp = (const unsigned*)(uintptr_t)counts;
+  const unsigned* bp = (const unsigned*)(uintptr_t)bases;
+  long long tr = total_rows;
+  unsigned long long* rp = (unsigned long long*)(uintptr_t)row_ptrs;
+  void* args[] = {&ne, &pp, &cp, &bp, &tr, &rp};
+  return launch_kernel((const void*)row_ptrs_kernel, dim3((unsigned)ne + 1), dim3(128), 0, args, (cudaStream_t)stream);
 }
 
 extern "C" int ill_gather_rows(int64_t rows, int64_t row_bytes, ill_dptr src, ill_dptr map, ill_dptr dst,

@@ -118,6 +118,34 @@ def dk_ffn_small(pool, norms, logits, nu, clamp, sc, **kw):
     return dk_ffn_routed_chunk(pool, norms, logits, nu, clamp, sc, **kw)
 
 
+def dk_ffn_small_mv(pool, norms, logits, nu, clamp, sc, mode=2, bias=None, scale=1.0, shared=None):
+    """DK-FFN-SMALL on the matvec path, as the reference runs it (src/cuda-ds4f-spec.lisp:82-97): the rows grouped by
+    expert, the tokens' FFN inputs gathered row by row (d4_gather_rows), then the one-token kernels with an expert's
+    rows next to each other -- ill_moe_glu (gate, up, SwiGLU and the routing weight in one launch), the middle values'
+    Q8_K, ill_moe_mv for down -- and the sum in slot order.  Same arguments and result as dk_ffn_routed_chunk (whose
+    scratch it uses, plus a table of a pointer a row and the gathered rows, made on first use)."""
+    n, d = norms.shape
+    ff, ne = pool.ff, pool.n_expert
+    st = _stream()
+    if not hasattr(sc, "row_ptrs"):
+        sc.row_ptrs = torch.empty(sc.rows, dtype=torch.int64, device=norms.device)
+        sc.xrows = torch.empty(sc.rows, d, dtype=torch.float32, device=norms.device)
+        sc.xrowq = D.make_qact(sc.rows * d, "q8k", device=norms.device)
+    _lib.call("ill_moe_route", ne, nu, mode, float(scale), n, _ptr(logits), _ptr(bias), _ptr(sc.sel), _ptr(sc.w), st)
+    _lib.call("ill_moe_group", sc.rows, ne, nu, _ptr(sc.sel), _ptr(sc.w), _ptr(sc.group), _ptr(sc.counts),
+              _ptr(sc.bases), _ptr(sc.rmap), _ptr(sc.smap), _ptr(sc.wrow), st)
+    _lib.call("ill_moe_row_ptrs", ne, _ptr(pool.ptrs_all), _ptr(sc.counts), _ptr(sc.bases), sc.rows, _ptr(sc.row_ptrs), st)
+    _lib.call("ill_gather_rows", sc.rows, 4 * d, _ptr(norms), _ptr(sc.rmap), _ptr(sc.xrows), st)
+    D.quant_q8(sc.xrows, sc.xrowq)
+    _lib.call("ill_moe_glu", pool.gate_fmt, d, ff, 0, pool.gate_bytes, _ptr(sc.row_ptrs), sc.rows, _ptr(sc.xrowq.xq),
+              _ptr(sc.xrowq.xs), _ptr(sc.xrowq.xsum), 1, float(clamp), _ptr(sc.wrow), _ptr(sc.mid), ff, st)
+    D.quant_q8(sc.mid, sc.midq)
+    _lib.call("ill_moe_mv", pool.down_fmt, ff, d, 2 * pool.gate_bytes, _ptr(sc.row_ptrs), sc.rows, _ptr(sc.midq.xq),
+              _ptr(sc.midq.xs), _ptr(sc.midq.xsum), 1, _ptr(sc.down), d, st)
+    _lib.call("ill_moe_sum", d, nu, n, _ptr(sc.down), _ptr(sc.smap), _ptr(shared), _ptr(sc.moe), st)
+    return sc.moe
+
+
 class HeadScratch:
     """The buffers of DK-FFN-HEAD-CHUNK for up to N tokens: NORM2 [n, d] floats and their Q8_0 quantization, the
     router's LOGITS [n, ne], the shared expert's gate / up [n, ff], the middle values' quantization, SOUT [n, d]."""

@@ -305,6 +305,15 @@ ILL_API int64_t ill_moe_group_scratch_bytes(int64_t rows, int ne);
 ILL_API int ill_moe_group(int64_t rows, int ne, int nu, ill_dptr sel, ill_dptr w, ill_dptr scratch, ill_dptr counts,
                           ill_dptr bases, ill_dptr rmap, ill_dptr smap, ill_dptr wrow, ill_stream stream);
 
+/* ROW_PTRS[place] = PTRS[e] for every place of expert e < NE as ill_moe_group counted them (COUNTS, BASES; TOTAL_ROWS
+ * places in all): the table ill_moe_glu / ill_moe_mv take with NZ = TOTAL_ROWS and X_PER_EXPERT = 1, so that the
+ * one-token kernels multiply a few tokens' rows expert by expert, an expert's rows next to each other (its weights
+ * come from HBM once, the other rows find them in L2).  The several-token form of the routed experts on the matvec
+ * path: DK-FFN-SMALL (src/cuda-ds4f-spec.lisp:31-132), whose d4_mv_iq2_xxs / d4_mv_q2_k take the same COUNTS and
+ * BASES (src/cuda/ds4f.cu:769-772, 837).  Places past the last expert's get expert 0's matrix. */
+ILL_API int ill_moe_row_ptrs(int ne, ill_dptr ptrs, ill_dptr counts, ill_dptr bases, int64_t total_rows, ill_dptr row_ptrs,
+                             ill_stream stream);
+
 /* ill_moe_group for callers that cannot allocate device memory and have none
  * to spare for scratch: a host whose whole device budget is committed at
  * start-up (illatio sizes its expert pool to all the memory that is left and

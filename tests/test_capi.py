@@ -62,3 +62,7 @@ def test_argument_checks_of_the_chunk_and_peer_entry_points():
     assert s("ill_peer_put", 18, 64, 16, 0, 16, 16, 2, 0, 2, 1, 0, None) == 2                           # SRC not a multiple of 4
     assert s("ill_ep_dispatch", 4, 33, 256, 16, 16, 16, 16, 16, 1, 2, 8, 0, 16, 16, 16, 16, 1, None) == 1   # more than 32 slots
     assert s("ill_quant_q8_k_f16", 16, 16, 16, 16, 0, 16, 1, None) == 1
+    # the table of a pointer a row for the one-token kernels: no experts, a misaligned table
+    assert s("ill_moe_row_ptrs", 0, 16, 16, 16, 8, 16, None) == 1
+    assert s("ill_moe_row_ptrs", 4, 16, 16, 16, 8, 20, None) == 1
+    assert s("ill_moe_row_ptrs", 4, 16, 16, 16, 0, 16, None) == 0   # no rows: nothing to do

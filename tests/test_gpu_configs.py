@@ -170,3 +170,26 @@ def test_c5_small_batch_64_sequences(oracle):
         one, _ = M.dk_ffn_tail(pool, norms[t], sel[t], w[t], 10.0)
         assert ((moe[t] - one).abs().max() / one.abs().max()).item() < TOL_SPEC
     print("c5 small batch: worst relative error %.3g over %d tokens" % (worst, checked))
+
+
+def test_c5_small_batch_matvec_path(oracle):
+    """DK-FFN-SMALL on the one-token kernels (ill_moe_row_ptrs: an expert's rows next to each other): the same 64 x
+    top-8 batch against the oracle, and token by token the very bits of the one-token driver (DK-FFN-TAIL), whose
+    kernels and order of sums it shares."""
+    cfg = MB.CONFIGS["c5"]
+    worst, counts, checked = _check_chunk(oracle, cfg, 64, 12, 10.0, seed=8, driver=P.dk_ffn_small_mv)
+    assert counts.sum() == 64 * 8 and checked >= 8
+    assert worst < TOL_SPEC, worst
+    from illatio_b200 import cuda_ds4f as M
+    pool = MB.make_pool(cfg, seed=8)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    norms = torch.randn(64, cfg["d"], device="cuda", generator=g)
+    logits = MB.router_logits(cfg, 64, seed=10)
+    sc = P.make_chunk_scratch(pool, 64, cfg["nu"])
+    moe = P.dk_ffn_small_mv(pool, norms, logits, cfg["nu"], 10.0, sc).clone()
+    sel, w = M.route(logits, cfg["nu"], mode=2)
+    for t in (0, 17, 42, 63):
+        one, _ = M.dk_ffn_tail(pool, norms[t], sel[t], w[t], 10.0)
+        assert torch.equal(moe[t], one), (t, (moe[t] - one).abs().max().item())
+    assert D.device_status() == 0
+    print("c5 small batch, matvec path: worst relative error %.3g over %d tokens" % (worst, checked))
