@@ -492,13 +492,13 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
         for (int kb = 0; kb < nkb && ok; ++kb, ++g_kb) {
           for (int j = 0; j < 4; ++j, ++g_st) {
             const int s = g_st % NX;
-            if (g_st >= NX && !mbar_wait(&kempty[s], (uint32_t)(g_st / NX - 1) & 1u, p.status, ST_MM_WAIT_EMPTY, 100)) { ok = false; break; }
+            if (g_st >= NX && !mbar_wait(&kempty[s], (uint32_t)(g_st / NX - 1) & 1u, p.status, ST_MM_WAIT_EMPTY, 0)) { ok = false; break; }
             mbar_expect_tx(&kfull[s], MM_TILE_BYTES);
             tma_load_2d(x_tiles + s * MM_TILE_BYTES, &xmap, kb * 256 + j * MM_BK, row0, &kfull[s]);
           }
           if (KM && ok) {
             const int sm = g_kb & 1;
-            if (g_kb >= 2 && !mbar_wait(&mempty[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 100)) { ok = false; break; }
+            if (g_kb >= 2 && !mbar_wait(&mempty[sm], (uint32_t)((g_kb >> 1) - 1) & 1u, p.status, ST_MM_WAIT_EMPTY + 3, 0)) { ok = false; break; }
             mbar_expect_tx(&mfull[sm], MM_TILE_BYTES);
             tma_load_2d(e_tiles + sm * MM_TILE_BYTES, &emap, kb * MM_BK, row0, &mfull[sm]);  // the sums of 16
           }
@@ -621,7 +621,7 @@ __global__ void __launch_bounds__(MM_THREADS) mm_id_kernel(const __grid_constant
       for (int i = 0; i < 64; ++i) out[i] = 0ull;
       for (int kb = 0; kb < nkb; ++kb, ++d_kb) {
         const int b = d_kb & 1;
-        const bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC, 100);
+        const bool e_ok = mbar_wait(&acc_full[b], (uint32_t)(d_kb / 2) & 1u, p.status, ST_MM_WAIT_ACC, 0);
         if (!__all_sync(0xffffffffu, e_ok)) { ok = false; break; }
         tc_fence_after();
         // Two fp32 at a time (fma.rn.f32x2: each half rounds as the scalar instruction does).
